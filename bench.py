@@ -1,0 +1,317 @@
+#!/usr/bin/env python
+"""Benchmark of the fused decode-in-matmul over a QVB8 linear stack.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layers L] [--rows M]
+
+Metric: compressed-weight bytes streamed per second at M = 1 (GB/s, the packs' own bytes: bit-packed ids + per-row
+metadata + escape entries), over the 9B-class dense decoder linear stack (32 layers: q/k/v/o 4096->4096/1024/1024/
+4096, gate/up 4096->12288, down 12288->4096; weights N(0, 0.02) with 0.1% +-10 sigma outliers, QVB8 tau = 1e-3,
+seeded).  One step = one pass over every projection of every layer = one decode token.
+
+  value   whole-job GB/s with the activations resident in HBM (CUDA-graph replay, CUDA events, max over ranks)
+  e2e     the same through LinearStack.step_host: pinned host activations -> device, the step, outputs -> host
+  N > 1   every projection is sharded by output rows over the ranks (column parallel) and the outputs are
+          all-gathered over NCCL after each layer; total bytes stay fixed ("strong" scaling)
+
+--impl reference times the CPU path the reference itself would run for this op (it ships no CPU GEMV): restore the
+pack to bf16 weights, then torch.matmul on the host cores -- here through the CPU oracle's restatement of the
+reference decoder, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "compressed_weight_stream_m1"
+UNIT = "GB/s"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as fh:
+            d = json.load(fh)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int, period: float = 0.05):
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {}
+        for n in ("HwSlowdown", "HwThermalSlowdown", "SwThermalSlowdown", "SwPowerCap", "HwPowerBrakeSlowdown"):
+            v = getattr(nv, "nvmlClocksEventReason" + n, None) or getattr(nv, "nvmlClocksThrottleReason" + n, None)
+            if v is not None:
+                names[int(v)] = n
+        get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                if get is not None:
+                    r = int(get(self.h))
+                    for bit, n in names.items():
+                        if r & bit:
+                            self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        def snake(n):
+            return "".join("_" + c.lower() if c.isupper() else c for c in n).lstrip("_")
+        return {"sm_mhz": int(statistics.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(snake(r) for r in self.reasons), "samples": len(self.samples)}
+
+
+def cpu_reference_step(sample, threads: int):
+    """One bounded CPU sample: restore each pack of `sample` to bf16 with the oracle's restatement of the reference
+    decoder, then torch.matmul with the bf16 activation on the host cores.  Returns bytes processed."""
+    import numpy as np
+    import oracle
+    nbytes = 0
+    for pk, x in sample:
+        bits = oracle.decode_16(pk["ids"], pk["nbits"], pk["bit_off"], pk["min_s"], pk["tau_s"], pk["Q"], pk["P"],
+                                pk["esc_idx"], pk["esc_vals"], "bf16")
+        W = torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16)
+        y = torch.matmul(x, W.t())
+        nbytes += pk["bytes"]
+        del W, y
+    return nbytes
+
+
+def build_cpu_sample(cfg, rows_cap: int = 4096):
+    """The first layer's q/k/v/o packs of the workload (seeded as on the GPU), on the host, as oracle dicts."""
+    from qvb8_b200 import synth
+    sample = []
+    for j, (name, Q, P, _) in enumerate(cfg.projections()[:4]):
+        pk = synth.synth_pack(min(Q, rows_cap), P, 1000 * cfg.config_id + j, tau=cfg.tau)
+        d = dict(Q=pk.Q, P=pk.P, ids=pk.ids.numpy(), nbits=pk.nbits.numpy(), bit_off=pk.bit_off.numpy(),
+                 min_s=pk.min_s.numpy(), tau_s=pk.tau_s.numpy(), esc_idx=pk.esc_idx.numpy(),
+                 esc_vals=pk.esc_vals.numpy(), bytes=pk.weight_bytes())
+        x = synth.synth_activation(1, P, seed=7)
+        sample.append((d, x))
+    return sample
+
+
+def run_reference_arm(args, cfg):
+    """CPU arm: rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    threads = oracle.num_threads()
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    sample = build_cpu_sample(cfg)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_reference_step(sample, threads)
+    t0 = time.perf_counter()
+    nbytes = 0
+    for _ in range(args.steps):
+        nbytes += cpu_reference_step(sample, threads)
+    dt = time.perf_counter() - t0
+    gbs = nbytes / dt / 1e9
+    desc = "layer-0 q,k,v,o packs of the workload (4096x4096, 2x 1024x4096, 4096x4096), M=1, per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{cfg.name} linear stack, decode M=1 (CPU sample)", "sample": desc},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="9b-dense")
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--rows", type=int, default=1, help="activation rows M (1 = decode)")
+    ap.add_argument("--policy", default="escape_outliers")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    from qvb8_b200 import stack as S
+    cfg = S.CONFIGS[args.config]
+    if args.impl == "reference":
+        run_reference_arm(args, cfg)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the kernels have no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    from qvb8_b200 import lib
+    lib.load()
+    t_build = time.perf_counter()
+    st = S.LinearStack(cfg, args.rows, dev, layers=args.layers, rank=rank, world=world, policy=args.policy)
+    torch.cuda.synchronize(dev)
+    t_build = time.perf_counter() - t_build
+
+    gather = None
+    if world > 1:
+        # column-parallel shard boundary: every rank needs the full activation of the next block
+        gather = [[torch.empty((world, *t.shape), dtype=t.dtype, device=dev) for t in row] for row in st.y]
+
+    def one_step():
+        st.step()
+        if world > 1:
+            for row, grow in zip(st.y, gather):
+                for t, gt in zip(row, grow):
+                    dist.all_gather_into_tensor(gt, t)
+
+    st.capture()
+    for _ in range(args.warmup):
+        one_step()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        torch.cuda.synchronize(dev)
+        ev0.record()
+        for _ in range(args.steps):
+            one_step()
+        ev1.record()
+        torch.cuda.synchronize(dev)
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        tot = torch.tensor([st.compressed_bytes, st.n_weights, st.launches_per_step], device=dev, dtype=torch.int64)
+        dist.all_reduce(tot)
+        total_bytes, total_weights, launches = (int(v) for v in tot.tolist())
+    else:
+        total_bytes, total_weights, launches = st.compressed_bytes, st.n_weights, st.launches_per_step
+    ms_step = ms / args.steps
+    gbs = total_bytes / (ms_step * 1e-3) / 1e9
+
+    # end to end through the host-buffer API
+    for _ in range(3):
+        st.step_host()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        st.step_host()
+        if world > 1:
+            for row, grow in zip(st.y, gather):
+                for t, gt in zip(row, grow):
+                    dist.all_gather_into_tensor(gt, t)
+            torch.cuda.synchronize(dev)
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_gbs = total_bytes / e2e_s / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peaks()
+    per_launch_bytes = total_bytes / world / (cfg.layers if args.layers is None else args.layers) / 7
+    line = {
+        "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {
+            "workload": f"{cfg.name} linear stack ({st.layers} layers x q,k,v,o,gate,up,down), decode M={args.rows}, "
+                        f"QVB8 tau={cfg.tau}, policy={args.policy}",
+            "weights": total_weights, "compressed_bytes": total_bytes,
+            "bits_per_weight": 8.0 * total_bytes / max(1, total_weights),
+            "row_width_hist": {str(k): v for k, v in sorted(st.width_hist.items())}, "escapes": st.n_escapes,
+            "parallelism": f"column-parallel x{world}" if world > 1 else "single GPU",
+            "l2": "working set (packs) far larger than L2; every step streams all of it",
+            "tokens_per_s": 1e3 / ms_step * args.rows, "pack_build_s": round(t_build, 1),
+        },
+        "clocks": clocks.summary(),
+        "e2e": {"value": e2e_gbs, "unit": UNIT, "h2d_bytes_per_step": st.h2d_bytes(), "d2h_bytes_per_step": st.d2h_bytes(),
+                "ms_per_step": e2e_s * 1e3},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "small_m_kernel",
+                     "bytes_per_launch_avg": per_launch_bytes,
+                     "note": "achieved = compressed bytes of one rank's stack / step time (all launches of the step, "
+                             "gaps included)"},
+    }
+    if world == 1:
+        import oracle
+        threads = oracle.num_threads()
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
+        sample = build_cpu_sample(cfg)
+        cpu_reference_step(sample, threads)
+        t0 = time.perf_counter()
+        nb = 0
+        reps = 0
+        while time.perf_counter() - t0 < args.cpu_seconds:
+            nb += cpu_reference_step(sample, threads)
+            reps += 1
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": nb / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"layer-0 q,k,v,o packs, M=1, restore to bf16 (C restatement of the reference "
+                                          f"decoder, OpenMP) + torch.matmul on CPU, {reps} repetitions in {dt:.1f} s"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,91 @@
+/*
+ * qvb8_b200 -- C ABI of the B200 (sm_100a) kernels for the fused decode-in-matmul over QVB8 / QVB8R weight packs.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, launches on that stream on the CURRENT
+ * device and returns a status code; nothing here allocates, synchronises the host or keeps state between calls.
+ * A non-zero return leaves a message retrievable with qvb8_last_error() (thread-local).  Preconditions are
+ * checked on the host and rejected with a status -- the kernels contain no trap or assert.
+ *
+ * Each declaration names the entry point of the reference's pybind extensions that it replaces (paths below
+ * src/qv_band/ of the reference project).
+ */
+#ifndef QVB8_B200_H
+#define QVB8_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QVB8_OK 0
+#define QVB8_ERR_ARG 1      /* a null pointer, a size out of range, an unsupported dtype code            */
+#define QVB8_ERR_ALIGN 2    /* a pointer the kernels need aligned is not                                  */
+#define QVB8_ERR_SCRATCH 3  /* scratch buffer missing or smaller than the *_scratch_bytes() figure        */
+#define QVB8_ERR_CUDA 4     /* the CUDA runtime reported an error at launch                               */
+#define QVB8_ERR_DEVICE 5   /* the current device is not compute capability 10.x                          */
+
+/* element type codes for activations and dense outputs */
+#define QVB8_F16 0
+#define QVB8_BF16 1
+#define QVB8_F32 2
+
+/* One QVB8 tensor resident in device memory, exactly the buffers the reference's QVBandLinearV8 holds
+ * (formats/qvb8/module.py:87-116).
+ *   ids        bit-packed ids, LSB-first, row q starting at bit bit_off[q], each id nbits[q] wide; the
+ *              buffer ends with at least 8 readable pad bytes (formats/qvb8/decode.py:303-306)
+ *   ids_bytes  size of that buffer INCLUDING the pad
+ *   min_s,tau_s   per-row origin and step: value = fma((float)id, tau_s[q], min_s[q])
+ *   esc_idx    flat positions q*P+c of the escapes, ascending; esc_vals their exact values              */
+typedef struct qvb8_pack {
+    const uint8_t *ids;
+    int64_t ids_bytes;
+    const float *min_s;
+    const float *tau_s;
+    const uint8_t *nbits;
+    const int64_t *bit_off;
+    int64_t Q;
+    int64_t P;
+    const int64_t *esc_idx;
+    const float *esc_vals;
+    int64_t n_esc;
+} qvb8_pack;
+
+/* Message of the last failing call on this thread ("" if none). */
+const char *qvb8_last_error(void);
+
+/* Library version string. */
+const char *qvb8_version(void);
+
+/* Dense restore W[q, c] = T(fma(id, tau_s, min_s)), one rounding to the output type, escapes narrowed the same
+ * way and written over their positions.  out is (Q, P) row-major of out_dtype (QVB8_F16 / QVB8_BF16 / QVB8_F32).
+ * Replaces `decode` and `decode_bf16` (formats/qvb8/backends/cuda_qvb8/qvb8_cuda.cu:651-699, 1711-1727; kernels
+ * :535-625); the F32 form is the un-narrowed value the GEMV multiplies (:346-353). */
+int qvb8_decode(const qvb8_pack *w, int out_dtype, void *out, void *stream);
+
+/* Bytes of scratch qvb8_small_m needs for these sizes (0 is possible).  The scratch must be zero-filled once
+ * when it is allocated; the kernel leaves it in a reusable state.  Calls that share one scratch buffer must not
+ * overlap on the device. */
+int64_t qvb8_small_m_scratch_bytes(int64_t M, int64_t Q, int64_t P);
+
+/* Y[m, q] = sum_c X[m, c] * W[q, c] for 1 <= M <= 48, fp32 result (M, Q), W never materialised.
+ *   X        (M, P) row-major of x_dtype
+ *   x_mode   0: X is narrowed to saturated fp16 first (|x| > 65504 clamps, NaN kept) -- what every fp16-mode
+ *               path of the reference does (qvb8_cuda.cu:761-841, :1082);
+ *            1: X keeps its range (an exact power-of-two prescale per token instead of the clamp)
+ * The weight is the un-narrowed fp32 band value (or the exact escape value), the contract of the reference's
+ * M <= 8 GEMV.  Replaces `forward` for M <= 8, `gemv`, `gemv_multi` (qvb8_cuda.cu:1059-1166, 1416-1512, kernels
+ * :306-453, :463-470, :507-533) and `mma_multi` (:2566-2671). */
+int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,
+                 int64_t scratch_bytes, void *stream);
+
+/* Same product through the layout-agnostic kernel (any P, any id alignment, widths 1..14).  The library falls
+ * back to it by itself when qvb8_small_m's layout preconditions do not hold; exported for tests. */
+int qvb8_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y,
+                         void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QVB8_B200_H */

@@ -1,0 +1,181 @@
+// Dense restore of a QVB8 pack: W[q, c] = T(fma(id, tau_s[q], min_s[q])), one rounding to T, bit-exact with the
+// reference decoder (formats/qvb8/decode.py:168-212; formats/qvb8/backends/cuda_qvb8/qvb8_cuda.cu:535-699, 1711-1727).
+//
+// HBM-bound on the STORE side: 2 bytes written per ~0.8 bytes read.  One warp restores a 256-column segment of one
+// row per step: a lane owns eight consecutive ids, which are exactly nb bytes of the row (rows are byte aligned when
+// P % 8 == 0), fetched as three aligned 32-bit words; the eight results leave as one 16-byte store (32 for fp32), so
+// a warp writes 512 contiguous bytes.  The grid is a fixed multiple of the SM count and strides over the segments.
+// Built WITHOUT fast-math: the fused multiply-add and the narrowing are IEEE round-to-nearest-even.
+#include "common.cuh"
+
+namespace qv {
+
+template <int NB, int J>
+__device__ __forceinline__ uint32_t field_ct(uint32_t lo, uint32_t hi) {
+    constexpr uint32_t MASK = (1u << NB) - 1u;
+    constexpr int S = J * NB;
+    if constexpr (S + NB <= 32) return (lo >> S) & MASK;
+    else if constexpr (S >= 32) return (hi >> (S - 32)) & MASK;
+    else return __funnelshift_r(lo, hi, S) & MASK;
+}
+
+template <int NB>
+__device__ __forceinline__ void ids8_fixed(const uint8_t *__restrict__ ids, int64_t byte, uint32_t (&id)[8]) {
+    const int64_t a0 = byte & ~(int64_t)3;
+    const uint32_t *p = reinterpret_cast<const uint32_t *>(ids + a0);
+    const uint32_t w0 = __ldg(p), w1 = __ldg(p + 1), w2 = __ldg(p + 2);
+    const uint32_t sh = (uint32_t)(byte & 3) * 8u;
+    const uint32_t lo = __funnelshift_r(w0, w1, sh), hi = __funnelshift_r(w1, w2, sh);
+    id[0] = field_ct<NB, 0>(lo, hi); id[1] = field_ct<NB, 1>(lo, hi); id[2] = field_ct<NB, 2>(lo, hi);
+    id[3] = field_ct<NB, 3>(lo, hi); id[4] = field_ct<NB, 4>(lo, hi); id[5] = field_ct<NB, 5>(lo, hi);
+    id[6] = field_ct<NB, 6>(lo, hi); id[7] = field_ct<NB, 7>(lo, hi);
+}
+
+template <typename T> struct Store8;
+template <> struct Store8<__half> {
+    static __device__ __forceinline__ void go(__half *dst, const float (&v)[8]) {
+        __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+        __half2 c = __floats2half2_rn(v[4], v[5]), d = __floats2half2_rn(v[6], v[7]);
+        uint4 u;
+        u.x = *reinterpret_cast<uint32_t *>(&a); u.y = *reinterpret_cast<uint32_t *>(&b);
+        u.z = *reinterpret_cast<uint32_t *>(&c); u.w = *reinterpret_cast<uint32_t *>(&d);
+        __stcs(reinterpret_cast<uint4 *>(dst), u);
+    }
+};
+template <> struct Store8<__nv_bfloat16> {
+    static __device__ __forceinline__ void go(__nv_bfloat16 *dst, const float (&v)[8]) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+        uint4 u;
+        u.x = *reinterpret_cast<uint32_t *>(&a); u.y = *reinterpret_cast<uint32_t *>(&b);
+        u.z = *reinterpret_cast<uint32_t *>(&c); u.w = *reinterpret_cast<uint32_t *>(&d);
+        __stcs(reinterpret_cast<uint4 *>(dst), u);
+    }
+};
+template <> struct Store8<float> {
+    static __device__ __forceinline__ void go(float *dst, const float (&v)[8]) {
+        __stcs(reinterpret_cast<float4 *>(dst), make_float4(v[0], v[1], v[2], v[3]));
+        __stcs(reinterpret_cast<float4 *>(dst) + 1, make_float4(v[4], v[5], v[6], v[7]));
+    }
+};
+
+// Fast path: P % 8 == 0, ids 4-byte aligned, out 16-byte aligned.
+template <typename T>
+__global__ void __launch_bounds__(256) decode_rows_kernel(const uint8_t *__restrict__ ids, const float *__restrict__ min_s,
+                                                          const float *__restrict__ tau_s,
+                                                          const uint8_t *__restrict__ nbits,
+                                                          const int64_t *__restrict__ bit_off, T *__restrict__ out,
+                                                          int Q, int P) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int nseg = (P + 255) >> 8;
+    const int64_t ntask = (int64_t)Q * nseg;
+    for (int64_t task = warp; task < ntask; task += nwarps) {
+        const int q = (int)(task / nseg);
+        const int seg = (int)(task - (int64_t)q * nseg);
+        const int c0 = seg * 256 + lane * 8;
+        const int nb = __ldg(nbits + q);
+        const int64_t base_bit = __ldg(bit_off + q);
+        const float m = __ldg(min_s + q), ts = __ldg(tau_s + q);
+        if (c0 >= P) continue;
+        uint32_t id[8];
+        const bool byte_row = (base_bit & 7) == 0;
+        const int64_t byte = (base_bit >> 3) + (int64_t)(c0 >> 3) * nb;
+        switch (byte_row ? nb : 0) {                       // warp-uniform
+            case 4: ids8_fixed<4>(ids, byte, id); break;
+            case 5: ids8_fixed<5>(ids, byte, id); break;
+            case 6: ids8_fixed<6>(ids, byte, id); break;
+            case 7: ids8_fixed<7>(ids, byte, id); break;
+            case 8: ids8_fixed<8>(ids, byte, id); break;
+            default:
+#pragma unroll
+                for (int j = 0; j < 8; ++j) id[j] = field_bytes(ids, base_bit + (int64_t)(c0 + j) * nb, nb);
+        }
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __fmaf_rn(small_u2f(id[j]), ts, m);
+        Store8<T>::go(out + (int64_t)q * P + c0, v);
+    }
+}
+
+// Any layout: one element per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) decode_elems_kernel(const uint8_t *__restrict__ ids, const float *__restrict__ min_s,
+                                                           const float *__restrict__ tau_s,
+                                                           const uint8_t *__restrict__ nbits,
+                                                           const int64_t *__restrict__ bit_off, T *__restrict__ out,
+                                                           int Q, int P) {
+    const int64_t n = (int64_t)Q * P;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int q = (int)(i / P);
+        const int c = (int)(i - (int64_t)q * P);
+        const int nb = __ldg(nbits + q);
+        const uint32_t id = field_bytes(ids, __ldg(bit_off + q) + (int64_t)c * nb, nb);
+        out[i] = narrow<T>(__fmaf_rn(small_u2f(id), __ldg(tau_s + q), __ldg(min_s + q)));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) scatter_escapes_kernel(const int64_t *__restrict__ esc_idx,
+                                                              const float *__restrict__ esc_vals, int64_t n_esc,
+                                                              int64_t n_out, T *__restrict__ out) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n_esc; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = __ldg(esc_idx + e);
+        if (i >= 0 && i < n_out) out[i] = narrow<T>(__ldg(esc_vals + e));
+    }
+}
+
+static int sm_count() {
+    static thread_local int dev_cached = -1, n = 148;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev != dev_cached) {
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        dev_cached = dev;
+    }
+    return n;
+}
+
+template <typename T>
+static int decode_launch(const qvb8_pack *w, T *out, cudaStream_t st) {
+    const int Q = (int)w->Q, P = (int)w->P;
+    if (Q == 0 || P == 0) return QVB8_OK;
+    const int sms = sm_count();
+    const bool fast = (P % 8 == 0) && aligned(w->ids, 4) && aligned(out, 16);
+    if (fast) {
+        const int64_t ntask = (int64_t)Q * ((P + 255) / 256);
+        const int64_t want = (ntask + 7) / 8;                         // 8 warps per block
+        const int grid = (int)(want < (int64_t)sms * 8 ? want : (int64_t)sms * 8);
+        decode_rows_kernel<T><<<grid, 256, 0, st>>>(w->ids, w->min_s, w->tau_s, w->nbits, w->bit_off, out, Q, P);
+    } else {
+        const int64_t n = (int64_t)Q * P;
+        const int64_t want = (n + 255) / 256;
+        const int grid = (int)(want < (int64_t)sms * 16 ? want : (int64_t)sms * 16);
+        decode_elems_kernel<T><<<grid, 256, 0, st>>>(w->ids, w->min_s, w->tau_s, w->nbits, w->bit_off, out, Q, P);
+    }
+    if (int rc = cuda_status("qvb8_decode launch")) return rc;
+    if (w->n_esc > 0) {
+        const int64_t want = (w->n_esc + 255) / 256;
+        const int grid = (int)(want < (int64_t)sms * 8 ? want : (int64_t)sms * 8);
+        scatter_escapes_kernel<T><<<grid, 256, 0, st>>>(w->esc_idx, w->esc_vals, w->n_esc, (int64_t)Q * P, out);
+        if (int rc = cuda_status("qvb8_decode escapes launch")) return rc;
+    }
+    return QVB8_OK;
+}
+
+}  // namespace qv
+
+QV_API int qvb8_decode(const qvb8_pack *w, int out_dtype, void *out, void *stream) {
+    using namespace qv;
+    if (int rc = check_pack(w, "qvb8_decode")) return rc;
+    if (int rc = check_device("qvb8_decode")) return rc;
+    if (!out && w->Q * w->P > 0) return fail(QVB8_ERR_ARG, "qvb8_decode: null output");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    switch (out_dtype) {
+        case QVB8_F16: return decode_launch<__half>(w, reinterpret_cast<__half *>(out), st);
+        case QVB8_BF16: return decode_launch<__nv_bfloat16>(w, reinterpret_cast<__nv_bfloat16 *>(out), st);
+        case QVB8_F32: return decode_launch<float>(w, reinterpret_cast<float *>(out), st);
+        default: return fail(QVB8_ERR_ARG, "qvb8_decode: out_dtype %d is not QVB8_F16/BF16/F32", out_dtype);
+    }
+}

@@ -1,0 +1,141 @@
+"""Drop-in object for the reference's ``qvb8_cuda`` extension module.
+
+The reference fetches its kernels through ``_load_ext()`` (formats/qvb8/module.py:20-36) and calls the attributes
+listed at formats/qvb8/backends/cuda_qvb8/qvb8_cuda.cu:2673-2691.  :data:`ext` exposes the same names, argument
+order, dtypes, return shapes and error type (``RuntimeError``), backed by the sm_100a kernels of this package.
+:func:`install` rebinds the reference's loaders to it, so ``QVBandLinearV8``, ``QVBandExpertsV8`` and the
+format registry run unchanged on top.
+
+Numerics shared by every small-M entry point here: the weight is the un-narrowed fp32 band value
+``fma(id, tau_s, min_s)`` (the contract of the reference's M <= 8 GEMV); X is narrowed to saturated fp16 first.
+The reference's 9..48-row kernels round the weight once to fp16 (or bf16) instead; the results agree within the
+1e-2 relative-Frobenius tolerance the parity tests state, and the un-narrowed value is at least as close to the
+certified weight.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import lib as _lib
+
+_SMALL_M_MAX = 48
+
+
+def _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
+    return _lib.pack_struct(ids, min_s, tau_s, row_nbits, row_bit_off, int(P), esc_idx, esc_vals)
+
+
+def _as_2d(X: torch.Tensor, P: int) -> torch.Tensor:
+    if X.dim() == 1:
+        X = X.reshape(1, -1)
+    if X.dim() != 2 or X.shape[1] != P:
+        raise RuntimeError(f"qvb8: X must be (M, {P}), got {tuple(X.shape)}")
+    if X.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        X = X.float()
+    return X
+
+
+def _sat_half(X: torch.Tensor) -> torch.Tensor:
+    """Saturating narrowing to fp16 (reference qvb8_cuda.cu:761-841): +-65504 clamp, NaN kept."""
+    if X.dtype == torch.float16:
+        return X
+    return X.float().clamp(-65504.0, 65504.0).to(torch.float16)
+
+
+class Qvb8Ext:
+    """Same attribute surface as the reference's ``qvb8_cuda`` pybind module."""
+
+    # ---- dense restore ------------------------------------------------------------------------------------
+    def decode(self, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
+        """(Q, P) fp16 restore: fp16(fma(id, tau_s, min_s)), escapes written over (qvb8_cuda.cu:651-699)."""
+        pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
+        return _lib.decode(pk, keep, torch.float16)
+
+    def decode_bf16(self, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
+        """(Q, P) bf16 restore, one rounding of the fp32 band value (qvb8_cuda.cu:1711-1727)."""
+        pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
+        return _lib.decode(pk, keep, torch.bfloat16)
+
+    def decode_f32(self, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
+        """(Q, P) fp32 band values with exact escapes (no counterpart entry point in the reference: its fp32 value
+        lives only inside the GEMV, qvb8_cuda.cu:346-353)."""
+        pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
+        return _lib.decode(pk, keep, torch.float32)
+
+    # ---- small M ------------------------------------------------------------------------------------------
+    def gemv(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
+        """M = 1: X fp16 of length P -> (1, Q) fp32 (qvb8_cuda.cu:1416-1512)."""
+        if X.dtype != torch.float16:
+            raise RuntimeError("X must be fp16")
+        if X.numel() != P:
+            raise RuntimeError("X length must equal P")
+        pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
+        return _lib.small_m(pk, keep, X.reshape(1, -1))
+
+    def gemv_multi(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
+        """M = 1..8 -> (M, Q) fp32 (qvb8_cuda.cu:1059-1166)."""
+        X = _as_2d(X, int(P))
+        if not 1 <= X.shape[0] <= 8:
+            raise RuntimeError(f"qvb8 GEMV-multi: M={X.shape[0]} is outside the range 1..8")
+        pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
+        return _lib.small_m(pk, keep, X)
+
+    def gemv_rb(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals, perm, tile_nb):
+        """The reference's register-blocked sm_70 variant (qvb8_cuda.cu:1350-1413); same result as gemv_multi.
+        perm / tile_nb are accepted and not needed: the kernel orders rows by width itself."""
+        return self.gemv_multi(X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
+
+    def mma_multi(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals, perm, tile_nb,
+                  bf16=False, esc_starts=None, general=-1):
+        """QVB8 tensor-core multi-row product (M<=48) -> (M, Q) fp32; accepts the bf16 mode flag.
+
+        (qvb8_cuda.cu:2566-2671.)  perm, tile_nb, esc_starts and general describe a row ordering the reference
+        computes per module; this kernel sorts rows by width on the fly, so they are validated and unused.
+        bf16=True keeps X's range (no fp16 clamp)."""
+        X = _as_2d(X, int(P))
+        M = X.shape[0]
+        if not 1 <= M <= _SMALL_M_MAX:
+            raise RuntimeError(f"qvb8 mma-multi: M={M} outside 1..48")
+        if int(P) % 128 != 0 or ids.data_ptr() % 4 != 0:
+            raise RuntimeError("qvb8 mma-multi: needs P%128==0 and 4-byte-aligned ids")
+        Q = min_s.numel()
+        if perm is not None and perm.numel() not in (0, Q):
+            raise RuntimeError("qvb8 mma-multi: perm must be an int32 CUDA tensor of length Q (or empty)")
+        pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
+        return _lib.small_m(pk, keep, X, x_mode=1 if bf16 else 0)
+
+    # ---- any M --------------------------------------------------------------------------------------------
+    def _forward(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals, out_half: bool):
+        X = _as_2d(X, int(P))
+        M = X.shape[0]
+        pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
+        if M <= _SMALL_M_MAX:
+            y = _lib.small_m(pk, keep, X)
+            return y.to(torch.float16) if (out_half and M > 8) else y
+        # prefill: restore once to fp16, then one tensor-core GEMM with fp32 accumulation (qvb8_cuda.cu:1542-1671)
+        W = _lib.decode(pk, keep, torch.float16)
+        Xh = _sat_half(X)
+        if out_half:
+            return torch.mm(Xh, W.t())
+        return torch.mm(Xh, W.t(), out_dtype=torch.float32)
+
+    def forward(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
+        """Any M -> (M, Q) fp32 (qvb8_cuda.cu:1520-1683)."""
+        return self._forward(X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals, False)
+
+    def forward_half(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
+        """As forward, but the M > 8 result is fp16 (qvb8_cuda.cu:1685-1697)."""
+        return self._forward(X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals, True)
+
+
+ext = Qvb8Ext()
+
+
+def install() -> None:
+    """Make the reference's QVB8 modules use this package's kernels: rebinds ``_load_ext`` in every reference module
+    that imported it (formats/qvb8/module.py:20, backends_experts.py:13).  The reference package must be importable
+    (it is not a dependency of this package)."""
+    import importlib
+    for name in ("qv_band.formats.qvb8.module", "qv_band.formats.qvb8.backends_experts"):
+        mod = importlib.import_module(name)
+        mod._load_ext = lambda: ext

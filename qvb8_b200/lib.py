@@ -1,0 +1,178 @@
+"""ctypes binding of ``libqvb8_b200.so`` (the C ABI declared in ``include/qvb8_b200.h``).
+
+The library is the product: there is no fallback.  :func:`load` raises if it has not been built
+(``python -m qvb8_b200.build``), and every wrapper raises ``RuntimeError`` with the library's own message on a
+non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libqvb8_b200.so")
+
+F16, BF16, F32 = 0, 1, 2
+_DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
+_CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
+
+# every symbol include/qvb8_b200.h declares
+EXPORTS = (
+    "qvb8_last_error", "qvb8_version", "qvb8_decode", "qvb8_small_m_scratch_bytes", "qvb8_small_m",
+    "qvb8_small_m_generic",
+)
+
+
+class PackStruct(ctypes.Structure):
+    """``struct qvb8_pack`` of the header."""
+    _fields_ = [
+        ("ids", ctypes.c_void_p), ("ids_bytes", ctypes.c_int64), ("min_s", ctypes.c_void_p),
+        ("tau_s", ctypes.c_void_p), ("nbits", ctypes.c_void_p), ("bit_off", ctypes.c_void_p),
+        ("Q", ctypes.c_int64), ("P", ctypes.c_int64), ("esc_idx", ctypes.c_void_p), ("esc_vals", ctypes.c_void_p),
+        ("n_esc", ctypes.c_int64),
+    ]
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise RuntimeError(
+                    f"{LIB_PATH} is missing: build the CUDA kernel library first (python -m qvb8_b200.build). "
+                    "There is no CPU or eager fallback for the QVB8 kernels.")
+            lib = ctypes.CDLL(LIB_PATH)
+            vp, i64, ci = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+            pk = ctypes.POINTER(PackStruct)
+            lib.qvb8_last_error.restype = ctypes.c_char_p
+            lib.qvb8_version.restype = ctypes.c_char_p
+            lib.qvb8_decode.argtypes = [pk, ci, vp, vp]
+            lib.qvb8_small_m_scratch_bytes.argtypes = [i64, i64, i64]
+            lib.qvb8_small_m_scratch_bytes.restype = i64
+            lib.qvb8_small_m.argtypes = [pk, vp, ci, ci, i64, vp, vp, i64, vp]
+            lib.qvb8_small_m_generic.argtypes = [pk, vp, ci, ci, i64, vp, vp]
+            _lib = lib
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed (status {rc}): {load().qvb8_last_error().decode()}")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dt]
+    except KeyError:
+        raise RuntimeError(f"qvb8_b200: dtype {dt} is not float16 / bfloat16 / float32") from None
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _cuda(t: torch.Tensor, name: str, dtype: torch.dtype) -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError(f"qvb8_b200: {name} must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise RuntimeError(f"qvb8_b200: {name} must be {dtype}, got {t.dtype}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def pack_struct(ids, min_s, tau_s, nbits, bit_off, P: int, esc_idx, esc_vals):
+    """Validated ``qvb8_pack`` for tensors on one CUDA device.  Returns (struct, keepalive list)."""
+    ids = _cuda(ids, "ids", torch.uint8)
+    min_s = _cuda(min_s, "min_s", torch.float32)
+    tau_s = _cuda(tau_s, "tau_s", torch.float32)
+    nbits = _cuda(nbits, "row_nbits", torch.uint8)
+    bit_off = _cuda(bit_off, "row_bit_off", torch.int64)
+    Q = min_s.numel()
+    if tau_s.numel() != Q or nbits.numel() != Q or bit_off.numel() != Q:
+        raise RuntimeError("qvb8_b200: min_s / tau_s / row_nbits / row_bit_off must all have Q entries")
+    n_esc = esc_idx.numel() if esc_idx is not None else 0
+    keep = [ids, min_s, tau_s, nbits, bit_off]
+    ei = ev = None
+    if n_esc:
+        ei = _cuda(esc_idx, "esc_idx", torch.int64)
+        ev = _cuda(esc_vals, "esc_vals", torch.float32)
+        if ev.numel() != n_esc:
+            raise RuntimeError("qvb8_b200: esc_idx and esc_vals differ in length")
+        keep += [ei, ev]
+    dev = ids.device
+    for t in keep:
+        if t.device != dev:
+            raise RuntimeError("qvb8_b200: all pack tensors must live on one device")
+    s = PackStruct(ids.data_ptr(), ids.numel(), min_s.data_ptr(), tau_s.data_ptr(), nbits.data_ptr(),
+                   bit_off.data_ptr(), Q, int(P), ei.data_ptr() if n_esc else None, ev.data_ptr() if n_esc else None,
+                   n_esc)
+    return s, keep
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# scratch (split-K partial sums + tickets), one zero-initialised buffer per (device, stream)
+
+_scratch: dict = {}
+
+
+def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor | None:
+    """A zero-initialised scratch buffer of at least `nbytes` for the current stream of `device`.  Kernels leave it
+    reusable; buffers are keyed by stream because two calls sharing one buffer must not overlap on the device."""
+    if nbytes <= 0:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr(device))
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def reserve_scratch(device: torch.device, M: int, Q: int, P: int) -> None:
+    """Allocate the scratch a later small-M call of these sizes needs (call before capturing a CUDA graph)."""
+    scratch_for(device, int(load().qvb8_small_m_scratch_bytes(M, Q, P)))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# thin wrappers
+
+def decode(pack, keep, out_dtype: torch.dtype) -> torch.Tensor:
+    dev = keep[0].device
+    out = torch.empty((pack.Q, pack.P), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(load().qvb8_decode(ctypes.byref(pack), dtype_code(out_dtype), out.data_ptr(), stream_ptr(dev)),
+              "qvb8_decode")
+    return out
+
+
+def small_m(pack, keep, X: torch.Tensor, x_mode: int = 0, generic: bool = False, out: torch.Tensor | None = None):
+    """(M, Q) fp32 = X (M, P) @ W^T through the fused kernel (M <= 48)."""
+    dev = keep[0].device
+    if not X.is_cuda or X.device != dev:
+        raise RuntimeError("qvb8_b200: X must be a CUDA tensor on the pack's device")
+    if X.dim() != 2 or X.shape[1] != pack.P:
+        raise RuntimeError(f"qvb8_b200: X must be (M, {pack.P}), got {tuple(X.shape)}")
+    X = X if X.is_contiguous() else X.contiguous()
+    M = X.shape[0]
+    Y = out if out is not None else torch.empty((M, pack.Q), dtype=torch.float32, device=dev)
+    lib = load()
+    with torch.cuda.device(dev):
+        if generic:
+            rc = lib.qvb8_small_m_generic(ctypes.byref(pack), X.data_ptr(), dtype_code(X.dtype), x_mode, M,
+                                          Y.data_ptr(), stream_ptr(dev))
+        else:
+            nbytes = int(lib.qvb8_small_m_scratch_bytes(M, pack.Q, pack.P))
+            sc = scratch_for(dev, nbytes)
+            rc = lib.qvb8_small_m(ctypes.byref(pack), X.data_ptr(), dtype_code(X.dtype), x_mode, M, Y.data_ptr(),
+                                  sc.data_ptr() if sc is not None else None, sc.numel() if sc is not None else 0,
+                                  stream_ptr(dev))
+    check(rc, "qvb8_small_m")
+    return Y

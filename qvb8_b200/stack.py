@@ -1,0 +1,156 @@
+"""The linear stack of a dense decoder as one replayable unit: every packed projection of every layer, run in order.
+
+This is the per-token hot path the reference walks with one Python call per linear (decode/spec_decode.py:3982-3998
+-> every q/k/v/o/gate/up/down ``forward``) and wraps in CUDA graphs to hide launch cost
+(decode/proj_graph.py, decode/layer_graph.py).  Here the whole stack is captured once into a CUDA graph and replayed;
+the packs stay resident in HBM and every replay streams each of them exactly once.
+
+Projections of one layer and their inputs (d = d_model, kv = kv heads x head_dim, f = MLP width):
+
+    q (d -> q_out)  k (d -> kv)  v (d -> kv)   read the attention input x_attn (M, d)
+    o (q_out -> d)                              reads x_o (M, q_out)
+    gate (d -> f)   up (d -> f)                 read the MLP input x_mlp (M, d)
+    down (f -> d)                               reads x_down (M, f)
+
+Attention, norms and activations between them are not part of this path; the stack feeds every projection a
+resident activation buffer of the right shape.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import lib as _lib
+from . import synth
+
+
+@dataclass(frozen=True)
+class StackConfig:
+    name: str
+    layers: int
+    d_model: int
+    q_out: int
+    kv_out: int
+    mlp: int
+    tau: float
+    config_id: int
+
+    def projections(self):
+        """(name, Q, P, input buffer) of one layer, in execution order."""
+        d, f = self.d_model, self.mlp
+        return [("q", self.q_out, d, "x_attn"), ("k", self.kv_out, d, "x_attn"), ("v", self.kv_out, d, "x_attn"),
+                ("o", d, self.q_out, "x_o"), ("gate", f, d, "x_mlp"), ("up", f, d, "x_mlp"), ("down", d, f, "x_down")]
+
+    def weights_per_layer(self) -> int:
+        return sum(q * p for _, q, p, _ in self.projections())
+
+
+# shapes of the benchmark configurations
+DENSE_9B = StackConfig("9b-dense", 32, 4096, 4096, 1024, 12288, 1e-3, 2)
+DENSE_27B = StackConfig("27b-dense", 64, 5120, 5120, 1024, 17408, 2e-3, 3)
+DENSE_65B = StackConfig("65b-dense", 80, 8192, 8192, 1024, 28672, 1e-3, 5)
+CONFIGS = {c.name: c for c in (DENSE_9B, DENSE_27B, DENSE_65B)}
+
+
+class LinearStack:
+    """Packs of `layers` decoder layers resident on one device + activation / output buffers + a captured graph.
+
+    rank / world: the stack is sharded by OUTPUT ROWS (column-parallel): rank r holds rows [r*Q/world, (r+1)*Q/world)
+    of every projection, which for a QVB8 pack is a slice of the per-row vectors and a byte range of the ids
+    (rows are independent, reference formats/qvb8/module.py:126-160)."""
+
+    def __init__(self, cfg: StackConfig, M: int, device, layers: int | None = None, seed_base: int | None = None,
+                 rank: int = 0, world: int = 1, policy: str = "escape_outliers", x_dtype=torch.bfloat16):
+        self.cfg, self.M, self.device = cfg, int(M), torch.device(device)
+        self.layers = cfg.layers if layers is None else int(layers)
+        self.rank, self.world = rank, world
+        self.packs = []          # [layer][proj] -> (name, QVB8Pack, struct, keepalive, xbuf name)
+        self.compressed_bytes = 0
+        self.n_weights = 0
+        self.width_hist: dict = {}
+        self.n_escapes = 0
+        seed_base = 1000 * cfg.config_id if seed_base is None else seed_base
+        for layer in range(self.layers):
+            row = []
+            for j, (name, Q, P, xname) in enumerate(cfg.projections()):
+                if Q % world:
+                    raise ValueError(f"{name}: {Q} rows do not split over {world} ranks")
+                Qr = Q // world
+                W = synth.synth_weight(Q, P, seed_base + layer * 16 + j, device=self.device)
+                W = W[rank * Qr:(rank + 1) * Qr]
+                pk = synth.encode_qvb8(W, tau=cfg.tau, policy=policy)
+                del W
+                st, keep = _lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx,
+                                            pk.esc_vals)
+                row.append((name, pk, st, keep, xname))
+                self.compressed_bytes += pk.weight_bytes()
+                self.n_weights += pk.Q * pk.P
+                self.n_escapes += int(pk.esc_idx.numel())
+                for b, n in pk.stats["nbits_hist"].items():
+                    self.width_hist[b] = self.width_hist.get(b, 0) + n
+            self.packs.append(row)
+        d, f = cfg.d_model, cfg.mlp
+        shapes = {"x_attn": d, "x_o": cfg.q_out, "x_mlp": d, "x_down": f}
+        self.x = {k: synth.synth_activation(self.M, p, seed=7 + i, device=self.device, dtype=x_dtype)
+                  for i, (k, p) in enumerate(shapes.items())}
+        self.y = [[torch.empty((self.M, pk.Q), dtype=torch.float32, device=self.device) for _, pk, *_ in row]
+                  for row in self.packs]
+        for row in self.packs:
+            for _, pk, *_ in row:
+                _lib.reserve_scratch(self.device, self.M, pk.Q, pk.P)
+        self.graph = None
+        self.launches_per_step = sum((1 + (1 if pk.esc_idx.numel() else 0)) for row in self.packs for _, pk, *_ in row)
+        self._host_in = self._host_out = None
+
+    # ---- execution ------------------------------------------------------------------------------------
+    def run_eager(self) -> None:
+        """One pass over every projection on the current stream (one fused launch each, plus the escape pass)."""
+        for li, row in enumerate(self.packs):
+            for j, (name, pk, st, keep, xname) in enumerate(row):
+                _lib.small_m(st, keep, self.x[xname], out=self.y[li][j])
+
+    def capture(self) -> None:
+        self.run_eager()                      # warm-up outside capture: shared-memory opt-in, scratch
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.run_eager()
+        self.graph = g
+
+    def step(self) -> None:
+        """One decode step of the stack with the activations already resident in HBM."""
+        if self.graph is None:
+            self.capture()
+        self.graph.replay()
+
+    # ---- the host-buffer API (end-to-end: pinned host activations in, last layer's outputs back) --------
+    def _host_buffers(self):
+        if self._host_in is None:
+            self._host_in = {k: torch.empty_like(v, device="cpu").pin_memory() for k, v in self.x.items()}
+            for k, v in self.x.items():
+                self._host_in[k].copy_(v)
+            last = self.y[-1]
+            self._host_out = [torch.empty_like(t, device="cpu").pin_memory() for t in last]
+        return self._host_in, self._host_out
+
+    def step_host(self, x_host: dict | None = None):
+        """Activations from pinned host memory -> one stack step -> the last layer's projection outputs on the host.
+        Returns the list of host tensors (valid after this call returns: it synchronises)."""
+        hin, hout = self._host_buffers()
+        if x_host is not None:
+            for k, v in x_host.items():
+                hin[k].copy_(v)
+        for k in self.x:
+            self.x[k].copy_(hin[k], non_blocking=True)
+        self.step()
+        for t, h in zip(self.y[-1], hout):
+            h.copy_(t, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return hout
+
+    def h2d_bytes(self) -> int:
+        return sum(v.numel() * v.element_size() for v in self.x.values())
+
+    def d2h_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.y[-1])
