@@ -80,6 +80,27 @@ int64_t qvb8_small_m_scratch_bytes(int64_t M, int64_t Q, int64_t P);
 int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,
                  int64_t scratch_bytes, void *stream);
 
+/* flags of qvb8_small_m_ex */
+#define QVB8_FLAG_PDL 1     /* launch with programmatic stream serialization: the kernel's weight prefetch may overlap
+                               the tail of the previous kernel in the stream; everything that depends on earlier
+                               work (reading X, writing Y and the scratch) waits for it to complete */
+
+/* Escape plan: the pack's escape list regrouped by row, with the difference (exact value - band value)
+ * precomputed, so that the fused kernel corrects escapes itself instead of running a second pass.  Build once per
+ * pack (and per escape table); the buffer must be 16-byte aligned and hold qvb8_escape_plan_bytes(Q, n_esc) bytes.
+ * The reference regroups its escapes the same way at load time for its mma path (formats/qvb8/module.py:279-288,
+ * esc_starts) and stores precomputed differences in its qvb8r files (formats/qvb8r/container.py:10-12). */
+int64_t qvb8_escape_plan_bytes(int64_t Q, int64_t n_esc);
+int qvb8_escape_plan(const qvb8_pack *w, void *plan, int64_t plan_bytes, void *stream);
+
+/* qvb8_small_m with an optional escape plan (may be NULL) and launch flags. */
+int qvb8_small_m_ex(const qvb8_pack *w, const void *esc_plan, const void *X, int x_dtype, int x_mode, int64_t M,
+                    float *Y, void *scratch, int64_t scratch_bytes, int flags, void *stream);
+
+/* Tuning hook for tests and sweeps (process-wide): nwarp 4 or 8 forces the CTA shape (0 = choose by size);
+ * fill = CTAs wanted per SM when the K dimension is split (default 3). */
+void qvb8_small_m_set_tuning(int nwarp, int fill);
+
 /* Same product through the layout-agnostic kernel (any P, any id alignment, widths 1..14).  The library falls
  * back to it by itself when qvb8_small_m's layout preconditions do not hold; exported for tests. */
 int qvb8_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y,

@@ -2,7 +2,8 @@
 // W read ONCE from HBM as bit-packed ids and never materialised.
 //
 // Replaces the reference's GEMV family and its mma.sync verify kernel
-// (formats/qvb8/backends/cuda_qvb8/qvb8_cuda.cu:306-453 qvb8_gemv_multi_v3, :463-489 split-K, :1813-2441 qvb8_mma_*).
+// (formats/qvb8/backends/cuda_qvb8/qvb8_cuda.cu:306-453 qvb8_gemv_multi_v3, :463-489 split-K, :507-533 escape
+// correction, :1813-2441 qvb8_mma_*).
 //
 // Arithmetic.  With w = min_s + id * tau_s the row sum factors (the identity the reference states at
 // qvb8_cuda.cu:3-9):   y[m, q] = min_s[q] * sum_c x[m, c]  +  tau_s[q] * sum_c x[m, c] * id[q, c].
@@ -11,11 +12,11 @@
 // is therefore the un-narrowed band value, the contract of the reference's M <= 8 GEMV; X is narrowed to saturated
 // fp16 first, as every fp16-mode path of the reference does (:761-841).
 //
-// Roofline: HBM.  Per weight the kernel moves nbits/8 bytes (about 0.8) and spends ~1.5 issue slots; the stream is
-// staged through shared memory with 16-byte cp.async copies (each warp keeps NST row-chunks in flight), so the
-// load pattern seen by HBM is whole 16-byte-aligned row segments while the fragment reads happen in shared memory.
+// Roofline: HBM.  Per weight the kernel moves nbits/8 bytes (about 0.8) and spends about two issue slots; the
+// stream is staged through shared memory with 16-byte cp.async copies (each warp keeps NST-1 row-chunks in flight),
+// so HBM sees whole 16-byte-aligned row segments while the fragment reads happen in shared memory.
 //
-// Work split.  A CTA owns 128 consecutive output rows and one K-range.  Rows of a pack have different widths, so the
+// Work split.  A CTA owns RB consecutive output rows and one K-range.  Rows of a pack have different widths, so the
 // CTA first sorts its rows by width into 16-row tiles of ONE width (shared-memory lists; no precomputed ordering is
 // needed).  A warp takes a tile, and for every 128-column chunk: thread (g = lane / 4, t = lane % 4) owns the 32 ids
 // of rows g and g + 8 that start at column 32 t -- exactly nb 32-bit words -- and turns them into the A fragments of
@@ -24,6 +25,11 @@
 // and one HFMA2 removes the 1024 and the 2^e exactly.  The B fragments are the activations, staged once per CTA as
 // fp16 in the order the fragments want.  K-ranges of one row block are summed in a fixed order by the last CTA of
 // the block to finish (a ticket counter), so results are identical from run to run.
+//
+// Escapes.  Positions whose exact value is stored separately get x * (exact - band) added.  With an escape plan
+// (row pointers + columns + precomputed differences, built once per pack by qvb8_escape_plan) the warp that finishes
+// a tile adds its rows' corrections in stored order before the result leaves the CTA; without a plan a second
+// kernel walks the raw (position, value) list.
 #include "common.cuh"
 
 namespace qv {
@@ -34,29 +40,33 @@ int launch_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x
 int check_small_m_args(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, const float *Y,
                        const char *who);
 
-constexpr int RB = 128;             // output rows per CTA
-constexpr int NWARP = 8;            // warps per CTA
 constexpr int KC = 128;             // columns per chunk (one cp.async stage of a tile)
-constexpr int NST = 4;              // stages in flight per warp
+constexpr int NST = 4;              // ring slots per warp (NST - 1 chunks in flight)
 constexpr int STAGE_BYTES = 16 * 144;   // 16 rows x (16 * nb bytes, +16 pad for nb = 8)
-constexpr int MAXTILES = 16;        // 128 rows in <= 7 width classes make at most 8 + 6 tiles
 constexpr int NCLASS = 7;           // widths 3..8 -> class 0..5; every other width -> class 6 (per-element path)
 constexpr int XS_MAX_BYTES = 64 * 1024;
 constexpr int64_t TICKET_BYTES = 64 * 1024;   // fixed-size counter area at the START of the scratch, so that calls of
                                               // different sizes sharing one scratch never find partial sums in it
 constexpr int MAX_TICKET_BLOCKS = (int)(TICKET_BYTES / 4);
+constexpr int MAX_M = 48;
 
+template <int NWARP>
 struct TileTable {
+    static constexpr int RB = 16 * NWARP;
+    static constexpr int MAXTILES = NWARP + NCLASS - 1;
+    // per row of the block (local index)
+    uint32_t row_b16[RB];           // byte offset of the row in `ids`, in 16-byte units
+    float row_ms[RB], row_ts[RB];
+    int8_t row_cls[RB];
+    uint8_t row_nb[RB];
+    // tiles
     int ntiles;
-    int tile_nb[MAXTILES];          // width of the tile's rows; 0 = per-element class
-    int tile_cnt[MAXTILES];         // real rows in the tile (the rest is padding)
-    int row[MAXTILES][16];          // global row index, -1 = padding
-    uint32_t base16[MAXTILES][16];  // byte offset of the row in `ids`, in 16-byte units
-    float ms[MAXTILES][16];
-    float ts[MAXTILES][16];
-    int list[NCLASS][RB];           // scratch of the classification: local row numbers per class
-    int count[NCLASS];
-    float sumx[48];
+    int need_b;                     // some tile pairs ids at distance 4: the second activation layout is needed
+    int8_t tile_nb[MAXTILES];       // width of the tile's rows; 0 = per-element class
+    int8_t tile_cnt[MAXTILES];      // real rows in the tile (the rest is padding)
+    int16_t tile_row[MAXTILES][16]; // local row index, -1 = padding
+    int16_t list[NCLASS][RB];       // scratch of the classification
+    float sumx[MAX_M];
     int is_last;
 };
 
@@ -69,6 +79,11 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
+// Programmatic dependent launch: everything before pdl_wait() may overlap the tail of the previous kernel in the
+// stream (it must not touch memory that kernel writes); both are no-ops for a normal launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -77,19 +92,23 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Pairing of a width: ids f and f + D share a register; the low one sits at mantissa bit E, the high one at bit 0
-// of the upper half-word (nb * D == 16 - E).
+// Pairing of a width: ids f and f + D share a register.  E > 0: the low id sits at mantissa bit E and the high id at
+// bit 0 of the upper half-word; E < 0: the low id at bit 0, the high id at mantissa bit -E.  (nb * D == 16 - E.)
 template <int NB> struct Pairing;
 template <> struct Pairing<8> { static constexpr int D = 2, E = 0; };
 template <> struct Pairing<7> { static constexpr int D = 2, E = 2; };
 template <> struct Pairing<6> { static constexpr int D = 2, E = 4; };
-template <> struct Pairing<5> { static constexpr int D = 4, E = -4; };   // high id shifted instead: see pair_reg
+template <> struct Pairing<5> { static constexpr int D = 4, E = -4; };
 template <> struct Pairing<4> { static constexpr int D = 4, E = 0; };
 template <> struct Pairing<3> { static constexpr int D = 4, E = 4; };
 
+// fp16 bit patterns of 2^-e and -1024 * 2^-e (written as integers: the conversion intrinsics are opaque to constant
+// folding and would run on the conversion pipe for every pair).
+__host__ __device__ constexpr uint32_t h_pow2(int e) { return (uint32_t)(15 - e) << 10; }
+__host__ __device__ constexpr uint32_t h_neg1024_pow2(int e) { return 0x8000u | ((uint32_t)(25 - e) << 10); }
+
 // Register holding fp16(id[fa]) in the low half and fp16(id[fa + D]) in the high half, from the nb words W of a
-// thread's 32-id block.  E >= 0: low id at mantissa bit E, high id at bit 0.  E < 0: low id at bit 0, high id at
-// mantissa bit -E.  All shifts and masks fold to constants after unrolling.
+// thread's 32-id block.  All shifts and masks fold to constants after unrolling.
 template <int NB>
 __device__ __forceinline__ uint32_t pair_reg(const uint32_t (&W)[NB], int fa) {
     constexpr int D = Pairing<NB>::D, E = Pairing<NB>::E;
@@ -99,6 +118,8 @@ __device__ __forceinline__ uint32_t pair_reg(const uint32_t (&W)[NB], int fa) {
     static_assert(EL + NB <= 10 && EH + NB <= 10, "id does not fit the fp16 mantissa");
     constexpr uint32_t FM = (1u << NB) - 1u;
     constexpr uint32_t MASK = (FM << EL) | (FM << (16 + EH));
+    constexpr uint32_t SCALE = h_pow2(EL) | (h_pow2(EH) << 16);
+    constexpr uint32_t BIAS = h_neg1024_pow2(EL) | (h_neg1024_pow2(EH) << 16);
     const int s = NB * fa - EL;                  // bit of the block that must land on bit 0
     uint32_t r;
     if (s < 0) {
@@ -111,11 +132,12 @@ __device__ __forceinline__ uint32_t pair_reg(const uint32_t (&W)[NB], int fa) {
         else r = __funnelshift_r(W[wi], W[wi + 1 < NB ? wi + 1 : wi], sh);
     }
     r = (r & MASK) | 0x64006400u;                // two fp16 numbers 1024 + id * 2^shift
-    const float sl = 1.0f / (float)(1 << EL), shh = 1.0f / (float)(1 << EH);
-    const __half2 scale = __floats2half2_rn(sl, shh);
-    const __half2 bias = __floats2half2_rn(-1024.0f * sl, -1024.0f * shh);
-    const __half2 v = __hfma2(*reinterpret_cast<const __half2 *>(&r), scale, bias);
-    return *reinterpret_cast<const uint32_t *>(&v);
+    if constexpr (EL == 0 && EH == 0) {
+        asm("sub.f16x2 %0, %1, %2;\n" : "=r"(r) : "r"(r), "r"(0x64006400u));
+    } else {
+        asm("fma.rn.f16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(r), "r"(SCALE), "r"(BIAS));
+    }
+    return r;
 }
 
 // The nb words of a thread's block, with the widest conflict-free shared-memory loads for that width.
@@ -123,42 +145,71 @@ template <int NB>
 __device__ __forceinline__ void load_block(uint32_t addr, uint32_t (&W)[NB]) {
     if constexpr (NB == 8) {
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(W[0]), "=r"(W[1]), "=r"(W[2]), "=r"(W[3]) : "r"(addr));
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(W[4]), "=r"(W[5]), "=r"(W[6]), "=r"(W[7]) : "r"(addr + 16));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+16];\n" : "=r"(W[4]), "=r"(W[5]), "=r"(W[6]), "=r"(W[7]) : "r"(addr));
     } else if constexpr (NB == 4) {
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(W[0]), "=r"(W[1]), "=r"(W[2]), "=r"(W[3]) : "r"(addr));
     } else if constexpr (NB == 6) {
-#pragma unroll
-        for (int k = 0; k < 6; k += 2)
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(W[k]), "=r"(W[k + 1]) : "r"(addr + 4 * k));
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(W[0]), "=r"(W[1]) : "r"(addr));
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+8];\n" : "=r"(W[2]), "=r"(W[3]) : "r"(addr));
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+16];\n" : "=r"(W[4]), "=r"(W[5]) : "r"(addr));
     } else {
-#pragma unroll
-        for (int k = 0; k < NB; ++k) asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(W[k]) : "r"(addr + 4 * k));
+        static_assert(NB == 8 || NB == 4 || NB == 6, "odd widths are specialised below");
     }
 }
 
-__device__ __forceinline__ int row_stride(int nb) { return nb == 8 ? 144 : 16 * nb; }
+// odd widths: nb scalar loads (an odd stride in words spreads the 32 lanes over all banks)
+template <>
+__device__ __forceinline__ void load_block<7>(uint32_t addr, uint32_t (&W)[7]) {
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(W[0]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+4];\n" : "=r"(W[1]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+8];\n" : "=r"(W[2]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+12];\n" : "=r"(W[3]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+16];\n" : "=r"(W[4]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+20];\n" : "=r"(W[5]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+24];\n" : "=r"(W[6]) : "r"(addr));
+}
+template <>
+__device__ __forceinline__ void load_block<5>(uint32_t addr, uint32_t (&W)[5]) {
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(W[0]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+4];\n" : "=r"(W[1]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+8];\n" : "=r"(W[2]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+12];\n" : "=r"(W[3]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+16];\n" : "=r"(W[4]) : "r"(addr));
+}
+template <>
+__device__ __forceinline__ void load_block<3>(uint32_t addr, uint32_t (&W)[3]) {
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(W[0]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+4];\n" : "=r"(W[1]) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+8];\n" : "=r"(W[2]) : "r"(addr));
+}
+
+__host__ __device__ constexpr int row_stride(int nb) { return nb == 8 ? 144 : 16 * nb; }
 
 // One 128-column chunk of a 16-row tile of width NB: 8 MMAs per token group.
-template <int NB, int NT>
-__device__ __forceinline__ void chunk_mma(uint32_t stage, uint32_t xs_chunk, int MP, int lane, float (&acc)[NT][4]) {
+//   wa, wb   shared addresses of this thread's blocks in rows g and g + 8 of the stage
+//   xa       shared address of this thread's first activation slot of the chunk (token 8n + g -> + n * 128 bytes)
+//   xstep    bytes between the slots of consecutive 8-column groups (= 4 * MP * 16)
+//   DUAL     true: a second activation layout exists for widths that pair ids at distance 4 (xa points into it);
+//            false: only layout A is staged and those widths rebuild their operands with byte permutes
+template <int NB, int NT, bool DUAL>
+__device__ __forceinline__ void chunk_mma(uint32_t wa, uint32_t wb, uint32_t xa, uint32_t xstep, bool xvalid,
+                                          float (&acc)[NT][4]) {
     constexpr int D = Pairing<NB>::D;
-    const int g = lane >> 2, t = lane & 3;
-    const int RS = NB == 8 ? 144 : 16 * NB;
     uint32_t Wa[NB], Wb[NB];
-    load_block<NB>(stage + g * RS + t * 4 * NB, Wa);
-    load_block<NB>(stage + (g + 8) * RS + t * 4 * NB, Wb);
+    load_block<NB>(wa, Wa);
+    load_block<NB>(wb, Wb);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        // activations of columns 32 t + 8 i .. + 7 for this thread's token(s): one 16-byte slot per token
+        // activations of columns 32 t + 8 i .. + 7 for this thread's token(s), already in fragment order:
+        // words (2h, 2h + 1) are the B operands of MMA h of this group
         uint32_t xw[NT][4];
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
-            const int m = 8 * n + g;
             xw[n][0] = xw[n][1] = xw[n][2] = xw[n][3] = 0u;
-            if (m < MP) {
-                const uint32_t a = xs_chunk + (uint32_t)(((i * 4 + t) * MP + m) * 16);
+            if (NT > 1 || xvalid) {
                 asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                             : "=r"(xw[n][0]), "=r"(xw[n][1]), "=r"(xw[n][2]), "=r"(xw[n][3]) : "r"(a));
+                             : "=r"(xw[n][0]), "=r"(xw[n][1]), "=r"(xw[n][2]), "=r"(xw[n][3])
+                             : "r"(xa + i * xstep + n * 128));
             }
         }
 #pragma unroll
@@ -169,42 +220,55 @@ __device__ __forceinline__ void chunk_mma(uint32_t stage, uint32_t xs_chunk, int
             const uint32_t a1 = pair_reg<NB>(Wb, f0), a3 = pair_reg<NB>(Wb, f0 + 1);
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
-                uint32_t lo, hi;                   // the two words holding x[f0 - 8i], x[f0 + 1 - 8i] and their partners
-                if (D == 2) { lo = xw[n][2 * h]; hi = xw[n][2 * h + 1]; }
-                else        { lo = xw[n][h];     hi = xw[n][h + 2]; }
-                const uint32_t b0 = __byte_perm(lo, hi, 0x5410), b1 = __byte_perm(lo, hi, 0x7632);
-                mma16816(acc[n], a0, a1, a2, a3, b0, b1);
+                if constexpr (D == 2 || DUAL) {
+                    mma16816(acc[n], a0, a1, a2, a3, xw[n][2 * h], xw[n][2 * h + 1]);
+                } else {
+                    // layout A words are (x0 x2)(x1 x3)(x4 x6)(x5 x7); distance-4 pairs are (x[2h] x[2h+4]), (x[2h+1] x[2h+5])
+                    const uint32_t sel = h == 0 ? 0x5410u : 0x7632u;
+                    mma16816(acc[n], a0, a1, a2, a3, __byte_perm(xw[n][0], xw[n][2], sel),
+                             __byte_perm(xw[n][1], xw[n][3], sel));
+                }
             }
         }
     }
 }
 
-// Position (in halves) of X[m, c] inside the staged activation array; c is relative to the CTA's first column.
-__device__ __forceinline__ int xs_index(int c, int m, int MP) {
-    const int chunk = c >> 7, t = (c >> 5) & 3, i = (c >> 3) & 3, e = c & 7;
-    return ((((chunk * 4 + i) * 4 + t) * MP + m) << 3) + e;
+// Activation layouts in shared memory.  A 16-byte slot holds the 8 activations of one token for one 8-column group;
+// slots are ordered (chunk, group-in-block i, block t, token).  Inside a slot the halves are permuted so that word
+// pairs are the B operands directly:  layout A (ids paired at distance 2): x0 x2 x1 x3 x4 x6 x5 x7;
+// layout B (distance 4): x0 x4 x1 x5 x2 x6 x3 x7.
+__device__ __forceinline__ int slot_of(int c, int m, int MP) {
+    const int chunk = c >> 7, t = (c >> 5) & 3, i = (c >> 3) & 3;
+    return ((chunk * 4 + i) * 4 + t) * MP + m;
+}
+__device__ __forceinline__ int pos_a(int e) { return (e & 4) | ((e & 1) << 1) | ((e >> 1) & 1); }
+// natural-order read of X[m, c] (c relative to the CTA's first column) from layout A
+__device__ __forceinline__ float xs_read(const __half *xs, int c, int m, int MP) {
+    return __half2float(xs[(slot_of(c, m, MP) << 3) + pos_a(c & 7)]);
 }
 
 template <int XT>
-__device__ __forceinline__ void stage_x8(const void *__restrict__ X, int64_t off, __half (&h)[8]) {
+__device__ __forceinline__ void stage_x8(const void *__restrict__ X, int64_t off, uint32_t (&h)[8]) {
+    // h[k] = fp16 bits of the k-th activation, saturated
     if constexpr (XT == QVB8_F16) {
         const uint4 u = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(X) + off));
-        const __half2 *p = reinterpret_cast<const __half2 *>(&u);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) { h[2 * k] = __low2half(p[k]); h[2 * k + 1] = __high2half(p[k]); }
+        for (int k = 0; k < 4; ++k) { h[2 * k] = w[k] & 0xffffu; h[2 * k + 1] = w[k] >> 16; }
     } else if constexpr (XT == QVB8_BF16) {
         const uint4 u = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(X) + off));
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            h[2 * k] = sat_half(__uint_as_float(w[k] << 16));
-            h[2 * k + 1] = sat_half(__uint_as_float(w[k] & 0xffff0000u));
+            h[2 * k] = __half_as_ushort(sat_half(__uint_as_float(w[k] << 16)));
+            h[2 * k + 1] = __half_as_ushort(sat_half(__uint_as_float(w[k] & 0xffff0000u)));
         }
     } else {
         const float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(X) + off));
         const float4 b = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(X) + off) + 1);
-        h[0] = sat_half(a.x); h[1] = sat_half(a.y); h[2] = sat_half(a.z); h[3] = sat_half(a.w);
-        h[4] = sat_half(b.x); h[5] = sat_half(b.y); h[6] = sat_half(b.z); h[7] = sat_half(b.w);
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) h[k] = __half_as_ushort(sat_half(v[k]));
     }
 }
 
@@ -218,18 +282,26 @@ struct SmallMParams {
     float *Y;          // (M, Q)
     float *part;       // (S, M, Q) partial sums when S > 1
     int *ticket;       // one counter per row block when S > 1 (zero on entry, zero on exit)
+    // escape plan (all null: escapes are corrected by a separate pass)
+    const int *esc_ptr;     // [Q + 1] first escape of each row
+    const int *esc_col;     // column of each escape
+    const float *esc_delta; // exact value - band value
     int Q, P, M, MP;   // MP: token slots per column group in shared memory (>= M)
     int S;             // K-ranges
     int nc_per;        // chunks per K-range (the last range may be shorter)
     int nc_total;      // P / 128
+    int debug;         // bit 0: skip the fragment math (copy stream only; tuning experiments)
 };
 
-template <int XT, int NT>
-__global__ void __launch_bounds__(NWARP * 32, 2) small_m_kernel(const SmallMParams p) {
+template <int XT, int NT, int NWARP>
+__global__ void __launch_bounds__(NWARP * 32, NWARP == 8 ? 2 : 4) small_m_kernel(const SmallMParams p) {
+    using TT = TileTable<NWARP>;
+    constexpr int RB = TT::RB;
+    constexpr int NTHREADS = NWARP * 32;
     extern __shared__ __align__(16) uint8_t smem[];
-    __shared__ TileTable tt;
+    __shared__ TT tt;
     uint8_t *ring = smem;                                              // NWARP * NST * STAGE_BYTES
-    __half *xs = reinterpret_cast<__half *>(smem + NWARP * NST * STAGE_BYTES);
+    __half *xs_a = reinterpret_cast<__half *>(smem + NWARP * NST * STAGE_BYTES);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int q0 = blockIdx.x * RB;
@@ -237,181 +309,247 @@ __global__ void __launch_bounds__(NWARP * 32, 2) small_m_kernel(const SmallMPara
     const int split = blockIdx.y;
     const int kc0 = split * p.nc_per;                                  // first chunk of this K-range
     const int NC = min(p.nc_per, p.nc_total - kc0);                    // chunks in this K-range (>= 1 by construction)
+    const int MP = p.MP;
+    constexpr bool DUAL = NT == 1;                                     // second activation layout (cheap for few tokens)
+    const int xs_halves = NC * 16 * MP * 8;                            // halves per activation layout
+    __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
 
-    // ---- 1. sort the block's rows by width into tiles (warp 0; stable, so the order is the same on every run)
+    // ---- 1. row metadata in one round trip, then sort the rows by width into tiles (stable: same order every run)
+    for (int r = tid; r < RB; r += NTHREADS) {
+        int cls = -1;
+        if (r < nrows) {
+            const int nb = __ldg(p.nbits + q0 + r);
+            const int64_t bo = __ldg(p.bit_off + q0 + r);
+            tt.row_ms[r] = __ldg(p.min_s + q0 + r);
+            tt.row_ts[r] = __ldg(p.tau_s + q0 + r);
+            tt.row_b16[r] = (uint32_t)(bo >> 7);
+            tt.row_nb[r] = (uint8_t)nb;
+            cls = (nb >= 3 && nb <= 8 && (bo & 127) == 0) ? nb - 3 : NCLASS - 1;     // 16-byte aligned row start
+        }
+        tt.row_cls[r] = (int8_t)cls;
+    }
+    __syncthreads();
     if (warp == 0) {
         int cnt[NCLASS];
 #pragma unroll
         for (int c = 0; c < NCLASS; ++c) cnt[c] = 0;
         for (int r0 = 0; r0 < RB; r0 += 32) {
             const int r = r0 + lane;
-            int cls = -1;
-            if (r < nrows) {
-                const int nb = __ldg(p.nbits + q0 + r);
-                const bool byte16 = (__ldg(p.bit_off + q0 + r) & 127) == 0;      // row starts on a 16-byte boundary
-                cls = (nb >= 3 && nb <= 8 && byte16) ? nb - 3 : NCLASS - 1;
-            }
+            const int cls = tt.row_cls[r];
 #pragma unroll
             for (int c = 0; c < NCLASS; ++c) {
                 const uint32_t mk = __ballot_sync(0xffffffffu, cls == c);
-                if (cls == c) tt.list[c][cnt[c] + __popc(mk & ((1u << lane) - 1u))] = r;
+                if (cls == c) tt.list[c][cnt[c] + __popc(mk & ((1u << lane) - 1u))] = (int16_t)r;
                 cnt[c] += __popc(mk);
             }
         }
         __syncwarp();
-        int nt = 0;
+        int nt = 0, need_b = 0;
 #pragma unroll
         for (int c = 0; c < NCLASS; ++c) {
+            if (c < 3 && cnt[c] > 0) need_b = 1;                          // widths 3, 4, 5 pair at distance 4
             for (int i0 = 0; i0 < cnt[c]; i0 += 16) {
-                if (lane < 16) {
-                    const int i = i0 + lane;
-                    int row = -1; uint32_t b16 = 0; float ms = 0.f, ts = 0.f;
-                    if (i < cnt[c]) {
-                        row = q0 + tt.list[c][i];
-                        b16 = (uint32_t)(__ldg(p.bit_off + row) >> 7);
-                        ms = __ldg(p.min_s + row); ts = __ldg(p.tau_s + row);
-                    }
-                    tt.row[nt][lane] = row; tt.base16[nt][lane] = b16; tt.ms[nt][lane] = ms; tt.ts[nt][lane] = ts;
+                if (lane < 16) tt.tile_row[nt][lane] = (i0 + lane < cnt[c]) ? tt.list[c][i0 + lane] : (int16_t)-1;
+                if (lane == 0) {
+                    tt.tile_nb[nt] = (int8_t)(c == NCLASS - 1 ? 0 : c + 3);
+                    tt.tile_cnt[nt] = (int8_t)min(16, cnt[c] - i0);
                 }
-                if (lane == 0) { tt.tile_nb[nt] = c == NCLASS - 1 ? 0 : c + 3; tt.tile_cnt[nt] = min(16, cnt[c] - i0); }
                 ++nt;
             }
         }
-        if (lane == 0) tt.ntiles = nt;
+        if (lane == 0) { tt.ntiles = nt; tt.need_b = need_b; }
     }
     __syncthreads();
 
-    // ---- 2. per-warp unit list (tile, chunk) and the first NST - 1 copies (weights do not depend on X)
+    // ---- 2. copy stream of this warp: tiles warp, warp + NWARP, ...; chunk after chunk, NST - 1 chunks ahead
     const int ntiles = tt.ntiles;
     const int n_my = warp < ntiles ? (ntiles - warp + NWARP - 1) / NWARP : 0;
-    const int units = n_my * NC;
     const uint32_t ring_w = smem_u32(ring + warp * NST * STAGE_BYTES);
-    auto issue = [&](int u) {
-        const int tile = warp + (u / NC) * NWARP, chunk = u - (u / NC) * NC;
-        const int nb = tt.tile_nb[tile];
-        if (nb == 0) return;                                            // per-element class reads global memory itself
-        const int pieces = tt.tile_cnt[tile] * nb;                      // 16-byte pieces of this row-chunk set
-        const uint32_t magic = (65536u + nb - 1) / nb;
-        const int RS = row_stride(nb);
-        const uint32_t dst0 = ring_w + (u % NST) * STAGE_BYTES;
-        for (int pc = lane; pc < pieces; pc += 32) {
-            const int r = (int)((pc * magic) >> 16), j = pc - r * nb;
-            const uint8_t *src = p.ids + ((int64_t)tt.base16[tile][r] + (int64_t)(kc0 + chunk) * nb + j) * 16;
-            cp_async16(dst0 + r * RS + j * 16, src);
+    // prefetch-side state: the tile being copied, its chunk cursor, and this lane's (up to 4) 16-byte pieces
+    int pf_ti = 0, pf_c = 0, pf_nb = 0;
+    uint32_t pf_off[4], pf_dst[4];
+    bool pf_ok[4];
+    auto pf_setup = [&]() {
+        if (pf_ti >= n_my) return;
+        const int tile = warp + pf_ti * NWARP;
+        pf_nb = tt.tile_nb[tile];
+        const int pieces = tt.tile_cnt[tile] * pf_nb;                   // 0 for the per-element class
+        const uint32_t magic = pf_nb ? (65536u + pf_nb - 1) / pf_nb : 0u;
+        const int RS = row_stride(pf_nb);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int pc = lane + 32 * k;
+            pf_ok[k] = pc < pieces;
+            const int r = (int)((pc * magic) >> 16), j = pc - r * pf_nb;
+            const int lr = pf_ok[k] ? tt.tile_row[tile][r] : 0;
+            pf_off[k] = tt.row_b16[lr] + (uint32_t)(kc0 * pf_nb + j);
+            pf_dst[k] = (uint32_t)(r * RS + j * 16);
         }
     };
+    auto pf_issue = [&](int slot) {
+        if (pf_ti < n_my) {
+            const uint32_t dst0 = ring_w + slot * STAGE_BYTES;
 #pragma unroll
-    for (int u = 0; u < NST - 1; ++u) {
-        if (u < units) issue(u);
+            for (int k = 0; k < 4; ++k) {
+                if (pf_ok[k]) cp_async16(dst0 + pf_dst[k], p.ids + (uint64_t)pf_off[k] * 16u);
+                pf_off[k] += (uint32_t)pf_nb;
+            }
+            if (++pf_c == NC) { pf_c = 0; ++pf_ti; pf_setup(); }
+        }
         cp_async_commit();
-    }
+    };
+    pf_setup();
+#pragma unroll
+    for (int s = 0; s < NST - 1; ++s) pf_issue(s);
 
-    // ---- 3. stage the activations of this K-range as fp16 in fragment order; per-token sums
+    // ---- 3. activations of this K-range as fp16 in fragment order (after the previous kernel in the stream is done)
+    pdl_wait();
     {
-        const int MP = p.MP, groups = NC * 16;                          // 8-column groups in the range
+        const int groups = NC * 16;                                     // 8-column groups in the range
         const int64_t col0 = (int64_t)kc0 * KC;
-        for (int idx = tid; idx < MP * groups; idx += NWARP * 32) {
+        const bool need_b = DUAL && tt.need_b != 0;
+        for (int idx = tid; idx < MP * groups; idx += NTHREADS) {
             const int m = idx / groups, u8 = idx - m * groups;         // u8: natural 8-column group number
-            __half h[8];
+            uint32_t h[8];
             if (m < p.M) {
                 stage_x8<XT>(p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h);
             } else {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) h[k] = __float2half_rn(0.f);
+                for (int k = 0; k < 8; ++k) h[k] = 0u;
             }
-            uint4 v;
-            __half2 h01 = __halves2half2(h[0], h[1]), h23 = __halves2half2(h[2], h[3]);
-            __half2 h45 = __halves2half2(h[4], h[5]), h67 = __halves2half2(h[6], h[7]);
-            v.x = *reinterpret_cast<uint32_t *>(&h01); v.y = *reinterpret_cast<uint32_t *>(&h23);
-            v.z = *reinterpret_cast<uint32_t *>(&h45); v.w = *reinterpret_cast<uint32_t *>(&h67);
-            *reinterpret_cast<uint4 *>(xs + xs_index(u8 * 8, m, MP)) = v;
+            const int slot = slot_of(u8 * 8, m, MP);
+            *reinterpret_cast<uint4 *>(xs_a + (slot << 3)) =
+                make_uint4(h[0] | (h[2] << 16), h[1] | (h[3] << 16), h[4] | (h[6] << 16), h[5] | (h[7] << 16));
+            if (need_b)
+                *reinterpret_cast<uint4 *>(xs_b + (slot << 3)) =
+                    make_uint4(h[0] | (h[4] << 16), h[1] | (h[5] << 16), h[2] | (h[6] << 16), h[3] | (h[7] << 16));
         }
         __syncthreads();
         for (int m = warp; m < p.M; m += NWARP) {                       // fixed-order sums: same bits every run
             float s = 0.f;
-            for (int c = lane; c < NC * KC; c += 32) s += __half2float(xs[xs_index(c, m, MP)]);
+            for (int c = lane; c < NC * KC; c += 32) s += xs_read(xs_a, c, m, MP);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
             if (lane == 0) tt.sumx[m] = s;
         }
         __syncthreads();
     }
+    pdl_launch_dependents();
 
     // ---- 4. stream the tiles
     float *out = p.S > 1 ? p.part + (int64_t)split * p.M * p.Q : p.Y;
-    const uint32_t xs_u32 = smem_u32(xs);
     const int g = lane >> 2, t = lane & 3;
-    float acc[NT][4];
-    for (int u = 0; u < units; ++u) {
-        if (u + NST - 1 < units) issue(u + NST - 1);
-        cp_async_commit();
-        cp_async_wait<NST - 1>();
-        __syncwarp();
-        const int tile = warp + (u / NC) * NWARP, chunk = u - (u / NC) * NC;
+    const uint32_t xstep = (uint32_t)(4 * MP * 16);                     // bytes between consecutive 8-column groups
+    const uint32_t xchunk = 4 * xstep;                                  // bytes per chunk
+    const bool xvalid = g < MP;                                         // NT == 1: lanes of token slots that exist
+    const uint32_t xoff = (uint32_t)((t * MP + (xvalid ? g : 0)) * 16);
+    const uint32_t xs_a32 = smem_u32(xs_a) + xoff, xs_b32 = smem_u32(xs_b) + xoff;
+    int slot = 0;
+    for (int ti = 0; ti < n_my; ++ti) {
+        const int tile = warp + ti * NWARP;
         const int nb = tt.tile_nb[tile];
-        if (chunk == 0) {
+        const int RS = row_stride(nb);
+        const uint32_t wa_off = (uint32_t)(g * RS + t * 4 * nb), wb_off = wa_off + 8 * RS;
+        const uint32_t xbase = nb >= 6 ? xs_a32 : xs_b32;
+        float acc[NT][4];
 #pragma unroll
-            for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+        for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+        for (int chunk = 0; chunk < NC; ++chunk) {
+            pf_issue(slot == 0 ? NST - 1 : slot - 1);                   // refill the slot consumed last
+            cp_async_wait<NST - 1>();
+            __syncwarp();
+            const uint32_t stage = ring_w + slot * STAGE_BYTES;
+            const uint32_t xa = xbase + chunk * xchunk;
+            if (!(p.debug & 1))
+            switch (nb) {                                               // warp-uniform
+                case 7: chunk_mma<7, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
+                case 6: chunk_mma<6, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
+                case 8: chunk_mma<8, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
+                case 5: chunk_mma<5, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
+                case 4: chunk_mma<4, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
+                case 3: chunk_mma<3, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
+                default: break;
+            }
+            __syncwarp();
+            slot = slot == NST - 1 ? 0 : slot + 1;
         }
-        const uint32_t stage = ring_w + (u % NST) * STAGE_BYTES;
-        const uint32_t xs_chunk = xs_u32 + (uint32_t)(chunk * 16 * p.MP * 16);
-        switch (nb) {                                                   // warp-uniform
-            case 8: chunk_mma<8, NT>(stage, xs_chunk, p.MP, lane, acc); break;
-            case 7: chunk_mma<7, NT>(stage, xs_chunk, p.MP, lane, acc); break;
-            case 6: chunk_mma<6, NT>(stage, xs_chunk, p.MP, lane, acc); break;
-            case 5: chunk_mma<5, NT>(stage, xs_chunk, p.MP, lane, acc); break;
-            case 4: chunk_mma<4, NT>(stage, xs_chunk, p.MP, lane, acc); break;
-            case 3: chunk_mma<3, NT>(stage, xs_chunk, p.MP, lane, acc); break;
-            default: break;
-        }
-        if (chunk == NC - 1) {
-            if (nb != 0) {
-                // y = tau_s * sum(x * id) + min_s * sum(x); thread holds rows g, g+8 and tokens 8n+2t, 8n+2t+1
+        // ---- tile epilogue
+        if (nb != 0) {
+            // y = tau_s * sum(x * id) + min_s * sum(x); thread holds rows g, g+8 and tokens 8n+2t, 8n+2t+1
 #pragma unroll
-                for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int rr = g + 8 * hrow;
-                    const int q = tt.row[tile][rr];
-                    if (q >= 0) {
-                        const float ms = tt.ms[tile][rr], ts = tt.ts[tile][rr];
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int lr = tt.tile_row[tile][g + 8 * hrow];
+                if (lr >= 0) {
+                    const float ms = tt.row_ms[lr], ts = tt.row_ts[lr];
+                    const int q = q0 + lr;
 #pragma unroll
-                        for (int n = 0; n < NT; ++n) {
+                    for (int n = 0; n < NT; ++n) {
 #pragma unroll
-                            for (int k = 0; k < 2; ++k) {
-                                const int m = 8 * n + 2 * t + k;
-                                if (m < p.M) out[(int64_t)m * p.Q + q] = __fmaf_rn(ts, acc[n][2 * hrow + k], ms * tt.sumx[m]);
-                            }
-                        }
-                    }
-                }
-            } else {
-                // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
-                // start on a 16-byte boundary).  One row at a time, ids byte-wise from global memory.
-                for (int rr = 0; rr < tt.tile_cnt[tile]; ++rr) {
-                    const int q = tt.row[tile][rr];
-                    const int rnb = __ldg(p.nbits + q);
-                    const int64_t base = __ldg(p.bit_off + q) + (int64_t)kc0 * KC * rnb;
-                    const float ms = tt.ms[tile][rr], ts = tt.ts[tile][rr];
-                    for (int m0 = 0; m0 < p.M; m0 += 8) {
-                        float a[8];
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) a[k] = 0.f;
-                        for (int c = lane; c < NC * KC; c += 32) {
-                            const float wv = band(field_bytes(p.ids, base + (int64_t)c * rnb, rnb), ts, ms);
-#pragma unroll
-                            for (int k = 0; k < 8; ++k)
-                                if (m0 + k < p.M) a[k] = __fmaf_rn(__half2float(xs[xs_index(c, m0 + k, p.MP)]), wv, a[k]);
-                        }
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-#pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
-                            if (lane == 0 && m0 + k < p.M) out[(int64_t)(m0 + k) * p.Q + q] = a[k];
+                        for (int k = 0; k < 2; ++k) {
+                            const int m = 8 * n + 2 * t + k;
+                            if (m < p.M) out[(int64_t)m * p.Q + q] = __fmaf_rn(ts, acc[n][2 * hrow + k], ms * tt.sumx[m]);
                         }
                     }
                 }
             }
+        } else {
+            // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
+            // start on a 16-byte boundary).  One row at a time, ids byte-wise from global memory.
+            for (int rr = 0; rr < tt.tile_cnt[tile]; ++rr) {
+                const int lr = tt.tile_row[tile][rr];
+                const int q = q0 + lr;
+                const int rnb = tt.row_nb[lr];
+                const int64_t base = __ldg(p.bit_off + q) + (int64_t)kc0 * KC * rnb;
+                const float ms = tt.row_ms[lr], ts = tt.row_ts[lr];
+                for (int m0 = 0; m0 < p.M; m0 += 8) {
+                    float a[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) a[k] = 0.f;
+                    for (int c = lane; c < NC * KC; c += 32) {
+                        const float wv = band(field_bytes(p.ids, base + (int64_t)c * rnb, rnb), ts, ms);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c, m0 + k, MP), wv, a[k]);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
+                        if (lane == 0 && m0 + k < p.M) out[(int64_t)(m0 + k) * p.Q + q] = a[k];
+                    }
+                }
+            }
         }
-        __syncwarp();
+        // ---- escapes of the tile's rows that fall in this K-range: lane r walks row r's list in stored order
+        if (p.esc_ptr != nullptr) {
+            __syncwarp();                                               // the tile's results are written
+            const int lr = lane < 16 ? tt.tile_row[tile][lane] : -1;
+            if (lr >= 0) {
+                const int q = q0 + lr;
+                const int e0 = __ldg(p.esc_ptr + q), e1 = __ldg(p.esc_ptr + q + 1);
+                const int clo = kc0 * KC, chi = clo + NC * KC;
+                for (int m0 = 0; m0 < p.M; m0 += 8) {
+                    float a[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) a[k] = 0.f;
+                    bool any = false;
+                    for (int e = e0; e < e1; ++e) {
+                        const int c = __ldg(p.esc_col + e);
+                        if (c < clo || c >= chi) continue;
+                        any = true;
+                        const float d = __ldg(p.esc_delta + e);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c - clo, m0 + k, MP), d, a[k]);
+                    }
+                    if (any) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            if (m0 + k < p.M) out[(int64_t)(m0 + k) * p.Q + q] += a[k];
+                    }
+                }
+            }
+        }
     }
     cp_async_wait<0>();
 
@@ -426,7 +564,7 @@ __global__ void __launch_bounds__(NWARP * 32, 2) small_m_kernel(const SmallMPara
         __syncthreads();
         if (tt.is_last) {
             __threadfence();
-            for (int idx = tid; idx < p.M * nrows; idx += NWARP * 32) {
+            for (int idx = tid; idx < p.M * nrows; idx += NTHREADS) {
                 const int m = idx / nrows, r = idx - m * nrows;
                 const int64_t o = (int64_t)m * p.Q + q0 + r;
                 float s = 0.f;
@@ -439,11 +577,40 @@ __global__ void __launch_bounds__(NWARP * 32, 2) small_m_kernel(const SmallMPara
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// escape plan
+
+__global__ void __launch_bounds__(256) escape_plan_kernel(const uint8_t *__restrict__ ids, const float *__restrict__ min_s,
+                                                          const float *__restrict__ tau_s,
+                                                          const uint8_t *__restrict__ nbits,
+                                                          const int64_t *__restrict__ bit_off,
+                                                          const int64_t *__restrict__ esc_idx,
+                                                          const float *__restrict__ esc_vals, int64_t n_esc, int Q, int P,
+                                                          int *__restrict__ esc_ptr, int *__restrict__ esc_col,
+                                                          float *__restrict__ esc_delta) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_esc) {
+        const int64_t f = __ldg(esc_idx + i);
+        const int q = (int)(f / P), c = (int)(f - (int64_t)q * P);
+        const int nb = __ldg(nbits + q);
+        const float b = band(field_bytes(ids, __ldg(bit_off + q) + (int64_t)c * nb, nb), __ldg(tau_s + q), __ldg(min_s + q));
+        esc_col[i] = c;
+        esc_delta[i] = __ldg(esc_vals + i) - b;
+        // esc_idx ascends: this escape opens every row after the previous escape's row, up to its own
+        const int qprev = i == 0 ? -1 : (int)(__ldg(esc_idx + i - 1) / P);
+        for (int r = qprev + 1; r <= q; ++r) esc_ptr[r] = (int)i;
+        if (i == n_esc - 1)
+            for (int r = q + 1; r <= Q; ++r) esc_ptr[r] = (int)n_esc;
+    } else if (i == 0 && n_esc == 0) {
+        for (int r = 0; r <= Q; ++r) esc_ptr[r] = 0;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // host side
 
 struct Plan {
-    int nblk, S, nc_per, nc_total, MP, NT;
-    size_t xs_bytes, smem_bytes;
+    int nwarp, rb, nblk, S, nc_per, nc_total, MP, NT;
+    size_t smem_bytes;
     int64_t part_bytes, ticket_bytes;
 };
 
@@ -458,18 +625,28 @@ static int device_sms() {
     return n;
 }
 
+static int g_force_nwarp = 0;   // test / tuning hook (qvb8_small_m_set_tuning)
+static int g_fill_x = 3;        // CTAs wanted per SM when choosing the K split
+static int g_debug = 0;
+
 static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     Plan pl{};
-    pl.nblk = (int)((Q + RB - 1) / RB);
     pl.nc_total = (int)(P / KC);
     pl.NT = (int)((M + 7) / 8);
     pl.MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * pl.NT;
-    // K-range length: bounded by the shared memory the staged activations may take ...
-    int nc_max = XS_MAX_BYTES / (KC * pl.MP * 2);
+    const int sms = device_sms();
+    // small outputs: 64-row CTAs of 4 warps give the scheduler twice as many, half as heavy, pieces
+    pl.nwarp = g_force_nwarp ? g_force_nwarp : (Q * (int64_t)pl.nc_total <= (int64_t)sms * 16 * 64 ? 4 : 8);
+    pl.rb = 16 * pl.nwarp;
+    pl.nblk = (int)((Q + pl.rb - 1) / pl.rb);
+    // K-range length: bounded by the shared memory the staged activations may take (two layouts) ...
+    const int layouts = pl.NT == 1 ? 2 : 1;
+    const int xs_budget = pl.NT >= 3 ? 2 * XS_MAX_BYTES : XS_MAX_BYTES;
+    int nc_max = xs_budget / (KC * pl.MP * 2 * layouts);
     if (nc_max < 1) nc_max = 1;
     int S = (pl.nc_total + nc_max - 1) / nc_max;
-    // ... and short enough that the grid fills the GPU about three times over, but not below 4 chunks per range
-    const int want = (3 * device_sms() + pl.nblk - 1) / (pl.nblk > 0 ? pl.nblk : 1);
+    // ... and short enough that the grid fills the GPU a few times over, but not below 4 chunks per range
+    const int want = (g_fill_x * sms + pl.nblk - 1) / (pl.nblk > 0 ? pl.nblk : 1);
     int s_fill = want;
     const int s_cap = pl.nc_total / 4 > 0 ? pl.nc_total / 4 : 1;
     if (s_fill > s_cap) s_fill = s_cap;
@@ -478,64 +655,106 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     if (pl.nblk > MAX_TICKET_BLOCKS) S = (pl.nc_total + nc_max - 1) / nc_max;   // more row blocks than counters
     pl.nc_per = (pl.nc_total + S - 1) / S;
     pl.S = (pl.nc_total + pl.nc_per - 1) / pl.nc_per;                   // no empty range
-    pl.xs_bytes = (size_t)pl.nc_per * KC * pl.MP * 2;
-    pl.smem_bytes = (size_t)NWARP * NST * STAGE_BYTES + pl.xs_bytes;
+    pl.smem_bytes = (size_t)pl.nwarp * NST * STAGE_BYTES + (size_t)pl.nc_per * KC * pl.MP * 2 * layouts;
     pl.part_bytes = pl.S > 1 ? (int64_t)pl.S * M * Q * 4 : 0;
     pl.part_bytes = (pl.part_bytes + 255) / 256 * 256;
     pl.ticket_bytes = pl.S > 1 ? TICKET_BYTES : 0;
     return pl;
 }
 
-static bool fast_layout_ok(const qvb8_pack *w, const void *X, int x_dtype) {
-    return w->P > 0 && w->P % KC == 0 && aligned(w->ids, 16) && aligned(X, 16) &&
-           (x_dtype != QVB8_F32 || aligned(X, 16));
+static bool fast_layout_ok(const qvb8_pack *w, const void *X) {
+    return w->P > 0 && w->P % KC == 0 && aligned(w->ids, 16) && aligned(X, 16);
 }
 
-template <int XT, int NT>
-static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st) {
-    auto kern = small_m_kernel<XT, NT>;
-    static thread_local size_t granted = 0;
+template <int XT, int NT, int NWARP>
+static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
+    auto kern = small_m_kernel<XT, NT, NWARP>;
     static thread_local int granted_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
-    if (pl.smem_bytes > granted || dev != granted_dev) {
+    if (dev != granted_dev) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024)) != cudaSuccess)
             return cuda_status("qvb8_small_m: shared memory opt-in");
-        granted = 200 * 1024;
         granted_dev = dev;
     }
-    kern<<<dim3(pl.nblk, pl.S), NWARP * 32, pl.smem_bytes, st>>>(prm);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(pl.nblk, pl.S);
+    cfg.blockDim = dim3(NWARP * 32);
+    cfg.dynamicSmemBytes = pl.smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kern, prm) != cudaSuccess) return cuda_status("qvb8_small_m launch");
     return cuda_status("qvb8_small_m launch");
 }
 
-template <int XT>
-static int launch_nt(const SmallMParams &prm, const Plan &pl, cudaStream_t st) {
+template <int XT, int NWARP>
+static int launch_nt(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
     switch (pl.NT) {
-        case 1: return launch_one<XT, 1>(prm, pl, st);
-        case 2: return launch_one<XT, 2>(prm, pl, st);
-        case 3: return launch_one<XT, 3>(prm, pl, st);
-        case 4: return launch_one<XT, 4>(prm, pl, st);
-        case 5: return launch_one<XT, 5>(prm, pl, st);
-        default: return launch_one<XT, 6>(prm, pl, st);
+        case 1: return launch_one<XT, 1, NWARP>(prm, pl, st, pdl);
+        case 2: return launch_one<XT, 2, NWARP>(prm, pl, st, pdl);
+        case 3: return launch_one<XT, 3, NWARP>(prm, pl, st, pdl);
+        case 4: return launch_one<XT, 4, NWARP>(prm, pl, st, pdl);
+        case 5: return launch_one<XT, 5, NWARP>(prm, pl, st, pdl);
+        default: return launch_one<XT, 6, NWARP>(prm, pl, st, pdl);
     }
+}
+
+template <int XT>
+static int launch_nw(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
+    return pl.nwarp == 4 ? launch_nt<XT, 4>(prm, pl, st, pdl) : launch_nt<XT, 8>(prm, pl, st, pdl);
 }
 
 }  // namespace qv
 
+QV_API void qvb8_small_m_set_tuning(int nwarp, int fill) {
+    qv::g_force_nwarp = (nwarp == 4 || nwarp == 8) ? nwarp : 0;
+    qv::g_fill_x = fill > 0 ? (fill & 0xff) : 3;
+    qv::g_debug = fill > 0 ? (fill >> 8) : 0;
+}
+
 QV_API int64_t qvb8_small_m_scratch_bytes(int64_t M, int64_t Q, int64_t P) {
     using namespace qv;
-    if (M < 1 || M > 48 || Q <= 0 || P <= 0 || P % KC != 0) return 0;
+    if (M < 1 || M > MAX_M || Q <= 0 || P <= 0 || P % KC != 0) return 0;
     const Plan pl = make_plan(M, Q, P);
     return pl.part_bytes + pl.ticket_bytes;
 }
 
-QV_API int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,
-                        int64_t scratch_bytes, void *stream) {
+QV_API int64_t qvb8_escape_plan_bytes(int64_t Q, int64_t n_esc) {
+    if (Q < 0 || n_esc < 0) return 0;
+    const int64_t ptr = ((Q + 1) * 4 + 255) / 256 * 256, col = (n_esc * 4 + 255) / 256 * 256;
+    return ptr + 2 * col;
+}
+
+QV_API int qvb8_escape_plan(const qvb8_pack *w, void *plan, int64_t plan_bytes, void *stream) {
+    using namespace qv;
+    if (int rc = check_pack(w, "qvb8_escape_plan")) return rc;
+    if (int rc = check_device("qvb8_escape_plan")) return rc;
+    if (w->n_esc > 0x7fffffff) return fail(QVB8_ERR_ARG, "qvb8_escape_plan: more than 2^31 escapes");
+    if (!plan || plan_bytes < qvb8_escape_plan_bytes(w->Q, w->n_esc) || !aligned(plan, 16))
+        return fail(QVB8_ERR_SCRATCH, "qvb8_escape_plan: plan buffer missing, unaligned or smaller than %lld bytes",
+                    (long long)qvb8_escape_plan_bytes(w->Q, w->n_esc));
+    const int64_t ptr_b = ((w->Q + 1) * 4 + 255) / 256 * 256, col_b = (w->n_esc * 4 + 255) / 256 * 256;
+    int *esc_ptr = reinterpret_cast<int *>(plan);
+    int *esc_col = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(plan) + ptr_b);
+    float *esc_delta = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(plan) + ptr_b + col_b);
+    const int64_t n = w->n_esc > 0 ? w->n_esc : 1;
+    escape_plan_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        w->ids, w->min_s, w->tau_s, w->nbits, w->bit_off, w->esc_idx, w->esc_vals, w->n_esc, (int)w->Q, (int)w->P, esc_ptr,
+        esc_col, esc_delta);
+    return cuda_status("qvb8_escape_plan launch");
+}
+
+QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *esc_plan, const void *X, int x_dtype, int x_mode, int64_t M,
+                           float *Y, void *scratch, int64_t scratch_bytes, int flags, void *stream) {
     using namespace qv;
     if (int rc = check_small_m_args(w, X, x_dtype, x_mode, M, Y, "qvb8_small_m")) return rc;
     if (w->Q == 0) return QVB8_OK;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (x_mode != 0 || !fast_layout_ok(w, X, x_dtype))
+    if (x_mode != 0 || !fast_layout_ok(w, X))
         return launch_small_m_generic(w, X, x_dtype, x_mode, (int)M, Y, st);
     const Plan pl = make_plan(M, w->Q, w->P);
     if (pl.part_bytes + pl.ticket_bytes > 0) {
@@ -544,20 +763,36 @@ QV_API int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mo
                         (long long)(pl.part_bytes + pl.ticket_bytes), (long long)scratch_bytes);
         if (!aligned(scratch, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: scratch must be 16-byte aligned");
     }
-    SmallMParams prm{};
-    prm.ids = w->ids; prm.min_s = w->min_s; prm.tau_s = w->tau_s; prm.nbits = w->nbits; prm.bit_off = w->bit_off;
-    prm.X = X; prm.Y = Y;
     if (pl.S > 1 && pl.nblk > MAX_TICKET_BLOCKS)
         return fail(QVB8_ERR_ARG, "qvb8_small_m: %d row blocks with a split K-range exceed the %d ticket counters",
                     pl.nblk, MAX_TICKET_BLOCKS);
+    SmallMParams prm{};
+    prm.ids = w->ids; prm.min_s = w->min_s; prm.tau_s = w->tau_s; prm.nbits = w->nbits; prm.bit_off = w->bit_off;
+    prm.X = X; prm.Y = Y;
     prm.ticket = reinterpret_cast<int *>(scratch);
     prm.part = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + TICKET_BYTES);
+    const bool planned = esc_plan != nullptr && w->n_esc > 0;
+    if (planned) {
+        if (!aligned(esc_plan, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: escape plan must be 16-byte aligned");
+        const int64_t ptr_b = ((w->Q + 1) * 4 + 255) / 256 * 256, col_b = (w->n_esc * 4 + 255) / 256 * 256;
+        prm.esc_ptr = reinterpret_cast<const int *>(esc_plan);
+        prm.esc_col = reinterpret_cast<const int *>(reinterpret_cast<const uint8_t *>(esc_plan) + ptr_b);
+        prm.esc_delta = reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(esc_plan) + ptr_b + col_b);
+    }
     prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.S = pl.S; prm.nc_per = pl.nc_per;
     prm.nc_total = pl.nc_total;
+    prm.debug = g_debug;
+    const bool pdl = (flags & QVB8_FLAG_PDL) != 0;
     int rc;
-    if (x_dtype == QVB8_F16) rc = launch_nt<QVB8_F16>(prm, pl, st);
-    else if (x_dtype == QVB8_BF16) rc = launch_nt<QVB8_BF16>(prm, pl, st);
-    else rc = launch_nt<QVB8_F32>(prm, pl, st);
+    if (x_dtype == QVB8_F16) rc = launch_nw<QVB8_F16>(prm, pl, st, pdl);
+    else if (x_dtype == QVB8_BF16) rc = launch_nw<QVB8_BF16>(prm, pl, st, pdl);
+    else rc = launch_nw<QVB8_F32>(prm, pl, st, pdl);
     if (rc) return rc;
+    if (planned || w->n_esc == 0) return QVB8_OK;
     return launch_fix_escapes(w, X, x_dtype, x_mode, (int)M, Y, st);
+}
+
+QV_API int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,
+                        int64_t scratch_bytes, void *stream) {
+    return qvb8_small_m_ex(w, nullptr, X, x_dtype, x_mode, M, Y, scratch, scratch_bytes, 0, stream);
 }

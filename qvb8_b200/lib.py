@@ -22,7 +22,7 @@ _CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
 # every symbol include/qvb8_b200.h declares
 EXPORTS = (
     "qvb8_last_error", "qvb8_version", "qvb8_decode", "qvb8_small_m_scratch_bytes", "qvb8_small_m",
-    "qvb8_small_m_generic",
+    "qvb8_small_m_generic", "qvb8_escape_plan_bytes", "qvb8_escape_plan", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
 )
 
 
@@ -60,6 +60,12 @@ def load() -> ctypes.CDLL:
             lib.qvb8_small_m_scratch_bytes.restype = i64
             lib.qvb8_small_m.argtypes = [pk, vp, ci, ci, i64, vp, vp, i64, vp]
             lib.qvb8_small_m_generic.argtypes = [pk, vp, ci, ci, i64, vp, vp]
+            lib.qvb8_escape_plan_bytes.argtypes = [i64, i64]
+            lib.qvb8_escape_plan_bytes.restype = i64
+            lib.qvb8_escape_plan.argtypes = [pk, vp, i64, vp]
+            lib.qvb8_small_m_ex.argtypes = [pk, vp, vp, ci, ci, i64, vp, vp, i64, ci, vp]
+            lib.qvb8_small_m_set_tuning.argtypes = [ci, ci]
+            lib.qvb8_small_m_set_tuning.restype = None
             _lib = lib
     return _lib
 
@@ -153,7 +159,24 @@ def decode(pack, keep, out_dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
-def small_m(pack, keep, X: torch.Tensor, x_mode: int = 0, generic: bool = False, out: torch.Tensor | None = None):
+FLAG_PDL = 1
+
+
+def escape_plan(pack, keep) -> torch.Tensor | None:
+    """Device buffer holding the pack's escapes regrouped by row with precomputed differences (None if no escapes)."""
+    if pack.n_esc == 0:
+        return None
+    dev = keep[0].device
+    lib = load()
+    nbytes = int(lib.qvb8_escape_plan_bytes(pack.Q, pack.n_esc))
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.qvb8_escape_plan(ctypes.byref(pack), buf.data_ptr(), nbytes, stream_ptr(dev)), "qvb8_escape_plan")
+    return buf
+
+
+def small_m(pack, keep, X: torch.Tensor, x_mode: int = 0, generic: bool = False, out: torch.Tensor | None = None,
+            plan: torch.Tensor | None = None, flags: int = 0):
     """(M, Q) fp32 = X (M, P) @ W^T through the fused kernel (M <= 48)."""
     dev = keep[0].device
     if not X.is_cuda or X.device != dev:
@@ -171,8 +194,9 @@ def small_m(pack, keep, X: torch.Tensor, x_mode: int = 0, generic: bool = False,
         else:
             nbytes = int(lib.qvb8_small_m_scratch_bytes(M, pack.Q, pack.P))
             sc = scratch_for(dev, nbytes)
-            rc = lib.qvb8_small_m(ctypes.byref(pack), X.data_ptr(), dtype_code(X.dtype), x_mode, M, Y.data_ptr(),
-                                  sc.data_ptr() if sc is not None else None, sc.numel() if sc is not None else 0,
-                                  stream_ptr(dev))
+            rc = lib.qvb8_small_m_ex(ctypes.byref(pack), plan.data_ptr() if plan is not None else None, X.data_ptr(),
+                                     dtype_code(X.dtype), x_mode, M, Y.data_ptr(),
+                                     sc.data_ptr() if sc is not None else None, sc.numel() if sc is not None else 0,
+                                     flags, stream_ptr(dev))
     check(rc, "qvb8_small_m")
     return Y

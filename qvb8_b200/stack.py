@@ -83,7 +83,8 @@ class LinearStack:
                 del W
                 st, keep = _lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx,
                                             pk.esc_vals)
-                row.append((name, pk, st, keep, xname))
+                plan = _lib.escape_plan(st, keep)
+                row.append((name, pk, st, keep + [plan], xname))
                 self.compressed_bytes += pk.weight_bytes()
                 self.n_weights += pk.Q * pk.P
                 self.n_escapes += int(pk.esc_idx.numel())
@@ -100,7 +101,8 @@ class LinearStack:
             for _, pk, *_ in row:
                 _lib.reserve_scratch(self.device, self.M, pk.Q, pk.P)
         self.graph = None
-        self.launches_per_step = sum((1 + (1 if pk.esc_idx.numel() else 0)) for row in self.packs for _, pk, *_ in row)
+        self.launches_per_step = sum(1 for row in self.packs for _ in row)
+        self.pdl = True
         self._host_in = self._host_out = None
 
     # ---- execution ------------------------------------------------------------------------------------
@@ -108,7 +110,8 @@ class LinearStack:
         """One pass over every projection on the current stream (one fused launch each, plus the escape pass)."""
         for li, row in enumerate(self.packs):
             for j, (name, pk, st, keep, xname) in enumerate(row):
-                _lib.small_m(st, keep, self.x[xname], out=self.y[li][j])
+                _lib.small_m(st, keep, self.x[xname], out=self.y[li][j], plan=keep[-1],
+                             flags=_lib.FLAG_PDL if self.pdl else 0)
 
     def capture(self) -> None:
         self.run_eager()                      # warm-up outside capture: shared-memory opt-in, scratch

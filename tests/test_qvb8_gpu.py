@@ -138,6 +138,44 @@ def test_generic_path_agrees(cuda_lib):
     assert rel_fro(a.cpu().numpy(), b.cpu().numpy()) < 1e-5
 
 
+@pytest.mark.parametrize("nwarp", [4, 8])
+@pytest.mark.parametrize("M", [1, 5, 16])
+def test_escape_plan_and_cta_shapes(cuda_lib, nwarp, M):
+    """The fused escape correction (row-grouped plan) and both CTA shapes give the same product as the oracle."""
+    from qvb8_b200 import lib
+    pk = random_pack(300, 1536, (4, 6, 7, 8, 11), seed=31 + M, esc_frac=0.004, device=DEV)
+    X = synth.synth_activation(M, 1536, seed=M, device=DEV)
+    st, keep = lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx, pk.esc_vals)
+    plan = lib.escape_plan(st, keep)
+    want = _oracle_y(pk, X)
+    try:
+        lib.load().qvb8_small_m_set_tuning(nwarp, 3)
+        for flags in (0, lib.FLAG_PDL):
+            y = lib.small_m(st, keep, X, plan=plan, flags=flags)
+            err = rel_fro(y.cpu().numpy(), want)
+            assert err < TIGHT, (err, flags)
+        y_noplan = lib.small_m(st, keep, X)
+        assert rel_fro(y_noplan.cpu().numpy(), want) < TIGHT
+    finally:
+        lib.load().qvb8_small_m_set_tuning(0, 3)
+
+
+def test_escape_plan_rows_without_escapes(cuda_lib):
+    """Rows before, between and after the escaped rows get empty ranges."""
+    from qvb8_b200 import lib
+    pk = random_pack(64, 256, (7,), seed=5, device=DEV)
+    idx = torch.tensor([3 * 256 + 7, 3 * 256 + 200, 40 * 256 + 1], dtype=torch.int64, device=DEV)
+    val = torch.tensor([0.25, -0.5, 0.125], device=DEV)
+    pk.esc_idx, pk.esc_vals = idx, val
+    st, keep = lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, idx, val)
+    plan = lib.escape_plan(st, keep)
+    ptr = plan[: 65 * 4].view(torch.int32).cpu().tolist()
+    assert ptr[:4] == [0, 0, 0, 0] and ptr[4] == 2 and ptr[40] == 2 and ptr[41] == 3 and ptr[64] == 3
+    X = synth.synth_activation(2, 256, seed=1, device=DEV)
+    y = lib.small_m(st, keep, X, plan=plan)
+    assert rel_fro(y.cpu().numpy(), _oracle_y(pk, X)) < TIGHT
+
+
 def test_small_m_is_deterministic(cuda_lib):
     pk = random_pack(512, 4096, (6, 7), seed=21, esc_frac=0.001, device=DEV)        # several K-ranges
     X = synth.synth_activation(8, 4096, seed=3, device=DEV)
