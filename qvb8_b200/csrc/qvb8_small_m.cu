@@ -12,24 +12,31 @@
 // is therefore the un-narrowed band value, the contract of the reference's M <= 8 GEMV; X is narrowed to saturated
 // fp16 first, as every fp16-mode path of the reference does (:761-841).
 //
-// Roofline: HBM.  Per weight the kernel moves nbits/8 bytes (about 0.8) and spends about two issue slots; the
-// stream is staged through shared memory with 16-byte cp.async copies (each warp keeps NST-1 row-chunks in flight),
-// so HBM sees whole 16-byte-aligned row segments while the fragment reads happen in shared memory.
+// Roofline: HBM.  Per weight the kernel moves nbits/8 bytes (about 0.8).  What HBM sees matters as much as how
+// much: rows of a pack are contiguous byte ranges, so a CTA fetches, for each of the 16 rows of a tile, ONE
+// contiguous run of up to 1 KB per stage with a bulk asynchronous copy (cp.async.bulk, completion on an mbarrier).
+// A producer warp keeps several stages in flight; eight consumer warps each take one 128-column chunk of the stage.
 //
-// Work split.  A CTA owns RB consecutive output rows and one K-range.  Rows of a pack have different widths, so the
-// CTA first sorts its rows by width into 16-row tiles of ONE width (shared-memory lists; no precomputed ordering is
-// needed).  A warp takes a tile, and for every 128-column chunk: thread (g = lane / 4, t = lane % 4) owns the 32 ids
-// of rows g and g + 8 that start at column 32 t -- exactly nb 32-bit words -- and turns them into the A fragments of
-// eight m16n8k16 MMAs.  Two ids are converted per instruction: a funnel shift puts one id in the low half-word
-// and one in the high half-word of a register, `(r & mask) | 0x64006400` makes the two fp16 numbers 1024 + id * 2^e,
-// and one HFMA2 removes the 1024 and the 2^e exactly.  The B fragments are the activations, staged once per CTA as
-// fp16 in the order the fragments want.  K-ranges of one row block are summed in a fixed order by the last CTA of
-// the block to finish (a ticket counter), so results are identical from run to run.
+// Work split.  A CTA owns a block of consecutive output rows and one K-range.  Rows of a pack have different widths,
+// so the CTA first sorts its rows by width into 16-row tiles of ONE width (shared-memory lists; no precomputed
+// ordering is needed) and walks the tiles one after the other.  Within a chunk, thread (g = lane / 4, t = lane % 4)
+// owns the 32 ids of rows g and g + 8 that start at column 32 t -- exactly nb 32-bit words -- and turns them into
+// the A fragments of eight m16n8k16 MMAs.  Two ids are converted per instruction: a funnel shift puts one id in the
+// low half-word and one in the high half-word of a register, `(r & mask) | 0x64006400` makes the two fp16 numbers
+// 1024 + id * 2^e, and one HFMA2 removes the 1024 and the 2^e exactly.  The B fragments are the activations, staged
+// once per CTA as fp16 in the order the fragments want.  At the end of a tile the eight warps' partial accumulators
+// are added in warp order by one warp, which writes the result.  K-ranges of one row block are summed in a fixed
+// order by the last CTA of the block to finish (a ticket counter).  Every sum has a fixed order: results are
+// identical from run to run.
 //
 // Escapes.  Positions whose exact value is stored separately get x * (exact - band) added.  With an escape plan
 // (row pointers + columns + precomputed differences, built once per pack by qvb8_escape_plan) the warp that finishes
 // a tile adds its rows' corrections in stored order before the result leaves the CTA; without a plan a second
 // kernel walks the raw (position, value) list.
+//
+// Waits.  Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the waiter raises a per-CTA abort flag and a
+// device-wide error word (qvb8_device_status), every other waiter gives up too, and the kernel runs to its end with
+// a meaningless result instead of hanging.
 #include "common.cuh"
 
 namespace qv {
@@ -40,44 +47,79 @@ int launch_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x
 int check_small_m_args(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, const float *Y,
                        const char *who);
 
-constexpr int KC = 128;             // columns per chunk (one cp.async stage of a tile)
-constexpr int NST = 4;              // ring slots per warp (NST - 1 chunks in flight)
-constexpr int STAGE_BYTES = 16 * 144;   // 16 rows x (16 * nb bytes, +16 pad for nb = 8)
-constexpr int NCLASS = 7;           // widths 3..8 -> class 0..5; every other width -> class 6 (per-element path)
-constexpr int XS_MAX_BYTES = 64 * 1024;
+constexpr int KC = 128;                   // columns per chunk
+constexpr int NW = 8;                     // consumer warps = chunks per stage
+constexpr int NTHREADS = (NW + 1) * 32;   // + one producer warp
+constexpr int STAGE_ROW_MAX = 1040;       // bytes of one row in a stage (8-bit rows: 8 * 128 + 16 pad)
+constexpr int STAGE_BYTES = 16 * STAGE_ROW_MAX;
+constexpr int MAX_STAGES = 8;
+constexpr int RB_MAX = 128;               // rows per CTA, at most
+constexpr int NCLASS = 7;                 // widths 3..8 -> class 0..5; every other width -> class 6 (per-element path)
+constexpr int MAXTILES = RB_MAX / 16 + NCLASS - 1;
 constexpr int64_t TICKET_BYTES = 64 * 1024;   // fixed-size counter area at the START of the scratch, so that calls of
                                               // different sizes sharing one scratch never find partial sums in it
 constexpr int MAX_TICKET_BLOCKS = (int)(TICKET_BYTES / 4);
 constexpr int MAX_M = 48;
+constexpr int SPIN_LIMIT = 1 << 22;
 
-template <int NWARP>
+__device__ int g_error_word = 0;          // first timeout of any kernel of this library (0 = none)
+
 struct TileTable {
-    static constexpr int RB = 16 * NWARP;
-    static constexpr int MAXTILES = NWARP + NCLASS - 1;
     // per row of the block (local index)
-    uint32_t row_b16[RB];           // byte offset of the row in `ids`, in 16-byte units
-    float row_ms[RB], row_ts[RB];
-    int8_t row_cls[RB];
-    uint8_t row_nb[RB];
+    uint32_t row_b16[RB_MAX];       // byte offset of the row in `ids`, in 16-byte units
+    float row_ms[RB_MAX], row_ts[RB_MAX];
+    int8_t row_cls[RB_MAX];
+    uint8_t row_nb[RB_MAX];
     // tiles
     int ntiles;
     int need_b;                     // some tile pairs ids at distance 4: the second activation layout is needed
     int8_t tile_nb[MAXTILES];       // width of the tile's rows; 0 = per-element class
     int8_t tile_cnt[MAXTILES];      // real rows in the tile (the rest is padding)
     int16_t tile_row[MAXTILES][16]; // local row index, -1 = padding
-    int16_t list[NCLASS][RB];       // scratch of the classification
+    int16_t list[NCLASS][RB_MAX];   // scratch of the classification
     float sumx[MAX_M];
     int is_last;
+    int abort;
+    alignas(8) uint64_t full[MAX_STAGES];
+    alignas(8) uint64_t empty[MAX_STAGES];
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+// ---- mbarrier / bulk copy ------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the barrier did not complete (this waiter or another one gave up).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+    for (int i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255) == 255 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_error_word, 0, code);
+    return false;
+}
+// global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned); completion is counted
+// on `bar`.  The destination is this CTA's own shared memory.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32) : "memory"); }
 
 // Programmatic dependent launch: everything before pdl_wait() may overlap the tail of the previous kernel in the
 // stream (it must not touch memory that kernel writes); both are no-ops for a normal launch.
@@ -156,7 +198,6 @@ __device__ __forceinline__ void load_block(uint32_t addr, uint32_t (&W)[NB]) {
         static_assert(NB == 8 || NB == 4 || NB == 6, "odd widths are specialised below");
     }
 }
-
 // odd widths: nb scalar loads (an odd stride in words spreads the 32 lanes over all banks)
 template <>
 __device__ __forceinline__ void load_block<7>(uint32_t addr, uint32_t (&W)[7]) {
@@ -183,17 +224,19 @@ __device__ __forceinline__ void load_block<3>(uint32_t addr, uint32_t (&W)[3]) {
     asm volatile("ld.shared.u32 %0, [%1+8];\n" : "=r"(W[2]) : "r"(addr));
 }
 
-__host__ __device__ constexpr int row_stride(int nb) { return nb == 8 ? 144 : 16 * nb; }
+// Bytes between rows of a stage.  The eight chunks of a row lie back to back (a contiguous copy); the stride adds
+// one chunk's worth of padding (16 bytes for 8-bit rows) so that the 32 lanes of a warp, which read rows g and
+// columns 32 t of ONE chunk, fall on distinct banks.
+__host__ __device__ constexpr int stage_row_stride(int nb) { return nb == 8 ? STAGE_ROW_MAX : 16 * nb * (NW + 1); }
 
 // One 128-column chunk of a 16-row tile of width NB: 8 MMAs per token group.
 //   wa, wb   shared addresses of this thread's blocks in rows g and g + 8 of the stage
 //   xa       shared address of this thread's first activation slot of the chunk (token 8n + g -> + n * 128 bytes)
-//   xstep    bytes between the slots of consecutive 8-column groups (= 4 * MP * 16)
+//   xstep    bytes between the slots of consecutive 8-column groups (= 4 * MP * 16; 0 for lanes without a token)
 //   DUAL     true: a second activation layout exists for widths that pair ids at distance 4 (xa points into it);
 //            false: only layout A is staged and those widths rebuild their operands with byte permutes
 template <int NB, int NT, bool DUAL>
-__device__ __forceinline__ void chunk_mma(uint32_t wa, uint32_t wb, uint32_t xa, uint32_t xstep, bool xvalid,
-                                          float (&acc)[NT][4]) {
+__device__ __forceinline__ void chunk_mma(uint32_t wa, uint32_t wb, uint32_t xa, uint32_t xstep, float (&acc)[NT][4]) {
     constexpr int D = Pairing<NB>::D;
     uint32_t Wa[NB], Wb[NB];
     load_block<NB>(wa, Wa);
@@ -204,14 +247,10 @@ __device__ __forceinline__ void chunk_mma(uint32_t wa, uint32_t wb, uint32_t xa,
         // words (2h, 2h + 1) are the B operands of MMA h of this group
         uint32_t xw[NT][4];
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            xw[n][0] = xw[n][1] = xw[n][2] = xw[n][3] = 0u;
-            if (NT > 1 || xvalid) {
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                             : "=r"(xw[n][0]), "=r"(xw[n][1]), "=r"(xw[n][2]), "=r"(xw[n][3])
-                             : "r"(xa + i * xstep + n * 128));
-            }
-        }
+        for (int n = 0; n < NT; ++n)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                         : "=r"(xw[n][0]), "=r"(xw[n][1]), "=r"(xw[n][2]), "=r"(xw[n][3])
+                         : "r"(xa + i * xstep + n * 128));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             // ids of this MMA: D == 2 -> {8i+4h .. 8i+4h+3} paired (f, f+2);  D == 4 -> {8i+2h, +1, +4, +5} paired (f, f+4)
@@ -287,35 +326,81 @@ struct SmallMParams {
     const int *esc_col;     // column of each escape
     const float *esc_delta; // exact value - band value
     int Q, P, M, MP;   // MP: token slots per column group in shared memory (>= M)
+    int rb;            // rows per CTA (multiple of 16, <= RB_MAX)
     int S;             // K-ranges
     int nc_per;        // chunks per K-range (the last range may be shorter)
     int nc_total;      // P / 128
+    int nstg;          // stages of the copy ring
     int debug;         // bit 0: skip the fragment math (copy stream only; tuning experiments)
 };
 
-template <int XT, int NT, int NWARP>
-__global__ void __launch_bounds__(NWARP * 32, NWARP == 8 ? 2 : 4) small_m_kernel(const SmallMParams p) {
-    using TT = TileTable<NWARP>;
-    constexpr int RB = TT::RB;
-    constexpr int NTHREADS = NWARP * 32;
-    extern __shared__ __align__(16) uint8_t smem[];
-    __shared__ TT tt;
-    uint8_t *ring = smem;                                              // NWARP * NST * STAGE_BYTES
-    __half *xs_a = reinterpret_cast<__half *>(smem + NWARP * NST * STAGE_BYTES);
+// Corrections of the escapes of the 16 rows of a tile that fall into this CTA's K-range, added to results that are
+// already written: lane r (< 16) walks row r's list in stored order.  Called by one warp.
+__device__ __forceinline__ void tile_escapes(const SmallMParams &p, const TileTable &tt, int ti, int lane, int q0,
+                                             int kc0, int NC, const __half *xs_a, int MP, float *out) {
+    const int lr = lane < 16 ? tt.tile_row[ti][lane] : -1;
+    if (lr < 0) return;
+    const int q = q0 + lr;
+    const int e0 = __ldg(p.esc_ptr + q), e1 = __ldg(p.esc_ptr + q + 1);
+    const int clo = kc0 * KC, chi = clo + NC * KC;
+    for (int m0 = 0; m0 < p.M; m0 += 8) {
+        float a[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a[k] = 0.f;
+        bool any = false;
+        for (int e = e0; e < e1; ++e) {
+            const int c = __ldg(p.esc_col + e);
+            if (c < clo || c >= chi) continue;
+            any = true;
+            const float d = __ldg(p.esc_delta + e);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c - clo, m0 + k, MP), d, a[k]);
+        }
+        if (any) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (m0 + k < p.M) out[(int64_t)(m0 + k) * p.Q + q] += a[k];
+        }
+    }
+}
+
+template <int XT, int NT>
+__global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(const SmallMParams p) {
+    constexpr bool DUAL = NT == 1;                                     // second activation layout (cheap for few tokens)
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ TileTable tt;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int RB = p.rb;
     const int q0 = blockIdx.x * RB;
     const int nrows = min(RB, p.Q - q0);
     const int split = blockIdx.y;
     const int kc0 = split * p.nc_per;                                  // first chunk of this K-range
     const int NC = min(p.nc_per, p.nc_total - kc0);                    // chunks in this K-range (>= 1 by construction)
+    const int NSK = (NC + NW - 1) / NW;                                // stages along K per tile
     const int MP = p.MP;
-    constexpr bool DUAL = NT == 1;                                     // second activation layout (cheap for few tokens)
-    const int xs_halves = NC * 16 * MP * 8;                            // halves per activation layout
+    const int nstg = p.nstg;
+    // dynamic shared memory: [stages][activations A][activations B][tile reduction x 2][16 zero bytes]
+    uint8_t *stages = smem;
+    const int xs_halves = p.nc_per * 16 * MP * 8;                      // halves per activation layout
+    __half *xs_a = reinterpret_cast<__half *>(smem + (size_t)nstg * STAGE_BYTES);
     __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
+    float *red = reinterpret_cast<float *>(xs_a + (DUAL ? 2 : 1) * xs_halves);     // [2][NW][4 * NT][32]
+    uint32_t *zero16 = reinterpret_cast<uint32_t *>(red + 2 * NW * 4 * NT * 32);
+    volatile int *abort_flag = &tt.abort;
 
-    // ---- 1. row metadata in one round trip, then sort the rows by width into tiles (stable: same order every run)
-    for (int r = tid; r < RB; r += NTHREADS) {
+    // ---- 1. barriers; row metadata in one round trip; rows sorted by width into tiles (stable order)
+    if (tid == 0) {
+        for (int s = 0; s < nstg; ++s) {
+            mbar_init(smem_u32(&tt.full[s]), 1);
+            mbar_init(smem_u32(&tt.empty[s]), NW);
+        }
+        tt.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (tid < 4) zero16[tid] = 0u;
+    for (int r = tid; r < RB_MAX; r += NTHREADS) {
         int cls = -1;
         if (r < nrows) {
             const int nb = __ldg(p.nbits + q0 + r);
@@ -360,200 +445,189 @@ __global__ void __launch_bounds__(NWARP * 32, NWARP == 8 ? 2 : 4) small_m_kernel
         if (lane == 0) { tt.ntiles = nt; tt.need_b = need_b; }
     }
     __syncthreads();
-
-    // ---- 2. copy stream of this warp: tiles warp, warp + NWARP, ...; chunk after chunk, NST - 1 chunks ahead
     const int ntiles = tt.ntiles;
-    const int n_my = warp < ntiles ? (ntiles - warp + NWARP - 1) / NWARP : 0;
-    const uint32_t ring_w = smem_u32(ring + warp * NST * STAGE_BYTES);
-    // prefetch-side state: the tile being copied, its chunk cursor, and this lane's (up to 4) 16-byte pieces
-    int pf_ti = 0, pf_c = 0, pf_nb = 0;
-    uint32_t pf_off[4], pf_dst[4];
-    bool pf_ok[4];
-    auto pf_setup = [&]() {
-        if (pf_ti >= n_my) return;
-        const int tile = warp + pf_ti * NWARP;
-        pf_nb = tt.tile_nb[tile];
-        const int pieces = tt.tile_cnt[tile] * pf_nb;                   // 0 for the per-element class
-        const uint32_t magic = pf_nb ? (65536u + pf_nb - 1) / pf_nb : 0u;
-        const int RS = row_stride(pf_nb);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int pc = lane + 32 * k;
-            pf_ok[k] = pc < pieces;
-            const int r = (int)((pc * magic) >> 16), j = pc - r * pf_nb;
-            const int lr = pf_ok[k] ? tt.tile_row[tile][r] : 0;
-            pf_off[k] = tt.row_b16[lr] + (uint32_t)(kc0 * pf_nb + j);
-            pf_dst[k] = (uint32_t)(r * RS + j * 16);
-        }
-    };
-    auto pf_issue = [&](int slot) {
-        if (pf_ti < n_my) {
-            const uint32_t dst0 = ring_w + slot * STAGE_BYTES;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                if (pf_ok[k]) cp_async16(dst0 + pf_dst[k], p.ids + (uint64_t)pf_off[k] * 16u);
-                pf_off[k] += (uint32_t)pf_nb;
-            }
-            if (++pf_c == NC) { pf_c = 0; ++pf_ti; pf_setup(); }
-        }
-        cp_async_commit();
-    };
-    pf_setup();
-#pragma unroll
-    for (int s = 0; s < NST - 1; ++s) pf_issue(s);
-
-    // ---- 3. activations of this K-range as fp16 in fragment order (after the previous kernel in the stream is done)
-    pdl_wait();
-    {
-        const int groups = NC * 16;                                     // 8-column groups in the range
-        const int64_t col0 = (int64_t)kc0 * KC;
-        const bool need_b = DUAL && tt.need_b != 0;
-        for (int idx = tid; idx < MP * groups; idx += NTHREADS) {
-            const int m = idx / groups, u8 = idx - m * groups;         // u8: natural 8-column group number
-            uint32_t h[8];
-            if (m < p.M) {
-                stage_x8<XT>(p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h);
-            } else {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) h[k] = 0u;
-            }
-            const int slot = slot_of(u8 * 8, m, MP);
-            *reinterpret_cast<uint4 *>(xs_a + (slot << 3)) =
-                make_uint4(h[0] | (h[2] << 16), h[1] | (h[3] << 16), h[4] | (h[6] << 16), h[5] | (h[7] << 16));
-            if (need_b)
-                *reinterpret_cast<uint4 *>(xs_b + (slot << 3)) =
-                    make_uint4(h[0] | (h[4] << 16), h[1] | (h[5] << 16), h[2] | (h[6] << 16), h[3] | (h[7] << 16));
-        }
-        __syncthreads();
-        for (int m = warp; m < p.M; m += NWARP) {                       // fixed-order sums: same bits every run
-            float s = 0.f;
-            for (int c = lane; c < NC * KC; c += 32) s += xs_read(xs_a, c, m, MP);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) tt.sumx[m] = s;
-        }
-        __syncthreads();
-    }
-    pdl_launch_dependents();
-
-    // ---- 4. stream the tiles
     float *out = p.S > 1 ? p.part + (int64_t)split * p.M * p.Q : p.Y;
-    const int g = lane >> 2, t = lane & 3;
-    const uint32_t xstep = (uint32_t)(4 * MP * 16);                     // bytes between consecutive 8-column groups
-    const uint32_t xchunk = 4 * xstep;                                  // bytes per chunk
-    const bool xvalid = g < MP;                                         // NT == 1: lanes of token slots that exist
-    const uint32_t xoff = (uint32_t)((t * MP + (xvalid ? g : 0)) * 16);
-    const uint32_t xs_a32 = smem_u32(xs_a) + xoff, xs_b32 = smem_u32(xs_b) + xoff;
-    int slot = 0;
-    for (int ti = 0; ti < n_my; ++ti) {
-        const int tile = warp + ti * NWARP;
-        const int nb = tt.tile_nb[tile];
-        const int RS = row_stride(nb);
-        const uint32_t wa_off = (uint32_t)(g * RS + t * 4 * nb), wb_off = wa_off + 8 * RS;
-        const uint32_t xbase = nb >= 6 ? xs_a32 : xs_b32;
-        float acc[NT][4];
-#pragma unroll
-        for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-        for (int chunk = 0; chunk < NC; ++chunk) {
-            pf_issue(slot == 0 ? NST - 1 : slot - 1);                   // refill the slot consumed last
-            cp_async_wait<NST - 1>();
-            __syncwarp();
-            const uint32_t stage = ring_w + slot * STAGE_BYTES;
-            const uint32_t xa = xbase + chunk * xchunk;
-            if (!(p.debug & 1))
-            switch (nb) {                                               // warp-uniform
-                case 7: chunk_mma<7, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
-                case 6: chunk_mma<6, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
-                case 8: chunk_mma<8, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
-                case 5: chunk_mma<5, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
-                case 4: chunk_mma<4, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
-                case 3: chunk_mma<3, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, xvalid, acc); break;
-                default: break;
+
+    if (warp == NW) {
+        // ================= producer warp: lane r copies row r of every stage =================
+        int slot = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int ti = 0; ti < ntiles && alive; ++ti) {
+            const int nb = tt.tile_nb[ti];
+            if (nb == 0) continue;
+            const int cnt = tt.tile_cnt[ti];
+            const int lr = lane < cnt ? tt.tile_row[ti][lane] : 0;
+            const uint8_t *src = p.ids + ((uint64_t)tt.row_b16[lr] + (uint64_t)kc0 * nb) * 16u;
+            const uint32_t dst_row = (uint32_t)(lane * stage_row_stride(nb));
+            for (int s = 0; s < NSK; ++s) {
+                const int chunks = min(NW, NC - s * NW);
+                const uint32_t bytes_row = (uint32_t)(chunks * 16 * nb);
+                const uint32_t full = smem_u32(&tt.full[slot]);
+                if (!mbar_wait(smem_u32(&tt.empty[slot]), phase ^ 1u, abort_flag, 1)) { alive = false; break; }
+                if (lane == 0) mbar_expect_tx(full, bytes_row * (uint32_t)cnt);
+                __syncwarp();
+                if (lane < cnt)
+                    bulk_g2s(smem_u32(stages + (size_t)slot * STAGE_BYTES) + dst_row, src + (size_t)s * NW * 16 * nb,
+                             bytes_row, full);
+                if (++slot == nstg) { slot = 0; phase ^= 1u; }
             }
-            __syncwarp();
-            slot = slot == NST - 1 ? 0 : slot + 1;
         }
-        // ---- tile epilogue
-        if (nb != 0) {
-            // y = tau_s * sum(x * id) + min_s * sum(x); thread holds rows g, g+8 and tokens 8n+2t, 8n+2t+1
+    } else {
+        // ================= consumer warps =================
+        // ---- 2. activations of this K-range as fp16 in fragment order (after the previous kernel in the stream)
+        pdl_wait();
+        {
+            const int groups = NC * 16;                                 // 8-column groups in the range
+            const int64_t col0 = (int64_t)kc0 * KC;
+            const bool need_b = DUAL && tt.need_b != 0;
+            for (int idx = tid; idx < MP * groups; idx += NW * 32) {
+                const int m = idx / groups, u8 = idx - m * groups;     // u8: natural 8-column group number
+                uint32_t h[8];
+                if (m < p.M) {
+                    stage_x8<XT>(p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h);
+                } else {
 #pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow) {
-                const int lr = tt.tile_row[tile][g + 8 * hrow];
-                if (lr >= 0) {
-                    const float ms = tt.row_ms[lr], ts = tt.row_ts[lr];
+                    for (int k = 0; k < 8; ++k) h[k] = 0u;
+                }
+                const int sl = slot_of(u8 * 8, m, MP);
+                *reinterpret_cast<uint4 *>(xs_a + (sl << 3)) =
+                    make_uint4(h[0] | (h[2] << 16), h[1] | (h[3] << 16), h[4] | (h[6] << 16), h[5] | (h[7] << 16));
+                if (need_b)
+                    *reinterpret_cast<uint4 *>(xs_b + (sl << 3)) =
+                        make_uint4(h[0] | (h[4] << 16), h[1] | (h[5] << 16), h[2] | (h[6] << 16), h[3] | (h[7] << 16));
+            }
+            consumer_sync();
+            for (int m = warp; m < p.M; m += NW) {                      // fixed-order sums: same bits every run
+                float s = 0.f;
+                for (int c = lane; c < NC * KC; c += 32) s += xs_read(xs_a, c, m, MP);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane == 0) tt.sumx[m] = s;
+            }
+            consumer_sync();
+        }
+        pdl_launch_dependents();
+
+        // ---- 3. walk the tiles
+        const int g = lane >> 2, t = lane & 3;
+        const bool xvalid = NT > 1 || g < MP;                           // lanes whose token slot exists
+        const uint32_t xstep = xvalid ? (uint32_t)(4 * MP * 16) : 0u;   // bytes between consecutive 8-column groups
+        const uint32_t xchunk = 4 * xstep;                              // bytes per chunk
+        const uint32_t xoff = (uint32_t)((t * MP + g) * 16);
+        const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
+        const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
+        const uint32_t stages32 = smem_u32(stages);
+        int slot = 0, staged = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int ti = 0; ti < ntiles; ++ti) {
+            const int nb = tt.tile_nb[ti];
+            const int cnt = tt.tile_cnt[ti];
+            if (nb == 0) {
+                // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
+                // start on a 16-byte boundary).  One row per warp at a time, ids byte-wise from global memory.
+                for (int rr = warp; rr < cnt; rr += NW) {
+                    const int lr = tt.tile_row[ti][rr];
                     const int q = q0 + lr;
+                    const int rnb = tt.row_nb[lr];
+                    const int64_t base = __ldg(p.bit_off + q) + (int64_t)kc0 * KC * rnb;
+                    const float ms = tt.row_ms[lr], ts = tt.row_ts[lr];
+                    for (int m0 = 0; m0 < p.M; m0 += 8) {
+                        float a[8];
 #pragma unroll
-                    for (int n = 0; n < NT; ++n) {
+                        for (int k = 0; k < 8; ++k) a[k] = 0.f;
+                        for (int c = lane; c < NC * KC; c += 32) {
+                            const float wv = band(field_bytes(p.ids, base + (int64_t)c * rnb, rnb), ts, ms);
 #pragma unroll
-                        for (int k = 0; k < 2; ++k) {
-                            const int m = 8 * n + 2 * t + k;
-                            if (m < p.M) out[(int64_t)m * p.Q + q] = __fmaf_rn(ts, acc[n][2 * hrow + k], ms * tt.sumx[m]);
+                            for (int k = 0; k < 8; ++k)
+                                if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c, m0 + k, MP), wv, a[k]);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
+                            if (lane == 0 && m0 + k < p.M) out[(int64_t)(m0 + k) * p.Q + q] = a[k];
                         }
                     }
                 }
+                if (p.esc_ptr != nullptr) {
+                    consumer_sync();                                    // every warp's rows of this tile are written
+                    if (warp == 0) tile_escapes(p, tt, ti, lane, q0, kc0, NC, xs_a, MP, out);
+                }
+                continue;
             }
-        } else {
-            // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
-            // start on a 16-byte boundary).  One row at a time, ids byte-wise from global memory.
-            for (int rr = 0; rr < tt.tile_cnt[tile]; ++rr) {
-                const int lr = tt.tile_row[tile][rr];
-                const int q = q0 + lr;
-                const int rnb = tt.row_nb[lr];
-                const int64_t base = __ldg(p.bit_off + q) + (int64_t)kc0 * KC * rnb;
-                const float ms = tt.row_ms[lr], ts = tt.row_ts[lr];
-                for (int m0 = 0; m0 < p.M; m0 += 8) {
-                    float a[8];
+            const int RS = stage_row_stride(nb);
+            const uint32_t wa_off = (uint32_t)(g * RS + warp * 16 * nb + t * 4 * nb), wb_off = wa_off + 8 * RS;
+            const uint32_t xbase = (nb >= 6 || !DUAL) ? xs_a32 : xs_b32;
+            float acc[NT][4];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) a[k] = 0.f;
-                    for (int c = lane; c < NC * KC; c += 32) {
-                        const float wv = band(field_bytes(p.ids, base + (int64_t)c * rnb, rnb), ts, ms);
-#pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c, m0 + k, MP), wv, a[k]);
-                    }
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
-                        if (lane == 0 && m0 + k < p.M) out[(int64_t)(m0 + k) * p.Q + q] = a[k];
+            for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+            for (int s = 0; s < NSK; ++s) {
+                if (alive) alive = mbar_wait(smem_u32(&tt.full[slot]), phase, abort_flag, 2);
+                const int chunk = s * NW + warp;
+                if (alive && chunk < NC && !(p.debug & 1)) {
+                    const uint32_t stage = stages32 + (uint32_t)slot * STAGE_BYTES;
+                    const uint32_t xa = xbase + chunk * xchunk;
+                    switch (nb) {                                       // CTA-uniform
+                        case 7: chunk_mma<7, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                        case 6: chunk_mma<6, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                        case 8: chunk_mma<8, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                        case 5: chunk_mma<5, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                        case 4: chunk_mma<4, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                        case 3: chunk_mma<3, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                        default: break;
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&tt.empty[slot]));
+                if (++slot == nstg) { slot = 0; phase ^= 1u; }
             }
-        }
-        // ---- escapes of the tile's rows that fall in this K-range: lane r walks row r's list in stored order
-        if (p.esc_ptr != nullptr) {
-            __syncwarp();                                               // the tile's results are written
-            const int lr = lane < 16 ? tt.tile_row[tile][lane] : -1;
-            if (lr >= 0) {
-                const int q = q0 + lr;
-                const int e0 = __ldg(p.esc_ptr + q), e1 = __ldg(p.esc_ptr + q + 1);
-                const int clo = kc0 * KC, chi = clo + NC * KC;
-                for (int m0 = 0; m0 < p.M; m0 += 8) {
-                    float a[8];
+            // ---- the eight warps' partial sums, added in warp order by one warp
+            float *rbuf = red + (size_t)(staged & 1) * (NW * 4 * NT * 32);
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) a[k] = 0.f;
-                    bool any = false;
-                    for (int e = e0; e < e1; ++e) {
-                        const int c = __ldg(p.esc_col + e);
-                        if (c < clo || c >= chi) continue;
-                        any = true;
-                        const float d = __ldg(p.esc_delta + e);
+            for (int n = 0; n < NT; ++n)
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c - clo, m0 + k, MP), d, a[k]);
+                for (int k = 0; k < 4; ++k) rbuf[(warp * 4 * NT + n * 4 + k) * 32 + lane] = acc[n][k];
+            consumer_sync();
+            if (warp == (staged & (NW - 1))) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float v = 0.f;
+#pragma unroll
+                        for (int w = 0; w < NW; ++w) v += rbuf[(w * 4 * NT + n * 4 + k) * 32 + lane];
+                        acc[n][k] = v;
                     }
-                    if (any) {
+                // y = tau_s * sum(x * id) + min_s * sum(x); thread holds rows g, g+8 and tokens 8n+2t, 8n+2t+1
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            if (m0 + k < p.M) out[(int64_t)(m0 + k) * p.Q + q] += a[k];
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    const int lr = tt.tile_row[ti][g + 8 * hrow];
+                    if (lr >= 0) {
+                        const float ms = tt.row_ms[lr], ts = tt.row_ts[lr];
+                        const int q = q0 + lr;
+#pragma unroll
+                        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const int m = 8 * n + 2 * t + k;
+                                if (m < p.M)
+                                    out[(int64_t)m * p.Q + q] = __fmaf_rn(ts, acc[n][2 * hrow + k], ms * tt.sumx[m]);
+                            }
+                        }
                     }
                 }
+                if (p.esc_ptr != nullptr) {
+                    __syncwarp();                                       // the tile's results are written
+                    tile_escapes(p, tt, ti, lane, q0, kc0, NC, xs_a, MP, out);
+                }
             }
+            ++staged;
         }
     }
-    cp_async_wait<0>();
 
-    // ---- 5. K-ranges: the last CTA of the row block adds the partial sums in range order
+    // ---- 4. K-ranges: the last CTA of the row block adds the partial sums in range order
     if (p.S > 1) {
         __threadfence();
         __syncthreads();
@@ -609,7 +683,7 @@ __global__ void __launch_bounds__(256) escape_plan_kernel(const uint8_t *__restr
 // host side
 
 struct Plan {
-    int nwarp, rb, nblk, S, nc_per, nc_total, MP, NT;
+    int rb, nblk, S, nc_per, nc_total, MP, NT, nstg;
     size_t smem_bytes;
     int64_t part_bytes, ticket_bytes;
 };
@@ -625,9 +699,8 @@ static int device_sms() {
     return n;
 }
 
-static int g_force_nwarp = 0;   // test / tuning hook (qvb8_small_m_set_tuning)
-static int g_fill_x = 3;        // CTAs wanted per SM when choosing the K split
-static int g_debug = 0;
+// tuning hooks (qvb8_small_m_set_tuning): 0 = choose automatically
+static int g_force_rb = 0, g_fill_x = 2, g_force_nstg = 0, g_debug = 0;
 
 static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     Plan pl{};
@@ -635,27 +708,42 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     pl.NT = (int)((M + 7) / 8);
     pl.MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * pl.NT;
     const int sms = device_sms();
-    // small outputs: 64-row CTAs of 4 warps give the scheduler twice as many, half as heavy, pieces
-    pl.nwarp = g_force_nwarp ? g_force_nwarp : (Q * (int64_t)pl.nc_total <= (int64_t)sms * 16 * 64 ? 4 : 8);
-    pl.rb = 16 * pl.nwarp;
-    pl.nblk = (int)((Q + pl.rb - 1) / pl.rb);
-    // K-range length: bounded by the shared memory the staged activations may take (two layouts) ...
     const int layouts = pl.NT == 1 ? 2 : 1;
-    const int xs_budget = pl.NT >= 3 ? 2 * XS_MAX_BYTES : XS_MAX_BYTES;
+    // K-range length: bounded by the shared memory the staged activations may take
+    const int xs_budget = pl.NT == 1 ? 32 * 1024 : pl.NT == 2 ? 48 * 1024 : 96 * 1024;
     int nc_max = xs_budget / (KC * pl.MP * 2 * layouts);
+    if (nc_max >= NW) nc_max = nc_max / NW * NW;                        // whole stages
     if (nc_max < 1) nc_max = 1;
-    int S = (pl.nc_total + nc_max - 1) / nc_max;
-    // ... and short enough that the grid fills the GPU a few times over, but not below 4 chunks per range
-    const int want = (g_fill_x * sms + pl.nblk - 1) / (pl.nblk > 0 ? pl.nblk : 1);
-    int s_fill = want;
-    const int s_cap = pl.nc_total / 4 > 0 ? pl.nc_total / 4 : 1;
-    if (s_fill > s_cap) s_fill = s_cap;
-    if (S < s_fill) S = s_fill;
-    if (S < 1) S = 1;
-    if (pl.nblk > MAX_TICKET_BLOCKS) S = (pl.nc_total + nc_max - 1) / nc_max;   // more row blocks than counters
+    const int s_xs = (pl.nc_total + nc_max - 1) / nc_max;
+    // rows per CTA and K split: enough CTAs to fill the GPU g_fill_x times over where the shape allows it, each
+    // K-range at least one full stage
+    const int s_cap = pl.nc_total / NW > 0 ? pl.nc_total / NW : 1;
+    const int target = g_fill_x * sms;
+    int rb = g_force_rb ? g_force_rb : RB_MAX;
+    int S = s_xs;
+    for (;;) {
+        const int nblk = (int)((Q + rb - 1) / rb);
+        int want = (target + nblk - 1) / nblk;
+        if (want > s_cap) want = s_cap;
+        S = s_xs > want ? s_xs : want;
+        if (g_force_rb || rb <= 32 || (int64_t)nblk * S >= target) break;
+        rb /= 2;
+    }
+    pl.rb = rb;
+    pl.nblk = (int)((Q + rb - 1) / rb);
+    if (pl.nblk > MAX_TICKET_BLOCKS) S = s_xs;                          // more row blocks than counters
     pl.nc_per = (pl.nc_total + S - 1) / S;
+    if (pl.nc_per > NW) pl.nc_per = (pl.nc_per + NW - 1) / NW * NW;     // K-ranges of whole stages
+    if (pl.nc_per > nc_max) pl.nc_per = nc_max;
     pl.S = (pl.nc_total + pl.nc_per - 1) / pl.nc_per;                   // no empty range
-    pl.smem_bytes = (size_t)pl.nwarp * NST * STAGE_BYTES + (size_t)pl.nc_per * KC * pl.MP * 2 * layouts;
+    const size_t xs_bytes = (size_t)pl.nc_per * KC * pl.MP * 2 * layouts;
+    const size_t red_bytes = (size_t)2 * NW * 4 * pl.NT * 32 * 4;
+    const size_t per_cta = (size_t)(pl.NT <= 2 ? 110 : 220) * 1024;
+    int nstg = g_force_nstg ? g_force_nstg : (int)((per_cta - xs_bytes - red_bytes - 64) / STAGE_BYTES);
+    if (nstg > MAX_STAGES) nstg = MAX_STAGES;
+    if (nstg < 2) nstg = 2;
+    pl.nstg = nstg;
+    pl.smem_bytes = (size_t)nstg * STAGE_BYTES + xs_bytes + red_bytes + 64;
     pl.part_bytes = pl.S > 1 ? (int64_t)pl.S * M * Q * 4 : 0;
     pl.part_bytes = (pl.part_bytes + 255) / 256 * 256;
     pl.ticket_bytes = pl.S > 1 ? TICKET_BYTES : 0;
@@ -666,20 +754,20 @@ static bool fast_layout_ok(const qvb8_pack *w, const void *X) {
     return w->P > 0 && w->P % KC == 0 && aligned(w->ids, 16) && aligned(X, 16);
 }
 
-template <int XT, int NT, int NWARP>
+template <int XT, int NT>
 static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
-    auto kern = small_m_kernel<XT, NT, NWARP>;
+    auto kern = small_m_kernel<XT, NT>;
     static thread_local int granted_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != granted_dev) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024)) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(222 * 1024)) != cudaSuccess)
             return cuda_status("qvb8_small_m: shared memory opt-in");
         granted_dev = dev;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(pl.nblk, pl.S);
-    cfg.blockDim = dim3(NWARP * 32);
+    cfg.blockDim = dim3(NTHREADS);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -691,29 +779,33 @@ static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, 
     return cuda_status("qvb8_small_m launch");
 }
 
-template <int XT, int NWARP>
+template <int XT>
 static int launch_nt(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
     switch (pl.NT) {
-        case 1: return launch_one<XT, 1, NWARP>(prm, pl, st, pdl);
-        case 2: return launch_one<XT, 2, NWARP>(prm, pl, st, pdl);
-        case 3: return launch_one<XT, 3, NWARP>(prm, pl, st, pdl);
-        case 4: return launch_one<XT, 4, NWARP>(prm, pl, st, pdl);
-        case 5: return launch_one<XT, 5, NWARP>(prm, pl, st, pdl);
-        default: return launch_one<XT, 6, NWARP>(prm, pl, st, pdl);
+        case 1: return launch_one<XT, 1>(prm, pl, st, pdl);
+        case 2: return launch_one<XT, 2>(prm, pl, st, pdl);
+        case 3: return launch_one<XT, 3>(prm, pl, st, pdl);
+        case 4: return launch_one<XT, 4>(prm, pl, st, pdl);
+        case 5: return launch_one<XT, 5>(prm, pl, st, pdl);
+        default: return launch_one<XT, 6>(prm, pl, st, pdl);
     }
-}
-
-template <int XT>
-static int launch_nw(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
-    return pl.nwarp == 4 ? launch_nt<XT, 4>(prm, pl, st, pdl) : launch_nt<XT, 8>(prm, pl, st, pdl);
 }
 
 }  // namespace qv
 
-QV_API void qvb8_small_m_set_tuning(int nwarp, int fill) {
-    qv::g_force_nwarp = (nwarp == 4 || nwarp == 8) ? nwarp : 0;
-    qv::g_fill_x = fill > 0 ? (fill & 0xff) : 3;
-    qv::g_debug = fill > 0 ? (fill >> 8) : 0;
+QV_API void qvb8_small_m_set_tuning(int rb, int fill, int nstg, int debug) {
+    qv::g_force_rb = (rb == 16 || rb == 32 || rb == 64 || rb == 128) ? rb : 0;
+    qv::g_fill_x = fill > 0 ? fill : 2;
+    qv::g_force_nstg = (nstg >= 2 && nstg <= qv::MAX_STAGES) ? nstg : 0;
+    qv::g_debug = debug;
+}
+
+QV_API int qvb8_device_status(int *status) {
+    if (!status) return qv::fail(QVB8_ERR_ARG, "qvb8_device_status: null output");
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, qv::g_error_word, sizeof(int)) != cudaSuccess) return qv::cuda_status("qvb8_device_status");
+    *status = v;
+    return QVB8_OK;
 }
 
 QV_API int64_t qvb8_small_m_scratch_bytes(int64_t M, int64_t Q, int64_t P) {
@@ -779,14 +871,13 @@ QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *esc_plan, const void 
         prm.esc_col = reinterpret_cast<const int *>(reinterpret_cast<const uint8_t *>(esc_plan) + ptr_b);
         prm.esc_delta = reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(esc_plan) + ptr_b + col_b);
     }
-    prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.S = pl.S; prm.nc_per = pl.nc_per;
-    prm.nc_total = pl.nc_total;
-    prm.debug = g_debug;
+    prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.rb = pl.rb; prm.S = pl.S;
+    prm.nc_per = pl.nc_per; prm.nc_total = pl.nc_total; prm.nstg = pl.nstg; prm.debug = g_debug;
     const bool pdl = (flags & QVB8_FLAG_PDL) != 0;
     int rc;
-    if (x_dtype == QVB8_F16) rc = launch_nw<QVB8_F16>(prm, pl, st, pdl);
-    else if (x_dtype == QVB8_BF16) rc = launch_nw<QVB8_BF16>(prm, pl, st, pdl);
-    else rc = launch_nw<QVB8_F32>(prm, pl, st, pdl);
+    if (x_dtype == QVB8_F16) rc = launch_nt<QVB8_F16>(prm, pl, st, pdl);
+    else if (x_dtype == QVB8_BF16) rc = launch_nt<QVB8_BF16>(prm, pl, st, pdl);
+    else rc = launch_nt<QVB8_F32>(prm, pl, st, pdl);
     if (rc) return rc;
     if (planned || w->n_esc == 0) return QVB8_OK;
     return launch_fix_escapes(w, X, x_dtype, x_mode, (int)M, Y, st);

@@ -23,6 +23,7 @@ _CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
 EXPORTS = (
     "qvb8_last_error", "qvb8_version", "qvb8_decode", "qvb8_small_m_scratch_bytes", "qvb8_small_m",
     "qvb8_small_m_generic", "qvb8_escape_plan_bytes", "qvb8_escape_plan", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
+    "qvb8_device_status",
 )
 
 
@@ -64,7 +65,8 @@ def load() -> ctypes.CDLL:
             lib.qvb8_escape_plan_bytes.restype = i64
             lib.qvb8_escape_plan.argtypes = [pk, vp, i64, vp]
             lib.qvb8_small_m_ex.argtypes = [pk, vp, vp, ci, ci, i64, vp, vp, i64, ci, vp]
-            lib.qvb8_small_m_set_tuning.argtypes = [ci, ci]
+            lib.qvb8_small_m_set_tuning.argtypes = [ci, ci, ci, ci]
+            lib.qvb8_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
             lib.qvb8_small_m_set_tuning.restype = None
             _lib = lib
     return _lib
@@ -160,6 +162,14 @@ def decode(pack, keep, out_dtype: torch.dtype) -> torch.Tensor:
 
 
 FLAG_PDL = 1
+
+
+def device_status(device=None) -> int:
+    """Error word of `device` (0 = no kernel of this library ever gave up on a wait).  Synchronises."""
+    v = ctypes.c_int(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        check(load().qvb8_device_status(ctypes.byref(v)), "qvb8_device_status")
+    return int(v.value)
 
 
 def escape_plan(pack, keep) -> torch.Tensor | None:

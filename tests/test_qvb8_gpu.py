@@ -138,10 +138,10 @@ def test_generic_path_agrees(cuda_lib):
     assert rel_fro(a.cpu().numpy(), b.cpu().numpy()) < 1e-5
 
 
-@pytest.mark.parametrize("nwarp", [4, 8])
+@pytest.mark.parametrize("rb,nstg", [(16, 2), (32, 3), (64, 0), (128, 8)])
 @pytest.mark.parametrize("M", [1, 5, 16])
-def test_escape_plan_and_cta_shapes(cuda_lib, nwarp, M):
-    """The fused escape correction (row-grouped plan) and both CTA shapes give the same product as the oracle."""
+def test_escape_plan_and_cta_shapes(cuda_lib, rb, nstg, M):
+    """The fused escape correction (row-grouped plan), every CTA row-block size and ring depth give the oracle's product."""
     from qvb8_b200 import lib
     pk = random_pack(300, 1536, (4, 6, 7, 8, 11), seed=31 + M, esc_frac=0.004, device=DEV)
     X = synth.synth_activation(M, 1536, seed=M, device=DEV)
@@ -149,7 +149,7 @@ def test_escape_plan_and_cta_shapes(cuda_lib, nwarp, M):
     plan = lib.escape_plan(st, keep)
     want = _oracle_y(pk, X)
     try:
-        lib.load().qvb8_small_m_set_tuning(nwarp, 3)
+        lib.load().qvb8_small_m_set_tuning(rb, 2, nstg, 0)
         for flags in (0, lib.FLAG_PDL):
             y = lib.small_m(st, keep, X, plan=plan, flags=flags)
             err = rel_fro(y.cpu().numpy(), want)
@@ -157,7 +157,7 @@ def test_escape_plan_and_cta_shapes(cuda_lib, nwarp, M):
         y_noplan = lib.small_m(st, keep, X)
         assert rel_fro(y_noplan.cpu().numpy(), want) < TIGHT
     finally:
-        lib.load().qvb8_small_m_set_tuning(0, 3)
+        lib.load().qvb8_small_m_set_tuning(0, 0, 0, 0)
 
 
 def test_escape_plan_rows_without_escapes(cuda_lib):
@@ -182,6 +182,12 @@ def test_small_m_is_deterministic(cuda_lib):
     a = ext.forward(X, *ext_args(pk))
     for _ in range(3):
         assert torch.equal(a, ext.forward(X, *ext_args(pk)))
+
+
+def test_no_wait_ever_gave_up(cuda_lib):
+    """Runs late in this file: the device-side error word must still be zero after every kernel above."""
+    from qvb8_b200 import lib
+    assert lib.device_status() == 0
 
 
 def test_gemv_m1_entry_point(cuda_lib):
