@@ -97,13 +97,14 @@ int qvb8_escape_plan(const qvb8_pack *w, void *plan, int64_t plan_bytes, void *s
 int qvb8_small_m_ex(const qvb8_pack *w, const void *esc_plan, const void *X, int x_dtype, int x_mode, int64_t M,
                     float *Y, void *scratch, int64_t scratch_bytes, int flags, void *stream);
 
-/* Tuning hook for tests and sweeps (process-wide; 0 = choose automatically): rb = output rows per CTA (16, 32, 64
- * or 128); fill = how many CTAs per SM the K split aims for (default 2); nstg = stages of the copy ring (2..8);
+/* Tuning hook for tests and sweeps (process-wide; 0 = choose automatically): rb = output rows per CTA (16, 32, 48
+ * or 64); fill = how many CTAs per SM the split aims for (default: one full wave); nstg = stages of the copy ring (2..8);
  * debug bit 0 = skip the fragment math (copy stream only). */
 void qvb8_small_m_set_tuning(int rb, int fill, int nstg, int debug);
 
 /* Device-side error word of the current device: 0, or the code of the first bounded wait that gave up inside a
- * kernel of this library (1 = copy ring slot never freed, 2 = copy never landed).  Synchronises the host. */
+ * kernel of this library (1 = copy ring slot never freed, 2 = copy never landed, 3 / 4 = escape-correction
+ * hand-over).  Synchronises the host. */
 int qvb8_device_status(int *status);
 
 /* Same product through the layout-agnostic kernel (any P, any id alignment, widths 1..14).  The library falls

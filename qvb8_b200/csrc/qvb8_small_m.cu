@@ -48,12 +48,12 @@ int check_small_m_args(const qvb8_pack *w, const void *X, int x_dtype, int x_mod
                        const char *who);
 
 constexpr int KC = 128;                   // columns per chunk
-constexpr int NW = 8;                     // consumer warps = chunks per stage
-constexpr int NTHREADS = (NW + 1) * 32;   // + one producer warp
-constexpr int STAGE_ROW_MAX = 1040;       // bytes of one row in a stage (8-bit rows: 8 * 128 + 16 pad)
-constexpr int STAGE_BYTES = 16 * STAGE_ROW_MAX;
+constexpr int NW = 4;                     // consumer warps = chunks per stage
+constexpr int PRODUCER_WARP = NW;         // issues the bulk copies
+constexpr int ESCAPE_WARP = NW + 1;       // sums the escape corrections of the tile being streamed
+constexpr int NTHREADS = (NW + 2) * 32;
 constexpr int MAX_STAGES = 8;
-constexpr int RB_MAX = 128;               // rows per CTA, at most
+constexpr int RB_MAX = 64;                // rows per CTA, at most
 constexpr int NCLASS = 7;                 // widths 3..8 -> class 0..5; every other width -> class 6 (per-element path)
 constexpr int MAXTILES = RB_MAX / 16 + NCLASS - 1;
 constexpr int64_t TICKET_BYTES = 64 * 1024;   // fixed-size counter area at the START of the scratch, so that calls of
@@ -70,6 +70,7 @@ struct TileTable {
     float row_ms[RB_MAX], row_ts[RB_MAX];
     int8_t row_cls[RB_MAX];
     uint8_t row_nb[RB_MAX];
+    int row_e0[RB_MAX], row_e1[RB_MAX];   // the row's range in the escape plan
     // tiles
     int ntiles;
     int need_b;                     // some tile pairs ids at distance 4: the second activation layout is needed
@@ -82,6 +83,8 @@ struct TileTable {
     int abort;
     alignas(8) uint64_t full[MAX_STAGES];
     alignas(8) uint64_t empty[MAX_STAGES];
+    alignas(8) uint64_t corr_full[2];     // escape corrections of a tile are in corr[buf]
+    alignas(8) uint64_t corr_empty[2];    // ... and have been consumed
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -227,7 +230,21 @@ __device__ __forceinline__ void load_block<3>(uint32_t addr, uint32_t (&W)[3]) {
 // Bytes between rows of a stage.  The eight chunks of a row lie back to back (a contiguous copy); the stride adds
 // one chunk's worth of padding (16 bytes for 8-bit rows) so that the 32 lanes of a warp, which read rows g and
 // columns 32 t of ONE chunk, fall on distinct banks.
-__host__ __device__ constexpr int stage_row_stride(int nb) { return nb == 8 ? STAGE_ROW_MAX : 16 * nb * (NW + 1); }
+__host__ __device__ constexpr bool stride_ok(int nb, int rs) {
+    return nb == 8 ? (rs / 16) % 8 == 1                  // 16-byte loads, quarter warps (rows 2i, 2i+1)
+         : nb == 4 ? (rs / 16) % 8 == 4
+         : nb == 6 ? (rs / 8) % 16 == 12                 // 8-byte loads, half warps (rows 4i .. 4i+3)
+                   : (rs / 4) % 32 == (4 * nb) % 32;     // 4-byte loads, whole warp
+}
+__host__ __device__ constexpr int stage_row_stride(int nb) {
+    int rs = 16 * nb * NW;
+    while (!stride_ok(nb, rs)) rs += 16;
+    return rs;
+}
+constexpr int STAGE_ROW_MAX = stage_row_stride(8) > stage_row_stride(7) ? stage_row_stride(8) : stage_row_stride(7);
+constexpr int STAGE_BYTES = 16 * STAGE_ROW_MAX;
+static_assert(stage_row_stride(3) <= STAGE_ROW_MAX && stage_row_stride(4) <= STAGE_ROW_MAX &&
+              stage_row_stride(5) <= STAGE_ROW_MAX && stage_row_stride(6) <= STAGE_ROW_MAX, "stage row size");
 
 // One 128-column chunk of a 16-row tile of width NB: 8 MMAs per token group.
 //   wa, wb   shared addresses of this thread's blocks in rows g and g + 8 of the stage
@@ -365,9 +382,9 @@ __device__ __forceinline__ void tile_escapes(const SmallMParams &p, const TileTa
     }
 }
 
-template <int XT, int NT>
-__global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(const SmallMParams p) {
-    constexpr bool DUAL = NT == 1;                                     // second activation layout (cheap for few tokens)
+// DUAL: a second activation layout is staged for widths that pair ids at distance 4 (cheap for few tokens).
+template <int XT, int NT, bool DUAL>
+__global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small_m_kernel(const SmallMParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ TileTable tt;
 
@@ -381,13 +398,15 @@ __global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(cons
     const int NSK = (NC + NW - 1) / NW;                                // stages along K per tile
     const int MP = p.MP;
     const int nstg = p.nstg;
-    // dynamic shared memory: [stages][activations A][activations B][tile reduction x 2][16 zero bytes]
+    // dynamic shared memory: [stages][activations A][activations B][tile reduction x 2][16 zero bytes][corrections x 2]
     uint8_t *stages = smem;
     const int xs_halves = p.nc_per * 16 * MP * 8;                      // halves per activation layout
     __half *xs_a = reinterpret_cast<__half *>(smem + (size_t)nstg * STAGE_BYTES);
     __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
     float *red = reinterpret_cast<float *>(xs_a + (DUAL ? 2 : 1) * xs_halves);     // [2][NW][4 * NT][32]
     uint32_t *zero16 = reinterpret_cast<uint32_t *>(red + 2 * NW * 4 * NT * 32);
+    float *corr = reinterpret_cast<float *>(zero16 + 4);               // [2][16][M] escape corrections of a tile
+    const bool planned = p.esc_ptr != nullptr;
     volatile int *abort_flag = &tt.abort;
 
     // ---- 1. barriers; row metadata in one round trip; rows sorted by width into tiles (stable order)
@@ -395,6 +414,10 @@ __global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(cons
         for (int s = 0; s < nstg; ++s) {
             mbar_init(smem_u32(&tt.full[s]), 1);
             mbar_init(smem_u32(&tt.empty[s]), NW);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&tt.corr_full[b]), 1);
+            mbar_init(smem_u32(&tt.corr_empty[b]), 1);
         }
         tt.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -409,6 +432,7 @@ __global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(cons
             tt.row_ts[r] = __ldg(p.tau_s + q0 + r);
             tt.row_b16[r] = (uint32_t)(bo >> 7);
             tt.row_nb[r] = (uint8_t)nb;
+            if (planned) { tt.row_e0[r] = __ldg(p.esc_ptr + q0 + r); tt.row_e1[r] = __ldg(p.esc_ptr + q0 + r + 1); }
             cls = (nb >= 3 && nb <= 8 && (bo & 127) == 0) ? nb - 3 : NCLASS - 1;     // 16-byte aligned row start
         }
         tt.row_cls[r] = (int8_t)cls;
@@ -448,7 +472,7 @@ __global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(cons
     const int ntiles = tt.ntiles;
     float *out = p.S > 1 ? p.part + (int64_t)split * p.M * p.Q : p.Y;
 
-    if (warp == NW) {
+    if (warp == PRODUCER_WARP) {
         // ================= producer warp: lane r copies row r of every stage =================
         int slot = 0;
         uint32_t phase = 0;
@@ -471,6 +495,54 @@ __global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(cons
                     bulk_g2s(smem_u32(stages + (size_t)slot * STAGE_BYTES) + dst_row, src + (size_t)s * NW * 16 * nb,
                              bytes_row, full);
                 if (++slot == nstg) { slot = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == ESCAPE_WARP) {
+        // ================= escape warp: per tile, lane r sums row r's corrections x * (exact - band) in stored
+        // order over the escapes that fall into this K-range, ahead of the warp that will write the tile =========
+        asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // activations are staged
+        if (planned) {
+            int staged = 0;
+            bool alive = true;
+            const int clo = kc0 * KC, chi = clo + NC * KC;
+            for (int ti = 0; ti < ntiles; ++ti) {
+                if (tt.tile_nb[ti] == 0) continue;
+                const int buf = staged & 1;
+                if (alive) alive = mbar_wait(smem_u32(&tt.corr_empty[buf]), ((staged >> 1) & 1) ^ 1u, abort_flag, 3);
+                const int lr = lane < 16 ? tt.tile_row[ti][lane] : -1;
+                if (lr >= 0 && alive) {
+                    const int e0 = tt.row_e0[lr], e1 = tt.row_e1[lr];
+                    float *dst = corr + (buf * 16 + lane) * p.M;
+                    for (int m0 = 0; m0 < p.M; m0 += 8) {
+                        float a[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) a[k] = 0.f;
+                        for (int e = e0; e < e1; e += 4) {
+                            int c[4];
+                            float d[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {                   // four independent loads in flight
+                                const bool ok = e + j < e1;
+                                c[j] = ok ? __ldg(p.esc_col + e + j) : -1;
+                                d[j] = ok ? __ldg(p.esc_delta + e + j) : 0.f;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (c[j] >= clo && c[j] < chi) {
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k)
+                                        if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c[j] - clo, m0 + k, MP), d[j], a[k]);
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            if (m0 + k < p.M) dst[m0 + k] = a[k];
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&tt.corr_full[buf]));
+                ++staged;
             }
         }
     } else {
@@ -505,7 +577,7 @@ __global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(cons
                 for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                 if (lane == 0) tt.sumx[m] = s;
             }
-            consumer_sync();
+            asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // consumers + escape warp
         }
         pdl_launch_dependents();
 
@@ -551,7 +623,7 @@ __global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(cons
                         }
                     }
                 }
-                if (p.esc_ptr != nullptr) {
+                if (planned) {
                     consumer_sync();                                    // every warp's rows of this tile are written
                     if (warp == 0) tile_escapes(p, tt, ti, lane, q0, kc0, NC, xs_a, MP, out);
                 }
@@ -583,7 +655,7 @@ __global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(cons
                 if (lane == 0) mbar_arrive(smem_u32(&tt.empty[slot]));
                 if (++slot == nstg) { slot = 0; phase ^= 1u; }
             }
-            // ---- the eight warps' partial sums, added in warp order by one warp
+            // ---- the warps' partial sums, added in warp order by one warp
             float *rbuf = red + (size_t)(staged & 1) * (NW * 4 * NT * 32);
 #pragma unroll
             for (int n = 0; n < NT; ++n)
@@ -600,27 +672,34 @@ __global__ void __launch_bounds__(NTHREADS, NT <= 2 ? 2 : 1) small_m_kernel(cons
                         for (int w = 0; w < NW; ++w) v += rbuf[(w * 4 * NT + n * 4 + k) * 32 + lane];
                         acc[n][k] = v;
                     }
-                // y = tau_s * sum(x * id) + min_s * sum(x); thread holds rows g, g+8 and tokens 8n+2t, 8n+2t+1
+                const int buf = staged & 1;
+                if (planned && alive) alive = mbar_wait(smem_u32(&tt.corr_full[buf]), (staged >> 1) & 1, abort_flag, 4);
+                // y = tau_s * sum(x * id) + min_s * sum(x) (+ escape corrections); thread holds rows g, g+8 and
+                // tokens 8n+2t, 8n+2t+1
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
                     const int lr = tt.tile_row[ti][g + 8 * hrow];
                     if (lr >= 0) {
                         const float ms = tt.row_ms[lr], ts = tt.row_ts[lr];
                         const int q = q0 + lr;
+                        const float *cr = corr + (buf * 16 + g + 8 * hrow) * p.M;
 #pragma unroll
                         for (int n = 0; n < NT; ++n) {
 #pragma unroll
                             for (int k = 0; k < 2; ++k) {
                                 const int m = 8 * n + 2 * t + k;
-                                if (m < p.M)
-                                    out[(int64_t)m * p.Q + q] = __fmaf_rn(ts, acc[n][2 * hrow + k], ms * tt.sumx[m]);
+                                if (m < p.M) {
+                                    float y = __fmaf_rn(ts, acc[n][2 * hrow + k], ms * tt.sumx[m]);
+                                    if (planned) y += cr[m];
+                                    out[(int64_t)m * p.Q + q] = y;
+                                }
                             }
                         }
                     }
                 }
-                if (p.esc_ptr != nullptr) {
-                    __syncwarp();                                       // the tile's results are written
-                    tile_escapes(p, tt, ti, lane, q0, kc0, NC, xs_a, MP, out);
+                if (planned) {
+                    __syncwarp();                                       // every lane has read its corrections
+                    if (lane == 0) mbar_arrive(smem_u32(&tt.corr_empty[buf]));
                 }
             }
             ++staged;
@@ -700,7 +779,7 @@ static int device_sms() {
 }
 
 // tuning hooks (qvb8_small_m_set_tuning): 0 = choose automatically
-static int g_force_rb = 0, g_fill_x = 2, g_force_nstg = 0, g_debug = 0;
+static int g_force_rb = 0, g_fill_x = 0, g_force_nstg = 0, g_debug = 0;
 
 static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     Plan pl{};
@@ -708,9 +787,9 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     pl.NT = (int)((M + 7) / 8);
     pl.MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * pl.NT;
     const int sms = device_sms();
-    const int layouts = pl.NT == 1 ? 2 : 1;
+    const int layouts = pl.MP <= 4 ? 2 : 1;
     // K-range length: bounded by the shared memory the staged activations may take
-    const int xs_budget = pl.NT == 1 ? 32 * 1024 : pl.NT == 2 ? 48 * 1024 : 96 * 1024;
+    const int xs_budget = pl.MP <= 4 ? 8 * 1024 : pl.NT == 1 ? 16 * 1024 : pl.NT == 2 ? 32 * 1024 : 96 * 1024;
     int nc_max = xs_budget / (KC * pl.MP * 2 * layouts);
     if (nc_max >= NW) nc_max = nc_max / NW * NW;                        // whole stages
     if (nc_max < 1) nc_max = 1;
@@ -718,7 +797,7 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     // rows per CTA and K split: enough CTAs to fill the GPU g_fill_x times over where the shape allows it, each
     // K-range at least one full stage
     const int s_cap = pl.nc_total / NW > 0 ? pl.nc_total / NW : 1;
-    const int target = g_fill_x * sms;
+    const int target = (g_fill_x ? g_fill_x : (pl.NT == 1 ? 4 : pl.NT == 2 ? 2 : 1)) * sms;   // default: one full wave
     int rb = g_force_rb ? g_force_rb : RB_MAX;
     int S = s_xs;
     for (;;) {
@@ -726,7 +805,7 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
         int want = (target + nblk - 1) / nblk;
         if (want > s_cap) want = s_cap;
         S = s_xs > want ? s_xs : want;
-        if (g_force_rb || rb <= 32 || (int64_t)nblk * S >= target) break;
+        if (g_force_rb || rb <= 16 || (int64_t)nblk * S >= target) break;
         rb /= 2;
     }
     pl.rb = rb;
@@ -737,8 +816,8 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     if (pl.nc_per > nc_max) pl.nc_per = nc_max;
     pl.S = (pl.nc_total + pl.nc_per - 1) / pl.nc_per;                   // no empty range
     const size_t xs_bytes = (size_t)pl.nc_per * KC * pl.MP * 2 * layouts;
-    const size_t red_bytes = (size_t)2 * NW * 4 * pl.NT * 32 * 4;
-    const size_t per_cta = (size_t)(pl.NT <= 2 ? 110 : 220) * 1024;
+    const size_t red_bytes = (size_t)2 * NW * 4 * pl.NT * 32 * 4 + (size_t)2 * 16 * M * 4;   // + escape corrections
+    const size_t per_cta = (size_t)(pl.NT == 1 ? 51 : pl.NT == 2 ? 106 : 216) * 1024;        // 4 / 2 / 1 CTAs per SM
     int nstg = g_force_nstg ? g_force_nstg : (int)((per_cta - xs_bytes - red_bytes - 64) / STAGE_BYTES);
     if (nstg > MAX_STAGES) nstg = MAX_STAGES;
     if (nstg < 2) nstg = 2;
@@ -754,9 +833,9 @@ static bool fast_layout_ok(const qvb8_pack *w, const void *X) {
     return w->P > 0 && w->P % KC == 0 && aligned(w->ids, 16) && aligned(X, 16);
 }
 
-template <int XT, int NT>
+template <int XT, int NT, bool DUAL>
 static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
-    auto kern = small_m_kernel<XT, NT>;
+    auto kern = small_m_kernel<XT, NT, DUAL>;
     static thread_local int granted_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -782,20 +861,20 @@ static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, 
 template <int XT>
 static int launch_nt(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
     switch (pl.NT) {
-        case 1: return launch_one<XT, 1>(prm, pl, st, pdl);
-        case 2: return launch_one<XT, 2>(prm, pl, st, pdl);
-        case 3: return launch_one<XT, 3>(prm, pl, st, pdl);
-        case 4: return launch_one<XT, 4>(prm, pl, st, pdl);
-        case 5: return launch_one<XT, 5>(prm, pl, st, pdl);
-        default: return launch_one<XT, 6>(prm, pl, st, pdl);
+        case 1: return pl.MP <= 4 ? launch_one<XT, 1, true>(prm, pl, st, pdl) : launch_one<XT, 1, false>(prm, pl, st, pdl);
+        case 2: return launch_one<XT, 2, false>(prm, pl, st, pdl);
+        case 3: return launch_one<XT, 3, false>(prm, pl, st, pdl);
+        case 4: return launch_one<XT, 4, false>(prm, pl, st, pdl);
+        case 5: return launch_one<XT, 5, false>(prm, pl, st, pdl);
+        default: return launch_one<XT, 6, false>(prm, pl, st, pdl);
     }
 }
 
 }  // namespace qv
 
 QV_API void qvb8_small_m_set_tuning(int rb, int fill, int nstg, int debug) {
-    qv::g_force_rb = (rb == 16 || rb == 32 || rb == 64 || rb == 128) ? rb : 0;
-    qv::g_fill_x = fill > 0 ? fill : 2;
+    qv::g_force_rb = (rb == 16 || rb == 32 || rb == 48 || rb == 64) ? rb : 0;
+    qv::g_fill_x = fill > 0 ? fill : 0;
     qv::g_force_nstg = (nstg >= 2 && nstg <= qv::MAX_STAGES) ? nstg : 0;
     qv::g_debug = debug;
 }
