@@ -76,7 +76,8 @@ int64_t qvb8_small_m_scratch_bytes(int64_t M, int64_t Q, int64_t P);
  *            1: X keeps its range (an exact power-of-two prescale per token instead of the clamp)
  * The weight is the un-narrowed fp32 band value (or the exact escape value), the contract of the reference's
  * M <= 8 GEMV.  Replaces `forward` for M <= 8, `gemv`, `gemv_multi` (qvb8_cuda.cu:1059-1166, 1416-1512, kernels
- * :306-453, :463-470, :507-533) and `mma_multi` (:2566-2671). */
+ * :306-453, :463-470, :507-533) and `mma_multi` (:2566-2671).  Without a plan (see qvb8_small_m_ex) this entry point
+ * runs the layout-agnostic kernel; it needs no scratch then. */
 int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,
                  int64_t scratch_bytes, void *stream);
 
@@ -85,22 +86,27 @@ int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int
                                the tail of the previous kernel in the stream; everything that depends on earlier
                                work (reading X, writing Y and the scratch) waits for it to complete */
 
-/* Escape plan: the pack's escape list regrouped by row, with the difference (exact value - band value)
- * precomputed, so that the fused kernel corrects escapes itself instead of running a second pass.  Build once per
- * pack (and per escape table); the buffer must be 16-byte aligned and hold qvb8_escape_plan_bytes(Q, n_esc) bytes.
- * The reference regroups its escapes the same way at load time for its mma path (formats/qvb8/module.py:279-288,
- * esc_starts) and stores precomputed differences in its qvb8r files (formats/qvb8r/container.py:10-12). */
-int64_t qvb8_escape_plan_bytes(int64_t Q, int64_t n_esc);
-int qvb8_escape_plan(const qvb8_pack *w, void *plan, int64_t plan_bytes, void *stream);
+/* Plan of a pack, built once per pack (and per escape table) and then passed to every qvb8_small_m_ex call:
+ *   - the rows sorted by width (stable) into 16-row tiles of one width, one 400-byte descriptor per tile
+ *     (rows, byte offsets, min_s, tau_s, escape ranges) -- the ordering the reference computes per module for its
+ *     tensor-core path (formats/qvb8/module.py:230-277 _mma_order: perm / tile_nb);
+ *   - the escape list regrouped by row with the difference (exact value - band value) precomputed -- as the
+ *     reference does at load time for its mma path (module.py:279-288 esc_starts) and stores in its qvb8r files
+ *     (formats/qvb8r/container.py:10-12 esc_delta).
+ * The buffer must be 16-byte aligned and hold qvb8_plan_bytes(Q, n_esc) bytes.  The plan refers to the pack's
+ * buffers by offset only; it stays valid while their contents do. */
+int64_t qvb8_plan_bytes(int64_t Q, int64_t n_esc);
+int qvb8_plan_build(const qvb8_pack *w, void *plan, int64_t plan_bytes, void *stream);
 
-/* qvb8_small_m with an optional escape plan (may be NULL) and launch flags. */
-int qvb8_small_m_ex(const qvb8_pack *w, const void *esc_plan, const void *X, int x_dtype, int x_mode, int64_t M,
+/* qvb8_small_m through the streaming kernel: `plan` from qvb8_plan_build (NULL selects the layout-agnostic
+ * kernel), plus launch flags. */
+int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int x_mode, int64_t M,
                     float *Y, void *scratch, int64_t scratch_bytes, int flags, void *stream);
 
-/* Tuning hook for tests and sweeps (process-wide; 0 = choose automatically): rb = output rows per CTA (16, 32, 48
- * or 64); fill = how many CTAs per SM the split aims for (default: one full wave); nstg = stages of the copy ring (2..8);
- * debug bit 0 = skip the fragment math (copy stream only). */
-void qvb8_small_m_set_tuning(int rb, int fill, int nstg, int debug);
+/* Tuning hook for tests and sweeps (process-wide; 0 = choose automatically): fill_pct = CTAs launched, in percent of
+ * one resident wave; force_s = number of K-ranges (raised to what shared memory requires); nstg = slots of the copy
+ * ring (2..8); debug bit 0 = skip the fragment math (copy stream only). */
+void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int debug);
 
 /* Device-side error word of the current device: 0, or the code of the first bounded wait that gave up inside a
  * kernel of this library (1 = copy ring slot never freed, 2 = copy never landed, 3 / 4 = escape-correction

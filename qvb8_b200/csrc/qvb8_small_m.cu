@@ -3,7 +3,8 @@
 //
 // Replaces the reference's GEMV family and its mma.sync verify kernel
 // (formats/qvb8/backends/cuda_qvb8/qvb8_cuda.cu:306-453 qvb8_gemv_multi_v3, :463-489 split-K, :507-533 escape
-// correction, :1813-2441 qvb8_mma_*).
+// correction, :1813-2441 qvb8_mma_*), and the per-module row ordering the reference computes for it
+// (formats/qvb8/module.py:230-288 _mma_order / _esc_row_starts).
 //
 // Arithmetic.  With w = min_s + id * tau_s the row sum factors (the identity the reference states at
 // qvb8_cuda.cu:3-9):   y[m, q] = min_s[q] * sum_c x[m, c]  +  tau_s[q] * sum_c x[m, c] * id[q, c].
@@ -12,27 +13,27 @@
 // is therefore the un-narrowed band value, the contract of the reference's M <= 8 GEMV; X is narrowed to saturated
 // fp16 first, as every fp16-mode path of the reference does (:761-841).
 //
+// Plan.  Rows of a pack have different widths.  Once per pack, qvb8_plan_build sorts the rows by width (stable) into
+// 16-row TILES of one width and writes one 400-byte descriptor per tile (rows, byte offsets, origins, steps, escape
+// ranges), and regroups the escapes by row with the difference (exact - band) precomputed.  The product kernel only
+// follows descriptors.
+//
 // Roofline: HBM.  Per weight the kernel moves nbits/8 bytes (about 0.8).  What HBM sees matters as much as how
-// much: rows of a pack are contiguous byte ranges, so a CTA fetches, for each of the 16 rows of a tile, ONE
-// contiguous run of up to 1 KB per stage with a bulk asynchronous copy (cp.async.bulk, completion on an mbarrier).
-// A producer warp keeps several stages in flight; eight consumer warps each take one 128-column chunk of the stage.
+// much: a row is a contiguous byte range, so for each of the 16 rows of a tile a producer warp fetches ONE
+// contiguous run of 512 columns (384 - 512 bytes) per stage with a bulk asynchronous copy (cp.async.bulk, completion
+// counted on an mbarrier), several stages ahead; the tile's descriptor travels with its first stage.  CTAs are
+// persistent: a CTA keeps one K-range (its activations stay staged in shared memory as fp16, in fragment order) and
+// walks every (gridDim.x)-th tile, so the copy stream never drains between tiles.
 //
-// Work split.  A CTA owns a block of consecutive output rows and one K-range.  Rows of a pack have different widths,
-// so the CTA first sorts its rows by width into 16-row tiles of ONE width (shared-memory lists; no precomputed
-// ordering is needed) and walks the tiles one after the other.  Within a chunk, thread (g = lane / 4, t = lane % 4)
-// owns the 32 ids of rows g and g + 8 that start at column 32 t -- exactly nb 32-bit words -- and turns them into
-// the A fragments of eight m16n8k16 MMAs.  Two ids are converted per instruction: a funnel shift puts one id in the
-// low half-word and one in the high half-word of a register, `(r & mask) | 0x64006400` makes the two fp16 numbers
-// 1024 + id * 2^e, and one HFMA2 removes the 1024 and the 2^e exactly.  The B fragments are the activations, staged
-// once per CTA as fp16 in the order the fragments want.  At the end of a tile the eight warps' partial accumulators
-// are added in warp order by one warp, which writes the result.  K-ranges of one row block are summed in a fixed
-// order by the last CTA of the block to finish (a ticket counter).  Every sum has a fixed order: results are
-// identical from run to run.
-//
-// Escapes.  Positions whose exact value is stored separately get x * (exact - band) added.  With an escape plan
-// (row pointers + columns + precomputed differences, built once per pack by qvb8_escape_plan) the warp that finishes
-// a tile adds its rows' corrections in stored order before the result leaves the CTA; without a plan a second
-// kernel walks the raw (position, value) list.
+// Math.  Four consumer warps each take one 128-column chunk of the stage.  Thread (g = lane / 4, t = lane % 4) owns
+// the 32 ids of rows g and g + 8 that start at column 32 t -- exactly nb 32-bit words -- and turns them into the A
+// fragments of eight m16n8k16 MMAs.  Two ids are converted per instruction: a funnel shift puts one id in the low
+// half-word and one in the high half-word of a register, `(r & mask) | 0x64006400` makes the two fp16 numbers
+// 1024 + id * 2^e, and one HFMA2 removes the 1024 and the 2^e exactly.  At the end of a tile the warps' partial
+// accumulators are added in warp order by one warp, which applies min_s / tau_s, adds the escape corrections a
+// sixth warp has summed meanwhile (per row, in stored order) and writes the result.  K-ranges of one tile are added
+// in range order by whichever CTA finishes the tile last (a ticket counter per tile).  Every sum has a fixed order:
+// results are identical from run to run.
 //
 // Waits.  Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the waiter raises a per-CTA abort flag and a
 // device-wide error word (qvb8_device_status), every other waiter gives up too, and the kernel runs to its end with
@@ -53,33 +54,55 @@ constexpr int PRODUCER_WARP = NW;         // issues the bulk copies
 constexpr int ESCAPE_WARP = NW + 1;       // sums the escape corrections of the tile being streamed
 constexpr int NTHREADS = (NW + 2) * 32;
 constexpr int MAX_STAGES = 8;
-constexpr int RB_MAX = 64;                // rows per CTA, at most
 constexpr int NCLASS = 7;                 // widths 3..8 -> class 0..5; every other width -> class 6 (per-element path)
-constexpr int MAXTILES = RB_MAX / 16 + NCLASS - 1;
-constexpr int64_t TICKET_BYTES = 64 * 1024;   // fixed-size counter area at the START of the scratch, so that calls of
-                                              // different sizes sharing one scratch never find partial sums in it
-constexpr int MAX_TICKET_BLOCKS = (int)(TICKET_BYTES / 4);
+constexpr int64_t TICKET_BYTES = 256 * 1024;  // fixed-size counter area at the START of the scratch (one counter per
+                                              // tile), so that calls of different sizes sharing one scratch never
+                                              // find partial sums in it
+constexpr int MAX_TICKET_TILES = (int)(TICKET_BYTES / 4);
 constexpr int MAX_M = 48;
 constexpr int SPIN_LIMIT = 1 << 22;
 
 __device__ int g_error_word = 0;          // first timeout of any kernel of this library (0 = none)
 
-struct TileTable {
-    // per row of the block (local index)
-    uint32_t row_b16[RB_MAX];       // byte offset of the row in `ids`, in 16-byte units
-    float row_ms[RB_MAX], row_ts[RB_MAX];
-    int8_t row_cls[RB_MAX];
-    uint8_t row_nb[RB_MAX];
-    int row_e0[RB_MAX], row_e1[RB_MAX];   // the row's range in the escape plan
-    // tiles
-    int ntiles;
-    int need_b;                     // some tile pairs ids at distance 4: the second activation layout is needed
-    int8_t tile_nb[MAXTILES];       // width of the tile's rows; 0 = per-element class
-    int8_t tile_cnt[MAXTILES];      // real rows in the tile (the rest is padding)
-    int16_t tile_row[MAXTILES][16]; // local row index, -1 = padding
-    int16_t list[NCLASS][RB_MAX];   // scratch of the classification
+// One tile of the plan: up to 16 rows of one width.  400 bytes, 16-byte aligned: copied whole by one bulk copy.
+struct TileDesc {
+    int nb;                 // width of the rows; 0 = per-element class (width outside 3..8 or unaligned row start)
+    int cnt;                // real rows (the rest is padding)
+    int pad[2];
+    int row[16];            // output row, -1 = padding
+    uint32_t b16[16];       // byte offset of the row in `ids`, in 16-byte units
+    float ms[16], ts[16];   // min_s, tau_s
+    int e0[16], e1[16];     // the row's range in the escape plan
+};
+static_assert(sizeof(TileDesc) == 400, "descriptor size");
+constexpr int DESC_BYTES = 400;
+constexpr int DESC_SLOT = 416;            // descriptor area of a ring slot
+
+// Plan buffer layout (offsets in bytes, each section 256-byte aligned):
+//   [0]  header: int ntiles
+//   esc_ptr   int[Q + 1]     first escape of each row
+//   esc_col   int[n_esc]     column of each escape
+//   esc_delta float[n_esc]   exact value - band value
+//   tiles     TileDesc[ceil(Q / 16) + NCLASS - 1]
+struct PlanLayout {
+    int64_t esc_ptr, esc_col, esc_delta, tiles, total;
+    int max_tiles;
+};
+__host__ __device__ inline int64_t up256(int64_t v) { return (v + 255) / 256 * 256; }
+inline PlanLayout plan_layout(int64_t Q, int64_t n_esc) {
+    PlanLayout L{};
+    L.max_tiles = (int)((Q + 15) / 16 + NCLASS - 1);
+    L.esc_ptr = 256;
+    L.esc_col = L.esc_ptr + up256((Q + 1) * 4);
+    L.esc_delta = L.esc_col + up256(n_esc * 4);
+    L.tiles = L.esc_delta + up256(n_esc * 4);
+    L.total = L.tiles + up256((int64_t)L.max_tiles * DESC_BYTES);
+    return L;
+}
+
+// Per-CTA control block in static shared memory.
+struct Control {
     float sumx[MAX_M];
-    int is_last;
     int abort;
     alignas(8) uint64_t full[MAX_STAGES];
     alignas(8) uint64_t empty[MAX_STAGES];
@@ -328,410 +351,14 @@ __device__ __forceinline__ void stage_x8(const void *__restrict__ X, int64_t off
     }
 }
 
-struct SmallMParams {
-    const uint8_t *ids;
-    const float *min_s;
-    const float *tau_s;
-    const uint8_t *nbits;
-    const int64_t *bit_off;
-    const void *X;
-    float *Y;          // (M, Q)
-    float *part;       // (S, M, Q) partial sums when S > 1
-    int *ticket;       // one counter per row block when S > 1 (zero on entry, zero on exit)
-    // escape plan (all null: escapes are corrected by a separate pass)
-    const int *esc_ptr;     // [Q + 1] first escape of each row
-    const int *esc_col;     // column of each escape
-    const float *esc_delta; // exact value - band value
-    int Q, P, M, MP;   // MP: token slots per column group in shared memory (>= M)
-    int rb;            // rows per CTA (multiple of 16, <= RB_MAX)
-    int S;             // K-ranges
-    int nc_per;        // chunks per K-range (the last range may be shorter)
-    int nc_total;      // P / 128
-    int nstg;          // stages of the copy ring
-    int debug;         // bit 0: skip the fragment math (copy stream only; tuning experiments)
-};
-
-// Corrections of the escapes of the 16 rows of a tile that fall into this CTA's K-range, added to results that are
-// already written: lane r (< 16) walks row r's list in stored order.  Called by one warp.
-__device__ __forceinline__ void tile_escapes(const SmallMParams &p, const TileTable &tt, int ti, int lane, int q0,
-                                             int kc0, int NC, const __half *xs_a, int MP, float *out) {
-    const int lr = lane < 16 ? tt.tile_row[ti][lane] : -1;
-    if (lr < 0) return;
-    const int q = q0 + lr;
-    const int e0 = __ldg(p.esc_ptr + q), e1 = __ldg(p.esc_ptr + q + 1);
-    const int clo = kc0 * KC, chi = clo + NC * KC;
-    for (int m0 = 0; m0 < p.M; m0 += 8) {
-        float a[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) a[k] = 0.f;
-        bool any = false;
-        for (int e = e0; e < e1; ++e) {
-            const int c = __ldg(p.esc_col + e);
-            if (c < clo || c >= chi) continue;
-            any = true;
-            const float d = __ldg(p.esc_delta + e);
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-                if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c - clo, m0 + k, MP), d, a[k]);
-        }
-        if (any) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-                if (m0 + k < p.M) out[(int64_t)(m0 + k) * p.Q + q] += a[k];
-        }
-    }
-}
-
-// DUAL: a second activation layout is staged for widths that pair ids at distance 4 (cheap for few tokens).
-template <int XT, int NT, bool DUAL>
-__global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small_m_kernel(const SmallMParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ TileTable tt;
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int RB = p.rb;
-    const int q0 = blockIdx.x * RB;
-    const int nrows = min(RB, p.Q - q0);
-    const int split = blockIdx.y;
-    const int kc0 = split * p.nc_per;                                  // first chunk of this K-range
-    const int NC = min(p.nc_per, p.nc_total - kc0);                    // chunks in this K-range (>= 1 by construction)
-    const int NSK = (NC + NW - 1) / NW;                                // stages along K per tile
-    const int MP = p.MP;
-    const int nstg = p.nstg;
-    // dynamic shared memory: [stages][activations A][activations B][tile reduction x 2][16 zero bytes][corrections x 2]
-    uint8_t *stages = smem;
-    const int xs_halves = p.nc_per * 16 * MP * 8;                      // halves per activation layout
-    __half *xs_a = reinterpret_cast<__half *>(smem + (size_t)nstg * STAGE_BYTES);
-    __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
-    float *red = reinterpret_cast<float *>(xs_a + (DUAL ? 2 : 1) * xs_halves);     // [2][NW][4 * NT][32]
-    uint32_t *zero16 = reinterpret_cast<uint32_t *>(red + 2 * NW * 4 * NT * 32);
-    float *corr = reinterpret_cast<float *>(zero16 + 4);               // [2][16][M] escape corrections of a tile
-    const bool planned = p.esc_ptr != nullptr;
-    volatile int *abort_flag = &tt.abort;
-
-    // ---- 1. barriers; row metadata in one round trip; rows sorted by width into tiles (stable order)
-    if (tid == 0) {
-        for (int s = 0; s < nstg; ++s) {
-            mbar_init(smem_u32(&tt.full[s]), 1);
-            mbar_init(smem_u32(&tt.empty[s]), NW);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&tt.corr_full[b]), 1);
-            mbar_init(smem_u32(&tt.corr_empty[b]), 1);
-        }
-        tt.abort = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    if (tid < 4) zero16[tid] = 0u;
-    for (int r = tid; r < RB_MAX; r += NTHREADS) {
-        int cls = -1;
-        if (r < nrows) {
-            const int nb = __ldg(p.nbits + q0 + r);
-            const int64_t bo = __ldg(p.bit_off + q0 + r);
-            tt.row_ms[r] = __ldg(p.min_s + q0 + r);
-            tt.row_ts[r] = __ldg(p.tau_s + q0 + r);
-            tt.row_b16[r] = (uint32_t)(bo >> 7);
-            tt.row_nb[r] = (uint8_t)nb;
-            if (planned) { tt.row_e0[r] = __ldg(p.esc_ptr + q0 + r); tt.row_e1[r] = __ldg(p.esc_ptr + q0 + r + 1); }
-            cls = (nb >= 3 && nb <= 8 && (bo & 127) == 0) ? nb - 3 : NCLASS - 1;     // 16-byte aligned row start
-        }
-        tt.row_cls[r] = (int8_t)cls;
-    }
-    __syncthreads();
-    if (warp == 0) {
-        int cnt[NCLASS];
-#pragma unroll
-        for (int c = 0; c < NCLASS; ++c) cnt[c] = 0;
-        for (int r0 = 0; r0 < RB; r0 += 32) {
-            const int r = r0 + lane;
-            const int cls = tt.row_cls[r];
-#pragma unroll
-            for (int c = 0; c < NCLASS; ++c) {
-                const uint32_t mk = __ballot_sync(0xffffffffu, cls == c);
-                if (cls == c) tt.list[c][cnt[c] + __popc(mk & ((1u << lane) - 1u))] = (int16_t)r;
-                cnt[c] += __popc(mk);
-            }
-        }
-        __syncwarp();
-        int nt = 0, need_b = 0;
-#pragma unroll
-        for (int c = 0; c < NCLASS; ++c) {
-            if (c < 3 && cnt[c] > 0) need_b = 1;                          // widths 3, 4, 5 pair at distance 4
-            for (int i0 = 0; i0 < cnt[c]; i0 += 16) {
-                if (lane < 16) tt.tile_row[nt][lane] = (i0 + lane < cnt[c]) ? tt.list[c][i0 + lane] : (int16_t)-1;
-                if (lane == 0) {
-                    tt.tile_nb[nt] = (int8_t)(c == NCLASS - 1 ? 0 : c + 3);
-                    tt.tile_cnt[nt] = (int8_t)min(16, cnt[c] - i0);
-                }
-                ++nt;
-            }
-        }
-        if (lane == 0) { tt.ntiles = nt; tt.need_b = need_b; }
-    }
-    __syncthreads();
-    const int ntiles = tt.ntiles;
-    float *out = p.S > 1 ? p.part + (int64_t)split * p.M * p.Q : p.Y;
-
-    if (warp == PRODUCER_WARP) {
-        // ================= producer warp: lane r copies row r of every stage =================
-        int slot = 0;
-        uint32_t phase = 0;
-        bool alive = true;
-        for (int ti = 0; ti < ntiles && alive; ++ti) {
-            const int nb = tt.tile_nb[ti];
-            if (nb == 0) continue;
-            const int cnt = tt.tile_cnt[ti];
-            const int lr = lane < cnt ? tt.tile_row[ti][lane] : 0;
-            const uint8_t *src = p.ids + ((uint64_t)tt.row_b16[lr] + (uint64_t)kc0 * nb) * 16u;
-            const uint32_t dst_row = (uint32_t)(lane * stage_row_stride(nb));
-            for (int s = 0; s < NSK; ++s) {
-                const int chunks = min(NW, NC - s * NW);
-                const uint32_t bytes_row = (uint32_t)(chunks * 16 * nb);
-                const uint32_t full = smem_u32(&tt.full[slot]);
-                if (!mbar_wait(smem_u32(&tt.empty[slot]), phase ^ 1u, abort_flag, 1)) { alive = false; break; }
-                if (lane == 0) mbar_expect_tx(full, bytes_row * (uint32_t)cnt);
-                __syncwarp();
-                if (lane < cnt)
-                    bulk_g2s(smem_u32(stages + (size_t)slot * STAGE_BYTES) + dst_row, src + (size_t)s * NW * 16 * nb,
-                             bytes_row, full);
-                if (++slot == nstg) { slot = 0; phase ^= 1u; }
-            }
-        }
-    } else if (warp == ESCAPE_WARP) {
-        // ================= escape warp: per tile, lane r sums row r's corrections x * (exact - band) in stored
-        // order over the escapes that fall into this K-range, ahead of the warp that will write the tile =========
-        asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // activations are staged
-        if (planned) {
-            int staged = 0;
-            bool alive = true;
-            const int clo = kc0 * KC, chi = clo + NC * KC;
-            for (int ti = 0; ti < ntiles; ++ti) {
-                if (tt.tile_nb[ti] == 0) continue;
-                const int buf = staged & 1;
-                if (alive) alive = mbar_wait(smem_u32(&tt.corr_empty[buf]), ((staged >> 1) & 1) ^ 1u, abort_flag, 3);
-                const int lr = lane < 16 ? tt.tile_row[ti][lane] : -1;
-                if (lr >= 0 && alive) {
-                    const int e0 = tt.row_e0[lr], e1 = tt.row_e1[lr];
-                    float *dst = corr + (buf * 16 + lane) * p.M;
-                    for (int m0 = 0; m0 < p.M; m0 += 8) {
-                        float a[8];
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) a[k] = 0.f;
-                        for (int e = e0; e < e1; e += 4) {
-                            int c[4];
-                            float d[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {                   // four independent loads in flight
-                                const bool ok = e + j < e1;
-                                c[j] = ok ? __ldg(p.esc_col + e + j) : -1;
-                                d[j] = ok ? __ldg(p.esc_delta + e + j) : 0.f;
-                            }
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                if (c[j] >= clo && c[j] < chi) {
-#pragma unroll
-                                    for (int k = 0; k < 8; ++k)
-                                        if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c[j] - clo, m0 + k, MP), d[j], a[k]);
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            if (m0 + k < p.M) dst[m0 + k] = a[k];
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&tt.corr_full[buf]));
-                ++staged;
-            }
-        }
-    } else {
-        // ================= consumer warps =================
-        // ---- 2. activations of this K-range as fp16 in fragment order (after the previous kernel in the stream)
-        pdl_wait();
-        {
-            const int groups = NC * 16;                                 // 8-column groups in the range
-            const int64_t col0 = (int64_t)kc0 * KC;
-            const bool need_b = DUAL && tt.need_b != 0;
-            for (int idx = tid; idx < MP * groups; idx += NW * 32) {
-                const int m = idx / groups, u8 = idx - m * groups;     // u8: natural 8-column group number
-                uint32_t h[8];
-                if (m < p.M) {
-                    stage_x8<XT>(p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h);
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) h[k] = 0u;
-                }
-                const int sl = slot_of(u8 * 8, m, MP);
-                *reinterpret_cast<uint4 *>(xs_a + (sl << 3)) =
-                    make_uint4(h[0] | (h[2] << 16), h[1] | (h[3] << 16), h[4] | (h[6] << 16), h[5] | (h[7] << 16));
-                if (need_b)
-                    *reinterpret_cast<uint4 *>(xs_b + (sl << 3)) =
-                        make_uint4(h[0] | (h[4] << 16), h[1] | (h[5] << 16), h[2] | (h[6] << 16), h[3] | (h[7] << 16));
-            }
-            consumer_sync();
-            for (int m = warp; m < p.M; m += NW) {                      // fixed-order sums: same bits every run
-                float s = 0.f;
-                for (int c = lane; c < NC * KC; c += 32) s += xs_read(xs_a, c, m, MP);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (lane == 0) tt.sumx[m] = s;
-            }
-            asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // consumers + escape warp
-        }
-        pdl_launch_dependents();
-
-        // ---- 3. walk the tiles
-        const int g = lane >> 2, t = lane & 3;
-        const bool xvalid = NT > 1 || g < MP;                           // lanes whose token slot exists
-        const uint32_t xstep = xvalid ? (uint32_t)(4 * MP * 16) : 0u;   // bytes between consecutive 8-column groups
-        const uint32_t xchunk = 4 * xstep;                              // bytes per chunk
-        const uint32_t xoff = (uint32_t)((t * MP + g) * 16);
-        const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
-        const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
-        const uint32_t stages32 = smem_u32(stages);
-        int slot = 0, staged = 0;
-        uint32_t phase = 0;
-        bool alive = true;
-        for (int ti = 0; ti < ntiles; ++ti) {
-            const int nb = tt.tile_nb[ti];
-            const int cnt = tt.tile_cnt[ti];
-            if (nb == 0) {
-                // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
-                // start on a 16-byte boundary).  One row per warp at a time, ids byte-wise from global memory.
-                for (int rr = warp; rr < cnt; rr += NW) {
-                    const int lr = tt.tile_row[ti][rr];
-                    const int q = q0 + lr;
-                    const int rnb = tt.row_nb[lr];
-                    const int64_t base = __ldg(p.bit_off + q) + (int64_t)kc0 * KC * rnb;
-                    const float ms = tt.row_ms[lr], ts = tt.row_ts[lr];
-                    for (int m0 = 0; m0 < p.M; m0 += 8) {
-                        float a[8];
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) a[k] = 0.f;
-                        for (int c = lane; c < NC * KC; c += 32) {
-                            const float wv = band(field_bytes(p.ids, base + (int64_t)c * rnb, rnb), ts, ms);
-#pragma unroll
-                            for (int k = 0; k < 8; ++k)
-                                if (m0 + k < p.M) a[k] = __fmaf_rn(xs_read(xs_a, c, m0 + k, MP), wv, a[k]);
-                        }
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-#pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
-                            if (lane == 0 && m0 + k < p.M) out[(int64_t)(m0 + k) * p.Q + q] = a[k];
-                        }
-                    }
-                }
-                if (planned) {
-                    consumer_sync();                                    // every warp's rows of this tile are written
-                    if (warp == 0) tile_escapes(p, tt, ti, lane, q0, kc0, NC, xs_a, MP, out);
-                }
-                continue;
-            }
-            const int RS = stage_row_stride(nb);
-            const uint32_t wa_off = (uint32_t)(g * RS + warp * 16 * nb + t * 4 * nb), wb_off = wa_off + 8 * RS;
-            const uint32_t xbase = (nb >= 6 || !DUAL) ? xs_a32 : xs_b32;
-            float acc[NT][4];
-#pragma unroll
-            for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-            for (int s = 0; s < NSK; ++s) {
-                if (alive) alive = mbar_wait(smem_u32(&tt.full[slot]), phase, abort_flag, 2);
-                const int chunk = s * NW + warp;
-                if (alive && chunk < NC && !(p.debug & 1)) {
-                    const uint32_t stage = stages32 + (uint32_t)slot * STAGE_BYTES;
-                    const uint32_t xa = xbase + chunk * xchunk;
-                    switch (nb) {                                       // CTA-uniform
-                        case 7: chunk_mma<7, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                        case 6: chunk_mma<6, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                        case 8: chunk_mma<8, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                        case 5: chunk_mma<5, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                        case 4: chunk_mma<4, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                        case 3: chunk_mma<3, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                        default: break;
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&tt.empty[slot]));
-                if (++slot == nstg) { slot = 0; phase ^= 1u; }
-            }
-            // ---- the warps' partial sums, added in warp order by one warp
-            float *rbuf = red + (size_t)(staged & 1) * (NW * 4 * NT * 32);
-#pragma unroll
-            for (int n = 0; n < NT; ++n)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) rbuf[(warp * 4 * NT + n * 4 + k) * 32 + lane] = acc[n][k];
-            consumer_sync();
-            if (warp == (staged & (NW - 1))) {
-#pragma unroll
-                for (int n = 0; n < NT; ++n)
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        float v = 0.f;
-#pragma unroll
-                        for (int w = 0; w < NW; ++w) v += rbuf[(w * 4 * NT + n * 4 + k) * 32 + lane];
-                        acc[n][k] = v;
-                    }
-                const int buf = staged & 1;
-                if (planned && alive) alive = mbar_wait(smem_u32(&tt.corr_full[buf]), (staged >> 1) & 1, abort_flag, 4);
-                // y = tau_s * sum(x * id) + min_s * sum(x) (+ escape corrections); thread holds rows g, g+8 and
-                // tokens 8n+2t, 8n+2t+1
-#pragma unroll
-                for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int lr = tt.tile_row[ti][g + 8 * hrow];
-                    if (lr >= 0) {
-                        const float ms = tt.row_ms[lr], ts = tt.row_ts[lr];
-                        const int q = q0 + lr;
-                        const float *cr = corr + (buf * 16 + g + 8 * hrow) * p.M;
-#pragma unroll
-                        for (int n = 0; n < NT; ++n) {
-#pragma unroll
-                            for (int k = 0; k < 2; ++k) {
-                                const int m = 8 * n + 2 * t + k;
-                                if (m < p.M) {
-                                    float y = __fmaf_rn(ts, acc[n][2 * hrow + k], ms * tt.sumx[m]);
-                                    if (planned) y += cr[m];
-                                    out[(int64_t)m * p.Q + q] = y;
-                                }
-                            }
-                        }
-                    }
-                }
-                if (planned) {
-                    __syncwarp();                                       // every lane has read its corrections
-                    if (lane == 0) mbar_arrive(smem_u32(&tt.corr_empty[buf]));
-                }
-            }
-            ++staged;
-        }
-    }
-
-    // ---- 4. K-ranges: the last CTA of the row block adds the partial sums in range order
-    if (p.S > 1) {
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const int old = atomicAdd(p.ticket + blockIdx.x, 1);
-            tt.is_last = old == p.S - 1;
-        }
-        __syncthreads();
-        if (tt.is_last) {
-            __threadfence();
-            for (int idx = tid; idx < p.M * nrows; idx += NTHREADS) {
-                const int m = idx / nrows, r = idx - m * nrows;
-                const int64_t o = (int64_t)m * p.Q + q0 + r;
-                float s = 0.f;
-                for (int k = 0; k < p.S; ++k) s += __ldcg(p.part + (int64_t)k * p.M * p.Q + o);
-                p.Y[o] = s;
-            }
-            if (tid == 0) p.ticket[blockIdx.x] = 0;
-        }
-    }
-}
-
 // ---------------------------------------------------------------------------------------------------------------
-// escape plan
+// plan build (once per pack)
 
+__device__ __forceinline__ int row_class(int nb, int64_t bit_off) {
+    return (nb >= 3 && nb <= 8 && (bit_off & 127) == 0) ? nb - 3 : NCLASS - 1;      // fragment path needs 16-byte aligned rows
+}
+
+// Escapes regrouped by row: first escape of every row, column and (exact - band) of every escape.
 __global__ void __launch_bounds__(256) escape_plan_kernel(const uint8_t *__restrict__ ids, const float *__restrict__ min_s,
                                                           const float *__restrict__ tau_s,
                                                           const uint8_t *__restrict__ nbits,
@@ -758,11 +385,449 @@ __global__ void __launch_bounds__(256) escape_plan_kernel(const uint8_t *__restr
     }
 }
 
+
+// Rows sorted by class (stable) into tiles.  One block: the sort is a counting sort over at most seven classes.
+__global__ void __launch_bounds__(1024) plan_tiles_kernel(const uint8_t *__restrict__ nbits,
+                                                          const int64_t *__restrict__ bit_off,
+                                                          const float *__restrict__ min_s, const float *__restrict__ tau_s,
+                                                          const int *__restrict__ esc_ptr, int Q, TileDesc *__restrict__ tiles,
+                                                          int *__restrict__ header) {
+    __shared__ int cnt[NCLASS], base_tile[NCLASS], running[NCLASS];
+    __shared__ int wtot[32][NCLASS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < NCLASS) { cnt[tid] = 0; running[tid] = 0; }
+    __syncthreads();
+    {
+        int local[NCLASS];
+#pragma unroll
+        for (int c = 0; c < NCLASS; ++c) local[c] = 0;
+        for (int q = tid; q < Q; q += 1024) {
+            const int c = row_class(__ldg(nbits + q), __ldg(bit_off + q));
+#pragma unroll
+            for (int k = 0; k < NCLASS; ++k) local[k] += (c == k);
+        }
+#pragma unroll
+        for (int c = 0; c < NCLASS; ++c)
+            if (local[c]) atomicAdd(&cnt[c], local[c]);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int t = 0;
+        for (int c = 0; c < NCLASS; ++c) { base_tile[c] = t; t += (cnt[c] + 15) / 16; }
+        header[0] = t;
+    }
+    __syncthreads();
+    for (int q0 = 0; q0 < Q; q0 += 1024) {
+        const int q = q0 + tid;
+        int c = -1, nb = 0;
+        int64_t bo = 0;
+        if (q < Q) { nb = __ldg(nbits + q); bo = __ldg(bit_off + q); c = row_class(nb, bo); }
+        int before = 0;                                     // rows of my class earlier in my warp
+#pragma unroll
+        for (int k = 0; k < NCLASS; ++k) {
+            const uint32_t mk = __ballot_sync(0xffffffffu, c == k);
+            if (c == k) before = __popc(mk & ((1u << lane) - 1u));
+            if (lane == 0) wtot[warp][k] = __popc(mk);
+        }
+        __syncthreads();
+        if (c >= 0) {
+            int pos = running[c] + before;
+            for (int w = 0; w < warp; ++w) pos += wtot[w][c];
+            TileDesc &d = tiles[base_tile[c] + (pos >> 4)];
+            const int s = pos & 15;
+            d.row[s] = q;
+            d.b16[s] = (uint32_t)(bo >> 7);
+            d.ms[s] = __ldg(min_s + q);
+            d.ts[s] = __ldg(tau_s + q);
+            d.e0[s] = esc_ptr ? __ldg(esc_ptr + q) : 0;
+            d.e1[s] = esc_ptr ? __ldg(esc_ptr + q + 1) : 0;
+        }
+        __syncthreads();
+        if (tid < NCLASS) {
+            int t = 0;
+            for (int w = 0; w < 32; ++w) t += wtot[w][tid];
+            running[tid] += t;
+        }
+        __syncthreads();
+    }
+    const int ntiles = header[0];
+    for (int t = tid; t < ntiles; t += 1024) {
+        int c = 0;
+        for (int k = 0; k < NCLASS; ++k)
+            if (cnt[k] > 0 && t >= base_tile[k] && t < base_tile[k] + (cnt[k] + 15) / 16) c = k;
+        const int n = min(16, cnt[c] - 16 * (t - base_tile[c]));
+        tiles[t].nb = c == NCLASS - 1 ? 0 : c + 3;
+        tiles[t].cnt = n;
+        for (int s = n; s < 16; ++s) tiles[t].row[s] = -1;
+    }
+}
+
+struct SmallMParams {
+    const uint8_t *ids;
+    const uint8_t *nbits;      // per-element class only
+    const int64_t *bit_off;    // per-element class only
+    const TileDesc *tiles;
+    const int *ntiles_ptr;     // plan header
+    const int *esc_col;        // null: the pack has no escapes
+    const float *esc_delta;
+    const void *X;
+    float *Y;                  // (M, Q)
+    float *part;               // (S, M, Q) partial sums when S > 1
+    int *ticket;               // one counter per tile when S > 1 (zero on entry, zero on exit)
+    int Q, P, M, MP;           // MP: token slots per column group in shared memory (>= M)
+    int S;                     // K-ranges (= gridDim.y)
+    int nc_per;                // chunks per K-range (the last range may be shorter)
+    int nc_total;              // P / 128
+    int nstg;                  // slots of the copy ring
+    int debug;                 // bit 0: skip the fragment math (copy stream only; tuning experiments)
+};
+
+constexpr int SLOT_BYTES = STAGE_BYTES + DESC_SLOT;
+
+// DUAL: a second activation layout is staged for widths that pair ids at distance 4 (cheap for few tokens).
+template <int XT, int NT, bool DUAL>
+__global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small_m_kernel(const SmallMParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ Control ctl;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int split = blockIdx.y;
+    const int kc0 = split * p.nc_per;                                  // first chunk of this K-range
+    const int NC = min(p.nc_per, p.nc_total - kc0);                    // chunks in this K-range (>= 1 by construction)
+    const int NSK = (NC + NW - 1) / NW;                                // stages along K per tile
+    const int MP = p.MP, M = p.M;
+    const int nstg = p.nstg;
+    // dynamic shared memory:
+    //   [ring: nstg x (16-row stage + descriptor)] [activations A] [activations B] [warp partials x 2]
+    //   [per-element row results x 2] [16 zero bytes] [escape corrections x 2]
+    const int xs_halves = p.nc_per * 16 * MP * 8;                      // halves per activation layout
+    __half *xs_a = reinterpret_cast<__half *>(smem + (size_t)nstg * SLOT_BYTES);
+    __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
+    float *red = reinterpret_cast<float *>(xs_a + (DUAL ? 2 : 1) * xs_halves);     // [2][NW][4 * NT][32]
+    float *rowres = red + 2 * NW * 4 * NT * 32;                        // [2][16][M]
+    uint32_t *zero16 = reinterpret_cast<uint32_t *>(rowres + 2 * 16 * M);
+    float *corr = reinterpret_cast<float *>(zero16 + 4);               // [2][16][M]
+    const bool planned = p.esc_col != nullptr;
+    volatile int *abort_flag = &ctl.abort;
+
+    if (tid == 0) {
+        for (int s = 0; s < nstg; ++s) {
+            mbar_init(smem_u32(&ctl.full[s]), 1);
+            mbar_init(smem_u32(&ctl.empty[s]), NW);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&ctl.corr_full[b]), 1);
+            mbar_init(smem_u32(&ctl.corr_empty[b]), 1);
+        }
+        ctl.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (tid < 4) zero16[tid] = 0u;
+    __syncthreads();
+    const int ntiles = __ldg(p.ntiles_ptr);
+    const int tstep = gridDim.x;
+
+    if (warp == PRODUCER_WARP) {
+        // ================= producer warp: lane r copies row r of every stage; lane 16 the tile's descriptor ===========
+        int slot = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        int tile = blockIdx.x;
+        int nb = 0, cnt = 0;
+        uint32_t b16 = 0;
+        auto fetch = [&](int t) {
+            if (t < ntiles) {
+                nb = __ldg(&p.tiles[t].nb);
+                cnt = __ldg(&p.tiles[t].cnt);
+                b16 = lane < 16 ? __ldg(&p.tiles[t].b16[lane]) : 0u;
+            }
+        };
+        fetch(tile);
+        while (tile < ntiles && alive) {
+            const int cur = tile, cnb = nb, ccnt = cnt;
+            const uint8_t *src = p.ids + ((uint64_t)b16 + (uint64_t)kc0 * cnb) * 16u;
+            tile += tstep;
+            fetch(tile);                                                // next descriptor loads while this tile is issued
+            const uint32_t dst_row = (uint32_t)(lane * stage_row_stride(cnb ? cnb : 8));
+            const int nstages = cnb ? NSK : 1;
+            for (int s = 0; s < nstages; ++s) {
+                const int chunks = min(NW, NC - s * NW);
+                const uint32_t bytes_row = cnb ? (uint32_t)(chunks * 16 * cnb) : 0u;
+                const uint32_t full = smem_u32(&ctl.full[slot]);
+                if (!mbar_wait(smem_u32(&ctl.empty[slot]), phase ^ 1u, abort_flag, 1)) { alive = false; break; }
+                if (lane == 0) mbar_expect_tx(full, bytes_row * (uint32_t)ccnt + (s == 0 ? (uint32_t)DESC_BYTES : 0u));
+                __syncwarp();
+                const uint32_t slot32 = smem_u32(smem + (size_t)slot * SLOT_BYTES);
+                if (cnb && lane < ccnt) bulk_g2s(slot32 + dst_row, src + (size_t)s * NW * 16 * cnb, bytes_row, full);
+                if (s == 0 && lane == 16) bulk_g2s(slot32 + STAGE_BYTES, p.tiles + cur, DESC_BYTES, full);
+                if (++slot == nstg) { slot = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == ESCAPE_WARP) {
+        // ================= escape warp: per tile, lane r sums row r's corrections x * (exact - band) in stored
+        // order over the escapes that fall into this K-range, ahead of the warp that will write the tile =========
+        asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // activations are staged
+        if (planned) {
+            int count = 0;
+            bool alive = true;
+            const int clo = kc0 * KC, chi = clo + NC * KC;
+            int row = -1, e0 = 0, e1 = 0;
+            auto fetch = [&](int t) {
+                if (t < ntiles && lane < 16) {
+                    row = __ldg(&p.tiles[t].row[lane]);
+                    e0 = __ldg(&p.tiles[t].e0[lane]);
+                    e1 = __ldg(&p.tiles[t].e1[lane]);
+                }
+            };
+            int tile = blockIdx.x;
+            fetch(tile);
+            while (tile < ntiles) {
+                const int crow = lane < 16 ? row : -1, ce0 = e0, ce1 = e1;
+                tile += tstep;
+                fetch(tile);
+                const int buf = count & 1;
+                if (alive) alive = mbar_wait(smem_u32(&ctl.corr_empty[buf]), ((count >> 1) & 1) ^ 1u, abort_flag, 3);
+                if (crow >= 0 && alive) {
+                    float *dst = corr + (buf * 16 + lane) * M;
+                    for (int m0 = 0; m0 < M; m0 += 8) {
+                        float a[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) a[k] = 0.f;
+                        for (int e = ce0; e < ce1; e += 4) {
+                            int c[4];
+                            float d[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {                   // four independent loads in flight
+                                const bool ok = e + j < ce1;
+                                c[j] = ok ? __ldg(p.esc_col + e + j) : -1;
+                                d[j] = ok ? __ldg(p.esc_delta + e + j) : 0.f;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (c[j] >= clo && c[j] < chi) {
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k)
+                                        if (m0 + k < M) a[k] = __fmaf_rn(xs_read(xs_a, c[j] - clo, m0 + k, MP), d[j], a[k]);
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            if (m0 + k < M) dst[m0 + k] = a[k];
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl.corr_full[buf]));
+                ++count;
+            }
+        }
+    } else {
+        // ================= consumer warps =================
+        // ---- activations of this K-range as fp16 in fragment order (after the previous kernel in the stream)
+        pdl_wait();
+        {
+            const int groups = NC * 16;                                 // 8-column groups in the range
+            const int64_t col0 = (int64_t)kc0 * KC;
+            for (int idx = tid; idx < MP * groups; idx += NW * 32) {
+                const int m = idx / groups, u8 = idx - m * groups;     // u8: natural 8-column group number
+                uint32_t h[8];
+                if (m < M) {
+                    stage_x8<XT>(p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) h[k] = 0u;
+                }
+                const int sl = slot_of(u8 * 8, m, MP);
+                *reinterpret_cast<uint4 *>(xs_a + (sl << 3)) =
+                    make_uint4(h[0] | (h[2] << 16), h[1] | (h[3] << 16), h[4] | (h[6] << 16), h[5] | (h[7] << 16));
+                if (DUAL)
+                    *reinterpret_cast<uint4 *>(xs_b + (sl << 3)) =
+                        make_uint4(h[0] | (h[4] << 16), h[1] | (h[5] << 16), h[2] | (h[6] << 16), h[3] | (h[7] << 16));
+            }
+            consumer_sync();
+            for (int m = warp; m < M; m += NW) {                        // fixed-order sums: same bits every run
+                float s = 0.f;
+                for (int c = lane; c < NC * KC; c += 32) s += xs_read(xs_a, c, m, MP);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane == 0) ctl.sumx[m] = s;
+            }
+            asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // consumers + escape warp
+        }
+        pdl_launch_dependents();
+
+        // ---- walk the tiles
+        const int g = lane >> 2, t = lane & 3;
+        const bool xvalid = NT > 1 || g < MP;                           // lanes whose token slot exists
+        const uint32_t xstep = xvalid ? (uint32_t)(4 * MP * 16) : 0u;   // bytes between consecutive 8-column groups
+        const uint32_t xchunk = 4 * xstep;                              // bytes per chunk
+        const uint32_t xoff = (uint32_t)((t * MP + g) * 16);
+        const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
+        const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
+        const uint32_t ring32 = smem_u32(smem);
+        float *out = p.S > 1 ? p.part + (int64_t)split * M * p.Q : p.Y;
+        int slot = 0, count = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < ntiles; tile += tstep, ++count) {
+            // the tile's first stage carries its descriptor
+            if (alive) alive = mbar_wait(smem_u32(&ctl.full[slot]), phase, abort_flag, 2);
+            const TileDesc *d = reinterpret_cast<const TileDesc *>(smem + (size_t)slot * SLOT_BYTES + STAGE_BYTES);
+            const int nb = alive ? d->nb : 0, cnt = alive ? d->cnt : 0;
+            int myrow[2];
+            float myms[2], myts[2];
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                myrow[hrow] = alive ? d->row[g + 8 * hrow] : -1;
+                myms[hrow] = d->ms[g + 8 * hrow];
+                myts[hrow] = d->ts[g + 8 * hrow];
+            }
+            const int buf = count & 1;
+            float acc[NT][4];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+            if (nb == 0) {
+                // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
+                // start on a 16-byte boundary).  One row per warp at a time, ids byte-wise from global memory; the
+                // stage holds only the descriptor.
+                float *rr_out = rowres + buf * 16 * M;
+                for (int rr = warp; rr < cnt; rr += NW) {
+                    const int q = d->row[rr];
+                    const float ms = d->ms[rr], ts = d->ts[rr];
+                    const int rnb = __ldg(p.nbits + q);
+                    const int64_t base = __ldg(p.bit_off + q) + (int64_t)kc0 * KC * rnb;
+                    for (int m0 = 0; m0 < M; m0 += 8) {
+                        float a[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) a[k] = 0.f;
+                        for (int c = lane; c < NC * KC; c += 32) {
+                            const float wv = band(field_bytes(p.ids, base + (int64_t)c * rnb, rnb), ts, ms);
+#pragma unroll
+                            for (int k = 0; k < 8; ++k)
+                                if (m0 + k < M) a[k] = __fmaf_rn(xs_read(xs_a, c, m0 + k, MP), wv, a[k]);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
+                            if (lane == 0 && m0 + k < M) rr_out[rr * M + m0 + k] = a[k];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl.empty[slot]));
+                if (++slot == nstg) { slot = 0; phase ^= 1u; }
+            } else {
+                const int RS = stage_row_stride(nb);
+                const uint32_t wa_off = (uint32_t)(g * RS + warp * 16 * nb + t * 4 * nb), wb_off = wa_off + 8 * RS;
+                const uint32_t xbase = (nb >= 6 || !DUAL) ? xs_a32 : xs_b32;
+                for (int s = 0; s < NSK; ++s) {
+                    if (s > 0 && alive) alive = mbar_wait(smem_u32(&ctl.full[slot]), phase, abort_flag, 2);
+                    const int chunk = s * NW + warp;
+                    if (alive && chunk < NC && !(p.debug & 1)) {
+                        const uint32_t stage = ring32 + (uint32_t)slot * SLOT_BYTES;
+                        const uint32_t xa = xbase + chunk * xchunk;
+                        switch (nb) {                                   // CTA-uniform
+                            case 7: chunk_mma<7, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                            case 6: chunk_mma<6, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                            case 8: chunk_mma<8, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                            case 5: chunk_mma<5, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                            case 4: chunk_mma<4, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                            case 3: chunk_mma<3, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
+                            default: break;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl.empty[slot]));
+                    if (++slot == nstg) { slot = 0; phase ^= 1u; }
+                }
+                float *rbuf = red + (size_t)buf * (NW * 4 * NT * 32);
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) rbuf[(warp * 4 * NT + n * 4 + k) * 32 + lane] = acc[n][k];
+            }
+            consumer_sync();
+            if (warp != (count & (NW - 1))) continue;
+            // ---- one warp finishes the tile: warps' partial sums in warp order, scale, corrections, K-ranges
+            if (nb != 0) {
+                const float *rbuf = red + (size_t)buf * (NW * 4 * NT * 32);
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float v = 0.f;
+#pragma unroll
+                        for (int w = 0; w < NW; ++w) v += rbuf[(w * 4 * NT + n * 4 + k) * 32 + lane];
+                        acc[n][k] = v;
+                    }
+            }
+            if (planned && alive) alive = mbar_wait(smem_u32(&ctl.corr_full[buf]), (count >> 1) & 1, abort_flag, 4);
+            // thread holds rows g, g+8 of the tile and tokens 8n+2t, 8n+2t+1
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int q = myrow[hrow];
+                if (q < 0) continue;
+                const float *cr = corr + (buf * 16 + g + 8 * hrow) * M;
+                const float *rr = rowres + (buf * 16 + g + 8 * hrow) * M;
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int m = 8 * n + 2 * t + k;
+                        if (m < M) {
+                            // y = tau_s * sum(x * id) + min_s * sum(x)   (per-element rows are already complete)
+                            float y = nb != 0 ? __fmaf_rn(myts[hrow], acc[n][2 * hrow + k], myms[hrow] * ctl.sumx[m]) : rr[m];
+                            if (planned) y += cr[m];
+                            out[(int64_t)m * p.Q + q] = y;
+                        }
+                    }
+                }
+            }
+            if (planned) {
+                __syncwarp();                                           // every lane has read its corrections
+                if (lane == 0) mbar_arrive(smem_u32(&ctl.corr_empty[buf]));
+            }
+            if (p.S > 1) {
+                // K-ranges: whichever CTA finishes this tile last adds the partial sums in range order
+                __syncwarp();
+                __threadfence();
+                int last = 0;
+                if (lane == 0) last = atomicAdd(p.ticket + tile, 1) == p.S - 1;
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; ++hrow) {
+                        const int q = myrow[hrow];
+                        if (q < 0) continue;
+#pragma unroll
+                        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const int m = 8 * n + 2 * t + k;
+                                if (m < M) {
+                                    const int64_t o = (int64_t)m * p.Q + q;
+                                    float s = 0.f;
+                                    for (int r = 0; r < p.S; ++r) s += __ldcg(p.part + (int64_t)r * M * p.Q + o);
+                                    p.Y[o] = s;
+                                }
+                            }
+                        }
+                    }
+                    if (lane == 0) p.ticket[tile] = 0;
+                }
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // host side
 
 struct Plan {
-    int rb, nblk, S, nc_per, nc_total, MP, NT, nstg;
+    int ctas_x, S, nc_per, nc_total, MP, NT, nstg;
+    bool dual;
     size_t smem_bytes;
     int64_t part_bytes, ticket_bytes;
 };
@@ -779,50 +844,52 @@ static int device_sms() {
 }
 
 // tuning hooks (qvb8_small_m_set_tuning): 0 = choose automatically
-static int g_force_rb = 0, g_fill_x = 0, g_force_nstg = 0, g_debug = 0;
+static int g_fill_pct = 0, g_force_s = 0, g_force_nstg = 0, g_debug = 0;
 
 static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     Plan pl{};
     pl.nc_total = (int)(P / KC);
     pl.NT = (int)((M + 7) / 8);
     pl.MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * pl.NT;
-    const int sms = device_sms();
-    const int layouts = pl.MP <= 4 ? 2 : 1;
+    pl.dual = pl.MP <= 4;
+    const int layouts = pl.dual ? 2 : 1;
+    const int per_sm = pl.NT == 1 ? 4 : pl.NT == 2 ? 2 : 1;             // resident CTAs per SM the kernel is built for
     // K-range length: bounded by the shared memory the staged activations may take
     const int xs_budget = pl.MP <= 4 ? 8 * 1024 : pl.NT == 1 ? 16 * 1024 : pl.NT == 2 ? 32 * 1024 : 96 * 1024;
     int nc_max = xs_budget / (KC * pl.MP * 2 * layouts);
     if (nc_max >= NW) nc_max = nc_max / NW * NW;                        // whole stages
     if (nc_max < 1) nc_max = 1;
     const int s_xs = (pl.nc_total + nc_max - 1) / nc_max;
-    // rows per CTA and K split: enough CTAs to fill the GPU g_fill_x times over where the shape allows it, each
-    // K-range at least one full stage
+    // CTAs: one resident wave (persistent CTAs walk the tiles); few tiles -> split K further, down to one stage
+    const int max_tiles = (int)((Q + 15) / 16 + NCLASS - 1);
+    int64_t slots = (int64_t)per_sm * device_sms() * (g_fill_pct ? g_fill_pct : 100) / 100;
+    if (slots < 1) slots = 1;
     const int s_cap = pl.nc_total / NW > 0 ? pl.nc_total / NW : 1;
-    const int target = (g_fill_x ? g_fill_x : (pl.NT == 1 ? 4 : pl.NT == 2 ? 2 : 1)) * sms;   // default: one full wave
-    int rb = g_force_rb ? g_force_rb : RB_MAX;
     int S = s_xs;
-    for (;;) {
-        const int nblk = (int)((Q + rb - 1) / rb);
-        int want = (target + nblk - 1) / nblk;
-        if (want > s_cap) want = s_cap;
-        S = s_xs > want ? s_xs : want;
-        if (g_force_rb || rb <= 16 || (int64_t)nblk * S >= target) break;
-        rb /= 2;
+    if ((int64_t)max_tiles * S < slots) {
+        S = (int)((slots + max_tiles - 1) / max_tiles);
+        if (S > s_cap) S = s_cap;
+        if (S < s_xs) S = s_xs;
     }
-    pl.rb = rb;
-    pl.nblk = (int)((Q + rb - 1) / rb);
-    if (pl.nblk > MAX_TICKET_BLOCKS) S = s_xs;                          // more row blocks than counters
+    if (g_force_s) S = g_force_s > s_xs ? g_force_s : s_xs;
+    if (S > pl.nc_total) S = pl.nc_total;
+    if (max_tiles > MAX_TICKET_TILES) S = s_xs;                         // more tiles than counters: no extra split
     pl.nc_per = (pl.nc_total + S - 1) / S;
     if (pl.nc_per > NW) pl.nc_per = (pl.nc_per + NW - 1) / NW * NW;     // K-ranges of whole stages
     if (pl.nc_per > nc_max) pl.nc_per = nc_max;
     pl.S = (pl.nc_total + pl.nc_per - 1) / pl.nc_per;                   // no empty range
+    int64_t cx = slots / pl.S;
+    if (cx < 1) cx = 1;
+    if (cx > max_tiles) cx = max_tiles;
+    pl.ctas_x = (int)cx;
     const size_t xs_bytes = (size_t)pl.nc_per * KC * pl.MP * 2 * layouts;
-    const size_t red_bytes = (size_t)2 * NW * 4 * pl.NT * 32 * 4 + (size_t)2 * 16 * M * 4;   // + escape corrections
-    const size_t per_cta = (size_t)(pl.NT == 1 ? 51 : pl.NT == 2 ? 106 : 216) * 1024;        // 4 / 2 / 1 CTAs per SM
-    int nstg = g_force_nstg ? g_force_nstg : (int)((per_cta - xs_bytes - red_bytes - 64) / STAGE_BYTES);
+    const size_t red_bytes = (size_t)2 * NW * 4 * pl.NT * 32 * 4 + (size_t)4 * 16 * M * 4;   // partials, row results, corrections
+    const size_t per_cta = (size_t)(pl.NT == 1 ? 51 : pl.NT == 2 ? 106 : 216) * 1024;
+    int nstg = g_force_nstg ? g_force_nstg : (int)((per_cta - xs_bytes - red_bytes - 64) / SLOT_BYTES);
     if (nstg > MAX_STAGES) nstg = MAX_STAGES;
     if (nstg < 2) nstg = 2;
     pl.nstg = nstg;
-    pl.smem_bytes = (size_t)nstg * STAGE_BYTES + xs_bytes + red_bytes + 64;
+    pl.smem_bytes = (size_t)nstg * SLOT_BYTES + xs_bytes + red_bytes + 64;
     pl.part_bytes = pl.S > 1 ? (int64_t)pl.S * M * Q * 4 : 0;
     pl.part_bytes = (pl.part_bytes + 255) / 256 * 256;
     pl.ticket_bytes = pl.S > 1 ? TICKET_BYTES : 0;
@@ -845,7 +912,7 @@ static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, 
         granted_dev = dev;
     }
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(pl.nblk, pl.S);
+    cfg.gridDim = dim3(pl.ctas_x, pl.S);
     cfg.blockDim = dim3(NTHREADS);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream = st;
@@ -861,7 +928,7 @@ static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, 
 template <int XT>
 static int launch_nt(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
     switch (pl.NT) {
-        case 1: return pl.MP <= 4 ? launch_one<XT, 1, true>(prm, pl, st, pdl) : launch_one<XT, 1, false>(prm, pl, st, pdl);
+        case 1: return pl.dual ? launch_one<XT, 1, true>(prm, pl, st, pdl) : launch_one<XT, 1, false>(prm, pl, st, pdl);
         case 2: return launch_one<XT, 2, false>(prm, pl, st, pdl);
         case 3: return launch_one<XT, 3, false>(prm, pl, st, pdl);
         case 4: return launch_one<XT, 4, false>(prm, pl, st, pdl);
@@ -872,9 +939,9 @@ static int launch_nt(const SmallMParams &prm, const Plan &pl, cudaStream_t st, b
 
 }  // namespace qv
 
-QV_API void qvb8_small_m_set_tuning(int rb, int fill, int nstg, int debug) {
-    qv::g_force_rb = (rb == 16 || rb == 32 || rb == 48 || rb == 64) ? rb : 0;
-    qv::g_fill_x = fill > 0 ? fill : 0;
+QV_API void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int debug) {
+    qv::g_fill_pct = fill_pct > 0 ? fill_pct : 0;
+    qv::g_force_s = force_s > 0 ? force_s : 0;
     qv::g_force_nstg = (nstg >= 2 && nstg <= qv::MAX_STAGES) ? nstg : 0;
     qv::g_debug = debug;
 }
@@ -894,39 +961,50 @@ QV_API int64_t qvb8_small_m_scratch_bytes(int64_t M, int64_t Q, int64_t P) {
     return pl.part_bytes + pl.ticket_bytes;
 }
 
-QV_API int64_t qvb8_escape_plan_bytes(int64_t Q, int64_t n_esc) {
+QV_API int64_t qvb8_plan_bytes(int64_t Q, int64_t n_esc) {
     if (Q < 0 || n_esc < 0) return 0;
-    const int64_t ptr = ((Q + 1) * 4 + 255) / 256 * 256, col = (n_esc * 4 + 255) / 256 * 256;
-    return ptr + 2 * col;
+    return qv::plan_layout(Q, n_esc).total;
 }
 
-QV_API int qvb8_escape_plan(const qvb8_pack *w, void *plan, int64_t plan_bytes, void *stream) {
+QV_API int qvb8_plan_build(const qvb8_pack *w, void *plan, int64_t plan_bytes, void *stream) {
     using namespace qv;
-    if (int rc = check_pack(w, "qvb8_escape_plan")) return rc;
-    if (int rc = check_device("qvb8_escape_plan")) return rc;
-    if (w->n_esc > 0x7fffffff) return fail(QVB8_ERR_ARG, "qvb8_escape_plan: more than 2^31 escapes");
-    if (!plan || plan_bytes < qvb8_escape_plan_bytes(w->Q, w->n_esc) || !aligned(plan, 16))
-        return fail(QVB8_ERR_SCRATCH, "qvb8_escape_plan: plan buffer missing, unaligned or smaller than %lld bytes",
-                    (long long)qvb8_escape_plan_bytes(w->Q, w->n_esc));
-    const int64_t ptr_b = ((w->Q + 1) * 4 + 255) / 256 * 256, col_b = (w->n_esc * 4 + 255) / 256 * 256;
-    int *esc_ptr = reinterpret_cast<int *>(plan);
-    int *esc_col = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(plan) + ptr_b);
-    float *esc_delta = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(plan) + ptr_b + col_b);
-    const int64_t n = w->n_esc > 0 ? w->n_esc : 1;
-    escape_plan_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        w->ids, w->min_s, w->tau_s, w->nbits, w->bit_off, w->esc_idx, w->esc_vals, w->n_esc, (int)w->Q, (int)w->P, esc_ptr,
-        esc_col, esc_delta);
-    return cuda_status("qvb8_escape_plan launch");
+    if (int rc = check_pack(w, "qvb8_plan_build")) return rc;
+    if (int rc = check_device("qvb8_plan_build")) return rc;
+    if (w->n_esc > 0x7fffffff) return fail(QVB8_ERR_ARG, "qvb8_plan_build: more than 2^31 escapes");
+    const PlanLayout L = plan_layout(w->Q, w->n_esc);
+    if (!plan || plan_bytes < L.total || !aligned(plan, 16))
+        return fail(QVB8_ERR_SCRATCH, "qvb8_plan_build: plan buffer missing, unaligned or smaller than %lld bytes",
+                    (long long)L.total);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    uint8_t *base = reinterpret_cast<uint8_t *>(plan);
+    int *esc_ptr = reinterpret_cast<int *>(base + L.esc_ptr);
+    if (cudaMemsetAsync(base, 0, 256, st) != cudaSuccess ||
+        cudaMemsetAsync(base + L.tiles, 0, (size_t)(L.total - L.tiles), st) != cudaSuccess)
+        return cuda_status("qvb8_plan_build memset");
+    if (w->n_esc > 0) {
+        escape_plan_kernel<<<(unsigned)((w->n_esc + 255) / 256), 256, 0, st>>>(
+            w->ids, w->min_s, w->tau_s, w->nbits, w->bit_off, w->esc_idx, w->esc_vals, w->n_esc, (int)w->Q, (int)w->P,
+            esc_ptr, reinterpret_cast<int *>(base + L.esc_col), reinterpret_cast<float *>(base + L.esc_delta));
+        if (int rc = cuda_status("qvb8_plan_build escapes")) return rc;
+    }
+    if (w->Q > 0) {
+        plan_tiles_kernel<<<1, 1024, 0, st>>>(w->nbits, w->bit_off, w->min_s, w->tau_s, w->n_esc > 0 ? esc_ptr : nullptr,
+                                              (int)w->Q, reinterpret_cast<TileDesc *>(base + L.tiles),
+                                              reinterpret_cast<int *>(base));
+        if (int rc = cuda_status("qvb8_plan_build tiles")) return rc;
+    }
+    return QVB8_OK;
 }
 
-QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *esc_plan, const void *X, int x_dtype, int x_mode, int64_t M,
+QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int x_mode, int64_t M,
                            float *Y, void *scratch, int64_t scratch_bytes, int flags, void *stream) {
     using namespace qv;
     if (int rc = check_small_m_args(w, X, x_dtype, x_mode, M, Y, "qvb8_small_m")) return rc;
     if (w->Q == 0) return QVB8_OK;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (x_mode != 0 || !fast_layout_ok(w, X))
+    if (plan == nullptr || x_mode != 0 || !fast_layout_ok(w, X))
         return launch_small_m_generic(w, X, x_dtype, x_mode, (int)M, Y, st);
+    if (!aligned(plan, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: the plan must be 16-byte aligned");
     const Plan pl = make_plan(M, w->Q, w->P);
     if (pl.part_bytes + pl.ticket_bytes > 0) {
         if (!scratch || scratch_bytes < pl.part_bytes + pl.ticket_bytes)
@@ -934,32 +1012,28 @@ QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *esc_plan, const void 
                         (long long)(pl.part_bytes + pl.ticket_bytes), (long long)scratch_bytes);
         if (!aligned(scratch, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: scratch must be 16-byte aligned");
     }
-    if (pl.S > 1 && pl.nblk > MAX_TICKET_BLOCKS)
-        return fail(QVB8_ERR_ARG, "qvb8_small_m: %d row blocks with a split K-range exceed the %d ticket counters",
-                    pl.nblk, MAX_TICKET_BLOCKS);
+    const PlanLayout L = plan_layout(w->Q, w->n_esc);
+    if (pl.S > 1 && L.max_tiles > MAX_TICKET_TILES)
+        return fail(QVB8_ERR_ARG, "qvb8_small_m: %d tiles with a split K-range exceed the %d ticket counters", L.max_tiles,
+                    MAX_TICKET_TILES);
+    const uint8_t *base = reinterpret_cast<const uint8_t *>(plan);
     SmallMParams prm{};
-    prm.ids = w->ids; prm.min_s = w->min_s; prm.tau_s = w->tau_s; prm.nbits = w->nbits; prm.bit_off = w->bit_off;
+    prm.ids = w->ids; prm.nbits = w->nbits; prm.bit_off = w->bit_off;
+    prm.tiles = reinterpret_cast<const TileDesc *>(base + L.tiles);
+    prm.ntiles_ptr = reinterpret_cast<const int *>(base);
+    if (w->n_esc > 0) {
+        prm.esc_col = reinterpret_cast<const int *>(base + L.esc_col);
+        prm.esc_delta = reinterpret_cast<const float *>(base + L.esc_delta);
+    }
     prm.X = X; prm.Y = Y;
     prm.ticket = reinterpret_cast<int *>(scratch);
     prm.part = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + TICKET_BYTES);
-    const bool planned = esc_plan != nullptr && w->n_esc > 0;
-    if (planned) {
-        if (!aligned(esc_plan, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: escape plan must be 16-byte aligned");
-        const int64_t ptr_b = ((w->Q + 1) * 4 + 255) / 256 * 256, col_b = (w->n_esc * 4 + 255) / 256 * 256;
-        prm.esc_ptr = reinterpret_cast<const int *>(esc_plan);
-        prm.esc_col = reinterpret_cast<const int *>(reinterpret_cast<const uint8_t *>(esc_plan) + ptr_b);
-        prm.esc_delta = reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(esc_plan) + ptr_b + col_b);
-    }
-    prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.rb = pl.rb; prm.S = pl.S;
+    prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.S = pl.S;
     prm.nc_per = pl.nc_per; prm.nc_total = pl.nc_total; prm.nstg = pl.nstg; prm.debug = g_debug;
     const bool pdl = (flags & QVB8_FLAG_PDL) != 0;
-    int rc;
-    if (x_dtype == QVB8_F16) rc = launch_nt<QVB8_F16>(prm, pl, st, pdl);
-    else if (x_dtype == QVB8_BF16) rc = launch_nt<QVB8_BF16>(prm, pl, st, pdl);
-    else rc = launch_nt<QVB8_F32>(prm, pl, st, pdl);
-    if (rc) return rc;
-    if (planned || w->n_esc == 0) return QVB8_OK;
-    return launch_fix_escapes(w, X, x_dtype, x_mode, (int)M, Y, st);
+    if (x_dtype == QVB8_F16) return launch_nt<QVB8_F16>(prm, pl, st, pdl);
+    if (x_dtype == QVB8_BF16) return launch_nt<QVB8_BF16>(prm, pl, st, pdl);
+    return launch_nt<QVB8_F32>(prm, pl, st, pdl);
 }
 
 QV_API int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,

@@ -25,6 +25,20 @@ def _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
     return _lib.pack_struct(ids, min_s, tau_s, row_nbits, row_bit_off, int(P), esc_idx, esc_vals)
 
 
+def _small_m(ids, pk, keep, X, x_mode=0):
+    """The streaming kernel needs the pack's plan (row ordering + regrouped escapes).  The reference keeps such
+    per-weight metadata on the module (formats/qvb8/module.py:267-276); this extension object has no module to hold
+    it, so it is cached on the `ids` tensor object the module owns, built on first use."""
+    if int(pk.P) % 128 == 0 and ids.data_ptr() % 16 == 0 and not torch.cuda.is_current_stream_capturing():
+        return _lib.small_m(pk, keep, X, x_mode=x_mode, plan=_lib.plan_on(ids, pk, keep))
+    plans = getattr(ids, "_qvb8_plans", None)
+    if plans:                                             # capturing: use a plan only if one already exists
+        key = (pk.ids, pk.Q, pk.P, pk.n_esc, pk.esc_idx, pk.min_s, pk.bit_off)
+        if key in plans:
+            return _lib.small_m(pk, keep, X, x_mode=x_mode, plan=plans[key])
+    return _lib.small_m(pk, keep, X, x_mode=x_mode)
+
+
 def _as_2d(X: torch.Tensor, P: int) -> torch.Tensor:
     if X.dim() == 1:
         X = X.reshape(1, -1)
@@ -70,7 +84,7 @@ class Qvb8Ext:
         if X.numel() != P:
             raise RuntimeError("X length must equal P")
         pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
-        return _lib.small_m(pk, keep, X.reshape(1, -1))
+        return _small_m(ids, pk, keep, X.reshape(1, -1))
 
     def gemv_multi(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
         """M = 1..8 -> (M, Q) fp32 (qvb8_cuda.cu:1059-1166)."""
@@ -78,11 +92,11 @@ class Qvb8Ext:
         if not 1 <= X.shape[0] <= 8:
             raise RuntimeError(f"qvb8 GEMV-multi: M={X.shape[0]} is outside the range 1..8")
         pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
-        return _lib.small_m(pk, keep, X)
+        return _small_m(ids, pk, keep, X)
 
     def gemv_rb(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals, perm, tile_nb):
         """The reference's register-blocked sm_70 variant (qvb8_cuda.cu:1350-1413); same result as gemv_multi.
-        perm / tile_nb are accepted and not needed: the kernel orders rows by width itself."""
+        perm / tile_nb are accepted and not needed: the pack's plan holds this library's own row ordering."""
         return self.gemv_multi(X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
 
     def mma_multi(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals, perm, tile_nb,
@@ -90,7 +104,7 @@ class Qvb8Ext:
         """QVB8 tensor-core multi-row product (M<=48) -> (M, Q) fp32; accepts the bf16 mode flag.
 
         (qvb8_cuda.cu:2566-2671.)  perm, tile_nb, esc_starts and general describe a row ordering the reference
-        computes per module; this kernel sorts rows by width on the fly, so they are validated and unused.
+        computes per module; this library keeps its own ordering in the pack's plan, so they are validated and unused.
         bf16=True keeps X's range (no fp16 clamp)."""
         X = _as_2d(X, int(P))
         M = X.shape[0]
@@ -102,7 +116,7 @@ class Qvb8Ext:
         if perm is not None and perm.numel() not in (0, Q):
             raise RuntimeError("qvb8 mma-multi: perm must be an int32 CUDA tensor of length Q (or empty)")
         pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
-        return _lib.small_m(pk, keep, X, x_mode=1 if bf16 else 0)
+        return _small_m(ids, pk, keep, X, x_mode=1 if bf16 else 0)
 
     # ---- any M --------------------------------------------------------------------------------------------
     def _forward(self, X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals, out_half: bool):
@@ -110,7 +124,7 @@ class Qvb8Ext:
         M = X.shape[0]
         pk, keep = _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals)
         if M <= _SMALL_M_MAX:
-            y = _lib.small_m(pk, keep, X)
+            y = _small_m(ids, pk, keep, X)
             return y.to(torch.float16) if (out_half and M > 8) else y
         # prefill: restore once to fp16, then one tensor-core GEMM with fp32 accumulation (qvb8_cuda.cu:1542-1671)
         W = _lib.decode(pk, keep, torch.float16)

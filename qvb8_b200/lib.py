@@ -22,7 +22,7 @@ _CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
 # every symbol include/qvb8_b200.h declares
 EXPORTS = (
     "qvb8_last_error", "qvb8_version", "qvb8_decode", "qvb8_small_m_scratch_bytes", "qvb8_small_m",
-    "qvb8_small_m_generic", "qvb8_escape_plan_bytes", "qvb8_escape_plan", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
+    "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
     "qvb8_device_status",
 )
 
@@ -61,9 +61,9 @@ def load() -> ctypes.CDLL:
             lib.qvb8_small_m_scratch_bytes.restype = i64
             lib.qvb8_small_m.argtypes = [pk, vp, ci, ci, i64, vp, vp, i64, vp]
             lib.qvb8_small_m_generic.argtypes = [pk, vp, ci, ci, i64, vp, vp]
-            lib.qvb8_escape_plan_bytes.argtypes = [i64, i64]
-            lib.qvb8_escape_plan_bytes.restype = i64
-            lib.qvb8_escape_plan.argtypes = [pk, vp, i64, vp]
+            lib.qvb8_plan_bytes.argtypes = [i64, i64]
+            lib.qvb8_plan_bytes.restype = i64
+            lib.qvb8_plan_build.argtypes = [pk, vp, i64, vp]
             lib.qvb8_small_m_ex.argtypes = [pk, vp, vp, ci, ci, i64, vp, vp, i64, ci, vp]
             lib.qvb8_small_m_set_tuning.argtypes = [ci, ci, ci, ci]
             lib.qvb8_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
@@ -172,22 +172,36 @@ def device_status(device=None) -> int:
     return int(v.value)
 
 
-def escape_plan(pack, keep) -> torch.Tensor | None:
-    """Device buffer holding the pack's escapes regrouped by row with precomputed differences (None if no escapes)."""
-    if pack.n_esc == 0:
-        return None
+def build_plan(pack, keep) -> torch.Tensor:
+    """Device buffer with the pack's plan (rows sorted by width into tile descriptors + escapes regrouped by row)."""
     dev = keep[0].device
     lib = load()
-    nbytes = int(lib.qvb8_escape_plan_bytes(pack.Q, pack.n_esc))
+    nbytes = int(lib.qvb8_plan_bytes(pack.Q, pack.n_esc))
     buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
-        check(lib.qvb8_escape_plan(ctypes.byref(pack), buf.data_ptr(), nbytes, stream_ptr(dev)), "qvb8_escape_plan")
+        check(lib.qvb8_plan_build(ctypes.byref(pack), buf.data_ptr(), nbytes, stream_ptr(dev)), "qvb8_plan_build")
     return buf
+
+
+def plan_on(ids: torch.Tensor, pack, keep) -> torch.Tensor:
+    """The plan of a pack, cached on the `ids` tensor OBJECT (so it lives and dies with the weight and can never be
+    matched to another weight that later reuses the address); rebuilt if the pack's geometry or escape table differ."""
+    key = (pack.ids, pack.Q, pack.P, pack.n_esc, pack.esc_idx, pack.min_s, pack.bit_off)
+    cache = ids.__dict__.setdefault("_qvb8_plans", {}) if hasattr(ids, "__dict__") else None
+    if cache is None:
+        return build_plan(pack, keep)
+    plan = cache.get(key)
+    if plan is None:
+        if len(cache) > 8:
+            cache.clear()
+        plan = cache[key] = build_plan(pack, keep)
+    return plan
 
 
 def small_m(pack, keep, X: torch.Tensor, x_mode: int = 0, generic: bool = False, out: torch.Tensor | None = None,
             plan: torch.Tensor | None = None, flags: int = 0):
-    """(M, Q) fp32 = X (M, P) @ W^T through the fused kernel (M <= 48)."""
+    """(M, Q) fp32 = X (M, P) @ W^T through the fused kernel (M <= 48).  `plan` from build_plan / plan_on selects the
+    streaming kernel; without it the layout-agnostic kernel runs."""
     dev = keep[0].device
     if not X.is_cuda or X.device != dev:
         raise RuntimeError("qvb8_b200: X must be a CUDA tensor on the pack's device")

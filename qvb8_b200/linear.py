@@ -145,19 +145,27 @@ class QVBandLinearV8(nn.Module):
         hit = cache.get(key)
         if hit is None:
             ei, ev = (self.esc_idx_bf16, self.esc_vals_bf16) if table == "bf16" else (self.esc_idx, self.esc_vals)
-            hit = cache[key] = _lib.pack_struct(self.ids, self.min_s, self.tau_s, self.nbits, self.bit_off,
-                                                self.in_features, ei, ev)
+            st, keep = _lib.pack_struct(self.ids, self.min_s, self.tau_s, self.nbits, self.bit_off, self.in_features,
+                                        ei, ev)
+            plan = None
+            if self.ids.is_cuda and self.in_features % 128 == 0 and self.ids.data_ptr() % 16 == 0 \
+                    and not torch.cuda.is_current_stream_capturing():
+                plan = _lib.build_plan(st, keep)       # once per weight (and escape table), like the reference's _mma_order
+            hit = cache[key] = (st, keep, plan)
         return hit
 
     def dense(self, dtype=torch.float16) -> torch.Tensor:
         """(Q, P) restored weight rounded once to `dtype`, escapes of the matching table applied."""
         self.escapes(dtype)
-        pk, keep = self._pack("bf16" if dtype == torch.bfloat16 else "fp16")
+        pk, keep, _ = self._pack("bf16" if dtype == torch.bfloat16 else "fp16")
         return _lib.decode(pk, keep, dtype)
 
     def reserve(self, max_rows: int = SMALL_M_MAX) -> None:
         """Pre-allocate the scratch the fused kernel needs for up to `max_rows` rows (before graph capture)."""
-        for m in {1, 2, 4, 8, min(max_rows, SMALL_M_MAX)}:
+        self._pack("fp16")
+        if self.bf16_certified:
+            self._pack("bf16")
+        for m in {1, 2, 4, 8, 16, min(max_rows, SMALL_M_MAX)}:
             if m <= max_rows:
                 _lib.reserve_scratch(self.ids.device, m, self.out_features, self.in_features)
 
@@ -180,12 +188,12 @@ class QVBandLinearV8(nn.Module):
             x2 = x2.float()
         bf16_mode = bool(self.bf16_certified) and x2.dtype == torch.bfloat16
         if M <= SMALL_M_SPLIT_MAX:
-            pk, keep = self._pack("bf16" if bf16_mode else "fp16")
+            pk, keep, plan = self._pack("bf16" if bf16_mode else "fp16")
             if M <= SMALL_M_MAX:
-                y = _lib.small_m(pk, keep, x2, x_mode=1 if bf16_mode else 0)
+                y = _lib.small_m(pk, keep, x2, x_mode=1 if bf16_mode else 0, plan=plan)
             else:
                 step = -(-M // 2)
-                y = torch.cat([_lib.small_m(pk, keep, x2[i:i + step], x_mode=1 if bf16_mode else 0)
+                y = torch.cat([_lib.small_m(pk, keep, x2[i:i + step], x_mode=1 if bf16_mode else 0, plan=plan)
                                for i in range(0, M, step)])
         elif bf16_mode and self.bf16_gemm:
             b = None if self.bias is None else self.bias.to(torch.bfloat16)

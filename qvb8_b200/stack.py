@@ -83,7 +83,7 @@ class LinearStack:
                 del W
                 st, keep = _lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx,
                                             pk.esc_vals)
-                plan = _lib.escape_plan(st, keep)
+                plan = _lib.build_plan(st, keep)
                 row.append((name, pk, st, keep + [plan], xname))
                 self.compressed_bytes += pk.weight_bytes()
                 self.n_weights += pk.Q * pk.P

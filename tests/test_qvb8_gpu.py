@@ -138,41 +138,61 @@ def test_generic_path_agrees(cuda_lib):
     assert rel_fro(a.cpu().numpy(), b.cpu().numpy()) < 1e-5
 
 
-@pytest.mark.parametrize("rb,nstg", [(16, 2), (32, 3), (48, 0), (64, 8)])
+@pytest.mark.parametrize("fill,force_s,nstg", [(100, 0, 0), (25, 1, 2), (300, 3, 3), (50, 12, 8)])
 @pytest.mark.parametrize("M", [1, 5, 16])
-def test_escape_plan_and_cta_shapes(cuda_lib, rb, nstg, M):
-    """The fused escape correction (row-grouped plan), every CTA row-block size and ring depth give the oracle's product."""
+def test_plan_kernel_configurations(cuda_lib, fill, force_s, nstg, M):
+    """The streaming kernel under different grid sizes, K splits and ring depths, with escapes, gives the oracle's
+    product; so does the layout-agnostic kernel (no plan)."""
     from qvb8_b200 import lib
     pk = random_pack(300, 1536, (4, 6, 7, 8, 11), seed=31 + M, esc_frac=0.004, device=DEV)
     X = synth.synth_activation(M, 1536, seed=M, device=DEV)
     st, keep = lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx, pk.esc_vals)
-    plan = lib.escape_plan(st, keep)
+    plan = lib.build_plan(st, keep)
     want = _oracle_y(pk, X)
     try:
-        lib.load().qvb8_small_m_set_tuning(rb, 2, nstg, 0)
+        lib.load().qvb8_small_m_set_tuning(fill, force_s, nstg, 0)
         for flags in (0, lib.FLAG_PDL):
             y = lib.small_m(st, keep, X, plan=plan, flags=flags)
             err = rel_fro(y.cpu().numpy(), want)
             assert err < TIGHT, (err, flags)
-        y_noplan = lib.small_m(st, keep, X)
-        assert rel_fro(y_noplan.cpu().numpy(), want) < TIGHT
     finally:
         lib.load().qvb8_small_m_set_tuning(0, 0, 0, 0)
+    y_noplan = lib.small_m(st, keep, X)
+    assert rel_fro(y_noplan.cpu().numpy(), want) < TIGHT
 
 
-def test_escape_plan_rows_without_escapes(cuda_lib):
-    """Rows before, between and after the escaped rows get empty ranges."""
+def test_plan_contents(cuda_lib):
+    """Tile descriptors: rows sorted by width (stable), 16 per tile, padding marked; escapes regrouped by row."""
     from qvb8_b200 import lib
-    pk = random_pack(64, 256, (7,), seed=5, device=DEV)
-    idx = torch.tensor([3 * 256 + 7, 3 * 256 + 200, 40 * 256 + 1], dtype=torch.int64, device=DEV)
+    Q, P = 100, 256
+    pk = random_pack(Q, P, (5, 7, 7, 7, 12), seed=5, device=DEV)
+    idx = torch.tensor([3 * P + 7, 3 * P + 200, 40 * P + 1], dtype=torch.int64, device=DEV)
     val = torch.tensor([0.25, -0.5, 0.125], device=DEV)
     pk.esc_idx, pk.esc_vals = idx, val
     st, keep = lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, idx, val)
-    plan = lib.escape_plan(st, keep)
-    ptr = plan[: 65 * 4].view(torch.int32).cpu().tolist()
-    assert ptr[:4] == [0, 0, 0, 0] and ptr[4] == 2 and ptr[40] == 2 and ptr[41] == 3 and ptr[64] == 3
-    X = synth.synth_activation(2, 256, seed=1, device=DEV)
-    y = lib.small_m(st, keep, X, plan=plan)
+    plan = lib.build_plan(st, keep).cpu()
+    ntiles = int(plan[:4].view(torch.int32)[0])
+    nbits = pk.nbits.cpu().numpy().astype(int)
+    cls = np.where((nbits >= 3) & (nbits <= 8), nbits - 3, 6)
+    want_tiles = sum((int((cls == c).sum()) + 15) // 16 for c in range(7))
+    assert ntiles == want_tiles
+    ptr = plan[256: 256 + (Q + 1) * 4].view(torch.int32).tolist()
+    assert ptr[:4] == [0, 0, 0, 0] and ptr[4] == 2 and ptr[40] == 2 and ptr[41] == 3 and ptr[Q] == 3
+    up = lambda v: (v + 255) // 256 * 256
+    tiles_off = 256 + up((Q + 1) * 4) + 2 * up(3 * 4)
+    seen = []
+    for t in range(ntiles):
+        d = plan[tiles_off + 400 * t: tiles_off + 400 * (t + 1)].view(torch.int32)
+        nb, cnt = int(d[0]), int(d[1])
+        rows = d[4:20].tolist()
+        assert all(r >= 0 for r in rows[:cnt]) and all(r == -1 for r in rows[cnt:])
+        assert rows[:cnt] == sorted(rows[:cnt])
+        for r in rows[:cnt]:
+            assert (nbits[r] if 3 <= nbits[r] <= 8 else 0) == nb
+        seen += rows[:cnt]
+    assert sorted(seen) == list(range(Q))
+    X = synth.synth_activation(2, P, seed=1, device=DEV)
+    y = lib.small_m(st, keep, X, plan=plan.to(DEV))
     assert rel_fro(y.cpu().numpy(), _oracle_y(pk, X)) < TIGHT
 
 
