@@ -105,8 +105,12 @@ int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, int x_d
 
 /* Tuning hook for tests and sweeps (process-wide; 0 = choose automatically): fill_pct = CTAs launched, in percent of
  * one resident wave; force_s = number of K-ranges (raised to what shared memory requires); nstg = slots of the copy
- * ring (2..8); debug bit 0 = skip the fragment math (copy stream only). */
+ * ring (2..8); debug bit 0 = skip the fragment math (copy stream only), bit 1 = record qvb8_debug_trace stamps. */
 void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int debug);
+
+/* Tuning aid: with debug bit 1 set, CTA (0, 0) of the streaming kernel stamps the device nanosecond timer at 14 points
+ * of its life into a device array; this copies the 32 slots out.  Synchronises the host. */
+int qvb8_debug_trace(unsigned long long *out32);
 
 /* Device-side error word of the current device: 0, or the code of the first bounded wait that gave up inside a
  * kernel of this library (1 = copy ring slot never freed, 2 = copy never landed, 3 / 4 = escape-correction

@@ -29,11 +29,11 @@
 // the 32 ids of rows g and g + 8 that start at column 32 t -- exactly nb 32-bit words -- and turns them into the A
 // fragments of eight m16n8k16 MMAs.  Two ids are converted per instruction: a funnel shift puts one id in the low
 // half-word and one in the high half-word of a register, `(r & mask) | 0x64006400` makes the two fp16 numbers
-// 1024 + id * 2^e, and one HFMA2 removes the 1024 and the 2^e exactly.  At the end of a tile the warps' partial
-// accumulators are added in warp order by one warp, which applies min_s / tau_s, adds the escape corrections a
-// sixth warp has summed meanwhile (per row, in stored order) and writes the result.  K-ranges of one tile are added
-// in range order by whichever CTA finishes the tile last (a ticket counter per tile).  Every sum has a fixed order:
-// results are identical from run to run.
+// 1024 + id * 2^e, and one HFMA2 removes the 1024 and the 2^e exactly.  At the end of a tile the warps hand their
+// partial accumulators to a sixth, finishing warp through shared memory and go on streaming; the finishing warp adds
+// them in warp order, applies min_s / tau_s, adds the escape corrections it has summed meanwhile (per row, in
+// stored order) and writes the result.  K-ranges of one tile are added in range order by whichever CTA finishes the
+// tile last (a ticket counter per tile).  Every sum has a fixed order: results are identical from run to run.
 //
 // Waits.  Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the waiter raises a per-CTA abort flag and a
 // device-wide error word (qvb8_device_status), every other waiter gives up too, and the kernel runs to its end with
@@ -51,7 +51,7 @@ int check_small_m_args(const qvb8_pack *w, const void *X, int x_dtype, int x_mod
 constexpr int KC = 128;                   // columns per chunk
 constexpr int NW = 4;                     // consumer warps = chunks per stage
 constexpr int PRODUCER_WARP = NW;         // issues the bulk copies
-constexpr int ESCAPE_WARP = NW + 1;       // sums the escape corrections of the tile being streamed
+constexpr int FINISHER_WARP = NW + 1;     // escape corrections, cross-warp sums, scaling, output, K-range tickets
 constexpr int NTHREADS = (NW + 2) * 32;
 constexpr int MAX_STAGES = 8;
 constexpr int NCLASS = 7;                 // widths 3..8 -> class 0..5; every other width -> class 6 (per-element path)
@@ -63,6 +63,14 @@ constexpr int MAX_M = 48;
 constexpr int SPIN_LIMIT = 1 << 22;
 
 __device__ int g_error_word = 0;          // first timeout of any kernel of this library (0 = none)
+__device__ unsigned long long g_trace[32];   // tuning aid: nanosecond stamps of CTA (0, 0) when debug bit 1 is set
+__device__ __forceinline__ void trace(int debug, int slot) {
+    if ((debug & 2) && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_trace[slot] = t;
+    }
+}
 
 // One tile of the plan: up to 16 rows of one width.  400 bytes, 16-byte aligned: copied whole by one bulk copy.
 struct TileDesc {
@@ -106,8 +114,8 @@ struct Control {
     int abort;
     alignas(8) uint64_t full[MAX_STAGES];
     alignas(8) uint64_t empty[MAX_STAGES];
-    alignas(8) uint64_t corr_full[2];     // escape corrections of a tile are in corr[buf]
-    alignas(8) uint64_t corr_empty[2];    // ... and have been consumed
+    alignas(8) uint64_t red_full[4];      // the consumer warps' partial sums of a tile are in red[buf]
+    alignas(8) uint64_t red_empty[4];     // ... and have been consumed by the finishing warp
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -483,14 +491,17 @@ struct SmallMParams {
 };
 
 constexpr int SLOT_BYTES = STAGE_BYTES + DESC_SLOT;
+constexpr int NRED = 2;                   // hand-over buffers between the consumer warps and the finishing warp
 
 // DUAL: a second activation layout is staged for widths that pair ids at distance 4 (cheap for few tokens).
 template <int XT, int NT, bool DUAL>
 __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small_m_kernel(const SmallMParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ Control ctl;
+    constexpr int RED_FLOATS = NW * 4 * NT * 32;                       // one hand-over buffer (>= 16 * M floats)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) trace(p.debug, 0);
     const int split = blockIdx.y;
     const int kc0 = split * p.nc_per;                                  // first chunk of this K-range
     const int NC = min(p.nc_per, p.nc_total - kc0);                    // chunks in this K-range (>= 1 by construction)
@@ -498,15 +509,14 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
     const int MP = p.MP, M = p.M;
     const int nstg = p.nstg;
     // dynamic shared memory:
-    //   [ring: nstg x (16-row stage + descriptor)] [activations A] [activations B] [warp partials x 2]
-    //   [per-element row results x 2] [16 zero bytes] [escape corrections x 2]
+    //   [ring: nstg x (16-row stage + descriptor)] [activations A] [activations B] [warp partials x NRED]
+    //   [16 zero bytes] [escape corrections]
     const int xs_halves = p.nc_per * 16 * MP * 8;                      // halves per activation layout
     __half *xs_a = reinterpret_cast<__half *>(smem + (size_t)nstg * SLOT_BYTES);
     __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
-    float *red = reinterpret_cast<float *>(xs_a + (DUAL ? 2 : 1) * xs_halves);     // [2][NW][4 * NT][32]
-    float *rowres = red + 2 * NW * 4 * NT * 32;                        // [2][16][M]
-    uint32_t *zero16 = reinterpret_cast<uint32_t *>(rowres + 2 * 16 * M);
-    float *corr = reinterpret_cast<float *>(zero16 + 4);               // [2][16][M]
+    float *red = reinterpret_cast<float *>(xs_a + (DUAL ? 2 : 1) * xs_halves);     // [NRED][NW][4 * NT][32]
+    uint32_t *zero16 = reinterpret_cast<uint32_t *>(red + NRED * RED_FLOATS);
+    float *corr = reinterpret_cast<float *>(zero16 + 4);               // [16][M], private to the finishing warp
     const bool planned = p.esc_col != nullptr;
     volatile int *abort_flag = &ctl.abort;
 
@@ -515,9 +525,9 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
             mbar_init(smem_u32(&ctl.full[s]), 1);
             mbar_init(smem_u32(&ctl.empty[s]), NW);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&ctl.corr_full[b]), 1);
-            mbar_init(smem_u32(&ctl.corr_empty[b]), 1);
+        for (int b = 0; b < NRED; ++b) {
+            mbar_init(smem_u32(&ctl.red_full[b]), NW);
+            mbar_init(smem_u32(&ctl.red_empty[b]), 1);
         }
         ctl.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -526,6 +536,7 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
     __syncthreads();
     const int ntiles = __ldg(p.ntiles_ptr);
     const int tstep = gridDim.x;
+    if (tid == 0) trace(p.debug, 1);
 
     if (warp == PRODUCER_WARP) {
         // ================= producer warp: lane r copies row r of every stage; lane 16 the tile's descriptor ===========
@@ -543,8 +554,10 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
             }
         };
         fetch(tile);
+        bool first = true;
         while (tile < ntiles && alive) {
             const int cur = tile, cnb = nb, ccnt = cnt;
+            if (first) trace(p.debug, 2);
             const uint8_t *src = p.ids + ((uint64_t)b16 + (uint64_t)kc0 * cnb) * 16u;
             tile += tstep;
             fetch(tile);                                                // next descriptor loads while this tile is issued
@@ -560,54 +573,65 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
                 const uint32_t slot32 = smem_u32(smem + (size_t)slot * SLOT_BYTES);
                 if (cnb && lane < ccnt) bulk_g2s(slot32 + dst_row, src + (size_t)s * NW * 16 * cnb, bytes_row, full);
                 if (s == 0 && lane == 16) bulk_g2s(slot32 + STAGE_BYTES, p.tiles + cur, DESC_BYTES, full);
+                if (first) { trace(p.debug, 3); first = false; }
                 if (++slot == nstg) { slot = 0; phase ^= 1u; }
             }
         }
-    } else if (warp == ESCAPE_WARP) {
-        // ================= escape warp: per tile, lane r sums row r's corrections x * (exact - band) in stored
-        // order over the escapes that fall into this K-range, ahead of the warp that will write the tile =========
-        asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // activations are staged
-        if (planned) {
-            int count = 0;
-            bool alive = true;
-            const int clo = kc0 * KC, chi = clo + NC * KC;
-            int row = -1, e0 = 0, e1 = 0;
-            auto fetch = [&](int t) {
-                if (t < ntiles && lane < 16) {
-                    row = __ldg(&p.tiles[t].row[lane]);
-                    e0 = __ldg(&p.tiles[t].e0[lane]);
-                    e1 = __ldg(&p.tiles[t].e1[lane]);
+    } else if (warp == FINISHER_WARP) {
+        // ================= finishing warp: per tile, sums the escape corrections of its rows while the tile streams,
+        // then takes the consumer warps' partial sums, scales, corrects and writes the rows =================
+        asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // activations staged, sums ready
+        const int g = lane >> 2, t = lane & 3;
+        const int clo = kc0 * KC, chi = clo + NC * KC;
+        float *out = p.S > 1 ? p.part + (int64_t)split * M * p.Q : p.Y;
+        // descriptor fields of the next tile, prefetched: rows g, g+8 (fragment owner) and row `lane` (escapes)
+        int nb = 0, frow[2] = {-1, -1}, erow = -1, e0 = 0, e1 = 0;
+        float fms[2] = {0.f, 0.f}, fts[2] = {0.f, 0.f};
+        auto fetch = [&](int tl) {
+            if (tl < ntiles) {
+                const TileDesc *d = p.tiles + tl;
+                nb = __ldg(&d->nb);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    frow[h] = __ldg(&d->row[g + 8 * h]);
+                    fms[h] = __ldg(&d->ms[g + 8 * h]);
+                    fts[h] = __ldg(&d->ts[g + 8 * h]);
                 }
-            };
-            int tile = blockIdx.x;
+                if (lane < 16) { erow = __ldg(&d->row[lane]); e0 = __ldg(&d->e0[lane]); e1 = __ldg(&d->e1[lane]); }
+            }
+        };
+        int tile = blockIdx.x, count = 0;
+        bool alive = true;
+        fetch(tile);
+        while (tile < ntiles) {
+            const int cur = tile, cnb = nb, crow = lane < 16 ? erow : -1, ce0 = e0, ce1 = e1;
+            const int myrow[2] = {frow[0], frow[1]};
+            const float myms[2] = {fms[0], fms[1]}, myts[2] = {fts[0], fts[1]};
+            tile += tstep;
             fetch(tile);
-            while (tile < ntiles) {
-                const int crow = lane < 16 ? row : -1, ce0 = e0, ce1 = e1;
-                tile += tstep;
-                fetch(tile);
-                const int buf = count & 1;
-                if (alive) alive = mbar_wait(smem_u32(&ctl.corr_empty[buf]), ((count >> 1) & 1) ^ 1u, abort_flag, 3);
-                if (crow >= 0 && alive) {
-                    float *dst = corr + (buf * 16 + lane) * M;
+            // ---- escapes: lane r sums row r's corrections x * (exact - band), in stored order, over this K-range
+            if (planned) {
+                if (crow >= 0) {
+                    float *dst = corr + lane * M;
                     for (int m0 = 0; m0 < M; m0 += 8) {
                         float a[8];
 #pragma unroll
                         for (int k = 0; k < 8; ++k) a[k] = 0.f;
                         for (int e = ce0; e < ce1; e += 4) {
                             int c[4];
-                            float d[4];
+                            float dl[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {                   // four independent loads in flight
                                 const bool ok = e + j < ce1;
                                 c[j] = ok ? __ldg(p.esc_col + e + j) : -1;
-                                d[j] = ok ? __ldg(p.esc_delta + e + j) : 0.f;
+                                dl[j] = ok ? __ldg(p.esc_delta + e + j) : 0.f;
                             }
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 if (c[j] >= clo && c[j] < chi) {
 #pragma unroll
                                     for (int k = 0; k < 8; ++k)
-                                        if (m0 + k < M) a[k] = __fmaf_rn(xs_read(xs_a, c[j] - clo, m0 + k, MP), d[j], a[k]);
+                                        if (m0 + k < M) a[k] = __fmaf_rn(xs_read(xs_a, c[j] - clo, m0 + k, MP), dl[j], a[k]);
                                 }
                             }
                         }
@@ -617,14 +641,84 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
                     }
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl.corr_full[buf]));
-                ++count;
             }
+            if (count == 0) trace(p.debug, 9);
+            // ---- the consumer warps' partial sums (or, for a per-element tile, complete row results)
+            const int buf = count % NRED;
+            if (alive) alive = mbar_wait(smem_u32(&ctl.red_full[buf]), (count / NRED) & 1, abort_flag, 3);
+            if (count == 0) trace(p.debug, 10);
+            const float *rbuf = red + (size_t)buf * RED_FLOATS;
+            float acc[NT][4];
+            if (cnb != 0) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float v = 0.f;
+#pragma unroll
+                        for (int w = 0; w < NW; ++w) v += rbuf[(w * 4 * NT + n * 4 + k) * 32 + lane];
+                        acc[n][k] = v;
+                    }
+            }
+            // thread holds rows g, g+8 of the tile and tokens 8n+2t, 8n+2t+1
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int m = 8 * n + 2 * t + k;
+                        float y = 0.f;
+                        if (myrow[hrow] >= 0 && m < M) {
+                            // y = tau_s * sum(x * id) + min_s * sum(x)   (per-element rows arrive complete)
+                            y = cnb != 0 ? __fmaf_rn(myts[hrow], acc[n][2 * hrow + k], myms[hrow] * ctl.sumx[m])
+                                         : rbuf[(g + 8 * hrow) * M + m];
+                            if (planned) y += corr[(g + 8 * hrow) * M + m];
+                            out[(int64_t)m * p.Q + myrow[hrow]] = y;
+                        }
+                    }
+                }
+            }
+            __syncwarp();                                               // every lane is done with red[buf] and corr
+            if (lane == 0) mbar_arrive(smem_u32(&ctl.red_empty[buf]));
+            if (count == 0) trace(p.debug, 11);
+            if (p.S > 1) {
+                // K-ranges: whichever CTA finishes this tile last adds the partial sums in range order
+                __threadfence();
+                int last = 0;
+                if (lane == 0) last = atomicAdd(p.ticket + cur, 1) == p.S - 1;
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; ++hrow) {
+                        if (myrow[hrow] < 0) continue;
+#pragma unroll
+                        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const int m = 8 * n + 2 * t + k;
+                                if (m < M) {
+                                    const int64_t o = (int64_t)m * p.Q + myrow[hrow];
+                                    float s = 0.f;
+                                    for (int r = 0; r < p.S; ++r) s += __ldcg(p.part + (int64_t)r * M * p.Q + o);
+                                    p.Y[o] = s;
+                                }
+                            }
+                        }
+                    }
+                    if (lane == 0) p.ticket[cur] = 0;
+                }
+            }
+            if (count == 0) trace(p.debug, 12);
+            ++count;
         }
+        trace(p.debug, 13);
     } else {
         // ================= consumer warps =================
         // ---- activations of this K-range as fp16 in fragment order (after the previous kernel in the stream)
         pdl_wait();
+        if (warp == 0) trace(p.debug, 4);
         {
             const int groups = NC * 16;                                 // 8-column groups in the range
             const int64_t col0 = (int64_t)kc0 * KC;
@@ -655,6 +749,7 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
             asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // consumers + escape warp
         }
         pdl_launch_dependents();
+        if (warp == 0) trace(p.debug, 5);
 
         // ---- walk the tiles
         const int g = lane >> 2, t = lane & 3;
@@ -665,24 +760,18 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
         const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
         const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
         const uint32_t ring32 = smem_u32(smem);
-        float *out = p.S > 1 ? p.part + (int64_t)split * M * p.Q : p.Y;
         int slot = 0, count = 0;
         uint32_t phase = 0;
         bool alive = true;
         for (int tile = blockIdx.x; tile < ntiles; tile += tstep, ++count) {
             // the tile's first stage carries its descriptor
             if (alive) alive = mbar_wait(smem_u32(&ctl.full[slot]), phase, abort_flag, 2);
+            if (warp == 0 && count == 0) trace(p.debug, 6);
             const TileDesc *d = reinterpret_cast<const TileDesc *>(smem + (size_t)slot * SLOT_BYTES + STAGE_BYTES);
             const int nb = alive ? d->nb : 0, cnt = alive ? d->cnt : 0;
-            int myrow[2];
-            float myms[2], myts[2];
-#pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow) {
-                myrow[hrow] = alive ? d->row[g + 8 * hrow] : -1;
-                myms[hrow] = d->ms[g + 8 * hrow];
-                myts[hrow] = d->ts[g + 8 * hrow];
-            }
-            const int buf = count & 1;
+            const int buf = count % NRED;
+            const uint32_t red_par = ((count / NRED) & 1) ^ 1u;        // the finishing warp has released red[buf]
+            float *rbuf = red + (size_t)buf * RED_FLOATS;
             float acc[NT][4];
 #pragma unroll
             for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
@@ -690,7 +779,8 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
                 // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
                 // start on a 16-byte boundary).  One row per warp at a time, ids byte-wise from global memory; the
                 // stage holds only the descriptor.
-                float *rr_out = rowres + buf * 16 * M;
+                if (alive) alive = mbar_wait(smem_u32(&ctl.red_empty[buf]), red_par, abort_flag, 4);
+                float *rr_out = rbuf;                                   // [16][M] complete row results
                 for (int rr = warp; rr < cnt; rr += NW) {
                     const int q = d->row[rr];
                     const float ms = d->ms[rr], ts = d->ts[rr];
@@ -741,84 +831,18 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
                     if (lane == 0) mbar_arrive(smem_u32(&ctl.empty[slot]));
                     if (++slot == nstg) { slot = 0; phase ^= 1u; }
                 }
-                float *rbuf = red + (size_t)buf * (NW * 4 * NT * 32);
+                // hand the partial sums to the finishing warp and go on with the next tile
+                if (alive) alive = mbar_wait(smem_u32(&ctl.red_empty[buf]), red_par, abort_flag, 4);
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
 #pragma unroll
                     for (int k = 0; k < 4; ++k) rbuf[(warp * 4 * NT + n * 4 + k) * 32 + lane] = acc[n][k];
             }
-            consumer_sync();
-            if (warp != (count & (NW - 1))) continue;
-            // ---- one warp finishes the tile: warps' partial sums in warp order, scale, corrections, K-ranges
-            if (nb != 0) {
-                const float *rbuf = red + (size_t)buf * (NW * 4 * NT * 32);
-#pragma unroll
-                for (int n = 0; n < NT; ++n)
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        float v = 0.f;
-#pragma unroll
-                        for (int w = 0; w < NW; ++w) v += rbuf[(w * 4 * NT + n * 4 + k) * 32 + lane];
-                        acc[n][k] = v;
-                    }
-            }
-            if (planned && alive) alive = mbar_wait(smem_u32(&ctl.corr_full[buf]), (count >> 1) & 1, abort_flag, 4);
-            // thread holds rows g, g+8 of the tile and tokens 8n+2t, 8n+2t+1
-#pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow) {
-                const int q = myrow[hrow];
-                if (q < 0) continue;
-                const float *cr = corr + (buf * 16 + g + 8 * hrow) * M;
-                const float *rr = rowres + (buf * 16 + g + 8 * hrow) * M;
-#pragma unroll
-                for (int n = 0; n < NT; ++n) {
-#pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        const int m = 8 * n + 2 * t + k;
-                        if (m < M) {
-                            // y = tau_s * sum(x * id) + min_s * sum(x)   (per-element rows are already complete)
-                            float y = nb != 0 ? __fmaf_rn(myts[hrow], acc[n][2 * hrow + k], myms[hrow] * ctl.sumx[m]) : rr[m];
-                            if (planned) y += cr[m];
-                            out[(int64_t)m * p.Q + q] = y;
-                        }
-                    }
-                }
-            }
-            if (planned) {
-                __syncwarp();                                           // every lane has read its corrections
-                if (lane == 0) mbar_arrive(smem_u32(&ctl.corr_empty[buf]));
-            }
-            if (p.S > 1) {
-                // K-ranges: whichever CTA finishes this tile last adds the partial sums in range order
-                __syncwarp();
-                __threadfence();
-                int last = 0;
-                if (lane == 0) last = atomicAdd(p.ticket + tile, 1) == p.S - 1;
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __threadfence();
-#pragma unroll
-                    for (int hrow = 0; hrow < 2; ++hrow) {
-                        const int q = myrow[hrow];
-                        if (q < 0) continue;
-#pragma unroll
-                        for (int n = 0; n < NT; ++n) {
-#pragma unroll
-                            for (int k = 0; k < 2; ++k) {
-                                const int m = 8 * n + 2 * t + k;
-                                if (m < M) {
-                                    const int64_t o = (int64_t)m * p.Q + q;
-                                    float s = 0.f;
-                                    for (int r = 0; r < p.S; ++r) s += __ldcg(p.part + (int64_t)r * M * p.Q + o);
-                                    p.Y[o] = s;
-                                }
-                            }
-                        }
-                    }
-                    if (lane == 0) p.ticket[tile] = 0;
-                }
-            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl.red_full[buf]));
+            if (warp == 0 && count == 0) trace(p.debug, 7);
         }
+        if (warp == 0) trace(p.debug, 8);
     }
 }
 
@@ -851,11 +875,12 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     pl.nc_total = (int)(P / KC);
     pl.NT = (int)((M + 7) / 8);
     pl.MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * pl.NT;
-    pl.dual = pl.MP <= 4;
-    const int layouts = pl.dual ? 2 : 1;
     const int per_sm = pl.NT == 1 ? 4 : pl.NT == 2 ? 2 : 1;             // resident CTAs per SM the kernel is built for
-    // K-range length: bounded by the shared memory the staged activations may take
-    const int xs_budget = pl.MP <= 4 ? 8 * 1024 : pl.NT == 1 ? 16 * 1024 : pl.NT == 2 ? 32 * 1024 : 96 * 1024;
+    // K-range length: bounded by the shared memory the staged activations may take.  The second activation layout
+    // (no byte permutes for widths 3..5) is staged only when it does not shorten the K-range.
+    const int xs_budget = pl.NT == 1 ? 16 * 1024 : pl.NT == 2 ? 32 * 1024 : 96 * 1024;
+    pl.dual = pl.MP <= 4 && (int64_t)P * pl.MP * 2 * 2 <= xs_budget;
+    const int layouts = pl.dual ? 2 : 1;
     int nc_max = xs_budget / (KC * pl.MP * 2 * layouts);
     if (nc_max >= NW) nc_max = nc_max / NW * NW;                        // whole stages
     if (nc_max < 1) nc_max = 1;
@@ -883,7 +908,7 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     if (cx > max_tiles) cx = max_tiles;
     pl.ctas_x = (int)cx;
     const size_t xs_bytes = (size_t)pl.nc_per * KC * pl.MP * 2 * layouts;
-    const size_t red_bytes = (size_t)2 * NW * 4 * pl.NT * 32 * 4 + (size_t)4 * 16 * M * 4;   // partials, row results, corrections
+    const size_t red_bytes = (size_t)NRED * NW * 4 * pl.NT * 32 * 4 + (size_t)16 * M * 4;    // hand-over buffers, corrections
     const size_t per_cta = (size_t)(pl.NT == 1 ? 51 : pl.NT == 2 ? 106 : 216) * 1024;
     int nstg = g_force_nstg ? g_force_nstg : (int)((per_cta - xs_bytes - red_bytes - 64) / SLOT_BYTES);
     if (nstg > MAX_STAGES) nstg = MAX_STAGES;
@@ -944,6 +969,13 @@ QV_API void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int deb
     qv::g_force_s = force_s > 0 ? force_s : 0;
     qv::g_force_nstg = (nstg >= 2 && nstg <= qv::MAX_STAGES) ? nstg : 0;
     qv::g_debug = debug;
+}
+
+QV_API int qvb8_debug_trace(unsigned long long *out32) {
+    if (!out32) return qv::fail(QVB8_ERR_ARG, "qvb8_debug_trace: null output");
+    if (cudaMemcpyFromSymbol(out32, qv::g_trace, sizeof(unsigned long long) * 32) != cudaSuccess)
+        return qv::cuda_status("qvb8_debug_trace");
+    return QVB8_OK;
 }
 
 QV_API int qvb8_device_status(int *status) {

@@ -23,7 +23,7 @@ _CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
 EXPORTS = (
     "qvb8_last_error", "qvb8_version", "qvb8_decode", "qvb8_small_m_scratch_bytes", "qvb8_small_m",
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
-    "qvb8_device_status",
+    "qvb8_device_status", "qvb8_debug_trace",
 )
 
 
@@ -67,6 +67,7 @@ def load() -> ctypes.CDLL:
             lib.qvb8_small_m_ex.argtypes = [pk, vp, vp, ci, ci, i64, vp, vp, i64, ci, vp]
             lib.qvb8_small_m_set_tuning.argtypes = [ci, ci, ci, ci]
             lib.qvb8_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+            lib.qvb8_debug_trace.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
             lib.qvb8_small_m_set_tuning.restype = None
             _lib = lib
     return _lib
