@@ -35,9 +35,9 @@
 // stored order) and writes the result.  K-ranges of one tile are added in range order by whichever CTA finishes the
 // tile last (a ticket counter per tile).  Every sum has a fixed order: results are identical from run to run.
 //
-// Waits.  Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the waiter raises a per-CTA abort flag and a
-// device-wide error word (qvb8_device_status), every other waiter gives up too, and the kernel runs to its end with
-// a meaningless result instead of hanging.
+// Waits.  Every wait on an mbarrier is bounded: after two seconds (or SPIN_LIMIT polls) the waiter raises a per-CTA
+// abort flag and a device-wide error word (qvb8_device_status), every other waiter gives up too, and the kernel
+// runs to its end with a meaningless result instead of hanging.
 #include "common.cuh"
 
 namespace qv {
@@ -130,22 +130,39 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
+// One poll.  The barrier unit parks the warp until the phase completes or the time hint (nanoseconds) runs out, so a
+// waiting warp issues a handful of instructions per hint period instead of competing with the working warps.
+constexpr uint32_t WAIT_HINT_NS = 20000;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;      // a wait gives up after two seconds (or SPIN_LIMIT polls)
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(WAIT_HINT_NS) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 // Bounded wait.  Returns false if the barrier did not complete (this waiter or another one gave up).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+    const uint64_t t0 = global_ns();
     for (int i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255) == 255 && *abort_flag) return false;
+        if ((i & 7) == 7) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+        }
     }
     *abort_flag = 1;
     atomicCAS(&g_error_word, 0, code);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, code);
 }
 // global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned); completion is counted
 // on `bar`.  The destination is this CTA's own shared memory.
@@ -722,31 +739,58 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
         {
             const int groups = NC * 16;                                 // 8-column groups in the range
             const int64_t col0 = (int64_t)kc0 * KC;
-            for (int idx = tid; idx < MP * groups; idx += NW * 32) {
-                const int m = idx / groups, u8 = idx - m * groups;     // u8: natural 8-column group number
-                uint32_t h[8];
-                if (m < M) {
-                    stage_x8<XT>(p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h);
-                } else {
+            const int total = MP * groups;
+            constexpr int UNR = 4;                                      // loads in flight per thread
+            for (int base = tid; base < total; base += NW * 32 * UNR) {
+                uint32_t h[UNR][8];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) h[k] = 0u;
+                for (int u = 0; u < UNR; ++u) {
+                    const int idx = base + u * NW * 32;
+                    const int m = idx / groups, u8 = idx - m * groups; // u8: natural 8-column group number
+                    if (idx < total && m < M) {
+                        stage_x8<XT>(p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h[u]);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) h[u][k] = 0u;
+                    }
                 }
-                const int sl = slot_of(u8 * 8, m, MP);
-                *reinterpret_cast<uint4 *>(xs_a + (sl << 3)) =
-                    make_uint4(h[0] | (h[2] << 16), h[1] | (h[3] << 16), h[4] | (h[6] << 16), h[5] | (h[7] << 16));
-                if (DUAL)
-                    *reinterpret_cast<uint4 *>(xs_b + (sl << 3)) =
-                        make_uint4(h[0] | (h[4] << 16), h[1] | (h[5] << 16), h[2] | (h[6] << 16), h[3] | (h[7] << 16));
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const int idx = base + u * NW * 32;
+                    if (idx >= total) continue;
+                    const int m = idx / groups, u8 = idx - m * groups;
+                    const int sl = slot_of(u8 * 8, m, MP);
+                    *reinterpret_cast<uint4 *>(xs_a + (sl << 3)) = make_uint4(
+                        h[u][0] | (h[u][2] << 16), h[u][1] | (h[u][3] << 16), h[u][4] | (h[u][6] << 16), h[u][5] | (h[u][7] << 16));
+                    if (DUAL)
+                        *reinterpret_cast<uint4 *>(xs_b + (sl << 3)) = make_uint4(
+                            h[u][0] | (h[u][4] << 16), h[u][1] | (h[u][5] << 16), h[u][2] | (h[u][6] << 16), h[u][3] | (h[u][7] << 16));
+                }
             }
             consumer_sync();
-            for (int m = warp; m < M; m += NW) {                        // fixed-order sums: same bits every run
-                float s = 0.f;
-                for (int c = lane; c < NC * KC; c += 32) s += xs_read(xs_a, c, m, MP);
+            // per-token sums of the narrowed activations, in a fixed order: thread -> every 128th slot, then a fixed
+            // tree over the 128 threads (same bits every run)
+            float *psum = red;                                          // 128 floats of the hand-over area, free until the first tile ends
+            for (int m = 0; m < M; ++m) {
+                float sacc = 0.f;
+                for (int j = tid; j < groups; j += NW * 32) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(xs_a + ((size_t)(j * MP + m) << 3));
+                    const __half2 *hp = reinterpret_cast<const __half2 *>(&v);
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (lane == 0) ctl.sumx[m] = s;
+                    for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(hp[k]); sacc += f.x; sacc += f.y; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
+                if (lane == 0) psum[m * NW + warp] = sacc;
             }
-            asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // consumers + escape warp
+            consumer_sync();
+            if (tid < M) {
+                float sacc = 0.f;
+#pragma unroll
+                for (int w = 0; w < NW; ++w) sacc += psum[tid * NW + w];
+                ctl.sumx[tid] = sacc;
+            }
+            asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // consumers + finishing warp
         }
         pdl_launch_dependents();
         if (warp == 0) trace(p.debug, 5);
