@@ -49,11 +49,12 @@ int check_small_m_args(const qvb8_pack *w, const void *X, int x_dtype, int x_mod
                        const char *who);
 
 constexpr int KC = 128;                   // columns per chunk
-constexpr int NW = 4;                     // consumer warps = chunks per stage
+constexpr int NW = 4;                     // consumer warps
+constexpr int MAX_CPS = 16;               // most chunks per stage (a stage holds cps chunks, cps a multiple of NW)
 constexpr int PRODUCER_WARP = NW;         // issues the bulk copies
 constexpr int FINISHER_WARP = NW + 1;     // escape corrections, cross-warp sums, scaling, output, K-range tickets
-constexpr int NTHREADS = (NW + 2) * 32;
-constexpr int MAX_STAGES = 8;
+constexpr int PIPE_THREADS = (NW + 2) * 32;  // threads of one pipe
+constexpr int MAX_STAGES = 6;
 constexpr int NCLASS = 7;                 // widths 3..8 -> class 0..5; every other width -> class 6 (per-element path)
 constexpr int64_t TICKET_BYTES = 256 * 1024;  // fixed-size counter area at the START of the scratch (one counter per
                                               // tile), so that calls of different sizes sharing one scratch never
@@ -76,15 +77,20 @@ __device__ __forceinline__ void trace(int debug, int slot) {
 struct TileDesc {
     int nb;                 // width of the rows; 0 = per-element class (width outside 3..8 or unaligned row start)
     int cnt;                // real rows (the rest is padding)
-    int pad[2];
+    int esc0;               // first entry of the tile's escapes in the plan's entry list (even: 16-byte aligned)
+    int nesc;               // number of entries
     int row[16];            // output row, -1 = padding
     uint32_t b16[16];       // byte offset of the row in `ids`, in 16-byte units
     float ms[16], ts[16];   // min_s, tau_s
-    int e0[16], e1[16];     // the row's range in the escape plan
+    int e0[16], e1[16];     // the row's range within the tile's entries
 };
 static_assert(sizeof(TileDesc) == 400, "descriptor size");
+struct EscEntry { int col; float delta; };   // column, exact value - band value
 constexpr int DESC_BYTES = 400;
-constexpr int DESC_SLOT = 416;            // descriptor area of a ring slot
+constexpr int DESC_SLOT = 416;            // descriptor area of a side slot
+constexpr int ESC_CAP = 192;              // escape entries that travel with a descriptor (the rest is read from global memory)
+constexpr int SIDE_BYTES = DESC_SLOT + ESC_CAP * 8;
+constexpr int NSIDE = 3;                  // side slots per pipe: descriptors and escapes of the visits ahead
 
 // Plan buffer layout (offsets in bytes, each section 256-byte aligned):
 //   [0]  header: int ntiles
@@ -92,8 +98,10 @@ constexpr int DESC_SLOT = 416;            // descriptor area of a ring slot
 //   esc_col   int[n_esc]     column of each escape
 //   esc_delta float[n_esc]   exact value - band value
 //   tiles     TileDesc[ceil(Q / 16) + NCLASS - 1]
+//   esc_ent   EscEntry[n_esc + tiles]   the escapes again, grouped by tile (each tile's list padded to an even
+//                                       length), so that one contiguous copy brings a tile's escapes
 struct PlanLayout {
-    int64_t esc_ptr, esc_col, esc_delta, tiles, total;
+    int64_t esc_ptr, esc_col, esc_delta, tiles, esc_ent, total;
     int max_tiles;
 };
 __host__ __device__ inline int64_t up256(int64_t v) { return (v + 255) / 256 * 256; }
@@ -104,18 +112,27 @@ inline PlanLayout plan_layout(int64_t Q, int64_t n_esc) {
     L.esc_col = L.esc_ptr + up256((Q + 1) * 4);
     L.esc_delta = L.esc_col + up256(n_esc * 4);
     L.tiles = L.esc_delta + up256(n_esc * 4);
-    L.total = L.tiles + up256((int64_t)L.max_tiles * DESC_BYTES);
+    L.esc_ent = L.tiles + up256((int64_t)L.max_tiles * DESC_BYTES);
+    L.total = L.esc_ent + up256((n_esc + L.max_tiles + 2) * 8);
     return L;
 }
 
 // Per-CTA control block in static shared memory.
-struct Control {
-    float sumx[MAX_M];
-    int abort;
+struct PipeControl {
     alignas(8) uint64_t full[MAX_STAGES];
     alignas(8) uint64_t empty[MAX_STAGES];
-    alignas(8) uint64_t red_full[4];      // the consumer warps' partial sums of a tile are in red[buf]
-    alignas(8) uint64_t red_empty[4];     // ... and have been consumed by the finishing warp
+    alignas(8) uint64_t side_full[NSIDE];   // a visit's descriptor and escapes have landed
+    alignas(8) uint64_t side_empty[NSIDE];  // ... and the four consumer warps and the finishing warp are done with them
+    alignas(8) uint64_t red_full;         // the consumer warps' partial sums of a visit are in the hand-over buffer
+    alignas(8) uint64_t red_empty;        // ... and have been taken by the finishing warp
+};
+struct Control {
+    float sumx[MAX_M];                    // per-token sums of the narrowed activations of this K-range
+    int abort;
+    alignas(16) uint32_t pair_table[24];  // pair-conversion constants of widths 3..8 (see pair_const)
+    alignas(8) uint64_t x_ready;          // every consumer warp has staged its share of the activations
+    alignas(8) uint64_t sums_ready;       // every finishing warp has summed its share of the tokens
+    PipeControl pipe[3];
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -170,7 +187,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32) : "memory"); }
 
 // Programmatic dependent launch: everything before pdl_wait() may overlap the tail of the previous kernel in the
 // stream (it must not touch memory that kernel writes); both are no-ops for a normal launch.
@@ -200,19 +216,39 @@ template <> struct Pairing<3> { static constexpr int D = 4, E = 4; };
 __host__ __device__ constexpr uint32_t h_pow2(int e) { return (uint32_t)(15 - e) << 10; }
 __host__ __device__ constexpr uint32_t h_neg1024_pow2(int e) { return 0x8000u | ((uint32_t)(25 - e) << 10); }
 
+// The four constants of a width, held in registers for a whole tile.  They are read from a small table in shared
+// memory with volatile loads: values the compiler can see (literals, or moves of literals) it re-creates next to
+// every use -- one extra instruction per pair, measured -- because the fp16 multiply-add takes only one of its two
+// constants as an immediate.
+struct PairConst { uint32_t mask, magic, scale, bias; };
+__host__ __device__ constexpr uint32_t pair_const_word(int nb, int k) {
+    const int D = nb >= 6 ? 2 : 4;
+    const int E = 16 - nb * D;                                   // Pairing<nb>::E
+    const int EL = E > 0 ? E : 0, EH = E < 0 ? -E : 0;
+    const uint32_t FM = (1u << nb) - 1u;
+    return k == 0 ? ((FM << EL) | (FM << (16 + EH)))
+         : k == 1 ? 0x64006400u
+         : k == 2 ? (h_pow2(EL) | (h_pow2(EH) << 16))
+                  : (h_neg1024_pow2(EL) | (h_neg1024_pow2(EH) << 16));
+}
+constexpr int PAIR_TABLE_WORDS = 6 * 4;                          // widths 3..8
+__device__ __forceinline__ PairConst pair_const(const uint32_t *table, int nb) {
+    const uint32_t a = smem_u32(table + (nb - 3) * 4);
+    PairConst c;
+    asm volatile("ld.volatile.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(c.mask), "=r"(c.magic), "=r"(c.scale), "=r"(c.bias) : "r"(a));
+    return c;
+}
+
 // Register holding fp16(id[fa]) in the low half and fp16(id[fa + D]) in the high half, from the nb words W of a
-// thread's 32-id block.  All shifts and masks fold to constants after unrolling.
+// thread's 32-id block.  All shifts fold to constants after unrolling.
 template <int NB>
-__device__ __forceinline__ uint32_t pair_reg(const uint32_t (&W)[NB], int fa) {
+__device__ __forceinline__ uint32_t pair_reg(const uint32_t (&W)[NB], int fa, const PairConst &pc) {
     constexpr int D = Pairing<NB>::D, E = Pairing<NB>::E;
     constexpr int EL = E > 0 ? E : 0;            // mantissa shift of the low id
     constexpr int EH = E < 0 ? -E : 0;           // mantissa shift of the high id
     static_assert(NB * D == 16 + EH - EL, "pairing does not line the two ids up");
     static_assert(EL + NB <= 10 && EH + NB <= 10, "id does not fit the fp16 mantissa");
-    constexpr uint32_t FM = (1u << NB) - 1u;
-    constexpr uint32_t MASK = (FM << EL) | (FM << (16 + EH));
-    constexpr uint32_t SCALE = h_pow2(EL) | (h_pow2(EH) << 16);
-    constexpr uint32_t BIAS = h_neg1024_pow2(EL) | (h_neg1024_pow2(EH) << 16);
     const int s = NB * fa - EL;                  // bit of the block that must land on bit 0
     uint32_t r;
     if (s < 0) {
@@ -222,13 +258,13 @@ __device__ __forceinline__ uint32_t pair_reg(const uint32_t (&W)[NB], int fa) {
         const int top = sh + 16 + EH + NB;       // one past the highest bit needed, relative to W[wi]
         if (sh == 0) r = W[wi];
         else if (top <= 32) r = W[wi] >> sh;
-        else r = __funnelshift_r(W[wi], W[wi + 1 < NB ? wi + 1 : wi], sh);
+        else asm("shf.r.wrap.b32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(W[wi]), "r"(W[wi + 1 < NB ? wi + 1 : wi]), "r"(sh));
     }
-    r = (r & MASK) | 0x64006400u;                // two fp16 numbers 1024 + id * 2^shift
-    if constexpr (EL == 0 && EH == 0) {
-        asm("sub.f16x2 %0, %1, %2;\n" : "=r"(r) : "r"(r), "r"(0x64006400u));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(r) : "r"(r), "r"(pc.mask), "r"(pc.magic));   // (r & mask) | magic:
+    if constexpr (EL == 0 && EH == 0) {                                                         // 1024 + id * 2^shift, twice
+        asm("sub.f16x2 %0, %1, %2;\n" : "=r"(r) : "r"(r), "r"(pc.magic));
     } else {
-        asm("fma.rn.f16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(r), "r"(SCALE), "r"(BIAS));
+        asm("fma.rn.f16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(r), "r"(pc.scale), "r"(pc.bias));
     }
     return r;
 }
@@ -275,24 +311,20 @@ __device__ __forceinline__ void load_block<3>(uint32_t addr, uint32_t (&W)[3]) {
     asm volatile("ld.shared.u32 %0, [%1+8];\n" : "=r"(W[2]) : "r"(addr));
 }
 
-// Bytes between rows of a stage.  The eight chunks of a row lie back to back (a contiguous copy); the stride adds
-// one chunk's worth of padding (16 bytes for 8-bit rows) so that the 32 lanes of a warp, which read rows g and
-// columns 32 t of ONE chunk, fall on distinct banks.
+// Bytes between rows of a stage.  The chunks of a row lie back to back (one contiguous copy per row and stage); the
+// stride adds padding so that the 32 lanes of a warp, which read rows g and columns 32 t of ONE chunk, fall on
+// distinct banks.
 __host__ __device__ constexpr bool stride_ok(int nb, int rs) {
     return nb == 8 ? (rs / 16) % 8 == 1                  // 16-byte loads, quarter warps (rows 2i, 2i+1)
          : nb == 4 ? (rs / 16) % 8 == 4
          : nb == 6 ? (rs / 8) % 16 == 12                 // 8-byte loads, half warps (rows 4i .. 4i+3)
                    : (rs / 4) % 32 == (4 * nb) % 32;     // 4-byte loads, whole warp
 }
-__host__ __device__ constexpr int stage_row_stride(int nb) {
-    int rs = 16 * nb * NW;
+__host__ __device__ constexpr int stage_row_stride(int nb, int cps) {
+    int rs = 16 * nb * cps;
     while (!stride_ok(nb, rs)) rs += 16;
     return rs;
 }
-constexpr int STAGE_ROW_MAX = stage_row_stride(8) > stage_row_stride(7) ? stage_row_stride(8) : stage_row_stride(7);
-constexpr int STAGE_BYTES = 16 * STAGE_ROW_MAX;
-static_assert(stage_row_stride(3) <= STAGE_ROW_MAX && stage_row_stride(4) <= STAGE_ROW_MAX &&
-              stage_row_stride(5) <= STAGE_ROW_MAX && stage_row_stride(6) <= STAGE_ROW_MAX, "stage row size");
 
 // One 128-column chunk of a 16-row tile of width NB: 8 MMAs per token group.
 //   wa, wb   shared addresses of this thread's blocks in rows g and g + 8 of the stage
@@ -301,7 +333,8 @@ static_assert(stage_row_stride(3) <= STAGE_ROW_MAX && stage_row_stride(4) <= STA
 //   DUAL     true: a second activation layout exists for widths that pair ids at distance 4 (xa points into it);
 //            false: only layout A is staged and those widths rebuild their operands with byte permutes
 template <int NB, int NT, bool DUAL>
-__device__ __forceinline__ void chunk_mma(uint32_t wa, uint32_t wb, uint32_t xa, uint32_t xstep, float (&acc)[NT][4]) {
+__device__ __forceinline__ void chunk_mma(uint32_t wa, uint32_t wb, uint32_t xa, uint32_t xstep, float (&acc)[NT][4],
+                                          const PairConst &pc) {
     constexpr int D = Pairing<NB>::D;
     uint32_t Wa[NB], Wb[NB];
     load_block<NB>(wa, Wa);
@@ -320,8 +353,8 @@ __device__ __forceinline__ void chunk_mma(uint32_t wa, uint32_t wb, uint32_t xa,
         for (int h = 0; h < 2; ++h) {
             // ids of this MMA: D == 2 -> {8i+4h .. 8i+4h+3} paired (f, f+2);  D == 4 -> {8i+2h, +1, +4, +5} paired (f, f+4)
             const int f0 = D == 2 ? 8 * i + 4 * h : 8 * i + 2 * h;
-            const uint32_t a0 = pair_reg<NB>(Wa, f0), a2 = pair_reg<NB>(Wa, f0 + 1);
-            const uint32_t a1 = pair_reg<NB>(Wb, f0), a3 = pair_reg<NB>(Wb, f0 + 1);
+            const uint32_t a0 = pair_reg<NB>(Wa, f0, pc), a2 = pair_reg<NB>(Wa, f0 + 1, pc);
+            const uint32_t a1 = pair_reg<NB>(Wb, f0, pc), a3 = pair_reg<NB>(Wb, f0 + 1, pc);
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 if constexpr (D == 2 || DUAL) {
@@ -487,169 +520,401 @@ __global__ void __launch_bounds__(1024) plan_tiles_kernel(const uint8_t *__restr
     }
 }
 
+// The escapes once more, grouped by tile: entry list of tile t = the escapes of its rows in row-slot order, padded to
+// an even length.  Rewrites the descriptors' e0 / e1 (absolute positions in the by-row arrays on entry) to positions
+// within the tile's list.  One block.
+__global__ void __launch_bounds__(1024) tile_escapes_kernel(TileDesc *__restrict__ tiles, const int *__restrict__ header,
+                                                            const int *__restrict__ esc_col,
+                                                            const float *__restrict__ esc_delta,
+                                                            EscEntry *__restrict__ ent) {
+    __shared__ int wsum[32];
+    __shared__ int running;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ntiles = header[0];
+    if (tid == 0) running = 0;
+    __syncthreads();
+    for (int t0 = 0; t0 < ntiles; t0 += 1024) {
+        const int t = t0 + tid;
+        int n = 0;
+        if (t < ntiles)
+            for (int s = 0; s < 16; ++s)
+                if (tiles[t].row[s] >= 0) n += tiles[t].e1[s] - tiles[t].e0[s];
+        const int np = (n + 1) & ~1;
+        int incl = np;                                              // inclusive scan over the block
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) wsum[warp] = incl;
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += wsum[w];
+        const int base = running + before + incl - np;
+        if (t < ntiles) {
+            TileDesc &d = tiles[t];
+            d.esc0 = base;
+            d.nesc = n;
+            int pos = 0;
+            for (int s = 0; s < 16; ++s) {
+                int g0 = 0, g1 = 0;
+                if (d.row[s] >= 0) { g0 = d.e0[s]; g1 = d.e1[s]; }
+                d.e0[s] = pos;
+                for (int e = g0; e < g1; ++e, ++pos) ent[base + pos] = EscEntry{esc_col[e], esc_delta[e]};
+                d.e1[s] = pos;
+            }
+            if (n & 1) ent[base + n] = EscEntry{-1, 0.f};
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int tot = 0;
+            for (int w = 0; w < 32; ++w) tot += wsum[w];
+            running += tot;
+        }
+        __syncthreads();
+    }
+}
+
 struct SmallMParams {
     const uint8_t *ids;
     const uint8_t *nbits;      // per-element class only
     const int64_t *bit_off;    // per-element class only
     const TileDesc *tiles;
     const int *ntiles_ptr;     // plan header
-    const int *esc_col;        // null: the pack has no escapes
-    const float *esc_delta;
+    const EscEntry *esc_ent;   // escapes grouped by tile; null: the pack has no escapes
     const void *X;
     float *Y;                  // (M, Q)
-    float *part;               // (S, M, Q) partial sums when S > 1
-    int *ticket;               // one counter per tile when S > 1 (zero on entry, zero on exit)
+    float *part;               // (slots, M, Q) partial results of tiles shared by several visits
+    int *ticket;               // one counter per tile (zero on entry, zero on exit)
     int Q, P, M, MP;           // MP: token slots per column group in shared memory (>= M)
+    int x_dtype;
     int S;                     // K-ranges (= gridDim.y)
     int nc_per;                // chunks per K-range (the last range may be shorter)
     int nc_total;              // P / 128
-    int nstg;                  // slots of the copy ring
-    int debug;                 // bit 0: skip the fragment math (copy stream only; tuning experiments)
+    int nstg;                  // slots of each pipe's copy ring
+    int cps;                   // chunks per stage (a multiple of NW)
+    int rs[6];                 // bytes between rows of a stage, by width 3..8
+    int slot_bytes;            // a ring slot: 16 rows of the widest width
+    int debug;                 // bit 0: skip the fragment math (copy stream only); bit 1: time stamps of CTA (0, 0);
+                               // bit 2: skip the row copies (math on whatever the ring holds; tuning experiments)
 };
 
-constexpr int SLOT_BYTES = STAGE_BYTES + DESC_SLOT;
-constexpr int NRED = 2;                   // hand-over buffers between the consumer warps and the finishing warp
+// Pipes per CTA: a pipe is four consumer warps, a producer warp and a finishing warp with a copy ring of their own.
+// One CTA per SM; its pipes share the staged activations.
+__host__ __device__ constexpr int pipes_for(int NT) { return NT == 1 ? 3 : NT == 2 ? 2 : 1; }
+
+// Work division.  A K-range of a tile is NSK stages long; the units (tile, stage), tile-major, are cut into equal
+// runs of L units, one run per pipe, so that every pipe streams the same number of bytes whatever the number of
+// tiles.  A pipe's run visits one tile after another; a tile that several visits share is summed through the
+// partial-result buffer in a fixed order (K-range, then pipe).
+struct Visit { int tile, sb, se; };                                     // stages [sb, se) of the tile
+__host__ __device__ inline int run_length(int ntiles, int NSK, int npipes) {
+    const long long total = (long long)ntiles * NSK;
+    const int L = (int)((total + npipes - 1) / npipes);
+    return L > 0 ? L : 1;
+}
+__host__ __device__ inline int visits_of_tile(int t, int NSK, int L) {  // how many pipes touch the tile in one K-range
+    return (t * NSK + NSK - 1) / L - (t * NSK) / L + 1;
+}
+// A pipe's run [u0, u1) as a list of visits.  Order: a run that ends inside a tile takes that (shared) tile first,
+// so that the waiting a shared tile costs (fence, ticket, possibly the final sum) is hidden behind the rest of the
+// run and the run ends with tiles it writes alone.
+struct Run {
+    int u0, u1, NSK, t_first, t_last, nv;
+    bool last_first;
+};
+__device__ __forceinline__ Run make_run(int u0, int u1, int NSK) {
+    Run r;
+    r.u0 = u0; r.u1 = u1; r.NSK = NSK;
+    r.nv = 0; r.t_first = r.t_last = 0; r.last_first = false;
+    if (u1 > u0) {
+        r.t_first = u0 / NSK;
+        r.t_last = (u1 - 1) / NSK;
+        r.nv = r.t_last - r.t_first + 1;
+        r.last_first = r.nv > 1 && (u1 - r.t_last * NSK) < NSK;
+    }
+    return r;
+}
+__device__ __forceinline__ Visit run_visit(const Run &r, int i) {
+    int j = i;                                                          // position in tile order
+    if (r.last_first) j = i == 0 ? r.nv - 1 : i - 1;
+    Visit v;
+    v.tile = r.t_first + j;
+    v.sb = j == 0 ? r.u0 - r.t_first * r.NSK : 0;
+    v.se = v.tile == r.t_last ? r.u1 - r.t_last * r.NSK : r.NSK;
+    return v;
+}
+
+// A warp's position in its pipe's copy ring.
+struct RingPos {
+    uint32_t full, empty;      // shared addresses of the current slot's barriers
+    uint32_t data;             // ... and of its stage
+    int slot;
+    uint32_t phase;
+};
+__device__ __forceinline__ void ring_advance(RingPos &rp, uint32_t slot_bytes, int nstg) {
+    rp.full += 8; rp.empty += 8; rp.data += slot_bytes;
+    if (++rp.slot == nstg) {
+        rp.full -= 8 * nstg; rp.empty -= 8 * nstg; rp.data -= slot_bytes * nstg;
+        rp.slot = 0; rp.phase ^= 1u;
+    }
+}
+
+// Stages [sb, se) of one tile of width NB: this warp's chunks of every stage.  CPW: chunks per warp per stage when known at compile time (0: read it from the parameters).
+// Returns false if a wait gave up.
+template <int NB, int NT, bool DUAL, int CPW>
+__device__ __forceinline__ bool stream_tile(const SmallMParams &p, const uint32_t *pair_table, volatile int *abort_flag,
+                                            RingPos &rp, int NC, int sb, int se, int warp, int lane, uint32_t xbase,
+                                            uint32_t xstep, float (&acc)[NT][4]) {
+    const PairConst pc = pair_const(pair_table, NB);
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t RS = (uint32_t)p.rs[NB - 3];
+    const uint32_t woff = (uint32_t)g * RS + (uint32_t)(t * 4 * NB) + (uint32_t)(warp * 16 * NB);
+    const uint32_t xchunk = 4 * xstep;
+    const int cps = CPW ? CPW * NW : p.cps;
+    const int cpw = CPW ? CPW : p.cps / NW;
+    const uint32_t slot_bytes = (uint32_t)p.slot_bytes;
+    const int nstg = p.nstg;
+    const bool math = !(p.debug & 1);
+    uint32_t xptr = xbase + (uint32_t)(sb * cps + warp) * xchunk;       // this warp's first chunk of the stage
+    for (int s = sb; s < se; ++s) {
+        if (!mbar_wait(rp.full, rp.phase, abort_flag, 2)) return false;
+        if (math) {
+            const uint32_t wa = rp.data + woff;
+            if ((s + 1) * cps <= NC) {                                  // a full stage
+#pragma unroll
+                for (int j = 0; j < (CPW ? CPW : 1); ++j) {
+                    if (CPW) {
+                        chunk_mma<NB, NT, DUAL>(wa + j * (NW * 16 * NB), wa + j * (NW * 16 * NB) + 8 * RS,
+                                                xptr + j * NW * xchunk, xstep, acc, pc);
+                    } else {
+                        for (int jj = 0; jj < cpw; ++jj)
+                            chunk_mma<NB, NT, DUAL>(wa + jj * (NW * 16 * NB), wa + jj * (NW * 16 * NB) + 8 * RS,
+                                                    xptr + jj * NW * xchunk, xstep, acc, pc);
+                    }
+                }
+            } else {                                                    // the K-range ends inside this stage
+                for (int jj = 0; jj < cpw; ++jj)
+                    if (s * cps + jj * NW + warp < NC)
+                        chunk_mma<NB, NT, DUAL>(wa + jj * (NW * 16 * NB), wa + jj * (NW * 16 * NB) + 8 * RS,
+                                                xptr + jj * NW * xchunk, xstep, acc, pc);
+            }
+        }
+        xptr += (uint32_t)cps * xchunk;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(rp.empty);
+        ring_advance(rp, slot_bytes, nstg);
+    }
+    return true;
+}
+
+// X staging: 8 activations as saturated fp16 bit patterns, whatever the input type (runtime switch: the staging
+// loop is short, and one kernel serves the three input types)
+__device__ __forceinline__ void stage_x8_any(int x_dtype, const void *__restrict__ X, int64_t off, uint32_t (&h)[8]) {
+    if (x_dtype == QVB8_BF16) stage_x8<QVB8_BF16>(X, off, h);
+    else if (x_dtype == QVB8_F16) stage_x8<QVB8_F16>(X, off, h);
+    else stage_x8<QVB8_F32>(X, off, h);
+}
 
 // DUAL: a second activation layout is staged for widths that pair ids at distance 4 (cheap for few tokens).
-template <int XT, int NT, bool DUAL>
-__global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small_m_kernel(const SmallMParams p) {
+template <int NT, bool DUAL>
+__global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kernel(const SmallMParams p) {
+    constexpr int NPIPE = pipes_for(NT);
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ Control ctl;
-    constexpr int RED_FLOATS = NW * 4 * NT * 32;                       // one hand-over buffer (>= 16 * M floats)
+    constexpr int RED_FLOATS = NW * 4 * NT * 32;                       // a pipe's hand-over buffer (>= 16 * M floats)
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) trace(p.debug, 0);
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int pipe = tid / PIPE_THREADS, warp = (tid % PIPE_THREADS) >> 5;     // warp: role within the pipe
     const int split = blockIdx.y;
     const int kc0 = split * p.nc_per;                                  // first chunk of this K-range
     const int NC = min(p.nc_per, p.nc_total - kc0);                    // chunks in this K-range (>= 1 by construction)
-    const int NSK = (NC + NW - 1) / NW;                                // stages along K per tile
+    const int cps = p.cps;
+    const int NSK = (NC + cps - 1) / cps;                              // stages along K per tile
     const int MP = p.MP, M = p.M;
     const int nstg = p.nstg;
     // dynamic shared memory:
-    //   [ring: nstg x (16-row stage + descriptor)] [activations A] [activations B] [warp partials x NRED]
-    //   [16 zero bytes] [escape corrections]
+    //   [activations A] [activations B] [16 zero bytes, padded to 128]
+    //   per pipe: [ring: nstg stages of 16 rows] [side ring: NSIDE x (descriptor + escapes)] [hand-over buffer]
+    //             [escape corrections]
     const int xs_halves = p.nc_per * 16 * MP * 8;                      // halves per activation layout
-    __half *xs_a = reinterpret_cast<__half *>(smem + (size_t)nstg * SLOT_BYTES);
+    __half *xs_a = reinterpret_cast<__half *>(smem);
     __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
-    float *red = reinterpret_cast<float *>(xs_a + (DUAL ? 2 : 1) * xs_halves);     // [NRED][NW][4 * NT][32]
-    uint32_t *zero16 = reinterpret_cast<uint32_t *>(red + NRED * RED_FLOATS);
-    float *corr = reinterpret_cast<float *>(zero16 + 4);               // [16][M], private to the finishing warp
-    const bool planned = p.esc_col != nullptr;
+    uint32_t *zero16 = reinterpret_cast<uint32_t *>(xs_a + (DUAL ? 2 : 1) * xs_halves);
+    const size_t pipe_bytes = (size_t)nstg * p.slot_bytes + (size_t)NSIDE * SIDE_BYTES + (size_t)RED_FLOATS * 4 +
+                              (size_t)((16 * M * 4 + 127) / 128 * 128);
+    uint8_t *pbase = reinterpret_cast<uint8_t *>(zero16) + 128 + (size_t)pipe * pipe_bytes;
+    uint8_t *side = pbase + (size_t)nstg * p.slot_bytes;               // [NSIDE][SIDE_BYTES]
+    float *red = reinterpret_cast<float *>(side + NSIDE * SIDE_BYTES); // [NW][4 * NT][32]
+    float *corr = red + RED_FLOATS;                                    // [16][M], private to the finishing warp
+    PipeControl &pc_ = ctl.pipe[pipe];
+    const bool planned = p.esc_ent != nullptr;
     volatile int *abort_flag = &ctl.abort;
+    const bool tracer = (p.debug & 2) && pipe == 0;
 
-    if (tid == 0) {
+    if (tracer) trace(p.debug, 0);
+    if (tid < NPIPE) {
+        PipeControl &q = ctl.pipe[tid];
         for (int s = 0; s < nstg; ++s) {
-            mbar_init(smem_u32(&ctl.full[s]), 1);
-            mbar_init(smem_u32(&ctl.empty[s]), NW);
+            mbar_init(smem_u32(&q.full[s]), 1);
+            mbar_init(smem_u32(&q.empty[s]), NW);
         }
-        for (int b = 0; b < NRED; ++b) {
-            mbar_init(smem_u32(&ctl.red_full[b]), NW);
-            mbar_init(smem_u32(&ctl.red_empty[b]), 1);
+        for (int s = 0; s < NSIDE; ++s) {
+            mbar_init(smem_u32(&q.side_full[s]), 1);
+            mbar_init(smem_u32(&q.side_empty[s]), NW + 1);
         }
-        ctl.abort = 0;
+        mbar_init(smem_u32(&q.red_full), NW);
+        mbar_init(smem_u32(&q.red_empty), 1);
+        if (tid == 0) {
+            mbar_init(smem_u32(&ctl.x_ready), NW * NPIPE);
+            mbar_init(smem_u32(&ctl.sums_ready), NPIPE);
+            ctl.abort = 0;
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (tid < 4) zero16[tid] = 0u;
+    if (tid >= 32 && tid < 36) zero16[tid - 32] = 0u;
+    if (tid >= 64 && tid < 64 + PAIR_TABLE_WORDS) ctl.pair_table[tid - 64] = pair_const_word(3 + ((tid - 64) >> 2), (tid - 64) & 3);
     __syncthreads();
+    pdl_launch_dependents();                                            // what follows in the stream may start its own prologue
+    if (tracer) trace(p.debug, 1);
     const int ntiles = __ldg(p.ntiles_ptr);
-    const int tstep = gridDim.x;
-    if (tid == 0) trace(p.debug, 1);
+    // this pipe's run of (tile, stage) units; pipe-major numbering spreads a short list over all SMs first
+    const int npipes = gridDim.x * NPIPE;
+    const int pipe_id = pipe * gridDim.x + blockIdx.x;
+    const int L = run_length(ntiles, NSK, npipes);
+    const long long total_units = (long long)ntiles * NSK;
+    const long long u0l = (long long)pipe_id * L;
+    const int u0 = (int)(u0l < total_units ? u0l : total_units);
+    const int u1 = (int)(u0l + L < total_units ? u0l + L : total_units);
+    const Run run = make_run(u0, u1, NSK);
+    RingPos rp;
+    rp.full = smem_u32(&pc_.full[0]); rp.empty = smem_u32(&pc_.empty[0]); rp.data = smem_u32(pbase);
+    rp.slot = 0; rp.phase = 0;
+    const uint32_t side_full0 = smem_u32(&pc_.side_full[0]), side_empty0 = smem_u32(&pc_.side_empty[0]);
 
     if (warp == PRODUCER_WARP) {
-        // ================= producer warp: lane r copies row r of every stage; lane 16 the tile's descriptor ===========
-        int slot = 0;
-        uint32_t phase = 0;
+        // ================= producer warp: per visit, lane 16 copies the tile's descriptor and lane 17 its escapes into
+        // a side slot; per stage, lane r copies row r =================
         bool alive = true;
-        int tile = blockIdx.x;
-        int nb = 0, cnt = 0;
+        int nb = 0, cnt = 0, esc0 = 0, nesc = 0;
         uint32_t b16 = 0;
-        auto fetch = [&](int t) {
-            if (t < ntiles) {
-                nb = __ldg(&p.tiles[t].nb);
-                cnt = __ldg(&p.tiles[t].cnt);
-                b16 = lane < 16 ? __ldg(&p.tiles[t].b16[lane]) : 0u;
+        auto fetch = [&](int i) {
+            if (i < run.nv) {
+                const TileDesc *d = p.tiles + run_visit(run, i).tile;
+                nb = __ldg(&d->nb);
+                cnt = __ldg(&d->cnt);
+                esc0 = __ldg(&d->esc0);
+                nesc = __ldg(&d->nesc);
+                b16 = lane < 16 ? __ldg(&d->b16[lane]) : 0u;
             }
         };
-        fetch(tile);
-        bool first = true;
-        while (tile < ntiles && alive) {
-            const int cur = tile, cnb = nb, ccnt = cnt;
-            if (first) trace(p.debug, 2);
-            const uint8_t *src = p.ids + ((uint64_t)b16 + (uint64_t)kc0 * cnb) * 16u;
-            tile += tstep;
-            fetch(tile);                                                // next descriptor loads while this tile is issued
-            const uint32_t dst_row = (uint32_t)(lane * stage_row_stride(cnb ? cnb : 8));
-            const int nstages = cnb ? NSK : 1;
-            for (int s = 0; s < nstages; ++s) {
-                const int chunks = min(NW, NC - s * NW);
-                const uint32_t bytes_row = cnb ? (uint32_t)(chunks * 16 * cnb) : 0u;
-                const uint32_t full = smem_u32(&ctl.full[slot]);
-                if (!mbar_wait(smem_u32(&ctl.empty[slot]), phase ^ 1u, abort_flag, 1)) { alive = false; break; }
-                if (lane == 0) mbar_expect_tx(full, bytes_row * (uint32_t)ccnt + (s == 0 ? (uint32_t)DESC_BYTES : 0u));
+        fetch(0);
+        if (tracer) trace(p.debug, 2);
+        const bool nocopy = (p.debug & 4) != 0;
+        for (int i = 0; i < run.nv && alive; ++i) {
+            const Visit v = run_visit(run, i);
+            const int cnb = nb, ccnt = cnt;
+            const uint32_t ebytes = planned ? (uint32_t)(min((nesc + 1) & ~1, ESC_CAP) * 8) : 0u;
+            const EscEntry *esrc = p.esc_ent + esc0;
+            const uint32_t step = (uint32_t)(cps * 16 * cnb);           // bytes of a row per full stage
+            const uint8_t *src = p.ids + ((uint64_t)b16 + (uint64_t)kc0 * cnb) * 16u + (size_t)v.sb * step;
+            fetch(i + 1);                                               // next descriptor loads while this visit is issued
+            // descriptor and escapes
+            const int sslot = i % NSIDE;
+            if (!mbar_wait(side_empty0 + 8 * sslot, ((i / NSIDE) & 1) ^ 1u, abort_flag, 7)) { alive = false; break; }
+            const uint32_t sfull = side_full0 + 8 * sslot, sdst = smem_u32(side + sslot * SIDE_BYTES);
+            if (lane == 0) mbar_expect_tx(sfull, (uint32_t)DESC_BYTES + ebytes);
+            __syncwarp();
+            if (lane == 16) bulk_g2s(sdst, p.tiles + v.tile, DESC_BYTES, sfull);
+            if (lane == 17 && ebytes) bulk_g2s(sdst + DESC_SLOT, esrc, ebytes, sfull);
+            // rows (a per-element tile has none: its rows are read from global memory)
+            const uint32_t dst_row = (uint32_t)(lane * (cnb ? p.rs[cnb - 3] : 0));
+            const int s_end = cnb ? v.se : v.sb;
+            for (int s = v.sb; s < s_end; ++s) {
+                const int chunks = min(cps, NC - s * cps);
+                const uint32_t bytes_row = nocopy ? 0u : (uint32_t)(chunks * 16 * cnb);
+                if (!mbar_wait(rp.empty, rp.phase ^ 1u, abort_flag, 1)) { alive = false; break; }
+                if (lane == 0) mbar_expect_tx(rp.full, bytes_row * (uint32_t)ccnt);
                 __syncwarp();
-                const uint32_t slot32 = smem_u32(smem + (size_t)slot * SLOT_BYTES);
-                if (cnb && lane < ccnt) bulk_g2s(slot32 + dst_row, src + (size_t)s * NW * 16 * cnb, bytes_row, full);
-                if (s == 0 && lane == 16) bulk_g2s(slot32 + STAGE_BYTES, p.tiles + cur, DESC_BYTES, full);
-                if (first) { trace(p.debug, 3); first = false; }
-                if (++slot == nstg) { slot = 0; phase ^= 1u; }
+                if (bytes_row && lane < ccnt) bulk_g2s(rp.data + dst_row, src, bytes_row, rp.full);
+                src += step;
+                if (tracer && i == 0 && s == v.sb) trace(p.debug, 3);
+                ring_advance(rp, (uint32_t)p.slot_bytes, nstg);
             }
         }
+        // nothing may be in flight when the CTA exits: wait until every issued stage and side slot has been consumed
+        for (int s = 0; s < nstg && alive; ++s) {
+            alive = mbar_wait(rp.empty, rp.phase ^ 1u, abort_flag, 1);
+            ring_advance(rp, (uint32_t)p.slot_bytes, nstg);
+        }
+        for (int k = 0; k < NSIDE && alive; ++k) {
+            const int i = run.nv + k;                                   // as if about to reuse the slot
+            alive = mbar_wait(side_empty0 + 8 * (i % NSIDE), ((i / NSIDE) & 1) ^ 1u, abort_flag, 7);
+        }
+        if (!alive) {
+            // a wait gave up somewhere: copies may still be in flight towards this CTA's shared memory; keep the CTA
+            // resident until any such copy (a few kilobytes at most) has certainly landed
+            const uint64_t t0 = global_ns();
+            while (global_ns() - t0 < 200000ull) {}
+        }
     } else if (warp == FINISHER_WARP) {
-        // ================= finishing warp: per tile, sums the escape corrections of its rows while the tile streams,
+        // ================= finishing warp: per visit, sums the escape corrections of its rows while the stages stream,
         // then takes the consumer warps' partial sums, scales, corrects and writes the rows =================
-        asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // activations staged, sums ready
         const int g = lane >> 2, t = lane & 3;
-        const int clo = kc0 * KC, chi = clo + NC * KC;
-        float *out = p.S > 1 ? p.part + (int64_t)split * M * p.Q : p.Y;
-        // descriptor fields of the next tile, prefetched: rows g, g+8 (fragment owner) and row `lane` (escapes)
-        int nb = 0, frow[2] = {-1, -1}, erow = -1, e0 = 0, e1 = 0;
-        float fms[2] = {0.f, 0.f}, fts[2] = {0.f, 0.f};
-        auto fetch = [&](int tl) {
-            if (tl < ntiles) {
-                const TileDesc *d = p.tiles + tl;
-                nb = __ldg(&d->nb);
+        // per-token sums of the narrowed activations (fixed order: same bits every run); the pipes share the work
+        bool alive = mbar_wait(smem_u32(&ctl.x_ready), 0, abort_flag, 5);      // every consumer warp has staged its part
+        for (int m = pipe; m < M; m += NPIPE) {
+            float sacc = 0.f;
+            for (int j = lane; j < NC * 16; j += 32) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(xs_a + ((size_t)(j * MP + m) << 3));
+                const __half2 *hp = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(hp[k]); sacc += f.x; sacc += f.y; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
+            if (lane == 0) ctl.sumx[m] = sacc;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl.sums_ready));
+        if (alive) alive = mbar_wait(smem_u32(&ctl.sums_ready), 0, abort_flag, 6);
+        for (int i = 0; i < run.nv; ++i) {
+            const Visit v = run_visit(run, i);
+            // ---- the tile's descriptor and escapes arrive in a side slot
+            const int sslot = i % NSIDE;
+            if (alive) alive = mbar_wait(side_full0 + 8 * sslot, (i / NSIDE) & 1, abort_flag, 8);
+            const TileDesc *d = reinterpret_cast<const TileDesc *>(side + sslot * SIDE_BYTES);
+            const EscEntry *ent = reinterpret_cast<const EscEntry *>(side + sslot * SIDE_BYTES + DESC_SLOT);
+            int cnb = 0, myrow[2] = {-1, -1};
+            float myms[2] = {0.f, 0.f}, myts[2] = {0.f, 0.f};
+            if (alive) {
+                cnb = d->nb;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    frow[h] = __ldg(&d->row[g + 8 * h]);
-                    fms[h] = __ldg(&d->ms[g + 8 * h]);
-                    fts[h] = __ldg(&d->ts[g + 8 * h]);
+                    myrow[h] = d->row[g + 8 * h];
+                    myms[h] = d->ms[g + 8 * h];
+                    myts[h] = d->ts[g + 8 * h];
                 }
-                if (lane < 16) { erow = __ldg(&d->row[lane]); e0 = __ldg(&d->e0[lane]); e1 = __ldg(&d->e1[lane]); }
             }
-        };
-        int tile = blockIdx.x, count = 0;
-        bool alive = true;
-        fetch(tile);
-        while (tile < ntiles) {
-            const int cur = tile, cnb = nb, crow = lane < 16 ? erow : -1, ce0 = e0, ce1 = e1;
-            const int myrow[2] = {frow[0], frow[1]};
-            const float myms[2] = {fms[0], fms[1]}, myts[2] = {fts[0], fts[1]};
-            tile += tstep;
-            fetch(tile);
-            // ---- escapes: lane r sums row r's corrections x * (exact - band), in stored order, over this K-range
-            if (planned) {
-                if (crow >= 0) {
+            // ---- escapes: lane r sums row r's corrections x * (exact - band), in stored order, over the visit's columns
+            if (planned && alive) {
+                const int clo = (kc0 + v.sb * cps) * KC, chi = (kc0 + min(v.se * cps, NC)) * KC, cbase = kc0 * KC;
+                if (lane < 16 && d->row[lane] >= 0) {
+                    const int ce0 = d->e0[lane], ce1 = d->e1[lane];
+                    const EscEntry *gent = p.esc_ent + d->esc0;         // the same list in global memory (for the overflow)
                     float *dst = corr + lane * M;
                     for (int m0 = 0; m0 < M; m0 += 8) {
                         float a[8];
 #pragma unroll
                         for (int k = 0; k < 8; ++k) a[k] = 0.f;
-                        for (int e = ce0; e < ce1; e += 4) {
-                            int c[4];
-                            float dl[4];
+                        for (int e = ce0; e < ce1; ++e) {
+                            EscEntry en;
+                            if (e < ESC_CAP) en = ent[e];
+                            else { en.col = __ldg(&gent[e].col); en.delta = __ldg(&gent[e].delta); }
+                            if (en.col >= clo && en.col < chi) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {                   // four independent loads in flight
-                                const bool ok = e + j < ce1;
-                                c[j] = ok ? __ldg(p.esc_col + e + j) : -1;
-                                dl[j] = ok ? __ldg(p.esc_delta + e + j) : 0.f;
-                            }
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                if (c[j] >= clo && c[j] < chi) {
-#pragma unroll
-                                    for (int k = 0; k < 8; ++k)
-                                        if (m0 + k < M) a[k] = __fmaf_rn(xs_read(xs_a, c[j] - clo, m0 + k, MP), dl[j], a[k]);
-                                }
+                                for (int k = 0; k < 8; ++k)
+                                    if (m0 + k < M) a[k] = __fmaf_rn(xs_read(xs_a, en.col - cbase, m0 + k, MP), en.delta, a[k]);
                             }
                         }
 #pragma unroll
@@ -657,26 +922,46 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
                             if (m0 + k < M) dst[m0 + k] = a[k];
                     }
                 }
-                __syncwarp();
             }
-            if (count == 0) trace(p.debug, 9);
-            // ---- the consumer warps' partial sums (or, for a per-element tile, complete row results)
-            const int buf = count % NRED;
-            if (alive) alive = mbar_wait(smem_u32(&ctl.red_full[buf]), (count / NRED) & 1, abort_flag, 3);
-            if (count == 0) trace(p.debug, 10);
-            const float *rbuf = red + (size_t)buf * RED_FLOATS;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(side_empty0 + 8 * sslot);        // done with the side slot
+            if (tracer && i == 0) trace(p.debug, 9);
+            // ---- the consumer warps' partial sums (or, for a per-element tile, complete row results): taken into
+            // registers and the buffer handed straight back
+            if (alive) alive = mbar_wait(smem_u32(&pc_.red_full), i & 1, abort_flag, 3);
+            if (tracer && i == 0) trace(p.debug, 10);
             float acc[NT][4];
-            if (cnb != 0) {
 #pragma unroll
-                for (int n = 0; n < NT; ++n)
+            for (int n = 0; n < NT; ++n)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        float v = 0.f;
+                for (int k = 0; k < 4; ++k) {
+                    float a = 0.f;
+                    if (cnb != 0) {
 #pragma unroll
-                        for (int w = 0; w < NW; ++w) v += rbuf[(w * 4 * NT + n * 4 + k) * 32 + lane];
-                        acc[n][k] = v;
+                        for (int w = 0; w < NW; ++w) a += red[(w * 4 * NT + n * 4 + k) * 32 + lane];
+                    } else {
+                        // k = 2 * hrow + kk  ->  row g + 8 * hrow, token 8n + 2t + kk
+                        const int m = 8 * n + 2 * t + (k & 1);
+                        if (m < M) a = red[(g + 8 * (k >> 1)) * M + m];
                     }
+                    acc[n][k] = a;
+                }
+            __syncwarp();                                               // every lane is done with the buffer
+            if (lane == 0) mbar_arrive(smem_u32(&pc_.red_empty));
+            // a visit that covers its tile alone writes the result; otherwise it writes a partial result and whichever
+            // visit of the tile finishes last adds them up in a fixed order (K-range, then pipe)
+            const bool whole = p.S == 1 && v.sb == 0 && v.se == NSK;
+            int slot = 0, expected = 1;
+            if (!whole) {
+                expected = 0;
+                for (int r = 0; r < p.S; ++r) {
+                    const int ncr = min(p.nc_per, p.nc_total - r * p.nc_per), nskr = (ncr + cps - 1) / cps;
+                    const int Lr = run_length(ntiles, nskr, npipes);
+                    if (r == split) slot = expected + pipe_id - (v.tile * nskr) / Lr;
+                    expected += visits_of_tile(v.tile, nskr, Lr);
+                }
             }
+            float *out = whole ? p.Y : p.part + (int64_t)slot * M * p.Q;
             // thread holds rows g, g+8 of the tile and tokens 8n+2t, 8n+2t+1
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
@@ -685,25 +970,26 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const int m = 8 * n + 2 * t + k;
-                        float y = 0.f;
                         if (myrow[hrow] >= 0 && m < M) {
-                            // y = tau_s * sum(x * id) + min_s * sum(x)   (per-element rows arrive complete)
-                            y = cnb != 0 ? __fmaf_rn(myts[hrow], acc[n][2 * hrow + k], myms[hrow] * ctl.sumx[m])
-                                         : rbuf[(g + 8 * hrow) * M + m];
+                            // y = tau_s * sum(x * id) + min_s * sum(x)   (per-element rows arrive complete); the
+                            // min_s term of a K-range goes with the visit that holds the range's first stage
+                            float y = acc[n][2 * hrow + k];
+                            if (cnb != 0) {
+                                y *= myts[hrow];
+                                if (v.sb == 0) y = __fmaf_rn(myms[hrow], ctl.sumx[m], y);
+                            }
                             if (planned) y += corr[(g + 8 * hrow) * M + m];
                             out[(int64_t)m * p.Q + myrow[hrow]] = y;
                         }
                     }
                 }
             }
-            __syncwarp();                                               // every lane is done with red[buf] and corr
-            if (lane == 0) mbar_arrive(smem_u32(&ctl.red_empty[buf]));
-            if (count == 0) trace(p.debug, 11);
-            if (p.S > 1) {
-                // K-ranges: whichever CTA finishes this tile last adds the partial sums in range order
+            __syncwarp();                                               // every lane is done with corr
+            if (tracer && i == 0) trace(p.debug, 11);
+            if (!whole && alive) {
                 __threadfence();
                 int last = 0;
-                if (lane == 0) last = atomicAdd(p.ticket + cur, 1) == p.S - 1;
+                if (lane == 0) last = atomicAdd(p.ticket + v.tile, 1) == expected - 1;
                 last = __shfl_sync(0xffffffffu, last, 0);
                 if (last) {
                     __threadfence();
@@ -718,113 +1004,92 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
                                 if (m < M) {
                                     const int64_t o = (int64_t)m * p.Q + myrow[hrow];
                                     float s = 0.f;
-                                    for (int r = 0; r < p.S; ++r) s += __ldcg(p.part + (int64_t)r * M * p.Q + o);
+                                    for (int r = 0; r < expected; ++r) s += __ldcg(p.part + (int64_t)r * M * p.Q + o);
                                     p.Y[o] = s;
                                 }
                             }
                         }
                     }
-                    if (lane == 0) p.ticket[cur] = 0;
+                    if (lane == 0) p.ticket[v.tile] = 0;
                 }
             }
-            if (count == 0) trace(p.debug, 12);
-            ++count;
+            if (tracer && i == 0) trace(p.debug, 12);
         }
-        trace(p.debug, 13);
+        if (tracer) trace(p.debug, 13);
     } else {
         // ================= consumer warps =================
-        // ---- activations of this K-range as fp16 in fragment order (after the previous kernel in the stream)
+        // ---- activations of the K-range as fp16 in fragment order (after the previous kernel in the stream): all
+        // consumer warps of the CTA share the work, every one of them reads all of it afterwards
         pdl_wait();
-        if (warp == 0) trace(p.debug, 4);
+        if (tracer && warp == 0) trace(p.debug, 4);
         {
             const int groups = NC * 16;                                 // 8-column groups in the range
-            const int64_t col0 = (int64_t)kc0 * KC;
             const int total = MP * groups;
+            const int64_t col0 = (int64_t)kc0 * KC;
+            const int ctid = (pipe * NW + warp) * 32 + lane;            // index among the consumer threads
+            constexpr int CTHREADS = NPIPE * NW * 32;
             constexpr int UNR = 4;                                      // loads in flight per thread
-            for (int base = tid; base < total; base += NW * 32 * UNR) {
+            const int x_dtype = p.x_dtype;
+            for (int base = ctid; base < total; base += CTHREADS * UNR) {
                 uint32_t h[UNR][8];
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) {
-                    const int idx = base + u * NW * 32;
-                    const int m = idx / groups, u8 = idx - m * groups; // u8: natural 8-column group number
+                for (int i = 0; i < UNR; ++i) {
+                    const int idx = base + i * CTHREADS;
+                    const int m = idx / groups, u8 = idx - m * groups;  // u8: natural 8-column group number
                     if (idx < total && m < M) {
-                        stage_x8<XT>(p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h[u]);
+                        stage_x8_any(x_dtype, p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h[i]);
                     } else {
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) h[u][k] = 0u;
+                        for (int j = 0; j < 8; ++j) h[i][j] = 0u;
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < UNR; ++u) {
-                    const int idx = base + u * NW * 32;
+                for (int i = 0; i < UNR; ++i) {
+                    const int idx = base + i * CTHREADS;
                     if (idx >= total) continue;
                     const int m = idx / groups, u8 = idx - m * groups;
                     const int sl = slot_of(u8 * 8, m, MP);
                     *reinterpret_cast<uint4 *>(xs_a + (sl << 3)) = make_uint4(
-                        h[u][0] | (h[u][2] << 16), h[u][1] | (h[u][3] << 16), h[u][4] | (h[u][6] << 16), h[u][5] | (h[u][7] << 16));
+                        h[i][0] | (h[i][2] << 16), h[i][1] | (h[i][3] << 16), h[i][4] | (h[i][6] << 16), h[i][5] | (h[i][7] << 16));
                     if (DUAL)
                         *reinterpret_cast<uint4 *>(xs_b + (sl << 3)) = make_uint4(
-                            h[u][0] | (h[u][4] << 16), h[u][1] | (h[u][5] << 16), h[u][2] | (h[u][6] << 16), h[u][3] | (h[u][7] << 16));
+                            h[i][0] | (h[i][4] << 16), h[i][1] | (h[i][5] << 16), h[i][2] | (h[i][6] << 16), h[i][3] | (h[i][7] << 16));
                 }
             }
-            consumer_sync();
-            // per-token sums of the narrowed activations, in a fixed order: thread -> every 128th slot, then a fixed
-            // tree over the 128 threads (same bits every run)
-            float *psum = red;                                          // 128 floats of the hand-over area, free until the first tile ends
-            for (int m = 0; m < M; ++m) {
-                float sacc = 0.f;
-                for (int j = tid; j < groups; j += NW * 32) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(xs_a + ((size_t)(j * MP + m) << 3));
-                    const __half2 *hp = reinterpret_cast<const __half2 *>(&v);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(hp[k]); sacc += f.x; sacc += f.y; }
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
-                if (lane == 0) psum[m * NW + warp] = sacc;
-            }
-            consumer_sync();
-            if (tid < M) {
-                float sacc = 0.f;
-#pragma unroll
-                for (int w = 0; w < NW; ++w) sacc += psum[tid * NW + w];
-                ctl.sumx[tid] = sacc;
-            }
-            asm volatile("bar.sync 2, %0;\n" ::"n"((NW + 1) * 32) : "memory");     // consumers + finishing warp
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl.x_ready));
         }
-        pdl_launch_dependents();
-        if (warp == 0) trace(p.debug, 5);
+        bool alive = mbar_wait(smem_u32(&ctl.x_ready), 0, abort_flag, 5);
+        if (tracer && warp == 0) trace(p.debug, 5);
 
-        // ---- walk the tiles
+        // ---- walk the run
         const int g = lane >> 2, t = lane & 3;
         const bool xvalid = NT > 1 || g < MP;                           // lanes whose token slot exists
         const uint32_t xstep = xvalid ? (uint32_t)(4 * MP * 16) : 0u;   // bytes between consecutive 8-column groups
-        const uint32_t xchunk = 4 * xstep;                              // bytes per chunk
         const uint32_t xoff = (uint32_t)((t * MP + g) * 16);
         const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
         const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
-        const uint32_t ring32 = smem_u32(smem);
-        int slot = 0, count = 0;
-        uint32_t phase = 0;
-        bool alive = true;
-        for (int tile = blockIdx.x; tile < ntiles; tile += tstep, ++count) {
-            // the tile's first stage carries its descriptor
-            if (alive) alive = mbar_wait(smem_u32(&ctl.full[slot]), phase, abort_flag, 2);
-            if (warp == 0 && count == 0) trace(p.debug, 6);
-            const TileDesc *d = reinterpret_cast<const TileDesc *>(smem + (size_t)slot * SLOT_BYTES + STAGE_BYTES);
-            const int nb = alive ? d->nb : 0, cnt = alive ? d->cnt : 0;
-            const int buf = count % NRED;
-            const uint32_t red_par = ((count / NRED) & 1) ^ 1u;        // the finishing warp has released red[buf]
-            float *rbuf = red + (size_t)buf * RED_FLOATS;
+        const uint32_t red_full = smem_u32(&pc_.red_full), red_empty = smem_u32(&pc_.red_empty);
+        const int cpw = cps / NW;
+        for (int i = 0; i < run.nv && alive; ++i) {
+            const Visit v = run_visit(run, i);
+            // the tile's descriptor arrives in a side slot
+            const int sslot = i % NSIDE;
+            if (!mbar_wait(side_full0 + 8 * sslot, (i / NSIDE) & 1, abort_flag, 8)) { alive = false; break; }
+            if (tracer && warp == 0 && i == 0) trace(p.debug, 6);
+            const TileDesc *d = reinterpret_cast<const TileDesc *>(side + sslot * SIDE_BYTES);
+            const int nb = d->nb, cnt = d->cnt;
+            const uint32_t red_par = (i & 1) ^ 1u;                      // the finishing warp has taken the previous visit's sums
             float acc[NT][4];
 #pragma unroll
             for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
             if (nb == 0) {
                 // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
                 // start on a 16-byte boundary).  One row per warp at a time, ids byte-wise from global memory; the
-                // stage holds only the descriptor.
-                if (alive) alive = mbar_wait(smem_u32(&ctl.red_empty[buf]), red_par, abort_flag, 4);
-                float *rr_out = rbuf;                                   // [16][M] complete row results
+                // ring is not used.
+                if (!mbar_wait(red_empty, red_par, abort_flag, 4)) { alive = false; break; }
+                float *rr_out = red;                                    // [16][M] complete row results
+                const int c_lo = v.sb * cps * KC, c_hi = min(v.se * cps, NC) * KC;
                 for (int rr = warp; rr < cnt; rr += NW) {
                     const int q = d->row[rr];
                     const float ms = d->ms[rr], ts = d->ts[rr];
@@ -834,7 +1099,7 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
                         float a[8];
 #pragma unroll
                         for (int k = 0; k < 8; ++k) a[k] = 0.f;
-                        for (int c = lane; c < NC * KC; c += 32) {
+                        for (int c = c_lo + lane; c < c_hi; c += 32) {
                             const float wv = band(field_bytes(p.ids, base + (int64_t)c * rnb, rnb), ts, ms);
 #pragma unroll
                             for (int k = 0; k < 8; ++k)
@@ -849,44 +1114,38 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
                     }
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl.empty[slot]));
-                if (++slot == nstg) { slot = 0; phase ^= 1u; }
+                if (lane == 0) mbar_arrive(side_empty0 + 8 * sslot);
             } else {
-                const int RS = stage_row_stride(nb);
-                const uint32_t wa_off = (uint32_t)(g * RS + warp * 16 * nb + t * 4 * nb), wb_off = wa_off + 8 * RS;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(side_empty0 + 8 * sslot);    // only the width was needed
                 const uint32_t xbase = (nb >= 6 || !DUAL) ? xs_a32 : xs_b32;
-                for (int s = 0; s < NSK; ++s) {
-                    if (s > 0 && alive) alive = mbar_wait(smem_u32(&ctl.full[slot]), phase, abort_flag, 2);
-                    const int chunk = s * NW + warp;
-                    if (alive && chunk < NC && !(p.debug & 1)) {
-                        const uint32_t stage = ring32 + (uint32_t)slot * SLOT_BYTES;
-                        const uint32_t xa = xbase + chunk * xchunk;
-                        switch (nb) {                                   // CTA-uniform
-                            case 7: chunk_mma<7, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                            case 6: chunk_mma<6, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                            case 8: chunk_mma<8, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                            case 5: chunk_mma<5, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                            case 4: chunk_mma<4, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                            case 3: chunk_mma<3, NT, DUAL>(stage + wa_off, stage + wb_off, xa, xstep, acc); break;
-                            default: break;
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl.empty[slot]));
-                    if (++slot == nstg) { slot = 0; phase ^= 1u; }
+                bool ok;
+#define QV_STREAM(NB_)                                                                                                    \
+    ok = cpw == 2 ? stream_tile<NB_, NT, DUAL, 2>(p, ctl.pair_table, abort_flag, rp, NC, v.sb, v.se, warp, lane, xbase, xstep, acc) \
+       : cpw == 4 ? stream_tile<NB_, NT, DUAL, 4>(p, ctl.pair_table, abort_flag, rp, NC, v.sb, v.se, warp, lane, xbase, xstep, acc) \
+                  : stream_tile<NB_, NT, DUAL, 0>(p, ctl.pair_table, abort_flag, rp, NC, v.sb, v.se, warp, lane, xbase, xstep, acc)
+                switch (nb) {                                           // uniform over the pipe
+                    case 7: QV_STREAM(7); break;
+                    case 6: QV_STREAM(6); break;
+                    case 8: QV_STREAM(8); break;
+                    case 5: QV_STREAM(5); break;
+                    case 4: QV_STREAM(4); break;
+                    default: QV_STREAM(3); break;
                 }
-                // hand the partial sums to the finishing warp and go on with the next tile
-                if (alive) alive = mbar_wait(smem_u32(&ctl.red_empty[buf]), red_par, abort_flag, 4);
+#undef QV_STREAM
+                if (!ok) { alive = false; break; }
+                // hand the partial sums to the finishing warp and go on with the next visit
+                if (!mbar_wait(red_empty, red_par, abort_flag, 4)) { alive = false; break; }
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) rbuf[(warp * 4 * NT + n * 4 + k) * 32 + lane] = acc[n][k];
+                    for (int k = 0; k < 4; ++k) red[(warp * 4 * NT + n * 4 + k) * 32 + lane] = acc[n][k];
             }
+            if (tracer && warp == 0 && i == 0) trace(p.debug, 7);
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl.red_full[buf]));
-            if (warp == 0 && count == 0) trace(p.debug, 7);
+            if (lane == 0) mbar_arrive(red_full);
         }
-        if (warp == 0) trace(p.debug, 8);
+        if (tracer && warp == 0) trace(p.debug, 8);
     }
 }
 
@@ -894,7 +1153,8 @@ __global__ void __launch_bounds__(NTHREADS, NT == 1 ? 4 : NT == 2 ? 2 : 1) small
 // host side
 
 struct Plan {
-    int ctas_x, S, nc_per, nc_total, MP, NT, nstg;
+    int ctas_x, S, nc_per, nc_total, MP, NT, nstg, cps, part_slots;
+    int rs[6], slot_bytes;
     bool dual;
     size_t smem_bytes;
     int64_t part_bytes, ticket_bytes;
@@ -911,57 +1171,83 @@ static int device_sms() {
     return n;
 }
 
+// Dynamic shared memory of a CTA: 227 KB per block on this architecture, less one kilobyte for the static part.
+constexpr int64_t MAX_DYN_SMEM = 227 * 1024 - 1024;
+static_assert(sizeof(Control) <= 1024 - 64, "static shared memory allowance");
+
 // tuning hooks (qvb8_small_m_set_tuning): 0 = choose automatically
-static int g_fill_pct = 0, g_force_s = 0, g_force_nstg = 0, g_debug = 0;
+static int g_fill_pct = 0, g_force_s = 0, g_force_nstg = 0, g_force_cps = 0, g_debug = 0;
 
 static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     Plan pl{};
     pl.nc_total = (int)(P / KC);
     pl.NT = (int)((M + 7) / 8);
     pl.MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * pl.NT;
-    const int per_sm = pl.NT == 1 ? 4 : pl.NT == 2 ? 2 : 1;             // resident CTAs per SM the kernel is built for
-    // K-range length: bounded by the shared memory the staged activations may take.  The second activation layout
-    // (no byte permutes for widths 3..5) is staged only when it does not shorten the K-range.
-    const int xs_budget = pl.NT == 1 ? 16 * 1024 : pl.NT == 2 ? 32 * 1024 : 96 * 1024;
-    pl.dual = pl.MP <= 4 && (int64_t)P * pl.MP * 2 * 2 <= xs_budget;
+    const int npipe = pipes_for(pl.NT);                                 // one CTA per SM, npipe pipes in it
+    const int64_t cta_bytes = MAX_DYN_SMEM - 256;                       // dynamic shared memory a CTA may take
+    // chunks per stage: long stages mean few, large copies (what the copy engine and HBM like); short K -> short stages
+    int cps = g_force_cps ? g_force_cps : (pl.nc_total >= 16 ? 8 : 4);
+    cps = cps / NW * NW;
+    if (cps < NW) cps = NW;
+    if (cps > MAX_CPS) cps = MAX_CPS;
+    pl.cps = cps;
+    pl.slot_bytes = 0;                                                  // a ring slot: 16 rows of the widest width
+    for (int nb = 3; nb <= 8; ++nb) {
+        pl.rs[nb - 3] = stage_row_stride(nb, cps);
+        if (16 * pl.rs[nb - 3] > pl.slot_bytes) pl.slot_bytes = 16 * pl.rs[nb - 3];
+    }
+    // per pipe next to its ring: side ring, hand-over buffer, escape corrections
+    const int64_t pipe_fixed = (int64_t)NSIDE * SIDE_BYTES + (int64_t)NW * 4 * pl.NT * 32 * 4 + (16 * M * 4 + 127) / 128 * 128;
+    // K-range length: what is left of the CTA's shared memory, after every pipe has a ring of three stages, holds the
+    // staged activations.  The second activation layout (no byte permutes for widths 3..5) is staged only when it
+    // does not shorten the K-range or the rings.
+    const int min_stages = cps > 8 ? 2 : 3;
+    const int64_t xs_budget = cta_bytes - 128 - npipe * (pipe_fixed + (int64_t)min_stages * pl.slot_bytes);
+    const int64_t xs_one = (int64_t)P * pl.MP * 2;
+    pl.dual = pl.MP <= 4 && cta_bytes - 128 - npipe * (pipe_fixed + (int64_t)(min_stages + 1) * pl.slot_bytes) >= 2 * xs_one;
     const int layouts = pl.dual ? 2 : 1;
-    int nc_max = xs_budget / (KC * pl.MP * 2 * layouts);
-    if (nc_max >= NW) nc_max = nc_max / NW * NW;                        // whole stages
+    int nc_max = xs_budget > 0 ? (int)(xs_budget / (KC * pl.MP * 2 * layouts)) : 0;
+    if (nc_max >= cps) nc_max = nc_max / cps * cps;                     // whole stages
+    else if (nc_max >= NW) nc_max = nc_max / NW * NW;
     if (nc_max < 1) nc_max = 1;
     const int s_xs = (pl.nc_total + nc_max - 1) / nc_max;
-    // CTAs: one resident wave (persistent CTAs walk the tiles); few tiles -> split K further, down to one stage
+    // one CTA per SM at most; K is split only when the activations of a whole row do not fit
     const int max_tiles = (int)((Q + 15) / 16 + NCLASS - 1);
-    int64_t slots = (int64_t)per_sm * device_sms() * (g_fill_pct ? g_fill_pct : 100) / 100;
-    if (slots < 1) slots = 1;
-    const int s_cap = pl.nc_total / NW > 0 ? pl.nc_total / NW : 1;
-    int S = s_xs;
-    if ((int64_t)max_tiles * S < slots) {
-        S = (int)((slots + max_tiles - 1) / max_tiles);
-        if (S > s_cap) S = s_cap;
-        if (S < s_xs) S = s_xs;
-    }
+    int64_t ctas = (int64_t)device_sms() * (g_fill_pct ? g_fill_pct : 100) / 100;
+    if (ctas < 1) ctas = 1;
+    int S = s_xs;                                                       // the run division balances the pipes by itself
     if (g_force_s) S = g_force_s > s_xs ? g_force_s : s_xs;
     if (S > pl.nc_total) S = pl.nc_total;
-    if (max_tiles > MAX_TICKET_TILES) S = s_xs;                         // more tiles than counters: no extra split
     pl.nc_per = (pl.nc_total + S - 1) / S;
-    if (pl.nc_per > NW) pl.nc_per = (pl.nc_per + NW - 1) / NW * NW;     // K-ranges of whole stages
+    if (pl.nc_per > cps) pl.nc_per = (pl.nc_per + cps - 1) / cps * cps; // K-ranges of whole stages
     if (pl.nc_per > nc_max) pl.nc_per = nc_max;
     pl.S = (pl.nc_total + pl.nc_per - 1) / pl.nc_per;                   // no empty range
-    int64_t cx = slots / pl.S;
+    int64_t cx = ctas / pl.S;
     if (cx < 1) cx = 1;
-    if (cx > max_tiles) cx = max_tiles;
+    {
+        const int nsk = (pl.nc_per + cps - 1) / cps;
+        const int64_t need = ((int64_t)max_tiles * nsk + npipe - 1) / npipe;   // CTAs that give every unit a pipe of its own
+        if (cx > need) cx = need;
+    }
     pl.ctas_x = (int)cx;
-    const size_t xs_bytes = (size_t)pl.nc_per * KC * pl.MP * 2 * layouts;
-    const size_t red_bytes = (size_t)NRED * NW * 4 * pl.NT * 32 * 4 + (size_t)16 * M * 4;    // hand-over buffers, corrections
-    const size_t per_cta = (size_t)(pl.NT == 1 ? 51 : pl.NT == 2 ? 106 : 216) * 1024;
-    int nstg = g_force_nstg ? g_force_nstg : (int)((per_cta - xs_bytes - red_bytes - 64) / SLOT_BYTES);
+    const int64_t xs_bytes = (int64_t)pl.nc_per * KC * pl.MP * 2 * layouts;
+    int nstg = (int)(((cta_bytes - 128 - xs_bytes) / npipe - pipe_fixed) / pl.slot_bytes);
+    if (g_force_nstg && g_force_nstg < nstg) nstg = g_force_nstg;
     if (nstg > MAX_STAGES) nstg = MAX_STAGES;
     if (nstg < 2) nstg = 2;
     pl.nstg = nstg;
-    pl.smem_bytes = (size_t)nstg * SLOT_BYTES + xs_bytes + red_bytes + 64;
-    pl.part_bytes = pl.S > 1 ? (int64_t)pl.S * M * Q * 4 : 0;
-    pl.part_bytes = (pl.part_bytes + 255) / 256 * 256;
-    pl.ticket_bytes = pl.S > 1 ? TICKET_BYTES : 0;
+    pl.smem_bytes = (size_t)(xs_bytes + 128 + npipe * (pipe_fixed + (int64_t)nstg * pl.slot_bytes));
+    // partial results: a tile of one K-range is shared by at most `maxparts` pipes (runs of L units cut tiles of NSK
+    // units); L is smallest for the fewest tiles the pack can have
+    {
+        const int npipes = pl.ctas_x * npipe;
+        const int nsk = (pl.nc_per + cps - 1) / cps;
+        const int Lmin = run_length((int)((Q + 15) / 16), nsk, npipes);
+        const int maxparts = Lmin >= nsk ? 2 : (nsk + Lmin - 1) / Lmin + 1;
+        pl.part_slots = pl.S * maxparts;
+    }
+    pl.part_bytes = ((int64_t)pl.part_slots * M * Q * 4 + 255) / 256 * 256;
+    pl.ticket_bytes = TICKET_BYTES;
     return pl;
 }
 
@@ -969,20 +1255,22 @@ static bool fast_layout_ok(const qvb8_pack *w, const void *X) {
     return w->P > 0 && w->P % KC == 0 && aligned(w->ids, 16) && aligned(X, 16);
 }
 
-template <int XT, int NT, bool DUAL>
+template <int NT, bool DUAL>
 static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
-    auto kern = small_m_kernel<XT, NT, DUAL>;
+    auto kern = small_m_kernel<NT, DUAL>;
     static thread_local int granted_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != granted_dev) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(222 * 1024)) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM) != cudaSuccess)
             return cuda_status("qvb8_small_m: shared memory opt-in");
         granted_dev = dev;
     }
+    if (pl.smem_bytes > (size_t)MAX_DYN_SMEM)
+        return fail(QVB8_ERR_ARG, "qvb8_small_m: %zu bytes of shared memory needed (tuning out of range)", pl.smem_bytes);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(pl.ctas_x, pl.S);
-    cfg.blockDim = dim3(NTHREADS);
+    cfg.blockDim = dim3(pipes_for(NT) * PIPE_THREADS);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -994,24 +1282,24 @@ static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, 
     return cuda_status("qvb8_small_m launch");
 }
 
-template <int XT>
 static int launch_nt(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
     switch (pl.NT) {
-        case 1: return pl.dual ? launch_one<XT, 1, true>(prm, pl, st, pdl) : launch_one<XT, 1, false>(prm, pl, st, pdl);
-        case 2: return launch_one<XT, 2, false>(prm, pl, st, pdl);
-        case 3: return launch_one<XT, 3, false>(prm, pl, st, pdl);
-        case 4: return launch_one<XT, 4, false>(prm, pl, st, pdl);
-        case 5: return launch_one<XT, 5, false>(prm, pl, st, pdl);
-        default: return launch_one<XT, 6, false>(prm, pl, st, pdl);
+        case 1: return pl.dual ? launch_one<1, true>(prm, pl, st, pdl) : launch_one<1, false>(prm, pl, st, pdl);
+        case 2: return launch_one<2, false>(prm, pl, st, pdl);
+        case 3: return launch_one<3, false>(prm, pl, st, pdl);
+        case 4: return launch_one<4, false>(prm, pl, st, pdl);
+        case 5: return launch_one<5, false>(prm, pl, st, pdl);
+        default: return launch_one<6, false>(prm, pl, st, pdl);
     }
 }
 
 }  // namespace qv
 
-QV_API void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int debug) {
+QV_API void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int cps, int debug) {
     qv::g_fill_pct = fill_pct > 0 ? fill_pct : 0;
     qv::g_force_s = force_s > 0 ? force_s : 0;
     qv::g_force_nstg = (nstg >= 2 && nstg <= qv::MAX_STAGES) ? nstg : 0;
+    qv::g_force_cps = (cps >= qv::NW && cps <= qv::MAX_CPS && cps % qv::NW == 0) ? cps : 0;
     qv::g_debug = debug;
 }
 
@@ -1068,6 +1356,13 @@ QV_API int qvb8_plan_build(const qvb8_pack *w, void *plan, int64_t plan_bytes, v
                                               (int)w->Q, reinterpret_cast<TileDesc *>(base + L.tiles),
                                               reinterpret_cast<int *>(base));
         if (int rc = cuda_status("qvb8_plan_build tiles")) return rc;
+        if (w->n_esc > 0) {
+            tile_escapes_kernel<<<1, 1024, 0, st>>>(reinterpret_cast<TileDesc *>(base + L.tiles), reinterpret_cast<int *>(base),
+                                                    reinterpret_cast<int *>(base + L.esc_col),
+                                                    reinterpret_cast<float *>(base + L.esc_delta),
+                                                    reinterpret_cast<EscEntry *>(base + L.esc_ent));
+            if (int rc = cuda_status("qvb8_plan_build tile escapes")) return rc;
+        }
     }
     return QVB8_OK;
 }
@@ -1078,38 +1373,30 @@ QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, 
     if (int rc = check_small_m_args(w, X, x_dtype, x_mode, M, Y, "qvb8_small_m")) return rc;
     if (w->Q == 0) return QVB8_OK;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (plan == nullptr || x_mode != 0 || !fast_layout_ok(w, X))
+    if (plan == nullptr || x_mode != 0 || !fast_layout_ok(w, X) || (w->Q + 15) / 16 + NCLASS - 1 > MAX_TICKET_TILES)
         return launch_small_m_generic(w, X, x_dtype, x_mode, (int)M, Y, st);
     if (!aligned(plan, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: the plan must be 16-byte aligned");
     const Plan pl = make_plan(M, w->Q, w->P);
-    if (pl.part_bytes + pl.ticket_bytes > 0) {
-        if (!scratch || scratch_bytes < pl.part_bytes + pl.ticket_bytes)
-            return fail(QVB8_ERR_SCRATCH, "qvb8_small_m: scratch of %lld bytes needed, %lld given",
-                        (long long)(pl.part_bytes + pl.ticket_bytes), (long long)scratch_bytes);
-        if (!aligned(scratch, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: scratch must be 16-byte aligned");
-    }
+    if (!scratch || scratch_bytes < pl.part_bytes + pl.ticket_bytes)
+        return fail(QVB8_ERR_SCRATCH, "qvb8_small_m: scratch of %lld bytes needed, %lld given",
+                    (long long)(pl.part_bytes + pl.ticket_bytes), (long long)scratch_bytes);
+    if (!aligned(scratch, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: scratch must be 16-byte aligned");
     const PlanLayout L = plan_layout(w->Q, w->n_esc);
-    if (pl.S > 1 && L.max_tiles > MAX_TICKET_TILES)
-        return fail(QVB8_ERR_ARG, "qvb8_small_m: %d tiles with a split K-range exceed the %d ticket counters", L.max_tiles,
-                    MAX_TICKET_TILES);
     const uint8_t *base = reinterpret_cast<const uint8_t *>(plan);
     SmallMParams prm{};
     prm.ids = w->ids; prm.nbits = w->nbits; prm.bit_off = w->bit_off;
     prm.tiles = reinterpret_cast<const TileDesc *>(base + L.tiles);
     prm.ntiles_ptr = reinterpret_cast<const int *>(base);
-    if (w->n_esc > 0) {
-        prm.esc_col = reinterpret_cast<const int *>(base + L.esc_col);
-        prm.esc_delta = reinterpret_cast<const float *>(base + L.esc_delta);
-    }
+    if (w->n_esc > 0) prm.esc_ent = reinterpret_cast<const EscEntry *>(base + L.esc_ent);
     prm.X = X; prm.Y = Y;
     prm.ticket = reinterpret_cast<int *>(scratch);
     prm.part = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + TICKET_BYTES);
-    prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.S = pl.S;
+    prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.S = pl.S; prm.x_dtype = x_dtype;
     prm.nc_per = pl.nc_per; prm.nc_total = pl.nc_total; prm.nstg = pl.nstg; prm.debug = g_debug;
+    prm.cps = pl.cps; prm.slot_bytes = pl.slot_bytes;
+    for (int i = 0; i < 6; ++i) prm.rs[i] = pl.rs[i];
     const bool pdl = (flags & QVB8_FLAG_PDL) != 0;
-    if (x_dtype == QVB8_F16) return launch_nt<QVB8_F16>(prm, pl, st, pdl);
-    if (x_dtype == QVB8_BF16) return launch_nt<QVB8_BF16>(prm, pl, st, pdl);
-    return launch_nt<QVB8_F32>(prm, pl, st, pdl);
+    return launch_nt(prm, pl, st, pdl);
 }
 
 QV_API int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,

@@ -65,7 +65,7 @@ def load() -> ctypes.CDLL:
             lib.qvb8_plan_bytes.restype = i64
             lib.qvb8_plan_build.argtypes = [pk, vp, i64, vp]
             lib.qvb8_small_m_ex.argtypes = [pk, vp, vp, ci, ci, i64, vp, vp, i64, ci, vp]
-            lib.qvb8_small_m_set_tuning.argtypes = [ci, ci, ci, ci]
+            lib.qvb8_small_m_set_tuning.argtypes = [ci, ci, ci, ci, ci]
             lib.qvb8_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
             lib.qvb8_debug_trace.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
             lib.qvb8_small_m_set_tuning.restype = None

@@ -138,10 +138,11 @@ def test_generic_path_agrees(cuda_lib):
     assert rel_fro(a.cpu().numpy(), b.cpu().numpy()) < 1e-5
 
 
-@pytest.mark.parametrize("fill,force_s,nstg", [(100, 0, 0), (25, 1, 2), (300, 3, 3), (50, 12, 8)])
+@pytest.mark.parametrize("fill,force_s,nstg,cps", [(100, 0, 0, 0), (25, 1, 2, 4), (300, 3, 3, 8), (50, 12, 8, 4), (100, 2, 2, 16),
+                                                    (100, 0, 3, 12)])
 @pytest.mark.parametrize("M", [1, 5, 16])
-def test_plan_kernel_configurations(cuda_lib, fill, force_s, nstg, M):
-    """The streaming kernel under different grid sizes, K splits and ring depths, with escapes, gives the oracle's
+def test_plan_kernel_configurations(cuda_lib, fill, force_s, nstg, cps, M):
+    """The streaming kernel under different grid sizes, K splits, ring depths and stage lengths, with escapes, gives the oracle's
     product; so does the layout-agnostic kernel (no plan)."""
     from qvb8_b200 import lib
     pk = random_pack(300, 1536, (4, 6, 7, 8, 11), seed=31 + M, esc_frac=0.004, device=DEV)
@@ -150,13 +151,13 @@ def test_plan_kernel_configurations(cuda_lib, fill, force_s, nstg, M):
     plan = lib.build_plan(st, keep)
     want = _oracle_y(pk, X)
     try:
-        lib.load().qvb8_small_m_set_tuning(fill, force_s, nstg, 0)
+        lib.load().qvb8_small_m_set_tuning(fill, force_s, nstg, cps, 0)
         for flags in (0, lib.FLAG_PDL):
             y = lib.small_m(st, keep, X, plan=plan, flags=flags)
             err = rel_fro(y.cpu().numpy(), want)
             assert err < TIGHT, (err, flags)
     finally:
-        lib.load().qvb8_small_m_set_tuning(0, 0, 0, 0)
+        lib.load().qvb8_small_m_set_tuning(0, 0, 0, 0, 0)
     y_noplan = lib.small_m(st, keep, X)
     assert rel_fro(y_noplan.cpu().numpy(), want) < TIGHT
 
