@@ -132,6 +132,7 @@ struct Control {
     alignas(16) uint32_t pair_table[24];  // pair-conversion constants of widths 3..8 (see pair_const)
     alignas(8) uint64_t x_ready;          // every consumer warp has staged its share of the activations
     alignas(8) uint64_t sums_ready;       // every finishing warp has summed its share of the tokens
+    alignas(8) uint64_t xch_full[4];      // [owner pipe][contributor]: a contributed part of a shared tile is in place
     PipeControl pipe[3];
 };
 
@@ -603,18 +604,15 @@ struct SmallMParams {
 // One CTA per SM; its pipes share the staged activations.
 __host__ __device__ constexpr int pipes_for(int NT) { return NT == 1 ? 3 : NT == 2 ? 2 : 1; }
 
-// Work division.  A K-range of a tile is NSK stages long; the units (tile, stage), tile-major, are cut into equal
-// runs of L units, one run per pipe, so that every pipe streams the same number of bytes whatever the number of
-// tiles.  A pipe's run visits one tile after another; a tile that several visits share is summed through the
-// partial-result buffer in a fixed order (K-range, then pipe).
+// Work division.  A K-range of a tile is NSK stages long.  CTA c takes a contiguous share of whole tiles (the CTAs'
+// shares differ by at most one tile); the (tile, stage) units of the share, tile-major, are cut into equal runs, one
+// per pipe, so that the pipes of a CTA stream the same number of bytes.  A tile cut by a run boundary is summed
+// through shared memory: the pipe that holds its first stage owns it, the others contribute.
 struct Visit { int tile, sb, se; };                                     // stages [sb, se) of the tile
-__host__ __device__ inline int run_length(int ntiles, int NSK, int npipes) {
-    const long long total = (long long)ntiles * NSK;
-    const int L = (int)((total + npipes - 1) / npipes);
-    return L > 0 ? L : 1;
-}
-__host__ __device__ inline int visits_of_tile(int t, int NSK, int L) {  // how many pipes touch the tile in one K-range
-    return (t * NSK + NSK - 1) / L - (t * NSK) / L + 1;
+__host__ __device__ inline void cta_tiles(int ntiles, int nctas, int c, int &t0, int &t1) {
+    const int base = ntiles / nctas, extra = ntiles % nctas;
+    t0 = c * base + min(c, extra);
+    t1 = t0 + base + (c < extra ? 1 : 0);
 }
 // A pipe's run [u0, u1) as a list of visits.  Order: a run that ends inside a tile takes that (shared) tile first,
 // so that the waiting a shared tile costs (fence, ticket, possibly the final sum) is hidden behind the rest of the
@@ -734,16 +732,20 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
     const int MP = p.MP, M = p.M;
     const int nstg = p.nstg;
     // dynamic shared memory:
-    //   [activations A] [activations B] [16 zero bytes, padded to 128]
+    //   [activations A] [activations B] [16 zero bytes, padded to 128] [exchange buffers of tiles shared by pipes]
     //   per pipe: [ring: nstg stages of 16 rows] [side ring: NSIDE x (descriptor + escapes)] [hand-over buffer]
     //             [escape corrections]
     const int xs_halves = p.nc_per * 16 * MP * 8;                      // halves per activation layout
     __half *xs_a = reinterpret_cast<__half *>(smem);
     __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
     uint32_t *zero16 = reinterpret_cast<uint32_t *>(xs_a + (DUAL ? 2 : 1) * xs_halves);
+    const int xch_floats = 16 * M;                                     // one tile's results
+    float *xch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(zero16) + 128);    // [2 owners][2 contributors][16][M]
+    float *own = xch + 4 * xch_floats;                                 // [NPIPE][16][M]: an owner's own part of its shared tile
+    const size_t shared_bytes = (size_t)(((4 + NPIPE) * xch_floats * 4 + 127) / 128 * 128);
     const size_t pipe_bytes = (size_t)nstg * p.slot_bytes + (size_t)NSIDE * SIDE_BYTES + (size_t)RED_FLOATS * 4 +
                               (size_t)((16 * M * 4 + 127) / 128 * 128);
-    uint8_t *pbase = reinterpret_cast<uint8_t *>(zero16) + 128 + (size_t)pipe * pipe_bytes;
+    uint8_t *pbase = reinterpret_cast<uint8_t *>(zero16) + 128 + shared_bytes + (size_t)pipe * pipe_bytes;
     uint8_t *side = pbase + (size_t)nstg * p.slot_bytes;               // [NSIDE][SIDE_BYTES]
     float *red = reinterpret_cast<float *>(side + NSIDE * SIDE_BYTES); // [NW][4 * NT][32]
     float *corr = red + RED_FLOATS;                                    // [16][M], private to the finishing warp
@@ -768,6 +770,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
         if (tid == 0) {
             mbar_init(smem_u32(&ctl.x_ready), NW * NPIPE);
             mbar_init(smem_u32(&ctl.sums_ready), NPIPE);
+            for (int k = 0; k < 4; ++k) mbar_init(smem_u32(&ctl.xch_full[k]), 1);
             ctl.abort = 0;
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -778,14 +781,12 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
     pdl_launch_dependents();                                            // what follows in the stream may start its own prologue
     if (tracer) trace(p.debug, 1);
     const int ntiles = __ldg(p.ntiles_ptr);
-    // this pipe's run of (tile, stage) units; pipe-major numbering spreads a short list over all SMs first
-    const int npipes = gridDim.x * NPIPE;
-    const int pipe_id = pipe * gridDim.x + blockIdx.x;
-    const int L = run_length(ntiles, NSK, npipes);
-    const long long total_units = (long long)ntiles * NSK;
-    const long long u0l = (long long)pipe_id * L;
-    const int u0 = (int)(u0l < total_units ? u0l : total_units);
-    const int u1 = (int)(u0l + L < total_units ? u0l + L : total_units);
+    // this CTA's tiles and this pipe's run of their (tile, stage) units
+    int ct0, ct1;
+    cta_tiles(ntiles, gridDim.x, blockIdx.x, ct0, ct1);
+    const int uc0 = ct0 * NSK, uc1 = ct1 * NSK;
+    const int Lp = max(1, (uc1 - uc0 + NPIPE - 1) / NPIPE);
+    const int u0 = min(uc0 + pipe * Lp, uc1), u1 = min(u0 + Lp, uc1);
     const Run run = make_run(u0, u1, NSK);
     RingPos rp;
     rp.full = smem_u32(&pc_.full[0]); rp.empty = smem_u32(&pc_.empty[0]); rp.data = smem_u32(pbase);
@@ -878,6 +879,46 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctl.sums_ready));
         if (alive) alive = mbar_wait(smem_u32(&ctl.sums_ready), 0, abort_flag, 6);
+        int own_contrib = 0, own_tile = 0, own_row[2] = {-1, -1};
+        // writes a finished tile (of this K-range): the result itself, or with several K-ranges a partial result that
+        // whichever range finishes the tile last adds up in range order
+        auto emit_tile = [&](int tile, const int (&rows)[2], const float (&y)[2][NT][2]) {
+            float *out = p.S == 1 ? p.Y : p.part + (int64_t)split * M * p.Q;
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow)
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int m = 8 * n + 2 * t + k;
+                        if (rows[hrow] >= 0 && m < M) out[(int64_t)m * p.Q + rows[hrow]] = y[hrow][n][k];
+                    }
+            if (p.S == 1) return;
+            __syncwarp();
+            __threadfence();
+            const int tkt = tile;
+            int last = 0;
+            if (lane == 0) last = atomicAdd(p.ticket + tkt, 1) == p.S - 1;
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence();
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow)
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const int m = 8 * n + 2 * t + k;
+                            if (rows[hrow] >= 0 && m < M) {
+                                const int64_t o = (int64_t)m * p.Q + rows[hrow];
+                                float sum = 0.f;
+                                for (int r = 0; r < p.S; ++r) sum += __ldcg(p.part + (int64_t)r * M * p.Q + o);
+                                p.Y[o] = sum;
+                            }
+                        }
+                if (lane == 0) p.ticket[tkt] = 0;
+            }
+        };
         for (int i = 0; i < run.nv; ++i) {
             const Visit v = run_visit(run, i);
             // ---- the tile's descriptor and escapes arrive in a side slot
@@ -948,72 +989,82 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
                 }
             __syncwarp();                                               // every lane is done with the buffer
             if (lane == 0) mbar_arrive(smem_u32(&pc_.red_empty));
-            // a visit that covers its tile alone writes the result; otherwise it writes a partial result and whichever
-            // visit of the tile finishes last adds them up in a fixed order (K-range, then pipe)
-            const bool whole = p.S == 1 && v.sb == 0 && v.se == NSK;
-            int slot = 0, expected = 1;
-            if (!whole) {
-                expected = 0;
-                for (int r = 0; r < p.S; ++r) {
-                    const int ncr = min(p.nc_per, p.nc_total - r * p.nc_per), nskr = (ncr + cps - 1) / cps;
-                    const int Lr = run_length(ntiles, nskr, npipes);
-                    if (r == split) slot = expected + pipe_id - (v.tile * nskr) / Lr;
-                    expected += visits_of_tile(v.tile, nskr, Lr);
-                }
-            }
-            float *out = whole ? p.Y : p.part + (int64_t)slot * M * p.Q;
-            // thread holds rows g, g+8 of the tile and tokens 8n+2t, 8n+2t+1
+            // y = tau_s * sum(x * id) + min_s * sum(x) + corrections for rows g, g+8 and tokens 8n+2t, 8n+2t+1
+            // (per-element rows arrive complete); the min_s term goes with the visit that holds the first stage
+            float y[2][NT][2];
 #pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow) {
+            for (int hrow = 0; hrow < 2; ++hrow)
 #pragma unroll
-                for (int n = 0; n < NT; ++n) {
+                for (int n = 0; n < NT; ++n)
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const int m = 8 * n + 2 * t + k;
+                        float val = acc[n][2 * hrow + k];
                         if (myrow[hrow] >= 0 && m < M) {
-                            // y = tau_s * sum(x * id) + min_s * sum(x)   (per-element rows arrive complete); the
-                            // min_s term of a K-range goes with the visit that holds the range's first stage
-                            float y = acc[n][2 * hrow + k];
                             if (cnb != 0) {
-                                y *= myts[hrow];
-                                if (v.sb == 0) y = __fmaf_rn(myms[hrow], ctl.sumx[m], y);
+                                val *= myts[hrow];
+                                if (v.sb == 0) val = __fmaf_rn(myms[hrow], ctl.sumx[m], val);
                             }
-                            if (planned) y += corr[(g + 8 * hrow) * M + m];
-                            out[(int64_t)m * p.Q + myrow[hrow]] = y;
+                            if (planned) val += corr[(g + 8 * hrow) * M + m];
                         }
+                        y[hrow][n][k] = val;
                     }
-                }
-            }
             __syncwarp();                                               // every lane is done with corr
-            if (tracer && i == 0) trace(p.debug, 11);
-            if (!whole && alive) {
-                __threadfence();
-                int last = 0;
-                if (lane == 0) last = atomicAdd(p.ticket + v.tile, 1) == expected - 1;
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __threadfence();
-#pragma unroll
-                    for (int hrow = 0; hrow < 2; ++hrow) {
-                        if (myrow[hrow] < 0) continue;
-#pragma unroll
-                        for (int n = 0; n < NT; ++n) {
-#pragma unroll
-                            for (int k = 0; k < 2; ++k) {
-                                const int m = 8 * n + 2 * t + k;
-                                if (m < M) {
-                                    const int64_t o = (int64_t)m * p.Q + myrow[hrow];
-                                    float s = 0.f;
-                                    for (int r = 0; r < expected; ++r) s += __ldcg(p.part + (int64_t)r * M * p.Q + o);
-                                    p.Y[o] = s;
-                                }
-                            }
-                        }
-                    }
-                    if (lane == 0) p.ticket[v.tile] = 0;
+            // a tile cut by run boundaries: the pipe that holds its first stage owns it, the later pipes hand their
+            // parts over in shared memory; the owner adds them up when its run is done
+            const bool partial = !(v.sb == 0 && v.se == NSK);
+            bool emit = true;
+            if (partial) {
+                const int op = (v.tile * NSK - uc0) / Lp;               // the pipe that holds the tile's first stage
+                float *dst;
+                if (op == pipe) {
+                    dst = own + pipe * xch_floats;
+                    own_contrib = min((v.tile * NSK + NSK - 1 - uc0) / Lp, NPIPE - 1) - op;
+                    own_row[0] = myrow[0]; own_row[1] = myrow[1];
+                    own_tile = v.tile;
+                } else {
+                    dst = xch + (op * 2 + (pipe - op - 1)) * xch_floats;
                 }
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow)
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const int m = 8 * n + 2 * t + k;
+                            if (m < M) dst[(g + 8 * hrow) * M + m] = y[hrow][n][k];
+                        }
+                if (op != pipe) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl.xch_full[op * 2 + (pipe - op - 1)]));
+                }
+                emit = false;
             }
+            if (tracer && i == 0) trace(p.debug, 11);
+            if (emit) emit_tile(v.tile, myrow, y);
             if (tracer && i == 0) trace(p.debug, 12);
+        }
+        // ---- the tile this pipe shares with later pipes: their parts have long arrived
+        if (own_contrib > 0) {
+            for (int j = 0; j < own_contrib; ++j)
+                if (alive) alive = mbar_wait(smem_u32(&ctl.xch_full[pipe * 2 + j]), 0, abort_flag, 9);
+            float y[2][NT][2];
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow)
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int m = 8 * n + 2 * t + k;
+                        float val = 0.f;
+                        if (m < M) {
+                            const int o = (g + 8 * hrow) * M + m;
+                            val = own[pipe * xch_floats + o];
+                            for (int j = 0; j < own_contrib; ++j) val += xch[(pipe * 2 + j) * xch_floats + o];
+                        }
+                        y[hrow][n][k] = val;
+                    }
+            if (alive) emit_tile(own_tile, own_row, y);
         }
         if (tracer) trace(p.debug, 13);
     } else {
@@ -1202,9 +1253,10 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     // staged activations.  The second activation layout (no byte permutes for widths 3..5) is staged only when it
     // does not shorten the K-range or the rings.
     const int min_stages = cps > 8 ? 2 : 3;
-    const int64_t xs_budget = cta_bytes - 128 - npipe * (pipe_fixed + (int64_t)min_stages * pl.slot_bytes);
+    const int64_t shared_fixed = 128 + ((4 + npipe) * 16 * M * 4 + 127) / 128 * 128;      // zeros, exchange buffers
+    const int64_t xs_budget = cta_bytes - shared_fixed - npipe * (pipe_fixed + (int64_t)min_stages * pl.slot_bytes);
     const int64_t xs_one = (int64_t)P * pl.MP * 2;
-    pl.dual = pl.MP <= 4 && cta_bytes - 128 - npipe * (pipe_fixed + (int64_t)(min_stages + 1) * pl.slot_bytes) >= 2 * xs_one;
+    pl.dual = pl.MP <= 4 && cta_bytes - shared_fixed - npipe * (pipe_fixed + (int64_t)(min_stages + 1) * pl.slot_bytes) >= 2 * xs_one;
     const int layouts = pl.dual ? 2 : 1;
     int nc_max = xs_budget > 0 ? (int)(xs_budget / (KC * pl.MP * 2 * layouts)) : 0;
     if (nc_max >= cps) nc_max = nc_max / cps * cps;                     // whole stages
@@ -1224,30 +1276,18 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     pl.S = (pl.nc_total + pl.nc_per - 1) / pl.nc_per;                   // no empty range
     int64_t cx = ctas / pl.S;
     if (cx < 1) cx = 1;
-    {
-        const int nsk = (pl.nc_per + cps - 1) / cps;
-        const int64_t need = ((int64_t)max_tiles * nsk + npipe - 1) / npipe;   // CTAs that give every unit a pipe of its own
-        if (cx > need) cx = need;
-    }
+    if (cx > max_tiles) cx = max_tiles;                                 // a CTA takes whole tiles
     pl.ctas_x = (int)cx;
     const int64_t xs_bytes = (int64_t)pl.nc_per * KC * pl.MP * 2 * layouts;
-    int nstg = (int)(((cta_bytes - 128 - xs_bytes) / npipe - pipe_fixed) / pl.slot_bytes);
+    int nstg = (int)(((cta_bytes - shared_fixed - xs_bytes) / npipe - pipe_fixed) / pl.slot_bytes);
     if (g_force_nstg && g_force_nstg < nstg) nstg = g_force_nstg;
     if (nstg > MAX_STAGES) nstg = MAX_STAGES;
     if (nstg < 2) nstg = 2;
     pl.nstg = nstg;
-    pl.smem_bytes = (size_t)(xs_bytes + 128 + npipe * (pipe_fixed + (int64_t)nstg * pl.slot_bytes));
-    // partial results: a tile of one K-range is shared by at most `maxparts` pipes (runs of L units cut tiles of NSK
-    // units); L is smallest for the fewest tiles the pack can have
-    {
-        const int npipes = pl.ctas_x * npipe;
-        const int nsk = (pl.nc_per + cps - 1) / cps;
-        const int Lmin = run_length((int)((Q + 15) / 16), nsk, npipes);
-        const int maxparts = Lmin >= nsk ? 2 : (nsk + Lmin - 1) / Lmin + 1;
-        pl.part_slots = pl.S * maxparts;
-    }
+    pl.smem_bytes = (size_t)(xs_bytes + shared_fixed + npipe * (pipe_fixed + (int64_t)nstg * pl.slot_bytes));
+    pl.part_slots = pl.S > 1 ? pl.S : 0;                                // partial results only between K-ranges
     pl.part_bytes = ((int64_t)pl.part_slots * M * Q * 4 + 255) / 256 * 256;
-    pl.ticket_bytes = TICKET_BYTES;
+    pl.ticket_bytes = pl.S > 1 ? TICKET_BYTES : 0;
     return pl;
 }
 
@@ -1377,10 +1417,12 @@ QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, 
         return launch_small_m_generic(w, X, x_dtype, x_mode, (int)M, Y, st);
     if (!aligned(plan, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: the plan must be 16-byte aligned");
     const Plan pl = make_plan(M, w->Q, w->P);
-    if (!scratch || scratch_bytes < pl.part_bytes + pl.ticket_bytes)
-        return fail(QVB8_ERR_SCRATCH, "qvb8_small_m: scratch of %lld bytes needed, %lld given",
-                    (long long)(pl.part_bytes + pl.ticket_bytes), (long long)scratch_bytes);
-    if (!aligned(scratch, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: scratch must be 16-byte aligned");
+    if (pl.part_bytes + pl.ticket_bytes > 0) {
+        if (!scratch || scratch_bytes < pl.part_bytes + pl.ticket_bytes)
+            return fail(QVB8_ERR_SCRATCH, "qvb8_small_m: scratch of %lld bytes needed, %lld given",
+                        (long long)(pl.part_bytes + pl.ticket_bytes), (long long)scratch_bytes);
+        if (!aligned(scratch, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: scratch must be 16-byte aligned");
+    }
     const PlanLayout L = plan_layout(w->Q, w->n_esc);
     const uint8_t *base = reinterpret_cast<const uint8_t *>(plan);
     SmallMParams prm{};
