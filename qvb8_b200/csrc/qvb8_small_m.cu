@@ -449,8 +449,8 @@ __global__ void __launch_bounds__(256) escape_plan_kernel(const uint8_t *__restr
 __global__ void __launch_bounds__(1024) plan_tiles_kernel(const uint8_t *__restrict__ nbits,
                                                           const int64_t *__restrict__ bit_off,
                                                           const float *__restrict__ min_s, const float *__restrict__ tau_s,
-                                                          const int *__restrict__ esc_ptr, int Q, TileDesc *__restrict__ tiles,
-                                                          int *__restrict__ header) {
+                                                          const int *__restrict__ esc_ptr, int Q, int max_tiles,
+                                                          TileDesc *__restrict__ tiles, int *__restrict__ header) {
     __shared__ int cnt[NCLASS], base_tile[NCLASS], running[NCLASS];
     __shared__ int wtot[32][NCLASS];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -519,6 +519,12 @@ __global__ void __launch_bounds__(1024) plan_tiles_kernel(const uint8_t *__restr
         tiles[t].cnt = n;
         for (int s = n; s < 16; ++s) tiles[t].row[s] = -1;
     }
+    // the table is as long as the largest tile count a pack of Q rows can have; the surplus tiles are empty
+    for (int t = ntiles + tid; t < max_tiles; t += 1024) {
+        tiles[t].nb = 0;
+        tiles[t].cnt = 0;
+        for (int s = 0; s < 16; ++s) tiles[t].row[s] = -1;
+    }
 }
 
 // The escapes once more, grouped by tile: entry list of tile t = the escapes of its rows in row-slot order, padded to
@@ -581,7 +587,7 @@ struct SmallMParams {
     const uint8_t *nbits;      // per-element class only
     const int64_t *bit_off;    // per-element class only
     const TileDesc *tiles;
-    const int *ntiles_ptr;     // plan header
+    int ntiles;                // length of the tile table (real tiles first, then empty ones)
     const EscEntry *esc_ent;   // escapes grouped by tile; null: the pack has no escapes
     const void *X;
     float *Y;                  // (M, Q)
@@ -780,7 +786,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
     __syncthreads();
     pdl_launch_dependents();                                            // what follows in the stream may start its own prologue
     if (tracer) trace(p.debug, 1);
-    const int ntiles = __ldg(p.ntiles_ptr);
+    const int ntiles = p.ntiles;
     // this CTA's tiles and this pipe's run of their (tile, stage) units
     int ct0, ct1;
     cta_tiles(ntiles, gridDim.x, blockIdx.x, ct0, ct1);
@@ -1393,7 +1399,7 @@ QV_API int qvb8_plan_build(const qvb8_pack *w, void *plan, int64_t plan_bytes, v
     }
     if (w->Q > 0) {
         plan_tiles_kernel<<<1, 1024, 0, st>>>(w->nbits, w->bit_off, w->min_s, w->tau_s, w->n_esc > 0 ? esc_ptr : nullptr,
-                                              (int)w->Q, reinterpret_cast<TileDesc *>(base + L.tiles),
+                                              (int)w->Q, L.max_tiles, reinterpret_cast<TileDesc *>(base + L.tiles),
                                               reinterpret_cast<int *>(base));
         if (int rc = cuda_status("qvb8_plan_build tiles")) return rc;
         if (w->n_esc > 0) {
@@ -1428,7 +1434,7 @@ QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, 
     SmallMParams prm{};
     prm.ids = w->ids; prm.nbits = w->nbits; prm.bit_off = w->bit_off;
     prm.tiles = reinterpret_cast<const TileDesc *>(base + L.tiles);
-    prm.ntiles_ptr = reinterpret_cast<const int *>(base);
+    prm.ntiles = L.max_tiles;
     if (w->n_esc > 0) prm.esc_ent = reinterpret_cast<const EscEntry *>(base + L.esc_ent);
     prm.X = X; prm.Y = Y;
     prm.ticket = reinterpret_cast<int *>(scratch);

@@ -14,6 +14,10 @@ Projections of one layer and their inputs (d = d_model, kv = kv heads x head_dim
 
 Attention, norms and activations between them are not part of this path; the stack feeds every projection a
 resident activation buffer of the right shape.
+
+Projections that read the same input (q/k/v; gate/up) are fused into one pack and one launch by default, as the
+reference fuses its entropy-coded linears (formats/qvb8r/fuse.py:1-60); the members' outputs are views of the fused
+output and every compressed byte is still streamed exactly once per step.
 """
 from __future__ import annotations
 
@@ -21,6 +25,7 @@ from dataclasses import dataclass
 
 import torch
 
+from . import fuse as _fuse
 from . import lib as _lib
 from . import synth
 
@@ -61,56 +66,82 @@ class LinearStack:
     (rows are independent, reference formats/qvb8/module.py:126-160)."""
 
     def __init__(self, cfg: StackConfig, M: int, device, layers: int | None = None, seed_base: int | None = None,
-                 rank: int = 0, world: int = 1, policy: str = "escape_outliers", x_dtype=torch.bfloat16):
+                 rank: int = 0, world: int = 1, policy: str = "escape_outliers", x_dtype=torch.bfloat16,
+                 fuse_same_input: bool = True):
         self.cfg, self.M, self.device = cfg, int(M), torch.device(device)
         self.layers = cfg.layers if layers is None else int(layers)
         self.rank, self.world = rank, world
-        self.packs = []          # [layer][proj] -> (name, QVB8Pack, struct, keepalive, xbuf name)
+        self.fused = bool(fuse_same_input)
+        self.launches = []       # [layer][launch] -> (name, QVB8Pack, struct, keepalive (+ plan), input name, member names)
         self.compressed_bytes = 0
         self.n_weights = 0
         self.width_hist: dict = {}
         self.n_escapes = 0
         seed_base = 1000 * cfg.config_id if seed_base is None else seed_base
+        groups = dict(_fuse.SAME_INPUT_GROUPS) if self.fused else {}
+        member_group = {m: g for g, ms in groups.items() for m in ms}
         for layer in range(self.layers):
-            row = []
+            made = {}
             for j, (name, Q, P, xname) in enumerate(cfg.projections()):
                 if Q % world:
                     raise ValueError(f"{name}: {Q} rows do not split over {world} ranks")
                 Qr = Q // world
                 W = synth.synth_weight(Q, P, seed_base + layer * 16 + j, device=self.device)
                 W = W[rank * Qr:(rank + 1) * Qr]
-                pk = synth.encode_qvb8(W, tau=cfg.tau, policy=policy)
+                made[name] = (synth.encode_qvb8(W, tau=cfg.tau, policy=policy), xname)
                 del W
+            row, done = [], set()
+            for name, _, _, xname in cfg.projections():
+                if name in done:
+                    continue
+                g = member_group.get(name)
+                members = [m for m in groups[g] if m in made] if g else [name]
+                if len(members) > 1:
+                    pk, _ = _fuse.concat_packs([made[m][0] for m in members])
+                    lname = g
+                else:
+                    pk, lname = made[name][0], name
+                done.update(members)
                 st, keep = _lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx,
                                             pk.esc_vals)
                 plan = _lib.build_plan(st, keep)
-                row.append((name, pk, st, keep + [plan], xname))
+                row.append((lname, pk, st, keep + [plan], xname, members))
                 self.compressed_bytes += pk.weight_bytes()
                 self.n_weights += pk.Q * pk.P
                 self.n_escapes += int(pk.esc_idx.numel())
                 for b, n in pk.stats["nbits_hist"].items():
                     self.width_hist[b] = self.width_hist.get(b, 0) + n
-            self.packs.append(row)
+            del made
+            self.launches.append(row)
         d, f = cfg.d_model, cfg.mlp
         shapes = {"x_attn": d, "x_o": cfg.q_out, "x_mlp": d, "x_down": f}
         self.x = {k: synth.synth_activation(self.M, p, seed=7 + i, device=self.device, dtype=x_dtype)
                   for i, (k, p) in enumerate(shapes.items())}
-        self.y = [[torch.empty((self.M, pk.Q), dtype=torch.float32, device=self.device) for _, pk, *_ in row]
-                  for row in self.packs]
-        for row in self.packs:
+        # one output buffer per launch; y[layer][name] are the members' views of it
+        self.y_launch = [[torch.empty((self.M, pk.Q), dtype=torch.float32, device=self.device) for _, pk, *_ in row]
+                         for row in self.launches]
+        self.y = []
+        for row, outs in zip(self.launches, self.y_launch):
+            views = {}
+            for (lname, pk, _, _, _, members), out in zip(row, outs):
+                sizes = pk.stats.get("members", [pk.Q]) if len(members) > 1 else [pk.Q]
+                for m, t in zip(members, torch.split(out, sizes, dim=1)):
+                    views[m] = t
+            self.y.append(views)
+        for row in self.launches:
             for _, pk, *_ in row:
                 _lib.reserve_scratch(self.device, self.M, pk.Q, pk.P)
         self.graph = None
-        self.launches_per_step = sum(1 for row in self.packs for _ in row)
+        self.launches_per_step = sum(len(row) for row in self.launches)
         self.pdl = True
         self._host_in = self._host_out = None
 
     # ---- execution ------------------------------------------------------------------------------------
     def run_eager(self) -> None:
-        """One pass over every projection on the current stream (one fused launch each, plus the escape pass)."""
-        for li, row in enumerate(self.packs):
-            for j, (name, pk, st, keep, xname) in enumerate(row):
-                _lib.small_m(st, keep, self.x[xname], out=self.y[li][j], plan=keep[-1],
+        """One pass over every launch of every layer on the current stream."""
+        for li, row in enumerate(self.launches):
+            for j, (name, pk, st, keep, xname, _) in enumerate(row):
+                _lib.small_m(st, keep, self.x[xname], out=self.y_launch[li][j], plan=keep[-1],
                              flags=_lib.FLAG_PDL if self.pdl else 0)
 
     def capture(self) -> None:
@@ -133,7 +164,7 @@ class LinearStack:
             self._host_in = {k: torch.empty_like(v, device="cpu").pin_memory() for k, v in self.x.items()}
             for k, v in self.x.items():
                 self._host_in[k].copy_(v)
-            last = self.y[-1]
+            last = self.y_launch[-1]
             self._host_out = [torch.empty_like(t, device="cpu").pin_memory() for t in last]
         return self._host_in, self._host_out
 
@@ -147,7 +178,7 @@ class LinearStack:
         for k in self.x:
             self.x[k].copy_(hin[k], non_blocking=True)
         self.step()
-        for t, h in zip(self.y[-1], hout):
+        for t, h in zip(self.y_launch[-1], hout):
             h.copy_(t, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         return hout
@@ -156,4 +187,4 @@ class LinearStack:
         return sum(v.numel() * v.element_size() for v in self.x.values())
 
     def d2h_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.y[-1])
+        return sum(t.numel() * t.element_size() for t in self.y_launch[-1])

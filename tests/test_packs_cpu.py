@@ -111,3 +111,19 @@ def test_bad_blobs_are_rejected():
         synth.encode_qvb8(torch.full((2, 128), 0.1234567), tau=1e-3)       # not bf16-representable
     with pytest.raises(ValueError):
         synth.encode_qvb8(torch.randn(4, 128).bfloat16() * 1e-5, tau=1e-8)   # below half an fp16 ulp: not certifiable
+
+
+def test_concat_packs_is_the_members_side_by_side():
+    """Same-input fusion (reference formats/qvb8r/fuse.py:22-50 for its entropy-coded format): the fused pack
+    restores to the members' dense weights stacked by rows, escapes included."""
+    from qvb8_b200 import fuse
+    members = [random_pack(40, 256, (5, 7, 8), seed=1, esc_frac=0.01),
+               random_pack(17, 256, (3, 6), seed=2, esc_frac=0.0),
+               random_pack(64, 256, (7, 11), seed=3, esc_frac=0.02)]
+    fused, splits = fuse.concat_packs(members)
+    assert fused.Q == 121 and splits == [40, 57]
+    want = np.concatenate([oracle.qvb8_dense(pack_np(m)) for m in members], axis=0)
+    got = oracle.qvb8_dense(pack_np(fused))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    with pytest.raises(ValueError):
+        fuse.concat_packs([members[0], random_pack(8, 128, (7,), seed=4)])

@@ -197,6 +197,24 @@ def test_plan_contents(cuda_lib):
     assert rel_fro(y.cpu().numpy(), _oracle_y(pk, X)) < TIGHT
 
 
+def test_fused_stack_equals_separate_launches(cuda_lib):
+    """q/k/v and gate/up fused into one pack and one launch each give bit-identical outputs to one launch per
+    projection (each row's sum is computed the same way), and the oracle's product."""
+    from qvb8_b200 import stack
+    cfg = stack.StackConfig("tiny", 1, 512, 512, 128, 1024, 1e-3, 9)
+    for M in (1, 3):
+        a = stack.LinearStack(cfg, M, DEV, fuse_same_input=True)
+        b = stack.LinearStack(cfg, M, DEV, fuse_same_input=False)
+        assert a.launches_per_step == 4 and b.launches_per_step == 7
+        assert a.compressed_bytes == b.compressed_bytes
+        a.step(); b.step()
+        torch.cuda.synchronize()
+        for name in ("q", "k", "v", "o", "gate", "up", "down"):
+            assert torch.equal(a.y[0][name], b.y[0][name]), name
+        for (lname, pk, _, _, xname, _), y in zip(b.launches[0], b.y_launch[0]):
+            assert rel_fro(y.cpu().numpy(), _oracle_y(pk, b.x[xname])) < TIGHT, lname
+
+
 def test_small_m_is_deterministic(cuda_lib):
     pk = random_pack(512, 4096, (6, 7), seed=21, esc_frac=0.001, device=DEV)        # several K-ranges
     X = synth.synth_activation(8, 4096, seed=3, device=DEV)
