@@ -114,14 +114,31 @@ void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int cps, int d
 int qvb8_debug_trace(unsigned long long *out32);
 
 /* Device-side error word of the current device: 0, or the code of the first bounded wait that gave up inside a
- * kernel of this library (1 = copy ring slot never freed, 2 = copy never landed, 3 / 4 = escape-correction
- * hand-over).  Synchronises the host. */
+ * kernel of this library (1 = copy ring slot never freed, 2 = copy never landed, 3 / 4 = hand-over between the
+ * consumer and finishing warps, 5 / 6 = activation staging, 7 / 8 = descriptor ring, 9 = part of a shared tile).
+ * Synchronises the host. */
 int qvb8_device_status(int *status);
 
 /* Same product through the layout-agnostic kernel (any P, any id alignment, widths 1..14).  The library falls
  * back to it by itself when qvb8_small_m's layout preconditions do not hold; exported for tests. */
 int qvb8_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y,
                          void *stream);
+
+/* qvb8_small_m_ex without a scratch argument and without any allocation (no counterpart in the reference, whose
+ * extension allocates its split-K buffer through torch on every call).  For callers that cannot allocate device
+ * memory and have no buffer to pass: code running inside an allocator or memory-pool callback, a thread that must
+ * stay out of the CUDA allocator while another thread's stream capture is open, a host binding with no device
+ * allocator.  The partial results and tile tickets go to a fixed array inside the loaded module
+ * (qvb8_small_m_static_max_scratch() bytes: 4 MiB); a product that needs more (qvb8_small_m_scratch_bytes) is
+ * refused with QVB8_ERR_SCRATCH and nothing is launched.
+ *   - The first call on each device looks the array up and clears its ticket area with that device current (a
+ *     synchronous step): make it before any stream capture that uses this entry point.
+ *   - The array is shared by every call on the device and keeps its last contents; only the ticket area must be zero
+ *     on entry, and every call leaves it zero.
+ *   - Two calls that overlap on the device (different streams) race on the array: serialise them. */
+int64_t qvb8_small_m_static_max_scratch(void);
+int qvb8_small_m_static(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int x_mode, int64_t M,
+                        float *Y, int flags, void *stream);
 
 #ifdef __cplusplus
 }

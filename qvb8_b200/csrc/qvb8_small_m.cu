@@ -40,6 +40,8 @@
 // runs to its end with a meaningless result instead of hanging.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace qv {
 
 int launch_fix_escapes(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int M, float *Y, cudaStream_t st);
@@ -1450,4 +1452,61 @@ QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, 
 QV_API int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,
                         int64_t scratch_bytes, void *stream) {
     return qvb8_small_m_ex(w, nullptr, X, x_dtype, x_mode, M, Y, scratch, scratch_bytes, 0, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// qvb8_small_m_static: the streaming product for callers that cannot hand the library a scratch buffer and cannot
+// let it allocate one -- a call made from inside a memory-pool callback, from a thread that must never enter the
+// CUDA allocator because another thread holds a capture open, or from a host binding (cgo, JNI) whose runtime gives
+// it no device allocator at all.  Their K-range partial results and tile tickets live in a fixed array that is part
+// of the loaded module; its address is looked up once per device.
+namespace qv {
+
+constexpr int64_t STATIC_SCRATCH_BYTES = 4ll << 20;            // tickets (256 KB) + 3.75 MB of partial results
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_STATIC_DEVICES = 64;
+static void *g_static_ptr[MAX_STATIC_DEVICES] = {};
+
+// Address of the array on the current device; on first use per device also clears the ticket area, the only part
+// that must start at zero (every call leaves it zero again).  Not capturable: the first call per device must come
+// before any stream capture that uses the entry point.
+static int static_scratch(void **out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return cuda_status("qvb8_small_m_static: current device");
+    if (dev < 0 || dev >= MAX_STATIC_DEVICES)
+        return fail(QVB8_ERR_ARG, "qvb8_small_m_static: device index %d is beyond the %d this entry point tracks", dev,
+                    MAX_STATIC_DEVICES);
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!g_static_ptr[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p)
+            return cuda_status("qvb8_small_m_static: address of the module's scratch array");
+        if (cudaMemset(p, 0, (size_t)TICKET_BYTES) != cudaSuccess)
+            return cuda_status("qvb8_small_m_static: clearing the ticket area");
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return QVB8_OK;
+}
+
+}  // namespace qv
+
+QV_API int64_t qvb8_small_m_static_max_scratch(void) { return qv::STATIC_SCRATCH_BYTES; }
+
+QV_API int qvb8_small_m_static(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int x_mode, int64_t M,
+                               float *Y, int flags, void *stream) {
+    using namespace qv;
+    if (int rc = check_small_m_args(w, X, x_dtype, x_mode, M, Y, "qvb8_small_m_static")) return rc;
+    if (w->Q == 0) return QVB8_OK;
+    const int64_t need = (w->P > 0 && w->P % KC == 0) ? qvb8_small_m_scratch_bytes(M, w->Q, w->P) : 0;
+    if (need > STATIC_SCRATCH_BYTES)
+        return fail(QVB8_ERR_SCRATCH,
+                    "qvb8_small_m_static: this product needs %lld bytes of scratch, the built-in array holds %lld; "
+                    "use qvb8_small_m_ex with a caller-provided buffer",
+                    (long long)need, (long long)STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    if (int rc = static_scratch(&scratch)) return rc;
+    return qvb8_small_m_ex(w, plan, X, x_dtype, x_mode, M, Y, scratch, STATIC_SCRATCH_BYTES, flags, stream);
 }

@@ -23,7 +23,7 @@ _CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
 EXPORTS = (
     "qvb8_last_error", "qvb8_version", "qvb8_decode", "qvb8_small_m_scratch_bytes", "qvb8_small_m",
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
-    "qvb8_device_status", "qvb8_debug_trace",
+    "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
 )
 
 
@@ -61,6 +61,9 @@ def load() -> ctypes.CDLL:
             lib.qvb8_small_m_scratch_bytes.restype = i64
             lib.qvb8_small_m.argtypes = [pk, vp, ci, ci, i64, vp, vp, i64, vp]
             lib.qvb8_small_m_generic.argtypes = [pk, vp, ci, ci, i64, vp, vp]
+            lib.qvb8_small_m_static.argtypes = [pk, vp, vp, ci, ci, i64, vp, ci, vp]
+            lib.qvb8_small_m_static_max_scratch.argtypes = []
+            lib.qvb8_small_m_static_max_scratch.restype = i64
             lib.qvb8_plan_bytes.argtypes = [i64, i64]
             lib.qvb8_plan_bytes.restype = i64
             lib.qvb8_plan_build.argtypes = [pk, vp, i64, vp]
