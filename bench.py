@@ -10,8 +10,8 @@ seeded).  One step = one pass over every projection of every layer = one decode 
 
   value   whole-job GB/s with the activations resident in HBM (CUDA-graph replay, CUDA events, max over ranks)
   e2e     the same through LinearStack.step_host: pinned host activations -> device, the step, outputs -> host
-  N > 1   every projection is sharded by output rows over the ranks (column parallel) and the outputs are
-          all-gathered over NCCL after each layer; total bytes stay fixed ("strong" scaling)
+  N > 1   q/k/v and gate/up are sharded by output rows (column parallel), o and down by input columns (row parallel)
+          with one NCCL all-reduce of the (M, d_model) partial sums after each; total bytes stay fixed ("strong")
 
 --impl reference times the CPU path the reference itself would run for this op (it ships no CPU GEMV): restore the
 pack to bf16 weights, then torch.matmul on the host cores -- here through the CPU oracle's restatement of the
@@ -162,6 +162,17 @@ def run_reference_arm(args, cfg):
     print(json.dumps(line), flush=True)
 
 
+def finish(world, dist):
+    """Leave a multi-rank run without tearing NCCL down: communicators referenced by captured graphs make
+    destroy_process_group wait for ever, so the ranks meet at a barrier, flush and exit."""
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -203,17 +214,11 @@ def main():
     torch.cuda.synchronize(dev)
     t_build = time.perf_counter() - t_build
 
-    gather = None
     if world > 1:
-        # column-parallel shard boundary: every rank needs the full activation of the next block
-        gather = [[torch.empty((world, *t.shape), dtype=t.dtype, device=dev) for t in row] for row in st.y_launch]
+        st.enable_collectives()      # all-reduce after o and after down: the only exchanges of a layer
 
     def one_step():
         st.step()
-        if world > 1:
-            for row, grow in zip(st.y_launch, gather):
-                for t, gt in zip(row, grow):
-                    dist.all_gather_into_tensor(gt, t)
 
     st.capture()
     for _ in range(args.warmup):
@@ -251,11 +256,6 @@ def main():
     t0 = time.perf_counter()
     for _ in range(args.steps):
         st.step_host()
-        if world > 1:
-            for row, grow in zip(st.y_launch, gather):
-                for t, gt in zip(row, grow):
-                    dist.all_gather_into_tensor(gt, t)
-            torch.cuda.synchronize(dev)
     e2e_s = (time.perf_counter() - t0) / args.steps
     if world > 1:
         t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
@@ -264,8 +264,7 @@ def main():
     e2e_gbs = total_bytes / e2e_s / 1e9
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        finish(world, dist)
         return
 
     peak, peak_kind = measured_peaks()
@@ -282,7 +281,7 @@ def main():
             "weights": total_weights, "compressed_bytes": total_bytes,
             "bits_per_weight": 8.0 * total_bytes / max(1, total_weights),
             "row_width_hist": {str(k): v for k, v in sorted(st.width_hist.items())}, "escapes": st.n_escapes,
-            "parallelism": f"column-parallel x{world}" if world > 1 else "single GPU",
+            "parallelism": f"column/row-parallel pairs x{world}, 2 all-reduces per layer" if world > 1 else "single GPU",
             "l2": "working set (packs) far larger than L2; every step streams all of it",
             "tokens_per_s": 1e3 / ms_step * args.rows, "pack_build_s": round(t_build, 1),
         },
@@ -315,8 +314,7 @@ def main():
                                 "sample": f"layer-0 q,k,v,o packs, M=1, restore to bf16 (C restatement of the reference "
                                           f"decoder, OpenMP) + torch.matmul on CPU, {reps} repetitions in {dt:.1f} s"}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    finish(world, dist)
 
 
 if __name__ == "__main__":

@@ -58,12 +58,18 @@ DENSE_65B = StackConfig("65b-dense", 80, 8192, 8192, 1024, 28672, 1e-3, 5)
 CONFIGS = {c.name: c for c in (DENSE_9B, DENSE_27B, DENSE_65B)}
 
 
+ROW_PARALLEL = ("o", "down")      # sharded by input columns when world > 1; the others by output rows
+
+
 class LinearStack:
     """Packs of `layers` decoder layers resident on one device + activation / output buffers + a captured graph.
 
-    rank / world: the stack is sharded by OUTPUT ROWS (column-parallel): rank r holds rows [r*Q/world, (r+1)*Q/world)
-    of every projection, which for a QVB8 pack is a slice of the per-row vectors and a byte range of the ids
-    (rows are independent, reference formats/qvb8/module.py:126-160)."""
+    rank / world: q/k/v and gate/up are sharded by OUTPUT ROWS (column-parallel): rank r holds rows
+    [r*Q/world, (r+1)*Q/world), which for a QVB8 pack is a slice of the per-row vectors and a byte range of the ids
+    (rows are independent, reference formats/qvb8/module.py:126-160).  Their consumers o and down are sharded by
+    INPUT COLUMNS (row-parallel): rank r holds columns [r*P/world, (r+1)*P/world) of every row, encoded as a pack of
+    its own, reads the matching slice of the activation and produces a partial (M, Q) sum; one all-reduce per
+    column->row pair is the only exchange (two per layer)."""
 
     def __init__(self, cfg: StackConfig, M: int, device, layers: int | None = None, seed_base: int | None = None,
                  rank: int = 0, world: int = 1, policy: str = "escape_outliers", x_dtype=torch.bfloat16,
@@ -83,11 +89,17 @@ class LinearStack:
         for layer in range(self.layers):
             made = {}
             for j, (name, Q, P, xname) in enumerate(cfg.projections()):
-                if Q % world:
-                    raise ValueError(f"{name}: {Q} rows do not split over {world} ranks")
-                Qr = Q // world
                 W = synth.synth_weight(Q, P, seed_base + layer * 16 + j, device=self.device)
-                W = W[rank * Qr:(rank + 1) * Qr]
+                if name in ROW_PARALLEL:
+                    if P % (128 * world):
+                        raise ValueError(f"{name}: {P} columns do not split over {world} ranks in 128-column units")
+                    Pr = P // world
+                    W = W[:, rank * Pr:(rank + 1) * Pr].contiguous()
+                else:
+                    if Q % world:
+                        raise ValueError(f"{name}: {Q} rows do not split over {world} ranks")
+                    Qr = Q // world
+                    W = W[rank * Qr:(rank + 1) * Qr]
                 made[name] = (synth.encode_qvb8(W, tau=cfg.tau, policy=policy), xname)
                 del W
             row, done = [], set()
@@ -114,7 +126,8 @@ class LinearStack:
             del made
             self.launches.append(row)
         d, f = cfg.d_model, cfg.mlp
-        shapes = {"x_attn": d, "x_o": cfg.q_out, "x_mlp": d, "x_down": f}
+        # row-parallel projections read only this rank's slice of their input
+        shapes = {"x_attn": d, "x_o": cfg.q_out // world, "x_mlp": d, "x_down": f // world}
         self.x = {k: synth.synth_activation(self.M, p, seed=7 + i, device=self.device, dtype=x_dtype)
                   for i, (k, p) in enumerate(shapes.items())}
         # one output buffer per launch; y[layer][name] are the members' views of it
@@ -132,23 +145,35 @@ class LinearStack:
             for _, pk, *_ in row:
                 _lib.reserve_scratch(self.device, self.M, pk.Q, pk.P)
         self.graph = None
+        self.reduce = False      # all-reduce the row-parallel projections' partial sums (set by enable_collectives)
         self.launches_per_step = sum(len(row) for row in self.launches)
         self.pdl = True
         self._host_in = self._host_out = None
 
     # ---- execution ------------------------------------------------------------------------------------
+    def enable_collectives(self) -> None:
+        """The shard boundaries: after o and after down the ranks all-reduce their partial (M, d_model) sums (NCCL on
+        the compute stream, captured into the graph with the launches).  q/k/v and gate/up need no exchange: their
+        consumers work on the local slice."""
+        import torch.distributed as dist
+        self.reduce = self.world > 1 and dist.is_initialized()
+
     def run_eager(self) -> None:
         """One pass over every launch of every layer on the current stream."""
+        if self.reduce:
+            import torch.distributed as dist
         for li, row in enumerate(self.launches):
             for j, (name, pk, st, keep, xname, _) in enumerate(row):
                 _lib.small_m(st, keep, self.x[xname], out=self.y_launch[li][j], plan=keep[-1],
                              flags=_lib.FLAG_PDL if self.pdl else 0)
+                if self.reduce and name in ROW_PARALLEL:
+                    dist.all_reduce(self.y_launch[li][j])
 
     def capture(self) -> None:
         self.run_eager()                      # warm-up outside capture: shared-memory opt-in, scratch
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
             self.run_eager()
         self.graph = g
 
