@@ -56,7 +56,13 @@ constexpr int MAX_CPS = 16;               // most chunks per stage (a stage hold
 constexpr int PRODUCER_WARP = NW;         // issues the bulk copies
 constexpr int FINISHER_WARP = NW + 1;     // escape corrections, cross-warp sums, scaling, output, K-range tickets
 constexpr int PIPE_THREADS = (NW + 2) * 32;  // threads of one pipe
-constexpr int MAX_STAGES = 6;
+constexpr int MAX_STAGES = 4;
+constexpr int MAX_PIPES = 4;               // pipes per CTA at most
+#ifndef QVB8_PIPES_NT1
+#define QVB8_PIPES_NT1 4
+#endif
+constexpr int PIPES_NT1 = QVB8_PIPES_NT1;  // pipes per CTA for up to 8 tokens
+constexpr int XCH_SLOTS = (MAX_PIPES - 1) * (MAX_PIPES - 1);   // [owner pipe][contributor]
 constexpr int NCLASS = 7;                 // widths 3..8 -> class 0..5; every other width -> class 6 (per-element path)
 constexpr int64_t TICKET_BYTES = 256 * 1024;  // fixed-size counter area at the START of the scratch (one counter per
                                               // tile), so that calls of different sizes sharing one scratch never
@@ -134,8 +140,8 @@ struct Control {
     alignas(16) uint32_t pair_table[24];  // pair-conversion constants of widths 3..8 (see pair_const)
     alignas(8) uint64_t x_ready;          // every consumer warp has staged its share of the activations
     alignas(8) uint64_t sums_ready;       // every finishing warp has summed its share of the tokens
-    alignas(8) uint64_t xch_full[4];      // [owner pipe][contributor]: a contributed part of a shared tile is in place
-    PipeControl pipe[3];
+    alignas(8) uint64_t xch_full[XCH_SLOTS];   // [owner pipe][contributor]: a contributed part of a shared tile is in place
+    PipeControl pipe[MAX_PIPES];
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -167,10 +173,14 @@ __device__ __forceinline__ uint64_t global_ns() {
     return t;
 }
 // Bounded wait.  Returns false if the barrier did not complete (this waiter or another one gave up).
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+// backoff_ns > 0: the waiter is not on the critical path (a producer waiting for a free slot, a finishing warp waiting
+// for sums) and sleeps between polls, leaving the issue slots to the warps that compute.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code,
+                                            uint32_t backoff_ns) {
     const uint64_t t0 = global_ns();
     for (int i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (backoff_ns) __nanosleep(backoff_ns);
         if ((i & 7) == 7) {
             if (*abort_flag) return false;
             if (global_ns() - t0 > WAIT_LIMIT_NS) break;
@@ -180,9 +190,10 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
     atomicCAS(&g_error_word, 0, code);
     return false;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code,
+                                          uint32_t backoff_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, code);
+    return mbar_wait_slow(bar, parity, abort_flag, code, backoff_ns);
 }
 // global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned); completion is counted
 // on `bar`.  The destination is this CTA's own shared memory.
@@ -610,7 +621,7 @@ struct SmallMParams {
 
 // Pipes per CTA: a pipe is four consumer warps, a producer warp and a finishing warp with a copy ring of their own.
 // One CTA per SM; its pipes share the staged activations.
-__host__ __device__ constexpr int pipes_for(int NT) { return NT == 1 ? 3 : NT == 2 ? 2 : 1; }
+__host__ __device__ constexpr int pipes_for(int NT) { return NT == 1 ? PIPES_NT1 : NT == 2 ? 2 : 1; }
 
 // Work division.  A K-range of a tile is NSK stages long.  CTA c takes a contiguous share of whole tiles (the CTAs'
 // shares differ by at most one tile); the (tile, stage) units of the share, tile-major, are cut into equal runs, one
@@ -748,9 +759,9 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
     __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
     uint32_t *zero16 = reinterpret_cast<uint32_t *>(xs_a + (DUAL ? 2 : 1) * xs_halves);
     const int xch_floats = 16 * M;                                     // one tile's results
-    float *xch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(zero16) + 128);    // [2 owners][2 contributors][16][M]
-    float *own = xch + 4 * xch_floats;                                 // [NPIPE][16][M]: an owner's own part of its shared tile
-    const size_t shared_bytes = (size_t)(((4 + NPIPE) * xch_floats * 4 + 127) / 128 * 128);
+    float *xch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(zero16) + 128);    // [owner][contributor][16][M]
+    float *own = xch + XCH_SLOTS * xch_floats;                                 // [NPIPE][16][M]: an owner's own part of its shared tile
+    const size_t shared_bytes = (size_t)(((XCH_SLOTS + NPIPE) * xch_floats * 4 + 127) / 128 * 128);
     const size_t pipe_bytes = (size_t)nstg * p.slot_bytes + (size_t)NSIDE * SIDE_BYTES + (size_t)RED_FLOATS * 4 +
                               (size_t)((16 * M * 4 + 127) / 128 * 128);
     uint8_t *pbase = reinterpret_cast<uint8_t *>(zero16) + 128 + shared_bytes + (size_t)pipe * pipe_bytes;
@@ -778,7 +789,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
         if (tid == 0) {
             mbar_init(smem_u32(&ctl.x_ready), NW * NPIPE);
             mbar_init(smem_u32(&ctl.sums_ready), NPIPE);
-            for (int k = 0; k < 4; ++k) mbar_init(smem_u32(&ctl.xch_full[k]), 1);
+            for (int k = 0; k < XCH_SLOTS; ++k) mbar_init(smem_u32(&ctl.xch_full[k]), 1);
             ctl.abort = 0;
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -830,7 +841,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
             fetch(i + 1);                                               // next descriptor loads while this visit is issued
             // descriptor and escapes
             const int sslot = i % NSIDE;
-            if (!mbar_wait(side_empty0 + 8 * sslot, ((i / NSIDE) & 1) ^ 1u, abort_flag, 7)) { alive = false; break; }
+            if (!mbar_wait(side_empty0 + 8 * sslot, ((i / NSIDE) & 1) ^ 1u, abort_flag, 7, 200)) { alive = false; break; }
             const uint32_t sfull = side_full0 + 8 * sslot, sdst = smem_u32(side + sslot * SIDE_BYTES);
             if (lane == 0) mbar_expect_tx(sfull, (uint32_t)DESC_BYTES + ebytes);
             __syncwarp();
@@ -842,7 +853,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
             for (int s = v.sb; s < s_end; ++s) {
                 const int chunks = min(cps, NC - s * cps);
                 const uint32_t bytes_row = nocopy ? 0u : (uint32_t)(chunks * 16 * cnb);
-                if (!mbar_wait(rp.empty, rp.phase ^ 1u, abort_flag, 1)) { alive = false; break; }
+                if (!mbar_wait(rp.empty, rp.phase ^ 1u, abort_flag, 1, 100)) { alive = false; break; }
                 if (lane == 0) mbar_expect_tx(rp.full, bytes_row * (uint32_t)ccnt);
                 __syncwarp();
                 if (bytes_row && lane < ccnt) bulk_g2s(rp.data + dst_row, src, bytes_row, rp.full);
@@ -853,7 +864,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
         }
         // nothing may be in flight when the CTA exits: wait until every issued stage and side slot has been consumed
         for (int s = 0; s < nstg && alive; ++s) {
-            alive = mbar_wait(rp.empty, rp.phase ^ 1u, abort_flag, 1);
+            alive = mbar_wait(rp.empty, rp.phase ^ 1u, abort_flag, 1, 200);
             ring_advance(rp, (uint32_t)p.slot_bytes, nstg);
         }
         for (int k = 0; k < NSIDE && alive; ++k) {
@@ -931,7 +942,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
             const Visit v = run_visit(run, i);
             // ---- the tile's descriptor and escapes arrive in a side slot
             const int sslot = i % NSIDE;
-            if (alive) alive = mbar_wait(side_full0 + 8 * sslot, (i / NSIDE) & 1, abort_flag, 8);
+            if (alive) alive = mbar_wait(side_full0 + 8 * sslot, (i / NSIDE) & 1, abort_flag, 8, 200);
             const TileDesc *d = reinterpret_cast<const TileDesc *>(side + sslot * SIDE_BYTES);
             const EscEntry *ent = reinterpret_cast<const EscEntry *>(side + sslot * SIDE_BYTES + DESC_SLOT);
             int cnb = 0, myrow[2] = {-1, -1};
@@ -977,7 +988,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
             if (tracer && i == 0) trace(p.debug, 9);
             // ---- the consumer warps' partial sums (or, for a per-element tile, complete row results): taken into
             // registers and the buffer handed straight back
-            if (alive) alive = mbar_wait(smem_u32(&pc_.red_full), i & 1, abort_flag, 3);
+            if (alive) alive = mbar_wait(smem_u32(&pc_.red_full), i & 1, abort_flag, 3, 200);
             if (tracer && i == 0) trace(p.debug, 10);
             float acc[NT][4];
 #pragma unroll
@@ -1031,7 +1042,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
                     own_row[0] = myrow[0]; own_row[1] = myrow[1];
                     own_tile = v.tile;
                 } else {
-                    dst = xch + (op * 2 + (pipe - op - 1)) * xch_floats;
+                    dst = xch + (op * (MAX_PIPES - 1) + (pipe - op - 1)) * xch_floats;
                 }
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow)
@@ -1044,7 +1055,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
                         }
                 if (op != pipe) {
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl.xch_full[op * 2 + (pipe - op - 1)]));
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl.xch_full[op * (MAX_PIPES - 1) + (pipe - op - 1)]));
                 }
                 emit = false;
             }
@@ -1055,7 +1066,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
         // ---- the tile this pipe shares with later pipes: their parts have long arrived
         if (own_contrib > 0) {
             for (int j = 0; j < own_contrib; ++j)
-                if (alive) alive = mbar_wait(smem_u32(&ctl.xch_full[pipe * 2 + j]), 0, abort_flag, 9);
+                if (alive) alive = mbar_wait(smem_u32(&ctl.xch_full[pipe * (MAX_PIPES - 1) + j]), 0, abort_flag, 9);
             float y[2][NT][2];
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow)
@@ -1068,7 +1079,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
                         if (m < M) {
                             const int o = (g + 8 * hrow) * M + m;
                             val = own[pipe * xch_floats + o];
-                            for (int j = 0; j < own_contrib; ++j) val += xch[(pipe * 2 + j) * xch_floats + o];
+                            for (int j = 0; j < own_contrib; ++j) val += xch[(pipe * (MAX_PIPES - 1) + j) * xch_floats + o];
                         }
                         y[hrow][n][k] = val;
                     }
@@ -1237,7 +1248,7 @@ static_assert(sizeof(Control) <= 1024 - 64, "static shared memory allowance");
 // tuning hooks (qvb8_small_m_set_tuning): 0 = choose automatically
 static int g_fill_pct = 0, g_force_s = 0, g_force_nstg = 0, g_force_cps = 0, g_debug = 0;
 
-static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
+static Plan make_plan(int64_t M, int64_t Q, int64_t P, int max_width = 8) {
     Plan pl{};
     pl.nc_total = (int)(P / KC);
     pl.NT = (int)((M + 7) / 8);
@@ -1249,19 +1260,24 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P) {
     cps = cps / NW * NW;
     if (cps < NW) cps = NW;
     if (cps > MAX_CPS) cps = MAX_CPS;
-    pl.cps = cps;
-    pl.slot_bytes = 0;                                                  // a ring slot: 16 rows of the widest width
-    for (int nb = 3; nb <= 8; ++nb) {
-        pl.rs[nb - 3] = stage_row_stride(nb, cps);
-        if (16 * pl.rs[nb - 3] > pl.slot_bytes) pl.slot_bytes = 16 * pl.rs[nb - 3];
-    }
     // per pipe next to its ring: side ring, hand-over buffer, escape corrections
     const int64_t pipe_fixed = (int64_t)NSIDE * SIDE_BYTES + (int64_t)NW * 4 * pl.NT * 32 * 4 + (16 * M * 4 + 127) / 128 * 128;
+    const int64_t shared_fixed = 128 + ((XCH_SLOTS + npipe) * 16 * M * 4 + 127) / 128 * 128;      // zeros, exchange buffers
+    for (;; cps -= NW) {                                                // the longest stage of which two fit per pipe
+        pl.cps = cps;
+        pl.slot_bytes = 0;                                              // a ring slot: 16 rows of the widest width
+        for (int nb = 3; nb <= 8; ++nb) {
+            pl.rs[nb - 3] = stage_row_stride(nb, cps);
+            if (nb <= max_width && 16 * pl.rs[nb - 3] > pl.slot_bytes) pl.slot_bytes = 16 * pl.rs[nb - 3];
+        }
+        if (cps <= NW || cta_bytes - shared_fixed - npipe * (pipe_fixed + 2 * (int64_t)pl.slot_bytes) >=
+                             (int64_t)KC * pl.MP * 2 * cps)
+            break;
+    }
     // K-range length: what is left of the CTA's shared memory, after every pipe has a ring of three stages, holds the
     // staged activations.  The second activation layout (no byte permutes for widths 3..5) is staged only when it
     // does not shorten the K-range or the rings.
-    const int min_stages = cps > 8 ? 2 : 3;
-    const int64_t shared_fixed = 128 + ((4 + npipe) * 16 * M * 4 + 127) / 128 * 128;      // zeros, exchange buffers
+    const int min_stages = (cps > 8 || npipe > 3) ? 2 : 3;
     const int64_t xs_budget = cta_bytes - shared_fixed - npipe * (pipe_fixed + (int64_t)min_stages * pl.slot_bytes);
     const int64_t xs_one = (int64_t)P * pl.MP * 2;
     pl.dual = pl.MP <= 4 && cta_bytes - shared_fixed - npipe * (pipe_fixed + (int64_t)(min_stages + 1) * pl.slot_bytes) >= 2 * xs_one;
