@@ -124,6 +124,36 @@ int qvb8_device_status(int *status);
 int qvb8_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y,
                          void *stream);
 
+/* ---- mixture-of-experts MLP over stacked expert packs -------------------------------------------------------------
+ * Stacked layout of one projection of all E experts (reference formats/qvb8/backends_experts.py:144-196): every
+ * expert's bit-packed rows concatenated into ONE buffer (expert segments 16-byte aligned, at least 16 pad bytes after
+ * the last row), per-row metadata laid out [expert][row], bit offsets global into `ids`.  No escapes. */
+typedef struct qvb8_expert_stack {
+    const uint8_t *ids;
+    int64_t ids_bytes;
+    const float *min_s;      /* [E][Q] */
+    const float *tau_s;      /* [E][Q] */
+    const uint8_t *nbits;    /* [E][Q] */
+    const int64_t *bit_off;  /* [E][Q], bits from the start of ids, byte-aligned rows */
+    int64_t Q, P;            /* rows per expert, columns (P % 8 == 0) */
+} qvb8_expert_stack;
+
+/* out[t] = sum_j w[t,j] * down_e(act(up_e(x_t))), e = idx[t,j]  (reference qvb8_moe_experts_forward,
+ * qvb8_cuda.cu:949-992, and qvb8_moe_experts_relu2_forward, :1002-1058).
+ *   act 0: `up` is the gate_up pack (2 I rows: gate rows 0..I-1, up rows I..2I-1), H = silu(gate) * up, I = dn->P
+ *   act 1: `up` has I rows, H = relu(up)^2
+ * X (M, up->P) of x_dtype is narrowed to saturated fp16 first; idx int64 (M, topk); w fp32 (M, topk);
+ * out (M, dn->Q) of x_dtype.  Every distinct selected expert is streamed once for all the tokens that chose it.
+ * scratch: qvb8_moe_scratch_bytes(M, topk, E, up->Q, dn->Q, act) bytes, 256-byte aligned, contents don't matter.
+ * An expert index outside [0, E) never causes an out-of-range access; it leaves that token's output undefined and
+ * is reported by qvb8_moe_bad_index (which synchronises). */
+int64_t qvb8_moe_scratch_bytes(int64_t M, int64_t topk, int64_t E, int64_t Qup, int64_t Qdn, int act);
+int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t *idx, const float *w, int64_t topk, int64_t E,
+                     const qvb8_expert_stack *up, const qvb8_expert_stack *dn, int act, void *out, void *scratch,
+                     int64_t scratch_bytes, void *stream);
+int qvb8_moe_bad_index(const void *scratch, int64_t M, int64_t topk, int64_t E, int64_t Qup, int64_t Qdn, int act,
+                       int *bad);
+
 /* qvb8_small_m_ex without a scratch argument and without any allocation (no counterpart in the reference, whose
  * extension allocates its split-K buffer through torch on every call).  For callers that cannot allocate device
  * memory and have no buffer to pass: code running inside an allocator or memory-pool callback, a thread that must

@@ -18,7 +18,7 @@ _lib = None
 __all__ = [
     "build", "num_threads", "unpack_ids", "restore_f32", "decode_16", "matmul_f32w", "f32_to_f16_bits",
     "f32_to_bf16_bits", "sat_half", "rans_decode_ids", "rans_restore_f32", "slot_tables", "qvb8_dense",
-    "qvb8r_dense",
+    "qvb8r_dense", "moe_experts",
 ]
 
 
@@ -177,3 +177,30 @@ def qvb8r_dense(d: dict) -> np.ndarray:
     if len(d["esc_idx"]):
         W.reshape(-1)[np.asarray(d["esc_idx"], np.int64)] = np.asarray(d["esc_val"], np.float32)
     return W
+
+
+def moe_experts(X, idx, w, up_dense, dn_dense, act: str = "silu") -> np.ndarray:
+    """Expert MLP the grouped kernels compute (reference qvb8_cuda.cu:949-992 gated SiLU; :1002-1058 relu^2):
+    out[t] = sum_j w[t, j] * W_dn[e] @ act(W_up[e] @ x_t), e = idx[t, j], x narrowed to saturated fp16 first, the
+    hidden activations kept in full precision.  up_dense / dn_dense: per-expert restored fp32 weights (E, Q, P).
+    Accumulates in float64; returns float64 (M, Qdn)."""
+    X = np.asarray(X, dtype=np.float32)
+    xs = sat_half(X).astype(np.float64)
+    idx = np.asarray(idx)
+    w = np.asarray(w, dtype=np.float32).astype(np.float64)
+    M, topk = idx.shape
+    out = np.zeros((M, dn_dense.shape[1]), dtype=np.float64)
+    for t in range(M):
+        for j in range(topk):
+            e = int(idx[t, j])
+            y = up_dense[e].astype(np.float64) @ xs[t]
+            if act == "silu":
+                half = y.shape[0] // 2
+                g, u = y[:half], y[half:]
+                h = (g / (1.0 + np.exp(-g))) * u
+            else:
+                h = np.maximum(y, 0.0) ** 2
+            # the kernels keep h in fp32
+            h = h.astype(np.float32).astype(np.float64)
+            out[t] += w[t, j] * (dn_dense[e].astype(np.float64) @ h)
+    return out

@@ -142,6 +142,34 @@ class Qvb8Ext:
         return self._forward(X, ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals, True)
 
 
+    # ---- mixture of experts ---------------------------------------------------------------------------------
+    def moe_experts(self, X, idx, w, gu_ids, gu_min, gu_tau, gu_nb, gu_off, Qgu, Pgu,
+                    dn_ids, dn_min, dn_tau, dn_nb, dn_off, Qdn, Pdn):
+        """Gated-SiLU expert MLP over stacked packs -> (M, Qdn) in X.dtype (qvb8_cuda.cu:949-992)."""
+        if X.dim() != 2 or X.shape[1] != Pgu:
+            raise RuntimeError("moe: bad X")
+        if Qgu % 2 != 0 or Qgu // 2 != Pdn:
+            raise RuntimeError("moe: gate_up/down shapes disagree")
+        if Pgu % 8 != 0 or Pdn % 8 != 0:
+            raise RuntimeError("moe: P must be a multiple of 8")
+        up = _lib.expert_stack_struct(gu_ids, gu_min, gu_tau, gu_nb, gu_off, Qgu, Pgu)
+        dn = _lib.expert_stack_struct(dn_ids, dn_min, dn_tau, dn_nb, dn_off, Qdn, Pdn)
+        return _lib.moe_experts(X, idx, w, up, dn, 0)
+
+    def moe_experts_relu2(self, X, idx, w, up_ids, up_min, up_tau, up_nb, up_off, Qup, Pup,
+                          dn_ids, dn_min, dn_tau, dn_nb, dn_off, Qdn, Pdn):
+        """Non-gated expert MLP, H = relu(up(x))^2 -> (M, Qdn) in X.dtype (qvb8_cuda.cu:1002-1058)."""
+        if X.dim() != 2 or X.shape[1] != Pup:
+            raise RuntimeError("moe_relu2: bad X")
+        if Qup != Pdn:
+            raise RuntimeError("moe_relu2: up/down shapes disagree")
+        if Pup % 8 != 0 or Pdn % 8 != 0:
+            raise RuntimeError("moe_relu2: P must be a multiple of 8")
+        up = _lib.expert_stack_struct(up_ids, up_min, up_tau, up_nb, up_off, Qup, Pup)
+        dn = _lib.expert_stack_struct(dn_ids, dn_min, dn_tau, dn_nb, dn_off, Qdn, Pdn)
+        return _lib.moe_experts(X, idx, w, up, dn, 1)
+
+
 ext = Qvb8Ext()
 
 

@@ -24,6 +24,7 @@ EXPORTS = (
     "qvb8_last_error", "qvb8_version", "qvb8_decode", "qvb8_small_m_scratch_bytes", "qvb8_small_m",
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
+    "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
 )
 
 
@@ -34,6 +35,15 @@ class PackStruct(ctypes.Structure):
         ("tau_s", ctypes.c_void_p), ("nbits", ctypes.c_void_p), ("bit_off", ctypes.c_void_p),
         ("Q", ctypes.c_int64), ("P", ctypes.c_int64), ("esc_idx", ctypes.c_void_p), ("esc_vals", ctypes.c_void_p),
         ("n_esc", ctypes.c_int64),
+    ]
+
+
+class ExpertStackStruct(ctypes.Structure):
+    """``struct qvb8_expert_stack`` of the header."""
+    _fields_ = [
+        ("ids", ctypes.c_void_p), ("ids_bytes", ctypes.c_int64), ("min_s", ctypes.c_void_p),
+        ("tau_s", ctypes.c_void_p), ("nbits", ctypes.c_void_p), ("bit_off", ctypes.c_void_p),
+        ("Q", ctypes.c_int64), ("P", ctypes.c_int64),
     ]
 
 
@@ -72,6 +82,11 @@ def load() -> ctypes.CDLL:
             lib.qvb8_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
             lib.qvb8_debug_trace.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
             lib.qvb8_small_m_set_tuning.restype = None
+            es = ctypes.POINTER(ExpertStackStruct)
+            lib.qvb8_moe_scratch_bytes.argtypes = [i64, i64, i64, i64, i64, ci]
+            lib.qvb8_moe_scratch_bytes.restype = i64
+            lib.qvb8_moe_experts.argtypes = [vp, ci, i64, vp, vp, i64, i64, es, es, ci, vp, vp, i64, vp]
+            lib.qvb8_moe_bad_index.argtypes = [vp, i64, i64, i64, i64, i64, ci, ctypes.POINTER(ctypes.c_int)]
             _lib = lib
     return _lib
 
@@ -228,3 +243,49 @@ def small_m(pack, keep, X: torch.Tensor, x_mode: int = 0, generic: bool = False,
                                      flags, stream_ptr(dev))
     check(rc, "qvb8_small_m")
     return Y
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# mixture of experts
+
+def expert_stack_struct(ids, min_s, tau_s, nbits, bit_off, Q: int, P: int):
+    """Validated ``qvb8_expert_stack`` for stacked expert tensors on one CUDA device.  Returns (struct, keepalive)."""
+    ids = _cuda(ids, "stacked ids", torch.uint8)
+    min_s = _cuda(min_s, "stacked min_s", torch.float32)
+    tau_s = _cuda(tau_s, "stacked tau_s", torch.float32)
+    nbits = _cuda(nbits, "stacked nbits", torch.uint8)
+    bit_off = _cuda(bit_off, "stacked bit_off", torch.int64)
+    n = min_s.numel()
+    if n == 0 or n % int(Q) or tau_s.numel() != n or nbits.numel() != n or bit_off.numel() != n:
+        raise RuntimeError("qvb8_b200: stacked expert metadata must all have E * Q entries")
+    s = ExpertStackStruct(ids.data_ptr(), ids.numel(), min_s.data_ptr(), tau_s.data_ptr(), nbits.data_ptr(),
+                          bit_off.data_ptr(), int(Q), int(P))
+    return s, [ids, min_s, tau_s, nbits, bit_off], n // int(Q)
+
+
+def moe_experts(X: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, up, dn, act: int) -> torch.Tensor:
+    """(M, Qdn) in X.dtype.  `up` / `dn` = (struct, keepalive, E) from expert_stack_struct; act 0 gated SiLU, 1 relu^2."""
+    ust, ukeep, E = up
+    dst, dkeep, E2 = dn
+    if E != E2:
+        raise RuntimeError("moe: up and down stacks hold different numbers of experts")
+    dev = ukeep[0].device
+    if not X.is_cuda or X.device != dev or X.dim() != 2 or X.shape[1] != ust.P:
+        raise RuntimeError("moe: bad X")
+    if idx.dtype != torch.int64 or w.dtype != torch.float32:
+        raise RuntimeError("moe: idx must be int64 and w float32")
+    if X.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        X = X.float()
+    X, idx, w = X.contiguous(), idx.to(dev).contiguous(), w.to(dev).contiguous()
+    M, topk = idx.shape
+    if M != X.shape[0] or tuple(w.shape) != (M, topk):
+        raise RuntimeError("moe: idx / w must be (M, topk)")
+    lib = load()
+    nbytes = int(lib.qvb8_moe_scratch_bytes(M, topk, E, ust.Q, dst.Q, act))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)       # stream-ordered: torch's allocator
+    out = torch.empty((M, dst.Q), dtype=X.dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.qvb8_moe_experts(X.data_ptr(), dtype_code(X.dtype), M, idx.data_ptr(), w.data_ptr(), topk, E,
+                                   ctypes.byref(ust), ctypes.byref(dst), act, out.data_ptr(), scratch.data_ptr(),
+                                   nbytes, stream_ptr(dev)), "qvb8_moe_experts")
+    return out

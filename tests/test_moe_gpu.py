@@ -1,0 +1,101 @@
+"""Grouped expert MLP (reference qvb8_moe_experts_forward / _relu2_forward, qvb8_cuda.cu:949-1058) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from qvb8_b200 import experts, synth
+from qvb8_b200.ext_qvb8 import ext
+from util import pack_np, random_pack, rel_fro
+
+DEV = "cuda:0"
+TOL = 1e-2          # stated tolerance: relative Frobenius against the reference kernel / a dense product
+TIGHT = 2e-4        # what fp32 accumulation actually gives
+
+
+def _experts(E, Qup, P, Qdn, hidden, widths, seed):
+    ups = [random_pack(Qup, P, widths, seed=seed + e) for e in range(E)]
+    dns = [random_pack(Qdn, hidden, widths, seed=seed + 100 + e) for e in range(E)]
+    return ups, dns
+
+
+def _routing(M, E, topk, seed):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(M, E, generator=g)
+    w, idx = torch.topk(torch.softmax(logits, -1), topk, dim=-1)
+    return idx.to(torch.int64), (w / w.sum(-1, keepdim=True)).float()
+
+
+def test_stack_layout_cpu():
+    ups, _ = _experts(3, 16, 64, 64, 8, (5, 7), seed=1)
+    st = experts.stack_packs(ups)
+    assert st["min_s"].shape == (3, 16) and st["bit_off"].shape == (3, 16) and st["ids"].numel() % 16 == 0
+    for e, m in enumerate(ups):
+        base = int(st["bit_off"][e, 0]) // 8
+        assert base % 16 == 0
+        n = m.ids.numel() - 8
+        assert torch.equal(st["ids"][base:base + n], m.ids[:n])
+        assert torch.equal(st["bit_off"][e] - base * 8, m.bit_off)
+    bad = random_pack(16, 64, (7,), seed=9, esc_frac=0.01)
+    with pytest.raises(ValueError):
+        experts.stack_packs([ups[0], bad])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("act", ["silu", "relu2"])
+@pytest.mark.parametrize("M,dtype", [(1, torch.bfloat16), (5, torch.float16), (19, torch.float32)])
+def test_moe_matches_oracle(cuda_lib, act, M, dtype):
+    E, topk, P, hidden, Qdn = 10, 3, 256, 96, 256
+    Qup = 2 * hidden if act == "silu" else hidden
+    ups, dns = _experts(E, Qup, P, Qdn, hidden, (4, 6, 7, 8, 10), seed=40 + M)
+    mod = experts.QVBandExpertsV8([u.to(DEV) for u in ups], [d.to(DEV) for d in dns], num_experts=E, act=act)
+    idx, w = _routing(M, E, topk, seed=M)
+    X = synth.synth_activation(M, P, seed=3, device=DEV, dtype=dtype) * 0.5
+    out = mod(X, idx.to(DEV), w.to(DEV))
+    assert out.dtype == dtype and tuple(out.shape) == (M, Qdn)
+    upd = np.stack([oracle.qvb8_dense(pack_np(u)) for u in ups])
+    dnd = np.stack([oracle.qvb8_dense(pack_np(d)) for d in dns])
+    want = oracle.moe_experts(X.float().cpu().numpy(), idx.numpy(), w.numpy(), upd, dnd, act)
+    err = rel_fro(out.float().cpu().numpy(), want)
+    tol = TIGHT if dtype == torch.float32 else 6e-3          # bf16 / fp16 outputs carry their own rounding
+    assert err < TOL and err < tol, err
+    again = mod(X, idx.to(DEV), w.to(DEV))
+    assert torch.equal(out, again)                           # fixed summation order
+
+
+@pytest.mark.gpu
+def test_moe_config_shape_and_bad_index(cuda_lib):
+    """The benchmark's expert shapes (d_model 2048, expert FFN 768) at a few tokens; an out-of-range expert index is
+    reported and touches nothing out of range."""
+    from qvb8_b200 import lib
+    E, topk, P, hidden = 16, 8, 2048, 768
+    ups, dns = _experts(E, 2 * hidden, P, P, hidden, (6, 7), seed=7)
+    mod = experts.QVBandExpertsV8([u.to(DEV) for u in ups], [d.to(DEV) for d in dns], num_experts=E)
+    M = 8
+    idx, w = _routing(M, E, topk, seed=11)
+    X = synth.synth_activation(M, P, seed=5, device=DEV) * 0.25
+    out = mod(X, idx.to(DEV), w.to(DEV))
+    upd = np.stack([oracle.qvb8_dense(pack_np(u)) for u in ups])
+    dnd = np.stack([oracle.qvb8_dense(pack_np(d)) for d in dns])
+    want = oracle.moe_experts(X.float().cpu().numpy(), idx.numpy(), w.numpy(), upd, dnd, "silu")
+    assert rel_fro(out.float().cpu().numpy(), want) < 6e-3
+    # bad index
+    L = lib.load()
+    u, d = mod.up, mod.down
+    ust = lib.expert_stack_struct(u["ids"], u["min_s"], u["tau_s"], u["nbits"], u["bit_off"], u["Q"], u["P"])
+    dst = lib.expert_stack_struct(d["ids"], d["min_s"], d["tau_s"], d["nbits"], d["bit_off"], d["Q"], d["P"])
+    bad_idx = idx.clone()
+    bad_idx[0, 0] = E + 5
+    import ctypes
+    nbytes = int(L.qvb8_moe_scratch_bytes(M, topk, E, u["Q"], d["Q"], 0))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+    o = torch.empty(M, d["Q"], dtype=X.dtype, device=DEV)
+    bi, wd = bad_idx.to(DEV), w.to(DEV)
+    rc = L.qvb8_moe_experts(X.data_ptr(), lib.dtype_code(X.dtype), M, bi.data_ptr(), wd.data_ptr(), topk, E,
+                            ctypes.byref(ust[0]), ctypes.byref(dst[0]), 0, o.data_ptr(), scratch.data_ptr(), nbytes,
+                            lib.stream_ptr(torch.device(DEV)))
+    assert rc == 0
+    flag = ctypes.c_int(0)
+    assert L.qvb8_moe_bad_index(scratch.data_ptr(), M, topk, E, u["Q"], d["Q"], 0, ctypes.byref(flag)) == 0
+    assert flag.value == 1
+    assert lib.device_status() == 0
