@@ -144,15 +144,48 @@ typedef struct qvb8_expert_stack {
  *   act 1: `up` has I rows, H = relu(up)^2
  * X (M, up->P) of x_dtype is narrowed to saturated fp16 first; idx int64 (M, topk); w fp32 (M, topk);
  * out (M, dn->Q) of x_dtype.  Every distinct selected expert is streamed once for all the tokens that chose it.
- * scratch: qvb8_moe_scratch_bytes(M, topk, E, up->Q, dn->Q, act) bytes, 256-byte aligned, contents don't matter.
+ * scratch: qvb8_moe_scratch_bytes(M, topk, E, up->P, up->Q, dn->Q, act) bytes, 256-byte aligned, contents don't matter.
  * An expert index outside [0, E) never causes an out-of-range access; it leaves that token's output undefined and
  * is reported by qvb8_moe_bad_index (which synchronises). */
-int64_t qvb8_moe_scratch_bytes(int64_t M, int64_t topk, int64_t E, int64_t Qup, int64_t Qdn, int act);
+int64_t qvb8_moe_scratch_bytes(int64_t M, int64_t topk, int64_t E, int64_t Pup, int64_t Qup, int64_t Qdn, int act);
 int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t *idx, const float *w, int64_t topk, int64_t E,
                      const qvb8_expert_stack *up, const qvb8_expert_stack *dn, int act, void *out, void *scratch,
                      int64_t scratch_bytes, void *stream);
-int qvb8_moe_bad_index(const void *scratch, int64_t M, int64_t topk, int64_t E, int64_t Qup, int64_t Qdn, int act,
-                       int *bad);
+int qvb8_moe_bad_index(const void *scratch, int64_t M, int64_t topk, int64_t E, int64_t Pup, int64_t Qup, int64_t Qdn,
+                       int act, int *bad);
+
+/* ---- QVB8R: entropy-coded QVB8 (rANS) ------------------------------------------------------------------------------
+ * The arrays a reader builds at load from a .qvb8r file (reference formats/qvb8r/container.py:52-89 runtime_tables,
+ * blocks_for; the "core" arguments of every qvb8r_cuda entry point, qvb8r_cuda.cu:322-335).  All device pointers. */
+typedef struct qvb8r_pack {
+    const uint32_t *words;    /* the word stream followed by at least 2048 zero words (readers fetch ahead) */
+    const int64_t *tile_off;  /* [n_tiles + 1] first word of each tile */
+    const uint64_t *states;   /* [n_tiles][32] initial rANS states */
+    const int64_t *tiles;     /* [n_tiles][3] class, first sorted row, rows */
+    int64_t n_tiles;
+    const int32_t *blocks;    /* [n_blocks][3] class, first tile, tiles (<= 8): runs of same-class tiles */
+    int64_t n_blocks;
+    const uint32_t *tab;      /* [K][4096] slot tables: symbol | offset << 11 | (freq - 1) << 22 */
+    const int32_t *perm;      /* [Q] sorted row -> original row */
+    const float *min_s;       /* [Q] by original row */
+    const float *tau_s;       /* [Q] */
+    const int32_t *drow;      /* [Q] id = symbol + drow[row] */
+    int64_t Q, P;             /* P % 64 == 0 */
+} qvb8r_pack;
+
+/* every id, (Q, P) int16 in original row order (reference `ids`, qvb8r_cuda.cu:351-363) */
+int qvb8r_ids(const qvb8r_pack *w, int16_t *out, void *stream);
+/* dense rows of blocks [b0, b0 + nb): T(fma(id, tau_s, min_s)), out_dtype QVB8_F16 / QVB8_BF16 / QVB8_F32.
+ * row_base < 0: each row at its ORIGINAL index of a (Q, P) output; row_base >= 0: at its sorted position - row_base
+ * (a block range fills a compact chunk).  (reference `decode`, :272-308, :414-432) */
+int qvb8r_decode(const qvb8r_pack *w, int out_dtype, void *out, int64_t b0, int64_t nb, int64_t row_base, void *stream);
+/* Y (M, Q) fp32 = X (M, P) @ W^T, 1 <= M <= 16, band part only (escapes: qvb8r_fix_escapes).  round_w_fp16 = 0: fp32
+ * band value (reference `gemv` / `multi`, fp32 or bf16 X); 1: band value rounded once to fp16 (reference `tc`, fp16 X). */
+int qvb8r_small_m(const qvb8r_pack *w, const void *X, int x_dtype, int64_t M, int round_w_fp16, float *Y, void *stream);
+/* Y[m, uq[u]] += sum over e in [ptr[u], ptr[u+1]) of X[m, ec[e]] * ed[e], in stored order (reference `fix_escapes`,
+ * :310-320, :434-444): X (M, P) fp32, Y (M, Q) fp32, U outputs that have escapes. */
+int qvb8r_fix_escapes(const float *X, const int64_t *uq, const int64_t *ptr, const int64_t *ec, const float *ed, float *Y,
+                      int64_t U, int64_t M, int64_t P, int64_t Q, void *stream);
 
 /* qvb8_small_m_ex without a scratch argument and without any allocation (no counterpart in the reference, whose
  * extension allocates its split-K buffer through torch on every call).  For callers that cannot allocate device

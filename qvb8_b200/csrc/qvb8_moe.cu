@@ -28,9 +28,21 @@ struct MoeRoute {                          // device tables built by the route k
     int *bad;                              // [1] set when an expert index is out of range
 };
 
-// One block.  Thread e scans the pairs for expert e (at most a few hundred pairs): deterministic, no atomics.
+// Block 0: thread e scans the pairs for expert e (at most a few hundred pairs): deterministic, no atomics.
+// Blocks 1..: the activations once as fp32 values of their saturated-fp16 narrowing (what every row product reads,
+// qvb8_cuda.cu:963 `saturating_half(X).to(float)`).
 __global__ void __launch_bounds__(256) moe_route_kernel(const int64_t *__restrict__ idx, int npairs, int E, int M,
-                                                        MoeRoute r) {
+                                                        MoeRoute r, const void *__restrict__ X, int x_dtype, int64_t nx,
+                                                        float *__restrict__ Xf) {
+    if (blockIdx.x > 0) {
+        for (int64_t i = (int64_t)(blockIdx.x - 1) * blockDim.x + threadIdx.x; i < nx; i += (int64_t)(gridDim.x - 1) * blockDim.x) {
+            const float v = x_dtype == QVB8_F32 ? __ldg(reinterpret_cast<const float *>(X) + i)
+                          : x_dtype == QVB8_BF16 ? __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16 *>(X) + i))
+                                                 : __half2float(__ldg(reinterpret_cast<const __half *>(X) + i));
+            Xf[i] = __half2float(sat_half(v));
+        }
+        return;
+    }
     __shared__ int any_bad;
     if (threadIdx.x == 0) any_bad = 0;
     __syncthreads();
@@ -55,8 +67,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const int64_t *__restric
 }
 
 struct MoeRows {
-    const void *X;             // ACT 0/1: (M, P) activations of x_dtype, by token; ACT 2: (npairs, P) fp32, by pair
-    int x_dtype, topk;
+    const float *X;            // ACT 0/1: (M, P) narrowed activations, by token; ACT 2: (npairs, P) hidden, by pair
+    int topk;
     const uint8_t *ids;
     const float *min_s, *tau_s;   // [E][Q]
     const uint8_t *nbits;
@@ -77,119 +89,124 @@ __device__ __forceinline__ uint64_t load_8_fields(const uint8_t *__restrict__ id
     return sh ? (lo >> sh) | (hi << (64 - sh)) : lo;
 }
 
-__device__ __forceinline__ void load_x8_any(const void *__restrict__ X, int x_dtype, int64_t off, bool narrow_x, float (&x)[8]) {
-    if (x_dtype == QVB8_F32) {
-        const float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(X) + off));
-        const float4 b = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(X) + off) + 1);
-        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-    } else {
-        const uint4 u = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(X) + off));
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            if (x_dtype == QVB8_BF16) {
-                x[2 * k] = __uint_as_float(w[k] << 16);
-                x[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
-            } else {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
-                x[2 * k] = f.x; x[2 * k + 1] = f.y;
-            }
-        }
-    }
-    if (narrow_x) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) x[k] = __half2float(sat_half(x[k]));
-    }
+__device__ __forceinline__ void load_x8(const float *__restrict__ X, int64_t off, float (&x)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(X + off));
+    const float4 b = __ldg(reinterpret_cast<const float4 *>(X + off) + 1);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
 }
 
 // ACT: 0 = gated SiLU (rows i and I + i of the up pack -> H[p, i] = silu(g) * u), 1 = relu^2 (row i -> H[p, i]),
 // 2 = none (row d of the down pack, X by pair -> Y[p, d]).
+struct MoeRowMeta {
+    int nb;
+    int64_t bit0;
+    float ms, ts;
+};
+__device__ __forceinline__ MoeRowMeta moe_row_meta(const MoeRows &p, size_t mi) {
+    MoeRowMeta m;
+    m.nb = __ldg(p.nbits + mi);
+    m.bit0 = __ldg(p.bit_off + mi);
+    m.ms = __ldg(p.min_s + mi);
+    m.ts = __ldg(p.tau_s + mi);
+    return m;
+}
+
 template <int ACT>
-__global__ void __launch_bounds__(MOE_WARPS * 32) moe_rows_kernel(const MoeRows p) {
+__global__ void __launch_bounds__(MOE_WARPS * 32, 2) moe_rows_kernel(const MoeRows p) {
     const int s = blockIdx.y;
     if (s >= *p.route.nslots) return;
     const int e = p.route.slots[s];
     const int c = p.route.counts[e];
     const int *plist = p.route.lists + (size_t)e * p.M;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = blockIdx.x * MOE_WARPS + warp;
-    if (r >= p.R) return;
+    const int wstride = gridDim.x * MOE_WARPS;
     constexpr int NR = ACT == 0 ? 2 : 1;
-    int nb[NR];
-    int64_t byte0[NR], bit0[NR];
-    float ms[NR], ts[NR];
+    int r = blockIdx.x * MOE_WARPS + warp;
+    if (r >= p.R) return;
+    MoeRowMeta nxt[NR];
 #pragma unroll
-    for (int k = 0; k < NR; ++k) {
-        const size_t mi = (size_t)e * p.Q + r + (size_t)k * p.R;
-        nb[k] = __ldg(p.nbits + mi);
-        bit0[k] = __ldg(p.bit_off + mi);
-        byte0[k] = bit0[k] >> 3;
-        ms[k] = __ldg(p.min_s + mi);
-        ts[k] = __ldg(p.tau_s + mi);
-    }
-    const bool narrow_x = ACT != 2;
-    for (int g0 = 0; g0 < c; g0 += MOE_TOK) {
-        const int nt = min(MOE_TOK, c - g0);
-        int64_t xrow[MOE_TOK];
+    for (int k = 0; k < NR; ++k) nxt[k] = moe_row_meta(p, (size_t)e * p.Q + r + (size_t)k * p.R);
+    for (; r < p.R; r += wstride) {
+        MoeRowMeta m[NR];
 #pragma unroll
-        for (int j = 0; j < MOE_TOK; ++j) {
-            const int pp = plist[g0 + (j < nt ? j : 0)];
-            xrow[j] = (int64_t)(ACT == 2 ? pp : pp / p.topk) * p.P;
+        for (int k = 0; k < NR; ++k) m[k] = nxt[k];
+        if (r + wstride < p.R) {                                       // the next row's metadata loads under this row's work
+#pragma unroll
+            for (int k = 0; k < NR; ++k) nxt[k] = moe_row_meta(p, (size_t)e * p.Q + r + wstride + (size_t)k * p.R);
         }
-        float acc[NR][MOE_TOK];
+        for (int g0 = 0; g0 < c; g0 += MOE_TOK) {
+            const int nt = min(MOE_TOK, c - g0);
+            float acc[NR][MOE_TOK];
 #pragma unroll
-        for (int k = 0; k < NR; ++k)
+            for (int k = 0; k < NR; ++k)
 #pragma unroll
-            for (int j = 0; j < MOE_TOK; ++j) acc[k][j] = 0.f;
-        for (int col = lane * 8; col < p.P; col += 256) {
-            float wv[NR][8];
+                for (int j = 0; j < MOE_TOK; ++j) acc[k][j] = 0.f;
+            const bool fast = NR == 1 ? (m[0].nb <= 8 && (m[0].bit0 & 7) == 0)
+                                      : (m[0].nb <= 8 && (m[0].bit0 & 7) == 0 && m[NR - 1].nb <= 8 && (m[NR - 1].bit0 & 7) == 0);
+            constexpr int UN = 4;                                       // 256-column blocks whose ids are fetched together
+            for (int col0 = lane * 8; col0 < p.P; col0 += 256 * UN) {
+                uint64_t v[NR][UN];
+                if (fast) {                                             // all the row bytes of this step in flight at once
 #pragma unroll
-            for (int k = 0; k < NR; ++k) {
-                if (nb[k] <= 8 && (bit0[k] & 7) == 0) {
-                    const uint64_t v = load_8_fields(p.ids, byte0[k] + (int64_t)(col >> 3) * nb[k]);
-                    const uint32_t mask = (1u << nb[k]) - 1u;
+                    for (int u = 0; u < UN; ++u)
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) wv[k][i] = band((uint32_t)(v >> (i * nb[k])) & mask, ts[k], ms[k]);
-                } else {
+                        for (int k = 0; k < NR; ++k) {
+                            const int col = col0 + 256 * u;
+                            v[k][u] = col < p.P ? load_8_fields(p.ids, (m[k].bit0 >> 3) + (int64_t)(col >> 3) * m[k].nb) : 0ull;
+                        }
+                }
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        wv[k][i] = band(field_bytes(p.ids, bit0[k] + (int64_t)(col + i) * nb[k], nb[k]), ts[k], ms[k]);
+                for (int u = 0; u < UN; ++u) {
+                    const int col = col0 + 256 * u;
+                    if (col >= p.P) break;
+                    float wv[NR][8];
+#pragma unroll
+                    for (int k = 0; k < NR; ++k) {
+                        if (fast) {
+                            const uint32_t mask = (1u << m[k].nb) - 1u;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                wv[k][i] = __fmaf_rn(small_u2f((uint32_t)(v[k][u] >> (i * m[k].nb)) & mask), m[k].ts, m[k].ms);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                wv[k][i] = band(field_bytes(p.ids, m[k].bit0 + (int64_t)(col + i) * m[k].nb, m[k].nb), m[k].ts, m[k].ms);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < MOE_TOK; ++j) {
+                        if (j < nt) {
+                            const int pp = plist[g0 + j];
+                            float x[8];
+                            load_x8(p.X, (int64_t)(ACT == 2 ? pp : pp / p.topk) * p.P + col, x);
+#pragma unroll
+                            for (int k = 0; k < NR; ++k)
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) acc[k][j] = __fmaf_rn(x[i], wv[k][i], acc[k][j]);
+                        }
+                    }
                 }
             }
 #pragma unroll
             for (int j = 0; j < MOE_TOK; ++j) {
-                if (j < nt) {
-                    float x[8];
-                    load_x8_any(p.X, ACT == 2 ? QVB8_F32 : p.x_dtype, xrow[j] + col, narrow_x, x);
+                if (j < nt) {                                           // warp-uniform
 #pragma unroll
                     for (int k = 0; k < NR; ++k)
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[k][j] = __fmaf_rn(x[i], wv[k][i], acc[k][j]);
-                }
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < NR; ++k)
-#pragma unroll
-            for (int j = 0; j < MOE_TOK; ++j)
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) acc[k][j] += __shfl_xor_sync(0xffffffffu, acc[k][j], o);
-        if (lane == 0) {
-#pragma unroll
-            for (int j = 0; j < MOE_TOK; ++j) {
-                if (j < nt) {
-                    const int pp = plist[g0 + j];
-                    float v;
-                    if (ACT == 0) {
-                        const float gt = acc[0][j];
-                        v = (gt / (1.0f + __expf(-gt))) * acc[NR - 1][j];
-                    } else if (ACT == 1) {
-                        const float u = fmaxf(acc[0][j], 0.f);
-                        v = u * u;
-                    } else {
-                        v = acc[0][j];
+                        for (int o = 16; o > 0; o >>= 1) acc[k][j] += __shfl_xor_sync(0xffffffffu, acc[k][j], o);
+                    if (lane == 0) {
+                        float v;
+                        if (ACT == 0) {
+                            const float gt = acc[0][j];
+                            v = (gt / (1.0f + __expf(-gt))) * acc[NR - 1][j];
+                        } else if (ACT == 1) {
+                            const float u = fmaxf(acc[0][j], 0.f);
+                            v = u * u;
+                        } else {
+                            v = acc[0][j];
+                        }
+                        p.out[(size_t)plist[g0 + j] * p.R + r] = v;
                     }
-                    p.out[(size_t)pp * p.R + r] = v;
                 }
             }
         }
@@ -208,9 +225,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restric
 }
 
 struct MoeScratch {
-    int64_t counts, lists, slots, nslots, bad, H, Yd, total;
+    int64_t counts, lists, slots, nslots, bad, Xf, H, Yd, total;
 };
-static MoeScratch moe_scratch(int64_t M, int64_t topk, int64_t E, int64_t R_up, int64_t Qdn) {
+static MoeScratch moe_scratch(int64_t M, int64_t topk, int64_t E, int64_t Pup, int64_t R_up, int64_t Qdn) {
     MoeScratch s{};
     const int64_t npairs = M * topk;
     auto up = [](int64_t v) { return (v + 255) / 256 * 256; };
@@ -219,7 +236,8 @@ static MoeScratch moe_scratch(int64_t M, int64_t topk, int64_t E, int64_t R_up, 
     s.slots = s.lists + up(E * M * 4);
     s.nslots = s.slots + up(E * 4);
     s.bad = s.nslots + 256;
-    s.H = s.bad + 256;
+    s.Xf = s.bad + 256;
+    s.H = s.Xf + up(M * Pup * 4);
     s.Yd = s.H + up(npairs * R_up * 4);
     s.total = s.Yd + up(npairs * Qdn * 4);
     return s;
@@ -236,9 +254,9 @@ static int check_stack(const qvb8_expert_stack *st, const char *who) {
 
 }  // namespace qv
 
-QV_API int64_t qvb8_moe_scratch_bytes(int64_t M, int64_t topk, int64_t E, int64_t Qup, int64_t Qdn, int act) {
-    if (M <= 0 || topk <= 0 || E <= 0 || Qup <= 0 || Qdn <= 0) return 0;
-    return qv::moe_scratch(M, topk, E, act == 0 ? Qup / 2 : Qup, Qdn).total;
+QV_API int64_t qvb8_moe_scratch_bytes(int64_t M, int64_t topk, int64_t E, int64_t Pup, int64_t Qup, int64_t Qdn, int act) {
+    if (M <= 0 || topk <= 0 || E <= 0 || Pup <= 0 || Qup <= 0 || Qdn <= 0) return 0;
+    return qv::moe_scratch(M, topk, E, Pup, act == 0 ? Qup / 2 : Qup, Qdn).total;
 }
 
 QV_API int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t *idx, const float *w, int64_t topk,
@@ -257,7 +275,7 @@ QV_API int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t
     if (act == 0 && up->Q % 2 != 0) return fail(QVB8_ERR_ARG, "%s: gate_up must have an even number of rows", who);
     if (R_up != dn->P) return fail(QVB8_ERR_ARG, "%s: up and down shapes disagree (%lld hidden vs %lld columns)", who, (long long)R_up, (long long)dn->P);
     if (!aligned(X, 16)) return fail(QVB8_ERR_ALIGN, "%s: X must be 16-byte aligned", who);
-    const MoeScratch L = moe_scratch(M, topk, E, R_up, dn->Q);
+    const MoeScratch L = moe_scratch(M, topk, E, up->P, R_up, dn->Q);
     if (!scratch || scratch_bytes < L.total || !aligned(scratch, 256))
         return fail(QVB8_ERR_SCRATCH, "%s: scratch of %lld bytes (256-byte aligned) needed, %lld given", who, (long long)L.total, (long long)scratch_bytes);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -266,19 +284,27 @@ QV_API int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t
                    reinterpret_cast<int *>(base + L.slots), reinterpret_cast<int *>(base + L.nslots),
                    reinterpret_cast<int *>(base + L.bad)};
     const int npairs = (int)(M * topk);
-    moe_route_kernel<<<1, 256, 0, st>>>(idx, npairs, (int)E, (int)M, route);
+    float *Xf = reinterpret_cast<float *>(base + L.Xf);
+    const int64_t nx = M * up->P;
+    moe_route_kernel<<<1 + (unsigned)((nx + 2047) / 2048), 256, 0, st>>>(idx, npairs, (int)E, (int)M, route, X, x_dtype, nx, Xf);
     if (int rc = cuda_status("qvb8_moe route")) return rc;
     const int max_slots = (int)(E < npairs ? E : npairs);
     float *H = reinterpret_cast<float *>(base + L.H), *Yd = reinterpret_cast<float *>(base + L.Yd);
-    MoeRows a{X, x_dtype, (int)topk, up->ids, up->min_s, up->tau_s, up->nbits, up->bit_off, (int)up->Q, (int)up->P,
+    MoeRows a{Xf, (int)topk, up->ids, up->min_s, up->tau_s, up->nbits, up->bit_off, (int)up->Q, (int)up->P,
               (int)R_up, H, route, (int)M};
-    const dim3 gu((unsigned)((R_up + MOE_WARPS - 1) / MOE_WARPS), (unsigned)max_slots);
+    // a few CTAs per expert, every warp walking several rows: short rows (a kilobyte or two) would otherwise be all
+    // start-up latency
+    auto row_blocks = [&](int64_t rows) {                              // about eight CTAs per SM over all experts
+        const int64_t all = (rows + MOE_WARPS - 1) / MOE_WARPS, want = (1184 + max_slots - 1) / max_slots;
+        return (unsigned)(all < want ? all : (want < 4 ? 4 : want));
+    };
+    const dim3 gu(row_blocks(R_up), (unsigned)max_slots);
     if (act == 0) moe_rows_kernel<0><<<gu, MOE_WARPS * 32, 0, st>>>(a);
     else moe_rows_kernel<1><<<gu, MOE_WARPS * 32, 0, st>>>(a);
     if (int rc = cuda_status("qvb8_moe up")) return rc;
-    MoeRows b{H, QVB8_F32, (int)topk, dn->ids, dn->min_s, dn->tau_s, dn->nbits, dn->bit_off, (int)dn->Q, (int)dn->P,
+    MoeRows b{H, (int)topk, dn->ids, dn->min_s, dn->tau_s, dn->nbits, dn->bit_off, (int)dn->Q, (int)dn->P,
               (int)dn->Q, Yd, route, (int)M};
-    const dim3 gd((unsigned)((dn->Q + MOE_WARPS - 1) / MOE_WARPS), (unsigned)max_slots);
+    const dim3 gd(row_blocks(dn->Q), (unsigned)max_slots);
     moe_rows_kernel<2><<<gd, MOE_WARPS * 32, 0, st>>>(b);
     if (int rc = cuda_status("qvb8_moe down")) return rc;
     const dim3 gc((unsigned)((dn->Q + 255) / 256), (unsigned)M);
@@ -293,11 +319,11 @@ QV_API int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t
 
 // Expert index check of the last qvb8_moe_experts call that used `scratch` (after the stream has run it):
 // 1 if an index was outside [0, E).  Synchronises the host.
-QV_API int qvb8_moe_bad_index(const void *scratch, int64_t M, int64_t topk, int64_t E, int64_t Qup, int64_t Qdn, int act,
-                              int *bad) {
+QV_API int qvb8_moe_bad_index(const void *scratch, int64_t M, int64_t topk, int64_t E, int64_t Pup, int64_t Qup, int64_t Qdn,
+                              int act, int *bad) {
     using namespace qv;
     if (!scratch || !bad) return fail(QVB8_ERR_ARG, "qvb8_moe_bad_index: null argument");
-    const MoeScratch L = moe_scratch(M, topk, E, act == 0 ? Qup / 2 : Qup, Qdn);
+    const MoeScratch L = moe_scratch(M, topk, E, Pup, act == 0 ? Qup / 2 : Qup, Qdn);
     if (cudaMemcpy(bad, reinterpret_cast<const uint8_t *>(scratch) + L.bad, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
         return cuda_status("qvb8_moe_bad_index");
     return QVB8_OK;

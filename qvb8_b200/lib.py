@@ -25,6 +25,7 @@ EXPORTS = (
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
+    "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes",
 )
 
 
@@ -44,6 +45,16 @@ class ExpertStackStruct(ctypes.Structure):
         ("ids", ctypes.c_void_p), ("ids_bytes", ctypes.c_int64), ("min_s", ctypes.c_void_p),
         ("tau_s", ctypes.c_void_p), ("nbits", ctypes.c_void_p), ("bit_off", ctypes.c_void_p),
         ("Q", ctypes.c_int64), ("P", ctypes.c_int64),
+    ]
+
+
+class RPackStruct(ctypes.Structure):
+    """``struct qvb8r_pack`` of the header."""
+    _fields_ = [
+        ("words", ctypes.c_void_p), ("tile_off", ctypes.c_void_p), ("states", ctypes.c_void_p),
+        ("tiles", ctypes.c_void_p), ("n_tiles", ctypes.c_int64), ("blocks", ctypes.c_void_p),
+        ("n_blocks", ctypes.c_int64), ("tab", ctypes.c_void_p), ("perm", ctypes.c_void_p), ("min_s", ctypes.c_void_p),
+        ("tau_s", ctypes.c_void_p), ("drow", ctypes.c_void_p), ("Q", ctypes.c_int64), ("P", ctypes.c_int64),
     ]
 
 
@@ -83,10 +94,15 @@ def load() -> ctypes.CDLL:
             lib.qvb8_debug_trace.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
             lib.qvb8_small_m_set_tuning.restype = None
             es = ctypes.POINTER(ExpertStackStruct)
-            lib.qvb8_moe_scratch_bytes.argtypes = [i64, i64, i64, i64, i64, ci]
+            rp = ctypes.POINTER(RPackStruct)
+            lib.qvb8r_ids.argtypes = [rp, vp, vp]
+            lib.qvb8r_decode.argtypes = [rp, ci, vp, i64, i64, i64, vp]
+            lib.qvb8r_small_m.argtypes = [rp, vp, ci, i64, ci, vp, vp]
+            lib.qvb8r_fix_escapes.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]
+            lib.qvb8_moe_scratch_bytes.argtypes = [i64, i64, i64, i64, i64, i64, ci]
             lib.qvb8_moe_scratch_bytes.restype = i64
             lib.qvb8_moe_experts.argtypes = [vp, ci, i64, vp, vp, i64, i64, es, es, ci, vp, vp, i64, vp]
-            lib.qvb8_moe_bad_index.argtypes = [vp, i64, i64, i64, i64, i64, ci, ctypes.POINTER(ctypes.c_int)]
+            lib.qvb8_moe_bad_index.argtypes = [vp, i64, i64, i64, i64, i64, i64, ci, ctypes.POINTER(ctypes.c_int)]
             _lib = lib
     return _lib
 
@@ -281,7 +297,7 @@ def moe_experts(X: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, up, dn, act
     if M != X.shape[0] or tuple(w.shape) != (M, topk):
         raise RuntimeError("moe: idx / w must be (M, topk)")
     lib = load()
-    nbytes = int(lib.qvb8_moe_scratch_bytes(M, topk, E, ust.Q, dst.Q, act))
+    nbytes = int(lib.qvb8_moe_scratch_bytes(M, topk, E, ust.P, ust.Q, dst.Q, act))
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)       # stream-ordered: torch's allocator
     out = torch.empty((M, dst.Q), dtype=X.dtype, device=dev)
     with torch.cuda.device(dev):

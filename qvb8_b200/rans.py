@@ -1,0 +1,177 @@
+"""QVB8R (entropy-coded QVB8): a seeded synthetic encoder and the tables a reader builds at load.
+
+The reference ships only the READER of this format (formats/qvb8r/codec.py:1 "the pack writer / calibration is not
+included"; its C++ ``encode`` is the inverse walk of ``embed_rows``, qvb8r_cpu.cpp:60-110).  This module restates the
+writer from the reader's contract so that seeded packs exist to test and time the kernels on:
+
+  stream  a tile = `rows` consecutive sorted rows of one class, 32 interleaved 64-bit rANS states; state j codes
+          column 32 * step + j; symbols go in pairs; after a lane decoded two symbols a state below 2^32 takes the
+          tile's next 32-bit word, lanes in ascending order (qvb8r_cuda.cu:36-75, qvb8r_cpu.cpp:13-58)
+  symbol  s = id - drow[row] in [0, N), N <= 2048; rows are coded centred: drow places the row's median id at CENTRE
+          (codec.py:4-9)
+  model   K classes of rows, one frequency table per class, sum 4096, every frequency <= 1024 (it is stored as F - 1
+          in 10 bits of the slot entry, codec.py:11-20)
+
+The encoder runs the decoder backwards: rows, step pairs and lanes in reverse; before coding a pair (F1, F2) a state
+x >= (F1 * F2) << 40 emits its low 32 bits (exactly the states the decoder refills after that pair).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+PB = 12
+MQ = 1 << PB
+MAX_ID = 2048
+MAX_FREQ = 1024
+CENTRE = 256
+PAD_WORDS = 2048
+
+
+def slot_tables(freq: np.ndarray) -> np.ndarray:
+    """(K, N) frequencies -> (K, 4096) slot entries ``symbol | offset << 11 | (F - 1) << 22`` (codec.py:11-20)."""
+    F = np.asarray(freq, np.int64)
+    K, N = F.shape
+    tab = np.zeros((K, MQ), np.uint32)
+    for k in range(K):
+        if int(F[k].sum()) != MQ or int(F[k].max()) > MAX_FREQ:
+            raise ValueError("frequencies of a class must sum to 4096 with every entry <= 1024")
+        sym = np.repeat(np.arange(N, dtype=np.int64), F[k])
+        start = np.cumsum(F[k]) - F[k]
+        tab[k] = (sym | ((np.arange(MQ, dtype=np.int64) - start[sym]) << 11) | ((F[k][sym] - 1) << 22)).astype(np.uint32)
+    return tab
+
+
+def quantise_freq(hist: np.ndarray) -> np.ndarray:
+    """Symbol counts -> frequencies that sum to 4096, >= 1 for every symbol that occurs, <= 1024 for all."""
+    h = np.asarray(hist, np.float64)
+    present = h > 0
+    if not present.any():
+        raise ValueError("empty histogram")
+    f = np.zeros(h.shape, np.int64)
+    f[present] = np.clip(np.floor(h[present] / h.sum() * MQ), 1, MAX_FREQ).astype(np.int64)
+    # hand the rounding remainder out (or take it back) one count at a time, largest symbols first
+    order = np.argsort(-h, kind="stable")
+    diff = MQ - int(f.sum())
+    guard = 0
+    while diff != 0:
+        moved = False
+        for s in order:
+            if diff == 0:
+                break
+            if not present[s]:
+                continue
+            if diff > 0 and f[s] < MAX_FREQ:
+                f[s] += 1; diff -= 1; moved = True
+            elif diff < 0 and f[s] > 1:
+                f[s] -= 1; diff += 1; moved = True
+        guard += 1
+        if not moved or guard > MQ:
+            raise ValueError("cannot quantise: too few distinct symbols for a 1024 cap (needs >= 4 present symbols)")
+    return f
+
+
+def blocks_for(tiles: np.ndarray, tiles_per_block: int) -> np.ndarray:
+    """Runs of <= tiles_per_block consecutive tiles of one class -> (class, first tile, ntiles) (container.py:74-82)."""
+    out, i, n = [], 0, len(tiles)
+    while i < n:
+        j = i
+        while j < n and j - i < tiles_per_block and tiles[j][0] == tiles[i][0]:
+            j += 1
+        out.append((int(tiles[i][0]), i, j - i))
+        i = j
+    return np.asarray(out, np.int32).reshape(-1, 3)
+
+
+def encode_symbols(sym: np.ndarray, tile_class: np.ndarray, tile_rows: np.ndarray, freq: np.ndarray):
+    """rANS-code `sym` (rows in SORTED order, (R, P) ints in [0, N)) tile by tile.
+
+    tile_class[t], tile_rows[t]: class and row count of tile t (tiles cover the rows in order).
+    Returns (states u64 (nt, 32), words u32, tile_off u32 (nt + 1))."""
+    sym = np.asarray(sym, np.int64)
+    R, P = sym.shape
+    if P % 64:
+        raise ValueError("P must be a multiple of 64 (32 lanes, symbols in pairs)")
+    F = np.asarray(freq, np.int64)
+    C = np.cumsum(F, 1) - F
+    nt = len(tile_rows)
+    first = np.concatenate([[0], np.cumsum(tile_rows)[:-1]]).astype(np.int64)
+    x = np.full((nt, 32), 1 << 32, np.uint64)              # the decoder's state after its last pair
+    maxr = int(np.max(tile_rows))
+    S2 = P // 64
+    emitted = [[] for _ in range(nt)]                      # per tile: (nt_step) arrays of words in reverse order
+    cls = np.asarray(tile_class, np.int64)
+    lanes = np.arange(32)
+    for r in range(maxr - 1, -1, -1):
+        act = np.nonzero(np.asarray(tile_rows) > r)[0]     # tiles that have a row r
+        if act.size == 0:
+            continue
+        rows = first[act] + r
+        k = cls[act][:, None]
+        for sp in range(S2 - 1, -1, -1):
+            s0 = sym[rows][:, (2 * sp) * 32 + lanes]       # first symbol of the pair per lane
+            s1 = sym[rows][:, (2 * sp + 1) * 32 + lanes]
+            f0, f1 = F[k, s0], F[k, s1]
+            if (f0 == 0).any() or (f1 == 0).any():
+                raise ValueError("a coded symbol has frequency 0 in its class")
+            xa = x[act]
+            emit = xa >= ((f0 * f1).astype(np.uint64) << np.uint64(40))
+            low = (xa & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+            xa = np.where(emit, xa >> np.uint64(32), xa)
+            # decoder order inside a lane: symbol 0 then symbol 1 -> encode symbol 1 first
+            for f, c in ((f1, C[k, s1]), (f0, C[k, s0])):
+                fu = f.astype(np.uint64)
+                xa = ((xa // fu) << np.uint64(PB)) + (xa % fu) + c.astype(np.uint64)
+            x[act] = xa
+            for i, t in enumerate(act):                    # decoder hands words out by ascending lane
+                w = low[i][emit[i]]
+                if w.size:
+                    emitted[t].append(w[::-1])
+    words, tile_off = [], [0]
+    for t in range(nt):
+        w = np.concatenate(emitted[t])[::-1] if emitted[t] else np.zeros(0, np.uint32)
+        words.append(w)
+        tile_off.append(tile_off[-1] + w.size)
+    return x, (np.concatenate(words) if words else np.zeros(0, np.uint32)).astype(np.uint32), np.asarray(tile_off, np.uint32)
+
+
+def encode_ids(ids: np.ndarray, K: int = 2, T: int = 8, seed: int = 0) -> dict:
+    """Entropy-code integer ids (Q, P) (each row >= 0).  Rows are centred (drow), classed into K groups by their
+    spread, sorted by class (perm), cut into tiles of <= T rows and coded.  Returns the container arrays
+    (perm, freq, tiles, tile_off, states, words, drow, T, K, N)."""
+    ids = np.asarray(ids, np.int64)
+    Q, P = ids.shape
+    med = np.median(ids, axis=1).astype(np.int64)
+    drow = med - CENTRE                                    # symbol = id - drow puts the median at CENTRE
+    low = (ids - drow[:, None]).min(axis=1)
+    drow = drow + np.minimum(low, 0)                       # no negative symbols
+    sym = ids - drow[:, None]
+    N = int(sym.max()) + 1
+    if N > MAX_ID:
+        raise ValueError(f"symbols span {N} > {MAX_ID}")
+    spread = sym.std(axis=1)
+    order = np.argsort(spread, kind="stable")
+    cls_of_row = np.zeros(Q, np.int64)
+    for k, part in enumerate(np.array_split(order, K)):
+        cls_of_row[part] = k
+    perm = np.argsort(cls_of_row, kind="stable").astype(np.int32)      # sorted position -> original row
+    freq = np.zeros((K, N), np.int64)
+    for k in range(K):
+        rows = np.nonzero(cls_of_row == k)[0]
+        if rows.size:
+            freq[k] = quantise_freq(np.bincount(sym[rows].ravel(), minlength=N))
+        else:
+            freq[k, :4] = MAX_FREQ                          # an empty class still needs a valid table
+    tiles = []
+    pos = 0
+    sorted_cls = cls_of_row[perm]
+    while pos < Q:
+        k = sorted_cls[pos]
+        n = 1
+        while n < T and pos + n < Q and sorted_cls[pos + n] == k:
+            n += 1
+        tiles.append((int(k), pos, n))
+        pos += n
+    tiles = np.asarray(tiles, np.int32).reshape(-1, 3)
+    states, words, tile_off = encode_symbols(sym[perm], tiles[:, 0], tiles[:, 2], freq)
+    return dict(perm=perm, freq=freq.astype(np.uint16), tiles=tiles, tile_off=tile_off, states=states, words=words,
+                drow=drow.astype(np.int16), T=int(T), K=int(K), N=int(N))

@@ -158,7 +158,7 @@ def pack_payload(ids: torch.Tensor, nbits: torch.Tensor, rows_per_chunk: int = 2
 
 
 def encode_qvb8(W: torch.Tensor, tau: float = 1e-3, policy: str = "escape_outliers", restore: str = "fp16",
-                outlier_k: float = 6.0) -> QVB8Pack:
+                outlier_k: float = 6.0, keep_ids: bool = False) -> QVB8Pack:
     """Encode (Q, P) bf16 (or bf16-representable fp32) weights into a QVB8 pack on W's device.
 
     policy  'escape_outliers'  elements further than outlier_k row standard deviations from the row mean are
@@ -228,7 +228,7 @@ def encode_qvb8(W: torch.Tensor, tau: float = 1e-3, policy: str = "escape_outlie
     return QVB8Pack(Q=Q, P=P, tau=float(tau), restore=restore, ids=buf, min_s=min_s, tau_s=tau_s, nbits=nb8,
                     bit_off=bit_off, esc_idx=ei, esc_vals=ev, esc_idx_bf16=eib, esc_vals_bf16=evb, max_err=max_err,
                     stats=dict(nbits_hist={b: n for b, n in enumerate(hist) if n}, n_esc=int(ei.numel()),
-                               n_esc_bf16=int(eib.numel()), policy=policy))
+                               n_esc_bf16=int(eib.numel()), policy=policy, **({"ids": ids} if keep_ids else {})))
 
 
 def _pack_payload_host(ids, nbits, dev):
@@ -269,3 +269,25 @@ def reference_dense(pk: QVB8Pack, dtype=torch.float32, table: str | None = None)
     if ei.numel():
         out.view(-1)[ei] = ev.to(dtype)
     return out
+
+
+def encode_qvb8r(W: torch.Tensor, tau: float = 2e-3, K: int = 2, T: int | None = None,
+                 policy: str = "escape_outliers") -> dict:
+    """Encode (Q, P) weights into the arrays of a ``.qvb8r`` file (numpy, host): the QVB8 band of every row, its ids
+    entropy-coded by :mod:`qvb8_b200.rans`, the escapes with their exact value and the stored difference
+    ``exact - band`` the escape pass adds.  T (rows per tile) defaults to ceil(Q / 4096)."""
+    from . import rans
+    pk = encode_qvb8(W, tau=tau, policy=policy, keep_ids=True)
+    ids = pk.stats.pop("ids").cpu().numpy().astype(np.int64)
+    Q, P = ids.shape
+    enc = rans.encode_ids(ids, K=K, T=T if T is not None else max(1, -(-Q // 4096)))
+    ei = pk.esc_idx.cpu().numpy()
+    ev = pk.esc_vals.cpu().numpy()
+    rows = ei // P
+    # fma(id, tau_s, min_s) of the escaped positions: exact in float64, one narrowing (see band_value)
+    band = (ids.reshape(-1)[ei].astype(np.float64) * pk.tau_s.cpu().numpy().astype(np.float64)[rows]
+            + pk.min_s.cpu().numpy().astype(np.float64)[rows]).astype(np.float32)
+    enc.update(Q=Q, P=P, min_s=pk.min_s.cpu().numpy(), tau_s=pk.tau_s.cpu().numpy(), esc_idx=ei, esc_val=ev,
+               esc_delta=(ev.astype(np.float32) - band).astype(np.float32),
+               tau=float(tau), max_err=pk.max_err)
+    return enc

@@ -87,7 +87,7 @@ def test_moe_config_shape_and_bad_index(cuda_lib):
     bad_idx = idx.clone()
     bad_idx[0, 0] = E + 5
     import ctypes
-    nbytes = int(L.qvb8_moe_scratch_bytes(M, topk, E, u["Q"], d["Q"], 0))
+    nbytes = int(L.qvb8_moe_scratch_bytes(M, topk, E, u["P"], u["Q"], d["Q"], 0))
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
     o = torch.empty(M, d["Q"], dtype=X.dtype, device=DEV)
     bi, wd = bad_idx.to(DEV), w.to(DEV)
@@ -96,6 +96,6 @@ def test_moe_config_shape_and_bad_index(cuda_lib):
                             lib.stream_ptr(torch.device(DEV)))
     assert rc == 0
     flag = ctypes.c_int(0)
-    assert L.qvb8_moe_bad_index(scratch.data_ptr(), M, topk, E, u["Q"], d["Q"], 0, ctypes.byref(flag)) == 0
+    assert L.qvb8_moe_bad_index(scratch.data_ptr(), M, topk, E, u["P"], u["Q"], d["Q"], 0, ctypes.byref(flag)) == 0
     assert flag.value == 1
     assert lib.device_status() == 0

@@ -1,0 +1,132 @@
+"""QVB8R (entropy-coded QVB8): the synthetic encoder against the oracle decoder (which is pinned on the reference's own
+reader, tests/golden), the container round trip, and the CUDA kernels against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from qvb8_b200 import packs, rans, synth
+
+DEV = "cuda:0"
+TOL = 1e-2
+TIGHT = 2e-5
+
+
+def _pack(Q, P, seed, K=3, T=None, tau=2e-3):
+    W = synth.synth_weight(Q, P, seed)
+    return W, synth.encode_qvb8r(W, tau=tau, K=K, T=T)
+
+
+def _dense(d):
+    """fp32 restored weights with the exact escapes written over (what a dense reader produces)."""
+    return oracle.qvb8r_dense(d)
+
+
+def test_encoder_roundtrip_and_certificate():
+    W, d = _pack(80, 256, seed=11, K=3, T=4)
+    tab = rans.slot_tables(d["freq"])
+    assert np.array_equal(tab, oracle.slot_tables(d["freq"]))
+    assert int(d["freq"].astype(np.int64).sum(1).min()) == 4096 and int(d["freq"].max()) <= 1024
+    words = np.concatenate([d["words"], np.zeros(rans.PAD_WORDS, np.uint32)])
+    ids = oracle.rans_decode_ids(words, d["tile_off"].astype(np.int64), d["states"], d["tiles"].astype(np.int64), tab,
+                                 d["perm"], d["drow"].astype(np.int32), 80, 256)
+    band = oracle.rans_restore_f32(ids, d["min_s"], d["tau_s"])
+    Wd = _dense(d)
+    # every weight within tau of the source after the fp16 rounding the certificate is stated on
+    err = np.abs(Wd.astype(np.float16).astype(np.float64) - W.float().numpy().astype(np.float64))
+    assert float(err.max()) <= 2e-3
+    # the stored differences are exact - band at the escaped positions
+    ei = d["esc_idx"]
+    assert np.array_equal((d["esc_val"] - band.reshape(-1)[ei]).astype(np.float32), d["esc_delta"])
+    assert d["words"].size * 32 / (80 * 256) < 8.0       # it does compress
+
+
+def test_container_roundtrip():
+    _, d = _pack(48, 128, seed=5, K=2, T=8)
+    blob = packs.write_qvb8r(d, Q=d["Q"], P=d["P"], min_s=d["min_s"], tau_s=d["tau_s"], esc_idx=d["esc_idx"],
+                             esc_val=d["esc_val"], esc_delta=d["esc_delta"], cert=dict(tau=d["tau"], max_err=d["max_err"]))
+    r = packs.read_qvb8r(blob)
+    for k in ("perm", "freq", "tiles", "tile_off", "states", "words", "drow", "min_s", "tau_s", "esc_idx", "esc_val", "esc_delta"):
+        assert np.array_equal(np.asarray(r[k]), np.asarray(d[k]).astype(np.asarray(r[k]).dtype)), k
+    assert np.array_equal(_dense(r).view(np.uint32), _dense(d).view(np.uint32))
+    bad = bytearray(blob); bad[200] ^= 1
+    with pytest.raises(packs.PackFormatError):
+        packs.read_qvb8r(bytes(bad))
+
+
+def test_blocks_schedule():
+    tiles = np.array([[0, 0, 4]] * 10 + [[1, 40, 4]] * 3, np.int64)
+    b = rans.blocks_for(tiles, 8)
+    assert b.tolist() == [[0, 0, 8], [0, 8, 2], [1, 10, 3]]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Q,P,K,T", [(80, 256, 3, 4), (300, 1024, 2, 1), (64, 4096, 1, 8), (1000, 512, 4, 3)])
+def test_gpu_ids_and_decode(cuda_lib, Q, P, K, T):
+    from qvb8_b200.ext_qvb8r import core_tensors, ext
+    _, d = _pack(Q, P, seed=Q + P, K=K, T=T)
+    core = core_tensors(d, DEV)
+    tab = rans.slot_tables(d["freq"])
+    words = np.concatenate([d["words"], np.zeros(rans.PAD_WORDS, np.uint32)])
+    want_ids = oracle.rans_decode_ids(words, d["tile_off"].astype(np.int64), d["states"], d["tiles"].astype(np.int64), tab,
+                                      d["perm"], d["drow"].astype(np.int32), Q, P)
+    got = ext.ids(P, *core)
+    assert np.array_equal(got.cpu().numpy(), want_ids)                       # bit-exact
+    band = oracle.rans_restore_f32(want_ids, d["min_s"], d["tau_s"])
+    nblk = core[4].numel() // 3
+    for code, dt, ref in ((2, torch.float32, band),
+                          (0, torch.float16, torch.from_numpy(band).to(torch.float16).numpy()),
+                          (1, torch.bfloat16, None)):
+        Wg = ext.decode(*core, P, code, 0, nblk, -1, 0)
+        assert Wg.dtype == dt
+        if ref is None:
+            assert torch.equal(Wg.cpu(), torch.from_numpy(band).to(torch.bfloat16))
+        else:
+            assert np.array_equal(Wg.cpu().numpy().view(np.uint16 if code == 0 else np.uint32),
+                                  ref.view(np.uint16 if code == 0 else np.uint32))
+    # a block range as a compact chunk in sorted order
+    b0, nb = nblk // 3, max(1, nblk // 2)
+    blocks = core[4].cpu().numpy().reshape(-1, 3)
+    tiles = np.asarray(d["tiles"]).reshape(-1, 3)
+    t_first, t_last = blocks[b0][1], blocks[b0 + nb - 1][1] + blocks[b0 + nb - 1][2] - 1
+    row_base = int(tiles[t_first][1]); nrows = int(tiles[t_last][1] + tiles[t_last][2]) - row_base
+    chunk = ext.decode(*core, P, 2, b0, nb, row_base, nrows)
+    want_chunk = band[np.asarray(d["perm"])[row_base:row_base + nrows]]
+    assert np.array_equal(chunk.cpu().numpy().view(np.uint32), want_chunk.view(np.uint32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 3, 8, 13])
+def test_gpu_products(cuda_lib, M):
+    from qvb8_b200.ext_qvb8r import core_tensors, escape_csr, ext
+    Q, P = 260, 1024
+    _, d = _pack(Q, P, seed=70 + M, K=3, T=2)
+    core = core_tensors(d, DEV)
+    Wd = _dense(d)                                                           # exact escapes written over
+    X = synth.synth_activation(M, P, seed=M, device=DEV, dtype=torch.float32)
+    want = oracle.matmul_f32w(X.cpu().numpy(), Wd, narrow_x=False)
+    if M == 1:
+        y = ext.gemv(X.reshape(-1), *core).reshape(1, -1)
+    elif M <= 8:
+        y = ext.multi(X, *core)
+        yb = ext.multi(X.to(torch.bfloat16), *core)                           # bf16 X is exact in fp32
+        ext.fix_escapes(X.to(torch.bfloat16).float(), *escape_csr(d, DEV), yb)
+        wb = oracle.matmul_f32w(X.to(torch.bfloat16).float().cpu().numpy(), Wd, narrow_x=False)
+        assert np.linalg.norm(yb.cpu().numpy() - wb) / np.linalg.norm(wb) < TIGHT
+    else:
+        y = None
+    if y is not None:
+        ext.fix_escapes(X, *escape_csr(d, DEV), y)
+        err = np.linalg.norm(y.cpu().numpy() - want) / np.linalg.norm(want)
+        assert err < TOL and err < TIGHT, err
+    # tensor-core contract: band rounded once to fp16, fp16 X
+    Xh = X.to(torch.float16)
+    yt = ext.tc(Xh, *core, 8)
+    ids = oracle.rans_decode_ids(np.concatenate([d["words"], np.zeros(rans.PAD_WORDS, np.uint32)]),
+                                 d["tile_off"].astype(np.int64), d["states"], d["tiles"].astype(np.int64),
+                                 rans.slot_tables(d["freq"]), d["perm"], d["drow"].astype(np.int32), Q, P)
+    W16 = oracle.rans_restore_f32(ids, d["min_s"], d["tau_s"]).astype(np.float16).astype(np.float32)
+    wt = oracle.matmul_f32w(Xh.float().cpu().numpy(), W16, narrow_x=False)
+    errt = np.linalg.norm(yt.cpu().numpy() - wt) / np.linalg.norm(wt)
+    assert errt < TOL and errt < TIGHT, errt
+    assert torch.equal(yt, ext.tc(Xh, *core, 8))                              # fixed summation order
