@@ -18,7 +18,7 @@
 namespace qv {
 
 constexpr int MOE_WARPS = 8;
-constexpr int MOE_TOK = 8;                 // tokens per pass over a row
+constexpr int MOE_TOK = 4;                 // tokens per pass over a row
 
 struct MoeRoute {                          // device tables built by the route kernel
     int *counts;                           // [E] pairs that chose expert e
@@ -112,7 +112,7 @@ __device__ __forceinline__ MoeRowMeta moe_row_meta(const MoeRows &p, size_t mi) 
 }
 
 template <int ACT>
-__global__ void __launch_bounds__(MOE_WARPS * 32, 2) moe_rows_kernel(const MoeRows p) {
+__global__ void __launch_bounds__(MOE_WARPS * 32, 4) moe_rows_kernel(const MoeRows p) {
     const int s = blockIdx.y;
     if (s >= *p.route.nslots) return;
     const int e = p.route.slots[s];
@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(MOE_WARPS * 32, 2) moe_rows_kernel(const MoeRo
                 for (int j = 0; j < MOE_TOK; ++j) acc[k][j] = 0.f;
             const bool fast = NR == 1 ? (m[0].nb <= 8 && (m[0].bit0 & 7) == 0)
                                       : (m[0].nb <= 8 && (m[0].bit0 & 7) == 0 && m[NR - 1].nb <= 8 && (m[NR - 1].bit0 & 7) == 0);
-            constexpr int UN = 4;                                       // 256-column blocks whose ids are fetched together
+            constexpr int UN = 2;                                       // 256-column blocks whose ids are fetched together
             for (int col0 = lane * 8; col0 < p.P; col0 += 256 * UN) {
                 uint64_t v[NR][UN];
                 if (fast) {                                             // all the row bytes of this step in flight at once
