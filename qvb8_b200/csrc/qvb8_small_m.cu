@@ -774,39 +774,51 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
     const bool tracer = (p.debug & 2) && pipe == 0;
 
     if (tracer) trace(p.debug, 0);
-    if (tid < NPIPE) {
-        PipeControl &q = ctl.pipe[tid];
-        for (int s = 0; s < nstg; ++s) {
-            mbar_init(smem_u32(&q.full[s]), 1);
-            mbar_init(smem_u32(&q.empty[s]), NW);
-        }
-        for (int s = 0; s < NSIDE; ++s) {
-            mbar_init(smem_u32(&q.side_full[s]), 1);
-            mbar_init(smem_u32(&q.side_empty[s]), NW + 1);
-        }
-        mbar_init(smem_u32(&q.red_full), NW);
-        mbar_init(smem_u32(&q.red_empty), 1);
-        if (tid == 0) {
-            mbar_init(smem_u32(&ctl.x_ready), NW * NPIPE);
-            mbar_init(smem_u32(&ctl.sums_ready), NPIPE);
-            for (int k = 0; k < XCH_SLOTS; ++k) mbar_init(smem_u32(&ctl.xch_full[k]), 1);
-            ctl.abort = 0;
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    if (tid >= 32 && tid < 36) zero16[tid - 32] = 0u;
-    if (tid >= 64 && tid < 64 + PAIR_TABLE_WORDS) ctl.pair_table[tid - 64] = pair_const_word(3 + ((tid - 64) >> 2), (tid - 64) & 3);
-    __syncthreads();
-    pdl_launch_dependents();                                            // what follows in the stream may start its own prologue
-    if (tracer) trace(p.debug, 1);
-    const int ntiles = p.ntiles;
     // this CTA's tiles and this pipe's run of their (tile, stage) units
+    const int ntiles = p.ntiles;
     int ct0, ct1;
     cta_tiles(ntiles, gridDim.x, blockIdx.x, ct0, ct1);
     const int uc0 = ct0 * NSK, uc1 = ct1 * NSK;
     const int Lp = max(1, (uc1 - uc0 + NPIPE - 1) / NPIPE);
     const int u0 = min(uc0 + pipe * Lp, uc1), u1 = min(u0 + Lp, uc1);
     const Run run = make_run(u0, u1, NSK);
+    // the producer's first descriptor fields are on their way from memory while the barriers are set up
+    int pf_nb = 0, pf_cnt = 0, pf_esc0 = 0, pf_nesc = 0;
+    uint32_t pf_b16 = 0;
+    if (warp == PRODUCER_WARP && run.nv > 0) {
+        const TileDesc *d = p.tiles + run_visit(run, 0).tile;
+        pf_nb = __ldg(&d->nb);
+        pf_cnt = __ldg(&d->cnt);
+        pf_esc0 = __ldg(&d->esc0);
+        pf_nesc = __ldg(&d->nesc);
+        pf_b16 = lane < 16 ? __ldg(&d->b16[lane]) : 0u;
+    }
+    // barriers: one thread each
+    {
+        const int per_pipe = 2 * nstg + 2 * NSIDE + 2;
+        if (tid < NPIPE * per_pipe) {
+            PipeControl &q = ctl.pipe[tid / per_pipe];
+            const int k = tid % per_pipe;
+            if (k < nstg) mbar_init(smem_u32(&q.full[k]), 1);
+            else if (k < 2 * nstg) mbar_init(smem_u32(&q.empty[k - nstg]), NW);
+            else if (k < 2 * nstg + NSIDE) mbar_init(smem_u32(&q.side_full[k - 2 * nstg]), 1);
+            else if (k < 2 * nstg + 2 * NSIDE) mbar_init(smem_u32(&q.side_empty[k - 2 * nstg - NSIDE]), NW + 1);
+            else if (k == 2 * nstg + 2 * NSIDE) mbar_init(smem_u32(&q.red_full), NW);
+            else mbar_init(smem_u32(&q.red_empty), 1);
+        } else if (tid < NPIPE * per_pipe + XCH_SLOTS) {
+            mbar_init(smem_u32(&ctl.xch_full[tid - NPIPE * per_pipe]), 1);
+        } else if (tid == NPIPE * per_pipe + XCH_SLOTS) {
+            mbar_init(smem_u32(&ctl.x_ready), NW * NPIPE);
+            mbar_init(smem_u32(&ctl.sums_ready), NPIPE);
+            ctl.abort = 0;
+        }
+        if (tid <= NPIPE * per_pipe + XCH_SLOTS) asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (tid >= 160 && tid < 164) zero16[tid - 160] = 0u;
+    if (tid >= 128 && tid < 128 + PAIR_TABLE_WORDS) ctl.pair_table[tid - 128] = pair_const_word(3 + ((tid - 128) >> 2), (tid - 128) & 3);
+    __syncthreads();
+    pdl_launch_dependents();                                            // what follows in the stream may start its own prologue
+    if (tracer) trace(p.debug, 1);
     RingPos rp;
     rp.full = smem_u32(&pc_.full[0]); rp.empty = smem_u32(&pc_.empty[0]); rp.data = smem_u32(pbase);
     rp.slot = 0; rp.phase = 0;
@@ -816,8 +828,8 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
         // ================= producer warp: per visit, lane 16 copies the tile's descriptor and lane 17 its escapes into
         // a side slot; per stage, lane r copies row r =================
         bool alive = true;
-        int nb = 0, cnt = 0, esc0 = 0, nesc = 0;
-        uint32_t b16 = 0;
+        int nb = pf_nb, cnt = pf_cnt, esc0 = pf_esc0, nesc = pf_nesc;
+        uint32_t b16 = pf_b16;
         auto fetch = [&](int i) {
             if (i < run.nv) {
                 const TileDesc *d = p.tiles + run_visit(run, i).tile;
@@ -828,7 +840,6 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
                 b16 = lane < 16 ? __ldg(&d->b16[lane]) : 0u;
             }
         };
-        fetch(0);
         if (tracer) trace(p.debug, 2);
         const bool nocopy = (p.debug & 4) != 0;
         for (int i = 0; i < run.nv && alive; ++i) {
