@@ -96,7 +96,7 @@ static_assert(sizeof(TileDesc) == 400, "descriptor size");
 struct EscEntry { int col; float delta; };   // column, exact value - band value
 constexpr int DESC_BYTES = 400;
 constexpr int DESC_SLOT = 416;            // descriptor area of a side slot
-constexpr int ESC_CAP = 192;              // escape entries that travel with a descriptor (the rest is read from global memory)
+constexpr int ESC_CAP = 128;              // escape entries that travel with a descriptor (the rest is read from global memory)
 constexpr int SIDE_BYTES = DESC_SLOT + ESC_CAP * 8;
 constexpr int NSIDE = 3;                  // side slots per pipe: descriptors and escapes of the visits ahead
 
@@ -910,8 +910,8 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
         if (lane == 0) mbar_arrive(smem_u32(&ctl.sums_ready));
         if (alive) alive = mbar_wait(smem_u32(&ctl.sums_ready), 0, abort_flag, 6);
         int own_contrib = 0, own_tile = 0, own_row[2] = {-1, -1};
-        // writes a finished tile (of this K-range): the result itself, or with several K-ranges a partial result that
-        // whichever range finishes the tile last adds up in range order
+        // writes a finished tile (of this K-range): the result itself, or with several K-ranges a partial result; the
+        // K-ranges' partial results of all of a CTA's tiles are added up in range order at the end of the kernel
         auto emit_tile = [&](int tile, const int (&rows)[2], const float (&y)[2][NT][2]) {
             float *out = p.S == 1 ? p.Y : p.part + (int64_t)split * M * p.Q;
 #pragma unroll
@@ -923,31 +923,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
                         const int m = 8 * n + 2 * t + k;
                         if (rows[hrow] >= 0 && m < M) out[(int64_t)m * p.Q + rows[hrow]] = y[hrow][n][k];
                     }
-            if (p.S == 1) return;
-            __syncwarp();
-            __threadfence();
-            const int tkt = tile;
-            int last = 0;
-            if (lane == 0) last = atomicAdd(p.ticket + tkt, 1) == p.S - 1;
-            last = __shfl_sync(0xffffffffu, last, 0);
-            if (last) {
-                __threadfence();
-#pragma unroll
-                for (int hrow = 0; hrow < 2; ++hrow)
-#pragma unroll
-                    for (int n = 0; n < NT; ++n)
-#pragma unroll
-                        for (int k = 0; k < 2; ++k) {
-                            const int m = 8 * n + 2 * t + k;
-                            if (rows[hrow] >= 0 && m < M) {
-                                const int64_t o = (int64_t)m * p.Q + rows[hrow];
-                                float sum = 0.f;
-                                for (int r = 0; r < p.S; ++r) sum += __ldcg(p.part + (int64_t)r * M * p.Q + o);
-                                p.Y[o] = sum;
-                            }
-                        }
-                if (lane == 0) p.ticket[tkt] = 0;
-            }
+            (void)tile;
         };
         for (int i = 0; i < run.nv; ++i) {
             const Visit v = run_visit(run, i);
@@ -983,9 +959,12 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
                             if (e < ESC_CAP) en = ent[e];
                             else { en.col = __ldg(&gent[e].col); en.delta = __ldg(&gent[e].delta); }
                             if (en.col >= clo && en.col < chi) {
+                                // the column's activations of consecutive tokens lie one slot (8 halves) apart
+                                const int cc = en.col - cbase;
+                                const __half *xp = xs_a + ((size_t)(slot_of(cc, 0, MP) + m0) << 3) + pos_a(cc & 7);
 #pragma unroll
                                 for (int k = 0; k < 8; ++k)
-                                    if (m0 + k < M) a[k] = __fmaf_rn(xs_read(xs_a, en.col - cbase, m0 + k, MP), en.delta, a[k]);
+                                    if (m0 + k < M) a[k] = __fmaf_rn(__half2float(xp[k * 8]), en.delta, a[k]);
                             }
                         }
 #pragma unroll
@@ -1227,6 +1206,31 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
             if (lane == 0) mbar_arrive(red_full);
         }
         if (tracer && warp == 0) trace(p.debug, 8);
+    }
+    // ---- several K-ranges: the CTAs (x, 0..S-1) hold partial results of the same tiles; whichever of them gets here
+    // last adds the ranges up in range order for all those tiles at once (one ticket per CTA column, all threads load)
+    if (p.S > 1) {
+        __threadfence();                                                // this thread's partial results are visible
+        __syncthreads();
+        __shared__ int last_range;
+        if (tid == 0) last_range = atomicAdd(p.ticket + blockIdx.x, 1) == p.S - 1;
+        __syncthreads();
+        if (last_range) {
+            __threadfence();
+            const int per_tile = 16 * M;
+            const int total = (ct1 - ct0) * per_tile;
+            for (int i = tid; i < total; i += blockDim.x) {
+                const int tl = ct0 + i / per_tile, rem = i % per_tile;
+                const int row = __ldg(&p.tiles[tl].row[rem / M]), m = rem % M;
+                if (row >= 0) {
+                    const int64_t o = (int64_t)m * p.Q + row;
+                    float sum = 0.f;
+                    for (int r = 0; r < p.S; ++r) sum += __ldcg(p.part + (int64_t)r * M * p.Q + o);
+                    p.Y[o] = sum;
+                }
+            }
+            if (tid == 0) p.ticket[blockIdx.x] = 0;
+        }
     }
 }
 
