@@ -49,6 +49,7 @@ int launch_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x
                            cudaStream_t st);
 int check_small_m_args(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, const float *Y,
                        const char *who);
+int prefill_error_word(int *out);                 // qvb8_prefill.cu
 
 constexpr int KC = 128;                   // columns per chunk
 constexpr int NW = 4;                     // consumer warps
@@ -123,6 +124,16 @@ inline PlanLayout plan_layout(int64_t Q, int64_t n_esc) {
     L.esc_ent = L.tiles + up256((int64_t)L.max_tiles * DESC_BYTES);
     L.total = L.esc_ent + up256((n_esc + L.max_tiles + 2) * 8);
     return L;
+}
+
+// The escape sections of a plan, for the other kernels that read them (the prefill kernel's escape pass).
+void plan_escape_sections(const void *plan, int64_t Q, int64_t n_esc, const int **esc_ptr, const int **esc_col,
+                          const float **esc_delta) {
+    const PlanLayout L = plan_layout(Q, n_esc);
+    const uint8_t *base = reinterpret_cast<const uint8_t *>(plan);
+    *esc_ptr = reinterpret_cast<const int *>(base + L.esc_ptr);
+    *esc_col = reinterpret_cast<const int *>(base + L.esc_col);
+    *esc_delta = reinterpret_cast<const float *>(base + L.esc_delta);
 }
 
 // Per-CTA control block in static shared memory.
@@ -1393,6 +1404,8 @@ QV_API int qvb8_device_status(int *status) {
     if (!status) return qv::fail(QVB8_ERR_ARG, "qvb8_device_status: null output");
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, qv::g_error_word, sizeof(int)) != cudaSuccess) return qv::cuda_status("qvb8_device_status");
+    if (v == 0)
+        if (int rc = qv::prefill_error_word(&v)) return rc;
     *status = v;
     return QVB8_OK;
 }

@@ -39,6 +39,15 @@ def _small_m(ids, pk, keep, X, x_mode=0):
     return _lib.small_m(pk, keep, X, x_mode=x_mode)
 
 
+def _existing_or_new_plan(ids, pk, keep):
+    """The pack's plan; while a CUDA graph is being captured only one that already exists (building allocates and
+    launches outside the capture's intent), else None."""
+    if not torch.cuda.is_current_stream_capturing():
+        return _lib.plan_on(ids, pk, keep)
+    plans = getattr(ids, "_qvb8_plans", None) or {}
+    return plans.get((pk.ids, pk.Q, pk.P, pk.n_esc, pk.esc_idx, pk.min_s, pk.bit_off))
+
+
 def _as_2d(X: torch.Tensor, P: int) -> torch.Tensor:
     if X.dim() == 1:
         X = X.reshape(1, -1)
@@ -126,7 +135,13 @@ class Qvb8Ext:
         if M <= _SMALL_M_MAX:
             y = _small_m(ids, pk, keep, X)
             return y.to(torch.float16) if (out_half and M > 8) else y
-        # prefill: restore once to fp16, then one tensor-core GEMM with fp32 accumulation (qvb8_cuda.cu:1542-1671)
+        if int(P) % 64 == 0:
+            # prefill: the ids are unpacked into shared memory and contracted by tcgen05.mma, no dense copy of W
+            plan = _existing_or_new_plan(ids, pk, keep) if pk.n_esc > 0 else None
+            if pk.n_esc == 0 or plan is not None:
+                y = _lib.prefill(pk, keep, X, plan)
+                return y.to(torch.float16) if out_half else y
+        # other shapes: restore once to fp16, then one library GEMM with fp32 accumulation (qvb8_cuda.cu:1542-1671)
         W = _lib.decode(pk, keep, torch.float16)
         Xh = _sat_half(X)
         if out_half:

@@ -25,7 +25,7 @@ EXPORTS = (
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
-    "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes",
+    "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill",
 )
 
 
@@ -93,6 +93,9 @@ def load() -> ctypes.CDLL:
             lib.qvb8_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
             lib.qvb8_debug_trace.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
             lib.qvb8_small_m_set_tuning.restype = None
+            lib.qvb8_prefill_scratch_bytes.argtypes = [i64, i64, i64]
+            lib.qvb8_prefill_scratch_bytes.restype = i64
+            lib.qvb8_prefill.argtypes = [pk, vp, vp, ci, i64, vp, vp, i64, vp]
             es = ctypes.POINTER(ExpertStackStruct)
             rp = ctypes.POINTER(RPackStruct)
             lib.qvb8r_ids.argtypes = [rp, vp, vp]
@@ -258,6 +261,24 @@ def small_m(pack, keep, X: torch.Tensor, x_mode: int = 0, generic: bool = False,
                                      sc.data_ptr() if sc is not None else None, sc.numel() if sc is not None else 0,
                                      flags, stream_ptr(dev))
     check(rc, "qvb8_small_m")
+    return Y
+
+
+def prefill(pack, keep, X: torch.Tensor, plan: torch.Tensor | None = None) -> torch.Tensor:
+    """(M, Q) fp32 = X (M, P) @ W^T through the tcgen05 prefill kernel (any M; meant for M in the hundreds and up)."""
+    dev = keep[0].device
+    if not X.is_cuda or X.device != dev or X.dim() != 2 or X.shape[1] != pack.P:
+        raise RuntimeError(f"qvb8_b200: X must be a CUDA (M, {pack.P}) tensor on the pack's device")
+    X = X if X.is_contiguous() else X.contiguous()
+    M = X.shape[0]
+    lib = load()
+    nbytes = int(lib.qvb8_prefill_scratch_bytes(M, pack.Q, pack.P))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    Y = torch.empty((M, pack.Q), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.qvb8_prefill(ctypes.byref(pack), plan.data_ptr() if plan is not None else None, X.data_ptr(),
+                               dtype_code(X.dtype), M, Y.data_ptr(), scratch.data_ptr(), nbytes, stream_ptr(dev)),
+              "qvb8_prefill")
     return Y
 
 
