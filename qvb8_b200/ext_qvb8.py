@@ -137,8 +137,8 @@ class Qvb8Ext:
             return y.to(torch.float16) if (out_half and M > 8) else y
         if int(P) % 64 == 0:
             # prefill: the ids are unpacked into shared memory and contracted by tcgen05.mma, no dense copy of W
-            plan = _existing_or_new_plan(ids, pk, keep) if pk.n_esc > 0 else None
-            if pk.n_esc == 0 or plan is not None:
+            plan = _existing_or_new_plan(ids, pk, keep)
+            if plan is not None:
                 y = _lib.prefill(pk, keep, X, plan)
                 return y.to(torch.float16) if out_half else y
         # other shapes: restore once to fp16, then one library GEMM with fp32 accumulation (qvb8_cuda.cu:1542-1671)

@@ -25,7 +25,7 @@ EXPORTS = (
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
-    "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill",
+    "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
 )
 
 
@@ -96,6 +96,8 @@ def load() -> ctypes.CDLL:
             lib.qvb8_prefill_scratch_bytes.argtypes = [i64, i64, i64]
             lib.qvb8_prefill_scratch_bytes.restype = i64
             lib.qvb8_prefill.argtypes = [pk, vp, vp, ci, i64, vp, vp, i64, vp]
+            lib.qvb8_prefill_set_tuning.argtypes = [ci]
+            lib.qvb8_prefill_set_tuning.restype = None
             es = ctypes.POINTER(ExpertStackStruct)
             rp = ctypes.POINTER(RPackStruct)
             lib.qvb8r_ids.argtypes = [rp, vp, vp]
@@ -272,11 +274,13 @@ def prefill(pack, keep, X: torch.Tensor, plan: torch.Tensor | None = None) -> to
     X = X if X.is_contiguous() else X.contiguous()
     M = X.shape[0]
     lib = load()
+    if plan is None:
+        plan = build_plan(pack, keep)
     nbytes = int(lib.qvb8_prefill_scratch_bytes(M, pack.Q, pack.P))
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     Y = torch.empty((M, pack.Q), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        check(lib.qvb8_prefill(ctypes.byref(pack), plan.data_ptr() if plan is not None else None, X.data_ptr(),
+        check(lib.qvb8_prefill(ctypes.byref(pack), plan.data_ptr(), X.data_ptr(),
                                dtype_code(X.dtype), M, Y.data_ptr(), scratch.data_ptr(), nbytes, stream_ptr(dev)),
               "qvb8_prefill")
     return Y

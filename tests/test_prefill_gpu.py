@@ -15,7 +15,7 @@ TIGHT = 1e-4        # what exact products with fp32 accumulation give
 
 def _run(pk, M, dtype, seed):
     st, keep = lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx, pk.esc_vals)
-    plan = lib.build_plan(st, keep) if pk.esc_idx.numel() else None
+    plan = lib.build_plan(st, keep)
     X = synth.synth_activation(M, pk.P, seed=seed, device=DEV, dtype=dtype)
     Y = lib.prefill(st, keep, X, plan=plan)
     torch.cuda.synchronize()
@@ -27,11 +27,18 @@ def _run(pk, M, dtype, seed):
     (128, 64, 32, (7,), 0.0),                      # one CTA, one K block
     (256, 512, 100, (6, 7, 8), 0.0),               # two row tiles, ragged token tile
     (200, 1024, 300, (3, 5, 7, 8), 0.002),         # ragged rows, two token tiles, escapes
-    (384, 256, 257, (4, 9, 12), 0.001),            # rows wider than a byte take the per-id path
+    (384, 256, 257, (4, 9, 12), 0.001),            # 12-bit rows are recomputed in fp32
+    (300, 1280, 520, (1, 2, 10, 11, 14), 0.0),     # every unpack mode; 20 K blocks wrap the stage ring several times
+    (1000, 2048, 64, (7,), 0.001),                 # one width: four or eight row tiles, deep K
 ])
-def test_prefill_matches_oracle(cuda_lib, Q, P, M, widths, esc):
+@pytest.mark.parametrize("rows", [128, 256])
+def test_prefill_matches_oracle(cuda_lib, Q, P, M, widths, esc, rows):
     pk = random_pack(Q, P, widths, seed=Q + M, esc_frac=esc, device=DEV)
-    Y, want = _run(pk, M, torch.bfloat16, seed=M)
+    lib.load().qvb8_prefill_set_tuning(rows)
+    try:
+        Y, want = _run(pk, M, torch.bfloat16, seed=M)
+    finally:
+        lib.load().qvb8_prefill_set_tuning(0)
     err = rel_fro(Y.cpu().numpy(), want)
     assert err < TOL and err < TIGHT, err
     assert lib.device_status() == 0
