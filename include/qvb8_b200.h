@@ -116,8 +116,8 @@ int qvb8_debug_trace(unsigned long long *out32);
 /* Device-side error word of the current device: 0, or the code of the first bounded wait that gave up inside a
  * kernel of this library (1 = copy ring slot never freed, 2 = copy never landed, 3 / 4 = hand-over between the
  * consumer and finishing warps, 5 / 6 = activation staging, 7 / 8 = descriptor ring, 9 = part of a shared tile,
- * 21..25 = prefill: stage never freed (unpack / copy), weights or activations of a stage never arrived, accumulator
- * never completed).
+ * 21..27 = prefill: packed ids never landed, weight slot of tensor memory never freed, raw ring slot never freed,
+ * activation stage never freed, weights / activations of a K block never arrived, accumulator never completed).
  * Synchronises the host. */
 int qvb8_device_status(int *status);
 
@@ -130,13 +130,11 @@ int qvb8_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x_m
  * Y (M, Q) fp32 = X (M, P) @ W^T with the weight tiles restored from the packed ids inside the kernel and contracted
  * by tcgen05.mma with the accumulator in tensor memory (replaces the reference's restore-to-HBM + cublasGemmEx path,
  * qvb8_cuda.cu:1542-1671).  P % 64 == 0.  `plan` (qvb8_plan_build) gives the row order and the escapes.
- * scratch: qvb8_prefill_scratch_bytes(M, Q, P) bytes, 256-byte aligned (the tiled fp16 copy of X, its row sums, the
- * list of rows wider than 11 bits).
- * qvb8_prefill_set_tuning: rows per CTA, 128 or 256; 0 = chosen per shape (tests and sweeps only). */
+ * scratch: qvb8_prefill_scratch_bytes(M, Q, P) bytes, 256-byte aligned (two fp16 copies of X, its row sums, the
+ * list of rows wider than 11 bits). */
 int64_t qvb8_prefill_scratch_bytes(int64_t M, int64_t Q, int64_t P);
 int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int64_t M, float *Y, void *scratch,
                  int64_t scratch_bytes, void *stream);
-void qvb8_prefill_set_tuning(int rows_per_cta);
 
 /* ---- mixture-of-experts MLP over stacked expert packs -------------------------------------------------------------
  * Stacked layout of one projection of all E experts (reference formats/qvb8/backends_experts.py:144-196): every

@@ -13,16 +13,20 @@
 // Launches:
 //   narrow   X -> saturated fp16, stored tile by tile in the order the tensor cores read it (256 tokens x 64 columns =
 //            32 KB contiguous: [8-column group][token][8 values]), plus partial sums of the narrowed values
-//   main     a CTA owns 128 * NACC output rows (in the plan's width-sorted order) and 256 tokens; K advances in blocks
-//            of 64 columns through a ring of shared-memory stages.  Warp roles:
-//              warps 0..7  unpack: a thread owns one row; per K block it reads the row's 64 ids (8 * nb bytes, 8-byte
-//                          aligned), turns pairs into fp16 integers with shift / mask / or 0x6400 / subtract 1024 and
-//                          stores eight 16-byte rows of core matrices (K-major, no swizzle); the next block's words are
-//                          already in registers
-//              warp 8      one thread: one 32 KB bulk copy per stage for the activations
-//              warp 9      one thread: waits for both halves of a stage, issues 4 * NACC tcgen05.mma (128 x 256 x 16)
-//                          and commits them to the stage's "empty" barrier
-//            At the end the eight unpack warps read the accumulators with tcgen05.ld, apply tau_s, min_s * sum(x) and
+//   main     a CTA owns 128 output rows (in the plan's width-sorted order) and 256 tokens; K advances in blocks of 64
+//            columns.  The weights reach the tensor cores through TENSOR MEMORY (tcgen05.mma with the A operand in
+//            tensor memory), so shared memory carries only the activations and the packed ids:
+//              warp 8      copies.  Every lane: one bulk copy per row and super-stage (four K blocks = 32 * nb bytes of
+//                          a row) into a two-deep raw ring whose row stride is an odd multiple of 16 bytes; lane 0
+//                          also: one 32 KB bulk copy per K block for the activations (four stages)
+//              warps 0..7  unpack.  A thread owns one row; warps 0..3 take the first pair of K blocks of a
+//                          super-stage, warps 4..7 the second.  128 ids = nb 16-byte vectors from the raw ring,
+//                          pairs -> fp16 integers with shift / mask / or 0x6400 / subtract 1024, 64 registers ->
+//                          tcgen05.st into the thread's lane of one of four 64-column weight slots
+//              warp 9      one thread: waits for a weight slot and an activation stage, issues four tcgen05.mma
+//                          (128 x 256 x 16, accumulator in columns 0..255) per K block and commits them to the
+//                          barriers that free the stage and the slot
+//            At the end the eight unpack warps read the accumulator with tcgen05.ld, apply tau_s, min_s * sum(x) and
 //            write Y.
 //   wide, escapes   the corrections described above
 //
@@ -37,13 +41,16 @@ constexpr int PF_TOK = 256;                // tokens per CTA = MMA N
 constexpr int PF_BK = 64;                  // columns per stage
 constexpr int PF_UNPACK = 256;             // unpack threads (warps 0..7)
 constexpr int PF_THREADS = PF_UNPACK + 64; // + copy warp + MMA warp
-constexpr int PF_A_HALF = 128 * PF_BK * 2; // 16 KB: 128 rows of one accumulator
 constexpr int PF_B_BYTES = PF_TOK * PF_BK * 2;      // 32 KB
 constexpr int PF_SPIN = 1 << 22;
 constexpr int PF_KS = 8;                   // column ranges of the partial activation sums
 constexpr int PF_EXACT_BITS = 11;          // ids up to this width are exact in fp16
-constexpr int PF_MAX_STAGES = 4;
-constexpr int PF_WORDS = 10;               // 64-bit words of 64 ids of the widest row unpacked word-wise
+constexpr int PF_NBS = 4;                  // activation stages in shared memory
+constexpr int PF_NU = 4;                   // weight units (pairs of K blocks, 64 columns) in tensor memory
+constexpr int PF_VECS = 10;                // 16-byte vectors of a pair of K blocks (128 ids) of the widest bulk-copied row
+constexpr int PF_RAW_SS = 128 * (32 * PF_VECS + 16);   // bytes of one super-stage of the raw ring at the widest stride
+constexpr int PF_TMEM_COLS = 512;          // 256 accumulator columns + PF_NU * 64 weight columns
+constexpr int PF_SMEM = PF_NBS * PF_B_BYTES + 2 * PF_RAW_SS + 1024;
 
 __device__ int g_prefill_error = 0;
 
@@ -110,71 +117,142 @@ __device__ __forceinline__ int slot_row(const PrefillParams &p, int slot) {
     return (slot & 15) < __ldg(&td->cnt) ? __ldg(&td->row[slot & 15]) : -1;
 }
 
-// 64 ids of one row (NB 64-bit words) -> eight 16-byte groups of fp16 integers, group j at dst + j * 2048.
-template <int NB>
-__device__ __forceinline__ void unpack_row64(const uint64_t (&w)[PF_WORDS], uint8_t *dst) {
-    constexpr uint32_t m = (1u << NB) - 1u;
-    const __half2 k1024 = __halves2half2(__ushort_as_half((unsigned short)0x6400), __ushort_as_half((unsigned short)0x6400));
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-        uint32_t h[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int s = g * 8 * NB + 2 * i * NB;       // first bit of the pair within the row's 64 * NB bits
-            const int idx = s >> 5, sh = s & 31;
-            const uint32_t lo32 = (idx & 1) ? (uint32_t)(w[idx >> 1] >> 32) : (uint32_t)w[idx >> 1];
-            uint32_t t;
-            if (sh == 0) t = lo32;
-            else if (sh + 2 * NB <= 32) t = lo32 >> sh;
-            else {
-                const int i2 = idx + 1;
-                const uint32_t hi32 = (i2 & 1) ? (uint32_t)(w[i2 >> 1] >> 32) : (uint32_t)w[i2 >> 1];
-                t = __funnelshift_r(lo32, hi32, sh);
-            }
-            const uint32_t u = (t & m) | (((t >> NB) & m) << 16) | 0x64006400u;      // two fp16 numbers 1024 + id
-            const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&u), k1024);
-            h[i] = *reinterpret_cast<const uint32_t *>(&v);
-        }
-        *reinterpret_cast<uint4 *>(dst + g * 2048) = make_uint4(h[0], h[1], h[2], h[3]);
+// 32-bit word K of the row words held as 16-byte vectors.
+template <int K>
+__device__ __forceinline__ uint32_t word32(const uint4 (&q)[PF_VECS]) {
+    return (K & 3) == 0 ? q[K >> 2].x : (K & 3) == 1 ? q[K >> 2].y : (K & 3) == 2 ? q[K >> 2].z : q[K >> 2].w;
+}
+
+// The 64 ids of K block H (0 / 1) of a pair -> 32 registers of two fp16 integers each, in column order.
+// q holds the pair's 128 ids: 2 * NB 64-bit words.
+template <int NB, int H, int I = 0>
+__device__ __forceinline__ void unpack64(const uint4 (&q)[PF_VECS], uint32_t (&out)[32]) {
+    if constexpr (I < 32) {
+        constexpr uint32_t m = (1u << NB) - 1u;
+        constexpr int s = I * 2 * NB;                    // first bit of the pair of ids within the K block
+        constexpr int idx = H * 2 * NB + (s >> 5), sh = s & 31;
+        uint32_t t;
+        if constexpr (sh == 0) t = word32<idx>(q);
+        else if constexpr (sh + 2 * NB <= 32) t = word32<idx>(q) >> sh;
+        else t = __funnelshift_r(word32<idx>(q), word32<idx + 1>(q), sh);
+        const uint32_t u = (t & m) | (((t >> NB) & m) << 16) | 0x64006400u;          // two fp16 numbers 1024 + id
+        const __half2 k1024 = __halves2half2(__ushort_as_half((unsigned short)0x6400), __ushort_as_half((unsigned short)0x6400));
+        const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&u), k1024);
+        out[I] = *reinterpret_cast<const uint32_t *>(&v);
+        unpack64<NB, H, I + 1>(q, out);
     }
 }
 
-template <int NACC>
+// 32 registers -> 32 columns of tensor memory, lane = this thread's lane of the warp's quarter.
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+        :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+           "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+           "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+           "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+// Row of the CTA's tile: output row, width, first byte, and how its ids reach the unpack thread.
+//   mode 0: nothing to contract (padding, or a row wider than fp16 holds exactly: recomputed afterwards)
+//   mode 1: bulk copies into the raw ring (widths 1..10, row start 16-byte aligned);  mode 2: id by id from global memory
+struct RowInfo { int row, nb, mode; int64_t bit0; };
+__device__ __forceinline__ RowInfo row_info(const PrefillParams &p, int slot) {
+    RowInfo r;
+    r.row = slot_row(p, slot);
+    r.nb = r.row >= 0 ? __ldg(p.nbits + r.row) : 0;
+    r.bit0 = r.row >= 0 ? __ldg(p.bit_off + r.row) : 0;
+    const bool bulk_ok = (r.bit0 & 127) == 0 && (reinterpret_cast<uintptr_t>(p.ids) & 15) == 0 && r.nb >= 1 && r.nb <= 10;
+    r.mode = (r.row < 0 || r.nb > PF_EXACT_BITS || r.nb < 1) ? 0 : (bulk_ok ? 1 : 2);
+    return r;
+}
+
+// K block H of this thread's pair -> 32 registers (no tensor-memory access in here: rows of different widths or modes
+// diverge inside, and tcgen05.st is a warp-wide instruction that every lane must reach together).
+template <int H>
+__device__ __forceinline__ void unpack_half(const PrefillParams &p, const RowInfo &me, const uint4 (&q)[PF_VECS], int kb, int nkb,
+                                            uint32_t (&out)[32]) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) out[i] = 0u;
+    if (me.mode == 1) {
+        switch (me.nb) {
+        case 1: unpack64<1, H>(q, out); break;
+        case 2: unpack64<2, H>(q, out); break;
+        case 3: unpack64<3, H>(q, out); break;
+        case 4: unpack64<4, H>(q, out); break;
+        case 5: unpack64<5, H>(q, out); break;
+        case 6: unpack64<6, H>(q, out); break;
+        case 7: unpack64<7, H>(q, out); break;
+        case 8: unpack64<8, H>(q, out); break;
+        case 9: unpack64<9, H>(q, out); break;
+        default: unpack64<10, H>(q, out); break;
+        }
+    } else if (me.mode == 2 && kb < nkb) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int col = kb * PF_BK + 2 * i;
+            const uint32_t a0 = field_bytes(p.ids, me.bit0 + (int64_t)col * me.nb, me.nb);
+            const uint32_t a1 = field_bytes(p.ids, me.bit0 + (int64_t)(col + 1) * me.nb, me.nb);
+            const __half2 hh = __halves2half2(__ushort2half_rn((unsigned short)a0), __ushort2half_rn((unsigned short)a1));
+            out[i] = *reinterpret_cast<const uint32_t *>(&hh);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillParams p) {
-    constexpr int ROWS = 128 * NACC;
-    constexpr int A_BYTES = PF_A_HALF * NACC;
-    constexpr int STAGE = A_BYTES + PF_B_BYTES;
-    constexpr int NSTG = NACC == 2 ? 3 : 4;
-    constexpr int GROUPS = 2 / NACC;                    // unpack groups of ROWS threads; group g takes K blocks kb % GROUPS == g
-    constexpr uint32_t TMEM_COLS = 256 * NACC;
-    extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ alignas(8) uint64_t a_full[PF_MAX_STAGES];     // the unpack warps have written the stage's weights
-    __shared__ alignas(8) uint64_t b_full[PF_MAX_STAGES];     // the stage's activations have landed
-    __shared__ alignas(8) uint64_t empty[PF_MAX_STAGES];      // the MMAs that read the stage have completed
+    extern __shared__ __align__(1024) uint8_t smem[];         // PF_NBS activation stages, then the raw ring (2 super-stages)
+    __shared__ alignas(8) uint64_t raw_full[2];               // a super-stage's packed ids have landed
+    __shared__ alignas(8) uint64_t raw_empty[2];              // ... and all eight unpack warps have read them
+    __shared__ alignas(8) uint64_t a_full[PF_NU];             // a pair of K blocks of weights is in tensor memory
+    __shared__ alignas(8) uint64_t a_empty[PF_NU];            // ... and the MMAs that read it have completed
+    __shared__ alignas(8) uint64_t b_full[PF_NBS];            // a stage's activations have landed
+    __shared__ alignas(8) uint64_t b_empty[PF_NBS];           // ... and the MMAs that read them have completed
     __shared__ alignas(8) uint64_t all_done;
     __shared__ uint32_t tmem_base;
-    __shared__ int abort_word;
+    __shared__ int abort_word, nb_max, nb_sum;
     __shared__ float sx[PF_TOK];                              // sum of the narrowed activations of each token of the tile
     volatile int *abort_flag = &abort_word;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int slot0 = blockIdx.x * ROWS;                // first row slot (plan order) of this CTA
+    const int slot0 = blockIdx.x * 128;                 // first row slot (plan order) of this CTA
     const int n0 = blockIdx.y * PF_TOK;
     // surplus tiles at the end of the plan's table are empty: a CTA that starts in them has no rows at all
     if ((slot0 >> 4) >= p.max_tiles || __ldg(&p.tiles[slot0 >> 4].cnt) == 0) return;
     if (tid == 0) {
-        for (int s = 0; s < NSTG; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(pf_smem(&a_full[s])), "r"(4 * NACC) : "memory");
+        for (int s = 0; s < 2; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&raw_full[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;\n" ::"r"(pf_smem(&raw_empty[s])) : "memory");
+        }
+        for (int s = 0; s < PF_NU; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(pf_smem(&a_full[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&a_empty[s])) : "memory");
+        }
+        for (int s = 0; s < PF_NBS; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&b_full[s])) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&empty[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&b_empty[s])) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&all_done)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         abort_word = 0;
+        nb_max = 0;
+        nb_sum = 0;
     }
     if (warp == 0) {                                    // one warp allocates (and later frees) the tensor-memory columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(pf_smem(&tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(pf_smem(&tmem_base)), "r"((uint32_t)PF_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    __syncthreads();
+    // the widest bulk-copied row fixes the row stride of the raw ring; the sum of the widths is the bytes per K block
+    RowInfo me{};
+    if (tid < 128) {
+        me = row_info(p, slot0 + tid);
+        const int nb1 = me.mode == 1 ? me.nb : 0;
+        const int wmax = __reduce_max_sync(0xffffffffu, nb1), wsum = __reduce_add_sync(0xffffffffu, nb1);
+        if (lane == 0) { atomicMax(&nb_max, wmax); atomicAdd(&nb_sum, wsum); }
+    } else if (tid < PF_UNPACK) {
+        me = row_info(p, slot0 + tid - 128);
     }
     if (tid < PF_TOK) {
         float t = 0.f;
@@ -187,93 +265,104 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = tmem_base;
     const int nkb = p.P / PF_BK;
+    const int nss = (nkb + 3) >> 2;                     // super-stages of four K blocks
+    const int stride = 32 * nb_max + 16;                // bytes per row and super-stage in the raw ring: an odd multiple of 16
+    uint8_t *const raw = smem + PF_NBS * PF_B_BYTES;
 
     if (warp < 8) {
         // ------------------------------------------------------------------------------------------ unpack warps
-        const int grp = tid / ROWS;                     // 0 for NACC = 2
-        const int r = tid % ROWS;                       // row of the CTA's tile
-        const int row = slot_row(p, slot0 + r);
-        const int nb = row >= 0 ? __ldg(p.nbits + row) : 0;
-        const int64_t bit0 = row >= 0 ? __ldg(p.bit_off + row) : 0;
-        // mode 0: nothing to contract (padding, or a row wider than fp16 holds exactly: recomputed afterwards)
-        // mode 1: whole 64-bit words, widths 1..10;  mode 2: id by id
-        const bool words_ok = (bit0 & 63) == 0 && (reinterpret_cast<uintptr_t>(p.ids) & 7) == 0 && nb >= 1 && nb <= 10;
-        const int mode = (row < 0 || nb > PF_EXACT_BITS || nb < 1) ? 0 : (words_ok ? 1 : 2);
-        const uint64_t *wrow = reinterpret_cast<const uint64_t *>(p.ids + (bit0 >> 3));
-        uint8_t *const dst_row = smem + (r >> 7) * PF_A_HALF + (r & 127) * 16;
-
-        uint64_t w[PF_WORDS];
+        // group g = warp >> 2 takes K blocks 4 ss + 2 g, + 1 of every super-stage; a thread owns row (warp & 3) * 32 + lane
+        const int g = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 256u;
+        // every wait result is made warp-uniform: the tensor-memory stores below need the whole warp
+        for (int ss = 0; ss < nss; ++ss) {
+            const int kb0 = 4 * ss + 2 * g;
+            bool ok = true;
+            if (nb_sum > 0) ok = pf_wait(pf_smem(&raw_full[ss & 1]), (ss >> 1) & 1, abort_flag, 21);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            uint4 q[PF_VECS];
 #pragma unroll
-        for (int i = 0; i < PF_WORDS; ++i) w[i] = 0;
-        if (mode == 1 && grp < nkb) {
+            for (int i = 0; i < PF_VECS; ++i) q[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (me.mode == 1 && kb0 < nkb) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(raw + (ss & 1) * PF_RAW_SS + r * stride + g * 16 * me.nb);
 #pragma unroll
-            for (int i = 0; i < PF_WORDS; ++i)
-                if (i < nb) w[i] = __ldg(wrow + (int64_t)grp * nb + i);
-        }
-        bool alive = true;
-        for (int kb = grp; kb < nkb && alive; kb += GROUPS) {
-            const int s = kb % NSTG, u = kb / NSTG;
-            uint64_t nx[PF_WORDS];
-#pragma unroll
-            for (int i = 0; i < PF_WORDS; ++i) nx[i] = 0;
-            if (mode == 1 && kb + GROUPS < nkb) {        // the next block's words travel while this one is unpacked
-#pragma unroll
-                for (int i = 0; i < PF_WORDS; ++i)
-                    if (i < nb) nx[i] = __ldg(wrow + (int64_t)(kb + GROUPS) * nb + i);
+                for (int i = 0; i < PF_VECS; ++i)
+                    if (i < me.nb) q[i] = src[i];
             }
-            if (u > 0) alive = pf_wait(pf_smem(&empty[s]), (u - 1) & 1, abort_flag, 21);
-            if (!alive) break;
-            uint8_t *dst = dst_row + s * STAGE;
-            if (mode == 1) {
-                switch (nb) {
-                case 1: unpack_row64<1>(w, dst); break;
-                case 2: unpack_row64<2>(w, dst); break;
-                case 3: unpack_row64<3>(w, dst); break;
-                case 4: unpack_row64<4>(w, dst); break;
-                case 5: unpack_row64<5>(w, dst); break;
-                case 6: unpack_row64<6>(w, dst); break;
-                case 7: unpack_row64<7>(w, dst); break;
-                case 8: unpack_row64<8>(w, dst); break;
-                case 9: unpack_row64<9>(w, dst); break;
-                default: unpack_row64<10>(w, dst); break;
-                }
-            } else if (mode == 2) {
-                for (int g = 0; g < 8; ++g) {
-                    uint32_t h[4];
-                    for (int i = 0; i < 4; ++i) {
-                        const int col = kb * PF_BK + g * 8 + 2 * i;
-                        const uint32_t a0 = field_bytes(p.ids, bit0 + (int64_t)col * nb, nb);
-                        const uint32_t a1 = field_bytes(p.ids, bit0 + (int64_t)(col + 1) * nb, nb);
-                        const __half2 hh = __halves2half2(__ushort2half_rn((unsigned short)a0), __ushort2half_rn((unsigned short)a1));
-                        h[i] = *reinterpret_cast<const uint32_t *>(&hh);
-                    }
-                    *reinterpret_cast<uint4 *>(dst + g * 2048) = make_uint4(h[0], h[1], h[2], h[3]);
-                }
-            } else {
-#pragma unroll
-                for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4 *>(dst + g * 2048) = make_uint4(0u, 0u, 0u, 0u);
+            const int unit = 2 * ss + g, slot = unit & (PF_NU - 1), use = unit / PF_NU;
+            if (use > 0 && kb0 < nkb) ok = pf_wait(pf_smem(&a_empty[slot]), (use - 1) & 1, abort_flag, 22);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            if (kb0 < nkb) {                             // warp-uniform
+                const uint32_t taddr = lane_base + (uint32_t)(slot * 64);
+                uint32_t out[32];
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                unpack_half<0>(p, me, q, kb0, nkb, out);
+                __syncwarp();
+                tmem_store32(taddr, out);
+                unpack_half<1>(p, me, q, kb0 + 1, nkb, out);
+                __syncwarp();
+                tmem_store32(taddr + 32, out);
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // generic-proxy writes -> visible to the MMA
             __syncwarp();
-            if (lane == 0) pf_arrive(pf_smem(&a_full[s]));
-#pragma unroll
-            for (int i = 0; i < PF_WORDS; ++i) w[i] = nx[i];
+            if (lane == 0) {
+                pf_arrive(pf_smem(&raw_empty[ss & 1]));
+                if (kb0 < nkb) pf_arrive(pf_smem(&a_full[slot]));
+            }
         }
     } else if (warp == 8) {
-        // ------------------------------------------------------------------------------------------ activation copies
-        if (lane == 0) {
-            const uint8_t *src = reinterpret_cast<const uint8_t *>(p.X16) + (int64_t)blockIdx.y * nkb * PF_B_BYTES;
-            bool alive = true;
-            for (int kb = 0; kb < nkb && alive; ++kb) {
-                const int s = kb % NSTG, u = kb / NSTG;
-                if (u > 0) alive = pf_wait(pf_smem(&empty[s]), (u - 1) & 1, abort_flag, 22);
-                if (!alive) break;
-                const uint32_t bar = pf_smem(&b_full[s]);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((uint32_t)PF_B_BYTES) : "memory");
+        // ------------------------------------------------------------------------------------------ copies
+        // all lanes: the packed ids of rows lane, lane + 32, ... for a super-stage (one bulk copy per row);
+        // lane 0 also: one 32 KB bulk copy per K block for the activations
+        RowInfo mine[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mine[k] = row_info(p, slot0 + lane + 32 * k);
+        const uint8_t *xsrc = reinterpret_cast<const uint8_t *>(p.X16) + (int64_t)blockIdx.y * nkb * PF_B_BYTES;
+        bool alive = true;
+        auto raw_issue = [&](int ss) {
+            const int nk = min(4, nkb - 4 * ss);
+            if (nb_sum == 0) return;
+            if (ss >= 2) alive = pf_wait(pf_smem(&raw_empty[ss & 1]), ((ss >> 1) - 1) & 1, abort_flag, 23);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) return;
+            const uint32_t bar = pf_smem(&raw_full[ss & 1]);
+            // every row's copy is rounded up to 16 bytes (a row is followed by the next row or by the buffer's padding)
+            uint32_t bytes = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (mine[k].mode == 1) bytes += (uint32_t)((nk * 8 * mine[k].nb + 15) & ~15);
+            const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+            if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(total) : "memory");
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (mine[k].mode != 1) continue;
+                const uint32_t nbytes = (uint32_t)((nk * 8 * mine[k].nb + 15) & ~15);
+                const uint8_t *src = p.ids + (mine[k].bit0 >> 3) + (int64_t)ss * 32 * mine[k].nb;
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                             :: "r"(pf_smem(smem + s * STAGE + A_BYTES)), "l"(src + (int64_t)kb * PF_B_BYTES), "r"((uint32_t)PF_B_BYTES), "r"(bar)
+                             :: "r"(pf_smem(raw + (ss & 1) * PF_RAW_SS + (lane + 32 * k) * stride)), "l"(src), "r"(nbytes), "r"(bar)
                              : "memory");
             }
+        };
+        raw_issue(0);
+        for (int ss = 0; ss < nss && alive; ++ss) {
+            if (ss + 1 < nss) raw_issue(ss + 1);
+            if (!alive) break;
+            if (lane == 0) {
+                for (int kb = 4 * ss; kb < min(nkb, 4 * ss + 4) && alive; ++kb) {
+                    const int s = kb % PF_NBS, u = kb / PF_NBS;
+                    if (u > 0) alive = pf_wait(pf_smem(&b_empty[s]), (u - 1) & 1, abort_flag, 24);
+                    if (!alive) break;
+                    const uint32_t bar = pf_smem(&b_full[s]);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((uint32_t)PF_B_BYTES) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                                 :: "r"(pf_smem(smem + s * PF_B_BYTES)), "l"(xsrc + (int64_t)kb * PF_B_BYTES), "r"((uint32_t)PF_B_BYTES), "r"(bar)
+                                 : "memory");
+                }
+            }
+            alive = __all_sync(0xffffffffu, alive);
         }
     } else {
         // ------------------------------------------------------------------------------------------ MMA issue
@@ -282,49 +371,49 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
             constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(PF_TOK >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             bool alive = true;
             for (int kb = 0; kb < nkb && alive; ++kb) {
-                const int s = kb % NSTG, u = kb / NSTG;
-                alive = pf_wait(pf_smem(&a_full[s]), u & 1, abort_flag, 23);
-                if (alive) alive = pf_wait(pf_smem(&b_full[s]), u & 1, abort_flag, 24);
+                const int s = kb % PF_NBS, u = kb / PF_NBS;
+                const int unit = kb >> 1, slot = unit & (PF_NU - 1), use = unit / PF_NU;
+                if ((kb & 1) == 0) alive = pf_wait(pf_smem(&a_full[slot]), use & 1, abort_flag, 25);
+                if (alive) alive = pf_wait(pf_smem(&b_full[s]), u & 1, abort_flag, 26);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t a32 = pf_smem(smem + s * STAGE), b32 = a32 + A_BYTES;
+                const uint32_t b32 = pf_smem(smem + s * PF_B_BYTES);
+                const uint32_t a_t = tmem + 256u + (uint32_t)(slot * 64 + (kb & 1) * 32);
 #pragma unroll
-                for (int h = 0; h < NACC; ++h) {
-#pragma unroll
-                    for (int kk = 0; kk < PF_BK / 16; ++kk) {
-                        // one MMA covers two 8-column groups: core matrices 2 kk and 2 kk + 1 along K
-                        const uint64_t da = pf_desc(a32 + h * PF_A_HALF + 2 * kk * 2048, 2048, 128);
-                        const uint64_t db = pf_desc(b32 + 2 * kk * (PF_TOK * 16), PF_TOK * 16, 128);
-                        const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
-                        asm volatile(
-                            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                            " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n}\n"
-                            :: "r"(tmem + (uint32_t)(h * 256)), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-                            : "memory");
-                    }
+                for (int kk = 0; kk < PF_BK / 16; ++kk) {
+                    // 16 columns of K: 8 columns of tensor memory (two fp16 each) and two 8-column groups of activations
+                    const uint64_t db = pf_desc(b32 + 2 * kk * (PF_TOK * 16), PF_TOK * 16, 128);
+                    const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
+                    asm volatile(
+                        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n}\n"
+                        :: "r"(tmem), "r"(a_t + (uint32_t)(8 * kk)), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+                        : "memory");
                 }
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&empty[s])) : "memory");
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&b_empty[s])) : "memory");
+                if ((kb & 1) || kb == nkb - 1)
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&a_empty[slot])) : "memory");
                 if (kb == nkb - 1)
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&all_done)) : "memory");
             }
         }
     }
 
-    // ---- epilogue: tensor memory -> registers -> Y.  A warp reads the 32 lanes (warp & 3) * 32 ...; with two
-    // accumulators warps 4..7 take the second, with one they take the upper 128 tokens.
+    // ---- epilogue: tensor memory -> registers -> Y.  A warp reads the 32 lanes (warp & 3) * 32 ...; warps 4..7 take
+    // the upper 128 tokens.
     if (warp < 8) {
         bool alive = !*abort_flag;
-        if (alive) alive = pf_wait(pf_smem(&all_done), 0, abort_flag, 25);
+        if (alive) alive = pf_wait(pf_smem(&all_done), 0, abort_flag, 27);
+        alive = __all_sync(0xffffffffu, alive);          // tcgen05.ld is warp-wide: all lanes or none
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (alive) {
             const int lq = (warp & 3) * 32;
-            const int h = NACC == 2 ? (warp >> 2) : 0;
-            const int cbeg = NACC == 2 ? 0 : (warp >> 2) * 128, cend = NACC == 2 ? 256 : cbeg + 128;
-            const int row = slot_row(p, slot0 + h * 128 + lq + lane);
+            const int cbeg = (warp >> 2) * 128, cend = cbeg + 128;
+            const int row = me.row;
             const float ts = row >= 0 ? __ldg(p.tau_s + row) : 0.f, ms = row >= 0 ? __ldg(p.min_s + row) : 0.f;
             for (int c0 = cbeg; c0 < cend; c0 += 32) {
                 uint32_t d[32];
-                const uint32_t taddr = tmem + ((uint32_t)lq << 16) + (uint32_t)(h * 256 + c0);
+                const uint32_t taddr = tmem + ((uint32_t)lq << 16) + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
                     "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
@@ -354,14 +443,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)PF_TMEM_COLS) : "memory");
 }
 
 // X (M, P) of any input type -> saturated fp16 in the tiled order, tokens padded to Mpad with zeros, and the sums of
 // the narrowed values per token and column range (fixed order: a thread sums its groups in order, then eight warps are
-// added in order).  Block = 32 tokens (lane) x 8 warps; blockIdx.y = column range.
+// added in order).  With escapes a second, column-major copy (P, Mpad) is written for the escape pass.  Block = 32 tokens (lane) x 8 warps; blockIdx.y = column range.
 __global__ void __launch_bounds__(256) prefill_narrow_kernel(const void *__restrict__ X, int x_dtype, int M, int Mpad, int P,
-                                                             __half *__restrict__ X16, float *__restrict__ sumx) {
+                                                             __half *__restrict__ X16, __half *__restrict__ X16T,
+                                                             float *__restrict__ sumx) {
     __shared__ float part[8][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * 32 + lane;
@@ -396,6 +486,10 @@ __global__ void __launch_bounds__(256) prefill_narrow_kernel(const void *__restr
             for (int k = 0; k < 8; ++k) h[k] = __float2half_rn(0.f);
         }
         *reinterpret_cast<uint4 *>(X16 + x16_index(n, g * 8, nkb)) = *reinterpret_cast<const uint4 *>(h);
+        if (X16T) {                                      // column-major copy for the escape pass: tokens contiguous
+#pragma unroll
+            for (int k = 0; k < 8; ++k) X16T[(int64_t)(g * 8 + k) * Mpad + n] = h[k];
+        }
     }
     part[warp][lane] = s;
     __syncthreads();
@@ -407,18 +501,38 @@ __global__ void __launch_bounds__(256) prefill_narrow_kernel(const void *__restr
     }
 }
 
-// Y[m, q] += sum over the escapes of row q of x16[m, col] * (exact - band), in stored order
+// Y[m, q] += sum over the escapes of row q of x16[m, col] * (exact - band), in stored order.  Block = 32 consecutive
+// rows x 256 tokens, thread = token: the activations of an escape's column are read along the tokens (contiguous in the
+// column-major copy), a thread keeps the 32 rows' sums in registers and then updates 128 contiguous bytes of Y.
 __global__ void __launch_bounds__(256) prefill_escapes_kernel(const int *__restrict__ esc_ptr, const int *__restrict__ esc_col,
-                                                              const float *__restrict__ esc_delta, const __half *__restrict__ X16,
-                                                              float *__restrict__ Y, int Q, int P, int M) {
-    const int q = blockIdx.x;
-    const int e0 = __ldg(esc_ptr + q), e1 = __ldg(esc_ptr + q + 1);
-    if (e0 == e1) return;
-    const int nkb = P / PF_BK;
-    for (int m = threadIdx.x; m < M; m += blockDim.x) {
-        float a = 0.f;
-        for (int e = e0; e < e1; ++e) a = __fmaf_rn(__half2float(X16[x16_index(m, __ldg(esc_col + e), nkb)]), __ldg(esc_delta + e), a);
-        Y[(int64_t)m * Q + q] += a;
+                                                              const float *__restrict__ esc_delta, const __half *__restrict__ X16T,
+                                                              float *__restrict__ Y, int Q, int M, int Mpad) {
+    const int q0 = blockIdx.x * 32, n = blockIdx.y * 256 + threadIdx.x;
+    const int qe = min(Q, q0 + 32);
+    if (__ldg(esc_ptr + q0) == __ldg(esc_ptr + qe)) return;
+    float acc[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+        acc[r] = 0.f;
+        if (q0 + r < Q) {
+            const int e0 = __ldg(esc_ptr + q0 + r), e1 = __ldg(esc_ptr + q0 + r + 1);
+            for (int e = e0; e < e1; ++e)
+                acc[r] = __fmaf_rn(__half2float(X16T[(int64_t)__ldg(esc_col + e) * Mpad + n]), __ldg(esc_delta + e), acc[r]);
+        }
+    }
+    if (n >= M) return;
+    float *y = Y + (int64_t)n * Q + q0;
+    if ((Q & 3) == 0 && q0 + 32 <= Q) {
+#pragma unroll
+        for (int r = 0; r < 32; r += 4) {
+            float4 v = *reinterpret_cast<float4 *>(y + r);
+            v.x += acc[r]; v.y += acc[r + 1]; v.z += acc[r + 2]; v.w += acc[r + 3];
+            *reinterpret_cast<float4 *>(y + r) = v;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < 32; ++r)
+            if (q0 + r < Q) y[r] += acc[r];
     }
 }
 
@@ -458,35 +572,27 @@ int prefill_error_word(int *out) {
     return QVB8_OK;
 }
 
-static int g_prefill_rows = 0;      // tuning: 0 = choose, 128 / 256 = rows per CTA
-
-template <int NACC>
 static int launch_prefill(const PrefillParams &prm, cudaStream_t st) {
-    constexpr int STAGE = PF_A_HALF * NACC + PF_B_BYTES;
-    constexpr int NSTG = NACC == 2 ? 3 : 4;
-    constexpr int SMEM = NSTG * STAGE + 1024;
     static thread_local int granted_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != granted_dev) {
-        if (cudaFuncSetAttribute(prefill_kernel<NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM) != cudaSuccess)
             return cuda_status("qvb8_prefill: shared memory opt-in");
         granted_dev = dev;
     }
     const int slots = prm.max_tiles * 16;
-    const dim3 grid((unsigned)((slots + 128 * NACC - 1) / (128 * NACC)), (unsigned)(prm.Mpad / PF_TOK));
-    prefill_kernel<NACC><<<grid, PF_THREADS, SMEM, st>>>(prm);
+    const dim3 grid((unsigned)((slots + 127) / 128), (unsigned)(prm.Mpad / PF_TOK));
+    prefill_kernel<<<grid, PF_THREADS, PF_SMEM, st>>>(prm);
     return cuda_status("qvb8_prefill");
 }
 
 }  // namespace qv
 
-QV_API void qvb8_prefill_set_tuning(int rows_per_cta) { qv::g_prefill_rows = rows_per_cta; }
-
 QV_API int64_t qvb8_prefill_scratch_bytes(int64_t M, int64_t Q, int64_t P) {
     if (M <= 0 || P <= 0 || Q < 0) return 0;
     const int64_t Mpad = (M + qv::PF_TOK - 1) / qv::PF_TOK * qv::PF_TOK;
-    return qv::up256(Mpad * P * 2) + qv::up256(qv::PF_KS * Mpad * 4) + qv::up256((Q + 1) * 4);
+    return 2 * qv::up256(Mpad * P * 2) + qv::up256(qv::PF_KS * Mpad * 4) + qv::up256((Q + 1) * 4);
 }
 
 QV_API int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int64_t M, float *Y, void *scratch,
@@ -507,36 +613,26 @@ QV_API int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int
     const int64_t Mpad = (M + PF_TOK - 1) / PF_TOK * PF_TOK;
     uint8_t *sc = reinterpret_cast<uint8_t *>(scratch);
     __half *X16 = reinterpret_cast<__half *>(sc);
-    float *sumx = reinterpret_cast<float *>(sc + up256(Mpad * w->P * 2));
+    __half *X16T = reinterpret_cast<__half *>(sc + up256(Mpad * w->P * 2));      // written only for packs with escapes
+    float *sumx = reinterpret_cast<float *>(sc + 2 * up256(Mpad * w->P * 2));
     int *wide = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(sumx) + up256(PF_KS * Mpad * 4));      // [0] count, then rows
-    prefill_narrow_kernel<<<dim3((unsigned)(Mpad / 32), PF_KS), 256, 0, st>>>(X, x_dtype, (int)M, (int)Mpad, (int)w->P, X16, sumx);
+    prefill_narrow_kernel<<<dim3((unsigned)(Mpad / 32), PF_KS), 256, 0, st>>>(X, x_dtype, (int)M, (int)Mpad, (int)w->P, X16, w->n_esc > 0 ? X16T : nullptr, sumx);
     if (int rc = cuda_status("qvb8_prefill narrow")) return rc;
 
     const PlanLayout L = plan_layout(w->Q, w->n_esc);
     const uint8_t *pb = reinterpret_cast<const uint8_t *>(plan);
     PrefillParams prm{w->ids, w->min_s, w->tau_s, w->nbits, w->bit_off, reinterpret_cast<const TileDesc *>(pb + L.tiles), L.max_tiles,
                       X16, sumx, Y, (int)w->Q, (int)w->P, (int)M, (int)Mpad};
-    // rows per CTA: 256 halves the activation traffic per SM; 128 gives twice as many CTAs.  Take the one whose last
-    // wave wastes less (a 256-row CTA takes twice as long; a 128-row one is charged 15 % for the extra traffic).
-    int sms = 148;
-    {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    }
-    const int64_t tok_tiles = Mpad / PF_TOK;
-    const int64_t c256 = ((int64_t)L.max_tiles * 16 + 255) / 256 * tok_tiles, c128 = ((int64_t)L.max_tiles * 16 + 127) / 128 * tok_tiles;
-    const double t256 = (double)((c256 + sms - 1) / sms) * 2.0, t128 = (double)((c128 + sms - 1) / sms) * 1.15;
-    const int rows = g_prefill_rows ? g_prefill_rows : (t256 <= t128 ? 256 : 128);
-    if (int rc = rows == 256 ? launch_prefill<2>(prm, st) : launch_prefill<1>(prm, st)) return rc;
+    if (int rc = launch_prefill(prm, st)) return rc;
 
     if (cudaMemsetAsync(wide, 0, sizeof(int), st) != cudaSuccess) return cuda_status("qvb8_prefill memset");
     prefill_wide_list_kernel<<<(unsigned)((w->Q + 255) / 256), 256, 0, st>>>(w->nbits, (int)w->Q, wide + 1, wide);
     prefill_wide_rows_kernel<<<dim3(64, (unsigned)((M + 7) / 8)), 256, 0, st>>>(prm, wide + 1, wide);
     if (int rc = cuda_status("qvb8_prefill wide rows")) return rc;
     if (w->n_esc > 0) {
-        prefill_escapes_kernel<<<(unsigned)w->Q, 256, 0, st>>>(reinterpret_cast<const int *>(pb + L.esc_ptr), reinterpret_cast<const int *>(pb + L.esc_col),
-                                                              reinterpret_cast<const float *>(pb + L.esc_delta), X16, Y, (int)w->Q, (int)w->P, (int)M);
+        prefill_escapes_kernel<<<dim3((unsigned)((w->Q + 31) / 32), (unsigned)(Mpad / 256)), 256, 0, st>>>(
+            reinterpret_cast<const int *>(pb + L.esc_ptr), reinterpret_cast<const int *>(pb + L.esc_col),
+            reinterpret_cast<const float *>(pb + L.esc_delta), X16T, Y, (int)w->Q, (int)M, (int)Mpad);
         if (int rc = cuda_status("qvb8_prefill escapes")) return rc;
     }
     return QVB8_OK;
