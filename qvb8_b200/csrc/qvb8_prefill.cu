@@ -16,13 +16,14 @@
 //   main     a CTA owns 128 output rows (in the plan's width-sorted order) and 256 tokens; K advances in blocks of 64
 //            columns.  The weights reach the tensor cores through TENSOR MEMORY (tcgen05.mma with the A operand in
 //            tensor memory), so shared memory carries only the activations and the packed ids:
-//              warp 8      copies.  Every lane: one bulk copy per row and super-stage (four K blocks = 32 * nb bytes of
-//                          a row) into a two-deep raw ring whose row stride is an odd multiple of 16 bytes; lane 0
-//                          also: one 32 KB bulk copy per K block for the activations (four stages)
-//              warps 0..7  unpack.  A thread owns one row; warps 0..3 take the first pair of K blocks of a
-//                          super-stage, warps 4..7 the second.  128 ids = nb 16-byte vectors from the raw ring,
-//                          pairs -> fp16 integers with shift / mask / or 0x6400 / subtract 1024, 64 registers ->
-//                          tcgen05.st into the thread's lane of one of four 64-column weight slots
+//              warps 0..7  unpack.  A thread owns one row; warps 0..3 take the first pair of K blocks of every four,
+//                          warps 4..7 the second.  A warp fetches its own 32 rows x 128 ids with 16-byte cp.async
+//                          (eight lanes per row: whole lines, not one line per lane) into a private double buffer
+//                          whose row stride is an odd multiple of 16 bytes, one pair ahead; then every thread reads
+//                          its row (nb 16-byte vectors), turns pairs of ids into fp16 integers with shift / mask /
+//                          or 0x6400 / subtract 1024, and stores 64 registers with tcgen05.st into its lane of one of
+//                          four 64-column weight slots
+//              warp 8      one thread: one 32 KB bulk copy per K block for the activations (four stages)
 //              warp 9      one thread: waits for a weight slot and an activation stage, issues four tcgen05.mma
 //                          (128 x 256 x 16, accumulator in columns 0..255) per K block and commits them to the
 //                          barriers that free the stage and the slot
@@ -48,9 +49,9 @@ constexpr int PF_EXACT_BITS = 11;          // ids up to this width are exact in 
 constexpr int PF_NBS = 4;                  // activation stages in shared memory
 constexpr int PF_NU = 4;                   // weight units (pairs of K blocks, 64 columns) in tensor memory
 constexpr int PF_VECS = 10;                // 16-byte vectors of a pair of K blocks (128 ids) of the widest bulk-copied row
-constexpr int PF_RAW_SS = 128 * (32 * PF_VECS + 16);   // bytes of one super-stage of the raw ring at the widest stride
+constexpr int PF_RAW_BUF = 32 * 16 * (PF_VECS | 1);   // bytes of one warp's buffer for a pair at the widest row stride
 constexpr int PF_TMEM_COLS = 512;          // 256 accumulator columns + PF_NU * 64 weight columns
-constexpr int PF_SMEM = PF_NBS * PF_B_BYTES + 2 * PF_RAW_SS + 1024;
+constexpr int PF_SMEM = PF_NBS * PF_B_BYTES + 8 * 2 * PF_RAW_BUF + 1024;
 
 __device__ int g_prefill_error = 0;
 
@@ -157,7 +158,7 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)
 
 // Row of the CTA's tile: output row, width, first byte, and how its ids reach the unpack thread.
 //   mode 0: nothing to contract (padding, or a row wider than fp16 holds exactly: recomputed afterwards)
-//   mode 1: bulk copies into the raw ring (widths 1..10, row start 16-byte aligned);  mode 2: id by id from global memory
+//   mode 1: 16-byte copies into the warp's buffer (widths 1..10, row start 16-byte aligned);  mode 2: id by id from global memory
 struct RowInfo { int row, nb, mode; int64_t bit0; };
 __device__ __forceinline__ RowInfo row_info(const PrefillParams &p, int slot) {
     RowInfo r;
@@ -202,16 +203,16 @@ __device__ __forceinline__ void unpack_half(const PrefillParams &p, const RowInf
 }
 
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];         // PF_NBS activation stages, then the raw ring (2 super-stages)
-    __shared__ alignas(8) uint64_t raw_full[2];               // a super-stage's packed ids have landed
-    __shared__ alignas(8) uint64_t raw_empty[2];              // ... and all eight unpack warps have read them
+    extern __shared__ __align__(1024) uint8_t smem[];         // PF_NBS activation stages, then 8 warps x 2 buffers of packed ids
     __shared__ alignas(8) uint64_t a_full[PF_NU];             // a pair of K blocks of weights is in tensor memory
     __shared__ alignas(8) uint64_t a_empty[PF_NU];            // ... and the MMAs that read it have completed
     __shared__ alignas(8) uint64_t b_full[PF_NBS];            // a stage's activations have landed
     __shared__ alignas(8) uint64_t b_empty[PF_NBS];           // ... and the MMAs that read them have completed
     __shared__ alignas(8) uint64_t all_done;
     __shared__ uint32_t tmem_base;
-    __shared__ int abort_word, nb_max, nb_sum;
+    __shared__ int abort_word, nb_max;
+    __shared__ const uint8_t *row_src[128];                   // first byte of each row of the tile (mode 1 rows)
+    __shared__ int row_nb1[128];                              // its width, 0 unless mode 1
     __shared__ float sx[PF_TOK];                              // sum of the narrowed activations of each token of the tile
     volatile int *abort_flag = &abort_word;
 
@@ -221,10 +222,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
     // surplus tiles at the end of the plan's table are empty: a CTA that starts in them has no rows at all
     if ((slot0 >> 4) >= p.max_tiles || __ldg(&p.tiles[slot0 >> 4].cnt) == 0) return;
     if (tid == 0) {
-        for (int s = 0; s < 2; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&raw_full[s])) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;\n" ::"r"(pf_smem(&raw_empty[s])) : "memory");
-        }
         for (int s = 0; s < PF_NU; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(pf_smem(&a_full[s])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&a_empty[s])) : "memory");
@@ -237,20 +234,21 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         abort_word = 0;
         nb_max = 0;
-        nb_sum = 0;
     }
     if (warp == 0) {                                    // one warp allocates (and later frees) the tensor-memory columns
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(pf_smem(&tmem_base)), "r"((uint32_t)PF_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     __syncthreads();
-    // the widest bulk-copied row fixes the row stride of the raw ring; the sum of the widths is the bytes per K block
+    // the widest copied row fixes the row stride of the warps' buffers
     RowInfo me{};
     if (tid < 128) {
         me = row_info(p, slot0 + tid);
         const int nb1 = me.mode == 1 ? me.nb : 0;
-        const int wmax = __reduce_max_sync(0xffffffffu, nb1), wsum = __reduce_add_sync(0xffffffffu, nb1);
-        if (lane == 0) { atomicMax(&nb_max, wmax); atomicAdd(&nb_sum, wsum); }
+        row_src[tid] = p.ids + (me.bit0 >> 3);
+        row_nb1[tid] = nb1;
+        const int wmax = __reduce_max_sync(0xffffffffu, nb1);
+        if (lane == 0) atomicMax(&nb_max, wmax);
     } else if (tid < PF_UNPACK) {
         me = row_info(p, slot0 + tid - 128);
     }
@@ -265,27 +263,48 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = tmem_base;
     const int nkb = p.P / PF_BK;
-    const int nss = (nkb + 3) >> 2;                     // super-stages of four K blocks
-    const int stride = 32 * nb_max + 16;                // bytes per row and super-stage in the raw ring: an odd multiple of 16
-    uint8_t *const raw = smem + PF_NBS * PF_B_BYTES;
+    const int nss = (nkb + 3) >> 2;                     // rounds of four K blocks: one pair per unpack group
+    const int stride = 16 * (nb_max | 1);               // bytes per row in a warp's buffer: an odd multiple of 16
 
     if (warp < 8) {
         // ------------------------------------------------------------------------------------------ unpack warps
         // group g = warp >> 2 takes K blocks 4 ss + 2 g, + 1 of every super-stage; a thread owns row (warp & 3) * 32 + lane
         const int g = warp >> 2;
-        const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 256u;
+        uint8_t *const mybuf = smem + PF_NBS * PF_B_BYTES + warp * 2 * PF_RAW_BUF;
+        // the warp's rows of pair `unit` -> buffer (unit >> 1) & 1: eight lanes per row, 16 bytes each; one commit group
+        auto fetch = [&](int ss_) {
+            const int kb0_ = 4 * ss_ + 2 * g;
+            if (ss_ < nss && kb0_ < nkb) {
+                const int nkv = min(2, nkb - kb0_);
+                uint8_t *buf = mybuf + (ss_ & 1) * PF_RAW_BUF;
+#pragma unroll
+                for (int pp = 0; pp < 8; ++pp) {
+                    const int row = pp * 4 + (lane >> 3);
+                    const int nb1 = row_nb1[(warp & 3) * 32 + row];
+                    // a last, single K block is 8 * nb bytes: rounded up to 16 (a row is followed by the next row or by
+                    // the buffer's 8 bytes of padding)
+                    const int nv = (nkv * 8 * nb1 + 15) >> 4;
+                    const uint8_t *src = row_src[(warp & 3) * 32 + row] + (int64_t)(2 * ss_ + g) * 16 * nb1;
+                    for (int v = lane & 7; v < nv; v += 8)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(pf_smem(buf + row * stride + v * 16)), "l"(src + v * 16) : "memory");
+                }
+            }
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+        };
+        fetch(0);
         // every wait result is made warp-uniform: the tensor-memory stores below need the whole warp
         for (int ss = 0; ss < nss; ++ss) {
             const int kb0 = 4 * ss + 2 * g;
+            fetch(ss + 1);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+            __syncwarp();
             bool ok = true;
-            if (nb_sum > 0) ok = pf_wait(pf_smem(&raw_full[ss & 1]), (ss >> 1) & 1, abort_flag, 21);
-            if (!__all_sync(0xffffffffu, ok)) break;
             uint4 q[PF_VECS];
 #pragma unroll
             for (int i = 0; i < PF_VECS; ++i) q[i] = make_uint4(0u, 0u, 0u, 0u);
             if (me.mode == 1 && kb0 < nkb) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(raw + (ss & 1) * PF_RAW_SS + r * stride + g * 16 * me.nb);
+                const uint4 *src = reinterpret_cast<const uint4 *>(mybuf + (ss & 1) * PF_RAW_BUF + lane * stride);
 #pragma unroll
                 for (int i = 0; i < PF_VECS; ++i)
                     if (i < me.nb) q[i] = src[i];
@@ -307,62 +326,24 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
                 asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             }
             __syncwarp();
-            if (lane == 0) {
-                pf_arrive(pf_smem(&raw_empty[ss & 1]));
-                if (kb0 < nkb) pf_arrive(pf_smem(&a_full[slot]));
-            }
+            if (lane == 0 && kb0 < nkb) pf_arrive(pf_smem(&a_full[slot]));
         }
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     } else if (warp == 8) {
-        // ------------------------------------------------------------------------------------------ copies
-        // all lanes: the packed ids of rows lane, lane + 32, ... for a super-stage (one bulk copy per row);
-        // lane 0 also: one 32 KB bulk copy per K block for the activations
-        RowInfo mine[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mine[k] = row_info(p, slot0 + lane + 32 * k);
-        const uint8_t *xsrc = reinterpret_cast<const uint8_t *>(p.X16) + (int64_t)blockIdx.y * nkb * PF_B_BYTES;
-        bool alive = true;
-        auto raw_issue = [&](int ss) {
-            const int nk = min(4, nkb - 4 * ss);
-            if (nb_sum == 0) return;
-            if (ss >= 2) alive = pf_wait(pf_smem(&raw_empty[ss & 1]), ((ss >> 1) - 1) & 1, abort_flag, 23);
-            alive = __all_sync(0xffffffffu, alive);
-            if (!alive) return;
-            const uint32_t bar = pf_smem(&raw_full[ss & 1]);
-            // every row's copy is rounded up to 16 bytes (a row is followed by the next row or by the buffer's padding)
-            uint32_t bytes = 0;
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (mine[k].mode == 1) bytes += (uint32_t)((nk * 8 * mine[k].nb + 15) & ~15);
-            const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
-            if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(total) : "memory");
-            __syncwarp();
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                if (mine[k].mode != 1) continue;
-                const uint32_t nbytes = (uint32_t)((nk * 8 * mine[k].nb + 15) & ~15);
-                const uint8_t *src = p.ids + (mine[k].bit0 >> 3) + (int64_t)ss * 32 * mine[k].nb;
+        // ------------------------------------------------------------------------------------------ activation copies
+        if (lane == 0) {
+            const uint8_t *xsrc = reinterpret_cast<const uint8_t *>(p.X16) + (int64_t)blockIdx.y * nkb * PF_B_BYTES;
+            bool alive = true;
+            for (int kb = 0; kb < nkb && alive; ++kb) {
+                const int s = kb % PF_NBS, u = kb / PF_NBS;
+                if (u > 0) alive = pf_wait(pf_smem(&b_empty[s]), (u - 1) & 1, abort_flag, 24);
+                if (!alive) break;
+                const uint32_t bar = pf_smem(&b_full[s]);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((uint32_t)PF_B_BYTES) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                             :: "r"(pf_smem(raw + (ss & 1) * PF_RAW_SS + (lane + 32 * k) * stride)), "l"(src), "r"(nbytes), "r"(bar)
+                             :: "r"(pf_smem(smem + s * PF_B_BYTES)), "l"(xsrc + (int64_t)kb * PF_B_BYTES), "r"((uint32_t)PF_B_BYTES), "r"(bar)
                              : "memory");
             }
-        };
-        raw_issue(0);
-        for (int ss = 0; ss < nss && alive; ++ss) {
-            if (ss + 1 < nss) raw_issue(ss + 1);
-            if (!alive) break;
-            if (lane == 0) {
-                for (int kb = 4 * ss; kb < min(nkb, 4 * ss + 4) && alive; ++kb) {
-                    const int s = kb % PF_NBS, u = kb / PF_NBS;
-                    if (u > 0) alive = pf_wait(pf_smem(&b_empty[s]), (u - 1) & 1, abort_flag, 24);
-                    if (!alive) break;
-                    const uint32_t bar = pf_smem(&b_full[s]);
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((uint32_t)PF_B_BYTES) : "memory");
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                                 :: "r"(pf_smem(smem + s * PF_B_BYTES)), "l"(xsrc + (int64_t)kb * PF_B_BYTES), "r"((uint32_t)PF_B_BYTES), "r"(bar)
-                                 : "memory");
-                }
-            }
-            alive = __all_sync(0xffffffffu, alive);
         }
     } else {
         // ------------------------------------------------------------------------------------------ MMA issue
