@@ -93,9 +93,13 @@ __device__ __forceinline__ uint64_t pf_desc(uint32_t addr, uint32_t lbo, uint32_
            ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
 }
 
-// Position (in halves) of activation (token n, column c) in the tiled fp16 copy; nkb = P / 64.
+// Position (in halves) of activation (token n, column c) in the tiled fp16 copy; nkb = P / 64.  Inside every group of
+// four columns the order is 0, 2, 1, 3: the unpack threads build fp16 pairs from ids two columns apart (for 6..8-bit
+// rows such a pair comes out of ONE 32-bit window), so a 32-bit operand register holds columns (k, k + 2) and the
+// activations follow the same order.
+__host__ __device__ __forceinline__ int pair_order(int a) { return (((a >> 1) ^ a) & 1) ? (a ^ 3) : a; }
 __host__ __device__ __forceinline__ int64_t x16_index(int n, int c, int nkb) {
-    return ((((int64_t)(n >> 8) * nkb + (c >> 6)) * 8 + ((c >> 3) & 7)) * PF_TOK + (n & 255)) * 8 + (c & 7);
+    return ((((int64_t)(n >> 8) * nkb + (c >> 6)) * 8 + ((c >> 3) & 7)) * PF_TOK + (n & 255)) * 8 + pair_order(c & 7);
 }
 
 struct PrefillParams {
@@ -119,29 +123,69 @@ __device__ __forceinline__ int slot_row(const PrefillParams &p, int slot) {
 }
 
 // 32-bit word K of the row words held as 16-byte vectors.
-template <int K>
-__device__ __forceinline__ uint32_t word32(const uint4 (&q)[PF_VECS]) {
+template <int K, int NV>
+__device__ __forceinline__ uint32_t word32(const uint4 (&q)[NV]) {
+    static_assert(K >= 0 && K < 4 * NV, "word outside the pair");
     return (K & 3) == 0 ? q[K >> 2].x : (K & 3) == 1 ? q[K >> 2].y : (K & 3) == 2 ? q[K >> 2].z : q[K >> 2].w;
 }
 
-// The 64 ids of K block H (0 / 1) of a pair -> 32 registers of two fp16 integers each, in column order.
-// q holds the pair's 128 ids: 2 * NB 64-bit words.
+// 32 bits of the pair's bit string such that bit `G` of the string lands at bit `AT` of the result; the caller uses
+// the SPAN bits from AT on.
+template <int G, int AT, int SPAN, int NV>
+__device__ __forceinline__ uint32_t window(const uint4 (&q)[NV]) {
+    constexpr int P0 = G - AT;                            // string position of result bit 0
+    if constexpr (P0 < 0) return word32<0, NV>(q) << (-P0);
+    else {
+        constexpr int idx = P0 >> 5, sh = P0 & 31;
+        if constexpr (sh == 0) return word32<idx, NV>(q);
+        else if constexpr (sh + AT + SPAN <= 32) return word32<idx, NV>(q) >> sh;
+        else return __funnelshift_r(word32<idx, NV>(q), word32<idx + 1, NV>(q), sh);
+    }
+}
+
+// The 64 ids of K block H (0 / 1) of a pair of K blocks -> 32 registers of two fp16 integers each.  Register c holds
+// columns k and k + 2, k = 4 * (c >> 1) + (c & 1) (see pair_order).  q holds the 128 ids (NB 16-byte vectors).
+//   6..8 bits: ONE window puts id k at bit E = 16 - 2 NB and id k + 2 at bit 16; mask | 0x64006400 gives the fp16
+//              numbers 1024 + id * 2^E and 1024 + id; one HFMA2 scales and removes the 1024 (exact)
+//   others:    two windows, two masks, one subtraction of 1024
+// The shifts and logic operations run on the half-rate integer pipe, which is what bounds this kernel: two instead of
+// four of them per pair for the common widths.
 template <int NB, int H, int I = 0>
-__device__ __forceinline__ void unpack64(const uint4 (&q)[PF_VECS], uint32_t (&out)[32]) {
+__device__ __forceinline__ void unpack64(const uint4 (&q)[NB], uint32_t (&out)[32]) {
     if constexpr (I < 32) {
         constexpr uint32_t m = (1u << NB) - 1u;
-        constexpr int s = I * 2 * NB;                    // first bit of the pair of ids within the K block
-        constexpr int idx = H * 2 * NB + (s >> 5), sh = s & 31;
-        uint32_t t;
-        if constexpr (sh == 0) t = word32<idx>(q);
-        else if constexpr (sh + 2 * NB <= 32) t = word32<idx>(q) >> sh;
-        else t = __funnelshift_r(word32<idx>(q), word32<idx + 1>(q), sh);
-        const uint32_t u = (t & m) | (((t >> NB) & m) << 16) | 0x64006400u;          // two fp16 numbers 1024 + id
-        const __half2 k1024 = __halves2half2(__ushort_as_half((unsigned short)0x6400), __ushort_as_half((unsigned short)0x6400));
-        const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&u), k1024);
-        out[I] = *reinterpret_cast<const uint32_t *>(&v);
+        constexpr int k = 4 * (I >> 1) + (I & 1);
+        constexpr int G0 = (H * 64 + k) * NB, G1 = G0 + 2 * NB;
+        if constexpr (NB >= 6 && NB <= 8) {
+            constexpr int E = 16 - 2 * NB;
+            const uint32_t t = window<G0, E, 16 - E + NB, NB>(q);
+            const uint32_t u = (t & ((m << E) | (m << 16))) | 0x64006400u;
+            __half2 v;
+            if constexpr (E == 0) {
+                v = __hsub2(*reinterpret_cast<const __half2 *>(&u), __floats2half2_rn(1024.f, 1024.f));
+            } else {
+                constexpr float sc = 1.0f / (float)(1 << E);
+                v = __hfma2(*reinterpret_cast<const __half2 *>(&u), __floats2half2_rn(sc, 1.0f), __floats2half2_rn(-1024.f * sc, -1024.f));
+            }
+            out[I] = *reinterpret_cast<const uint32_t *>(&v);
+        } else {
+            const uint32_t lo = window<G0, 0, NB, NB>(q), hi = window<G1, 16, NB, NB>(q);
+            const uint32_t u = (hi & (m << 16)) | ((lo & m) | 0x64006400u);
+            const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&u), __floats2half2_rn(1024.f, 1024.f));
+            out[I] = *reinterpret_cast<const uint32_t *>(&v);
+        }
         unpack64<NB, H, I + 1>(q, out);
     }
+}
+
+// A row of width NB: its vectors from the warp's buffer, both K blocks of the pair to registers.
+template <int NB>
+__device__ __forceinline__ void unpack_row(const uint4 *__restrict__ src, uint32_t (&out0)[32], uint32_t (&out1)[32]) {
+    uint4 q[NB];
+#pragma unroll
+    for (int i = 0; i < NB; ++i) q[i] = src[i];
+    unpack64<NB, 0>(q, out0);
+    unpack64<NB, 1>(q, out1);
 }
 
 // 32 registers -> 32 columns of tensor memory, lane = this thread's lane of the warp's quarter.
@@ -170,34 +214,47 @@ __device__ __forceinline__ RowInfo row_info(const PrefillParams &p, int slot) {
     return r;
 }
 
-// K block H of this thread's pair -> 32 registers (no tensor-memory access in here: rows of different widths or modes
-// diverge inside, and tcgen05.st is a warp-wide instruction that every lane must reach together).
-template <int H>
-__device__ __forceinline__ void unpack_half(const PrefillParams &p, const RowInfo &me, const uint4 (&q)[PF_VECS], int kb, int nkb,
-                                            uint32_t (&out)[32]) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) out[i] = 0u;
+// The rare rows that are read id by id (11 bits wide, or not starting on 16 bytes): one K block to registers.
+__device__ __noinline__ void unpack_generic(const uint8_t *__restrict__ ids, int64_t bit0, int nb, int kb, uint32_t *out) {
+    for (int i = 0; i < 32; ++i) {
+        const int col = kb * PF_BK + 4 * (i >> 1) + (i & 1);          // register i holds columns col, col + 2
+        const uint32_t a0 = field_bytes(ids, bit0 + (int64_t)col * nb, nb);
+        const uint32_t a1 = field_bytes(ids, bit0 + (int64_t)(col + 2) * nb, nb);
+        const __half2 hh = __halves2half2(__ushort2half_rn((unsigned short)a0), __ushort2half_rn((unsigned short)a1));
+        out[i] = *reinterpret_cast<const uint32_t *>(&hh);
+    }
+}
+
+// Both K blocks of this thread's pair -> 2 x 32 registers.  No tensor-memory access in here: rows of different widths
+// or modes diverge inside, and tcgen05.st is a warp-wide instruction that every lane must reach together.
+__device__ __forceinline__ void unpack_pair(const PrefillParams &p, const RowInfo &me, const uint4 *__restrict__ src, int kb0, int nkb,
+                                            uint32_t (&out0)[32], uint32_t (&out1)[32]) {
     if (me.mode == 1) {
         switch (me.nb) {
-        case 1: unpack64<1, H>(q, out); break;
-        case 2: unpack64<2, H>(q, out); break;
-        case 3: unpack64<3, H>(q, out); break;
-        case 4: unpack64<4, H>(q, out); break;
-        case 5: unpack64<5, H>(q, out); break;
-        case 6: unpack64<6, H>(q, out); break;
-        case 7: unpack64<7, H>(q, out); break;
-        case 8: unpack64<8, H>(q, out); break;
-        case 9: unpack64<9, H>(q, out); break;
-        default: unpack64<10, H>(q, out); break;
+        case 1: unpack_row<1>(src, out0, out1); break;
+        case 2: unpack_row<2>(src, out0, out1); break;
+        case 3: unpack_row<3>(src, out0, out1); break;
+        case 4: unpack_row<4>(src, out0, out1); break;
+        case 5: unpack_row<5>(src, out0, out1); break;
+        case 6: unpack_row<6>(src, out0, out1); break;
+        case 7: unpack_row<7>(src, out0, out1); break;
+        case 8: unpack_row<8>(src, out0, out1); break;
+        case 9: unpack_row<9>(src, out0, out1); break;
+        default: unpack_row<10>(src, out0, out1); break;
         }
-    } else if (me.mode == 2 && kb < nkb) {
+    } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int col = kb * PF_BK + 2 * i;
-            const uint32_t a0 = field_bytes(p.ids, me.bit0 + (int64_t)col * me.nb, me.nb);
-            const uint32_t a1 = field_bytes(p.ids, me.bit0 + (int64_t)(col + 1) * me.nb, me.nb);
-            const __half2 hh = __halves2half2(__ushort2half_rn((unsigned short)a0), __ushort2half_rn((unsigned short)a1));
-            out[i] = *reinterpret_cast<const uint32_t *>(&hh);
+        for (int i = 0; i < 32; ++i) { out0[i] = 0u; out1[i] = 0u; }
+        if (me.mode == 2) {                              // through a stack buffer, so that out0 / out1 stay registers
+            uint32_t tmp[32];
+            unpack_generic(p.ids, me.bit0, me.nb, kb0, tmp);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) out0[i] = tmp[i];
+            if (kb0 + 1 < nkb) {
+                unpack_generic(p.ids, me.bit0, me.nb, kb0 + 1, tmp);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) out1[i] = tmp[i];
+            }
         }
     }
 }
@@ -272,22 +329,34 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
         const int g = warp >> 2;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 256u;
         uint8_t *const mybuf = smem + PF_NBS * PF_B_BYTES + warp * 2 * PF_RAW_BUF;
-        // the warp's rows of pair `unit` -> buffer (unit >> 1) & 1: eight lanes per row, 16 bytes each; one commit group
+        // the warp's rows of a pair -> one of its two buffers: eight lanes per row, 16 bytes each (a second round for
+        // rows wider than 8 bits); one commit group per pair.  Per-lane constants: this lane's vector of rows 4 pp + lane / 8.
+        const uint8_t *src0[8];
+        int step[8], nbr[8];
+#pragma unroll
+        for (int pp = 0; pp < 8; ++pp) {
+            const int rr = (warp & 3) * 32 + pp * 4 + (lane >> 3);
+            nbr[pp] = row_nb1[rr];
+            step[pp] = 16 * nbr[pp];
+            src0[pp] = row_src[rr] + (lane & 7) * 16;
+        }
+        const uint32_t dst0 = pf_smem(mybuf) + (uint32_t)((lane >> 3) * stride + (lane & 7) * 16);
         auto fetch = [&](int ss_) {
             const int kb0_ = 4 * ss_ + 2 * g;
             if (ss_ < nss && kb0_ < nkb) {
                 const int nkv = min(2, nkb - kb0_);
-                uint8_t *buf = mybuf + (ss_ & 1) * PF_RAW_BUF;
+                const int unit_ = 2 * ss_ + g;
+                const uint32_t dst = dst0 + (uint32_t)((ss_ & 1) * PF_RAW_BUF);
 #pragma unroll
                 for (int pp = 0; pp < 8; ++pp) {
-                    const int row = pp * 4 + (lane >> 3);
-                    const int nb1 = row_nb1[(warp & 3) * 32 + row];
                     // a last, single K block is 8 * nb bytes: rounded up to 16 (a row is followed by the next row or by
                     // the buffer's 8 bytes of padding)
-                    const int nv = (nkv * 8 * nb1 + 15) >> 4;
-                    const uint8_t *src = row_src[(warp & 3) * 32 + row] + (int64_t)(2 * ss_ + g) * 16 * nb1;
-                    for (int v = lane & 7; v < nv; v += 8)
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(pf_smem(buf + row * stride + v * 16)), "l"(src + v * 16) : "memory");
+                    const int nv = nkv == 2 ? nbr[pp] : (8 * nbr[pp] + 15) >> 4;
+                    const uint8_t *src = src0[pp] + (int64_t)unit_ * step[pp];
+                    if ((lane & 7) < nv)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t)(pp * 4 * stride)), "l"(src) : "memory");
+                    if (nb_max > 8 && (lane & 7) + 8 < nv)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t)(pp * 4 * stride + 128)), "l"(src + 128) : "memory");
                 }
             }
             asm volatile("cp.async.commit_group;\n" ::: "memory");
@@ -299,34 +368,24 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
             fetch(ss + 1);
             asm volatile("cp.async.wait_group 1;\n" ::: "memory");
             __syncwarp();
-            bool ok = true;
-            uint4 q[PF_VECS];
-#pragma unroll
-            for (int i = 0; i < PF_VECS; ++i) q[i] = make_uint4(0u, 0u, 0u, 0u);
-            if (me.mode == 1 && kb0 < nkb) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(mybuf + (ss & 1) * PF_RAW_BUF + lane * stride);
-#pragma unroll
-                for (int i = 0; i < PF_VECS; ++i)
-                    if (i < me.nb) q[i] = src[i];
-            }
+            if (kb0 >= nkb) continue;                    // warp-uniform: nothing left for this group
             const int unit = 2 * ss + g, slot = unit & (PF_NU - 1), use = unit / PF_NU;
-            if (use > 0 && kb0 < nkb) ok = pf_wait(pf_smem(&a_empty[slot]), (use - 1) & 1, abort_flag, 22);
-            if (!__all_sync(0xffffffffu, ok)) break;
-            if (kb0 < nkb) {                             // warp-uniform
+            {
                 const uint32_t taddr = lane_base + (uint32_t)(slot * 64);
-                uint32_t out[32];
+                uint32_t out0[32], out1[32];
+                unpack_pair(p, me, reinterpret_cast<const uint4 *>(mybuf + (ss & 1) * PF_RAW_BUF + lane * stride), kb0, nkb, out0, out1);
+                // only now is the slot needed: the MMAs that read its previous contents must have completed
+                bool ok = true;
+                if (use > 0) ok = pf_wait(pf_smem(&a_empty[slot]), (use - 1) & 1, abort_flag, 22);
+                if (!__all_sync(0xffffffffu, ok)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                unpack_half<0>(p, me, q, kb0, nkb, out);
-                __syncwarp();
-                tmem_store32(taddr, out);
-                unpack_half<1>(p, me, q, kb0 + 1, nkb, out);
-                __syncwarp();
-                tmem_store32(taddr + 32, out);
+                tmem_store32(taddr, out0);
+                tmem_store32(taddr + 32, out1);
                 asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             }
             __syncwarp();
-            if (lane == 0 && kb0 < nkb) pf_arrive(pf_smem(&a_full[slot]));
+            if (lane == 0) pf_arrive(pf_smem(&a_full[slot]));
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     } else if (warp == 8) {
@@ -466,7 +525,10 @@ __global__ void __launch_bounds__(256) prefill_narrow_kernel(const void *__restr
 #pragma unroll
             for (int k = 0; k < 8; ++k) h[k] = __float2half_rn(0.f);
         }
-        *reinterpret_cast<uint4 *>(X16 + x16_index(n, g * 8, nkb)) = *reinterpret_cast<const uint4 *>(h);
+        {
+            const __half t[8] = {h[0], h[2], h[1], h[3], h[4], h[6], h[5], h[7]};       // see pair_order
+            *reinterpret_cast<uint4 *>(X16 + x16_index(n, g * 8, nkb)) = *reinterpret_cast<const uint4 *>(t);
+        }
         if (X16T) {                                      // column-major copy for the escape pass: tokens contiguous
 #pragma unroll
             for (int k = 0; k < 8; ++k) X16T[(int64_t)(g * 8 + k) * Mpad + n] = h[k];
@@ -483,37 +545,59 @@ __global__ void __launch_bounds__(256) prefill_narrow_kernel(const void *__restr
 }
 
 // Y[m, q] += sum over the escapes of row q of x16[m, col] * (exact - band), in stored order.  Block = 32 consecutive
-// rows x 256 tokens, thread = token: the activations of an escape's column are read along the tokens (contiguous in the
-// column-major copy), a thread keeps the 32 rows' sums in registers and then updates 128 contiguous bytes of Y.
+// rows x 512 tokens, thread = two neighbouring tokens: the activations of an escape's column are read along the tokens
+// (contiguous in the column-major copy), a thread keeps the 32 rows' sums in registers and then updates 128 contiguous
+// bytes of Y per token.  Four escapes are fetched at a time so that their loads overlap.
+constexpr int PF_ESC_TOK = 512;
 __global__ void __launch_bounds__(256) prefill_escapes_kernel(const int *__restrict__ esc_ptr, const int *__restrict__ esc_col,
                                                               const float *__restrict__ esc_delta, const __half *__restrict__ X16T,
                                                               float *__restrict__ Y, int Q, int M, int Mpad) {
-    const int q0 = blockIdx.x * 32, n = blockIdx.y * 256 + threadIdx.x;
+    const int q0 = blockIdx.x * 32, n = blockIdx.y * PF_ESC_TOK + 2 * threadIdx.x;
     const int qe = min(Q, q0 + 32);
-    if (__ldg(esc_ptr + q0) == __ldg(esc_ptr + qe)) return;
-    float acc[32];
+    if (__ldg(esc_ptr + q0) == __ldg(esc_ptr + qe) || n >= Mpad) return;
+    const __half2 *xt = reinterpret_cast<const __half2 *>(X16T + n);          // Mpad and n are even
+    const int64_t ld = Mpad >> 1;
+    float a0[32], a1[32];
 #pragma unroll
     for (int r = 0; r < 32; ++r) {
-        acc[r] = 0.f;
+        a0[r] = 0.f;
+        a1[r] = 0.f;
         if (q0 + r < Q) {
             const int e0 = __ldg(esc_ptr + q0 + r), e1 = __ldg(esc_ptr + q0 + r + 1);
-            for (int e = e0; e < e1; ++e)
-                acc[r] = __fmaf_rn(__half2float(X16T[(int64_t)__ldg(esc_col + e) * Mpad + n]), __ldg(esc_delta + e), acc[r]);
+            for (int e = e0; e < e1; e += 4) {
+                float d[4];
+                __half2 x[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int ee = min(e + k, e1 - 1);
+                    d[k] = e + k < e1 ? __ldg(esc_delta + ee) : 0.f;
+                    x[k] = xt[(int64_t)__ldg(esc_col + ee) * ld];
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __half22float2(x[k]);
+                    a0[r] = __fmaf_rn(f.x, d[k], a0[r]);
+                    a1[r] = __fmaf_rn(f.y, d[k], a1[r]);
+                }
+            }
         }
     }
-    if (n >= M) return;
-    float *y = Y + (int64_t)n * Q + q0;
-    if ((Q & 3) == 0 && q0 + 32 <= Q) {
 #pragma unroll
-        for (int r = 0; r < 32; r += 4) {
-            float4 v = *reinterpret_cast<float4 *>(y + r);
-            v.x += acc[r]; v.y += acc[r + 1]; v.z += acc[r + 2]; v.w += acc[r + 3];
-            *reinterpret_cast<float4 *>(y + r) = v;
+    for (int t = 0; t < 2; ++t) {
+        if (n + t >= M) break;
+        float *y = Y + (int64_t)(n + t) * Q + q0;
+        if ((Q & 3) == 0 && q0 + 32 <= Q) {
+#pragma unroll
+            for (int r = 0; r < 32; r += 4) {
+                float4 v = *reinterpret_cast<float4 *>(y + r);
+                v.x += t ? a1[r] : a0[r]; v.y += t ? a1[r + 1] : a0[r + 1]; v.z += t ? a1[r + 2] : a0[r + 2]; v.w += t ? a1[r + 3] : a0[r + 3];
+                *reinterpret_cast<float4 *>(y + r) = v;
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < 32; ++r)
+                if (q0 + r < Q) y[r] += t ? a1[r] : a0[r];
         }
-    } else {
-#pragma unroll
-        for (int r = 0; r < 32; ++r)
-            if (q0 + r < Q) y[r] += acc[r];
     }
 }
 
@@ -611,7 +695,7 @@ QV_API int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int
     prefill_wide_rows_kernel<<<dim3(64, (unsigned)((M + 7) / 8)), 256, 0, st>>>(prm, wide + 1, wide);
     if (int rc = cuda_status("qvb8_prefill wide rows")) return rc;
     if (w->n_esc > 0) {
-        prefill_escapes_kernel<<<dim3((unsigned)((w->Q + 31) / 32), (unsigned)(Mpad / 256)), 256, 0, st>>>(
+        prefill_escapes_kernel<<<dim3((unsigned)((w->Q + 31) / 32), (unsigned)((Mpad + PF_ESC_TOK - 1) / PF_ESC_TOK)), 256, 0, st>>>(
             reinterpret_cast<const int *>(pb + L.esc_ptr), reinterpret_cast<const int *>(pb + L.esc_col),
             reinterpret_cast<const float *>(pb + L.esc_delta), X16T, Y, (int)w->Q, (int)M, (int)Mpad);
         if (int rc = cuda_status("qvb8_prefill escapes")) return rc;

@@ -101,7 +101,26 @@ __global__ void __launch_bounds__(32 * R_WPB) qvb8r_kernel(const RCore c, int b0
 #pragma unroll
         for (int k = 0; k < MP; ++k) acc[k] = 0.f;
         const int64_t orow_out = row_base < 0 ? (int64_t)orow : (int64_t)(r0 + r) - row_base;
+        // the activations of a step are fetched one step ahead: their latency hides behind the decoder's dependency chain
+        constexpr bool AHEAD = MODE == 2 && MP <= 8;       // beyond 8 tokens the extra registers cost more than they hide
+        float xa[MP], xb[MP];
+        if constexpr (AHEAD) {
+#pragma unroll
+            for (int k = 0; k < MP; ++k) {
+                xa[k] = k < M ? (float)X[(int64_t)k * c.P + lane] : 0.f;
+                xb[k] = k < M ? (float)X[(int64_t)k * c.P + lane + 32] : 0.f;
+            }
+        }
         for (int s0 = 0; s0 < S; s0 += 2) {
+            float na[MP], nb_[MP];
+            if constexpr (AHEAD) {
+                const int cn = min(s0 + 2, S - 2) * 32 + lane;
+#pragma unroll
+                for (int k = 0; k < MP; ++k) {
+                    na[k] = k < M ? (float)X[(int64_t)k * c.P + cn] : 0.f;
+                    nb_[k] = k < M ? (float)X[(int64_t)k * c.P + cn + 32] : 0.f;
+                }
+            }
             uint32_t s1, s2;
             rstream_pair(z, st, lane, s1, s2);
             const int i1 = (int)s1 + dr, i2 = (int)s2 + dr;
@@ -118,7 +137,12 @@ __global__ void __launch_bounds__(32 * R_WPB) qvb8r_kernel(const RCore c, int b0
                     if (WROUND) { w1 = __half2float(__float2half_rn(w1)); w2 = __half2float(__float2half_rn(w2)); }
 #pragma unroll
                     for (int k = 0; k < MP; ++k) {
-                        if (k < M) {
+                        if constexpr (AHEAD) {
+                            acc[k] = __fmaf_rn(xa[k], w1, acc[k]);
+                            acc[k] = __fmaf_rn(xb[k], w2, acc[k]);
+                            xa[k] = na[k];
+                            xb[k] = nb_[k];
+                        } else if (k < M) {
                             acc[k] = __fmaf_rn((float)X[(int64_t)k * c.P + c1], w1, acc[k]);
                             acc[k] = __fmaf_rn((float)X[(int64_t)k * c.P + c2], w2, acc[k]);
                         }
