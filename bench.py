@@ -208,6 +208,80 @@ def run_moe(args):
                      "peak_kind": peak_kind, "kernel": "moe_rows_kernel"}}), flush=True)
 
 
+def run_prefill(args):
+    """Prefill of one 27B-class layer's MLP projections (gate+up fused 34816 x 5120, down 5120 x 17408) for M tokens
+    (default 2048) through the tcgen05 kernel: QVB8 packs at tau = 2e-3, outliers escaped.  Metric: dense-equivalent
+    TFLOP/s (2 M Q P per projection) over the whole call, i.e. the fp16 narrowing of X, the main kernel and the
+    escape pass; beside it the same projections through dense restore + library GEMM."""
+    from qvb8_b200 import fuse, lib, synth
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    M = args.rows if args.rows > 1 else 2048
+    d, f = 5120, 17408
+    gate = synth.encode_qvb8(synth.synth_weight(f, d, 6001, device=dev), tau=2e-3, policy=args.policy)
+    up = synth.encode_qvb8(synth.synth_weight(f, d, 6002, device=dev), tau=2e-3, policy=args.policy)
+    down = synth.encode_qvb8(synth.synth_weight(d, f, 6003, device=dev), tau=2e-3, policy=args.policy)
+    packs = [fuse.concat_packs([gate, up])[0], down]
+    del gate, up
+    work = []
+    for pk in packs:
+        st, keep = lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx, pk.esc_vals)
+        work.append((pk, st, keep, lib.build_plan(st, keep), synth.synth_activation(M, pk.P, seed=pk.Q, device=dev)))
+    flops = sum(2.0 * M * pk.Q * pk.P for pk in packs)
+
+    def fused():
+        return [lib.prefill(st, keep, X, plan=plan) for _, st, keep, plan, X in work]
+
+    def dense():
+        return [torch.mm(X.to(torch.float16), lib.decode(st, keep, torch.float16).t(), out_dtype=torch.float32)
+                for _, st, keep, _, X in work]
+
+    def timed(fn, steps, clocks_on):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        with ClockSampler(0) as clocks:
+            for a, b in ev:
+                a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in ev) / steps, clocks.summary() if clocks_on else None
+
+    ms, clk = timed(fused, args.steps, True)
+    ms_dense, _ = timed(dense, max(3, args.steps // 2), False)
+    # end to end: X from pinned host memory, one value of every result read back
+    hx = [X.cpu().pin_memory() for *_, X in work]
+    def e2e_step():
+        outs = []
+        for (pk, st, keep, plan, _), h in zip(work, hx):
+            outs.append(lib.prefill(st, keep, h.to(dev, non_blocking=True), plan=plan))
+        return float(sum(o[0, 0] for o in outs))
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    ms_e2e = (time.perf_counter() - t0) / args.steps * 1e3
+    peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json"))) \
+        if os.path.exists(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) else {}
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    tf = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "prefill_dense_equivalent_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 x f16 -> f32", "data": "synthetic",
+        "config": {"workload": f"27B-class MLP projections (gate+up 34816x5120, down 5120x17408), prefill M={M}, QVB8 tau=2e-3, "
+                               f"policy {args.policy}", "l2": "weights + activations (> 400 MB) exceed L2",
+                   "dense_restore_plus_library_gemm_ms": ms_dense},
+        "clocks": clk, "gpu_launches": sum(4 + (1 if pk.esc_idx.numel() else 0) for pk in packs) * args.steps,
+        "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": int(sum(h.numel() * h.element_size() for h in hx)), "d2h_bytes_per_step": 8},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                     "peak_kind": "measured (burst)" if peaks else "fallback", "kernel": "prefill_kernel"}}), flush=True)
+
+
 def finish(world, dist):
     """Leave a multi-rank run without tearing NCCL down: communicators referenced by captured graphs make
     destroy_process_group wait for ever, so the ranks meet at a barrier, flush and exit."""
@@ -230,8 +304,9 @@ def main():
     ap.add_argument("--rows", type=int, default=1, help="activation rows M (1 = decode)")
     ap.add_argument("--policy", default="escape_outliers")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--workload", default="stack", choices=["stack", "moe"],
-                    help="stack: the dense linear stack (headline); moe: one 35B-A3B-class expert layer")
+    ap.add_argument("--workload", default="stack", choices=["stack", "moe", "prefill"],
+                    help="stack: the dense linear stack (headline); moe: one 35B-A3B-class expert layer; "
+                         "prefill: 27B-class MLP projections for 2048 tokens on the tcgen05 kernel")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection (no same-input fusion)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -240,6 +315,9 @@ def main():
     cfg = S.CONFIGS[args.config]
     if args.workload == "moe" and args.impl != "reference":
         run_moe(args)
+        return
+    if args.workload == "prefill" and args.impl != "reference":
+        run_prefill(args)
         return
     if args.impl == "reference":
         run_reference_arm(args, cfg)

@@ -62,11 +62,12 @@ __device__ __forceinline__ bool pf_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity), "r"(20000u) : "memory");
     return ok != 0;
 }
-__device__ __noinline__ bool pf_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+__device__ __noinline__ bool pf_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code, unsigned backoff_ns) {
     uint64_t t0;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
     for (int i = 0; i < PF_SPIN; ++i) {
         if (pf_try_wait(bar, parity)) return true;
+        if (backoff_ns) __nanosleep(backoff_ns);         // a polling warp takes issue slots from the unpack warps of its scheduler
         if ((i & 7) == 7) {
             if (*abort_flag) return false;
             uint64_t t;
@@ -78,9 +79,9 @@ __device__ __noinline__ bool pf_wait_slow(uint32_t bar, uint32_t parity, volatil
     atomicCAS(&g_prefill_error, 0, code);
     return false;
 }
-__device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+__device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code, unsigned backoff_ns = 0) {
     if (pf_try_wait(bar, parity)) return true;
-    return pf_wait_slow(bar, parity, abort_flag, code);
+    return pf_wait_slow(bar, parity, abort_flag, code, backoff_ns);
 }
 __device__ __forceinline__ void pf_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
@@ -150,42 +151,55 @@ __device__ __forceinline__ uint32_t window(const uint4 (&q)[NV]) {
 //   others:    two windows, two masks, one subtraction of 1024
 // The shifts and logic operations run on the half-rate integer pipe, which is what bounds this kernel: two instead of
 // four of them per pair for the common widths.
+// The constants of a width, read once per thread from a shared-memory table through volatile loads: as literals the
+// compiler re-creates them with a move in front of every use, which doubles the work of the integer pipe.
+struct PairConst {
+    uint32_t mask;      // (m << E) | (m << 16) for 6..8 bits; m for the others
+    uint32_t mask_hi;   // m << 16
+    uint32_t k64;       // 0x64006400
+    uint32_t scale;     // half2 (2^-E, 1)
+    uint32_t bias;      // half2 (-1024 * 2^-E, -1024)
+};
+__device__ __forceinline__ PairConst pair_const_of(int nb) {
+    const uint32_t m = (1u << nb) - 1u;
+    const int e = (nb >= 6 && nb <= 8) ? 16 - 2 * nb : 0;
+    PairConst c;
+    c.mask = (nb >= 6 && nb <= 8) ? ((m << e) | (m << 16)) : m;
+    c.mask_hi = m << 16;
+    c.k64 = 0x64006400u;
+    const __half2 sc = __floats2half2_rn(1.0f / (float)(1 << e), 1.0f), bi = __floats2half2_rn(-1024.0f / (float)(1 << e), -1024.0f);
+    c.scale = *reinterpret_cast<const uint32_t *>(&sc);
+    c.bias = *reinterpret_cast<const uint32_t *>(&bi);
+    return c;
+}
+
 template <int NB, int H, int I = 0>
-__device__ __forceinline__ void unpack64(const uint4 (&q)[NB], uint32_t (&out)[32]) {
+__device__ __forceinline__ void unpack64(const uint4 (&q)[NB], const PairConst &pc, uint32_t (&out)[32]) {
     if constexpr (I < 32) {
-        constexpr uint32_t m = (1u << NB) - 1u;
         constexpr int k = 4 * (I >> 1) + (I & 1);
         constexpr int G0 = (H * 64 + k) * NB, G1 = G0 + 2 * NB;
+        uint32_t u;
         if constexpr (NB >= 6 && NB <= 8) {
             constexpr int E = 16 - 2 * NB;
-            const uint32_t t = window<G0, E, 16 - E + NB, NB>(q);
-            const uint32_t u = (t & ((m << E) | (m << 16))) | 0x64006400u;
-            __half2 v;
-            if constexpr (E == 0) {
-                v = __hsub2(*reinterpret_cast<const __half2 *>(&u), __floats2half2_rn(1024.f, 1024.f));
-            } else {
-                constexpr float sc = 1.0f / (float)(1 << E);
-                v = __hfma2(*reinterpret_cast<const __half2 *>(&u), __floats2half2_rn(sc, 1.0f), __floats2half2_rn(-1024.f * sc, -1024.f));
-            }
-            out[I] = *reinterpret_cast<const uint32_t *>(&v);
+            u = (window<G0, E, 16 - E + NB, NB>(q) & pc.mask) | pc.k64;
         } else {
-            const uint32_t lo = window<G0, 0, NB, NB>(q), hi = window<G1, 16, NB, NB>(q);
-            const uint32_t u = (hi & (m << 16)) | ((lo & m) | 0x64006400u);
-            const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&u), __floats2half2_rn(1024.f, 1024.f));
-            out[I] = *reinterpret_cast<const uint32_t *>(&v);
+            u = (window<G1, 16, NB, NB>(q) & pc.mask_hi) | ((window<G0, 0, NB, NB>(q) & pc.mask) | pc.k64);
         }
-        unpack64<NB, H, I + 1>(q, out);
+        const __half2 v = __hfma2(*reinterpret_cast<const __half2 *>(&u), *reinterpret_cast<const __half2 *>(&pc.scale),
+                                  *reinterpret_cast<const __half2 *>(&pc.bias));
+        out[I] = *reinterpret_cast<const uint32_t *>(&v);
+        unpack64<NB, H, I + 1>(q, pc, out);
     }
 }
 
 // A row of width NB: its vectors from the warp's buffer, both K blocks of the pair to registers.
 template <int NB>
-__device__ __forceinline__ void unpack_row(const uint4 *__restrict__ src, uint32_t (&out0)[32], uint32_t (&out1)[32]) {
+__device__ __forceinline__ void unpack_row(const uint4 *__restrict__ src, const PairConst &pc, uint32_t (&out0)[32], uint32_t (&out1)[32]) {
     uint4 q[NB];
 #pragma unroll
     for (int i = 0; i < NB; ++i) q[i] = src[i];
-    unpack64<NB, 0>(q, out0);
-    unpack64<NB, 1>(q, out1);
+    unpack64<NB, 0>(q, pc, out0);
+    unpack64<NB, 1>(q, pc, out1);
 }
 
 // 32 registers -> 32 columns of tensor memory, lane = this thread's lane of the warp's quarter.
@@ -227,20 +241,20 @@ __device__ __noinline__ void unpack_generic(const uint8_t *__restrict__ ids, int
 
 // Both K blocks of this thread's pair -> 2 x 32 registers.  No tensor-memory access in here: rows of different widths
 // or modes diverge inside, and tcgen05.st is a warp-wide instruction that every lane must reach together.
-__device__ __forceinline__ void unpack_pair(const PrefillParams &p, const RowInfo &me, const uint4 *__restrict__ src, int kb0, int nkb,
-                                            uint32_t (&out0)[32], uint32_t (&out1)[32]) {
+__device__ __forceinline__ void unpack_pair(const PrefillParams &p, const RowInfo &me, const uint4 *__restrict__ src, const PairConst &pc,
+                                            int kb0, int nkb, uint32_t (&out0)[32], uint32_t (&out1)[32]) {
     if (me.mode == 1) {
         switch (me.nb) {
-        case 1: unpack_row<1>(src, out0, out1); break;
-        case 2: unpack_row<2>(src, out0, out1); break;
-        case 3: unpack_row<3>(src, out0, out1); break;
-        case 4: unpack_row<4>(src, out0, out1); break;
-        case 5: unpack_row<5>(src, out0, out1); break;
-        case 6: unpack_row<6>(src, out0, out1); break;
-        case 7: unpack_row<7>(src, out0, out1); break;
-        case 8: unpack_row<8>(src, out0, out1); break;
-        case 9: unpack_row<9>(src, out0, out1); break;
-        default: unpack_row<10>(src, out0, out1); break;
+        case 1: unpack_row<1>(src, pc, out0, out1); break;
+        case 2: unpack_row<2>(src, pc, out0, out1); break;
+        case 3: unpack_row<3>(src, pc, out0, out1); break;
+        case 4: unpack_row<4>(src, pc, out0, out1); break;
+        case 5: unpack_row<5>(src, pc, out0, out1); break;
+        case 6: unpack_row<6>(src, pc, out0, out1); break;
+        case 7: unpack_row<7>(src, pc, out0, out1); break;
+        case 8: unpack_row<8>(src, pc, out0, out1); break;
+        case 9: unpack_row<9>(src, pc, out0, out1); break;
+        default: unpack_row<10>(src, pc, out0, out1); break;
         }
     } else {
 #pragma unroll
@@ -271,6 +285,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
     __shared__ const uint8_t *row_src[128];                   // first byte of each row of the tile (mode 1 rows)
     __shared__ int row_nb1[128];                              // its width, 0 unless mode 1
     __shared__ float sx[PF_TOK];                              // sum of the narrowed activations of each token of the tile
+    __shared__ PairConst ctab[11];                            // per width, see PairConst
     volatile int *abort_flag = &abort_word;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -291,6 +306,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         abort_word = 0;
         nb_max = 0;
+        for (int nb = 1; nb <= 10; ++nb) ctab[nb] = pair_const_of(nb);
     }
     if (warp == 0) {                                    // one warp allocates (and later frees) the tensor-memory columns
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(pf_smem(&tmem_base)), "r"((uint32_t)PF_TMEM_COLS) : "memory");
@@ -329,6 +345,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
         const int g = warp >> 2;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 256u;
         uint8_t *const mybuf = smem + PF_NBS * PF_B_BYTES + warp * 2 * PF_RAW_BUF;
+        PairConst pc;
+        {
+            const volatile PairConst *vc = &ctab[me.mode == 1 ? me.nb : 1];
+            pc.mask = vc->mask; pc.mask_hi = vc->mask_hi; pc.k64 = vc->k64; pc.scale = vc->scale; pc.bias = vc->bias;
+        }
         // the warp's rows of a pair -> one of its two buffers: eight lanes per row, 16 bytes each (a second round for
         // rows wider than 8 bits); one commit group per pair.  Per-lane constants: this lane's vector of rows 4 pp + lane / 8.
         const uint8_t *src0[8];
@@ -373,7 +394,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
             {
                 const uint32_t taddr = lane_base + (uint32_t)(slot * 64);
                 uint32_t out0[32], out1[32];
-                unpack_pair(p, me, reinterpret_cast<const uint4 *>(mybuf + (ss & 1) * PF_RAW_BUF + lane * stride), kb0, nkb, out0, out1);
+                unpack_pair(p, me, reinterpret_cast<const uint4 *>(mybuf + (ss & 1) * PF_RAW_BUF + lane * stride), pc, kb0, nkb, out0, out1);
                 // only now is the slot needed: the MMAs that read its previous contents must have completed
                 bool ok = true;
                 if (use > 0) ok = pf_wait(pf_smem(&a_empty[slot]), (use - 1) & 1, abort_flag, 22);
@@ -395,7 +416,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
             bool alive = true;
             for (int kb = 0; kb < nkb && alive; ++kb) {
                 const int s = kb % PF_NBS, u = kb / PF_NBS;
-                if (u > 0) alive = pf_wait(pf_smem(&b_empty[s]), (u - 1) & 1, abort_flag, 24);
+                if (u > 0) alive = pf_wait(pf_smem(&b_empty[s]), (u - 1) & 1, abort_flag, 24, 200);
                 if (!alive) break;
                 const uint32_t bar = pf_smem(&b_full[s]);
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((uint32_t)PF_B_BYTES) : "memory");
@@ -413,8 +434,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
             for (int kb = 0; kb < nkb && alive; ++kb) {
                 const int s = kb % PF_NBS, u = kb / PF_NBS;
                 const int unit = kb >> 1, slot = unit & (PF_NU - 1), use = unit / PF_NU;
-                if ((kb & 1) == 0) alive = pf_wait(pf_smem(&a_full[slot]), use & 1, abort_flag, 25);
-                if (alive) alive = pf_wait(pf_smem(&b_full[s]), u & 1, abort_flag, 26);
+                if ((kb & 1) == 0) alive = pf_wait(pf_smem(&a_full[slot]), use & 1, abort_flag, 25, 32);
+                if (alive) alive = pf_wait(pf_smem(&b_full[s]), u & 1, abort_flag, 26, 32);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t b32 = pf_smem(smem + s * PF_B_BYTES);
@@ -443,7 +464,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
     // the upper 128 tokens.
     if (warp < 8) {
         bool alive = !*abort_flag;
-        if (alive) alive = pf_wait(pf_smem(&all_done), 0, abort_flag, 27);
+        if (alive) alive = pf_wait(pf_smem(&all_done), 0, abort_flag, 27, 100);
         alive = __all_sync(0xffffffffu, alive);          // tcgen05.ld is warp-wide: all lanes or none
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (alive) {
@@ -545,59 +566,64 @@ __global__ void __launch_bounds__(256) prefill_narrow_kernel(const void *__restr
 }
 
 // Y[m, q] += sum over the escapes of row q of x16[m, col] * (exact - band), in stored order.  Block = 32 consecutive
-// rows x 512 tokens, thread = two neighbouring tokens: the activations of an escape's column are read along the tokens
-// (contiguous in the column-major copy), a thread keeps the 32 rows' sums in registers and then updates 128 contiguous
-// bytes of Y per token.  Four escapes are fetched at a time so that their loads overlap.
-constexpr int PF_ESC_TOK = 512;
+// rows x 256 tokens.  Phase 1: warp w owns rows w, w + 8, w + 16, w + 24; a lane owns eight neighbouring tokens, so an
+// escape costs the warp ONE 512-byte read of its column in the column-major copy and eight FMAs per lane.  Phase 2: the
+// sums cross shared memory so that a thread owns one token and updates 128 contiguous bytes of Y.
 __global__ void __launch_bounds__(256) prefill_escapes_kernel(const int *__restrict__ esc_ptr, const int *__restrict__ esc_col,
                                                               const float *__restrict__ esc_delta, const __half *__restrict__ X16T,
                                                               float *__restrict__ Y, int Q, int M, int Mpad) {
-    const int q0 = blockIdx.x * 32, n = blockIdx.y * PF_ESC_TOK + 2 * threadIdx.x;
+    __shared__ float E[256][33];
+    const int q0 = blockIdx.x * 32, n0 = blockIdx.y * 256;
     const int qe = min(Q, q0 + 32);
-    if (__ldg(esc_ptr + q0) == __ldg(esc_ptr + qe) || n >= Mpad) return;
-    const __half2 *xt = reinterpret_cast<const __half2 *>(X16T + n);          // Mpad and n are even
-    const int64_t ld = Mpad >> 1;
-    float a0[32], a1[32];
+    if (__ldg(esc_ptr + q0) == __ldg(esc_ptr + qe)) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint4 *xt = reinterpret_cast<const uint4 *>(X16T + n0 + 8 * lane);       // Mpad is a multiple of 256
+    const int64_t ld = Mpad >> 3;
 #pragma unroll
-    for (int r = 0; r < 32; ++r) {
-        a0[r] = 0.f;
-        a1[r] = 0.f;
-        if (q0 + r < Q) {
-            const int e0 = __ldg(esc_ptr + q0 + r), e1 = __ldg(esc_ptr + q0 + r + 1);
-            for (int e = e0; e < e1; e += 4) {
-                float d[4];
-                __half2 x[4];
+    for (int j = 0; j < 4; ++j) {
+        const int q = q0 + warp + 8 * j;
+        float acc[8];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int ee = min(e + k, e1 - 1);
-                    d[k] = e + k < e1 ? __ldg(esc_delta + ee) : 0.f;
-                    x[k] = xt[(int64_t)__ldg(esc_col + ee) * ld];
+        for (int t = 0; t < 8; ++t) acc[t] = 0.f;
+        if (q < Q) {
+            const int e0 = __ldg(esc_ptr + q), e1 = __ldg(esc_ptr + q + 1);
+            for (int e = e0; e < e1; e += 2) {           // two at a time: the loads overlap
+                const int ee = min(e + 1, e1 - 1);
+                const float d0 = __ldg(esc_delta + e), d1 = e + 1 < e1 ? __ldg(esc_delta + ee) : 0.f;
+                const uint4 v0 = __ldg(xt + (int64_t)__ldg(esc_col + e) * ld), v1 = __ldg(xt + (int64_t)__ldg(esc_col + ee) * ld);
+                const __half2 *h0 = reinterpret_cast<const __half2 *>(&v0), *h1 = reinterpret_cast<const __half2 *>(&v1);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float2 f = __half22float2(h0[t]);
+                    acc[2 * t] = __fmaf_rn(f.x, d0, acc[2 * t]);
+                    acc[2 * t + 1] = __fmaf_rn(f.y, d0, acc[2 * t + 1]);
                 }
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float2 f = __half22float2(x[k]);
-                    a0[r] = __fmaf_rn(f.x, d[k], a0[r]);
-                    a1[r] = __fmaf_rn(f.y, d[k], a1[r]);
+                for (int t = 0; t < 4; ++t) {
+                    const float2 f = __half22float2(h1[t]);
+                    acc[2 * t] = __fmaf_rn(f.x, d1, acc[2 * t]);
+                    acc[2 * t + 1] = __fmaf_rn(f.y, d1, acc[2 * t + 1]);
                 }
             }
         }
+#pragma unroll
+        for (int t = 0; t < 8; ++t) E[8 * lane + t][warp + 8 * j] = acc[t];
     }
+    __syncthreads();
+    const int n = n0 + threadIdx.x;
+    if (n >= M) return;
+    float *y = Y + (int64_t)n * Q + q0;
+    const float *er = E[threadIdx.x];
+    if ((Q & 3) == 0 && q0 + 32 <= Q) {
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        if (n + t >= M) break;
-        float *y = Y + (int64_t)(n + t) * Q + q0;
-        if ((Q & 3) == 0 && q0 + 32 <= Q) {
-#pragma unroll
-            for (int r = 0; r < 32; r += 4) {
-                float4 v = *reinterpret_cast<float4 *>(y + r);
-                v.x += t ? a1[r] : a0[r]; v.y += t ? a1[r + 1] : a0[r + 1]; v.z += t ? a1[r + 2] : a0[r + 2]; v.w += t ? a1[r + 3] : a0[r + 3];
-                *reinterpret_cast<float4 *>(y + r) = v;
-            }
-        } else {
-#pragma unroll
-            for (int r = 0; r < 32; ++r)
-                if (q0 + r < Q) y[r] += t ? a1[r] : a0[r];
+        for (int r = 0; r < 32; r += 4) {
+            float4 v = *reinterpret_cast<float4 *>(y + r);
+            v.x += er[r]; v.y += er[r + 1]; v.z += er[r + 2]; v.w += er[r + 3];
+            *reinterpret_cast<float4 *>(y + r) = v;
         }
+    } else {
+        for (int r = 0; r < 32; ++r)
+            if (q0 + r < Q) y[r] += er[r];
     }
 }
 
@@ -695,7 +721,7 @@ QV_API int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int
     prefill_wide_rows_kernel<<<dim3(64, (unsigned)((M + 7) / 8)), 256, 0, st>>>(prm, wide + 1, wide);
     if (int rc = cuda_status("qvb8_prefill wide rows")) return rc;
     if (w->n_esc > 0) {
-        prefill_escapes_kernel<<<dim3((unsigned)((w->Q + 31) / 32), (unsigned)((Mpad + PF_ESC_TOK - 1) / PF_ESC_TOK)), 256, 0, st>>>(
+        prefill_escapes_kernel<<<dim3((unsigned)((w->Q + 31) / 32), (unsigned)(Mpad / 256)), 256, 0, st>>>(
             reinterpret_cast<const int *>(pb + L.esc_ptr), reinterpret_cast<const int *>(pb + L.esc_col),
             reinterpret_cast<const float *>(pb + L.esc_delta), X16T, Y, (int)w->Q, (int)M, (int)Mpad);
         if (int rc = cuda_status("qvb8_prefill escapes")) return rc;
