@@ -135,6 +135,9 @@ int qvb8_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x_m
 int64_t qvb8_prefill_scratch_bytes(int64_t M, int64_t Q, int64_t P);
 int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int64_t M, float *Y, void *scratch,
                  int64_t scratch_bytes, void *stream);
+/* Tuning aid for sweeps (results are wrong while it is set): 1 = no unpack arithmetic, 2 = no activation copies,
+ * 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs; 0 = normal. */
+void qvb8_prefill_set_tuning(int debug);
 
 /* ---- mixture-of-experts MLP over stacked expert packs -------------------------------------------------------------
  * Stacked layout of one projection of all E experts (reference formats/qvb8/backends_experts.py:144-196): every

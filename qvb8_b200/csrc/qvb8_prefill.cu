@@ -40,18 +40,26 @@ namespace qv {
 
 constexpr int PF_TOK = 256;                // tokens per CTA = MMA N
 constexpr int PF_BK = 64;                  // columns per stage
-constexpr int PF_UNPACK = 256;             // unpack threads (warps 0..7)
+#ifndef QVB8_PF_GROUPS
+#define QVB8_PF_GROUPS 3
+#endif
+constexpr int PF_G = QVB8_PF_GROUPS;       // unpack groups of four warps (a group owns whole pairs of K blocks)
+constexpr int PF_UW = 4 * PF_G;            // unpack warps
+constexpr int PF_UNPACK = 32 * PF_UW;      // unpack threads
 constexpr int PF_THREADS = PF_UNPACK + 64; // + copy warp + MMA warp
+constexpr int PF_NBUF = PF_G <= 2 ? 2 : 1; // buffers of packed ids per unpack warp
+constexpr int PF_EG = PF_G >= 4 ? 4 : 2;   // groups of four warps that share the epilogue
+// registers: the allocation is per four warps, so 14 warps (three groups) may use 128 each, 18 warps only 96
 constexpr int PF_B_BYTES = PF_TOK * PF_BK * 2;      // 32 KB
 constexpr int PF_SPIN = 1 << 22;
 constexpr int PF_KS = 8;                   // column ranges of the partial activation sums
 constexpr int PF_EXACT_BITS = 11;          // ids up to this width are exact in fp16
-constexpr int PF_NBS = 4;                  // activation stages in shared memory
+constexpr int PF_NBS = 4;                  // activation stages in shared memory (even: they are freed in pairs)
 constexpr int PF_NU = 4;                   // weight units (pairs of K blocks, 64 columns) in tensor memory
-constexpr int PF_VECS = 10;                // 16-byte vectors of a pair of K blocks (128 ids) of the widest bulk-copied row
+constexpr int PF_VECS = 8;                 // 16-byte vectors of a pair of K blocks (128 ids) of the widest row that is copied
 constexpr int PF_RAW_BUF = 32 * 16 * (PF_VECS | 1);   // bytes of one warp's buffer for a pair at the widest row stride
 constexpr int PF_TMEM_COLS = 512;          // 256 accumulator columns + PF_NU * 64 weight columns
-constexpr int PF_SMEM = PF_NBS * PF_B_BYTES + 8 * 2 * PF_RAW_BUF + 1024;
+constexpr int PF_SMEM = PF_NBS * PF_B_BYTES + PF_UW * PF_NBUF * PF_RAW_BUF + 1024;
 
 __device__ int g_prefill_error = 0;
 
@@ -114,6 +122,7 @@ struct PrefillParams {
     const float *sumx;         // (PF_KS, Mpad) partial sums of the narrowed activations
     float *Y;                  // (M, Q)
     int Q, P, M, Mpad;
+    int debug;                 // tuning aid: 1 = no unpack arithmetic, 2 = no activation copies, 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs
 };
 
 // The output row of a slot of the plan's order, -1 for padding.
@@ -192,14 +201,15 @@ __device__ __forceinline__ void unpack64(const uint4 (&q)[NB], const PairConst &
     }
 }
 
-// A row of width NB: its vectors from the warp's buffer, both K blocks of the pair to registers.
-template <int NB>
-__device__ __forceinline__ void unpack_row(const uint4 *__restrict__ src, const PairConst &pc, uint32_t (&out0)[32], uint32_t (&out1)[32]) {
+// K block H of a row of width NB: the vectors it touches from the warp's buffer, 64 ids to registers.
+template <int NB, int H>
+__device__ __forceinline__ void unpack_row_half(const uint4 *__restrict__ src, const PairConst &pc, uint32_t (&out)[32]) {
     uint4 q[NB];
+    // vectors of half H (a window of the second half may start in the last word of the first)
+    constexpr int V0 = H == 0 ? 0 : (NB / 2 > 0 ? NB / 2 - 1 : 0), V1 = H == 0 ? (NB + 1) / 2 + (NB > 1 ? 1 : 0) : NB;
 #pragma unroll
-    for (int i = 0; i < NB; ++i) q[i] = src[i];
-    unpack64<NB, 0>(q, pc, out0);
-    unpack64<NB, 1>(q, pc, out1);
+    for (int i = V0; i < (V1 < NB ? V1 : NB); ++i) q[i] = src[i];
+    unpack64<NB, H>(q, pc, out);
 }
 
 // 32 registers -> 32 columns of tensor memory, lane = this thread's lane of the warp's quarter.
@@ -216,14 +226,14 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)
 
 // Row of the CTA's tile: output row, width, first byte, and how its ids reach the unpack thread.
 //   mode 0: nothing to contract (padding, or a row wider than fp16 holds exactly: recomputed afterwards)
-//   mode 1: 16-byte copies into the warp's buffer (widths 1..10, row start 16-byte aligned);  mode 2: id by id from global memory
+//   mode 1: 16-byte copies into the warp's buffer (widths 1..8, row start 16-byte aligned);  mode 2: id by id from global memory
 struct RowInfo { int row, nb, mode; int64_t bit0; };
 __device__ __forceinline__ RowInfo row_info(const PrefillParams &p, int slot) {
     RowInfo r;
     r.row = slot_row(p, slot);
     r.nb = r.row >= 0 ? __ldg(p.nbits + r.row) : 0;
     r.bit0 = r.row >= 0 ? __ldg(p.bit_off + r.row) : 0;
-    const bool bulk_ok = (r.bit0 & 127) == 0 && (reinterpret_cast<uintptr_t>(p.ids) & 15) == 0 && r.nb >= 1 && r.nb <= 10;
+    const bool bulk_ok = (r.bit0 & 127) == 0 && (reinterpret_cast<uintptr_t>(p.ids) & 15) == 0 && r.nb >= 1 && r.nb <= PF_VECS;
     r.mode = (r.row < 0 || r.nb > PF_EXACT_BITS || r.nb < 1) ? 0 : (bulk_ok ? 1 : 2);
     return r;
 }
@@ -239,46 +249,40 @@ __device__ __noinline__ void unpack_generic(const uint8_t *__restrict__ ids, int
     }
 }
 
-// Both K blocks of this thread's pair -> 2 x 32 registers.  No tensor-memory access in here: rows of different widths
-// or modes diverge inside, and tcgen05.st is a warp-wide instruction that every lane must reach together.
-__device__ __forceinline__ void unpack_pair(const PrefillParams &p, const RowInfo &me, const uint4 *__restrict__ src, const PairConst &pc,
-                                            int kb0, int nkb, uint32_t (&out0)[32], uint32_t (&out1)[32]) {
+// K block H of this thread's pair -> 32 registers.  No tensor-memory access in here: rows of different widths or
+// modes diverge inside, and tcgen05.st is a warp-wide instruction that every lane must reach together.
+template <int H>
+__device__ __forceinline__ void unpack_half(const PrefillParams &p, const RowInfo &me, const uint4 *__restrict__ src, const PairConst &pc,
+                                            int kb, int nkb, uint32_t (&out)[32]) {
     if (me.mode == 1) {
         switch (me.nb) {
-        case 1: unpack_row<1>(src, pc, out0, out1); break;
-        case 2: unpack_row<2>(src, pc, out0, out1); break;
-        case 3: unpack_row<3>(src, pc, out0, out1); break;
-        case 4: unpack_row<4>(src, pc, out0, out1); break;
-        case 5: unpack_row<5>(src, pc, out0, out1); break;
-        case 6: unpack_row<6>(src, pc, out0, out1); break;
-        case 7: unpack_row<7>(src, pc, out0, out1); break;
-        case 8: unpack_row<8>(src, pc, out0, out1); break;
-        case 9: unpack_row<9>(src, pc, out0, out1); break;
-        default: unpack_row<10>(src, pc, out0, out1); break;
+        case 1: unpack_row_half<1, H>(src, pc, out); break;
+        case 2: unpack_row_half<2, H>(src, pc, out); break;
+        case 3: unpack_row_half<3, H>(src, pc, out); break;
+        case 4: unpack_row_half<4, H>(src, pc, out); break;
+        case 5: unpack_row_half<5, H>(src, pc, out); break;
+        case 6: unpack_row_half<6, H>(src, pc, out); break;
+        case 7: unpack_row_half<7, H>(src, pc, out); break;
+        default: unpack_row_half<8, H>(src, pc, out); break;
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { out0[i] = 0u; out1[i] = 0u; }
-        if (me.mode == 2) {                              // through a stack buffer, so that out0 / out1 stay registers
+        for (int i = 0; i < 32; ++i) out[i] = 0u;
+        if (me.mode == 2 && kb < nkb) {                  // through a stack buffer, so that `out` stays in registers
             uint32_t tmp[32];
-            unpack_generic(p.ids, me.bit0, me.nb, kb0, tmp);
+            unpack_generic(p.ids, me.bit0, me.nb, kb, tmp);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) out0[i] = tmp[i];
-            if (kb0 + 1 < nkb) {
-                unpack_generic(p.ids, me.bit0, me.nb, kb0 + 1, tmp);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) out1[i] = tmp[i];
-            }
+            for (int i = 0; i < 32; ++i) out[i] = tmp[i];
         }
     }
 }
 
-__global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillParams p) {
+__global__ void __maxnreg__(PF_G == 2 ? 168 : PF_G == 3 ? 128 : 96) prefill_kernel(const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];         // PF_NBS activation stages, then 8 warps x 2 buffers of packed ids
     __shared__ alignas(8) uint64_t a_full[PF_NU];             // a pair of K blocks of weights is in tensor memory
     __shared__ alignas(8) uint64_t a_empty[PF_NU];            // ... and the MMAs that read it have completed
     __shared__ alignas(8) uint64_t b_full[PF_NBS];            // a stage's activations have landed
-    __shared__ alignas(8) uint64_t b_empty[PF_NBS];           // ... and the MMAs that read them have completed
+    __shared__ alignas(8) uint64_t b_empty[PF_NBS / 2];       // ... and the MMAs that read a PAIR of stages have completed
     __shared__ alignas(8) uint64_t all_done;
     __shared__ uint32_t tmem_base;
     __shared__ int abort_word, nb_max;
@@ -300,13 +304,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
         }
         for (int s = 0; s < PF_NBS; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&b_full[s])) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&b_empty[s])) : "memory");
+            if (s < PF_NBS / 2) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&b_empty[s])) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(pf_smem(&all_done)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         abort_word = 0;
         nb_max = 0;
-        for (int nb = 1; nb <= 10; ++nb) ctab[nb] = pair_const_of(nb);
+        for (int nb = 1; nb <= PF_VECS; ++nb) ctab[nb] = pair_const_of(nb);
     }
     if (warp == 0) {                                    // one warp allocates (and later frees) the tensor-memory columns
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(pf_smem(&tmem_base)), "r"((uint32_t)PF_TMEM_COLS) : "memory");
@@ -323,7 +327,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
         const int wmax = __reduce_max_sync(0xffffffffu, nb1);
         if (lane == 0) atomicMax(&nb_max, wmax);
     } else if (tid < PF_UNPACK) {
-        me = row_info(p, slot0 + tid - 128);
+        me = row_info(p, slot0 + (tid & 127));
     }
     if (tid < PF_TOK) {
         float t = 0.f;
@@ -336,89 +340,95 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = tmem_base;
     const int nkb = p.P / PF_BK;
-    const int nss = (nkb + 3) >> 2;                     // rounds of four K blocks: one pair per unpack group
+    const int nunits = (nkb + 1) >> 1;                  // pairs of K blocks
     const int stride = 16 * (nb_max | 1);               // bytes per row in a warp's buffer: an odd multiple of 16
 
-    if (warp < 8) {
+    if (warp < PF_UW) {
         // ------------------------------------------------------------------------------------------ unpack warps
-        // group g = warp >> 2 takes K blocks 4 ss + 2 g, + 1 of every super-stage; a thread owns row (warp & 3) * 32 + lane
+        // group g = warp >> 2 takes the pairs of K blocks u = g, g + PF_G, ...; a thread owns row (warp & 3) * 32 + lane
         const int g = warp >> 2;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 256u;
-        uint8_t *const mybuf = smem + PF_NBS * PF_B_BYTES + warp * 2 * PF_RAW_BUF;
+        uint8_t *const mybuf = smem + PF_NBS * PF_B_BYTES + warp * PF_NBUF * PF_RAW_BUF;
         PairConst pc;
         {
             const volatile PairConst *vc = &ctab[me.mode == 1 ? me.nb : 1];
             pc.mask = vc->mask; pc.mask_hi = vc->mask_hi; pc.k64 = vc->k64; pc.scale = vc->scale; pc.bias = vc->bias;
         }
-        // the warp's rows of a pair -> one of its two buffers: eight lanes per row, 16 bytes each (a second round for
-        // rows wider than 8 bits); one commit group per pair.  Per-lane constants: this lane's vector of rows 4 pp + lane / 8.
-        const uint8_t *src0[8];
-        int step[8], nbr[8];
+        // the warp's rows of a pair -> its buffer: eight lanes per row, 16 bytes each; one commit group per pair.  Per-lane constants: this lane's vector of rows 4 pp + lane / 8.
+        uint32_t soff[8];
+        int step[8];
 #pragma unroll
         for (int pp = 0; pp < 8; ++pp) {
             const int rr = (warp & 3) * 32 + pp * 4 + (lane >> 3);
-            nbr[pp] = row_nb1[rr];
-            step[pp] = 16 * nbr[pp];
-            src0[pp] = row_src[rr] + (lane & 7) * 16;
+            step[pp] = 16 * row_nb1[rr];
+            soff[pp] = (uint32_t)(row_src[rr] - p.ids) + (uint32_t)((lane & 7) * 16);
         }
         const uint32_t dst0 = pf_smem(mybuf) + (uint32_t)((lane >> 3) * stride + (lane & 7) * 16);
-        auto fetch = [&](int ss_) {
-            const int kb0_ = 4 * ss_ + 2 * g;
-            if (ss_ < nss && kb0_ < nkb) {
-                const int nkv = min(2, nkb - kb0_);
-                const int unit_ = 2 * ss_ + g;
-                const uint32_t dst = dst0 + (uint32_t)((ss_ & 1) * PF_RAW_BUF);
+        auto fetch = [&](int u_, int b_) {
+            if (u_ < nunits && !(p.debug & 4)) {
+                const int nkv = min(2, nkb - 2 * u_);
+                const uint32_t dst = dst0 + (uint32_t)(b_ * PF_RAW_BUF);
 #pragma unroll
                 for (int pp = 0; pp < 8; ++pp) {
                     // a last, single K block is 8 * nb bytes: rounded up to 16 (a row is followed by the next row or by
                     // the buffer's 8 bytes of padding)
-                    const int nv = nkv == 2 ? nbr[pp] : (8 * nbr[pp] + 15) >> 4;
-                    const uint8_t *src = src0[pp] + (int64_t)unit_ * step[pp];
+                    const int nbr = step[pp] >> 4;
+                    const int nv = nkv == 2 ? nbr : (8 * nbr + 15) >> 4;
+                    const uint8_t *src = p.ids + soff[pp] + (int64_t)u_ * step[pp];
                     if ((lane & 7) < nv)
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t)(pp * 4 * stride)), "l"(src) : "memory");
-                    if (nb_max > 8 && (lane & 7) + 8 < nv)
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t)(pp * 4 * stride + 128)), "l"(src + 128) : "memory");
                 }
             }
             asm volatile("cp.async.commit_group;\n" ::: "memory");
         };
-        fetch(0);
+        fetch(g, 0);
         // every wait result is made warp-uniform: the tensor-memory stores below need the whole warp
-        for (int ss = 0; ss < nss; ++ss) {
-            const int kb0 = 4 * ss + 2 * g;
-            fetch(ss + 1);
-            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-            __syncwarp();
-            if (kb0 >= nkb) continue;                    // warp-uniform: nothing left for this group
-            const int unit = 2 * ss + g, slot = unit & (PF_NU - 1), use = unit / PF_NU;
-            {
-                const uint32_t taddr = lane_base + (uint32_t)(slot * 64);
-                uint32_t out0[32], out1[32];
-                unpack_pair(p, me, reinterpret_cast<const uint4 *>(mybuf + (ss & 1) * PF_RAW_BUF + lane * stride), pc, kb0, nkb, out0, out1);
-                // only now is the slot needed: the MMAs that read its previous contents must have completed
-                bool ok = true;
-                if (use > 0) ok = pf_wait(pf_smem(&a_empty[slot]), (use - 1) & 1, abort_flag, 22);
-                if (!__all_sync(0xffffffffu, ok)) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                tmem_store32(taddr, out0);
-                tmem_store32(taddr + 32, out1);
-                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        int it = 0;
+        for (int u = g; u < nunits; u += PF_G, ++it) {
+            const int kb0 = 2 * u;
+            const int b = PF_NBUF == 2 ? (it & 1) : 0;
+            if (PF_NBUF == 2) {                          // the next pair travels while this one is unpacked
+                fetch(u + PF_G, b ^ 1);
+                asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;\n" ::: "memory");
             }
+            __syncwarp();
+            const int slot = u & (PF_NU - 1), use = u / PF_NU;
+            const uint32_t taddr = lane_base + (uint32_t)(slot * 64);
+            const uint4 *src = reinterpret_cast<const uint4 *>(mybuf + b * PF_RAW_BUF + lane * stride);
+            uint32_t out[32];
+            if (p.debug & 1) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) out[i] = 0u;
+            } else unpack_half<0>(p, me, src, pc, kb0, nkb, out);
+            // only now is the slot needed: the MMAs that read its previous contents must have completed
+            bool ok = true;
+            if (use > 0) ok = pf_wait(pf_smem(&a_empty[slot]), (use - 1) & 1, abort_flag, 22);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (!(p.debug & 8)) tmem_store32(taddr, out);
+            if (!(p.debug & 1)) unpack_half<1>(p, me, src, pc, kb0 + 1, nkb, out);
+            __syncwarp();                                // every lane has read its row: the buffer is free
+            if (PF_NBUF == 1) fetch(u + PF_G, 0);
+            if (!(p.debug & 8)) tmem_store32(taddr + 32, out);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) pf_arrive(pf_smem(&a_full[slot]));
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    } else if (warp == 8) {
+    } else if (warp == PF_UW) {
         // ------------------------------------------------------------------------------------------ activation copies
         if (lane == 0) {
             const uint8_t *xsrc = reinterpret_cast<const uint8_t *>(p.X16) + (int64_t)blockIdx.y * nkb * PF_B_BYTES;
             bool alive = true;
             for (int kb = 0; kb < nkb && alive; ++kb) {
                 const int s = kb % PF_NBS, u = kb / PF_NBS;
-                if (u > 0) alive = pf_wait(pf_smem(&b_empty[s]), (u - 1) & 1, abort_flag, 24, 200);
+                if (u > 0 && (s & 1) == 0) alive = pf_wait(pf_smem(&b_empty[s >> 1]), (u - 1) & 1, abort_flag, 24, 20);
                 if (!alive) break;
                 const uint32_t bar = pf_smem(&b_full[s]);
+                if (p.debug & 2) { pf_arrive(bar); continue; }
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((uint32_t)PF_B_BYTES) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                              :: "r"(pf_smem(smem + s * PF_B_BYTES)), "l"(xsrc + (int64_t)kb * PF_B_BYTES), "r"((uint32_t)PF_B_BYTES), "r"(bar)
@@ -430,46 +440,55 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
         if (lane == 0) {
             // instruction descriptor: fp32 accumulate, fp16 x fp16, both operands K-major, N = 256, M = 128
             constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(PF_TOK >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            // descriptors of the activation stages differ only in the start address field: one addition per MMA
+            const uint64_t dbase = pf_desc(pf_smem(smem), PF_TOK * 16, 128);
+            const uint32_t dlo0 = (uint32_t)dbase, dhi = (uint32_t)(dbase >> 32);
             bool alive = true;
+            int s = 0;                                   // activation stage and the parity of its current use
+            uint32_t bpar = 0;
             for (int kb = 0; kb < nkb && alive; ++kb) {
-                const int s = kb % PF_NBS, u = kb / PF_NBS;
-                const int unit = kb >> 1, slot = unit & (PF_NU - 1), use = unit / PF_NU;
-                if ((kb & 1) == 0) alive = pf_wait(pf_smem(&a_full[slot]), use & 1, abort_flag, 25, 32);
-                if (alive) alive = pf_wait(pf_smem(&b_full[s]), u & 1, abort_flag, 26, 32);
+                const int unit = kb >> 1, slot = unit & (PF_NU - 1);
+                if ((kb & 1) == 0) alive = pf_wait(pf_smem(&a_full[slot]), (uint32_t)(unit / PF_NU) & 1u, abort_flag, 25, 32);
+                if (alive) alive = pf_wait(pf_smem(&b_full[s]), bpar, abort_flag, 26, 32);
                 if (!alive) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t b32 = pf_smem(smem + s * PF_B_BYTES);
+                if ((kb & 1) == 0) asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t a_t = tmem + 256u + (uint32_t)(slot * 64 + (kb & 1) * 32);
+                const uint32_t dlo = dlo0 + (uint32_t)(s * (PF_B_BYTES >> 4));
+                if (!(p.debug & 16)) {
 #pragma unroll
-                for (int kk = 0; kk < PF_BK / 16; ++kk) {
-                    // 16 columns of K: 8 columns of tensor memory (two fp16 each) and two 8-column groups of activations
-                    const uint64_t db = pf_desc(b32 + 2 * kk * (PF_TOK * 16), PF_TOK * 16, 128);
-                    const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
-                    asm volatile(
-                        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n}\n"
-                        :: "r"(tmem), "r"(a_t + (uint32_t)(8 * kk)), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-                        : "memory");
+                    for (int kk = 0; kk < PF_BK / 16; ++kk) {
+                        // 16 columns of K: 8 columns of tensor memory (two fp16 each) and two 8-column groups of activations
+                        uint64_t db;
+                        asm volatile("mov.b64 %0, {%1, %2};\n" : "=l"(db) : "r"(dlo + (uint32_t)(kk * ((2 * PF_TOK * 16) >> 4))), "r"(dhi));
+                        const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
+                        asm volatile(
+                            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                            " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n}\n"
+                            :: "r"(tmem), "r"(a_t + (uint32_t)(8 * kk)), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+                            : "memory");
+                    }
                 }
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&b_empty[s])) : "memory");
-                if ((kb & 1) || kb == nkb - 1)
+                if ((kb & 1) || kb == nkb - 1) {         // a pair of K blocks frees its two activation stages and its weight slot
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&b_empty[s >> 1])) : "memory");
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&a_empty[slot])) : "memory");
+                }
                 if (kb == nkb - 1)
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&all_done)) : "memory");
+                if (++s == PF_NBS) { s = 0; bpar ^= 1u; }
             }
         }
     }
 
-    // ---- epilogue: tensor memory -> registers -> Y.  A warp reads the 32 lanes (warp & 3) * 32 ...; warps 4..7 take
-    // the upper 128 tokens.
-    if (warp < 8) {
+    // ---- epilogue: tensor memory -> registers -> Y.  A warp reads the 32 lanes (warp & 3) * 32 ...; every group of four
+    // warps takes its share of the 256 tokens.
+    if (warp < 4 * PF_EG) {
         bool alive = !*abort_flag;
         if (alive) alive = pf_wait(pf_smem(&all_done), 0, abort_flag, 27, 100);
         alive = __all_sync(0xffffffffu, alive);          // tcgen05.ld is warp-wide: all lanes or none
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (alive) {
             const int lq = (warp & 3) * 32;
-            const int cbeg = (warp >> 2) * 128, cend = cbeg + 128;
+            const int cbeg = (warp >> 2) * (PF_TOK / PF_EG), cend = cbeg + PF_TOK / PF_EG;
             const int row = me.row;
             const float ts = row >= 0 ? __ldg(p.tau_s + row) : 0.f, ms = row >= 0 ? __ldg(p.min_s + row) : 0.f;
             for (int c0 = cbeg; c0 < cend; c0 += 32) {
@@ -492,7 +511,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const PrefillPar
             }
         }
     }
-    if (*abort_flag && warp == 8) {                      // copies may still be in flight: let them land before the CTA goes
+    if (*abort_flag && warp == PF_UW) {                      // copies may still be in flight: let them land before the CTA goes
         uint64_t t0, t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
         for (int i = 0; i < (1 << 16); ++i) {
@@ -663,6 +682,8 @@ int prefill_error_word(int *out) {
     return QVB8_OK;
 }
 
+static int g_prefill_debug = 0;
+
 static int launch_prefill(const PrefillParams &prm, cudaStream_t st) {
     static thread_local int granted_dev = -1;
     int dev = 0;
@@ -680,6 +701,8 @@ static int launch_prefill(const PrefillParams &prm, cudaStream_t st) {
 
 }  // namespace qv
 
+QV_API void qvb8_prefill_set_tuning(int debug) { qv::g_prefill_debug = debug; }
+
 QV_API int64_t qvb8_prefill_scratch_bytes(int64_t M, int64_t Q, int64_t P) {
     if (M <= 0 || P <= 0 || Q < 0) return 0;
     const int64_t Mpad = (M + qv::PF_TOK - 1) / qv::PF_TOK * qv::PF_TOK;
@@ -696,6 +719,7 @@ QV_API int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int
     if (w->Q == 0) return QVB8_OK;
     if (w->P % PF_BK != 0) return fail(QVB8_ERR_ARG, "qvb8_prefill: P must be a multiple of %d", PF_BK);
     if (!aligned(X, 16)) return fail(QVB8_ERR_ARG, "qvb8_prefill: X must be 16-byte aligned");
+    if (w->ids_bytes >= (1ll << 32)) return fail(QVB8_ERR_ARG, "qvb8_prefill: packs of 4 GiB and more are not supported");
     if (!plan || !aligned(plan, 256)) return fail(QVB8_ERR_ARG, "qvb8_prefill: the pack's plan is needed (qvb8_plan_build), 256-byte aligned");
     const int64_t need = qvb8_prefill_scratch_bytes(M, w->Q, w->P);
     if (!scratch || scratch_bytes < need || !aligned(scratch, 256))
@@ -713,7 +737,7 @@ QV_API int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int
     const PlanLayout L = plan_layout(w->Q, w->n_esc);
     const uint8_t *pb = reinterpret_cast<const uint8_t *>(plan);
     PrefillParams prm{w->ids, w->min_s, w->tau_s, w->nbits, w->bit_off, reinterpret_cast<const TileDesc *>(pb + L.tiles), L.max_tiles,
-                      X16, sumx, Y, (int)w->Q, (int)w->P, (int)M, (int)Mpad};
+                      X16, sumx, Y, (int)w->Q, (int)w->P, (int)M, (int)Mpad, g_prefill_debug};
     if (int rc = launch_prefill(prm, st)) return rc;
 
     if (cudaMemsetAsync(wide, 0, sizeof(int), st) != cudaSuccess) return cuda_status("qvb8_prefill memset");

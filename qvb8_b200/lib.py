@@ -25,7 +25,7 @@ EXPORTS = (
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
-    "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill",
+    "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
 )
 
 
@@ -96,6 +96,8 @@ def load() -> ctypes.CDLL:
             lib.qvb8_prefill_scratch_bytes.argtypes = [i64, i64, i64]
             lib.qvb8_prefill_scratch_bytes.restype = i64
             lib.qvb8_prefill.argtypes = [pk, vp, vp, ci, i64, vp, vp, i64, vp]
+            lib.qvb8_prefill_set_tuning.argtypes = [ci]
+            lib.qvb8_prefill_set_tuning.restype = None
             es = ctypes.POINTER(ExpertStackStruct)
             rp = ctypes.POINTER(RPackStruct)
             lib.qvb8r_ids.argtypes = [rp, vp, vp]
