@@ -136,7 +136,8 @@ int64_t qvb8_prefill_scratch_bytes(int64_t M, int64_t Q, int64_t P);
 int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int64_t M, float *Y, void *scratch,
                  int64_t scratch_bytes, void *stream);
 /* Tuning aid for sweeps (results are wrong while it is set): 1 = no unpack arithmetic, 2 = no activation copies,
- * 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs; 0 = normal. */
+ * 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs, 48 = no MMAs and plain
+ * barrier arrivals instead of commits; 0 = normal. */
 void qvb8_prefill_set_tuning(int debug);
 
 /* ---- mixture-of-experts MLP over stacked expert packs -------------------------------------------------------------

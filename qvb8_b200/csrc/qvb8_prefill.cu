@@ -122,7 +122,7 @@ struct PrefillParams {
     const float *sumx;         // (PF_KS, Mpad) partial sums of the narrowed activations
     float *Y;                  // (M, Q)
     int Q, P, M, Mpad;
-    int debug;                 // tuning aid: 1 = no unpack arithmetic, 2 = no activation copies, 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs
+    int debug;                 // tuning aid: 1 = no unpack arithmetic, 2 = no activation copies, 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs, 48 = no MMAs and plain barrier arrivals instead of commits
 };
 
 // The output row of a slot of the plan's order, -1 for padding.
@@ -469,8 +469,13 @@ __global__ void __maxnreg__(PF_G == 2 ? 168 : PF_G == 3 ? 128 : 96) prefill_kern
                     }
                 }
                 if ((kb & 1) || kb == nkb - 1) {         // a pair of K blocks frees its two activation stages and its weight slot
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&b_empty[s >> 1])) : "memory");
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&a_empty[slot])) : "memory");
+                    if ((p.debug & 48) == 48) {          // tuning aid, only without MMAs: plain arrivals instead of commits
+                        pf_arrive(pf_smem(&b_empty[s >> 1]));
+                        pf_arrive(pf_smem(&a_empty[slot]));
+                    } else {
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&b_empty[s >> 1])) : "memory");
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&a_empty[slot])) : "memory");
+                    }
                 }
                 if (kb == nkb - 1)
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(pf_smem(&all_done)) : "memory");

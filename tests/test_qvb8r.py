@@ -130,3 +130,41 @@ def test_gpu_products(cuda_lib, M):
     errt = np.linalg.norm(yt.cpu().numpy() - wt) / np.linalg.norm(wt)
     assert errt < TOL and errt < TIGHT, errt
     assert torch.equal(yt, ext.tc(Xh, *core, 8))                              # fixed summation order
+
+
+def test_linear_module_builds_on_cpu_and_chunks_cover_all_rows():
+    """Host-side logic of the module mirror: buffers, escape CSR, chunk spans (no kernel call)."""
+    from qvb8_b200.linear_r import QVBandLinearV8R
+    _, d = _pack(100, 256, seed=21, K=3, T=4)
+    mod = QVBandLinearV8R(d, device="cpu")
+    mod.CHUNK_BYTES = 1                                  # default: one chunk
+    assert sorted(mod.chunk_orows.tolist()) == list(range(100))
+    assert sum(c[3] for c in mod.chunks) == 100 and mod.chunks[-1][7] == mod.chunk_eflat.numel()
+    assert int(mod.esc_ptr[-1]) == len(d["esc_idx"]) == mod.esc_delta16.numel()
+    small = type("Small", (QVBandLinearV8R,), {"CHUNK_BYTES": 2 * 256 * 16})     # 16 rows of fp16 per chunk
+    m2 = small(d, device="cpu")
+    assert len(m2.chunks) > 1 and sorted(m2.chunk_orows.tolist()) == list(range(100))
+    mod.to(torch.bfloat16)
+    assert mod.min_s.dtype == torch.float32 and mod.esc_delta.dtype == torch.float32
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,chunk_rows", [(1, None), (5, None), (12, None), (40, None), (130, None), (130, 32)])
+def test_linear_module_forward(cuda_lib, M, chunk_rows):
+    from qvb8_b200.linear_r import QVBandLinearV8R
+    Q, P = 260, 1024
+    _, d = _pack(Q, P, seed=31, K=3, T=2)
+    cls = QVBandLinearV8R if chunk_rows is None else type("Small", (QVBandLinearV8R,), {"CHUNK_BYTES": 2 * P * chunk_rows})
+    bias = torch.linspace(-1, 1, Q)
+    mod = cls(d, bias=bias, device=DEV)
+    X = synth.synth_activation(M, P, seed=M, device=DEV, dtype=torch.bfloat16)
+    y = mod(X.reshape(1, M, P))
+    assert y.shape == (1, M, Q) and y.dtype == torch.bfloat16
+    want = oracle.matmul_f32w(X.float().cpu().numpy(), _dense(d), narrow_x=False) + bias.numpy()[None, :]
+    err = np.linalg.norm(y.float().cpu().numpy().reshape(M, Q) - want) / np.linalg.norm(want)
+    assert err < TOL, err                                 # bf16 output rounding: ~2e-3
+    yf = mod(X.float())
+    errf = np.linalg.norm(yf.cpu().numpy() - want) / np.linalg.norm(want)
+    assert errf < 1e-3, errf                             # fp16 weight rounding above 8 rows
+    Wd = mod.dense(torch.float32)
+    assert np.array_equal(Wd.cpu().numpy().view(np.uint32), _dense(d).view(np.uint32))
