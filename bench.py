@@ -308,6 +308,7 @@ def main():
                     help="stack: the dense linear stack (headline); moe: one 35B-A3B-class expert layer; "
                          "prefill: 27B-class MLP projections for 2048 tokens on the tcgen05 kernel")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection (no same-input fusion)")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: NCCL all-reduce instead of the peer push kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -343,8 +344,31 @@ def main():
     torch.cuda.synchronize(dev)
     t_build = time.perf_counter() - t_build
 
+    allreduce_kind = None
     if world > 1:
-        st.enable_collectives()      # all-reduce after o and after down: the only exchanges of a layer
+        # all-reduce after o and after down: the only exchanges of a layer.  The push kernel over peer memory is checked
+        # once against NCCL on seeded data; if the peers cannot map each other's memory the stack keeps NCCL.
+        allreduce_kind = "nccl"
+        if not args.nccl_allreduce:
+            try:
+                st.enable_collectives(peer=True)
+                probe = torch.randn(args.rows * cfg.d_model, device=dev, generator=torch.Generator(device=dev).manual_seed(rank))
+                mine = st.peer.allreduce(probe.clone())
+                ref = probe.clone()
+                dist.all_reduce(ref)
+                torch.cuda.synchronize(dev)
+                ok = torch.tensor([1 if torch.allclose(mine, ref, rtol=1e-5, atol=1e-5) else 0], device=dev)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                if int(ok.item()) == 1:
+                    allreduce_kind = "peer push kernel (checked against NCCL)"
+                else:
+                    st.peer = None
+            except RuntimeError as e:
+                if rank == 0:
+                    print(f"[bench] peer all-reduce unavailable ({e}); using NCCL", file=sys.stderr, flush=True)
+                st.enable_collectives(peer=False)
+        else:
+            st.enable_collectives(peer=False)
 
     def one_step():
         st.step()
@@ -410,7 +434,7 @@ def main():
             "weights": total_weights, "compressed_bytes": total_bytes,
             "bits_per_weight": 8.0 * total_bytes / max(1, total_weights),
             "row_width_hist": {str(k): v for k, v in sorted(st.width_hist.items())}, "escapes": st.n_escapes,
-            "parallelism": f"column/row-parallel pairs x{world}, 2 all-reduces per layer" if world > 1 else "single GPU",
+            "parallelism": f"column/row-parallel pairs x{world}, 2 all-reduces per layer ({allreduce_kind})" if world > 1 else "single GPU",
             "l2": "working set (packs) far larger than L2; every step streams all of it",
             "tokens_per_s": 1e3 / ms_step * args.rows, "pack_build_s": round(t_build, 1),
         },

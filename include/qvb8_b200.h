@@ -117,8 +117,8 @@ int qvb8_debug_trace(unsigned long long *out32);
  * kernel of this library (1 = copy ring slot never freed, 2 = copy never landed, 3 / 4 = hand-over between the
  * consumer and finishing warps, 5 / 6 = activation staging, 7 / 8 = descriptor ring, 9 = part of a shared tile,
  * 21..27 = prefill: packed ids never landed, weight slot of tensor memory never freed, raw ring slot never freed,
- * activation stage never freed, weights / activations of a K block never arrived, accumulator never completed).
- * Synchronises the host. */
+ * activation stage never freed, weights / activations of a K block never arrived, accumulator never completed;
+ * 31 = a peer's flag of an all-reduce never arrived).  Synchronises the host. */
 int qvb8_device_status(int *status);
 
 /* Same product through the layout-agnostic kernel (any P, any id alignment, widths 1..14).  The library falls
@@ -139,6 +139,22 @@ int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int x_dtyp
  * 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs, 48 = no MMAs and plain
  * barrier arrivals instead of commits; 0 = normal. */
 void qvb8_prefill_set_tuning(int debug);
+
+/* ---- all-reduce of the row-parallel projections' partial sums over NVLink peer memory ------------------------------
+ * Replaces the library collective at the shard boundary of a linear split across cards (reference
+ * formats/qvb8/module.py:126-160 row_subset + the NCCL exchange of run/placement.py).  Every rank allocates one exchange
+ * area with qvb8_peer_alloc (qvb8_peer_bytes(world, cap) bytes), hands the 64-byte IPC handle to the other ranks of the
+ * node, and maps theirs with qvb8_peer_open.  qvb8_peer_allreduce pushes this rank's `n` partial sums into a slot on
+ * every rank (plain peer stores, no multicast), raises a flag there, waits (bounded, status word 31) for the other
+ * ranks' flags and adds the slots in rank order: the sums are bit-identical on every rank.  bases[r] = rank r's area as
+ * mapped in this process; `epoch` = a zeroed uint32 in this rank's device memory.  All ranks make the same calls in the
+ * same order; a call is capturable into a CUDA graph. */
+int64_t qvb8_peer_bytes(int world, int64_t cap_floats);
+int qvb8_peer_alloc(int64_t bytes, void **ptr, unsigned char handle[64]);
+int qvb8_peer_open(const unsigned char handle[64], void **ptr);
+int qvb8_peer_close(void *ptr, int own);
+int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
+                        float *out, int64_t n, void *stream);
 
 /* ---- mixture-of-experts MLP over stacked expert packs -------------------------------------------------------------
  * Stacked layout of one projection of all E experts (reference formats/qvb8/backends_experts.py:144-196): every

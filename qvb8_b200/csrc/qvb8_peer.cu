@@ -1,0 +1,162 @@
+// One-shot all-reduce of the small partial results of the row-parallel projections (o, down) over NVLink peer memory.
+//
+// The reference splits a linear across cards by output rows and exchanges with NCCL at the shard boundary
+// (formats/qvb8/module.py:126-160 row_subset, run/placement.py).  For decode the exchanged vector is tiny (M x d_model
+// fp32 = 16 .. 256 KB), so the cost of a library all-reduce is its latency.  Here every rank PUSHES its partial sums
+// straight into a receive slot on every peer (plain peer stores, no multicast), raises a flag there, waits for the
+// peers' flags, and adds the slots up in rank order: every rank gets bit-identical sums.
+//
+// Memory of a rank (one allocation, shared with the peers through CUDA IPC):
+//   [0, 1024)                       flags[2][world]: flag[b][r] = last epoch whose data rank r has put into buffer b
+//   [1024 + b * world * cap ...)    recv[b][r][cap floats]: the partial sums of rank r for an epoch of parity b
+// Two buffers: a rank can run at most one all-reduce ahead of a peer (it needs the peer's flag of the current epoch,
+// which the peer raises only after it has finished reading the previous one).
+//
+// Waits are bounded (2 s): a wait that runs out raises the error word and the kernel carries on with what it has.
+#include "common.cuh"
+
+#include <cstring>
+
+namespace qv {
+
+constexpr int PEER_MAX_WORLD = 16;
+constexpr int PEER_FLAG_BYTES = 1024;
+constexpr int PEER_THREADS = 1024;
+
+__device__ int g_peer_error = 0;
+
+struct PeerParams {
+    uint8_t *base[PEER_MAX_WORLD];       // every rank's allocation as mapped in THIS process (base[rank] = own)
+    int rank, world;
+    int64_t cap;                         // floats per receive slot
+    uint32_t *epoch;                     // device counter of this rank: all-reduces done so far
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+
+// One block.  n floats (a multiple of 4), n <= cap.
+__global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const PeerParams p, const float *__restrict__ partial,
+                                                                      float *__restrict__ out, int n) {
+    __shared__ uint32_t s_epoch;
+    const int tid = threadIdx.x;
+    if (tid == 0) s_epoch = *p.epoch + 1u;
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    const int b = (int)(epoch & 1u);
+    const int64_t slot = ((int64_t)b * p.world + p.rank) * p.cap;
+    // 1. push: this rank's partial sums into slot [b][rank] of every rank (its own included)
+    const float4 *src = reinterpret_cast<const float4 *>(partial);
+    for (int r = 0; r < p.world; ++r) {
+        float4 *dst = reinterpret_cast<float4 *>(p.base[r] + PEER_FLAG_BYTES) + (slot >> 2);
+        for (int i = tid; i < (n >> 2); i += PEER_THREADS) dst[i] = src[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    // 2. flags: tell every rank that this rank's data of this epoch is in place
+    if (tid < p.world) st_release_sys(reinterpret_cast<uint32_t *>(p.base[tid]) + b * PEER_MAX_WORLD + p.rank, epoch);
+    // 3. wait for every rank's flag in this rank's memory
+    if (tid < p.world) {
+        const uint32_t *f = reinterpret_cast<const uint32_t *>(p.base[p.rank]) + b * PEER_MAX_WORLD + tid;
+        uint64_t t0, t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+        bool ok = false;
+        for (int i = 0; i < (1 << 24); ++i) {
+            if ((int32_t)(ld_acquire_sys(f) - epoch) >= 0) { ok = true; break; }
+            if ((i & 63) == 63) {
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+                if (t - t0 > 2000000000ull) break;
+            }
+        }
+        if (!ok) atomicCAS(&g_peer_error, 0, 31);
+    }
+    __syncthreads();
+    // 4. sum the slots in rank order
+    const float4 *rb = reinterpret_cast<const float4 *>(p.base[p.rank] + PEER_FLAG_BYTES) + (((int64_t)b * p.world * p.cap) >> 2);
+    for (int i = tid; i < (n >> 2); i += PEER_THREADS) {
+        float4 a = rb[i];
+        for (int r = 1; r < p.world; ++r) {
+            const float4 v = rb[(((int64_t)r * p.cap) >> 2) + i];
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        reinterpret_cast<float4 *>(out)[i] = a;
+    }
+    if (tid == 0) *p.epoch = epoch;
+}
+
+int peer_error_word(int *out) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_peer_error, sizeof(int)) != cudaSuccess) return cuda_status("qvb8_device_status");
+    *out = v;
+    return QVB8_OK;
+}
+
+}  // namespace qv
+
+QV_API int64_t qvb8_peer_bytes(int world, int64_t cap_floats) {
+    if (world < 1 || world > qv::PEER_MAX_WORLD || cap_floats < 4) return 0;
+    cap_floats = (cap_floats + 3) / 4 * 4;
+    return qv::PEER_FLAG_BYTES + 2 * (int64_t)world * cap_floats * 4 + 256;
+}
+
+/* Allocates (cudaMalloc, zeroed) this rank's exchange memory on the current device and returns its IPC handle (64
+ * bytes) for the peers. */
+QV_API int qvb8_peer_alloc(int64_t bytes, void **ptr, unsigned char handle[64]) {
+    using namespace qv;
+    if (int rc = check_device("qvb8_peer_alloc")) return rc;
+    if (!ptr || !handle || bytes <= 0) return fail(QVB8_ERR_ARG, "qvb8_peer_alloc: bad arguments");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (cudaMalloc(ptr, (size_t)bytes) != cudaSuccess) return cuda_status("qvb8_peer_alloc");
+    if (cudaMemset(*ptr, 0, (size_t)bytes) != cudaSuccess) return cuda_status("qvb8_peer_alloc memset");
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, *ptr) != cudaSuccess) return cuda_status("qvb8_peer_alloc handle");
+    memcpy(handle, &h, 64);
+    return cudaDeviceSynchronize() == cudaSuccess ? QVB8_OK : cuda_status("qvb8_peer_alloc sync");
+}
+
+QV_API int qvb8_peer_open(const unsigned char handle[64], void **ptr) {
+    using namespace qv;
+    if (int rc = check_device("qvb8_peer_open")) return rc;
+    if (!ptr || !handle) return fail(QVB8_ERR_ARG, "qvb8_peer_open: bad arguments");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    if (cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return cuda_status("qvb8_peer_open");
+    return QVB8_OK;
+}
+
+QV_API int qvb8_peer_close(void *ptr, int own) {
+    if (!ptr) return QVB8_OK;
+    const cudaError_t e = own ? cudaFree(ptr) : cudaIpcCloseMemHandle(ptr);
+    return e == cudaSuccess ? QVB8_OK : qv::cuda_status("qvb8_peer_close");
+}
+
+/* out[0 .. n) = sum over the ranks of their partial[0 .. n), identical on every rank.  bases[r] = rank r's exchange
+ * memory as mapped in this process (own allocation for r = rank); epoch = a zeroed uint32 of this rank in device
+ * memory, owned by the communicator.  n % 4 == 0, n <= cap_floats.  Every rank must make the same sequence of calls. */
+QV_API int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
+                               float *out, int64_t n, void *stream) {
+    using namespace qv;
+    if (int rc = check_device("qvb8_peer_allreduce")) return rc;
+    if (!bases || !epoch || !partial || !out || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world)
+        return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: bad arguments");
+    cap_floats = (cap_floats + 3) / 4 * 4;
+    if (n <= 0 || n % 4 != 0 || n > cap_floats) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: n must be a multiple of 4 within the slot size");
+    if (!aligned(partial, 16) || !aligned(out, 16)) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: partial / out must be 16-byte aligned");
+    PeerParams p{};
+    for (int r = 0; r < world; ++r) {
+        if (!bases[r]) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: null peer mapping");
+        p.base[r] = reinterpret_cast<uint8_t *>(bases[r]);
+    }
+    p.rank = rank;
+    p.world = world;
+    p.cap = cap_floats;
+    p.epoch = reinterpret_cast<uint32_t *>(epoch);
+    peer_allreduce_kernel<<<1, PEER_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p, partial, out, (int)n);
+    return cuda_status("qvb8_peer_allreduce");
+}

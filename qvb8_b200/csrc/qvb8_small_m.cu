@@ -51,6 +51,7 @@ int launch_small_m_generic(const qvb8_pack *w, const void *X, int x_dtype, int x
 int check_small_m_args(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, const float *Y,
                        const char *who);
 int prefill_error_word(int *out);                 // qvb8_prefill.cu
+int peer_error_word(int *out);                    // qvb8_peer.cu
 
 constexpr int KC = 128;                   // columns per chunk
 constexpr int NW = 4;                     // consumer warps
@@ -1357,6 +1358,8 @@ QV_API int qvb8_device_status(int *status) {
     if (cudaMemcpyFromSymbol(&v, qv::g_error_word, sizeof(int)) != cudaSuccess) return qv::cuda_status("qvb8_device_status");
     if (v == 0)
         if (int rc = qv::prefill_error_word(&v)) return rc;
+    if (v == 0)
+        if (int rc = qv::peer_error_word(&v)) return rc;
     *status = v;
     return QVB8_OK;
 }

@@ -26,6 +26,7 @@ EXPORTS = (
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
     "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
+    "qvb8_peer_bytes", "qvb8_peer_alloc", "qvb8_peer_open", "qvb8_peer_close", "qvb8_peer_allreduce",
 )
 
 
@@ -96,6 +97,12 @@ def load() -> ctypes.CDLL:
             lib.qvb8_prefill_scratch_bytes.argtypes = [i64, i64, i64]
             lib.qvb8_prefill_scratch_bytes.restype = i64
             lib.qvb8_prefill.argtypes = [pk, vp, vp, ci, i64, vp, vp, i64, vp]
+            lib.qvb8_peer_bytes.argtypes = [ci, i64]
+            lib.qvb8_peer_bytes.restype = i64
+            lib.qvb8_peer_alloc.argtypes = [i64, ctypes.POINTER(vp), ctypes.c_char_p]
+            lib.qvb8_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+            lib.qvb8_peer_close.argtypes = [vp, ci]
+            lib.qvb8_peer_allreduce.argtypes = [ctypes.POINTER(vp), ci, ci, i64, vp, vp, vp, i64, vp]
             lib.qvb8_prefill_set_tuning.argtypes = [ci]
             lib.qvb8_prefill_set_tuning.restype = None
             es = ctypes.POINTER(ExpertStackStruct)

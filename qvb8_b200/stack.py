@@ -146,28 +146,39 @@ class LinearStack:
                 _lib.reserve_scratch(self.device, self.M, pk.Q, pk.P)
         self.graph = None
         self.reduce = False      # all-reduce the row-parallel projections' partial sums (set by enable_collectives)
+        self.peer = None         # the NVLink push all-reduce, when enabled
         self.launches_per_step = sum(len(row) for row in self.launches)
         self.pdl = True
         self._host_in = self._host_out = None
 
     # ---- execution ------------------------------------------------------------------------------------
-    def enable_collectives(self) -> None:
-        """The shard boundaries: after o and after down the ranks all-reduce their partial (M, d_model) sums (NCCL on
-        the compute stream, captured into the graph with the launches).  q/k/v and gate/up need no exchange: their
-        consumers work on the local slice."""
+    def enable_collectives(self, peer: bool = True) -> None:
+        """The shard boundaries: after o and after down the ranks all-reduce their partial (M, d_model) sums, captured
+        into the graph with the launches.  peer=True: the push kernel over NVLink peer memory (qvb8_b200.peer); False:
+        NCCL on the compute stream.  q/k/v and gate/up need no exchange: their consumers work on the local slice."""
         import torch.distributed as dist
         self.reduce = self.world > 1 and dist.is_initialized()
+        self.peer = None
+        if self.reduce and peer:
+            from .peer import PeerAllReduce
+            cap = max(t.numel() for row in self.y_launch for t in row)
+            self.peer = PeerAllReduce(dist.group.WORLD, cap, self.device)
+
+    def _allreduce(self, t: torch.Tensor) -> None:
+        if self.peer is not None and t.numel() % 4 == 0:
+            self.peer.allreduce(t)
+        else:
+            import torch.distributed as dist
+            dist.all_reduce(t)
 
     def run_eager(self) -> None:
         """One pass over every launch of every layer on the current stream."""
-        if self.reduce:
-            import torch.distributed as dist
         for li, row in enumerate(self.launches):
             for j, (name, pk, st, keep, xname, _) in enumerate(row):
                 _lib.small_m(st, keep, self.x[xname], out=self.y_launch[li][j], plan=keep[-1],
                              flags=_lib.FLAG_PDL if self.pdl else 0)
                 if self.reduce and name in ROW_PARALLEL:
-                    dist.all_reduce(self.y_launch[li][j])
+                    self._allreduce(self.y_launch[li][j])
 
     def capture(self) -> None:
         self.run_eager()                      # warm-up outside capture: shared-memory opt-in, scratch
