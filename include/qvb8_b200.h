@@ -148,13 +148,13 @@ void qvb8_prefill_set_tuning(int debug);
  * every rank (plain peer stores, no multicast), raises a flag there, waits (bounded, status word 31) for the other
  * ranks' flags and adds the slots in rank order: the sums are bit-identical on every rank.  bases[r] = rank r's area as
  * mapped in this process; `epoch` = a zeroed uint32 in this rank's device memory.  All ranks make the same calls in the
- * same order; a call is capturable into a CUDA graph. */
+ * same order; a call is capturable into a CUDA graph.  flags: QVB8_FLAG_PDL as for qvb8_small_m_ex. */
 int64_t qvb8_peer_bytes(int world, int64_t cap_floats);
 int qvb8_peer_alloc(int64_t bytes, void **ptr, unsigned char handle[64]);
 int qvb8_peer_open(const unsigned char handle[64], void **ptr);
 int qvb8_peer_close(void *ptr, int own);
 int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
-                        float *out, int64_t n, void *stream);
+                        float *out, int64_t n, int flags, void *stream);
 
 /* ---- mixture-of-experts MLP over stacked expert packs -------------------------------------------------------------
  * Stacked layout of one projection of all E experts (reference formats/qvb8/backends_experts.py:144-196): every

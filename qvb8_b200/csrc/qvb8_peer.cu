@@ -46,6 +46,10 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const Peer
                                                                       float *__restrict__ out, int n) {
     __shared__ uint32_t s_epoch;
     const int tid = threadIdx.x;
+    // programmatic dependent launch: the next kernel may begin its prologue now (it waits for this grid's completion
+    // before it reads anything this grid writes); this grid waits for its predecessor before it reads `partial`
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     if (tid == 0) s_epoch = *p.epoch + 1u;
     __syncthreads();
     const uint32_t epoch = s_epoch;
@@ -138,9 +142,10 @@ QV_API int qvb8_peer_close(void *ptr, int own) {
 
 /* out[0 .. n) = sum over the ranks of their partial[0 .. n), identical on every rank.  bases[r] = rank r's exchange
  * memory as mapped in this process (own allocation for r = rank); epoch = a zeroed uint32 of this rank in device
- * memory, owned by the communicator.  n % 4 == 0, n <= cap_floats.  Every rank must make the same sequence of calls. */
+ * memory, owned by the communicator.  n % 4 == 0, n <= cap_floats.  Every rank must make the same sequence of calls.
+ * flags: QVB8_FLAG_PDL launches with programmatic stream serialization, like qvb8_small_m_ex. */
 QV_API int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
-                               float *out, int64_t n, void *stream) {
+                               float *out, int64_t n, int flags, void *stream) {
     using namespace qv;
     if (int rc = check_device("qvb8_peer_allreduce")) return rc;
     if (!bases || !epoch || !partial || !out || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world)
@@ -157,6 +162,16 @@ QV_API int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t 
     p.world = world;
     p.cap = cap_floats;
     p.epoch = reinterpret_cast<uint32_t *>(epoch);
-    peer_allreduce_kernel<<<1, PEER_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p, partial, out, (int)n);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(PEER_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & QVB8_FLAG_PDL) ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, p, partial, out, (int)n) != cudaSuccess) return cuda_status("qvb8_peer_allreduce launch");
     return cuda_status("qvb8_peer_allreduce");
 }

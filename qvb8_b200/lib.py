@@ -102,7 +102,7 @@ def load() -> ctypes.CDLL:
             lib.qvb8_peer_alloc.argtypes = [i64, ctypes.POINTER(vp), ctypes.c_char_p]
             lib.qvb8_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
             lib.qvb8_peer_close.argtypes = [vp, ci]
-            lib.qvb8_peer_allreduce.argtypes = [ctypes.POINTER(vp), ci, ci, i64, vp, vp, vp, i64, vp]
+            lib.qvb8_peer_allreduce.argtypes = [ctypes.POINTER(vp), ci, ci, i64, vp, vp, vp, i64, ci, vp]
             lib.qvb8_prefill_set_tuning.argtypes = [ci]
             lib.qvb8_prefill_set_tuning.restype = None
             es = ctypes.POINTER(ExpertStackStruct)

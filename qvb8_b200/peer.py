@@ -51,7 +51,7 @@ class PeerAllReduce:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)                         # every area is zeroed and mapped before the first push
 
-    def allreduce(self, partial: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def allreduce(self, partial: torch.Tensor, out: torch.Tensor | None = None, flags: int = 0) -> torch.Tensor:
         """out = sum over the ranks of `partial` (fp32, contiguous, numel % 4 == 0), on the current stream."""
         if partial.dtype != torch.float32 or not partial.is_contiguous() or partial.device != self.device:
             raise RuntimeError("qvb8_b200: the peer all-reduce takes contiguous fp32 tensors on its device")
@@ -59,7 +59,7 @@ class PeerAllReduce:
         n = partial.numel()
         with torch.cuda.device(self.device):
             _lib.check(_lib.load().qvb8_peer_allreduce(self._ptrs, self.rank, self.world, self.cap, self.epoch.data_ptr(),
-                                                       partial.data_ptr(), out.data_ptr(), n, _lib.stream_ptr(self.device)),
+                                                       partial.data_ptr(), out.data_ptr(), n, int(flags), _lib.stream_ptr(self.device)),
                        "qvb8_peer_allreduce")
         return out
 

@@ -166,7 +166,7 @@ class LinearStack:
 
     def _allreduce(self, t: torch.Tensor) -> None:
         if self.peer is not None and t.numel() % 4 == 0:
-            self.peer.allreduce(t)
+            self.peer.allreduce(t, flags=_lib.FLAG_PDL if self.pdl else 0)
         else:
             import torch.distributed as dist
             dist.all_reduce(t)
