@@ -64,6 +64,12 @@ const char *qvb8_version(void);
  * :535-625); the F32 form is the un-narrowed value the GEMV multiplies (:346-353). */
 int qvb8_decode(const qvb8_pack *w, int out_dtype, void *out, void *stream);
 
+/* Row gather: out (n, P) of out_dtype = the restored rows rows[0 .. n) (int64 device array), escapes written over.
+ * Replaces QVBandEmbeddingV8._decode_rows and the per-row escape loop of its forward (reference
+ * formats/qvb8/embedding.py:92-150); like them it restores with a multiplication and an addition (min_s + id * tau_s),
+ * so the table is bit-identical with the reference's.  A row index outside [0, Q) yields a row of zeros. */
+int qvb8_embed_rows(const qvb8_pack *w, const int64_t *rows, int64_t n, int out_dtype, void *out, void *stream);
+
 /* Bytes of scratch qvb8_small_m needs for these sizes (0 is possible).  The scratch must be zero-filled once
  * when it is allocated; the kernel leaves it in a reusable state.  Calls that share one scratch buffer must not
  * overlap on the device. */

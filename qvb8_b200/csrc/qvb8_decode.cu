@@ -164,6 +164,45 @@ static int decode_launch(const qvb8_pack *w, T *out, cudaStream_t st) {
     return QVB8_OK;
 }
 
+// Row gather for embeddings: out[i, :] = restored row rows[i] (reference formats/qvb8/embedding.py:92-150
+// QVBandEmbeddingV8._decode_rows + the escape loop of forward).  The reference computes min_s + id * tau_s with a
+// multiplication and an addition (two roundings in fp32), not the fused multiply-add of the linear kernels, and then
+// casts; the same two operations are used here so that the table is bit-identical.  One block per requested row; the
+// row's escapes are found by binary search in the ascending flat indices.  A row index outside [0, Q) gives a row of
+// zeros (the Python mirror checks the indices first, as torch's embedding does).
+template <typename T>
+__global__ void __launch_bounds__(256) embed_rows_kernel(const uint8_t *__restrict__ ids, const float *__restrict__ min_s,
+                                                         const float *__restrict__ tau_s, const uint8_t *__restrict__ nbits,
+                                                         const int64_t *__restrict__ bit_off, const int64_t *__restrict__ esc_idx,
+                                                         const float *__restrict__ esc_vals, int64_t n_esc, int64_t Q, int P,
+                                                         const int64_t *__restrict__ rows, T *__restrict__ out) {
+    const int64_t i = blockIdx.x;
+    const int64_t q = __ldg(rows + i);
+    T *o = out + i * P;
+    if (q < 0 || q >= Q) {
+        for (int c = threadIdx.x; c < P; c += blockDim.x) o[c] = narrow<T>(0.f);
+        return;
+    }
+    const int nb = __ldg(nbits + q);
+    const int64_t b0 = __ldg(bit_off + q);
+    const float ts = __ldg(tau_s + q), ms = __ldg(min_s + q);
+    for (int c = threadIdx.x; c < P; c += blockDim.x)
+        o[c] = narrow<T>(__fadd_rn(ms, __fmul_rn((float)field_bytes(ids, b0 + (int64_t)c * nb, nb), ts)));
+    if (n_esc == 0) return;
+    __syncthreads();
+    // [lo, hi) = escapes with flat index in [q * P, (q + 1) * P)
+    auto lower = [&](int64_t key) {
+        int64_t a = 0, b = n_esc;
+        while (a < b) {
+            const int64_t m = (a + b) >> 1;
+            if (__ldg(esc_idx + m) < key) a = m + 1; else b = m;
+        }
+        return a;
+    };
+    const int64_t lo = lower(q * P), hi = lower((q + 1) * P);
+    for (int64_t e = lo + threadIdx.x; e < hi; e += blockDim.x) o[__ldg(esc_idx + e) - q * P] = narrow<T>(__ldg(esc_vals + e));
+}
+
 }  // namespace qv
 
 QV_API int qvb8_decode(const qvb8_pack *w, int out_dtype, void *out, void *stream) {
@@ -178,4 +217,26 @@ QV_API int qvb8_decode(const qvb8_pack *w, int out_dtype, void *out, void *strea
         case QVB8_F32: return decode_launch<float>(w, reinterpret_cast<float *>(out), st);
         default: return fail(QVB8_ERR_ARG, "qvb8_decode: out_dtype %d is not QVB8_F16/BF16/F32", out_dtype);
     }
+}
+
+/* out (n, P) = the restored rows `rows[0 .. n)` (int64 device array) of the pack, escapes written over: the lookup of
+ * an embedding table kept as a pack. */
+QV_API int qvb8_embed_rows(const qvb8_pack *w, const int64_t *rows, int64_t n, int out_dtype, void *out, void *stream) {
+    using namespace qv;
+    if (int rc = check_pack(w, "qvb8_embed_rows")) return rc;
+    if (int rc = check_device("qvb8_embed_rows")) return rc;
+    if (n < 0 || n > 0x7fffffff || (n > 0 && (!rows || !out))) return fail(QVB8_ERR_ARG, "qvb8_embed_rows: bad rows / out / n");
+    if (n == 0 || w->P == 0) return QVB8_OK;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define QV_EMBED(T)                                                                                                   \
+    embed_rows_kernel<T><<<(unsigned)n, 256, 0, st>>>(w->ids, w->min_s, w->tau_s, w->nbits, w->bit_off, w->esc_idx, \
+                                                      w->esc_vals, w->n_esc, w->Q, (int)w->P, rows, reinterpret_cast<T *>(out))
+    switch (out_dtype) {
+        case QVB8_F16: QV_EMBED(__half); break;
+        case QVB8_BF16: QV_EMBED(__nv_bfloat16); break;
+        case QVB8_F32: QV_EMBED(float); break;
+        default: return fail(QVB8_ERR_ARG, "qvb8_embed_rows: out_dtype %d is not QVB8_F16/BF16/F32", out_dtype);
+    }
+#undef QV_EMBED
+    return cuda_status("qvb8_embed_rows");
 }

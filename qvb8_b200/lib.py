@@ -26,7 +26,7 @@ EXPORTS = (
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
     "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
-    "qvb8_peer_bytes", "qvb8_peer_alloc", "qvb8_peer_open", "qvb8_peer_close", "qvb8_peer_allreduce",
+    "qvb8_embed_rows", "qvb8_peer_bytes", "qvb8_peer_alloc", "qvb8_peer_open", "qvb8_peer_close", "qvb8_peer_allreduce",
 )
 
 
@@ -97,6 +97,7 @@ def load() -> ctypes.CDLL:
             lib.qvb8_prefill_scratch_bytes.argtypes = [i64, i64, i64]
             lib.qvb8_prefill_scratch_bytes.restype = i64
             lib.qvb8_prefill.argtypes = [pk, vp, vp, ci, i64, vp, vp, i64, vp]
+            lib.qvb8_embed_rows.argtypes = [pk, vp, i64, ci, vp, vp]
             lib.qvb8_peer_bytes.argtypes = [ci, i64]
             lib.qvb8_peer_bytes.restype = i64
             lib.qvb8_peer_alloc.argtypes = [i64, ctypes.POINTER(vp), ctypes.c_char_p]
@@ -205,6 +206,18 @@ def decode(pack, keep, out_dtype: torch.dtype) -> torch.Tensor:
     with torch.cuda.device(dev):
         check(load().qvb8_decode(ctypes.byref(pack), dtype_code(out_dtype), out.data_ptr(), stream_ptr(dev)),
               "qvb8_decode")
+    return out
+
+
+def embed_rows(pack, keep, rows: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """(n, P) restored rows `rows` (int64, on the pack's device) of a pack used as an embedding table."""
+    dev = keep[0].device
+    if rows.dtype != torch.int64 or rows.device != dev or not rows.is_contiguous() or rows.dim() != 1:
+        raise RuntimeError("qvb8_b200: embed_rows takes a contiguous 1-D int64 tensor on the pack's device")
+    out = torch.empty((rows.numel(), pack.P), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(load().qvb8_embed_rows(ctypes.byref(pack), rows.data_ptr(), rows.numel(), dtype_code(out_dtype),
+                                     out.data_ptr(), stream_ptr(dev)), "qvb8_embed_rows")
     return out
 
 
