@@ -60,7 +60,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(job):
         src, obj = job
-        cmd = [nvcc, *NVCC_FLAGS, *_host_cxx(), "-c", src, "-o", obj]
+        # QVB8_EXTRA_NVCC_FLAGS: extra -D switches for tuning builds (e.g. -DQVB8_PIPES_NT1=2); build with force=True
+        extra = os.environ.get("QVB8_EXTRA_NVCC_FLAGS", "").split()
+        cmd = [nvcc, *NVCC_FLAGS, *extra, *_host_cxx(), "-c", src, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         return src, r
 
