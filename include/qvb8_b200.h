@@ -112,7 +112,8 @@ int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, int x_d
 /* Tuning hook for tests and sweeps (process-wide; 0 = choose automatically): fill_pct = CTAs launched, in percent of
  * one resident wave; force_s = number of K-ranges (raised to what shared memory requires); nstg = slots of the copy
  * ring (2..8); cps = 128-column chunks per ring stage (4, 8, 12 or 16); debug bit 0 = skip the fragment math (copy
- * stream only), bit 1 = record qvb8_debug_trace stamps, bit 2 = skip the row copies (results meaningless). */
+ * stream only), bit 1 = record qvb8_debug_trace stamps, bit 2 = skip the row copies (results meaningless); bits 8..11 =
+ * pipes per CTA for up to 8 tokens (2 instead of the default 4). */
 void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int cps, int debug);
 
 /* Tuning aid: with debug bit 1 set, CTA (0, 0) of the streaming kernel stamps the device nanosecond timer at 14 points

@@ -697,9 +697,10 @@ __device__ __forceinline__ void stage_x8_any(int x_dtype, const void *__restrict
 }
 
 // DUAL: a second activation layout is staged for widths that pair ids at distance 4 (cheap for few tokens).
-template <int NT, bool DUAL>
-__global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kernel(const SmallMParams p) {
-    constexpr int NPIPE = pipes_for(NT);
+// NPIPE: pipes per CTA.  Four stream fastest; a two-pipe CTA is small enough (threads, registers, shared memory) for
+// the next kernel's CTA to sit beside it and run its prologue early (a tuning switch, see make_plan).
+template <int NT, bool DUAL, int NPIPE>
+__global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const SmallMParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ Control ctl;
     constexpr int RED_FLOATS = NW * 4 * NT * 32;                       // a pipe's hand-over buffer (>= 16 * M floats)
@@ -1201,7 +1202,7 @@ __global__ void __launch_bounds__(pipes_for(NT) * PIPE_THREADS, 1) small_m_kerne
 // host side
 
 struct Plan {
-    int ctas_x, S, nc_per, nc_total, MP, NT, nstg, cps, part_slots;
+    int ctas_x, S, nc_per, nc_total, MP, NT, nstg, cps, part_slots, npipe;
     int rs[6], slot_bytes;
     bool dual;
     size_t smem_bytes;
@@ -1224,14 +1225,20 @@ constexpr int64_t MAX_DYN_SMEM = 227 * 1024 - 1024;
 static_assert(sizeof(Control) <= 1024 - 64, "static shared memory allowance");
 
 // tuning hooks (qvb8_small_m_set_tuning): 0 = choose automatically
-static int g_fill_pct = 0, g_force_s = 0, g_force_nstg = 0, g_force_cps = 0, g_debug = 0;
+static int g_fill_pct = 0, g_force_s = 0, g_force_nstg = 0, g_force_cps = 0, g_debug = 0, g_force_pipes = 0;
 
 static Plan make_plan(int64_t M, int64_t Q, int64_t P, int max_width = 8) {
     Plan pl{};
     pl.nc_total = (int)(P / KC);
     pl.NT = (int)((M + 7) / 8);
     pl.MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * pl.NT;
-    const int npipe = pipes_for(pl.NT);                                 // one CTA per SM, npipe pipes in it
+    // one CTA per SM, npipe pipes in it.  Two-pipe CTAs (tuning switch) are small enough for the next launch's CTA to sit
+    // beside them: back-to-back launches of ONE small shape gain (6144 x 4096 11.5 -> 10.4 us, 4096 x 4096 8.7 -> 7.3 us),
+    // but in the layer sequence, where a small launch follows a large one, the whole stack loses (1.89 -> 2.07 ms per
+    // token), so four pipes stay the default.
+    int npipe = pipes_for(pl.NT);
+    if (pl.NT == 1 && npipe == 4 && g_force_pipes == 2) npipe = 2;
+    pl.npipe = npipe;
     const int64_t cta_bytes = MAX_DYN_SMEM - 256;                       // dynamic shared memory a CTA may take
     // chunks per stage: long stages mean few, large copies (what the copy engine and HBM like); short K -> short stages
     int cps = g_force_cps ? g_force_cps : (pl.nc_total >= 16 ? 8 : 4);
@@ -1297,9 +1304,9 @@ static bool fast_layout_ok(const qvb8_pack *w, const void *X) {
     return w->P > 0 && w->P % KC == 0 && aligned(w->ids, 16) && aligned(X, 16);
 }
 
-template <int NT, bool DUAL>
+template <int NT, bool DUAL, int NPIPE>
 static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
-    auto kern = small_m_kernel<NT, DUAL>;
+    auto kern = small_m_kernel<NT, DUAL, NPIPE>;
     static thread_local int granted_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1312,7 +1319,7 @@ static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, 
         return fail(QVB8_ERR_ARG, "qvb8_small_m: %zu bytes of shared memory needed (tuning out of range)", pl.smem_bytes);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(pl.ctas_x, pl.S);
-    cfg.blockDim = dim3(pipes_for(NT) * PIPE_THREADS);
+    cfg.blockDim = dim3(NPIPE * PIPE_THREADS);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -1326,12 +1333,14 @@ static int launch_one(const SmallMParams &prm, const Plan &pl, cudaStream_t st, 
 
 static int launch_nt(const SmallMParams &prm, const Plan &pl, cudaStream_t st, bool pdl) {
     switch (pl.NT) {
-        case 1: return pl.dual ? launch_one<1, true>(prm, pl, st, pdl) : launch_one<1, false>(prm, pl, st, pdl);
-        case 2: return launch_one<2, false>(prm, pl, st, pdl);
-        case 3: return launch_one<3, false>(prm, pl, st, pdl);
-        case 4: return launch_one<4, false>(prm, pl, st, pdl);
-        case 5: return launch_one<5, false>(prm, pl, st, pdl);
-        default: return launch_one<6, false>(prm, pl, st, pdl);
+        case 1:
+            if (pl.npipe == 2) return pl.dual ? launch_one<1, true, 2>(prm, pl, st, pdl) : launch_one<1, false, 2>(prm, pl, st, pdl);
+            return pl.dual ? launch_one<1, true, pipes_for(1)>(prm, pl, st, pdl) : launch_one<1, false, pipes_for(1)>(prm, pl, st, pdl);
+        case 2: return launch_one<2, false, pipes_for(2)>(prm, pl, st, pdl);
+        case 3: return launch_one<3, false, pipes_for(3)>(prm, pl, st, pdl);
+        case 4: return launch_one<4, false, pipes_for(4)>(prm, pl, st, pdl);
+        case 5: return launch_one<5, false, pipes_for(5)>(prm, pl, st, pdl);
+        default: return launch_one<6, false, pipes_for(6)>(prm, pl, st, pdl);
     }
 }
 
@@ -1342,7 +1351,8 @@ QV_API void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int cps
     qv::g_force_s = force_s > 0 ? force_s : 0;
     qv::g_force_nstg = (nstg >= 2 && nstg <= qv::MAX_STAGES) ? nstg : 0;
     qv::g_force_cps = (cps >= qv::NW && cps <= qv::MAX_CPS && cps % qv::NW == 0) ? cps : 0;
-    qv::g_debug = debug;
+    qv::g_debug = debug & 0xff;
+    qv::g_force_pipes = (debug >> 8) & 0xf;      // tuning: 2 pipes per CTA for up to 8 tokens instead of 4
 }
 
 QV_API int qvb8_debug_trace(unsigned long long *out32) {
