@@ -31,22 +31,40 @@ class PeerAllReduce:
         nbytes = int(L.qvb8_peer_bytes(self.world, self.cap))
         if nbytes <= 0:
             raise RuntimeError("qvb8_b200: bad world size / capacity for the peer all-reduce")
+        # Every step that can fail on one rank only is followed by an exchange of the outcome, so that all ranks raise
+        # together (a rank that left alone would leave the others waiting in the next collective).
         own = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
-        with torch.cuda.device(self.device):
-            _lib.check(L.qvb8_peer_alloc(nbytes, ctypes.byref(own), handle), "qvb8_peer_alloc")
+        err = None
+        try:
+            if self.device.type != "cuda" or not torch.cuda.is_available():
+                raise RuntimeError("the peer all-reduce needs a CUDA device")
+            with torch.cuda.device(self.device):
+                _lib.check(L.qvb8_peer_alloc(nbytes, ctypes.byref(own), handle), "qvb8_peer_alloc")
+        except RuntimeError as e:
+            err = str(e)
         handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        dist.all_gather_object(handles, None if err else bytes(handle.raw), group=group)
         self._ptrs = (ctypes.c_void_p * self.world)()
         self._own = own.value
+        if any(h is None for h in handles):
+            self._release(L)
+            raise RuntimeError(f"qvb8_b200: a rank could not allocate its exchange area ({err or 'another rank'})")
         with torch.cuda.device(self.device):
             for r in range(self.world):
                 if r == self.rank:
                     self._ptrs[r] = own.value
-                else:
-                    p = ctypes.c_void_p()
-                    _lib.check(L.qvb8_peer_open(handles[r], ctypes.byref(p)), "qvb8_peer_open")
-                    self._ptrs[r] = p.value
+                    continue
+                p = ctypes.c_void_p()
+                if L.qvb8_peer_open(handles[r], ctypes.byref(p)) != 0:
+                    err = L.qvb8_last_error().decode()
+                    break
+                self._ptrs[r] = p.value
+        outcomes = [None] * self.world
+        dist.all_gather_object(outcomes, err, group=group)
+        if any(o is not None for o in outcomes):
+            self._release(L)
+            raise RuntimeError(f"qvb8_b200: a rank could not map a peer's exchange area ({[o for o in outcomes if o][0]})")
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)                         # every area is zeroed and mapped before the first push
@@ -63,15 +81,20 @@ class PeerAllReduce:
                        "qvb8_peer_allreduce")
         return out
 
-    def close(self) -> None:
-        L = _lib.load()
+    def _release(self, L) -> None:
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            return
         with torch.cuda.device(self.device):
-            torch.cuda.synchronize(self.device)
             for r in range(self.world):
                 if self._ptrs[r] and r != self.rank:
                     L.qvb8_peer_close(self._ptrs[r], 0)
-                    self._ptrs[r] = None
-            self.dist.barrier(group=self.group)
+                self._ptrs[r] = None
             if self._own:
                 L.qvb8_peer_close(self._own, 1)
                 self._own = None
+
+    def close(self) -> None:
+        L = _lib.load()
+        torch.cuda.synchronize(self.device)
+        self.dist.barrier(group=self.group)              # nobody frees memory a peer may still write
+        self._release(L)

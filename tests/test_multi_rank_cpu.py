@@ -84,3 +84,30 @@ def test_row_subset_of_a_module_is_the_rows_of_the_whole():
              esc_idx_bf16=sub.esc_idx_bf16.numpy(), esc_vals_bf16=sub.esc_vals_bf16.numpy())
     want = oracle.qvb8_dense(pack_np(pk))[16:48]
     assert np.array_equal(oracle.qvb8_dense(d).view(np.uint32), want.view(np.uint32))
+
+
+def _peer_worker(rank: int, world: int, port: int, out_dir: str):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from qvb8_b200.peer import PeerAllReduce
+        outcome = "no error"
+        try:
+            PeerAllReduce(dist.group.WORLD, 1024, "cpu")
+        except RuntimeError as e:
+            outcome = "RuntimeError: " + str(e)[:60]
+        with open(os.path.join(out_dir, f"peer_{rank}.txt"), "w") as f:
+            f.write(outcome)
+        dist.barrier()                                   # still in step with the other rank after the failure
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_communicator_fails_on_all_ranks_together(tmp_path):
+    """Without a CUDA device no rank can allocate its exchange area: every rank must raise (none may be left waiting
+    in a collective), and the group stays usable afterwards."""
+    world = 2
+    mp.spawn(_peer_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / f"peer_{r}.txt").read_text().startswith("RuntimeError")
