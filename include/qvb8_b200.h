@@ -144,7 +144,7 @@ int qvb8_prefill(const qvb8_pack *w, const void *plan, const void *X, int x_dtyp
                  int64_t scratch_bytes, void *stream);
 /* Tuning aid for sweeps (results are wrong while it is set): 1 = no unpack arithmetic, 2 = no activation copies,
  * 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs, 48 = no MMAs and plain
- * barrier arrivals instead of commits; 0 = normal. */
+ * barrier arrivals instead of commits, 64 = polling waits in the MMA and copy threads; 0 = normal. */
 void qvb8_prefill_set_tuning(int debug);
 
 /* ---- all-reduce of the row-parallel projections' partial sums over NVLink peer memory ------------------------------

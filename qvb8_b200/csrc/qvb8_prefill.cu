@@ -91,6 +91,28 @@ __device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile 
     if (pf_try_wait(bar, parity)) return true;
     return pf_wait_slow(bar, parity, abort_flag, code, backoff_ns);
 }
+// Polling wait (tuning switch 64) for the single threads whose wake-up latency is on the critical path (MMA issue,
+// activation copies): mbarrier.test_wait never suspends the thread.  Bounded like pf_wait.  Measured slower than the
+// suspending wait (0.63 against 0.50 ms per call on 5120 x 17408 x 2048): the polling warps take issue slots.
+__device__ __noinline__ bool pf_wait_poll(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+    uint64_t t0 = 0;
+    for (int i = 0; i < (1 << 28); ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 255) == 255) {
+            if (*abort_flag) return false;
+            uint64_t t;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            if (t - t0 > 2000000000ull) break;
+        }
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_prefill_error, 0, code);
+    return false;
+}
 __device__ __forceinline__ void pf_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
@@ -122,7 +144,7 @@ struct PrefillParams {
     const float *sumx;         // (PF_KS, Mpad) partial sums of the narrowed activations
     float *Y;                  // (M, Q)
     int Q, P, M, Mpad;
-    int debug;                 // tuning aid: 1 = no unpack arithmetic, 2 = no activation copies, 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs, 48 = no MMAs and plain barrier arrivals instead of commits
+    int debug;                 // tuning aid: 1 = no unpack arithmetic, 2 = no activation copies, 4 = no weight fetch, 8 = no tensor-memory stores, 16 = no MMAs, 48 = no MMAs and plain barrier arrivals instead of commits, 64 = polling waits
 };
 
 // The output row of a slot of the plan's order, -1 for padding.
@@ -425,7 +447,7 @@ __global__ void __maxnreg__(PF_G == 2 ? 168 : PF_G == 3 ? 128 : 96) prefill_kern
             bool alive = true;
             for (int kb = 0; kb < nkb && alive; ++kb) {
                 const int s = kb % PF_NBS, u = kb / PF_NBS;
-                if (u > 0 && (s & 1) == 0) alive = pf_wait(pf_smem(&b_empty[s >> 1]), (u - 1) & 1, abort_flag, 24, 20);
+                if (u > 0 && (s & 1) == 0) alive = (p.debug & 64) ? pf_wait_poll(pf_smem(&b_empty[s >> 1]), (u - 1) & 1, abort_flag, 24) : pf_wait(pf_smem(&b_empty[s >> 1]), (u - 1) & 1, abort_flag, 24, 20);
                 if (!alive) break;
                 const uint32_t bar = pf_smem(&b_full[s]);
                 if (p.debug & 2) { pf_arrive(bar); continue; }
@@ -448,8 +470,8 @@ __global__ void __maxnreg__(PF_G == 2 ? 168 : PF_G == 3 ? 128 : 96) prefill_kern
             uint32_t bpar = 0;
             for (int kb = 0; kb < nkb && alive; ++kb) {
                 const int unit = kb >> 1, slot = unit & (PF_NU - 1);
-                if ((kb & 1) == 0) alive = pf_wait(pf_smem(&a_full[slot]), (uint32_t)(unit / PF_NU) & 1u, abort_flag, 25, 32);
-                if (alive) alive = pf_wait(pf_smem(&b_full[s]), bpar, abort_flag, 26, 32);
+                if ((kb & 1) == 0) alive = (p.debug & 64) ? pf_wait_poll(pf_smem(&a_full[slot]), (uint32_t)(unit / PF_NU) & 1u, abort_flag, 25) : pf_wait(pf_smem(&a_full[slot]), (uint32_t)(unit / PF_NU) & 1u, abort_flag, 25, 32);
+                if (alive) alive = (p.debug & 64) ? pf_wait_poll(pf_smem(&b_full[s]), bpar, abort_flag, 26) : pf_wait(pf_smem(&b_full[s]), bpar, abort_flag, 26, 32);
                 if (!alive) break;
                 if ((kb & 1) == 0) asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t a_t = tmem + 256u + (uint32_t)(slot * 64 + (kb & 1) * 32);
