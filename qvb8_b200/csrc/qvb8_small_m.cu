@@ -88,6 +88,10 @@ constexpr int ESC_CAP = 128;              // escape entries that travel with a d
 constexpr int SIDE_BYTES = DESC_SLOT + ESC_CAP * 8;
 constexpr int NSIDE = 3;                  // side slots per pipe: descriptors and escapes of the visits ahead
 
+// Bytes of a pipe's escape area: the finishing warp's corrections [16][M] and, for one token, a staging array of
+// (difference, activation) pairs of the tile's entries (see the finishing warp).
+__host__ __device__ constexpr int64_t corr_bytes(int64_t M) { return (16 * M * 4 + 127) / 128 * 128 + (M == 1 ? ESC_CAP * 8 : 0); }
+
 // Per-CTA control block in static shared memory.
 struct PipeControl {
     alignas(8) uint64_t full[MAX_STAGES];
@@ -727,7 +731,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     float *own = xch + XCH_SLOTS * xch_floats;                                 // [NPIPE][16][M]: an owner's own part of its shared tile
     const size_t shared_bytes = (size_t)(((XCH_SLOTS + NPIPE) * xch_floats * 4 + 127) / 128 * 128);
     const size_t pipe_bytes = (size_t)nstg * p.slot_bytes + (size_t)NSIDE * SIDE_BYTES + (size_t)RED_FLOATS * 4 +
-                              (size_t)((16 * M * 4 + 127) / 128 * 128);
+                              (size_t)corr_bytes(M);
     uint8_t *pbase = reinterpret_cast<uint8_t *>(zero16) + 128 + shared_bytes + (size_t)pipe * pipe_bytes;
     uint8_t *side = pbase + (size_t)nstg * p.slot_bytes;               // [NSIDE][SIDE_BYTES]
     float *red = reinterpret_cast<float *>(side + NSIDE * SIDE_BYTES); // [NW][4 * NT][32]
@@ -858,9 +862,17 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         const int g = lane >> 2, t = lane & 3;
         // per-token sums of the narrowed activations (fixed order: same bits every run); the pipes share the work
         bool alive = mbar_wait(smem_u32(&ctl.x_ready), 0, abort_flag, 5);      // every consumer warp has staged its part
-        for (int m = pipe; m < M; m += NPIPE) {
+        // Up to two tokens: every token's sum is cut into NPIPE column ranges so that all finishing warps share it
+        // (otherwise one of them would add up a whole row of activations alone while the others wait); sumx then
+        // holds the parts, [token][range], and the reader adds them in range order.  More tokens: one token per warp.
+        const bool split_sums = M <= 2;
+        const int nitems = split_sums ? M * NPIPE : M;
+        for (int it = pipe; it < nitems; it += NPIPE) {
+            const int m = split_sums ? it / NPIPE : it;
+            const int J = NC * 16;
+            const int j0 = split_sums ? (it % NPIPE) * (J / NPIPE) : 0, j1 = split_sums ? j0 + J / NPIPE : J;
             float sacc = 0.f;
-            for (int j = lane; j < NC * 16; j += 32) {
+            for (int j = j0 + lane; j < j1; j += 32) {
                 const uint4 v = *reinterpret_cast<const uint4 *>(xs_a + ((size_t)(j * MP + m) << 3));
                 const __half2 *hp = reinterpret_cast<const __half2 *>(&v);
 #pragma unroll
@@ -868,7 +880,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
-            if (lane == 0) ctl.sumx[m] = sacc;
+            if (lane == 0) ctl.sumx[it] = sacc;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctl.sums_ready));
@@ -908,7 +920,43 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 }
             }
             // ---- escapes: lane r sums row r's corrections x * (exact - band), in stored order, over the visit's columns
-            if (planned && alive) {
+            if (planned && alive && M == 1) {
+                // One token: the per-entry work (column test, activation fetch) is spread over all 32 lanes first; the
+                // row's sum then runs over (difference, activation) pairs in stored order with the same fused
+                // multiply-adds as below, so the result has the same bits.  This warp shares its scheduler with
+                // issue-bound consumer warps: a long serial loop here ends after the stream and delays the CTA's end.
+                const int clo = (kc0 + v.sb * cps) * KC, chi = (kc0 + min(v.se * cps, NC)) * KC, cbase = kc0 * KC;
+                float2 *pd = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(corr) + (16 * M * 4 + 127) / 128 * 128);
+                const int ne = min(d->nesc, ESC_CAP);
+                for (int e = lane; e < ne; e += 32) {
+                    const EscEntry en = ent[e];
+                    float2 r = make_float2(0.f, 0.f);
+                    if (en.col >= clo && en.col < chi) {
+                        const int cc = en.col - cbase;
+                        r = make_float2(en.delta, __half2float(xs_a[((size_t)slot_of(cc, 0, MP) << 3) + pos_a(cc & 7)]));
+                    }
+                    pd[e] = r;
+                }
+                __syncwarp();
+                if (lane < 16 && d->row[lane] >= 0) {
+                    const int ce0 = d->e0[lane], ce1 = d->e1[lane];
+                    const EscEntry *gent = p.esc_ent + d->esc0;
+                    float a = 0.f;
+                    for (int e = ce0; e < ce1; ++e) {
+                        if (e < ESC_CAP) {
+                            const float2 r = pd[e];
+                            a = __fmaf_rn(r.y, r.x, a);
+                        } else {
+                            const int col = __ldg(&gent[e].col);
+                            if (col >= clo && col < chi) {
+                                const int cc = col - cbase;
+                                a = __fmaf_rn(__half2float(xs_a[((size_t)slot_of(cc, 0, MP) << 3) + pos_a(cc & 7)]), __ldg(&gent[e].delta), a);
+                            }
+                        }
+                    }
+                    corr[lane * M] = a;
+                }
+            } else if (planned && alive) {
                 const int clo = (kc0 + v.sb * cps) * KC, chi = (kc0 + min(v.se * cps, NC)) * KC, cbase = kc0 * KC;
                 if (lane < 16 && d->row[lane] >= 0) {
                     const int ce0 = d->e0[lane], ce1 = d->e1[lane];
@@ -976,7 +1024,13 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                         if (myrow[hrow] >= 0 && m < M) {
                             if (cnb != 0) {
                                 val *= myts[hrow];
-                                if (v.sb == 0) val = __fmaf_rn(myms[hrow], ctl.sumx[m], val);
+                                if (v.sb == 0) {
+                                    float sx = ctl.sumx[split_sums ? m * NPIPE : m];
+                                    if (split_sums)
+#pragma unroll
+                                        for (int q = 1; q < NPIPE; ++q) sx += ctl.sumx[m * NPIPE + q];
+                                    val = __fmaf_rn(myms[hrow], sx, val);
+                                }
                             }
                             if (planned) val += corr[(g + 8 * hrow) * M + m];
                         }
@@ -1246,7 +1300,7 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P, int max_width = 8) {
     if (cps < NW) cps = NW;
     if (cps > MAX_CPS) cps = MAX_CPS;
     // per pipe next to its ring: side ring, hand-over buffer, escape corrections
-    const int64_t pipe_fixed = (int64_t)NSIDE * SIDE_BYTES + (int64_t)NW * 4 * pl.NT * 32 * 4 + (16 * M * 4 + 127) / 128 * 128;
+    const int64_t pipe_fixed = (int64_t)NSIDE * SIDE_BYTES + (int64_t)NW * 4 * pl.NT * 32 * 4 + corr_bytes(M);
     const int64_t shared_fixed = 128 + ((XCH_SLOTS + npipe) * 16 * M * 4 + 127) / 128 * 128;      // zeros, exchange buffers
     for (;; cps -= NW) {                                                // the longest stage of which two fit per pipe
         pl.cps = cps;
