@@ -67,3 +67,57 @@ def concat_packs(members: list[QVB8Pack]) -> tuple[QVB8Pack, list[int]]:
 
 # (group name, member names) of a decoder layer whose members are fed the same tensor
 SAME_INPUT_GROUPS = (("qkv", ("q", "k", "v")), ("gate_up", ("gate", "up")))
+
+
+def concat_qvb8r(members: list[dict]) -> tuple[dict, list[int]]:
+    """Same-input fusion for the entropy-coded format (reference formats/qvb8r/fuse.py:18-119): the members' parsed
+    ``.qvb8r`` dicts become ONE dict with the same keys.  Tiles keep their streams and states; only the bookkeeping
+    is shifted: a member's classes follow the previous members' classes (frequency tables stacked, padded to the
+    widest alphabet), its sorted rows and output rows follow theirs (`tiles[:, 1]`, `perm`, escape indices), its word
+    offsets follow their words.  Every kernel path and :class:`qvb8_b200.linear_r.QVBandLinearV8R` run unchanged on
+    the result; a row's symbols, band and escapes are the same bytes, so the output is the members' outputs side by
+    side.  Returns (dict, row split points)."""
+    import numpy as np
+    if not members:
+        raise ValueError("concat_qvb8r: no members")
+    P = int(members[0]["P"])
+    if any(int(m["P"]) != P for m in members):
+        raise ValueError("concat_qvb8r: members must share P (they read the same activation)")
+    N = max(int(np.asarray(m["freq"]).shape[1]) for m in members)
+    out = {k: [] for k in ("perm", "freq", "tiles", "tile_off", "states", "words", "drow", "min_s", "tau_s",
+                           "esc_idx", "esc_val", "esc_delta")}
+    q0 = k0 = w0 = 0
+    for m in members:
+        Q = int(m["Q"])
+        f = np.asarray(m["freq"])
+        out["freq"].append(np.pad(f, ((0, 0), (0, N - f.shape[1]))))
+        t = np.asarray(m["tiles"], np.int64).reshape(-1, 3).copy()
+        t[:, 0] += k0
+        t[:, 1] += q0
+        out["tiles"].append(t)
+        off = np.asarray(m["tile_off"], np.int64)
+        out["tile_off"].append(off[:-1] + w0)
+        out["states"].append(np.asarray(m["states"], np.uint64).reshape(-1, 32))
+        out["words"].append(np.asarray(m["words"], np.uint32))
+        out["perm"].append(np.asarray(m["perm"], np.int64) + q0)
+        for k in ("drow", "min_s", "tau_s", "esc_val", "esc_delta"):
+            out[k].append(np.asarray(m[k]))
+        out["esc_idx"].append(np.asarray(m["esc_idx"], np.int64) + q0 * P)
+        q0 += Q
+        k0 += f.shape[0]
+        w0 += int(off[-1])
+    cat = lambda k, dt: np.concatenate(out[k]).astype(dt)
+    first = members[0]
+    fused = dict(
+        Q=q0, P=P, K=k0, N=N, T=max(int(m["T"]) for m in members),
+        perm=cat("perm", np.int32), freq=cat("freq", np.asarray(first["freq"]).dtype), tiles=cat("tiles", np.int32),
+        tile_off=np.concatenate(out["tile_off"] + [np.asarray([w0], np.int64)]).astype(np.asarray(first["tile_off"]).dtype),
+        states=cat("states", np.uint64), words=cat("words", np.uint32), drow=cat("drow", np.asarray(first["drow"]).dtype),
+        min_s=cat("min_s", np.float32), tau_s=cat("tau_s", np.float32), esc_idx=cat("esc_idx", np.int64),
+        esc_val=cat("esc_val", np.float32), esc_delta=cat("esc_delta", np.float32),
+        tau=max(float(m.get("tau", 0.0)) for m in members), max_err=max(float(m.get("max_err", 0.0)) for m in members))
+    splits, acc = [], 0
+    for m in members[:-1]:
+        acc += int(m["Q"])
+        splits.append(acc)
+    return fused, splits

@@ -168,3 +168,39 @@ def test_linear_module_forward(cuda_lib, M, chunk_rows):
     assert errf < 1e-3, errf                             # fp16 weight rounding above 8 rows
     Wd = mod.dense(torch.float32)
     assert np.array_equal(Wd.cpu().numpy().view(np.uint32), _dense(d).view(np.uint32))
+
+
+def test_same_input_fusion_is_the_members_side_by_side():
+    """concat_qvb8r: the fused dict restores to the members' weights stacked, bit for bit (oracle decoder, CPU)."""
+    from qvb8_b200 import fuse
+    _, a = _pack(48, 256, seed=41, K=2, T=4)
+    _, b = _pack(80, 256, seed=42, K=3, T=2)
+    _, c = _pack(16, 256, seed=43, K=2, T=8)
+    fused, splits = fuse.concat_qvb8r([a, b, c])
+    assert splits == [48, 128] and fused["Q"] == 144 and fused["K"] == 7
+    want = np.vstack([_dense(a), _dense(b), _dense(c)])
+    assert np.array_equal(_dense(fused).view(np.uint32), want.view(np.uint32))
+    blob = packs.write_qvb8r(fused, Q=fused["Q"], P=fused["P"], min_s=fused["min_s"], tau_s=fused["tau_s"],
+                             esc_idx=fused["esc_idx"], esc_val=fused["esc_val"], esc_delta=fused["esc_delta"],
+                             cert=dict(tau=fused["tau"], max_err=fused["max_err"]))
+    assert np.array_equal(_dense(packs.read_qvb8r(blob)).view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 6, 14, 70])
+def test_same_input_fusion_module(cuda_lib, M):
+    """One module over the fused dict gives the members' module outputs side by side."""
+    from qvb8_b200 import fuse
+    from qvb8_b200.linear_r import QVBandLinearV8R
+    P = 512
+    ds = [_pack(Q, P, seed=50 + i, K=2, T=2)[1] for i, Q in enumerate((64, 32, 96))]
+    fused, splits = fuse.concat_qvb8r(ds)
+    X = synth.synth_activation(M, P, seed=M, device=DEV, dtype=torch.bfloat16)
+    y = QVBandLinearV8R(fused, device=DEV)(X).float()
+    parts = [QVBandLinearV8R(d, device=DEV)(X).float() for d in ds]
+    got = torch.tensor_split(y, splits, dim=-1)
+    for g, w in zip(got, parts):
+        if M <= 16:
+            assert torch.equal(g, w)                     # the same kernels on the same bytes
+        else:
+            assert torch.allclose(g, w, rtol=2e-2, atol=2e-2)        # library GEMM: the tile shape may differ
