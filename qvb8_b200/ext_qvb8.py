@@ -14,11 +14,17 @@ certified weight.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import lib as _lib
 
 _SMALL_M_MAX = 48
+# Many rows (M > 48): "fused" = the tcgen05 kernel that restores the weights inside the product; "dense" = restore to
+# fp16 once and run a library GEMM, the reference's own route (qvb8_cuda.cu:1542-1671), today still the faster of the
+# two for thousands of rows.  Set QVB8_PREFILL=dense to take it.
+PREFILL_PATH = os.environ.get("QVB8_PREFILL", "fused")
 
 
 def _pack(ids, min_s, row_nbits, row_bit_off, P, tau_s, esc_idx, esc_vals):
@@ -135,8 +141,8 @@ class Qvb8Ext:
         if M <= _SMALL_M_MAX:
             y = _small_m(ids, pk, keep, X)
             return y.to(torch.float16) if (out_half and M > 8) else y
-        if int(P) % 64 == 0:
-            # prefill: the ids are unpacked into shared memory and contracted by tcgen05.mma, no dense copy of W
+        if int(P) % 64 == 0 and PREFILL_PATH == "fused":
+            # prefill: the ids are unpacked into tensor memory and contracted by tcgen05.mma, no dense copy of W
             plan = _existing_or_new_plan(ids, pk, keep)
             if plan is not None:
                 y = _lib.prefill(pk, keep, X, plan)
