@@ -1295,7 +1295,9 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P, int max_width = 8) {
     pl.npipe = npipe;
     const int64_t cta_bytes = MAX_DYN_SMEM - 256;                       // dynamic shared memory a CTA may take
     // chunks per stage: long stages mean few, large copies (what the copy engine and HBM like); short K -> short stages
-    int cps = g_force_cps ? g_force_cps : (pl.nc_total >= 16 ? 8 : 4);
+    // (measured for 8 and 16 tokens: short stages win by 16 - 25 % on launches of 10240 rows and more -- more ring
+    // slots next to the large staged activations -- and lose 4 - 8 % on 4096 .. 6144 rows; up to 5 tokens long stages win)
+    int cps = g_force_cps ? g_force_cps : (pl.nc_total >= 16 && !(M >= 8 && Q >= 8192) ? 8 : 4);
     cps = cps / NW * NW;
     if (cps < NW) cps = NW;
     if (cps > MAX_CPS) cps = MAX_CPS;
