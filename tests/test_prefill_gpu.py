@@ -50,3 +50,23 @@ def test_prefill_dtypes_and_determinism(cuda_lib):
     b, _ = _run(pk, 200, torch.bfloat16, seed=4)
     assert torch.equal(a, b)
     assert lib.device_status() == 0
+
+
+def test_prefill_full_size_agrees_with_the_streaming_kernel(cuda_lib):
+    """27B-class down projection, 2048 tokens: too large for the oracle, so the tcgen05 kernel is checked against the
+    streaming kernel (itself oracle-checked at small sizes) on sampled tokens, and on size-independent properties:
+    zero activations give exactly zero, and f(2x) = 2 f(x) exactly (a power of two passes through every rounding)."""
+    Q, P, M = 5120, 17408, 2048
+    pk = synth.encode_qvb8(synth.synth_weight(Q, P, 77, device=DEV), tau=2e-3)
+    st, keep = lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx, pk.esc_vals)
+    plan = lib.build_plan(st, keep)
+    X = synth.synth_activation(M, P, seed=5, device=DEV, dtype=torch.float16)
+    X[X.abs() < 1e-3] = 0                                 # keep 2x exact: no fp16 subnormals
+    Y = lib.prefill(st, keep, X, plan=plan)
+    rows = torch.tensor([0, 1, 255, 256, 1000, 1535, 2046, 2047], device=DEV)
+    Ys = lib.small_m(st, keep, X[rows].contiguous(), plan=plan)
+    err = float((Y[rows] - Ys).norm() / Ys.norm())
+    assert err < TIGHT, err
+    assert torch.count_nonzero(lib.prefill(st, keep, torch.zeros_like(X), plan=plan)) == 0
+    assert torch.equal(lib.prefill(st, keep, X * 2, plan=plan), Y * 2)
+    assert lib.device_status() == 0
