@@ -99,3 +99,27 @@ def test_moe_config_shape_and_bad_index(cuda_lib):
     assert L.qvb8_moe_bad_index(scratch.data_ptr(), M, topk, E, u["P"], u["Q"], d["Q"], 0, ctypes.byref(flag)) == 0
     assert flag.value == 1
     assert lib.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_moe_full_size_properties(cuda_lib):
+    """The 35B-A3B-class layer at its full size (128 experts, top-8, d_model 2048, expert FFN 768, 32 tokens): too
+    large for the oracle, so size-independent properties are checked: doubling the routing weights doubles the result
+    exactly; reordering the tokens reorders the rows bit for bit; a token computed alone agrees with its row."""
+    E, topk, d, f, M = 128, 8, 2048, 768, 32
+    ups = [synth.encode_qvb8(synth.synth_weight(2 * f, d, 4000 + e, device=DEV), tau=1e-3, policy="inband") for e in range(E)]
+    dns = [synth.encode_qvb8(synth.synth_weight(d, f, 5000 + e, device=DEV), tau=1e-3, policy="inband") for e in range(E)]
+    mod = experts.QVBandExpertsV8(ups, dns, num_experts=E)
+    idx, w = _routing(M, E, topk, seed=3)
+    idx, w = idx.to(DEV), w.to(DEV)
+    X = synth.synth_activation(M, d, seed=9, device=DEV, dtype=torch.float32)
+    out = mod(X, idx, w)
+    assert out.shape == (M, d) and bool(torch.isfinite(out).all())
+    assert torch.equal(mod(X, idx, w * 2), out * 2)
+    perm = torch.randperm(M, generator=torch.Generator().manual_seed(1)).to(DEV)
+    assert torch.equal(mod(X[perm].contiguous(), idx[perm].contiguous(), w[perm].contiguous()), out[perm])
+    for t in (0, 17, 31):
+        one = mod(X[t:t + 1].contiguous(), idx[t:t + 1].contiguous(), w[t:t + 1].contiguous())
+        assert rel_fro(one.cpu().numpy(), out[t:t + 1].cpu().numpy()) < TIGHT
+    from qvb8_b200 import lib
+    assert lib.device_status() == 0
