@@ -16,19 +16,19 @@
 //   main     a CTA owns 128 output rows (in the plan's width-sorted order) and 256 tokens; K advances in blocks of 64
 //            columns.  The weights reach the tensor cores through TENSOR MEMORY (tcgen05.mma with the A operand in
 //            tensor memory), so shared memory carries only the activations and the packed ids:
-//              warps 0..7  unpack.  A thread owns one row; warps 0..3 take the first pair of K blocks of every four,
-//                          warps 4..7 the second.  A warp fetches its own 32 rows x 128 ids with 16-byte cp.async
-//                          (eight lanes per row: whole lines, not one line per lane) into a private double buffer
-//                          whose row stride is an odd multiple of 16 bytes, one pair ahead; then every thread reads
-//                          its row (nb 16-byte vectors), turns pairs of ids into fp16 integers with shift / mask /
-//                          or 0x6400 / subtract 1024, and stores 64 registers with tcgen05.st into its lane of one of
-//                          four 64-column weight slots
-//              warp 8      one thread: one 32 KB bulk copy per K block for the activations (four stages)
-//              warp 9      one thread: waits for a weight slot and an activation stage, issues four tcgen05.mma
-//                          (128 x 256 x 16, accumulator in columns 0..255) per K block and commits them to the
-//                          barriers that free the stage and the slot
-//            At the end the eight unpack warps read the accumulator with tcgen05.ld, apply tau_s, min_s * sum(x) and
-//            write Y.
+//              unpack warps (PF_G groups of four; three by default).  A thread owns one row = one lane of tensor
+//                          memory; group g takes the pairs of K blocks g, g + PF_G, ...  A warp fetches its own 32
+//                          rows x 128 ids with 16-byte cp.async (eight lanes per row: whole lines, not one line per
+//                          lane) into a private buffer whose row stride is an odd multiple of 16 bytes; then every
+//                          thread reads its row (nb 16-byte vectors), turns pairs of ids into fp16 integers (one
+//                          window, mask | 0x6400.., one HFMA2 for 6..8 bits) and stores 2 x 32 registers with
+//                          tcgen05.st into its lane of one of four 64-column weight slots
+//              copy warp   one thread: one 32 KB bulk copy per K block for the activations (four stages, freed in pairs)
+//              MMA warp    one thread: waits for a weight slot and an activation stage, issues four tcgen05.mma
+//                          (128 x 256 x 16, accumulator in columns 0..255) per K block and, per pair of K blocks,
+//                          commits them to the barriers that free the two stages and the slot
+//            At the end eight of the unpack warps read the accumulator with tcgen05.ld, apply tau_s, min_s * sum(x)
+//            and write Y.
 //   wide, escapes   the corrections described above
 //
 // Waits are bounded: a wait that runs out raises an abort flag and the error word, everybody falls through, copies in
