@@ -127,6 +127,9 @@ int qvb8_debug_trace(unsigned long long *out32);
  * activation stage never freed, weights / activations of a K block never arrived, accumulator never completed;
  * 31 = a peer's flag of an all-reduce never arrived).  Synchronises the host. */
 int qvb8_device_status(int *status);
+/* Clears code 31 (a late or absent peer is an event a caller may recover from: the all-reduce kernel returned and the
+ * context is intact).  Codes of the other kernels mean a defect and are not cleared.  Synchronises the host. */
+int qvb8_device_status_reset(void);
 
 /* Same product through the layout-agnostic kernel (any P, any id alignment, widths 1..14).  The library falls
  * back to it by itself when qvb8_small_m's layout preconditions do not hold; exported for tests. */
@@ -162,6 +165,16 @@ int qvb8_peer_open(const unsigned char handle[64], void **ptr);
 int qvb8_peer_close(void *ptr, int own);
 int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
                         float *out, int64_t n, int flags, void *stream);
+/* The same with the wait limit as a parameter: wait_ns nanoseconds for the peers' flags (0 = the default two seconds),
+ * after which the kernel raises status word 31, sums what it has and returns.  A failure detector uses a short limit. */
+int qvb8_peer_allreduce_ex(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
+                           float *out, int64_t n, int flags, uint64_t wait_ns, void *stream);
+/* Every rank of a world on ONE device in one cooperative launch, block r acting as rank r (no counterpart in the
+ * reference): bases[r] / epochs[r] / partials[r] / outs[r] are rank r's exchange area, epoch counter, input and output,
+ * all in this device's memory.  For machines with fewer GPUs than ranks: separate launches that wait on one another
+ * carry no guarantee of running together, the blocks of a cooperative launch do. */
+int qvb8_peer_allreduce_local(void *const *bases, int world, int64_t cap_floats, void *const *epochs,
+                              const float *const *partials, float *const *outs, int64_t n, uint64_t wait_ns, void *stream);
 
 /* ---- mixture-of-experts MLP over stacked expert packs -------------------------------------------------------------
  * Stacked layout of one projection of all E experts (reference formats/qvb8/backends_experts.py:144-196): every
@@ -184,8 +197,9 @@ typedef struct qvb8_expert_stack {
  * X (M, up->P) of x_dtype is narrowed to saturated fp16 first; idx int64 (M, topk); w fp32 (M, topk);
  * out (M, dn->Q) of x_dtype.  Every distinct selected expert is streamed once for all the tokens that chose it.
  * scratch: qvb8_moe_scratch_bytes(M, topk, E, up->P, up->Q, dn->Q, act) bytes, 256-byte aligned, contents don't matter.
- * An expert index outside [0, E) never causes an out-of-range access; it leaves that token's output undefined and
- * is reported by qvb8_moe_bad_index (which synchronises). */
+ * A (token, expert) pair whose expert index lies outside [0, E), or whose token names the same expert more than M
+ * times, never causes an out-of-range access: the pair contributes ZERO to out[t] (the result stays defined) and is
+ * reported by qvb8_moe_bad_index (which synchronises). */
 int64_t qvb8_moe_scratch_bytes(int64_t M, int64_t topk, int64_t E, int64_t Pup, int64_t Qup, int64_t Qdn, int act);
 int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t *idx, const float *w, int64_t topk, int64_t E,
                      const qvb8_expert_stack *up, const qvb8_expert_stack *dn, int act, void *out, void *scratch,
@@ -233,10 +247,10 @@ int qvb8r_fix_escapes(const float *X, const int64_t *uq, const int64_t *ptr, con
  * allocator.  The partial results and tile tickets go to a fixed array inside the loaded module
  * (qvb8_small_m_static_max_scratch() bytes: 4 MiB); a product that needs more (qvb8_small_m_scratch_bytes) is
  * refused with QVB8_ERR_SCRATCH and nothing is launched.
- *   - The first call on each device looks the array up and clears its ticket area with that device current (a
- *     synchronous step): make it before any stream capture that uses this entry point.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current): make that first call before any stream capture that uses this entry point.
  *   - The array is shared by every call on the device and keeps its last contents; only the ticket area must be zero
- *     on entry, and every call leaves it zero.
+ *     on entry: it is zero when the module is loaded and every call leaves it zero again.
  *   - Two calls that overlap on the device (different streams) race on the array: serialise them. */
 int64_t qvb8_small_m_static_max_scratch(void);
 int qvb8_small_m_static(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int x_mode, int64_t M,

@@ -7,11 +7,14 @@
  * smoke check and the CPU-baseline leg of the benchmark load this library.
  *
  * Parity pin: the reference ships no tests, fixtures or known-answer vectors
- * for this path.  The oracle is pinned instead against the reference's own
- * Python decoders (formats/qvb8/decode.py, pack_container.py) and its C++ rANS
- * walker (formats/qvb8r/backends/cuda_qvb8r/qvb8r_cpu.cpp) run on seeded
- * packs; the outputs of those runs are committed as golden fixtures together
- * with the script that produced them.
+ * for this path.  The oracle is pinned instead against outputs of the
+ * reference's own code run on seeded packs and committed as golden fixtures
+ * together with the scripts that produced them: for QVB8 its Python decoders
+ * (formats/qvb8/decode.py, pack_container.py; tests/golden/make_golden.py),
+ * for QVB8R files written by its container.py from streams coded by its C++
+ * encode and decoded by its C++ embed_rows
+ * (formats/qvb8r/backends/cuda_qvb8r/qvb8r_cpu.cpp;
+ * tests/golden/make_golden_qvb8r.py).
  *
  * Every function cites the reference lines it follows (paths are relative to
  * the reference project root, under src/qv_band/).
@@ -258,40 +261,50 @@ ORACLE_API void qvb8o_sat_half(const float *in, int64_t n, float *out)
  *   perm     (Q) int32 sorted row -> original row
  *   drow     (Q) int32 by original row
  * Returns 0, or -1 if a tile would read past n_words. */
+/* one decoding step of a lane: looks the state's low 12 bits up in the class's slot table, returns the symbol and
+ * advances the state to freq * (state >> 12) + offset_in_symbol (qvb8r_cpu.cpp:41-43; entry layout codec.py:19) */
+static inline int rans_step(const uint32_t *slot, uint64_t *state)
+{
+    const uint32_t entry = slot[*state & 4095u];
+    const uint64_t freq = (uint64_t)(entry >> 22) + 1u, within = (entry >> 11) & 2047u;
+    *state = freq * (*state >> 12) + within;
+    return (int)(entry & 2047u);
+}
+
 ORACLE_API int qvb8ro_decode_ids(const uint32_t *words, int64_t n_words, const int64_t *tile_off,
                                  const uint64_t *states, const int64_t *tiles, int64_t nt,
                                  const uint32_t *tab, const int32_t *perm, const int32_t *drow, int64_t P,
                                  int16_t *ids)
 {
-    const int64_t S = P / 32;
-    int bad = 0;
+    const int64_t pairs = P / 64;            /* a lane decodes two symbols (columns 64 k + lane, 64 k + 32 + lane) per visit */
+    int overrun = 0;
 #pragma omp parallel for schedule(dynamic, 4)
     for (int64_t t = 0; t < nt; ++t) {
-        const uint32_t *tb = tab + tiles[3 * t] * 4096;
-        const int64_t r0 = tiles[3 * t + 1], nr = tiles[3 * t + 2];
-        uint64_t x[32];
-        for (int j = 0; j < 32; ++j) x[j] = states[t * 32 + j];
-        int64_t ptr = tile_off[t];
-        for (int64_t r = 0; r < nr; ++r) {
-            const int32_t orow = perm[r0 + r];
-            const int dr = drow[orow];
-            int16_t *o = ids + (int64_t)orow * P;
-            for (int64_t s0 = 0; s0 < S; s0 += 2) {
-                for (int j = 0; j < 32; ++j) {
-                    for (int h = 0; h < 2; ++h) {
-                        const uint32_t E = tb[x[j] & 4095u];
-                        x[j] = (uint64_t)((E >> 22) + 1u) * (x[j] >> 12) + ((E >> 11) & 2047u);
-                        o[(s0 + h) * 32 + j] = (int16_t)((int)(E & 2047u) + dr);
+        const uint32_t *slot = tab + tiles[3 * t] * 4096;
+        const int64_t first = tiles[3 * t + 1], rows = tiles[3 * t + 2];
+        uint64_t lane_state[32];
+        memcpy(lane_state, states + t * 32, sizeof lane_state);
+        int64_t next_word = tile_off[t];
+        for (int64_t r = 0; r < rows; ++r) {
+            const int32_t q = perm[first + r];
+            int16_t *row = ids + (int64_t)q * P;
+            for (int64_t k = 0; k < pairs; ++k) {
+                for (int lane = 0; lane < 32; ++lane) {          /* ascending lanes: the order words are handed out in */
+                    uint64_t st = lane_state[lane];
+                    row[64 * k + lane] = (int16_t)(rans_step(slot, &st) + drow[q]);
+                    row[64 * k + 32 + lane] = (int16_t)(rans_step(slot, &st) + drow[q]);
+                    if (st < (1ull << 32)) {                      /* renormalise: take the tile's next 32-bit word */
+                        uint32_t w = 0;
+                        if (next_word < n_words) w = words[next_word++];
+                        else overrun = 1;
+                        st = (st << 32) | w;
                     }
-                    if (x[j] < (1ull << 32)) {
-                        if (ptr >= n_words) { bad = 1; x[j] <<= 32; }
-                        else x[j] = (x[j] << 32) | words[ptr++];
-                    }
+                    lane_state[lane] = st;
                 }
             }
         }
     }
-    return bad ? -1 : 0;
+    return overrun ? -1 : 0;
 }
 
 /* Band value of signed ids (QVB8R ids can be offset by drow): the GPU kernels

@@ -25,7 +25,10 @@ struct MoeRoute {                          // device tables built by the route k
     int *lists;                            // [E][M] their pair numbers p = t * topk + j, ascending
     int *slots;                            // [min(E, npairs)] the distinct chosen experts, ascending
     int *nslots;                           // [1]
-    int *bad;                              // [1] set when an expert index is out of range
+    int *bad;                              // [1] set when a pair could not be listed (see valid)
+    int *valid;                            // [npairs] 1 = the pair is in its expert's list; 0 = its expert index is outside
+                                           // [0, E), or the token named one expert more than M times: the pair's rows
+                                           // are never computed and the combine step counts them as zero
 };
 
 // Block 0: thread e scans the pairs for expert e (at most a few hundred pairs): deterministic, no atomics.
@@ -49,11 +52,16 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const int64_t *__restric
     for (int p = threadIdx.x; p < npairs; p += blockDim.x) {
         const int64_t e = idx[p];
         if (e < 0 || e >= E) any_bad = 1;
+        r.valid[p] = 0;
     }
+    __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int c = 0;
         for (int p = 0; p < npairs; ++p)
-            if (idx[p] == e && c < M) r.lists[(size_t)e * M + c++] = p;
+            if (idx[p] == e) {
+                if (c < M) { r.lists[(size_t)e * M + c++] = p; r.valid[p] = 1; }
+                else any_bad = 1;
+            }
         r.counts[e] = c;
     }
     __syncthreads();
@@ -216,16 +224,18 @@ __global__ void __launch_bounds__(MOE_WARPS * 32, 4) moe_rows_kernel(const MoeRo
 // out[t, d] = sum_j w[t, j] * Yd[t * topk + j, d], j ascending (qvb8_cuda.cu:936-947)
 template <typename OutT>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ Yd, const float *__restrict__ w,
-                                                          OutT *__restrict__ out, int topk, int D, int M) {
+                                                          OutT *__restrict__ out, int topk, int D, int M,
+                                                          const int *__restrict__ valid) {
     const int t = blockIdx.y, d = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= M || d >= D) return;
     float a = 0.f;
-    for (int j = 0; j < topk; ++j) a = __fmaf_rn(__ldg(w + t * topk + j), Yd[((size_t)t * topk + j) * D + d], a);
+    for (int j = 0; j < topk; ++j)                                      // a pair that was never computed counts as zero
+        if (valid[t * topk + j]) a = __fmaf_rn(__ldg(w + t * topk + j), Yd[((size_t)t * topk + j) * D + d], a);
     out[(size_t)t * D + d] = narrow<OutT>(a);
 }
 
 struct MoeScratch {
-    int64_t counts, lists, slots, nslots, bad, Xf, H, Yd, total;
+    int64_t counts, lists, slots, nslots, bad, valid, Xf, H, Yd, total;
 };
 static MoeScratch moe_scratch(int64_t M, int64_t topk, int64_t E, int64_t Pup, int64_t R_up, int64_t Qdn) {
     MoeScratch s{};
@@ -236,7 +246,8 @@ static MoeScratch moe_scratch(int64_t M, int64_t topk, int64_t E, int64_t Pup, i
     s.slots = s.lists + up(E * M * 4);
     s.nslots = s.slots + up(E * 4);
     s.bad = s.nslots + 256;
-    s.Xf = s.bad + 256;
+    s.valid = s.bad + 256;
+    s.Xf = s.valid + up(npairs * 4);
     s.H = s.Xf + up(M * Pup * 4);
     s.Yd = s.H + up(npairs * R_up * 4);
     s.total = s.Yd + up(npairs * Qdn * 4);
@@ -282,7 +293,7 @@ QV_API int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t
     uint8_t *base = reinterpret_cast<uint8_t *>(scratch);
     MoeRoute route{reinterpret_cast<int *>(base + L.counts), reinterpret_cast<int *>(base + L.lists),
                    reinterpret_cast<int *>(base + L.slots), reinterpret_cast<int *>(base + L.nslots),
-                   reinterpret_cast<int *>(base + L.bad)};
+                   reinterpret_cast<int *>(base + L.bad), reinterpret_cast<int *>(base + L.valid)};
     const int npairs = (int)(M * topk);
     float *Xf = reinterpret_cast<float *>(base + L.Xf);
     const int64_t nx = M * up->P;
@@ -309,16 +320,17 @@ QV_API int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t
     if (int rc = cuda_status("qvb8_moe down")) return rc;
     const dim3 gc((unsigned)((dn->Q + 255) / 256), (unsigned)M);
     if (x_dtype == QVB8_BF16)
-        moe_combine_kernel<__nv_bfloat16><<<gc, 256, 0, st>>>(Yd, w, reinterpret_cast<__nv_bfloat16 *>(out), (int)topk, (int)dn->Q, (int)M);
+        moe_combine_kernel<__nv_bfloat16><<<gc, 256, 0, st>>>(Yd, w, reinterpret_cast<__nv_bfloat16 *>(out), (int)topk, (int)dn->Q, (int)M, route.valid);
     else if (x_dtype == QVB8_F16)
-        moe_combine_kernel<__half><<<gc, 256, 0, st>>>(Yd, w, reinterpret_cast<__half *>(out), (int)topk, (int)dn->Q, (int)M);
+        moe_combine_kernel<__half><<<gc, 256, 0, st>>>(Yd, w, reinterpret_cast<__half *>(out), (int)topk, (int)dn->Q, (int)M, route.valid);
     else
-        moe_combine_kernel<float><<<gc, 256, 0, st>>>(Yd, w, reinterpret_cast<float *>(out), (int)topk, (int)dn->Q, (int)M);
+        moe_combine_kernel<float><<<gc, 256, 0, st>>>(Yd, w, reinterpret_cast<float *>(out), (int)topk, (int)dn->Q, (int)M, route.valid);
     return cuda_status("qvb8_moe combine");
 }
 
 // Expert index check of the last qvb8_moe_experts call that used `scratch` (after the stream has run it):
-// 1 if an index was outside [0, E).  Synchronises the host.
+// 1 if a pair was left out (its expert index outside [0, E), or its token named one expert more than M times); such a
+// pair contributes zero to the output.  Synchronises the host.
 QV_API int qvb8_moe_bad_index(const void *scratch, int64_t M, int64_t topk, int64_t E, int64_t Pup, int64_t Qup, int64_t Qdn,
                               int act, int *bad) {
     using namespace qv;

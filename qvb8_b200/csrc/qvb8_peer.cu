@@ -41,20 +41,19 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
 }
 
-// One block.  n floats (a multiple of 4), n <= cap.
-__global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const PeerParams p, const float *__restrict__ partial,
-                                                                      float *__restrict__ out, int n) {
+// One block per rank.  n floats (a multiple of 4), n <= cap.  `partial` and `out` may be the same buffer (every thread
+// reads the elements it later writes), so neither is declared restrict.  wait_ns: how long the wait for the peers'
+// flags may last before it gives up (error word 31); the time limit is what bounds the wait, the iteration cap only
+// guards against a timer that does not advance.
+__device__ __forceinline__ void peer_allreduce_body(const PeerParams &p, int rank, uint32_t *epoch_ctr, const float *partial,
+                                                    float *out, int n, uint64_t wait_ns) {
     __shared__ uint32_t s_epoch;
     const int tid = threadIdx.x;
-    // programmatic dependent launch: the next kernel may begin its prologue now (it waits for this grid's completion
-    // before it reads anything this grid writes); this grid waits for its predecessor before it reads `partial`
-    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    if (tid == 0) s_epoch = *p.epoch + 1u;
+    if (tid == 0) s_epoch = *epoch_ctr + 1u;
     __syncthreads();
     const uint32_t epoch = s_epoch;
     const int b = (int)(epoch & 1u);
-    const int64_t slot = ((int64_t)b * p.world + p.rank) * p.cap;
+    const int64_t slot = ((int64_t)b * p.world + rank) * p.cap;
     // 1. push: this rank's partial sums into slot [b][rank] of every rank (its own included)
     const float4 *src = reinterpret_cast<const float4 *>(partial);
     for (int r = 0; r < p.world; ++r) {
@@ -64,25 +63,25 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const Peer
     __threadfence_system();
     __syncthreads();
     // 2. flags: tell every rank that this rank's data of this epoch is in place
-    if (tid < p.world) st_release_sys(reinterpret_cast<uint32_t *>(p.base[tid]) + b * PEER_MAX_WORLD + p.rank, epoch);
+    if (tid < p.world) st_release_sys(reinterpret_cast<uint32_t *>(p.base[tid]) + b * PEER_MAX_WORLD + rank, epoch);
     // 3. wait for every rank's flag in this rank's memory
     if (tid < p.world) {
-        const uint32_t *f = reinterpret_cast<const uint32_t *>(p.base[p.rank]) + b * PEER_MAX_WORLD + tid;
+        const uint32_t *f = reinterpret_cast<const uint32_t *>(p.base[rank]) + b * PEER_MAX_WORLD + tid;
         uint64_t t0, t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
         bool ok = false;
-        for (int i = 0; i < (1 << 24); ++i) {
+        for (long long i = 0; i < (1ll << 34); ++i) {
             if ((int32_t)(ld_acquire_sys(f) - epoch) >= 0) { ok = true; break; }
-            if ((i & 63) == 63) {
+            if ((i & 15) == 15) {
                 asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-                if (t - t0 > 2000000000ull) break;
+                if (t - t0 > wait_ns) break;
             }
         }
         if (!ok) atomicCAS(&g_peer_error, 0, 31);
     }
     __syncthreads();
     // 4. sum the slots in rank order
-    const float4 *rb = reinterpret_cast<const float4 *>(p.base[p.rank] + PEER_FLAG_BYTES) + (((int64_t)b * p.world * p.cap) >> 2);
+    const float4 *rb = reinterpret_cast<const float4 *>(p.base[rank] + PEER_FLAG_BYTES) + (((int64_t)b * p.world * p.cap) >> 2);
     for (int i = tid; i < (n >> 2); i += PEER_THREADS) {
         float4 a = rb[i];
         for (int r = 1; r < p.world; ++r) {
@@ -91,13 +90,42 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const Peer
         }
         reinterpret_cast<float4 *>(out)[i] = a;
     }
-    if (tid == 0) *p.epoch = epoch;
+    if (tid == 0) *epoch_ctr = epoch;
+}
+
+__global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const PeerParams p, const float *partial, float *out,
+                                                                      int n, uint64_t wait_ns) {
+    // programmatic dependent launch: the next kernel may begin its prologue now (it waits for this grid's completion
+    // before it reads anything this grid writes); this grid waits for its predecessor before it reads `partial`
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    peer_allreduce_body(p, p.rank, p.epoch, partial, out, n, wait_ns);
+}
+
+// All ranks of a world in ONE cooperative launch on one device, block r = rank r: the protocol exactly as above, for
+// machines with fewer GPUs than ranks (blocks of a cooperative launch are co-resident, so their waits on one another
+// end; separate launches that wait on one another carry no such guarantee).
+struct PeerLocalRanks {
+    const float *partial[PEER_MAX_WORLD];
+    float *out[PEER_MAX_WORLD];
+    uint32_t *epoch[PEER_MAX_WORLD];
+};
+__global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_local_kernel(const PeerParams p, const PeerLocalRanks l, int n,
+                                                                            uint64_t wait_ns) {
+    const int rank = blockIdx.x;
+    peer_allreduce_body(p, rank, l.epoch[rank], l.partial[rank], l.out[rank], n, wait_ns);
 }
 
 int peer_error_word(int *out) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_peer_error, sizeof(int)) != cudaSuccess) return cuda_status("qvb8_device_status");
     *out = v;
+    return QVB8_OK;
+}
+
+int peer_error_reset() {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_peer_error, &zero, sizeof(int)) != cudaSuccess) return cuda_status("qvb8_device_status_reset");
     return QVB8_OK;
 }
 
@@ -143,24 +171,34 @@ QV_API int qvb8_peer_close(void *ptr, int own) {
 /* out[0 .. n) = sum over the ranks of their partial[0 .. n), identical on every rank.  bases[r] = rank r's exchange
  * memory as mapped in this process (own allocation for r = rank); epoch = a zeroed uint32 of this rank in device
  * memory, owned by the communicator.  n % 4 == 0, n <= cap_floats.  Every rank must make the same sequence of calls.
- * flags: QVB8_FLAG_PDL launches with programmatic stream serialization, like qvb8_small_m_ex. */
-QV_API int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
-                               float *out, int64_t n, int flags, void *stream) {
-    using namespace qv;
-    if (int rc = check_device("qvb8_peer_allreduce")) return rc;
-    if (!bases || !epoch || !partial || !out || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world)
-        return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: bad arguments");
+ * flags: QVB8_FLAG_PDL launches with programmatic stream serialization, like qvb8_small_m_ex.
+ * wait_ns: how long the kernel waits for the peers' flags before it gives up with error word 31 (0 = two seconds). */
+namespace qv {
+constexpr uint64_t PEER_WAIT_NS = 2000000000ull;
+static int peer_fill(PeerParams &p, void *const *bases, int rank, int world, int64_t &cap_floats, int64_t n, const char *who) {
+    if (!bases || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world)
+        return fail(QVB8_ERR_ARG, "%s: bad arguments", who);
     cap_floats = (cap_floats + 3) / 4 * 4;
-    if (n <= 0 || n % 4 != 0 || n > cap_floats) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: n must be a multiple of 4 within the slot size");
-    if (!aligned(partial, 16) || !aligned(out, 16)) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: partial / out must be 16-byte aligned");
-    PeerParams p{};
+    if (n <= 0 || n % 4 != 0 || n > cap_floats) return fail(QVB8_ERR_ARG, "%s: n must be a multiple of 4 within the slot size", who);
     for (int r = 0; r < world; ++r) {
-        if (!bases[r]) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: null peer mapping");
+        if (!bases[r]) return fail(QVB8_ERR_ARG, "%s: null peer mapping", who);
         p.base[r] = reinterpret_cast<uint8_t *>(bases[r]);
     }
     p.rank = rank;
     p.world = world;
     p.cap = cap_floats;
+    return QVB8_OK;
+}
+}  // namespace qv
+
+QV_API int qvb8_peer_allreduce_ex(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch,
+                                  const float *partial, float *out, int64_t n, int flags, uint64_t wait_ns, void *stream) {
+    using namespace qv;
+    if (int rc = check_device("qvb8_peer_allreduce")) return rc;
+    if (!epoch || !partial || !out) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: bad arguments");
+    PeerParams p{};
+    if (int rc = peer_fill(p, bases, rank, world, cap_floats, n, "qvb8_peer_allreduce")) return rc;
+    if (!aligned(partial, 16) || !aligned(out, 16)) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: partial / out must be 16-byte aligned");
     p.epoch = reinterpret_cast<uint32_t *>(epoch);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(1);
@@ -172,6 +210,45 @@ QV_API int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & QVB8_FLAG_PDL) ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, p, partial, out, (int)n) != cudaSuccess) return cuda_status("qvb8_peer_allreduce launch");
+    if (cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, p, partial, out, (int)n, wait_ns ? wait_ns : PEER_WAIT_NS) != cudaSuccess)
+        return cuda_status("qvb8_peer_allreduce launch");
     return cuda_status("qvb8_peer_allreduce");
+}
+
+QV_API int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
+                               float *out, int64_t n, int flags, void *stream) {
+    return qvb8_peer_allreduce_ex(bases, rank, world, cap_floats, epoch, partial, out, n, flags, 0, stream);
+}
+
+/* Every rank of a `world` on ONE device in one cooperative launch (block r acts as rank r): bases[r], epochs[r],
+ * partials[r], outs[r] are rank r's exchange area, epoch counter, input and output, all in this device's memory.  For
+ * machines with fewer GPUs than ranks: kernels that wait on one another must not run as separate launches on one
+ * GPU, the blocks of a cooperative launch may. */
+QV_API int qvb8_peer_allreduce_local(void *const *bases, int world, int64_t cap_floats, void *const *epochs,
+                                     const float *const *partials, float *const *outs, int64_t n, uint64_t wait_ns,
+                                     void *stream) {
+    using namespace qv;
+    if (int rc = check_device("qvb8_peer_allreduce_local")) return rc;
+    if (!epochs || !partials || !outs) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce_local: bad arguments");
+    PeerParams p{};
+    if (int rc = peer_fill(p, bases, 0, world, cap_floats, n, "qvb8_peer_allreduce_local")) return rc;
+    PeerLocalRanks l{};
+    for (int r = 0; r < world; ++r) {
+        if (!epochs[r] || !partials[r] || !outs[r] || !aligned(partials[r], 16) || !aligned(outs[r], 16))
+            return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce_local: null or unaligned buffer of rank %d", r);
+        l.partial[r] = partials[r];
+        l.out[r] = outs[r];
+        l.epoch[r] = reinterpret_cast<uint32_t *>(epochs[r]);
+    }
+    int dev = 0, coop = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    if (!coop) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce_local: the device has no cooperative launch");
+    int nn = (int)n;
+    uint64_t wn = wait_ns ? wait_ns : PEER_WAIT_NS;
+    void *args[] = {&p, &l, &nn, &wn};
+    if (cudaLaunchCooperativeKernel((const void *)peer_allreduce_local_kernel, dim3(world), dim3(PEER_THREADS), args, 0,
+                                    reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess)
+        return cuda_status("qvb8_peer_allreduce_local launch");
+    return cuda_status("qvb8_peer_allreduce_local");
 }

@@ -52,6 +52,7 @@ int check_small_m_args(const qvb8_pack *w, const void *X, int x_dtype, int x_mod
                        const char *who);
 int prefill_error_word(int *out);                 // qvb8_prefill.cu
 int peer_error_word(int *out);                    // qvb8_peer.cu
+int peer_error_reset();
 
 constexpr int KC = 128;                   // columns per chunk
 constexpr int NW = 4;                     // consumer warps
@@ -408,14 +409,20 @@ __global__ void __launch_bounds__(256) escape_plan_kernel(const uint8_t *__restr
                                                           float *__restrict__ esc_delta) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n_esc) {
+        // a position outside the weight (a corrupt escape list) is clamped to the last row and contributes nothing
         const int64_t f = __ldg(esc_idx + i);
-        const int q = (int)(f / P), c = (int)(f - (int64_t)q * P);
+        const bool inside = f >= 0 && f < (int64_t)Q * P;
+        const int q = inside ? (int)(f / P) : Q - 1, c = inside ? (int)(f - (int64_t)q * P) : 0;
         const int nb = __ldg(nbits + q);
         const float b = band(field_bytes(ids, __ldg(bit_off + q) + (int64_t)c * nb, nb), __ldg(tau_s + q), __ldg(min_s + q));
         esc_col[i] = c;
-        esc_delta[i] = __ldg(esc_vals + i) - b;
+        esc_delta[i] = inside ? __ldg(esc_vals + i) - b : 0.f;
         // esc_idx ascends: this escape opens every row after the previous escape's row, up to its own
-        const int qprev = i == 0 ? -1 : (int)(__ldg(esc_idx + i - 1) / P);
+        int qprev = -1;
+        if (i > 0) {
+            const int64_t fp = __ldg(esc_idx + i - 1);
+            qprev = (fp >= 0 && fp < (int64_t)Q * P) ? (int)(fp / P) : Q - 1;
+        }
         for (int r = qprev + 1; r <= q; ++r) esc_ptr[r] = (int)i;
         if (i == n_esc - 1)
             for (int r = q + 1; r <= Q; ++r) esc_ptr[r] = (int)n_esc;
@@ -1430,6 +1437,12 @@ QV_API int qvb8_device_status(int *status) {
     return QVB8_OK;
 }
 
+QV_API int qvb8_device_status_reset(void) {
+    // only the all-reduce's word can be cleared: its waits end by design when a peer is late or gone (the kernel returns
+    // and the context stays usable); a wait of the streaming or prefill kernels that gave up means a defect and stays
+    return qv::peer_error_reset();
+}
+
 QV_API int64_t qvb8_small_m_scratch_bytes(int64_t M, int64_t Q, int64_t P) {
     using namespace qv;
     if (M < 1 || M > MAX_M || Q <= 0 || P <= 0 || P % KC != 0) return 0;
@@ -1532,9 +1545,9 @@ static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_B
 constexpr int MAX_STATIC_DEVICES = 64;
 static void *g_static_ptr[MAX_STATIC_DEVICES] = {};
 
-// Address of the array on the current device; on first use per device also clears the ticket area, the only part
-// that must start at zero (every call leaves it zero again).  Not capturable: the first call per device must come
-// before any stream capture that uses the entry point.
+// Address of the array on the current device, looked up once per device.  Nothing is cleared here: a file-scope
+// __device__ array is zero when the module is loaded, and every call leaves the ticket area (the only part that must
+// start at zero) zero again.  The look-up is a host-side query that touches no stream.
 static int static_scratch(void **out) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return cuda_status("qvb8_small_m_static: current device");
@@ -1547,8 +1560,6 @@ static int static_scratch(void **out) {
         void *p = nullptr;
         if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p)
             return cuda_status("qvb8_small_m_static: address of the module's scratch array");
-        if (cudaMemset(p, 0, (size_t)TICKET_BYTES) != cudaSuccess)
-            return cuda_status("qvb8_small_m_static: clearing the ticket area");
         g_static_ptr[dev] = p;
     }
     *out = g_static_ptr[dev];
@@ -1564,7 +1575,11 @@ QV_API int qvb8_small_m_static(const qvb8_pack *w, const void *plan, const void 
     using namespace qv;
     if (int rc = check_small_m_args(w, X, x_dtype, x_mode, M, Y, "qvb8_small_m_static")) return rc;
     if (w->Q == 0) return QVB8_OK;
-    const int64_t need = (w->P > 0 && w->P % KC == 0) ? qvb8_small_m_scratch_bytes(M, w->Q, w->P) : 0;
+    // scratch is used only by the streaming kernel (same condition as qvb8_small_m_ex): the layout-agnostic kernel
+    // that serves every other call needs none, so those calls are never refused for their size
+    const bool streaming = plan != nullptr && x_mode == 0 && fast_layout_ok(w, X) &&
+                           (w->Q + 15) / 16 + NCLASS - 1 <= MAX_TICKET_TILES;
+    const int64_t need = streaming ? qvb8_small_m_scratch_bytes(M, w->Q, w->P) : 0;
     if (need > STATIC_SCRATCH_BYTES)
         return fail(QVB8_ERR_SCRATCH,
                     "qvb8_small_m_static: this product needs %lld bytes of scratch, the built-in array holds %lld; "

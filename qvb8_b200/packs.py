@@ -337,50 +337,94 @@ QVBR_MAGIC, QVBR_VERSION, QVBR_PB = b"QVBR", 2, 12
 QVBR_PAD_WORDS = 2048      # zero words appended at load: the stream readers fetch ahead of their cursor
 
 
+QVBR_ARRAYS = (("perm", np.int32), ("freq", np.uint16), ("tiles", np.int32), ("tile_off", np.uint32),
+               ("states", np.uint64), ("words", np.uint32), ("drow", np.int16), ("min_s", np.float32),
+               ("tau_s", np.float32), ("esc_idx", np.int64), ("esc_val", np.float32), ("esc_delta", np.float32))
+_QVBR_ALIGN = 64
+
+
+def _align64(n: int) -> int:
+    return -(-n // _QVBR_ALIGN) * _QVBR_ALIGN
+
+
+def _qvbr_directory(meta: dict, arrays: dict) -> tuple[bytes, dict]:
+    """The JSON header of a .qvb8r file and the byte offset of every array.  The directory sits inside the JSON whose
+    own length moves the offsets, so the text is regenerated until its length no longer changes (it can only grow by
+    a digit or two, so this settles in two or three rounds)."""
+    where: dict = {}
+    text_len = -1
+    while True:
+        cursor = _align64(12 + max(text_len, 0))
+        for name, a in arrays.items():
+            where[name] = cursor
+            cursor = _align64(cursor + a.nbytes)
+        head = dict(meta, arrays={n: [where[n], a.dtype.str, list(a.shape)] for n, a in arrays.items()})
+        text = json.dumps(head).encode()
+        if len(text) == text_len:
+            return text, where
+        text_len = len(text)
+
+
 def write_qvb8r(enc: dict, *, Q, P, min_s, tau_s, esc_idx, esc_val, esc_delta, cert: dict) -> bytes:
-    """enc: perm i32[Q], freq u16[K,N], tiles i32[nt,3], tile_off u32[nt+1], states u64[nt,32], words u32[],
-    drow i16[Q], T, K, N.  Layout: magic | u32 version | u32 header_len | JSON | pad to 64 | arrays (64-aligned) |
-    u32 crc32 of everything before it."""
-    arrs = dict(perm=np.asarray(enc["perm"], np.int32), freq=np.asarray(enc["freq"], np.uint16),
-                tiles=np.asarray(enc["tiles"], np.int32), tile_off=np.asarray(enc["tile_off"], np.uint32),
-                states=np.asarray(enc["states"], np.uint64), words=np.asarray(enc["words"], np.uint32),
-                drow=np.asarray(enc["drow"], np.int16), min_s=np.asarray(min_s, np.float32),
-                tau_s=np.asarray(tau_s, np.float32), esc_idx=np.asarray(esc_idx, np.int64),
-                esc_val=np.asarray(esc_val, np.float32), esc_delta=np.asarray(esc_delta, np.float32))
-    hdr = dict(Q=int(Q), P=int(P), T=int(enc["T"]), K=int(enc["K"]), N=int(enc["N"]), PB=QVBR_PB, cert=cert, arrays={})
-    for _ in range(8):                                    # array offsets depend on the header length: iterate to a fixpoint
-        hj = json.dumps(hdr).encode()
-        pos = (12 + len(hj) + 63) // 64 * 64
-        for k, a in arrs.items():
-            hdr["arrays"][k] = [pos, a.dtype.str, list(a.shape)]
-            pos = (pos + a.nbytes + 63) // 64 * 64
-        if json.dumps(hdr).encode() == hj:
-            break
-    else:
-        raise PackFormatError("qvb8r header did not stabilise")
-    buf = bytearray(QVBR_MAGIC + struct.pack("<II", QVBR_VERSION, len(hj)) + hj)
-    for k, a in arrs.items():
-        off = hdr["arrays"][k][0]
-        buf += b"\0" * (off - len(buf))
-        buf += a.tobytes()
-    buf += b"\0" * ((len(buf) + 63) // 64 * 64 - len(buf))
-    buf += struct.pack("<I", zlib.crc32(bytes(buf)) & 0xFFFFFFFF)
-    return bytes(buf)
+    """The bytes of a .qvb8r file (layout: reference formats/qvb8r/container.py:1-12): ``QVBR`` | u32 version 2 |
+    u32 header length | JSON header (Q, P, T, K, N, PB, cert, arrays: name -> [offset, dtype, shape]) | zero pad to
+    64 | the arrays, each starting on a multiple of 64 | zero pad to 64 | u32 crc32 of every byte before it.
+    enc: perm, freq, tiles, tile_off, states, words, drow, T, K, N (see :mod:`qvb8_b200.rans`)."""
+    given = dict(enc, min_s=min_s, tau_s=tau_s, esc_idx=esc_idx, esc_val=esc_val, esc_delta=esc_delta)
+    arrays = {name: np.ascontiguousarray(given[name], dtype=dt) for name, dt in QVBR_ARRAYS}
+    meta = dict(Q=int(Q), P=int(P), T=int(enc["T"]), K=int(enc["K"]), N=int(enc["N"]), PB=QVBR_PB, cert=cert)
+    text, where = _qvbr_directory(meta, arrays)
+    end = _align64(max([12 + len(text)] + [where[n] + a.nbytes for n, a in arrays.items()]))
+    out = np.zeros(end + 4, np.uint8)
+    out[:4] = np.frombuffer(QVBR_MAGIC, np.uint8)
+    out[4:12] = np.frombuffer(struct.pack("<II", QVBR_VERSION, len(text)), np.uint8)
+    out[12:12 + len(text)] = np.frombuffer(text, np.uint8)
+    for name, a in arrays.items():
+        out[where[name]:where[name] + a.nbytes] = np.frombuffer(a.tobytes(), np.uint8)
+    out[end:] = np.frombuffer(struct.pack("<I", zlib.crc32(out[:end].tobytes()) & 0xFFFFFFFF), np.uint8)
+    return out.tobytes()
 
 
 def read_qvb8r(blob: bytes, where: str = "<blob>") -> dict:
-    if blob[:4] != QVBR_MAGIC:
-        raise PackFormatError(f"{where}: not a .qvb8r file")
-    ver, hl = struct.unpack_from("<II", blob, 4)
-    if ver != QVBR_VERSION:
-        raise PackFormatError(f"{where}: .qvb8r version {ver}, this reader knows {QVBR_VERSION}")
-    if zlib.crc32(memoryview(blob)[:-4]) & 0xFFFFFFFF != struct.unpack_from("<I", blob, len(blob) - 4)[0]:
-        raise PackFormatError(f"{where}: crc32 mismatch (truncated or corrupt file)")
-    hdr = json.loads(bytes(blob[12:12 + hl]))
-    if hdr.get("PB") != QVBR_PB:
-        raise PackFormatError(f"{where}: PB {hdr.get('PB')} != {QVBR_PB}")
-    out = dict(hdr)
-    for k, (off, dt, shape) in hdr["arrays"].items():
-        n = int(np.prod(shape)) if shape else 1
-        out[k] = np.frombuffer(blob, np.dtype(dt), n, off).reshape(shape).copy()
+    """Header fields + arrays (copies) of a .qvb8r file; PackFormatError on anything that is not a sound version-2
+    file: wrong magic or version, checksum, model constants, an array outside the file or of the wrong type / shape."""
+    n = len(blob)
+    if n < 16 or bytes(blob[:4]) != QVBR_MAGIC:
+        raise PackFormatError(f"{where}: no QVBR magic at the start")
+    version, text_len = struct.unpack_from("<II", blob, 4)
+    if version != QVBR_VERSION:
+        raise PackFormatError(f"{where}: file version {version}; only version {QVBR_VERSION} "
+                              "(centred rows, 64-bit states, 32-bit words) can be read")
+    stored = struct.unpack_from("<I", blob, n - 4)[0]
+    if stored != zlib.crc32(memoryview(blob)[:n - 4]) & 0xFFFFFFFF:
+        raise PackFormatError(f"{where}: checksum does not match the contents (cut short or damaged)")
+    if 12 + text_len > n - 4:
+        raise PackFormatError(f"{where}: header length {text_len} runs past the file")
+    try:
+        head = json.loads(bytes(blob[12:12 + text_len]))
+        listing = head["arrays"]
+        Q, P = int(head["Q"]), int(head["P"])
+    except (ValueError, KeyError, TypeError) as ex:
+        raise PackFormatError(f"{where}: unreadable header ({ex})") from None
+    if head.get("PB") != QVBR_PB:
+        raise PackFormatError(f"{where}: probability precision {head.get('PB')} bits, the decoders are built for {QVBR_PB}")
+    out = {k: v for k, v in head.items()}
+    for name, want in QVBR_ARRAYS:
+        if name not in listing:
+            raise PackFormatError(f"{where}: array {name} is missing")
+        off, dt, shape = listing[name]
+        dt = np.dtype(dt)
+        count = int(np.prod(shape, dtype=np.int64)) if shape else 1
+        if dt != np.dtype(want) or off < 0 or off + count * dt.itemsize > n - 4:
+            raise PackFormatError(f"{where}: array {name} has the wrong type or lies outside the file")
+        out[name] = np.frombuffer(blob, dt, count, off).reshape(shape).copy()
+    nt = out["tiles"].shape[0] if out["tiles"].ndim == 2 else -1
+    ok = (out["perm"].shape == (Q,) and out["drow"].shape == (Q,) and out["min_s"].shape == (Q,)
+          and out["tau_s"].shape == (Q,) and out["tiles"].ndim == 2 and out["tiles"].shape[1:] == (3,)
+          and out["tile_off"].shape == (nt + 1,) and out["states"].shape == (nt, 32) and out["freq"].ndim == 2
+          and out["esc_idx"].shape == out["esc_val"].shape == out["esc_delta"].shape)
+    if not ok:
+        raise PackFormatError(f"{where}: array shapes do not fit Q = {Q}")
+    if nt and (int(out["tile_off"][-1]) > out["words"].size or np.any(np.diff(out["tile_off"].astype(np.int64)) < 0)):
+        raise PackFormatError(f"{where}: tile offsets do not fit the word stream")
     return out

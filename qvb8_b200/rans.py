@@ -71,15 +71,25 @@ def quantise_freq(hist: np.ndarray) -> np.ndarray:
 
 
 def blocks_for(tiles: np.ndarray, tiles_per_block: int) -> np.ndarray:
-    """Runs of <= tiles_per_block consecutive tiles of one class -> (class, first tile, ntiles) (container.py:74-82)."""
-    out, i, n = [], 0, len(tiles)
-    while i < n:
-        j = i
-        while j < n and j - i < tiles_per_block and tiles[j][0] == tiles[i][0]:
-            j += 1
-        out.append((int(tiles[i][0]), i, j - i))
-        i = j
-    return np.asarray(out, np.int32).reshape(-1, 3)
+    """The launch schedule of a tile table: (class, first tile, ntiles) per block, a block being at most
+    `tiles_per_block` consecutive tiles of ONE class -- the eight (sixteen) tiles of a CTA share the class's slot
+    table in shared memory (the reference derives the same schedule at load, container.py:74-82).  Computed from the
+    class column alone: a new block starts where the class changes or where the running length within a class run
+    reaches a multiple of `tiles_per_block`."""
+    cls = np.asarray(tiles, np.int64).reshape(-1, 3)[:, 0]
+    n = cls.size
+    if n == 0:
+        return np.zeros((0, 3), np.int32)
+    change = np.flatnonzero(np.diff(cls)) + 1                  # first tile of every class run but the first
+    run_start = np.concatenate([[0], change])
+    run_len = np.diff(np.concatenate([run_start, [n]]))
+    firsts, counts = [], []
+    for s0, ln in zip(run_start.tolist(), run_len.tolist()):
+        starts = np.arange(s0, s0 + ln, tiles_per_block)
+        firsts.append(starts)
+        counts.append(np.minimum(tiles_per_block, s0 + ln - starts))
+    first = np.concatenate(firsts)
+    return np.stack([cls[first], first, np.concatenate(counts)], axis=1).astype(np.int32)
 
 
 def encode_symbols(sym: np.ndarray, tile_class: np.ndarray, tile_rows: np.ndarray, freq: np.ndarray):
@@ -134,10 +144,11 @@ def encode_symbols(sym: np.ndarray, tile_class: np.ndarray, tile_rows: np.ndarra
     return x, (np.concatenate(words) if words else np.zeros(0, np.uint32)).astype(np.uint32), np.asarray(tile_off, np.uint32)
 
 
-def encode_ids(ids: np.ndarray, K: int = 2, T: int = 8, seed: int = 0) -> dict:
-    """Entropy-code integer ids (Q, P) (each row >= 0).  Rows are centred (drow), classed into K groups by their
-    spread, sorted by class (perm), cut into tiles of <= T rows and coded.  Returns the container arrays
-    (perm, freq, tiles, tile_off, states, words, drow, T, K, N)."""
+def model_for(ids: np.ndarray, K: int = 2, T: int = 8) -> dict:
+    """The coding model of integer ids (Q, P) (each row >= 0): rows centred (drow), classed into K groups by their
+    spread, sorted by class (perm), cut into tiles of <= T rows, one quantised frequency table per class.  Returns
+    sym (Q, P) symbols in ORIGINAL row order, perm, freq, tiles, drow, T, K, N.  The reference does not ship this
+    step (its writer is not in the release, codec.py:1); any model its reader accepts is a valid file."""
     ids = np.asarray(ids, np.int64)
     Q, P = ids.shape
     med = np.median(ids, axis=1).astype(np.int64)
@@ -161,17 +172,21 @@ def encode_ids(ids: np.ndarray, K: int = 2, T: int = 8, seed: int = 0) -> dict:
             freq[k] = quantise_freq(np.bincount(sym[rows].ravel(), minlength=N))
         else:
             freq[k, :4] = MAX_FREQ                          # an empty class still needs a valid table
-    tiles = []
-    pos = 0
     sorted_cls = cls_of_row[perm]
-    while pos < Q:
-        k = sorted_cls[pos]
-        n = 1
-        while n < T and pos + n < Q and sorted_cls[pos + n] == k:
-            n += 1
-        tiles.append((int(k), pos, n))
-        pos += n
+    # tiles: every class run cut into pieces of T rows
+    bounds = np.concatenate([[0], np.flatnonzero(np.diff(sorted_cls)) + 1, [Q]])
+    tiles = [(int(sorted_cls[a0]), int(p0), int(min(T, a1 - p0)))
+             for a0, a1 in zip(bounds[:-1], bounds[1:]) for p0 in range(a0, a1, T)]
     tiles = np.asarray(tiles, np.int32).reshape(-1, 3)
-    states, words, tile_off = encode_symbols(sym[perm], tiles[:, 0], tiles[:, 2], freq)
-    return dict(perm=perm, freq=freq.astype(np.uint16), tiles=tiles, tile_off=tile_off, states=states, words=words,
-                drow=drow.astype(np.int16), T=int(T), K=int(K), N=int(N))
+    return dict(sym=sym, perm=perm, freq=freq.astype(np.uint16), tiles=tiles, drow=drow.astype(np.int16), T=int(T),
+                K=int(K), N=int(N))
+
+
+def encode_ids(ids: np.ndarray, K: int = 2, T: int = 8, seed: int = 0) -> dict:
+    """Entropy-code integer ids (Q, P): :func:`model_for`, then :func:`encode_symbols` over the sorted rows.  Returns
+    the container arrays (perm, freq, tiles, tile_off, states, words, drow, T, K, N)."""
+    m = model_for(ids, K=K, T=T)
+    sym = m.pop("sym")
+    states, words, tile_off = encode_symbols(sym[m["perm"]], m["tiles"][:, 0], m["tiles"][:, 2], m["freq"])
+    m.update(tile_off=tile_off, states=states, words=words)
+    return m

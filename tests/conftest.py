@@ -15,7 +15,13 @@ def pytest_configure(config):
 
 
 def golden_cases():
-    return sorted(f[:-4] for f in os.listdir(GOLDEN) if f.endswith(".npz"))
+    """QVB8 fixtures (outputs of the reference's Python pack decoders)."""
+    return sorted(f[:-4] for f in os.listdir(GOLDEN) if f.endswith(".npz") and f.startswith(("qvbd_", "legacy_")))
+
+
+def golden_qvb8r_cases():
+    """QVB8R fixtures (files written and decoded by the reference's container.py + qvb8r_cpu.cpp)."""
+    return sorted(f[:-4] for f in os.listdir(GOLDEN) if f.endswith(".npz") and f.startswith("qvb8r_"))
 
 
 @pytest.fixture(scope="session")

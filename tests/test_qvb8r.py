@@ -1,5 +1,6 @@
-"""QVB8R (entropy-coded QVB8): the synthetic encoder against the oracle decoder (which is pinned on the reference's own
-reader, tests/golden), the container round trip, and the CUDA kernels against the oracle."""
+"""QVB8R (entropy-coded QVB8): the synthetic encoder against the oracle decoder, the container round trip, and the
+CUDA kernels against the oracle on seeded packs.  The oracle decoder, the encoder, the container code and the kernels
+are pinned on files written and decoded by the reference itself in tests/test_qvb8r_golden.py."""
 import numpy as np
 import pytest
 import torch
