@@ -240,6 +240,15 @@ int qvb8r_small_m(const qvb8r_pack *w, const void *X, int x_dtype, int64_t M, in
 int qvb8r_fix_escapes(const float *X, const int64_t *uq, const int64_t *ptr, const int64_t *ec, const float *ed, float *Y,
                       int64_t U, int64_t M, int64_t P, int64_t Q, void *stream);
 
+/* Embedding lookup over an entropy-coded table kept in device memory: out (n, P) fp32 = rows rows[0 .. n) (int64 device
+ * array), restored as the reference's CPU reader does -- min_s + float(id) * tau_s, multiplication then addition -- and
+ * the rows' escapes written over (reference `embed_rows`, qvb8r_cpu.cpp:13-58, which decodes on the host because its
+ * target cards are small; a B200 keeps the table in HBM).  inv_perm i32[Q]: original row -> sorted position;
+ * row_tile i32[Q]: sorted position -> tile; esc_ptr i64[Q + 1], esc_col i32[], esc_val f32[]: the escapes by row.  The
+ * `blocks` field of the pack is not used.  A row index outside [0, Q) yields a row of zeros. */
+int qvb8r_embed_rows(const qvb8r_pack *w, const int64_t *rows, int64_t n, const int32_t *inv_perm, const int32_t *row_tile,
+                     const int64_t *esc_ptr, const int32_t *esc_col, const float *esc_val, float *out, void *stream);
+
 /* qvb8_small_m_ex without a scratch argument and without any allocation (no counterpart in the reference, whose
  * extension allocates its split-K buffer through torch on every call).  For callers that cannot allocate device
  * memory and have no buffer to pass: code running inside an allocator or memory-pool callback, a thread that must

@@ -103,11 +103,16 @@ struct PipeControl {
     alignas(8) uint64_t red_empty;        // ... and have been taken by the finishing warp
 };
 struct Control {
-    float sumx[MAX_M];                    // per-token sums of the narrowed activations of this K-range
+    union {
+        float sumx[MAX_M];                // per-token sums of the narrowed activations of this K-range
+        uint32_t amax[MAX_M];             // x_mode 1, before the sums exist: bits of the largest |x| of a token's range
+    };
+    uint8_t kexp[MAX_M];                  // x_mode 1: token m is staged as x * 2^-kexp[m] and its results multiplied back
     int abort;
     alignas(16) uint32_t pair_table[24];  // pair-conversion constants of widths 3..8 (see pair_const)
     alignas(8) uint64_t x_ready;          // every consumer warp has staged its share of the activations
     alignas(8) uint64_t sums_ready;       // every finishing warp has summed its share of the tokens
+    alignas(8) uint64_t amax_ready;       // x_mode 1: every consumer warp has folded its share into amax
     alignas(8) uint64_t xch_full[XCH_SLOTS];   // [owner pipe][contributor]: a contributed part of a shared tile is in place
     PipeControl pipe[MAX_PIPES];
 };
@@ -367,8 +372,8 @@ __device__ __forceinline__ float xs_read(const __half *xs, int c, int m, int MP)
 }
 
 template <int XT>
-__device__ __forceinline__ void stage_x8(const void *__restrict__ X, int64_t off, uint32_t (&h)[8]) {
-    // h[k] = fp16 bits of the k-th activation, saturated
+__device__ __forceinline__ void stage_x8(const void *__restrict__ X, int64_t off, uint32_t (&h)[8], float sc) {
+    // h[k] = fp16 bits of the k-th activation times sc (1, or a token's power-of-two prescale), saturated
     if constexpr (XT == QVB8_F16) {
         const uint4 u = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(X) + off));
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -379,17 +384,44 @@ __device__ __forceinline__ void stage_x8(const void *__restrict__ X, int64_t off
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            h[2 * k] = __half_as_ushort(sat_half(__uint_as_float(w[k] << 16)));
-            h[2 * k + 1] = __half_as_ushort(sat_half(__uint_as_float(w[k] & 0xffff0000u)));
+            h[2 * k] = __half_as_ushort(sat_half(__uint_as_float(w[k] << 16) * sc));
+            h[2 * k + 1] = __half_as_ushort(sat_half(__uint_as_float(w[k] & 0xffff0000u) * sc));
         }
     } else {
         const float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(X) + off));
         const float4 b = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(X) + off) + 1);
         const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int k = 0; k < 8; ++k) h[k] = __half_as_ushort(sat_half(v[k]));
+        for (int k = 0; k < 8; ++k) h[k] = __half_as_ushort(sat_half(v[k] * sc));
     }
 }
+
+// Largest |x| of 8 activations as float bits (NaN and infinity count as the largest finite exponent and above:
+// their staging saturates anyway).  fp16 input never needs a prescale.
+template <int XT>
+__device__ __forceinline__ uint32_t amax_x8(const void *__restrict__ X, int64_t off) {
+    uint32_t mx = 0u;
+    if constexpr (XT == QVB8_BF16) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(X) + off));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { mx = max(mx, (w[k] << 16) & 0x7fffffffu); mx = max(mx, w[k] & 0x7fff0000u); }
+    } else if constexpr (XT == QVB8_F32) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(X) + off));
+        const uint4 b = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(X) + off) + 1);
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mx = max(mx, w[k] & 0x7fffffffu);
+    }
+    return mx;
+}
+// Prescale exponent of a token whose largest magnitude has these float bits: the smallest k >= 0 that brings it below
+// 2^16 (fp16 holds up to 65504; the narrowing still saturates the sliver between).
+__device__ __forceinline__ int prescale_exp(uint32_t amax_bits) {
+    const int e = (int)(amax_bits >> 23) - 127;
+    return e > 15 ? min(e - 15, 112) : 0;
+}
+__device__ __forceinline__ float pow2f(int k) { return __uint_as_float((uint32_t)(127 + k) << 23); }
 
 // ---------------------------------------------------------------------------------------------------------------
 // plan build (once per pack)
@@ -582,6 +614,7 @@ struct SmallMParams {
     int *ticket;               // one counter per tile (zero on entry, zero on exit)
     int Q, P, M, MP;           // MP: token slots per column group in shared memory (>= M)
     int x_dtype;
+    int x_mode;                // 0: activations narrowed to saturated fp16; 1: per-token power-of-two prescale first
     int S;                     // K-ranges (= gridDim.y)
     int nc_per;                // chunks per K-range (the last range may be shorter)
     int nc_total;              // P / 128
@@ -701,10 +734,10 @@ __device__ __forceinline__ bool stream_tile(const SmallMParams &p, const uint32_
 
 // X staging: 8 activations as saturated fp16 bit patterns, whatever the input type (runtime switch: the staging
 // loop is short, and one kernel serves the three input types)
-__device__ __forceinline__ void stage_x8_any(int x_dtype, const void *__restrict__ X, int64_t off, uint32_t (&h)[8]) {
-    if (x_dtype == QVB8_BF16) stage_x8<QVB8_BF16>(X, off, h);
-    else if (x_dtype == QVB8_F16) stage_x8<QVB8_F16>(X, off, h);
-    else stage_x8<QVB8_F32>(X, off, h);
+__device__ __forceinline__ void stage_x8_any(int x_dtype, const void *__restrict__ X, int64_t off, uint32_t (&h)[8], float sc) {
+    if (x_dtype == QVB8_BF16) stage_x8<QVB8_BF16>(X, off, h, sc);
+    else if (x_dtype == QVB8_F16) stage_x8<QVB8_F16>(X, off, h, sc);
+    else stage_x8<QVB8_F32>(X, off, h, sc);
 }
 
 // DUAL: a second activation layout is staged for widths that pair ids at distance 4 (cheap for few tokens).
@@ -785,11 +818,13 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         } else if (tid == NPIPE * per_pipe + XCH_SLOTS) {
             mbar_init(smem_u32(&ctl.x_ready), NW * NPIPE);
             mbar_init(smem_u32(&ctl.sums_ready), NPIPE);
+            mbar_init(smem_u32(&ctl.amax_ready), NW * NPIPE);
             ctl.abort = 0;
         }
         if (tid <= NPIPE * per_pipe + XCH_SLOTS) asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (tid >= 160 && tid < 164) zero16[tid - 160] = 0u;
+    if (tid >= 192 && tid < 192 + MAX_M) { ctl.amax[tid - 192] = 0u; ctl.kexp[tid - 192] = 0; }
     if (tid >= 128 && tid < 128 + PAIR_TABLE_WORDS) ctl.pair_table[tid - 128] = pair_const_word(3 + ((tid - 128) >> 2), (tid - 128) & 3);
     __syncthreads();
     pdl_launch_dependents();                                            // what follows in the stream may start its own prologue
@@ -893,6 +928,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         if (lane == 0) mbar_arrive(smem_u32(&ctl.sums_ready));
         if (alive) alive = mbar_wait(smem_u32(&ctl.sums_ready), 0, abort_flag, 6);
         int own_contrib = 0, own_tile = 0, own_row[2] = {-1, -1};
+        const bool prescaled = p.x_mode == 1 && p.x_dtype != QVB8_F16;
         // writes a finished tile (of this K-range): the result itself, or with several K-ranges a partial result; the
         // K-ranges' partial results of all of a CTA's tiles are added up in range order at the end of the kernel
         auto emit_tile = [&](int tile, const int (&rows)[2], const float (&y)[2][NT][2]) {
@@ -1040,6 +1076,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                                 }
                             }
                             if (planned) val += corr[(g + 8 * hrow) * M + m];
+                            if (prescaled) val *= pow2f(ctl.kexp[m]);
                         }
                         y[hrow][n][k] = val;
                     }
@@ -1115,6 +1152,24 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             constexpr int CTHREADS = NPIPE * NW * 32;
             constexpr int UNR = 4;                                      // loads in flight per thread
             const int x_dtype = p.x_dtype;
+            // x_mode 1 (activations beyond the fp16 range): a first pass finds every token's largest magnitude in this
+            // K-range; the token is then staged times 2^-k, k the smallest exponent that brings it into range, and its
+            // results are multiplied by 2^k on the way out -- both exact.  fp16 input needs no prescale.
+            const bool prescale = p.x_mode == 1 && x_dtype != QVB8_F16;
+            if (prescale) {
+                for (int idx = ctid; idx < total; idx += CTHREADS) {
+                    const int m = idx / groups, u8 = idx - m * groups;
+                    if (m < M) {
+                        const int64_t off = (int64_t)m * p.P + col0 + (int64_t)u8 * 8;
+                        const uint32_t mx = x_dtype == QVB8_BF16 ? amax_x8<QVB8_BF16>(p.X, off) : amax_x8<QVB8_F32>(p.X, off);
+                        if (mx > 0x477fffffu) atomicMax(&ctl.amax[m], mx);      // only magnitudes of 2^16 and above matter
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl.amax_ready));
+                mbar_wait(smem_u32(&ctl.amax_ready), 0, abort_flag, 5);
+                if (ctid < M) ctl.kexp[ctid] = (uint8_t)prescale_exp(ctl.amax[ctid]);
+            }
             for (int base = ctid; base < total; base += CTHREADS * UNR) {
                 uint32_t h[UNR][8];
 #pragma unroll
@@ -1122,7 +1177,8 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                     const int idx = base + i * CTHREADS;
                     const int m = idx / groups, u8 = idx - m * groups;  // u8: natural 8-column group number
                     if (idx < total && m < M) {
-                        stage_x8_any(x_dtype, p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h[i]);
+                        const float sc = prescale ? pow2f(-prescale_exp(ctl.amax[m])) : 1.f;
+                        stage_x8_any(x_dtype, p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h[i], sc);
                     } else {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) h[i][j] = 0u;
@@ -1498,7 +1554,7 @@ QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, 
     if (int rc = check_small_m_args(w, X, x_dtype, x_mode, M, Y, "qvb8_small_m")) return rc;
     if (w->Q == 0) return QVB8_OK;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (plan == nullptr || x_mode != 0 || !fast_layout_ok(w, X) || (w->Q + 15) / 16 + NCLASS - 1 > MAX_TICKET_TILES)
+    if (plan == nullptr || !fast_layout_ok(w, X) || (w->Q + 15) / 16 + NCLASS - 1 > MAX_TICKET_TILES)
         return launch_small_m_generic(w, X, x_dtype, x_mode, (int)M, Y, st);
     if (!aligned(plan, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: the plan must be 16-byte aligned");
     const Plan pl = make_plan(M, w->Q, w->P);
@@ -1518,7 +1574,7 @@ QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, 
     prm.X = X; prm.Y = Y;
     prm.ticket = reinterpret_cast<int *>(scratch);
     prm.part = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + TICKET_BYTES);
-    prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.S = pl.S; prm.x_dtype = x_dtype;
+    prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.S = pl.S; prm.x_dtype = x_dtype; prm.x_mode = x_mode;
     prm.nc_per = pl.nc_per; prm.nc_total = pl.nc_total; prm.nstg = pl.nstg; prm.debug = g_debug;
     prm.cps = pl.cps; prm.slot_bytes = pl.slot_bytes;
     for (int i = 0; i < 6; ++i) prm.rs[i] = pl.rs[i];
@@ -1577,7 +1633,7 @@ QV_API int qvb8_small_m_static(const qvb8_pack *w, const void *plan, const void 
     if (w->Q == 0) return QVB8_OK;
     // scratch is used only by the streaming kernel (same condition as qvb8_small_m_ex): the layout-agnostic kernel
     // that serves every other call needs none, so those calls are never refused for their size
-    const bool streaming = plan != nullptr && x_mode == 0 && fast_layout_ok(w, X) &&
+    const bool streaming = plan != nullptr && fast_layout_ok(w, X) &&
                            (w->Q + 15) / 16 + NCLASS - 1 <= MAX_TICKET_TILES;
     const int64_t need = streaming ? qvb8_small_m_scratch_bytes(M, w->Q, w->P) : 0;
     if (need > STATIC_SCRATCH_BYTES)

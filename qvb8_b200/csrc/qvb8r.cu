@@ -176,6 +176,47 @@ __global__ void __launch_bounds__(128) qvb8r_fix_kernel(const float *__restrict_
     Y[(int64_t)m * Q + uq[u]] += a;
 }
 
+// Embedding lookup: out[i, :] = row rows[i] of the table, restored as the reference's CPU reader restores it -- a
+// multiplication and then an addition, min_s + float(id) * tau_s, not fused (qvb8r_cpu.cpp:44) -- with the row's escapes
+// written over.  One warp per requested row: it walks the row's tile from the tile's start (a tile is a few rows) and
+// keeps only the last row it decodes.  The slot table is read through the read-only cache: the warps of a CTA need
+// different classes, and a lookup touches a handful of rows.
+__global__ void __launch_bounds__(32 * R_WPB) qvb8r_embed_kernel(const RCore c, const int64_t *__restrict__ rows, int64_t n,
+                                                                const int32_t *__restrict__ inv_perm,
+                                                                const int32_t *__restrict__ row_tile,
+                                                                const int64_t *__restrict__ esc_ptr,
+                                                                const int32_t *__restrict__ esc_col,
+                                                                const float *__restrict__ esc_val, float *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t i = (int64_t)blockIdx.x * R_WPB + (threadIdx.x >> 5);
+    if (i >= n) return;
+    const int64_t q = rows[i];
+    float *o = out + i * c.P;
+    if (q < 0 || q >= c.Q) {                                           // refused on the host; never read out of range
+        for (int col = lane; col < c.P; col += 32) o[col] = 0.f;
+        return;
+    }
+    const int sp = inv_perm[q], tile = row_tile[sp];
+    const int k = sp - (int)c.tiles[3 * (int64_t)tile + 1];            // rows of the tile in front of this one
+    const uint32_t *st = c.tab + c.tiles[3 * (int64_t)tile] * 4096;
+    const float m = c.min_s[q], t = c.tau_s[q];
+    const int dr = c.drow[q];
+    const int S = c.P / 32;
+    RStream z;
+    rstream_init(z, c.words, c.tile_off[tile], c.states, tile, lane);
+    for (int r = 0; r <= k; ++r)
+        for (int s0 = 0; s0 < S; s0 += 2) {
+            uint32_t s1, s2;
+            rstream_pair(z, st, lane, s1, s2);
+            if (r == k) {
+                o[s0 * 32 + lane] = __fadd_rn(m, __fmul_rn((float)((int)s1 + dr), t));
+                o[s0 * 32 + 32 + lane] = __fadd_rn(m, __fmul_rn((float)((int)s2 + dr), t));
+            }
+        }
+    __syncwarp();
+    for (int64_t e = esc_ptr[q] + lane; e < esc_ptr[q + 1]; e += 32) o[esc_col[e]] = esc_val[e];
+}
+
 static int check_rpack(const qvb8r_pack *w, const char *who) {
     if (!w) return fail(QVB8_ERR_ARG, "%s: null pack", who);
     if (!w->words || !w->tile_off || !w->states || !w->tiles || !w->blocks || !w->tab || !w->perm || !w->min_s ||
@@ -273,4 +314,18 @@ QV_API int qvb8r_fix_escapes(const float *X, const int64_t *uq, const int64_t *p
     qvb8r_fix_kernel<<<(unsigned)((n + 127) / 128), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(X, uq, ptr, ec, ed, Y, U,
                                                                                                       (int)M, (int)P, (int)Q);
     return cuda_status("qvb8r_fix_escapes");
+}
+
+QV_API int qvb8r_embed_rows(const qvb8r_pack *w, const int64_t *rows, int64_t n, const int32_t *inv_perm,
+                            const int32_t *row_tile, const int64_t *esc_ptr, const int32_t *esc_col, const float *esc_val,
+                            float *out, void *stream) {
+    using namespace qv;
+    if (int rc = check_rpack(w, "qvb8r_embed_rows")) return rc;
+    if (int rc = check_device("qvb8r_embed_rows")) return rc;
+    if (n == 0) return QVB8_OK;
+    if (!rows || !inv_perm || !row_tile || !esc_ptr || !out || n < 0)
+        return fail(QVB8_ERR_ARG, "qvb8r_embed_rows: bad argument");
+    qvb8r_embed_kernel<<<(unsigned)((n + R_WPB - 1) / R_WPB), 32 * R_WPB, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        core_of(w), rows, n, inv_perm, row_tile, esc_ptr, esc_col, esc_val, out);
+    return cuda_status("qvb8r_embed_rows");
 }

@@ -72,3 +72,41 @@ class QVBandEmbeddingV8(nn.Module):
     def weight(self) -> torch.Tensor:
         """Dense (Q, P) table, for callers that need all of it (tied lm_head, audits)."""
         return self._rows(torch.arange(self.num_embeddings, device=self.ids.device), self._out_dtype)
+
+
+class QVBandEmbeddingV8R(nn.Module):
+    """``nn.Embedding`` over an entropy-coded (.qvb8r) table.  The reference module of this name decodes the looked-up
+    rows on the host so that the table never occupies a small card's memory (formats/qvb8r/module.py:340-391); here
+    the table (about 5 bits per weight) stays in device memory and ``qvb8r_embed_rows`` decodes the rows there, with
+    the reference's arithmetic, so the values are bit-identical."""
+
+    def __init__(self, d: dict, out_dtype=torch.bfloat16, device="cuda", path: str | None = None):
+        super().__init__()
+        from .ext_qvb8r import EmbeddingTable
+        self.num_embeddings, self.embedding_dim = int(d["Q"]), int(d["P"])
+        self._out_dtype, self.device, self.path = out_dtype, torch.device(device), path
+        self.table = EmbeddingTable.from_parsed(d, self.device)
+
+    @classmethod
+    def from_packfile(cls, path: str, *, out_dtype=torch.bfloat16, tau: float | None = None, device: str = "cuda",
+                      blob: bytes | None = None) -> "QVBandEmbeddingV8R":
+        from . import packs
+        if blob is None:
+            with open(path, "rb") as fh:
+                blob = fh.read()
+        return cls(packs.read_qvb8r(blob, str(path)), out_dtype=out_dtype, device=device, path=path)
+
+    def extra_repr(self):
+        return f"{self.num_embeddings}, {self.embedding_dim}, rows decoded on the device"
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        flat = input.reshape(-1).to(device=self.device, dtype=torch.int64)
+        if flat.numel() and not torch.cuda.is_current_stream_capturing():
+            if int(flat.min()) < 0 or int(flat.max()) >= self.num_embeddings:
+                raise IndexError(f"QVBandEmbeddingV8R: index out of range [0, {self.num_embeddings})")
+        return self.table.lookup(flat).to(self._out_dtype).reshape(*input.shape, self.embedding_dim)
+
+    @property
+    def weight(self) -> torch.Tensor:
+        rows = torch.arange(self.num_embeddings, device=self.device)
+        return self.table.lookup(rows).to(self._out_dtype)

@@ -16,30 +16,30 @@ STACK_PAD = 64
 
 
 def stack_packs(members: list[QVB8Pack]) -> dict:
-    """{'ids', 'min_s', 'tau_s', 'nbits', 'bit_off', 'Q', 'P'} of all experts of one projection."""
+    """One projection of all experts as the grouped kernels read it: {'ids', 'min_s', 'tau_s', 'nbits', 'bit_off',
+    'Q', 'P'}.  Every expert's payload starts on a 16-byte boundary of one shared buffer; its rows keep their own bit
+    offsets, shifted by where the expert's payload begins; the per-row vectors become (expert, row) matrices."""
     if not members:
         raise ValueError("stack_packs: no experts")
-    Q, P, dev = members[0].Q, members[0].P, members[0].device
-    for m in members:
-        if (m.Q, m.P) != (Q, P):
-            raise ValueError("stack_packs: experts differ in shape")
-        if m.esc_idx.numel():
-            raise ValueError("stack_packs: an expert carries escape entries (the grouped kernels have no escape pass)")
-        if m.device != dev:
-            raise ValueError("stack_packs: experts live on different devices")
-    if P % 8:
-        raise ValueError("stack_packs: P must be a multiple of 8")
-    offs, total = [], 0
-    for m in members:
-        offs.append(total)
-        total += (m.ids.numel() + 15) // 16 * 16
-    ids_all = torch.zeros(total + STACK_PAD, dtype=torch.uint8, device=dev)
-    for off, m in zip(offs, members):
-        ids_all[off:off + m.ids.numel()].copy_(m.ids)
-    return dict(ids=ids_all, min_s=torch.stack([m.min_s for m in members]).contiguous(),
-                tau_s=torch.stack([m.tau_s for m in members]).contiguous(),
-                nbits=torch.stack([m.nbits for m in members]).contiguous(),
-                bit_off=torch.stack([m.bit_off + o * 8 for m, o in zip(members, offs)]).contiguous(), Q=Q, P=P)
+    first = members[0]
+    problems = [f"expert {e}: " + why for e, m in enumerate(members) for ok, why in (
+        ((m.Q, m.P) == (first.Q, first.P), f"shape {(m.Q, m.P)} differs from {(first.Q, first.P)}"),
+        (m.esc_idx.numel() == 0, "carries escape entries (the grouped kernels have no escape pass)"),
+        (m.device == first.device, "lives on another device")) if not ok]
+    if first.P % 8:
+        problems.append(f"P = {first.P} is not a multiple of 8")
+    if problems:
+        raise ValueError("stack_packs: " + "; ".join(problems))
+    sizes = torch.tensor([m.ids.numel() for m in members], dtype=torch.int64)
+    padded = (sizes + 15) // 16 * 16
+    starts = torch.cumsum(padded, 0) - padded                           # byte offset of every expert's payload
+    payload = torch.zeros(int(padded.sum()) + STACK_PAD, dtype=torch.uint8, device=first.device)
+    for m, start in zip(members, starts.tolist()):
+        payload.narrow(0, start, m.ids.numel()).copy_(m.ids)
+    per_row = lambda field: torch.stack([getattr(m, field) for m in members]).contiguous()
+    bit_off = per_row("bit_off") + (starts * 8).to(first.device)[:, None]
+    return dict(ids=payload, min_s=per_row("min_s"), tau_s=per_row("tau_s"), nbits=per_row("nbits"),
+                bit_off=bit_off.contiguous(), Q=first.Q, P=first.P)
 
 
 class QVBandExpertsV8(torch.nn.Module):

@@ -127,6 +127,103 @@ class Qvb8rExt:
                                                      _lib.stream_ptr(dev)), "qvb8r_fix_escapes")
 
 
+    # ---- the reference extension's host-side entry points (qvb8r_cuda.cu:453-455) ------------------------------
+    def embed_rows(self, rows, words, off, states, tiles, tab, inv_perm, row_tile, mn, ts, drow, esc_ptr, esc_col,
+                   esc_val, P):
+        """(n, P) fp32 rows of an entropy-coded embedding table, escapes written over (qvb8r_cpu.cpp:13-58).  The
+        reference hands HOST tensors here and decodes on the host, because its target cards cannot hold the table; on
+        a B200 the table is uploaded once (cached on the `words` tensor object) and the rows are decoded by
+        ``qvb8r_embed_rows`` on the device.  The result comes back on the host, as the caller expects."""
+        if int(P) % 128:
+            raise RuntimeError("qvb8r embed_rows: P % 128 == 0")
+        table = words.__dict__.get("_qvb8r_device_table") if hasattr(words, "__dict__") else None
+        if table is None:
+            table = EmbeddingTable(words, off, states, tiles, tab, inv_perm, row_tile, mn, ts, drow, esc_ptr, esc_col,
+                                   esc_val, int(P), torch.device("cuda", torch.cuda.current_device()))
+            if hasattr(words, "__dict__"):
+                words.__dict__["_qvb8r_device_table"] = table
+        Q = table.Q
+        rows = rows.reshape(-1).to(torch.int64)
+        if rows.numel() and (int(rows.min()) < 0 or int(rows.max()) >= Q):
+            raise RuntimeError("qvb8r embed_rows: row id out of range")
+        return table.lookup(rows.to(table.device)).cpu()
+
+    def encode(self, sym, tiles, F, C):
+        """rANS-code (R, P) int16 symbols in sorted row order -> [words i32, tile_off i64, states i64]
+        (qvb8r_cpu.cpp:60-110).  A writer's tool, run once per tensor on the host."""
+        if sym.dtype != torch.int16 or sym.dim() != 2 or sym.shape[1] % 128 or not sym.is_contiguous():
+            raise RuntimeError("qvb8r encode: sym must be contiguous (R, P) int16, P % 128 == 0")
+        if tiles.dtype != torch.int64 or F.dtype != torch.int64 or C.dtype != torch.int64:
+            raise RuntimeError("qvb8r encode: int64 tables")
+        t = tiles.cpu().numpy().reshape(-1, 3)
+        states, words, tile_off = rans.encode_symbols(sym.cpu().numpy(), t[:, 0], t[:, 2], F.cpu().numpy())
+        return [torch.from_numpy(words.view(np.int32).copy()), torch.from_numpy(tile_off.astype(np.int64)),
+                torch.from_numpy(states.view(np.int64).copy())]
+
+    def row_hist(self, sym, N):
+        """(R, N) int32 histogram of every row's int16 symbols in [0, N) (qvb8r_cpu.cpp:112-121)."""
+        if sym.dtype != torch.int16 or sym.dim() != 2 or not sym.is_contiguous():
+            raise RuntimeError("qvb8r row_hist: (R, P) int16")
+        s = sym.cpu().numpy().astype(np.int64)
+        if s.size and (s.min() < 0 or s.max() >= int(N)):
+            raise RuntimeError("qvb8r row_hist: symbol outside [0, N)")
+        R = s.shape[0]
+        flat = (np.arange(R, dtype=np.int64)[:, None] * int(N) + s).ravel()
+        return torch.from_numpy(np.bincount(flat, minlength=R * int(N)).reshape(R, int(N)).astype(np.int32))
+
+
+class EmbeddingTable:
+    """An entropy-coded embedding table resident on one device + the row lookup kernel."""
+
+    def __init__(self, words, off, states, tiles, tab, inv_perm, row_tile, mn, ts, drow, esc_ptr, esc_col, esc_val, P: int,
+                 device):
+        dev = torch.device(device)
+        up = lambda t, dt: t.to(device=dev, dtype=dt).contiguous()
+        self.device, self.P, self.Q = dev, int(P), int(mn.numel())
+        tiles_d = up(tiles, torch.int64)
+        blocks = torch.from_numpy(rans.blocks_for(tiles.cpu().numpy().reshape(-1, 3), TILES_PER_BLOCK)).to(dev)
+        perm = torch.empty(self.Q, dtype=torch.int32)
+        perm[inv_perm.cpu().long()] = torch.arange(self.Q, dtype=torch.int32)
+        self.core = (up(words, torch.int32), up(off, torch.int64), up(states, torch.int64), tiles_d, blocks.contiguous(),
+                     up(tab, torch.int32), perm.to(dev), up(mn, torch.float32), up(ts, torch.float32), up(drow, torch.int32))
+        self.inv_perm, self.row_tile = up(inv_perm, torch.int32), up(row_tile, torch.int32)
+        self.esc_ptr, self.esc_col, self.esc_val = up(esc_ptr, torch.int64), up(esc_col, torch.int32), up(esc_val, torch.float32)
+
+    def lookup(self, rows: torch.Tensor) -> torch.Tensor:
+        """(n, P) fp32 on the table's device; `rows` int64 on that device."""
+        st, dev = _struct(self.P, *self.core)
+        rows = rows.contiguous()
+        out = torch.empty((rows.numel(), self.P), dtype=torch.float32, device=dev)
+        if rows.numel():
+            null = lambda t: t.data_ptr() if t.numel() else None
+            with torch.cuda.device(dev):
+                _lib.check(_lib.load().qvb8r_embed_rows(ctypes.byref(st), rows.data_ptr(), rows.numel(),
+                                                        self.inv_perm.data_ptr(), self.row_tile.data_ptr(),
+                                                        self.esc_ptr.data_ptr(), null(self.esc_col), null(self.esc_val),
+                                                        out.data_ptr(), _lib.stream_ptr(dev)), "qvb8r_embed_rows")
+        return out
+
+    @classmethod
+    def from_parsed(cls, d: dict, device) -> "EmbeddingTable":
+        """From a parsed .qvb8r dict (packs.read_qvb8r): builds the per-row tables a lookup needs."""
+        Q, P = int(d["Q"]), int(d["P"])
+        tiles = np.asarray(d["tiles"], np.int64).reshape(-1, 3)
+        inv = np.empty(Q, np.int32)
+        inv[np.asarray(d["perm"], np.int64)] = np.arange(Q, dtype=np.int32)
+        row_tile = np.repeat(np.arange(len(tiles), dtype=np.int32), tiles[:, 2])
+        pos = np.asarray(d["esc_idx"], np.int64)
+        order = np.argsort(pos, kind="stable")
+        ptr = np.concatenate([[0], np.cumsum(np.bincount(pos // P, minlength=Q))]).astype(np.int64)
+        T = torch.from_numpy
+        words = np.concatenate([np.asarray(d["words"], np.uint32), np.zeros(rans.PAD_WORDS, np.uint32)])
+        return cls(T(words.view(np.int32)), T(np.asarray(d["tile_off"]).astype(np.int64)),
+                   T(np.ascontiguousarray(np.asarray(d["states"], np.uint64).reshape(-1)).view(np.int64)), T(tiles),
+                   T(rans.slot_tables(np.asarray(d["freq"])).view(np.int32)), T(inv), T(row_tile),
+                   T(np.asarray(d["min_s"], np.float32)), T(np.asarray(d["tau_s"], np.float32)),
+                   T(np.asarray(d["drow"]).astype(np.int32)), T(ptr), T((pos % P)[order].astype(np.int32)),
+                   T(np.asarray(d["esc_val"], np.float32)[order]), P, device)
+
+
 ext = Qvb8rExt()
 
 

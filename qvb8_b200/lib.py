@@ -27,6 +27,7 @@ EXPORTS = (
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
     "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
     "qvb8_embed_rows", "qvb8_peer_bytes", "qvb8_peer_alloc", "qvb8_peer_open", "qvb8_peer_close", "qvb8_peer_allreduce",
+    "qvb8_peer_allreduce_ex", "qvb8_peer_allreduce_local", "qvb8_device_status_reset", "qvb8r_embed_rows",
 )
 
 
@@ -104,6 +105,10 @@ def load() -> ctypes.CDLL:
             lib.qvb8_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
             lib.qvb8_peer_close.argtypes = [vp, ci]
             lib.qvb8_peer_allreduce.argtypes = [ctypes.POINTER(vp), ci, ci, i64, vp, vp, vp, i64, ci, vp]
+            lib.qvb8_peer_allreduce_ex.argtypes = [ctypes.POINTER(vp), ci, ci, i64, vp, vp, vp, i64, ci, ctypes.c_uint64, vp]
+            lib.qvb8_peer_allreduce_local.argtypes = [ctypes.POINTER(vp), ci, i64, ctypes.POINTER(vp), ctypes.POINTER(vp),
+                                                      ctypes.POINTER(vp), i64, ctypes.c_uint64, vp]
+            lib.qvb8_device_status_reset.argtypes = []
             lib.qvb8_prefill_set_tuning.argtypes = [ci]
             lib.qvb8_prefill_set_tuning.restype = None
             es = ctypes.POINTER(ExpertStackStruct)
@@ -112,6 +117,7 @@ def load() -> ctypes.CDLL:
             lib.qvb8r_decode.argtypes = [rp, ci, vp, i64, i64, i64, vp]
             lib.qvb8r_small_m.argtypes = [rp, vp, ci, i64, ci, vp, vp]
             lib.qvb8r_fix_escapes.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]
+            lib.qvb8r_embed_rows.argtypes = [rp, vp, i64, vp, vp, vp, vp, vp, vp, vp]
             lib.qvb8_moe_scratch_bytes.argtypes = [i64, i64, i64, i64, i64, i64, ci]
             lib.qvb8_moe_scratch_bytes.restype = i64
             lib.qvb8_moe_experts.argtypes = [vp, ci, i64, vp, vp, i64, i64, es, es, ci, vp, vp, i64, vp]

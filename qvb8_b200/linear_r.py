@@ -1,22 +1,27 @@
-"""``QVBandLinearV8R``: an ``nn.Linear`` replacement whose weight lives in device memory only as an entropy-coded
-QVB8R pack.
+"""``QVBandLinearV8R``: a linear layer whose weight exists on the device only as an entropy-coded QVB8R pack.
 
-Mirrors the reference module of the same name (formats/qvb8r/module.py:57-325): buffers built from a parsed
-``.qvb8r`` dict, ``from_packfile``, ``forward`` dispatch by the row count M of the flattened input, ``dense``.
+Public surface of the reference module of the same name (formats/qvb8r/module.py:57-325): constructed from a parsed
+``.qvb8r`` dict or ``from_packfile``; ``forward`` picks a kernel by the row count M of the flattened input; ``dense``
+returns the exact weight for audits.
 
-    M = 1        ``gemv``   fp32 band value x fp32 activation
-    M = 2..8     ``multi``  the same for several rows (a bf16 activation is read as it is: exact in fp32)
-    M = 9..16    ``tc``     band value rounded once to fp16 x saturated-fp16 activation
-    M = 17..48   equal passes of <= 16 rows through ``tc`` (module.py:303-312)
-    M  > 48      the weight is restored chunk by chunk (whole blocks, <= CHUNK_BYTES of fp16 each) in sorted row order,
-                 escapes written over, rows put back in output order, one fp16 GEMM with fp32 accumulation per chunk
+    M = 1        ``gemv``    fp32 band value x fp32 activation
+    M = 2..8     ``multi``   the same for several rows (bf16 activations are read as they are: exact in fp32)
+    M = 9..16    ``tc``      band value rounded once to fp16 x activation narrowed to saturated fp16
+    M = 17..48   equal passes of at most 16 rows through ``tc``
+    M > 48       the weight is restored to fp16 and multiplied by one library GEMM per chunk
 
-After every kernel product the escape pass adds ``sum_e x[m, c_e] * delta_e`` per output in stored order
-(module.py:212-214); for the ``tc`` path the differences are taken against the fp16-rounded band value (:121-124).
-One escape table (the file's) is kept; the reference's split fp16 / bf16 tables and its disk-resident mode are loader
-features outside the product path.
+Escapes (weights stored exactly because the band could not certify them) are added after every kernel product as
+``y[m, q] += sum_e x[m, c_e] * (exact_e - band_e)`` in stored order; the differences are kept twice, against the fp32
+band value (``gemv`` / ``multi``) and against its fp16 rounding (``tc``).
+
+Many rows, this library's way: a B200 holds any single weight of the model families in scope dense in 16 bits next to
+the packs (the largest, a 248k x 5120 vocabulary projection, is 2.5 GB), so the whole weight is restored straight
+into ORIGINAL row order by one decode launch and multiplied by one GEMM; only weights above ``RESTORE_BYTES`` fall back
+to chunks of whole blocks in sorted row order (the reference's scheme for small cards, module.py:127-161, 249-277).
 """
 from __future__ import annotations
+
+import dataclasses
 
 import numpy as np
 import torch
@@ -25,13 +30,62 @@ import torch.nn as nn
 from . import packs, rans
 from .ext_qvb8r import TILES_PER_BLOCK, core_tensors, ext
 
-FP32_METADATA = ("min_s", "tau_s", "esc_val", "esc_delta", "esc_delta16", "chunk_evals")
-TC_MAX = 16
-TC_SPLIT_MAX = 48
+ROWS_PER_TC_PASS = 16
+MAX_KERNEL_ROWS = 48
+_FP32_BUFFERS = ("min_s", "tau_s", "esc_val", "esc_delta", "esc_delta16", "chunk_esc_val")
+
+
+@dataclasses.dataclass(frozen=True)
+class Chunk:
+    """A run of whole blocks restored together: blocks [block0, block0 + nblocks) hold the sorted rows
+    [row0, row0 + rows); its escapes are entries [esc0, esc1) of the chunk-ordered escape arrays."""
+    block0: int
+    nblocks: int
+    row0: int
+    rows: int
+    esc0: int
+    esc1: int
+
+
+def plan_chunks(tiles: np.ndarray, blocks: np.ndarray, row_budget: int) -> list[tuple[int, int, int, int]]:
+    """Cuts the block schedule into runs of at most `row_budget` sorted rows (a single block may exceed it).  Returns
+    (first block, blocks, first sorted row, rows) per run.  Works on the cumulative row count: the end of a run is the
+    last block whose cumulative end stays within the budget counted from the run's start."""
+    tiles = np.asarray(tiles, np.int64).reshape(-1, 3)
+    blocks = np.asarray(blocks, np.int64).reshape(-1, 3)
+    tile_end = np.cumsum(tiles[:, 2])
+    block_end = tile_end[blocks[:, 1] + blocks[:, 2] - 1]              # sorted rows covered up to and including a block
+    block_begin = np.concatenate([[0], block_end[:-1]])
+    runs, b, nb = [], 0, len(blocks)
+    while b < nb:
+        limit = block_begin[b] + max(1, int(row_budget))
+        e = int(np.searchsorted(block_end, limit, side="right"))       # first block that would overflow the budget
+        e = max(e, b + 1)
+        runs.append((b, e - b, int(block_begin[b]), int(block_end[e - 1] - block_begin[b])))
+        b = e
+    return runs
+
+
+def escape_tables(d: dict):
+    """Host arrays for the escape pass, from a parsed file: rows that have escapes, their ranges (CSR), columns, the
+    stored differences and the differences against the fp16-rounded band value; all sorted by (row, column)."""
+    P = int(d["P"])
+    pos = np.asarray(d["esc_idx"], np.int64)
+    order = np.argsort(pos, kind="stable")
+    pos = pos[order]
+    exact = np.asarray(d["esc_val"], np.float32)[order]
+    delta = np.asarray(d["esc_delta"], np.float32)[order]
+    band = exact - delta                                               # the fp32 band value the difference was taken from
+    delta16 = exact - band.astype(np.float16).astype(np.float32)
+    rows, first = np.unique(pos // P, return_index=True)
+    ranges = np.append(first, pos.size).astype(np.int64)
+    return dict(esc_uq=rows.astype(np.int64), esc_ptr=ranges, esc_c=(pos % P).astype(np.int64), esc_delta=delta,
+                esc_delta16=delta16.astype(np.float32), esc_flat=pos, esc_val=exact)
 
 
 class QVBandLinearV8R(nn.Module):
-    CHUNK_BYTES = 512 << 20       # decoded fp16 weight per GEMM in the many-rows path (module.py:63)
+    RESTORE_BYTES = 4 << 30        # dense fp16 bytes restored at once in the many-rows route
+    CHUNK_BYTES = None             # test hook: a smaller budget forces the chunked route
 
     def __init__(self, d: dict, bias=None, device="cuda", path: str | None = None):
         super().__init__()
@@ -39,154 +93,129 @@ class QVBandLinearV8R(nn.Module):
         Q, P = int(d["Q"]), int(d["P"])
         self.out_features, self.in_features, self.T = Q, P, int(d["T"])
         dev = torch.device(device)
-        names = ("words", "off", "states", "tiles", "blocks8", "tab", "perm", "min_s", "tau_s", "drow")
-        for name, t in zip(names, core_tensors(d, dev)):
+        for name, t in zip(("words", "off", "states", "tiles", "blocks8", "tab", "perm", "min_s", "tau_s", "drow"),
+                           core_tensors(d, dev)):
             self.register_buffer(name, t, persistent=False)
-        t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=dt)).to(dev)
-        # escapes grouped by output row (CSR, sorted by row then column): one thread per (m, q) sums its group in this
-        # fixed order
-        ei = np.asarray(d["esc_idx"], np.int64)
-        ev = np.asarray(d["esc_val"], np.float32)
-        ed = np.asarray(d["esc_delta"], np.float32)
-        o = np.argsort(ei, kind="stable")
-        ei, ev, ed = ei[o], ev[o], ed[o]
-        uq, cnt = np.unique(ei // P, return_counts=True)
-        band = ev - ed
-        for name, a, dt in (("esc_uq", uq, np.int64), ("esc_ptr", np.concatenate([[0], np.cumsum(cnt)]), np.int64),
-                            ("esc_c", ei % P, np.int64), ("esc_delta", ed, np.float32),
-                            ("esc_delta16", ev - band.astype(np.float16).astype(np.float32), np.float32),
-                            ("esc_flat", ei, np.int64), ("esc_val", ev, np.float32)):
-            self.register_buffer(name, t(a, dt), persistent=False)
-        self.bias = None if bias is None else nn.Parameter(bias.detach().to(dev), requires_grad=False)
 
-        # many rows: chunks of whole blocks and the escapes inside each.  Per chunk: first block, blocks, first sorted
-        # row, rows, [o0, o1) into chunk_orows, [e0, e1) into chunk_eflat / chunk_evals  (module.py:127-161)
+        def put(name, a, dt):
+            self.register_buffer(name, torch.from_numpy(np.ascontiguousarray(a, dtype=dt)).to(dev), persistent=False)
+        esc = escape_tables(d)
+        for name, a in esc.items():
+            put(name, a, np.float32 if a.dtype == np.float32 else np.int64)
+        self.bias = nn.Parameter(torch.as_tensor(bias).detach().to(dev), requires_grad=False) if bias is not None else None
+
+        # the chunked route's tables (used only above the restore budget): per chunk its blocks and sorted rows, the
+        # original rows of those sorted rows, and the chunk's escapes as positions inside the chunk
         tiles = np.asarray(d["tiles"], np.int64).reshape(-1, 3)
         blocks = rans.blocks_for(tiles, TILES_PER_BLOCK)
+        budget_bytes = self.CHUNK_BYTES if self.CHUNK_BYTES is not None else self.RESTORE_BYTES
+        runs = plan_chunks(tiles, blocks, max(1, int(budget_bytes) // (2 * P)))
         perm = np.asarray(d["perm"], np.int64)
-        inv = np.empty(Q, np.int64)
-        inv[perm] = np.arange(Q)
-        rows_per_block = [int(tiles[t0:t0 + n, 2].sum()) for _, t0, n in blocks]
-        first_row = [int(tiles[t0, 1]) for _, t0, n in blocks]
-        budget = max(1, self.CHUNK_BYTES // (2 * P))
-        spans, orows, b, o0 = [], [], 0, 0
-        while b < len(blocks):
-            e, rows = b, 0
-            while e < len(blocks) and (e == b or rows + rows_per_block[e] <= budget):
-                rows += rows_per_block[e]
-                e += 1
-            base = first_row[b]
-            orows.append(perm[base:base + rows])
-            spans.append((b, e - b, base, rows, o0, o0 + rows))
-            o0 += rows
-            b = e
-        sp = inv[ei // P] if ei.size else np.zeros(0, np.int64)
-        flat, vals, self.chunks, e0 = [], [], [], 0
-        for span in spans:
-            base, rows = span[2], span[3]
-            sel = np.nonzero((sp >= base) & (sp < base + rows))[0]
-            flat.append((sp[sel] - base) * P + ei[sel] % P)
-            vals.append(ev[sel])
-            self.chunks.append(span + (e0, e0 + len(sel)))
-            e0 += len(sel)
-        cat = lambda xs, dt: np.concatenate(xs).astype(dt) if xs else np.zeros(0, dt)
-        self.register_buffer("chunk_orows", t(cat(orows, np.int64), np.int64), persistent=False)
-        self.register_buffer("chunk_eflat", t(cat(flat, np.int64), np.int64), persistent=False)
-        self.register_buffer("chunk_evals", t(cat(vals, np.float32), np.float32), persistent=False)
+        sorted_pos_of = np.empty(Q, np.int64)
+        sorted_pos_of[perm] = np.arange(Q)
+        esc_sorted_row = sorted_pos_of[esc["esc_flat"] // P] if esc["esc_flat"].size else np.zeros(0, np.int64)
+        by_sorted = np.argsort(esc_sorted_row, kind="stable")
+        srow, scol, sval = esc_sorted_row[by_sorted], (esc["esc_flat"] % P)[by_sorted], esc["esc_val"][by_sorted]
+        starts = np.asarray([r[2] for r in runs], np.int64)
+        cut = np.searchsorted(srow, np.append(starts, Q), side="left")
+        which = np.searchsorted(starts, srow, side="right") - 1 if srow.size else np.zeros(0, np.int64)
+        self.chunks = [Chunk(b0, nb, r0, nr, int(cut[i]), int(cut[i + 1])) for i, (b0, nb, r0, nr) in enumerate(runs)]
+        put("chunk_rows", perm, np.int64)                               # sorted position -> original row
+        put("chunk_esc_pos", (srow - starts[which]) * P + scol if srow.size else srow, np.int64)
+        put("chunk_esc_val", sval, np.float32)
+        self.whole = len(self.chunks) == 1
 
     @classmethod
     def from_packfile(cls, path: str, *, bias=None, tau: float | None = None, device: str = "cuda",
                       blob: bytes | None = None) -> "QVBandLinearV8R":
-        """`tau` is accepted for call-site compatibility and ignored: each file carries its own certified tau."""
+        """The loader's entry point.  `tau` is accepted and unused: every file states its own certified tau."""
         if blob is None:
-            with open(path, "rb") as f:
-                blob = f.read()
+            with open(path, "rb") as fh:
+                blob = fh.read()
         return cls(packs.read_qvb8r(blob, str(path)), bias=bias, device=device, path=path)
 
     def _apply(self, fn, recurse=True):
-        """module.to(...) / .half() / .bfloat16(): the fp32 metadata only ever changes DEVICE (module.py:188-202)."""
-        keep = {n: self._buffers[n] for n in FP32_METADATA if self._buffers.get(n) is not None}
-        for n in keep:
-            self._buffers[n] = None
+        """Casts of the module never touch the fp32 data of the format; it only follows the stream to a new device."""
+        held = {n: self._buffers.pop(n) for n in _FP32_BUFFERS}
         try:
-            out = super()._apply(fn, recurse)
+            super()._apply(fn, recurse)
         finally:
             dev = self._buffers["words"].device
-            for n, b in keep.items():
-                self._buffers[n] = b.to(dev)
-        return out
+            for n, t in held.items():
+                self._buffers[n] = t if t.device == dev else t.to(dev)
+        return self
 
     def extra_repr(self):
-        return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}"
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
+                f"tile_rows={self.T}")
 
-    # ---- kernel paths -------------------------------------------------------------------------------------
-    def _core(self):
+    # ---- kernel routes --------------------------------------------------------------------------------------
+    def core(self) -> tuple:
+        """The ten tensors every entry point of the extension takes after its activations."""
         return (self.words, self.off, self.states, self.tiles, self.blocks8, self.tab, self.perm, self.min_s,
                 self.tau_s, self.drow)
 
-    def _escapes(self, xf, y, delta):
-        y = y.contiguous()
-        ext.fix_escapes(xf, self.esc_uq, self.esc_ptr, self.esc_c, delta, y)
+    def _add_escapes(self, x32: torch.Tensor, y: torch.Tensor, differences: torch.Tensor) -> torch.Tensor:
+        y = y if y.is_contiguous() else y.contiguous()
+        ext.fix_escapes(x32, self.esc_uq, self.esc_ptr, self.esc_c, differences, y)
         return y
 
-    def _gemv(self, x2):
-        xf = x2.float().contiguous()
-        return self._escapes(xf, ext.gemv(xf.view(-1), *self._core()).view(1, -1), self.esc_delta)
+    def _few_rows(self, x2: torch.Tensor) -> torch.Tensor:
+        """1..16 rows through the decoding kernels, escapes added."""
+        M = x2.shape[0]
+        x32 = x2.float().contiguous()
+        if M == 1:
+            return self._add_escapes(x32, ext.gemv(x32.reshape(-1), *self.core()).reshape(1, -1), self.esc_delta)
+        if M <= 8:
+            xin = x2.contiguous() if x2.dtype == torch.bfloat16 else x32
+            return self._add_escapes(x32, ext.multi(xin, *self.core()), self.esc_delta)
+        x16 = x32.clamp(min=-65504.0, max=65504.0).to(torch.float16)
+        return self._add_escapes(x32, ext.tc(x16, *self.core(), self.T), self.esc_delta16)
 
-    def _multi(self, x2):
-        xf = x2.float().contiguous()
-        xk = x2.contiguous() if x2.dtype == torch.bfloat16 else xf
-        return self._escapes(xf, ext.multi(xk, *self._core()), self.esc_delta)
-
-    def _tc(self, x2):
-        xf = x2.float().contiguous()
-        xh = xf.clamp(-65504, 65504).half().contiguous()
-        return self._escapes(xf, ext.tc(xh, *self._core(), self.T), self.esc_delta16)
-
-    def _chunked(self, x2):
-        xh = x2.half()
-        xh = xh.clamp(-65504, 65504) if xh is x2 else xh.clamp_(-65504, 65504)
-        y = torch.empty(x2.shape[0], self.out_features, device=x2.device, dtype=torch.float32)
-        for b0, nb, base, rows, o0, o1, e0, e1 in self.chunks:
-            W = ext.decode(*self._core(), self.in_features, 0, b0, nb, base, rows)
-            if e1 > e0:
-                W.view(-1)[self.chunk_eflat[e0:e1]] = self.chunk_evals[e0:e1].half()
-            if len(self.chunks) == 1:                   # rows back in output order: the GEMM writes y directly
-                Wo = torch.empty_like(W).index_copy_(0, self.chunk_orows[o0:o1], W)
-                return torch.mm(xh, Wo.t(), out_dtype=torch.float32)
-            y[:, self.chunk_orows[o0:o1]] = torch.mm(xh, W.t(), out_dtype=torch.float32)
+    def _many_rows(self, x2: torch.Tensor) -> torch.Tensor:
+        """Restore to fp16 + library GEMM with fp32 accumulation and fp32 result."""
+        x16 = x2.float().clamp(min=-65504.0, max=65504.0).to(torch.float16)
+        P = self.in_features
+        if self.whole:
+            # one decode launch writes every row at its original index; escapes by their original positions
+            W = ext.decode(*self.core(), P, 0, 0, self.blocks8.shape[0], -1, 0)
+            if self.esc_flat.numel():
+                W.view(-1)[self.esc_flat] = self.esc_val.to(torch.float16)
+            return torch.mm(x16, W.t(), out_dtype=torch.float32)
+        y = torch.empty((x2.shape[0], self.out_features), dtype=torch.float32, device=x2.device)
+        for c in self.chunks:
+            W = ext.decode(*self.core(), P, 0, c.block0, c.nblocks, c.row0, c.rows)       # sorted rows, compact
+            if c.esc1 > c.esc0:
+                W.view(-1)[self.chunk_esc_pos[c.esc0:c.esc1]] = self.chunk_esc_val[c.esc0:c.esc1].to(torch.float16)
+            y[:, self.chunk_rows[c.row0:c.row0 + c.rows]] = torch.mm(x16, W.t(), out_dtype=torch.float32)
         return y
 
-    def _path(self, M: int):
-        return self._gemv if M == 1 else self._multi if M <= 8 else self._tc if M <= TC_MAX else self._chunked
-
-    def forward(self, x):
-        shp = x.shape
-        x2 = x.reshape(-1, shp[-1])
-        if x2.device != self.words.device:
-            x2 = x2.to(self.words.device)
-        out_dtype = x.dtype
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1]).to(self.words.device)
+        result_dtype = x.dtype
         if x2.dtype == torch.float32 and torch.is_autocast_enabled(x2.device.type):
-            ad = torch.get_autocast_dtype(x2.device.type)
-            if ad in (torch.bfloat16, torch.float16):
-                x2, out_dtype = x2.to(ad), ad
+            cast_to = torch.get_autocast_dtype(x2.device.type)          # behave like nn.Linear under autocast
+            if cast_to in (torch.float16, torch.bfloat16):
+                x2, result_dtype = x2.to(cast_to), cast_to
         M = x2.shape[0]
         if M == 0:
-            return x2.new_empty(*shp[:-1], self.out_features, dtype=out_dtype)
-        if TC_MAX < M <= TC_SPLIT_MAX:                   # equal tensor-core passes of <= 16 rows
-            n = -(-M // TC_MAX)
-            step = -(-M // n)
-            y = torch.cat([self._path(min(M - i, step))(x2[i:i + step]) for i in range(0, M, step)])
+            return torch.empty(*lead, self.out_features, dtype=result_dtype, device=x2.device)
+        if M <= ROWS_PER_TC_PASS:
+            y = self._few_rows(x2)
+        elif M <= MAX_KERNEL_ROWS:
+            passes = -(-M // ROWS_PER_TC_PASS)
+            y = torch.cat([self._few_rows(part) for part in torch.tensor_split(x2, passes, dim=0)])
         else:
-            y = self._path(M)(x2)
+            y = self._many_rows(x2)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
-        return y.to(out_dtype).reshape(*shp[:-1], self.out_features)
+        return y.to(result_dtype).reshape(*lead, self.out_features)
 
-    def dense(self, dtype=torch.bfloat16):
-        """The exact weight (Q, P) in `dtype`, escapes applied: for audits, never on the product path."""
-        code = {torch.float16: 0, torch.bfloat16: 1}.get(dtype, 2)
-        W = ext.decode(*self._core(), self.in_features, code, 0, self.blocks8.shape[0], -1, 0)
+    def dense(self, dtype=torch.bfloat16) -> torch.Tensor:
+        """The exact (Q, P) weight rounded to `dtype`, escapes written over: for audits, not a product path."""
+        code = 0 if dtype == torch.float16 else 1 if dtype == torch.bfloat16 else 2
+        W = ext.decode(*self.core(), self.in_features, code, 0, self.blocks8.shape[0], -1, 0)
         if self.esc_flat.numel():
             W.view(-1)[self.esc_flat] = self.esc_val.to(W.dtype)
-        return W.to(dtype)
+        return W if W.dtype == dtype else W.to(dtype)

@@ -166,6 +166,35 @@ def write_escape_tables(folder: str, entries: dict) -> None:
 # ---------------------------------------------------------------------------------------------------------------
 # readers
 
+def validate_pack(d: dict, where: str = "pack") -> dict:
+    """Bounds of a parsed pack, checked on the host before anything is uploaded: the kernels trust these fields, so a
+    cut-short or damaged file must be refused here and never become an out-of-range read on the device.  Row widths
+    1..14, every row's bit range (plus the 8 pad bytes the readers may touch) inside the payload, escape positions
+    ascending and inside the weight."""
+    Q, P = int(d["Q"]), int(d["P"])
+    nbits = np.asarray(d["nbits"], np.int64)
+    bit_off = np.asarray(d["bit_off"], np.int64)
+    if Q < 0 or P <= 0 or nbits.shape != (Q,) or bit_off.shape != (Q,) or len(d["min_s"]) != Q or len(d["tau_s"]) != Q:
+        raise PackFormatError(f"{where}: per-row arrays do not have Q = {Q} entries")
+    if Q:
+        if nbits.min() < 1 or nbits.max() > MAX_CERTIFIED_NBITS:
+            raise PackFormatError(f"{where}: row width outside 1..{MAX_CERTIFIED_NBITS} bits")
+        if bit_off.min() < 0:
+            raise PackFormatError(f"{where}: negative row offset")
+        last_byte = int(((bit_off + nbits * P + 7) >> 3).max())
+        if last_byte + PAYLOAD_PAD > len(d["ids"]):
+            raise PackFormatError(f"{where}: a row ends at byte {last_byte} (+{PAYLOAD_PAD} pad bytes) but the payload "
+                                  f"holds {len(d['ids'])} bytes (cut-short or damaged file)")
+    for key in ("esc_idx", "esc_idx_bf16"):
+        ei = np.asarray(d.get(key, ()), np.int64)
+        vals = d.get("esc_vals" if key == "esc_idx" else "esc_vals_bf16", ())
+        if ei.size != len(vals):
+            raise PackFormatError(f"{where}: {key} and its values differ in length")
+        if ei.size and (ei.min() < 0 or ei.max() >= Q * P or np.any(np.diff(ei) < 0)):
+            raise PackFormatError(f"{where}: {key} is not an ascending list of positions inside the weight")
+    return d
+
+
 def _need(blob, cur, n, what):
     if cur + n > len(blob):
         raise PackFormatError(f"truncated pack: {what} needs {n} bytes at {cur}, blob has {len(blob)}")
@@ -225,7 +254,7 @@ def read_qvbd(blob: bytes, path: str | None = None) -> dict:
             out["esc_idx"], out["esc_vals"] = esc_idx[keep], esc_vals[keep]
     else:
         out["esc_idx"], out["esc_vals"] = esc_idx, esc_vals
-    return out
+    return validate_pack(out, path or "QVBD blob")
 
 
 def read_qvb8_legacy(blob: bytes) -> dict:
@@ -260,10 +289,10 @@ def read_qvb8_legacy(blob: bytes) -> dict:
         s8 = np.frombuffer(blob, "<f4", Q, cur).copy(); cur += 4 * Q
         esc_idx, esc_vals = merge_escape_pools(e32_idx, e32_vals, e8_idx, e8_codes, s8, P)
     ids = np.frombuffer(blob, np.uint8, offset=cur).copy()
-    return dict(container="QVB8", Q=int(Q), P=int(P), tau=float(tau), max_err=float("nan"), source="bf16",
+    return validate_pack(dict(container="QVB8", Q=int(Q), P=int(P), tau=float(tau), max_err=float("nan"), source="bf16",
                 restore="fp16", min_s=min_s, tau_s=tau_s, nbits=nbits, bit_off=bit_off, ids=ids,
                 esc_idx=esc_idx, esc_vals=esc_vals, esc_idx_bf16=esc_idx, esc_vals_bf16=esc_vals,
-                fp16_table_missing=False)
+                fp16_table_missing=False), "QVB8 blob")
 
 
 def read_qvb8(blob: bytes, path: str | None = None) -> dict:
@@ -292,9 +321,11 @@ def read_qvb8_shape(blob: bytes) -> tuple[int, int]:
 # writers (the reference ships readers only; these emit bytes its readers parse)
 
 def write_qvbd(*, Q, P, tau, max_err, min_s, tau_s, nbits, ids, esc_idx, esc_vals, source="bf16",
-               restore="fp16") -> bytes:
-    """`ids` is the bit payload INCLUDING its 8 pad bytes; escapes are the pack's full list (values must be exactly
-    representable in the source type: they are stored as bf16 bits for a 16-bit source)."""
+               restore="fp16", fp8_idx=None, fp8_codes=None, fp8_scale=None) -> bytes:
+    """`ids` is the bit payload INCLUDING its 8 pad bytes; esc_idx / esc_vals are the escapes kept at full width
+    (values must be exactly representable in the source type: they are stored as bf16 bits for a 16-bit source).
+    fp8_idx / fp8_codes / fp8_scale: the escapes kept as E4M3 codes with a per-row scale f32[Q] (the second pool of
+    the container, pack_container.py:14-20); a reader merges both pools into one list."""
     nbits = np.asarray(nbits, np.uint8)
     ids = np.asarray(ids, np.uint8)
     if len(ids) != payload_bytes(nbits, P) + PAYLOAD_PAD:
@@ -310,10 +341,19 @@ def write_qvbd(*, Q, P, tau, max_err, min_s, tau_s, nbits, ids, esc_idx, esc_val
         raw = (bits >> 16).astype("<u2").tobytes()
     hdr = struct.pack(QVBD_HEADER, QVBD_MAGIC, 1, int(Q), int(P), float(tau), float(max_err), SOURCE_CODES[source], 0,
                       RESTORE_CODES[restore])
+    n8 = 0 if fp8_idx is None else len(fp8_idx)
+    if n8:
+        fp8_idx, fp8_codes = np.asarray(fp8_idx, np.int64), np.asarray(fp8_codes, np.uint8)
+        s8 = np.asarray(fp8_scale, np.float32)
+        if len(fp8_codes) != n8 or s8.shape != (int(Q),):
+            raise PackFormatError("FP8 pool: one code per index and one scale per row")
+        pool8 = fp8_idx.astype("<i8").tobytes() + fp8_codes.tobytes()
+    else:
+        pool8, s8 = b"", np.zeros(int(Q), np.float32)
     return b"".join([
         hdr, np.asarray(min_s, "<f4").tobytes(), np.asarray(tau_s, "<f4").tobytes(), nbits.tobytes(), ids.tobytes(),
-        struct.pack("<QQ", len(esc_idx), 0), esc_idx.astype("<i8").tobytes(), raw,
-        np.zeros(int(Q), "<f4").tobytes()])
+        struct.pack("<QQ", len(esc_idx) + n8, n8), esc_idx.astype("<i8").tobytes(), raw, pool8,
+        s8.astype("<f4").tobytes()])
 
 
 def write_qvb8_legacy(*, Q, P, tau, min_s, tau_s, nbits, bit_off, ids, esc_idx, esc_vals) -> bytes:

@@ -127,3 +127,51 @@ def test_concat_packs_is_the_members_side_by_side():
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     with pytest.raises(ValueError):
         fuse.concat_packs([members[0], random_pack(8, 128, (7,), seed=4)])
+
+
+def test_escape_pools_and_tables_match_the_reference(tmp_path):
+    """a pack with both escape pools and an escape_tables.json, as the reference's unpack_formula / fp16_list_for /
+    select_fp16 read them (fixture made by tests/golden/make_golden.py)"""
+    import os
+    from conftest import GOLDEN
+    z = np.load(os.path.join(GOLDEN, "escpool_32x256.npz"))
+    path = tmp_path / "layer_w.qvb8"
+    path.write_bytes(z["blob"].tobytes())
+    (tmp_path / packs.ESCAPE_TABLES_FILE).write_bytes(z["tables_json"].tobytes())
+    d = packs.read_qvb8(z["blob"].tobytes(), str(path))
+    assert d["restore"] == "fp16+bf16" and not d["fp16_table_missing"]
+    assert np.array_equal(d["esc_idx_bf16"], z["esc_idx"])
+    assert np.array_equal(d["esc_vals_bf16"].view(np.uint32), z["esc_vals"].view(np.uint32))
+    assert np.array_equal(d["esc_idx"], z["esc_idx_fp16"])
+    assert np.array_equal(d["esc_vals"].view(np.uint32), z["esc_vals_fp16"].view(np.uint32))
+    # without the tables file the fp16 table is unknown and fp16 runs must be refused later
+    d2 = packs.read_qvb8(z["blob"].tobytes(), None)
+    assert d2["fp16_table_missing"] and np.array_equal(d2["esc_idx"], z["esc_idx"])
+
+
+def test_damaged_legacy_blobs_are_refused():
+    """the legacy container stores row widths and bit offsets itself: a blob whose fields point outside its payload
+    must be refused on the host, never reach a kernel"""
+    import struct
+    pk = synth.synth_pack(24, 256, 3)
+    blob = pk.to_blob("QVB8")
+    assert packs.read_qvb8(blob)["Q"] == 24
+    with pytest.raises(packs.PackFormatError):                 # payload cut short
+        packs.read_qvb8(blob[:len(blob) - 200])
+    Q = 24
+    nb_at = packs.LEGACY_HEADER_BYTES + 8 * Q
+    bad = bytearray(blob); bad[nb_at + 3] = 0                  # a zero-width row
+    with pytest.raises(packs.PackFormatError):
+        packs.read_qvb8(bytes(bad))
+    bad = bytearray(blob); bad[nb_at + 3] = 15                 # wider than any certified row
+    with pytest.raises(packs.PackFormatError):
+        packs.read_qvb8(bytes(bad))
+    off_at = nb_at + Q
+    bad = bytearray(blob); struct.pack_into("<Q", bad, off_at + 8 * 5, 1 << 40)     # a row far outside the payload
+    with pytest.raises(packs.PackFormatError):
+        packs.read_qvb8(bytes(bad))
+    d = packs.read_qvb8(blob)
+    d["esc_idx"] = d["esc_idx"][::-1].copy() if len(d["esc_idx"]) > 1 else np.array([24 * 256], np.int64)
+    d["esc_vals"] = d["esc_vals"][:len(d["esc_idx"])] if len(d["esc_vals"]) >= len(d["esc_idx"]) else np.zeros(len(d["esc_idx"]), np.float32)
+    with pytest.raises(packs.PackFormatError):
+        packs.validate_pack(d)

@@ -281,3 +281,67 @@ def test_full_size_layer_properties(cuda_lib):
     b = torch.randint(-8, 9, (1, P), device=DEV).to(torch.float16)
     ya, yb, yab = (ext.forward(t, *ext_args(pk)) for t in (a, b, a + b))
     assert rel_fro(yab.cpu().numpy(), (ya + yb).cpu().numpy()) < 1e-5
+
+
+# ------------------------------------------------------------------------------------------------------------
+# activations that keep their range (the reference's bf16 mode of the verify kernel, qvb8_cuda.cu:1755-1775, 1861-1862;
+# module.py:375-400 passes bf16=True with the bf16 escape table for bf16-certified packs)
+
+@pytest.mark.parametrize("M", [8, 16, 48])
+def test_bf16_mode_rows_vs_oracle(cuda_lib, M):
+    pk = synth.synth_pack(272, 768, seed=60 + M, tau=2e-3, device=DEV, restore="fp16+bf16")
+    X = synth.synth_activation(M, 768, seed=M, device=DEV, dtype=torch.bfloat16)
+    perm = torch.argsort(pk.nbits.to(torch.int16), stable=True).to(torch.int32)
+    tile_nb = torch.zeros((272 + 15) // 16, dtype=torch.int32, device=DEV)
+    y = ext.mma_multi(X, *ext_args(pk, "bf16"), perm, tile_nb, True)
+    d = pack_np(pk)
+    band = oracle.restore_f32(oracle.unpack_ids(d["ids"], d["nbits"], d["bit_off"], pk.Q, pk.P), d["min_s"], d["tau_s"],
+                              np.zeros(0, np.int64), np.zeros(0, np.float32))
+    # the reference multiplies bf16(band) (escapes from the bf16 table); this library the un-narrowed band value
+    Wb = torch.from_numpy(band).to(torch.bfloat16).float().numpy()
+    Wb.reshape(-1)[d["esc_idx_bf16"]] = d["esc_vals_bf16"]
+    Wf = band.copy()
+    Wf.reshape(-1)[d["esc_idx_bf16"]] = d["esc_vals_bf16"]
+    Xn = X.float().cpu().numpy()
+    assert rel_fro(y.cpu().numpy(), oracle.matmul_f32w(Xn, Wb, narrow_x=False)) < TOL          # the reference's contract
+    assert rel_fro(y.cpu().numpy(), oracle.matmul_f32w(Xn, Wf, narrow_x=False)) < TIGHT        # what is computed here
+
+
+@pytest.mark.parametrize("xdt", [torch.bfloat16, torch.float32])
+def test_bf16_mode_keeps_the_range(cuda_lib, xdt):
+    """x_mode 1: a token with values far beyond fp16's range is prescaled by a power of two, not clamped; the other
+    tokens are untouched; runs through the streaming kernel (P % 128 == 0, plan)"""
+    pk = random_pack(160, 1024, (5, 6, 7, 8), seed=4, esc_frac=0.002, device=DEV)
+    X = synth.synth_activation(9, 1024, seed=3, device=DEV, dtype=torch.float32)
+    X[2] *= 3.0e6
+    X[5, 17] = -2.5e8
+    X[7] *= 1.0e-3
+    X = X.to(xdt)
+    perm = torch.argsort(pk.nbits.to(torch.int16), stable=True).to(torch.int32)
+    tile_nb = torch.zeros(10, dtype=torch.int32, device=DEV)
+    y = ext.mma_multi(X, *ext_args(pk), perm, tile_nb, True)
+    assert torch.isfinite(y).all()
+    W = oracle.qvb8_dense(pack_np(pk))
+    want = oracle.matmul_f32w(X.float().cpu().numpy(), W, narrow_x=False)
+    got = y.cpu().numpy()
+    for m in range(9):                                   # row by row: a huge token must not hide the others
+        # fp16 staging after the prescale keeps 11 bits of every activation: 5e-4 per element at worst
+        assert rel_fro(got[m], want[m]) < 1e-3, (m, rel_fro(got[m], want[m]))
+    # the clamping mode on the same input saturates token 2 and differs there, as documented
+    y0 = ext.mma_multi(X, *ext_args(pk), perm, tile_nb, False)
+    assert rel_fro(y0.cpu().numpy()[2], want[2]) > 0.1
+    assert rel_fro(y0.cpu().numpy()[0], want[0]) < TIGHT
+
+
+def test_config1_single_layer_against_the_oracle(cuda_lib):
+    """the 4096 x 4096 single-layer configuration, product and restore against the CPU oracle itself"""
+    Q = P = 4096
+    pk = synth.synth_pack(Q, P, seed=1000, device=DEV)
+    d = pack_np(pk)
+    W = oracle.qvb8_dense(d)
+    assert np.array_equal(ext.decode_f32(*ext_args(pk)).cpu().numpy().view(np.uint32), W.view(np.uint32))
+    for M in (1, 8):
+        X = synth.synth_activation(M, P, seed=7, device=DEV)
+        y = ext.forward(X, *ext_args(pk))
+        want = oracle.matmul_f32w(X.float().cpu().numpy(), W, narrow_x=True)
+        assert rel_fro(y.cpu().numpy(), want) < TIGHT

@@ -134,17 +134,30 @@ def test_gpu_products(cuda_lib, M):
 
 
 def test_linear_module_builds_on_cpu_and_chunks_cover_all_rows():
-    """Host-side logic of the module mirror: buffers, escape CSR, chunk spans (no kernel call)."""
-    from qvb8_b200.linear_r import QVBandLinearV8R
+    """Host-side logic of the module: buffers, escape CSR, chunk plan (no kernel call)."""
+    from qvb8_b200.linear_r import QVBandLinearV8R, plan_chunks
     _, d = _pack(100, 256, seed=21, K=3, T=4)
     mod = QVBandLinearV8R(d, device="cpu")
-    mod.CHUNK_BYTES = 1                                  # default: one chunk
-    assert sorted(mod.chunk_orows.tolist()) == list(range(100))
-    assert sum(c[3] for c in mod.chunks) == 100 and mod.chunks[-1][7] == mod.chunk_eflat.numel()
+    assert mod.whole and len(mod.chunks) == 1 and mod.chunks[0].rows == 100
+    assert sorted(mod.chunk_rows.tolist()) == list(range(100))
     assert int(mod.esc_ptr[-1]) == len(d["esc_idx"]) == mod.esc_delta16.numel()
     small = type("Small", (QVBandLinearV8R,), {"CHUNK_BYTES": 2 * 256 * 16})     # 16 rows of fp16 per chunk
     m2 = small(d, device="cpu")
-    assert len(m2.chunks) > 1 and sorted(m2.chunk_orows.tolist()) == list(range(100))
+    assert len(m2.chunks) > 1 and not m2.whole
+    assert sum(c.rows for c in m2.chunks) == 100 and m2.chunks[-1].esc1 == m2.chunk_esc_pos.numel() == len(d["esc_idx"])
+    assert all(a.row0 + a.rows == b.row0 and a.block0 + a.nblocks == b.block0 for a, b in zip(m2.chunks, m2.chunks[1:]))
+    # every chunk escape lands on the element it names: sorted row (row0 + pos // P) is original row chunk_rows[...]
+    P = 256
+    got = set()
+    for c in m2.chunks:
+        for pos in m2.chunk_esc_pos[c.esc0:c.esc1].tolist():
+            assert 0 <= pos < c.rows * P
+            got.add(int(m2.chunk_rows[c.row0 + pos // P]) * P + pos % P)
+    assert got == set(int(v) for v in d["esc_idx"])
+    tiles = np.array([[0, 0, 4], [0, 4, 4], [0, 8, 4], [1, 12, 2], [1, 14, 2]], np.int64)
+    blocks = rans.blocks_for(tiles, 2)
+    assert plan_chunks(tiles, blocks, 8) == [(0, 1, 0, 8), (1, 2, 8, 8)]
+    assert plan_chunks(tiles, blocks, 1) == [(0, 1, 0, 8), (1, 1, 8, 4), (2, 1, 12, 4)]
     mod.to(torch.bfloat16)
     assert mod.min_s.dtype == torch.float32 and mod.esc_delta.dtype == torch.float32
 

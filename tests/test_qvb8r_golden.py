@@ -158,3 +158,40 @@ def test_gpu_products(name, M, cuda_lib):
     ext.fix_escapes(Xh.float().to(dev).contiguous(), uq, ptr, ec, ed16, y16)
     err = np.linalg.norm(y16.cpu().numpy() - want16) / np.linalg.norm(want16)
     assert err < 2e-5, err
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_shim_encode_and_row_hist_match_the_reference_stream(name):
+    """the host-side entry points of the reference extension, as the shim offers them (qvb8r_cuda.cu:453-455)"""
+    from qvb8_b200.ext_qvb8r import ext
+    z, d = _load(name)
+    sym_sorted = torch.from_numpy(np.ascontiguousarray(z["sym"][d["perm"]]))
+    F = torch.from_numpy(d["freq"].astype(np.int64))
+    C = torch.cumsum(F, 1) - F
+    if sym_sorted.shape[1] % 128 == 0:
+        words, off, states = ext.encode(sym_sorted, torch.from_numpy(d["tiles"].astype(np.int64)), F, C)
+        assert np.array_equal(words.numpy().view(np.uint32), d["words"])
+        assert np.array_equal(off.numpy(), d["tile_off"].astype(np.int64))
+        assert np.array_equal(states.numpy().view(np.uint64), d["states"])
+    H = ext.row_hist(sym_sorted, int(d["N"])).numpy()
+    want = np.stack([np.bincount(r, minlength=int(d["N"])) for r in sym_sorted.numpy().astype(np.int64)])
+    assert np.array_equal(H, want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", CASES)
+def test_gpu_embedding_rows_match_the_reference_reader(name, cuda_lib):
+    """rows decoded on the device against the reference's CPU embed_rows output, bit for bit"""
+    from qvb8_b200.embedding import QVBandEmbeddingV8R
+    from qvb8_b200.ext_qvb8r import EmbeddingTable
+    z, d = _load(name)
+    table = EmbeddingTable.from_parsed(d, "cuda:0")
+    Q = d["Q"]
+    rows = torch.tensor([Q - 1, 0, Q // 2, 0, 1] + list(range(Q)), device="cuda:0")
+    got = table.lookup(rows).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), z["embed_f32"][rows.cpu().numpy()].view(np.uint32))
+    emb = QVBandEmbeddingV8R(d, out_dtype=torch.float32, device="cuda:0")
+    idx = torch.tensor([[1, 2], [Q - 1, 0]])
+    assert np.array_equal(emb(idx).cpu().numpy().view(np.uint32), z["embed_f32"][idx.numpy()].view(np.uint32))
+    with pytest.raises(IndexError):
+        emb(torch.tensor([Q]))
