@@ -109,6 +109,28 @@ int qvb8_plan_build(const qvb8_pack *w, void *plan, int64_t plan_bytes, void *st
 int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int x_mode, int64_t M,
                     float *Y, void *scratch, int64_t scratch_bytes, int flags, void *stream);
 
+/* Several products behind ONE launch (no counterpart in the reference, which launches per linear and hides the launch
+ * cost with CUDA graphs, decode/proj_graph.py, decode/layer_graph.py).  The jobs run back to back inside the kernel's
+ * persistent CTAs: copy rings, barriers and warp roles carry over from one job to the next, so the stream of weight
+ * bytes never drains at a job boundary, and the next job's activations are staged while the current one streams.
+ * The jobs must be INDEPENDENT: no job may read what another job of the same call writes (projections that read the
+ * outputs of earlier ones go into a later call).  All jobs share M; every job needs its plan.  Lists whose
+ * activations do not fit shared memory next to the rings (large M x P), or whose packs the streaming kernel cannot
+ * take, run job by job exactly as qvb8_small_m_ex would; only those need scratch
+ * (qvb8_small_m_group_scratch_bytes, zero-filled once); so do lists with x_mode 1 on bf16 / fp32 activations.  Results
+ * are deterministic (every sum has a fixed order) and agree with separate calls to rounding: the CTAs' shares are
+ * rotated from job to job, so a tile's fixed-order partial sums may be grouped differently. */
+typedef struct qvb8_job {
+    const qvb8_pack *w;
+    const void *plan;       /* qvb8_plan_build of w */
+    const void *X;          /* (M, w->P) of x_dtype */
+    float *Y;               /* (M, w->Q) fp32 */
+    int x_dtype, x_mode;    /* as for qvb8_small_m */
+} qvb8_job;
+int64_t qvb8_small_m_group_scratch_bytes(const qvb8_job *jobs, int njobs, int64_t M);
+int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *scratch, int64_t scratch_bytes, int flags,
+                       void *stream);
+
 /* Tuning hook for tests and sweeps (process-wide; 0 = choose automatically): fill_pct = CTAs launched, in percent of
  * one resident wave; force_s = number of K-ranges (raised to what shared memory requires); nstg = slots of the copy
  * ring (2..8); cps = 128-column chunks per ring stage (4, 8, 12 or 16); debug bit 0 = skip the fragment math (copy

@@ -58,7 +58,7 @@ constexpr int KC = 128;                   // columns per chunk
 constexpr int NW = 4;                     // consumer warps
 constexpr int MAX_CPS = 16;               // most chunks per stage (a stage holds cps chunks, cps a multiple of NW)
 constexpr int PRODUCER_WARP = NW;         // issues the bulk copies
-constexpr int FINISHER_WARP = NW + 1;     // escape corrections, cross-warp sums, scaling, output, K-range tickets
+constexpr int FINISHER_WARP = NW + 1;     // escape corrections, cross-warp sums, scaling, output
 constexpr int PIPE_THREADS = (NW + 2) * 32;  // threads of one pipe
 constexpr int MAX_STAGES = 4;
 constexpr int MAX_PIPES = 4;               // pipes per CTA at most
@@ -85,13 +85,22 @@ __device__ __forceinline__ void trace(int debug, int slot) {
 }
 
 constexpr int DESC_SLOT = 416;            // descriptor area of a side slot
-constexpr int ESC_CAP = 128;              // escape entries that travel with a descriptor (the rest is read from global memory)
-constexpr int SIDE_BYTES = DESC_SLOT + ESC_CAP * 8;
+constexpr int ESC_CAP_MIN = 64, ESC_CAP_MAX = 512;   // escape entries that travel with a descriptor (a launch picks the
+                                                     // capacity from its widest job; the rest is read from global memory)
 constexpr int NSIDE = 3;                  // side slots per pipe: descriptors and escapes of the visits ahead
+__host__ __device__ constexpr int64_t side_slot_bytes(int esc_cap) { return DESC_SLOT + (int64_t)esc_cap * 8; }
+// Entry capacity for rows of P columns: what 16 rows hold at 1.5 escapes per thousand weights (packs made with the
+// outliers escaped carry about 1 per thousand), within the limits above.
+__host__ __device__ constexpr int esc_cap_for(int64_t P) {
+    const int64_t want = (16 * P * 3 / 2000 + 31) / 32 * 32;
+    return (int)(want < ESC_CAP_MIN ? ESC_CAP_MIN : want > ESC_CAP_MAX ? ESC_CAP_MAX : want);
+}
 
 // Bytes of a pipe's escape area: the finishing warp's corrections [16][M] and, for one token, a staging array of
 // (difference, activation) pairs of the tile's entries (see the finishing warp).
-__host__ __device__ constexpr int64_t corr_bytes(int64_t M) { return (16 * M * 4 + 127) / 128 * 128 + (M == 1 ? ESC_CAP * 8 : 0); }
+__host__ __device__ constexpr int64_t corr_bytes(int64_t M, int esc_cap) {
+    return (16 * M * 4 + 127) / 128 * 128 + (M == 1 ? (int64_t)esc_cap * 8 : 0);
+}
 
 // Per-CTA control block in static shared memory.
 struct PipeControl {
@@ -99,21 +108,21 @@ struct PipeControl {
     alignas(8) uint64_t empty[MAX_STAGES];
     alignas(8) uint64_t side_full[NSIDE];   // a visit's descriptor and escapes have landed
     alignas(8) uint64_t side_empty[NSIDE];  // ... and the four consumer warps and the finishing warp are done with them
-    alignas(8) uint64_t red_full;         // the consumer warps' partial sums of a visit are in the hand-over buffer
-    alignas(8) uint64_t red_empty;        // ... and have been taken by the finishing warp
+    alignas(8) uint64_t red_full[2];      // the consumer warps' partial sums of a visit are in hand-over buffer b
+    alignas(8) uint64_t red_empty[2];     // ... and have been taken by the finishing warp
 };
 struct Control {
-    union {
-        float sumx[MAX_M];                // per-token sums of the narrowed activations of this K-range
-        uint32_t amax[MAX_M];             // x_mode 1, before the sums exist: bits of the largest |x| of a token's range
-    };
+    uint32_t amax[MAX_M];                 // x_mode 1: bits of the largest |x| of a token in this K-range
     uint8_t kexp[MAX_M];                  // x_mode 1: token m is staged as x * 2^-kexp[m] and its results multiplied back
     int abort;
     alignas(16) uint32_t pair_table[24];  // pair-conversion constants of widths 3..8 (see pair_const)
-    alignas(8) uint64_t x_ready;          // every consumer warp has staged its share of the activations
-    alignas(8) uint64_t sums_ready;       // every finishing warp has summed its share of the tokens
     alignas(8) uint64_t amax_ready;       // x_mode 1: every consumer warp has folded its share into amax
+    alignas(8) uint64_t x_ready;          // once per job: every consumer warp has staged its slice of the activations
+    alignas(8) uint64_t job_done;         // once per job boundary: every consumer warp has left the job before
+    alignas(8) uint64_t raw_full;         // once per later job: its raw activations have landed
+    alignas(8) uint64_t fin_started;      // once per job: every finishing warp has reached the job and taken its activation sums
     alignas(8) uint64_t xch_full[XCH_SLOTS];   // [owner pipe][contributor]: a contributed part of a shared tile is in place
+    alignas(8) uint64_t xch_empty[XCH_SLOTS];  // ... and the owner has taken it
     PipeControl pipe[MAX_PIPES];
 };
 
@@ -173,6 +182,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// The same copy marked evict-first in L2: the packed weights are read once per product, and a launch streams far more of
+// them than the L2 holds.  Without the hint they push everything else out -- the kernel's own instructions, tile
+// descriptors, activations -- and whatever then misses in L2 queues behind the weight stream in a saturated HBM
+// (microseconds per miss: a rarely executed code path then costs more than the tile it finishes).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_stream(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol) : "memory");
 }
 
 // Programmatic dependent launch: everything before pdl_wait() may overlap the tail of the previous kernel in the
@@ -371,16 +394,22 @@ __device__ __forceinline__ float xs_read(const __half *xs, int c, int m, int MP)
     return __half2float(xs[(slot_of(c, m, MP) << 3) + pos_a(c & 7)]);
 }
 
-template <int XT>
+// 16 bytes from global memory through the read-only path, or (GLOBAL = false) from wherever a generic pointer leads
+template <bool GLOBAL>
+__device__ __forceinline__ uint4 load16(const void *ptr) {
+    if constexpr (GLOBAL) return __ldg(reinterpret_cast<const uint4 *>(ptr));
+    else return *reinterpret_cast<const uint4 *>(ptr);
+}
+template <int XT, bool GLOBAL>
 __device__ __forceinline__ void stage_x8(const void *__restrict__ X, int64_t off, uint32_t (&h)[8], float sc) {
     // h[k] = fp16 bits of the k-th activation times sc (1, or a token's power-of-two prescale), saturated
     if constexpr (XT == QVB8_F16) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(X) + off));
+        const uint4 u = load16<GLOBAL>(reinterpret_cast<const __half *>(X) + off);
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) { h[2 * k] = w[k] & 0xffffu; h[2 * k + 1] = w[k] >> 16; }
     } else if constexpr (XT == QVB8_BF16) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(X) + off));
+        const uint4 u = load16<GLOBAL>(reinterpret_cast<const __nv_bfloat16 *>(X) + off);
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -388,11 +417,11 @@ __device__ __forceinline__ void stage_x8(const void *__restrict__ X, int64_t off
             h[2 * k + 1] = __half_as_ushort(sat_half(__uint_as_float(w[k] & 0xffff0000u) * sc));
         }
     } else {
-        const float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(X) + off));
-        const float4 b = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(X) + off) + 1);
-        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        const uint4 a = load16<GLOBAL>(reinterpret_cast<const float *>(X) + off);
+        const uint4 b = load16<GLOBAL>(reinterpret_cast<const float *>(X) + off + 4);
+        const uint32_t v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int k = 0; k < 8; ++k) h[k] = __half_as_ushort(sat_half(v[k] * sc));
+        for (int k = 0; k < 8; ++k) h[k] = __half_as_ushort(sat_half(__uint_as_float(v[k]) * sc));
     }
 }
 
@@ -601,27 +630,42 @@ __global__ void __launch_bounds__(1024) tile_escapes_kernel(TileDesc *__restrict
     }
 }
 
-struct SmallMParams {
+// One product of a launch: a pack (with its plan), its activations and its output.
+struct JobDesc {
     const uint8_t *ids;
     const uint8_t *nbits;      // per-element class only
     const int64_t *bit_off;    // per-element class only
     const TileDesc *tiles;
-    int ntiles;                // length of the tile table (real tiles first, then empty ones)
     const EscEntry *esc_ent;   // escapes grouped by tile; null: the pack has no escapes
-    const void *X;
+    const void *X;             // (M, P)
     float *Y;                  // (M, Q)
-    float *part;               // (slots, M, Q) partial results of tiles shared by several visits
-    int *ticket;               // one counter per tile (zero on entry, zero on exit)
-    int Q, P, M, MP;           // MP: token slots per column group in shared memory (>= M)
-    int x_dtype;
-    int x_mode;                // 0: activations narrowed to saturated fp16; 1: per-token power-of-two prescale first
-    int S;                     // K-ranges (= gridDim.y)
-    int nc_per;                // chunks per K-range (the last range may be shorter)
+    int ntiles;                // length of the tile table (real tiles first, then empty ones)
+    int Q, P;
     int nc_total;              // P / 128
+    int x_dtype, x_mode;
+    int rot;                   // rotation of the CTA numbering for this job: over a list of jobs every CTA gets its
+                               // fair share of the tiles that do not divide evenly
+    int prepass;               // 1: an escape pre-pass has put the job's corrections into Y; the product is added to them
+};
+static_assert(sizeof(JobDesc) == 88, "job record layout (host and device agree)");
+constexpr int MAX_JOBS = 32;   // jobs behind one launch
+
+struct SmallMParams {
+    JobDesc jobs[MAX_JOBS];    // the launch's jobs, by value (they travel with the launch: nothing to keep alive, and a
+                               // captured graph holds its own copy)
+    int njobs;
+    float *part;               // (slots, M, Q) partial results of tiles shared by several K-ranges (single job only)
+    int *ticket;               // one counter per CTA column (zero on entry, zero on exit)
+    int M, MP;                 // MP: token slots per column group in shared memory (>= M)
+    int S;                     // K-ranges (= gridDim.y); 1 when the launch has several jobs
+    int nc_per;                // chunks per K-range (the last range may be shorter)
+    int xs_halves;             // capacity of the staged activations in halves per layout
+    int raw_bytes;             // capacity of the raw-activation buffer (0 for a one-job launch)
     int nstg;                  // slots of each pipe's copy ring
     int cps;                   // chunks per stage (a multiple of NW)
     int rs[6];                 // bytes between rows of a stage, by width 3..8
     int slot_bytes;            // a ring slot: 16 rows of the widest width
+    int esc_cap;               // escape entries a side slot holds
     int debug;                 // bit 0: skip the fragment math (copy stream only); bit 1: time stamps of CTA (0, 0);
                                // bit 2: skip the row copies (math on whatever the ring holds; tuning experiments)
 };
@@ -734,76 +778,150 @@ __device__ __forceinline__ bool stream_tile(const SmallMParams &p, const uint32_
 
 // X staging: 8 activations as saturated fp16 bit patterns, whatever the input type (runtime switch: the staging
 // loop is short, and one kernel serves the three input types)
+template <bool GLOBAL>
 __device__ __forceinline__ void stage_x8_any(int x_dtype, const void *__restrict__ X, int64_t off, uint32_t (&h)[8], float sc) {
-    if (x_dtype == QVB8_BF16) stage_x8<QVB8_BF16>(X, off, h, sc);
-    else if (x_dtype == QVB8_F16) stage_x8<QVB8_F16>(X, off, h, sc);
-    else stage_x8<QVB8_F32>(X, off, h, sc);
+    if (x_dtype == QVB8_BF16) stage_x8<QVB8_BF16, GLOBAL>(X, off, h, sc);
+    else if (x_dtype == QVB8_F16) stage_x8<QVB8_F16, GLOBAL>(X, off, h, sc);
+    else stage_x8<QVB8_F32, GLOBAL>(X, off, h, sc);
 }
+
+// Geometry of one job for one pipe of one CTA: the CTA's share of whole tiles (CTA numbering rotated per job) and the
+// pipe's run of (tile, stage) units in it.
+struct JobGeom {
+    int kc0, NC, NSK;          // first chunk and chunk count of this CTA's K-range; stages along K per tile
+    int uc0, uc1, Lp;          // the CTA's units [uc0, uc1), units per pipe
+    int ct0, ct1;              // the CTA's tiles
+    Run run;                   // this pipe's run
+};
+template <int NPIPE>
+__device__ __forceinline__ JobGeom job_geom(const SmallMParams &p, const JobDesc &jd, int split, int pipe) {
+    JobGeom g;
+    g.kc0 = split * p.nc_per;
+    g.NC = p.njobs > 1 ? jd.nc_total : min(p.nc_per, jd.nc_total - g.kc0);
+    g.NSK = (g.NC + p.cps - 1) / p.cps;
+    int c = (int)blockIdx.x + jd.rot;
+    if (c >= (int)gridDim.x) c -= (int)gridDim.x;
+    cta_tiles(jd.ntiles, gridDim.x, c, g.ct0, g.ct1);
+    g.uc0 = g.ct0 * g.NSK;
+    g.uc1 = g.ct1 * g.NSK;
+    g.Lp = max(1, (g.uc1 - g.uc0 + NPIPE - 1) / NPIPE);
+    const int u0 = min(g.uc0 + pipe * g.Lp, g.uc1), u1 = min(u0 + g.Lp, g.uc1);
+    g.run = make_run(u0, u1, g.NSK);
+    return g;
+}
+
+// Stages this consumer warp's slice of a job's activations (all tokens) as saturated fp16 in MMA fragment order (layout
+// A, and layout B when DUAL) and leaves the slice's per-token sums in psum_w[m].  X points at row 0 of the (M, P)
+// activations: global memory (GLOBAL) or the raw copy in shared memory.  Warp cw of ncw takes the 8-column groups
+// [cw * per, (cw + 1) * per) of the K-range.  Sums run over the narrowed values in a fixed order (same bits every run).
+template <bool DUAL, bool GLOBAL, typename ScaleOf>
+__device__ __forceinline__ void stage_slice(const void *X, int x_dtype, int64_t ldx, int kc0, int NC, int M, int MP,
+                                            __half *xs_a, __half *xs_b, int cw, int ncw, int lane, ScaleOf sc_of,
+                                            float *psum_w) {
+    const int groups = NC * 16;
+    const int per = (groups + ncw - 1) / ncw;
+    const int g0 = cw * per, g1 = min(groups, g0 + per);
+    const int64_t col0 = (int64_t)kc0 * KC;
+    constexpr int UNR = 4;                                              // loads in flight per thread
+    for (int m = 0; m < MP; ++m) {
+        float s = 0.f;
+        const float sc = m < M ? sc_of(m) : 1.f;
+        for (int base = g0 + lane; base < g1; base += 32 * UNR) {
+            uint32_t h[UNR][8];
+#pragma unroll
+            for (int i = 0; i < UNR; ++i) {
+                const int u8 = base + i * 32;
+                if (u8 < g1 && m < M) {
+                    stage_x8_any<GLOBAL>(x_dtype, X, (int64_t)m * ldx + col0 + (int64_t)u8 * 8, h[i], sc);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) h[i][j] = 0u;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < UNR; ++i) {
+                const int u8 = base + i * 32;
+                if (u8 >= g1) continue;
+                const int sl = slot_of(u8 * 8, m, MP);
+                *reinterpret_cast<uint4 *>(xs_a + (sl << 3)) = make_uint4(
+                    h[i][0] | (h[i][2] << 16), h[i][1] | (h[i][3] << 16), h[i][4] | (h[i][6] << 16), h[i][5] | (h[i][7] << 16));
+                if (DUAL)
+                    *reinterpret_cast<uint4 *>(xs_b + (sl << 3)) = make_uint4(
+                        h[i][0] | (h[i][4] << 16), h[i][1] | (h[i][5] << 16), h[i][2] | (h[i][6] << 16), h[i][3] | (h[i][7] << 16));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s += __half2float(__ushort_as_half((unsigned short)h[i][j]));
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0 && m < M) psum_w[m] = s;
+    }
+}
+
+// Completion number n of a barrier that completes once per use -> the parity a waiter passes.
+__device__ __forceinline__ uint32_t par(int n) { return (uint32_t)(n & 1); }
 
 // DUAL: a second activation layout is staged for widths that pair ids at distance 4 (cheap for few tokens).
 // NPIPE: pipes per CTA.  Four stream fastest; a two-pipe CTA is small enough (threads, registers, shared memory) for
 // the next kernel's CTA to sit beside it and run its prologue early (a tuning switch, see make_plan).
+//
+// A launch runs a LIST of jobs (products) back to back inside the CTAs: the copy rings, barriers and warp roles
+// persist from one job to the next, so the stream of weight bytes never drains between jobs; the raw activations of job
+// j + 1 arrive by one bulk copy while job j streams and are converted by all consumer warps at the job boundary.  The jobs must not depend
+// on one another's outputs.  A launch with one job is the plain product.
 template <int NT, bool DUAL, int NPIPE>
-__global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const SmallMParams p) {
+__global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const __grid_constant__ SmallMParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ Control ctl;
     constexpr int RED_FLOATS = NW * 4 * NT * 32;                       // a pipe's hand-over buffer (>= 16 * M floats)
+    constexpr int CWARPS = NPIPE * NW;                                 // consumer warps of the CTA
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int pipe = tid / PIPE_THREADS, warp = (tid % PIPE_THREADS) >> 5;     // warp: role within the pipe
     const int split = blockIdx.y;
-    const int kc0 = split * p.nc_per;                                  // first chunk of this K-range
-    const int NC = min(p.nc_per, p.nc_total - kc0);                    // chunks in this K-range (>= 1 by construction)
     const int cps = p.cps;
-    const int NSK = (NC + cps - 1) / cps;                              // stages along K per tile
     const int MP = p.MP, M = p.M;
     const int nstg = p.nstg;
+    const int njobs = p.njobs;
     // dynamic shared memory:
-    //   [activations A] [activations B] [16 zero bytes, padded to 128] [exchange buffers of tiles shared by pipes]
-    //   per pipe: [ring: nstg stages of 16 rows] [side ring: NSIDE x (descriptor + escapes)] [hand-over buffer]
+    //   [job table] [activations: layout A, layout B] [raw activations of the next job] [16 zero bytes, padded to 128]
+    //   [activation sums by consumer warp, two sets] [exchange buffers of tiles shared by pipes]
+    //   per pipe: [ring: nstg stages of 16 rows] [side ring: NSIDE x (descriptor + escapes)] [two hand-over buffers]
     //             [escape corrections]
-    const int xs_halves = p.nc_per * 16 * MP * 8;                      // halves per activation layout
-    __half *xs_a = reinterpret_cast<__half *>(smem);
-    __half *xs_b = DUAL ? xs_a + xs_halves : xs_a;
-    uint32_t *zero16 = reinterpret_cast<uint32_t *>(xs_a + (DUAL ? 2 : 1) * xs_halves);
+    JobDesc *jobs = reinterpret_cast<JobDesc *>(smem);
+    const size_t jobs_bytes = (size_t)((njobs * (int)sizeof(JobDesc) + 127) / 128 * 128);
+    __half *xs_a = reinterpret_cast<__half *>(smem + jobs_bytes);
+    __half *xs_b = DUAL ? xs_a + p.xs_halves : xs_a;
+    uint8_t *raw = reinterpret_cast<uint8_t *>(xs_a + (DUAL ? 2 : 1) * p.xs_halves);   // p.raw_bytes (a multiple of 128)
+    uint32_t *zero16 = reinterpret_cast<uint32_t *>(raw + p.raw_bytes);
+    float *psum = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(zero16) + 128);   // [2][CWARPS][M]
+    const size_t psum_bytes = (size_t)((2 * CWARPS * M * 4 + 127) / 128 * 128);
     const int xch_floats = 16 * M;                                     // one tile's results
-    float *xch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(zero16) + 128);    // [owner][contributor][16][M]
+    float *xch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(psum) + psum_bytes);   // [owner][contributor][16][M]
     float *own = xch + XCH_SLOTS * xch_floats;                                 // [NPIPE][16][M]: an owner's own part of its shared tile
     const size_t shared_bytes = (size_t)(((XCH_SLOTS + NPIPE) * xch_floats * 4 + 127) / 128 * 128);
-    const size_t pipe_bytes = (size_t)nstg * p.slot_bytes + (size_t)NSIDE * SIDE_BYTES + (size_t)RED_FLOATS * 4 +
-                              (size_t)corr_bytes(M);
-    uint8_t *pbase = reinterpret_cast<uint8_t *>(zero16) + 128 + shared_bytes + (size_t)pipe * pipe_bytes;
-    uint8_t *side = pbase + (size_t)nstg * p.slot_bytes;               // [NSIDE][SIDE_BYTES]
-    float *red = reinterpret_cast<float *>(side + NSIDE * SIDE_BYTES); // [NW][4 * NT][32]
-    float *corr = red + RED_FLOATS;                                    // [16][M], private to the finishing warp
+    const int esc_cap = p.esc_cap;
+    const int side_bytes = (int)side_slot_bytes(esc_cap);
+    const size_t pipe_bytes = (size_t)nstg * p.slot_bytes + (size_t)NSIDE * side_bytes + (size_t)2 * RED_FLOATS * 4 +
+                              (size_t)corr_bytes(M, esc_cap);
+    uint8_t *pbase = reinterpret_cast<uint8_t *>(xch) + shared_bytes + (size_t)pipe * pipe_bytes;
+    uint8_t *side = pbase + (size_t)nstg * p.slot_bytes;               // [NSIDE][side_bytes]
+    float *red = reinterpret_cast<float *>(side + NSIDE * side_bytes); // [2][NW][4 * NT][32]
+    float *corr = red + 2 * RED_FLOATS;                                // [16][M], private to the finishing warp
     PipeControl &pc_ = ctl.pipe[pipe];
-    const bool planned = p.esc_ent != nullptr;
     volatile int *abort_flag = &ctl.abort;
     const bool tracer = (p.debug & 2) && pipe == 0;
 
     if (tracer) trace(p.debug, 0);
-    // this CTA's tiles and this pipe's run of their (tile, stage) units
-    const int ntiles = p.ntiles;
-    int ct0, ct1;
-    cta_tiles(ntiles, gridDim.x, blockIdx.x, ct0, ct1);
-    const int uc0 = ct0 * NSK, uc1 = ct1 * NSK;
-    const int Lp = max(1, (uc1 - uc0 + NPIPE - 1) / NPIPE);
-    const int u0 = min(uc0 + pipe * Lp, uc1), u1 = min(u0 + Lp, uc1);
-    const Run run = make_run(u0, u1, NSK);
-    // the producer's first descriptor fields are on their way from memory while the barriers are set up
-    int pf_nb = 0, pf_cnt = 0, pf_esc0 = 0, pf_nesc = 0;
-    uint32_t pf_b16 = 0;
-    if (warp == PRODUCER_WARP && run.nv > 0) {
-        const TileDesc *d = p.tiles + run_visit(run, 0).tile;
-        pf_nb = __ldg(&d->nb);
-        pf_cnt = __ldg(&d->cnt);
-        pf_esc0 = __ldg(&d->esc0);
-        pf_nesc = __ldg(&d->nesc);
-        pf_b16 = lane < 16 ? __ldg(&d->b16[lane]) : 0u;
+    // the job table: from the launch parameters into shared memory, where every warp reads it at each job boundary
+    {
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(p.jobs);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(jobs);
+        for (int i = tid; i < njobs * (int)(sizeof(JobDesc) / 4); i += blockDim.x) dst[i] = src[i];
     }
     // barriers: one thread each
     {
-        const int per_pipe = 2 * nstg + 2 * NSIDE + 2;
+        const int per_pipe = 2 * nstg + 2 * NSIDE + 4;
         if (tid < NPIPE * per_pipe) {
             PipeControl &q = ctl.pipe[tid / per_pipe];
             const int k = tid % per_pipe;
@@ -811,21 +929,24 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             else if (k < 2 * nstg) mbar_init(smem_u32(&q.empty[k - nstg]), NW);
             else if (k < 2 * nstg + NSIDE) mbar_init(smem_u32(&q.side_full[k - 2 * nstg]), 1);
             else if (k < 2 * nstg + 2 * NSIDE) mbar_init(smem_u32(&q.side_empty[k - 2 * nstg - NSIDE]), NW + 1);
-            else if (k == 2 * nstg + 2 * NSIDE) mbar_init(smem_u32(&q.red_full), NW);
-            else mbar_init(smem_u32(&q.red_empty), 1);
+            else if (k < 2 * nstg + 2 * NSIDE + 2) mbar_init(smem_u32(&q.red_full[k - 2 * nstg - 2 * NSIDE]), NW);
+            else mbar_init(smem_u32(&q.red_empty[k - 2 * nstg - 2 * NSIDE - 2]), 1);
         } else if (tid < NPIPE * per_pipe + XCH_SLOTS) {
             mbar_init(smem_u32(&ctl.xch_full[tid - NPIPE * per_pipe]), 1);
+            mbar_init(smem_u32(&ctl.xch_empty[tid - NPIPE * per_pipe]), 1);
         } else if (tid == NPIPE * per_pipe + XCH_SLOTS) {
-            mbar_init(smem_u32(&ctl.x_ready), NW * NPIPE);
-            mbar_init(smem_u32(&ctl.sums_ready), NPIPE);
-            mbar_init(smem_u32(&ctl.amax_ready), NW * NPIPE);
+            mbar_init(smem_u32(&ctl.amax_ready), CWARPS);
+            mbar_init(smem_u32(&ctl.x_ready), CWARPS);
+            mbar_init(smem_u32(&ctl.job_done), CWARPS);
+            mbar_init(smem_u32(&ctl.raw_full), 1);
+            mbar_init(smem_u32(&ctl.fin_started), NPIPE);
             ctl.abort = 0;
         }
         if (tid <= NPIPE * per_pipe + XCH_SLOTS) asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (tid >= 160 && tid < 164) zero16[tid - 160] = 0u;
-    if (tid >= 192 && tid < 192 + MAX_M) { ctl.amax[tid - 192] = 0u; ctl.kexp[tid - 192] = 0; }
+    if (tid >= 152 && tid < 156) zero16[tid - 152] = 0u;
     if (tid >= 128 && tid < 128 + PAIR_TABLE_WORDS) ctl.pair_table[tid - 128] = pair_const_word(3 + ((tid - 128) >> 2), (tid - 128) & 3);
+    if (tid < MAX_M) { ctl.amax[tid] = 0u; ctl.kexp[tid] = 0; }                       // (the smallest CTA has 192 threads)
     __syncthreads();
     pdl_launch_dependents();                                            // what follows in the stream may start its own prologue
     if (tracer) trace(p.debug, 1);
@@ -836,37 +957,60 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
 
     if (warp == PRODUCER_WARP) {
         // ================= producer warp: per visit, lane 16 copies the tile's descriptor and lane 17 its escapes into
-        // a side slot; per stage, lane r copies row r =================
+        // a side slot; per stage, lane r copies row r.  The next visit's descriptor fields are fetched one visit
+        // ahead, across job boundaries too =================
         bool alive = true;
-        int nb = pf_nb, cnt = pf_cnt, esc0 = pf_esc0, nesc = pf_nesc;
-        uint32_t b16 = pf_b16;
-        auto fetch = [&](int i) {
-            if (i < run.nv) {
-                const TileDesc *d = p.tiles + run_visit(run, i).tile;
-                nb = __ldg(&d->nb);
-                cnt = __ldg(&d->cnt);
-                esc0 = __ldg(&d->esc0);
-                nesc = __ldg(&d->nesc);
-                b16 = lane < 16 ? __ldg(&d->b16[lane]) : 0u;
+        int nb = 0, cnt = 0, esc0 = 0, nesc = 0;
+        uint32_t b16 = 0;
+        // cursor over (job, visit) pairs that exist
+        int cj = 0, ci = -1;
+        JobGeom cg = job_geom<NPIPE>(p, jobs[0], split, pipe);
+        auto advance = [&](int &j, int &i, JobGeom &g) {                // -> false when the list is exhausted
+            ++i;
+            while (i >= g.run.nv) {
+                if (++j >= njobs) return false;
+                g = job_geom<NPIPE>(p, jobs[j], split, pipe);
+                i = 0;
             }
+            return true;
         };
+        auto fetch = [&](int j, int i, const JobGeom &g) {
+            const TileDesc *d = jobs[j].tiles + run_visit(g.run, i).tile;
+            nb = __ldg(&d->nb);
+            cnt = __ldg(&d->cnt);
+            esc0 = __ldg(&d->esc0);
+            nesc = __ldg(&d->nesc);
+            b16 = lane < 16 ? __ldg(&d->b16[lane]) : 0u;
+        };
+        bool have = advance(cj, ci, cg);
+        if (have) fetch(cj, ci, cg);
         if (tracer) trace(p.debug, 2);
         const bool nocopy = (p.debug & 4) != 0;
-        for (int i = 0; i < run.nv && alive; ++i) {
-            const Visit v = run_visit(run, i);
+        const uint64_t stream_policy = l2_evict_first_policy();
+        int vis = 0;                                                    // visits issued so far (all jobs)
+        while (have && alive) {
+            const JobDesc &jd = jobs[cj];
+            const Visit v = run_visit(cg.run, ci);
+            const int NC = cg.NC, kc0 = cg.kc0;
             const int cnb = nb, ccnt = cnt;
-            const uint32_t ebytes = planned ? (uint32_t)(min((nesc + 1) & ~1, ESC_CAP) * 8) : 0u;
-            const EscEntry *esrc = p.esc_ent + esc0;
+            const bool planned = jd.esc_ent != nullptr && !jd.prepass;   // (a pre-pass has applied the job's escapes)
+            const uint32_t ebytes = planned ? (uint32_t)(min((nesc + 1) & ~1, esc_cap) * 8) : 0u;
+            const EscEntry *esrc = jd.esc_ent + esc0;
             const uint32_t step = (uint32_t)(cps * 16 * cnb);           // bytes of a row per full stage
-            const uint8_t *src = p.ids + ((uint64_t)b16 + (uint64_t)kc0 * cnb) * 16u + (size_t)v.sb * step;
-            fetch(i + 1);                                               // next descriptor loads while this visit is issued
+            const uint8_t *src = jd.ids + ((uint64_t)b16 + (uint64_t)kc0 * cnb) * 16u + (size_t)v.sb * step;
+            const TileDesc *dsrc = jd.tiles + v.tile;
+            // next visit's descriptor loads while this visit is issued
+            int nj = cj, ni = ci;
+            JobGeom ng = cg;
+            const bool more = advance(nj, ni, ng);
+            if (more) fetch(nj, ni, ng);
             // descriptor and escapes
-            const int sslot = i % NSIDE;
-            if (!mbar_wait(side_empty0 + 8 * sslot, ((i / NSIDE) & 1) ^ 1u, abort_flag, 7, 200)) { alive = false; break; }
-            const uint32_t sfull = side_full0 + 8 * sslot, sdst = smem_u32(side + sslot * SIDE_BYTES);
+            const int sslot = vis % NSIDE;
+            if (!mbar_wait(side_empty0 + 8 * sslot, par(vis / NSIDE) ^ 1u, abort_flag, 7, 200)) { alive = false; break; }
+            const uint32_t sfull = side_full0 + 8 * sslot, sdst = smem_u32(side + sslot * side_bytes);
             if (lane == 0) mbar_expect_tx(sfull, (uint32_t)DESC_BYTES + ebytes);
             __syncwarp();
-            if (lane == 16) bulk_g2s(sdst, p.tiles + v.tile, DESC_BYTES, sfull);
+            if (lane == 16) bulk_g2s(sdst, dsrc, DESC_BYTES, sfull);
             if (lane == 17 && ebytes) bulk_g2s(sdst + DESC_SLOT, esrc, ebytes, sfull);
             // rows (a per-element tile has none: its rows are read from global memory)
             const uint32_t dst_row = (uint32_t)(lane * (cnb ? p.rs[cnb - 3] : 0));
@@ -877,11 +1021,13 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 if (!mbar_wait(rp.empty, rp.phase ^ 1u, abort_flag, 1, 100)) { alive = false; break; }
                 if (lane == 0) mbar_expect_tx(rp.full, bytes_row * (uint32_t)ccnt);
                 __syncwarp();
-                if (bytes_row && lane < ccnt) bulk_g2s(rp.data + dst_row, src, bytes_row, rp.full);
+                if (bytes_row && lane < ccnt) bulk_g2s_stream(rp.data + dst_row, src, bytes_row, rp.full, stream_policy);
                 src += step;
-                if (tracer && i == 0 && s == v.sb) trace(p.debug, 3);
+                if (tracer && vis == 0 && s == v.sb) trace(p.debug, 3);
                 ring_advance(rp, (uint32_t)p.slot_bytes, nstg);
             }
+            ++vis;
+            cj = nj; ci = ni; cg = ng; have = more;
         }
         // nothing may be in flight when the CTA exits: wait until every issued stage and side slot has been consumed
         for (int s = 0; s < nstg && alive; ++s) {
@@ -889,8 +1035,8 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             ring_advance(rp, (uint32_t)p.slot_bytes, nstg);
         }
         for (int k = 0; k < NSIDE && alive; ++k) {
-            const int i = run.nv + k;                                   // as if about to reuse the slot
-            alive = mbar_wait(side_empty0 + 8 * (i % NSIDE), ((i / NSIDE) & 1) ^ 1u, abort_flag, 7);
+            const int i = vis + k;                                      // as if about to reuse the slot
+            alive = mbar_wait(side_empty0 + 8 * (i % NSIDE), par(i / NSIDE) ^ 1u, abort_flag, 7);
         }
         if (!alive) {
             // a wait gave up somewhere: copies may still be in flight towards this CTA's shared memory; keep the CTA
@@ -902,200 +1048,43 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         // ================= finishing warp: per visit, sums the escape corrections of its rows while the stages stream,
         // then takes the consumer warps' partial sums, scales, corrects and writes the rows =================
         const int g = lane >> 2, t = lane & 3;
-        // per-token sums of the narrowed activations (fixed order: same bits every run); the pipes share the work
-        bool alive = mbar_wait(smem_u32(&ctl.x_ready), 0, abort_flag, 5);      // every consumer warp has staged its part
-        // Up to two tokens: every token's sum is cut into NPIPE column ranges so that all finishing warps share it
-        // (otherwise one of them would add up a whole row of activations alone while the others wait); sumx then
-        // holds the parts, [token][range], and the reader adds them in range order.  More tokens: one token per warp.
-        const bool split_sums = M <= 2;
-        const int nitems = split_sums ? M * NPIPE : M;
-        for (int it = pipe; it < nitems; it += NPIPE) {
-            const int m = split_sums ? it / NPIPE : it;
-            const int J = NC * 16;
-            const int j0 = split_sums ? (it % NPIPE) * (J / NPIPE) : 0, j1 = split_sums ? j0 + J / NPIPE : J;
-            float sacc = 0.f;
-            for (int j = j0 + lane; j < j1; j += 32) {
-                const uint4 v = *reinterpret_cast<const uint4 *>(xs_a + ((size_t)(j * MP + m) << 3));
-                const __half2 *hp = reinterpret_cast<const __half2 *>(&v);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(hp[k]); sacc += f.x; sacc += f.y; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
-            if (lane == 0) ctl.sumx[it] = sacc;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctl.sums_ready));
-        if (alive) alive = mbar_wait(smem_u32(&ctl.sums_ready), 0, abort_flag, 6);
-        int own_contrib = 0, own_tile = 0, own_row[2] = {-1, -1};
-        const bool prescaled = p.x_mode == 1 && p.x_dtype != QVB8_F16;
-        // writes a finished tile (of this K-range): the result itself, or with several K-ranges a partial result; the
-        // K-ranges' partial results of all of a CTA's tiles are added up in range order at the end of the kernel
-        auto emit_tile = [&](int tile, const int (&rows)[2], const float (&y)[2][NT][2]) {
-            float *out = p.S == 1 ? p.Y : p.part + (int64_t)split * M * p.Q;
-#pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow)
+        bool alive = true;
+        int vis = 0;                                                    // visits handled so far (all jobs)
+        int own_uses[MAX_PIPES - 1] = {0, 0, 0};                        // completions waited for on this pipe's xch_full[j]
+        int give_uses[MAX_PIPES - 1] = {0, 0, 0};                       // parts handed to owner pipe op (index op)
+        for (int job = 0; job < njobs; ++job) {
+            const JobDesc &jd = jobs[job];
+            const JobGeom gm = job_geom<NPIPE>(p, jd, split, pipe);
+            const Run &run = gm.run;
+            const int kc0 = gm.kc0, NC = gm.NC, NSK = gm.NSK;
+            const __half *xsa = xs_a;
+            const bool planned = jd.esc_ent != nullptr && !jd.prepass;     // escapes corrected here (else: by the pre-pass)
+            const bool add_to_y = jd.esc_ent != nullptr && jd.prepass;     // Y holds the pre-pass's corrections: add to it
+            const bool prescaled = njobs == 1 && jd.x_mode == 1 && jd.x_dtype != QVB8_F16;
+            // the job's activations are staged and every consumer warp has left its partial sums of them: this lane
+            // keeps the sums of the tokens it writes (8n + 2t + k), added up in warp order (same bits every run)
+            if (alive) alive = mbar_wait(smem_u32(&ctl.x_ready), par(job), abort_flag, 5);
+            float sumx_nt[NT][2];
+            {
+                const float *ps = psum + (job & 1) * CWARPS * M;
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const int m = 8 * n + 2 * t + k;
-                        if (rows[hrow] >= 0 && m < M) out[(int64_t)m * p.Q + rows[hrow]] = y[hrow][n][k];
+                        float sx = 0.f;
+                        if (m < M)
+                            for (int w = 0; w < CWARPS; ++w) sx += ps[w * M + m];
+                        sumx_nt[n][k] = sx;
                     }
-            (void)tile;
-        };
-        for (int i = 0; i < run.nv; ++i) {
-            const Visit v = run_visit(run, i);
-            // ---- the tile's descriptor and escapes arrive in a side slot
-            const int sslot = i % NSIDE;
-            if (alive) alive = mbar_wait(side_full0 + 8 * sslot, (i / NSIDE) & 1, abort_flag, 8, 200);
-            const TileDesc *d = reinterpret_cast<const TileDesc *>(side + sslot * SIDE_BYTES);
-            const EscEntry *ent = reinterpret_cast<const EscEntry *>(side + sslot * SIDE_BYTES + DESC_SLOT);
-            int cnb = 0, myrow[2] = {-1, -1};
-            float myms[2] = {0.f, 0.f}, myts[2] = {0.f, 0.f};
-            if (alive) {
-                cnb = d->nb;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    myrow[h] = d->row[g + 8 * h];
-                    myms[h] = d->ms[g + 8 * h];
-                    myts[h] = d->ts[g + 8 * h];
-                }
-            }
-            // ---- escapes: lane r sums row r's corrections x * (exact - band), in stored order, over the visit's columns
-            if (planned && alive && M == 1) {
-                // One token: the per-entry work (column test, activation fetch) is spread over all 32 lanes first; the
-                // row's sum then runs over (difference, activation) pairs in stored order with the same fused
-                // multiply-adds as below, so the result has the same bits.  This warp shares its scheduler with
-                // issue-bound consumer warps: a long serial loop here ends after the stream and delays the CTA's end.
-                const int clo = (kc0 + v.sb * cps) * KC, chi = (kc0 + min(v.se * cps, NC)) * KC, cbase = kc0 * KC;
-                float2 *pd = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(corr) + (16 * M * 4 + 127) / 128 * 128);
-                const int ne = min(d->nesc, ESC_CAP);
-                for (int e = lane; e < ne; e += 32) {
-                    const EscEntry en = ent[e];
-                    float2 r = make_float2(0.f, 0.f);
-                    if (en.col >= clo && en.col < chi) {
-                        const int cc = en.col - cbase;
-                        r = make_float2(en.delta, __half2float(xs_a[((size_t)slot_of(cc, 0, MP) << 3) + pos_a(cc & 7)]));
-                    }
-                    pd[e] = r;
-                }
-                __syncwarp();
-                if (lane < 16 && d->row[lane] >= 0) {
-                    const int ce0 = d->e0[lane], ce1 = d->e1[lane];
-                    const EscEntry *gent = p.esc_ent + d->esc0;
-                    float a = 0.f;
-                    for (int e = ce0; e < ce1; ++e) {
-                        if (e < ESC_CAP) {
-                            const float2 r = pd[e];
-                            a = __fmaf_rn(r.y, r.x, a);
-                        } else {
-                            const int col = __ldg(&gent[e].col);
-                            if (col >= clo && col < chi) {
-                                const int cc = col - cbase;
-                                a = __fmaf_rn(__half2float(xs_a[((size_t)slot_of(cc, 0, MP) << 3) + pos_a(cc & 7)]), __ldg(&gent[e].delta), a);
-                            }
-                        }
-                    }
-                    corr[lane * M] = a;
-                }
-            } else if (planned && alive) {
-                const int clo = (kc0 + v.sb * cps) * KC, chi = (kc0 + min(v.se * cps, NC)) * KC, cbase = kc0 * KC;
-                if (lane < 16 && d->row[lane] >= 0) {
-                    const int ce0 = d->e0[lane], ce1 = d->e1[lane];
-                    const EscEntry *gent = p.esc_ent + d->esc0;         // the same list in global memory (for the overflow)
-                    float *dst = corr + lane * M;
-                    for (int m0 = 0; m0 < M; m0 += 8) {
-                        float a[8];
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) a[k] = 0.f;
-                        for (int e = ce0; e < ce1; ++e) {
-                            EscEntry en;
-                            if (e < ESC_CAP) en = ent[e];
-                            else { en.col = __ldg(&gent[e].col); en.delta = __ldg(&gent[e].delta); }
-                            if (en.col >= clo && en.col < chi) {
-                                // the column's activations of consecutive tokens lie one slot (8 halves) apart
-                                const int cc = en.col - cbase;
-                                const __half *xp = xs_a + ((size_t)(slot_of(cc, 0, MP) + m0) << 3) + pos_a(cc & 7);
-#pragma unroll
-                                for (int k = 0; k < 8; ++k)
-                                    if (m0 + k < M) a[k] = __fmaf_rn(__half2float(xp[k * 8]), en.delta, a[k]);
-                            }
-                        }
-#pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            if (m0 + k < M) dst[m0 + k] = a[k];
-                    }
-                }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(side_empty0 + 8 * sslot);        // done with the side slot
-            if (tracer && i == 0) trace(p.debug, 9);
-            // ---- the consumer warps' partial sums (or, for a per-element tile, complete row results): taken into
-            // registers and the buffer handed straight back
-            if (alive) alive = mbar_wait(smem_u32(&pc_.red_full), i & 1, abort_flag, 3, 200);
-            if (tracer && i == 0) trace(p.debug, 10);
-            float acc[NT][4];
-#pragma unroll
-            for (int n = 0; n < NT; ++n)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float a = 0.f;
-                    if (cnb != 0) {
-#pragma unroll
-                        for (int w = 0; w < NW; ++w) a += red[(w * 4 * NT + n * 4 + k) * 32 + lane];
-                    } else {
-                        // k = 2 * hrow + kk  ->  row g + 8 * hrow, token 8n + 2t + kk
-                        const int m = 8 * n + 2 * t + (k & 1);
-                        if (m < M) a = red[(g + 8 * (k >> 1)) * M + m];
-                    }
-                    acc[n][k] = a;
-                }
-            __syncwarp();                                               // every lane is done with the buffer
-            if (lane == 0) mbar_arrive(smem_u32(&pc_.red_empty));
-            // y = tau_s * sum(x * id) + min_s * sum(x) + corrections for rows g, g+8 and tokens 8n+2t, 8n+2t+1
-            // (per-element rows arrive complete); the min_s term goes with the visit that holds the first stage
-            float y[2][NT][2];
-#pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow)
-#pragma unroll
-                for (int n = 0; n < NT; ++n)
-#pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        const int m = 8 * n + 2 * t + k;
-                        float val = acc[n][2 * hrow + k];
-                        if (myrow[hrow] >= 0 && m < M) {
-                            if (cnb != 0) {
-                                val *= myts[hrow];
-                                if (v.sb == 0) {
-                                    float sx = ctl.sumx[split_sums ? m * NPIPE : m];
-                                    if (split_sums)
-#pragma unroll
-                                        for (int q = 1; q < NPIPE; ++q) sx += ctl.sumx[m * NPIPE + q];
-                                    val = __fmaf_rn(myms[hrow], sx, val);
-                                }
-                            }
-                            if (planned) val += corr[(g + 8 * hrow) * M + m];
-                            if (prescaled) val *= pow2f(ctl.kexp[m]);
-                        }
-                        y[hrow][n][k] = val;
-                    }
-            __syncwarp();                                               // every lane is done with corr
-            // a tile cut by run boundaries: the pipe that holds its first stage owns it, the later pipes hand their
-            // parts over in shared memory; the owner adds them up when its run is done
-            const bool partial = !(v.sb == 0 && v.se == NSK);
-            bool emit = true;
-            if (partial) {
-                const int op = (v.tile * NSK - uc0) / Lp;               // the pipe that holds the tile's first stage
-                float *dst;
-                if (op == pipe) {
-                    dst = own + pipe * xch_floats;
-                    own_contrib = min((v.tile * NSK + NSK - 1 - uc0) / Lp, NPIPE - 1) - op;
-                    own_row[0] = myrow[0]; own_row[1] = myrow[1];
-                    own_tile = v.tile;
-                } else {
-                    dst = xch + (op * (MAX_PIPES - 1) + (pipe - op - 1)) * xch_floats;
-                }
+            if (lane == 0) mbar_arrive(smem_u32(&ctl.fin_started));
+            int own_contrib = 0, own_row[2] = {-1, -1};
+            // writes a finished tile (of this K-range): the result itself, or with several K-ranges a partial result; the
+            // K-ranges' partial results of all of a CTA's tiles are added up in range order at the end of the kernel
+            auto emit_tile = [&](const int (&rows)[2], const float (&y)[2][NT][2]) {
+                float *out = p.S == 1 ? jd.Y : p.part + (int64_t)split * M * jd.Q;
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow)
 #pragma unroll
@@ -1103,193 +1092,375 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
 #pragma unroll
                         for (int k = 0; k < 2; ++k) {
                             const int m = 8 * n + 2 * t + k;
-                            if (m < M) dst[(g + 8 * hrow) * M + m] = y[hrow][n][k];
+                            if (rows[hrow] >= 0 && m < M) {
+                                float *dst = out + (int64_t)m * jd.Q + rows[hrow];
+                                if (add_to_y) atomicAdd(dst, y[hrow][n][k]);   // one addition per element: any order gives the same sum
+                                else *dst = y[hrow][n][k];
+                            }
                         }
-                if (op != pipe) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl.xch_full[op * (MAX_PIPES - 1) + (pipe - op - 1)]));
-                }
-                emit = false;
-            }
-            if (tracer && i == 0) trace(p.debug, 11);
-            if (emit) emit_tile(v.tile, myrow, y);
-            if (tracer && i == 0) trace(p.debug, 12);
-        }
-        // ---- the tile this pipe shares with later pipes: their parts have long arrived
-        if (own_contrib > 0) {
-            for (int j = 0; j < own_contrib; ++j)
-                if (alive) alive = mbar_wait(smem_u32(&ctl.xch_full[pipe * (MAX_PIPES - 1) + j]), 0, abort_flag, 9);
-            float y[2][NT][2];
+            };
+            for (int i = 0; i < run.nv; ++i, ++vis) {
+                const Visit v = run_visit(run, i);
+                // ---- the tile's descriptor and escapes arrive in a side slot
+                const int sslot = vis % NSIDE;
+                if (alive) alive = mbar_wait(side_full0 + 8 * sslot, par(vis / NSIDE), abort_flag, 8, 200);
+                const TileDesc *d = reinterpret_cast<const TileDesc *>(side + sslot * side_bytes);
+                const EscEntry *ent = reinterpret_cast<const EscEntry *>(side + sslot * side_bytes + DESC_SLOT);
+                int cnb = 0, myrow[2] = {-1, -1};
+                float myms[2] = {0.f, 0.f}, myts[2] = {0.f, 0.f};
+                if (alive) {
+                    cnb = d->nb;
 #pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow)
+                    for (int h = 0; h < 2; ++h) {
+                        myrow[h] = d->row[g + 8 * h];
+                        myms[h] = d->ms[g + 8 * h];
+                        myts[h] = d->ts[g + 8 * h];
+                    }
+                }
+                // ---- escapes: lane r sums row r's corrections x * (exact - band), in stored order, over the visit's columns
+                if (planned && alive && M == 1) {
+                    // One token: the per-entry work (column test, activation fetch) is spread over all 32 lanes first; the
+                    // row's sum then runs over (difference, activation) pairs in stored order with the same fused
+                    // multiply-adds as below, so the result has the same bits.  This warp shares its scheduler with
+                    // issue-bound consumer warps: a long serial loop here ends after the stream and delays the CTA's end.
+                    const int clo = (kc0 + v.sb * cps) * KC, chi = (kc0 + min(v.se * cps, NC)) * KC, cbase = kc0 * KC;
+                    float2 *pd = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(corr) + (16 * M * 4 + 127) / 128 * 128);
+                    const int ne = min(d->nesc, esc_cap);
+                    for (int e = lane; e < ne; e += 32) {
+                        const EscEntry en = ent[e];
+                        float2 r = make_float2(0.f, 0.f);
+                        if (en.col >= clo && en.col < chi) {
+                            const int cc = en.col - cbase;
+                            r = make_float2(en.delta, __half2float(xsa[((size_t)slot_of(cc, 0, MP) << 3) + pos_a(cc & 7)]));
+                        }
+                        pd[e] = r;
+                    }
+                    __syncwarp();
+                    if (lane < 16 && d->row[lane] >= 0) {
+                        const int ce0 = d->e0[lane], ce1 = d->e1[lane];
+                        const EscEntry *gent = jd.esc_ent + d->esc0;
+                        float a = 0.f;
+                        for (int e = ce0; e < ce1; ++e) {
+                            if (e < esc_cap) {
+                                const float2 r = pd[e];
+                                a = __fmaf_rn(r.y, r.x, a);
+                            } else {
+                                const int col = __ldg(&gent[e].col);
+                                if (col >= clo && col < chi) {
+                                    const int cc = col - cbase;
+                                    a = __fmaf_rn(__half2float(xsa[((size_t)slot_of(cc, 0, MP) << 3) + pos_a(cc & 7)]), __ldg(&gent[e].delta), a);
+                                }
+                            }
+                        }
+                        corr[lane * M] = a;
+                    }
+                } else if (planned && alive) {
+                    const int clo = (kc0 + v.sb * cps) * KC, chi = (kc0 + min(v.se * cps, NC)) * KC, cbase = kc0 * KC;
+                    if (lane < 16 && d->row[lane] >= 0) {
+                        const int ce0 = d->e0[lane], ce1 = d->e1[lane];
+                        const EscEntry *gent = jd.esc_ent + d->esc0;    // the same list in global memory (for the overflow)
+                        float *dst = corr + lane * M;
+                        for (int m0 = 0; m0 < M; m0 += 8) {
+                            float a[8];
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) a[k] = 0.f;
+                            for (int e = ce0; e < ce1; ++e) {
+                                EscEntry en;
+                                if (e < esc_cap) en = ent[e];
+                                else { en.col = __ldg(&gent[e].col); en.delta = __ldg(&gent[e].delta); }
+                                if (en.col >= clo && en.col < chi) {
+                                    // the column's activations of consecutive tokens lie one slot (8 halves) apart
+                                    const int cc = en.col - cbase;
+                                    const __half *xp = xsa + ((size_t)(slot_of(cc, 0, MP) + m0) << 3) + pos_a(cc & 7);
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k)
+                                        if (m0 + k < M) a[k] = __fmaf_rn(__half2float(xp[k * 8]), en.delta, a[k]);
+                                }
+                            }
+#pragma unroll
+                            for (int k = 0; k < 8; ++k)
+                                if (m0 + k < M) dst[m0 + k] = a[k];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(side_empty0 + 8 * sslot);    // done with the side slot
+                if (tracer && vis == 0) trace(p.debug, 9);
+                // ---- the consumer warps' partial sums (or, for a per-element tile, complete row results): taken into
+                // registers and the buffer handed straight back
+                const int rb = vis & 1;
+                const float *redb = red + rb * RED_FLOATS;
+                if (alive) alive = mbar_wait(smem_u32(&pc_.red_full[rb]), par(vis / 2), abort_flag, 3, 200);
+                if (tracer && vis == 0) trace(p.debug, 10);
+                float acc[NT][4];
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
 #pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        const int m = 8 * n + 2 * t + k;
-                        float val = 0.f;
-                        if (m < M) {
-                            const int o = (g + 8 * hrow) * M + m;
-                            val = own[pipe * xch_floats + o];
-                            for (int j = 0; j < own_contrib; ++j) val += xch[(pipe * (MAX_PIPES - 1) + j) * xch_floats + o];
+                    for (int k = 0; k < 4; ++k) {
+                        float a = 0.f;
+                        if (cnb != 0) {
+#pragma unroll
+                            for (int w = 0; w < NW; ++w) a += redb[(w * 4 * NT + n * 4 + k) * 32 + lane];
+                        } else {
+                            // k = 2 * hrow + kk  ->  row g + 8 * hrow, token 8n + 2t + kk
+                            const int m = 8 * n + 2 * t + (k & 1);
+                            if (m < M) a = redb[(g + 8 * (k >> 1)) * M + m];
                         }
-                        y[hrow][n][k] = val;
+                        acc[n][k] = a;
                     }
-            if (alive) emit_tile(own_tile, own_row, y);
+                __syncwarp();                                           // every lane is done with the buffer
+                if (lane == 0) mbar_arrive(smem_u32(&pc_.red_empty[rb]));
+                // y = tau_s * sum(x * id) + min_s * sum(x) + corrections for rows g, g+8 and tokens 8n+2t, 8n+2t+1
+                // (per-element rows arrive complete); the min_s term goes with the visit that holds the first stage
+                float y[2][NT][2];
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow)
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const int m = 8 * n + 2 * t + k;
+                            float val = acc[n][2 * hrow + k];
+                            if (myrow[hrow] >= 0 && m < M) {
+                                if (cnb != 0) {
+                                    val *= myts[hrow];
+                                    if (v.sb == 0) val = __fmaf_rn(myms[hrow], sumx_nt[n][k], val);
+                                }
+                                if (planned) val += corr[(g + 8 * hrow) * M + m];
+                                if (prescaled) val *= pow2f(ctl.kexp[m]);
+                            }
+                            y[hrow][n][k] = val;
+                        }
+                __syncwarp();                                           // every lane is done with corr
+                // a tile cut by run boundaries: the pipe that holds its first stage owns it, the later pipes hand their
+                // parts over in shared memory; the owner adds them up when its run is done
+                const bool partial = !(v.sb == 0 && v.se == NSK);
+                bool emit = true;
+                if (partial) {
+                    const int op = (v.tile * NSK - gm.uc0) / gm.Lp;     // the pipe that holds the tile's first stage
+                    float *dst;
+                    if (op == pipe) {
+                        dst = own + pipe * xch_floats;
+                        own_contrib = min((v.tile * NSK + NSK - 1 - gm.uc0) / gm.Lp, NPIPE - 1) - op;
+                        own_row[0] = myrow[0]; own_row[1] = myrow[1];
+                    } else {
+                        // the exchange slot is reused from job to job: the owner must have taken the previous part
+                        const int xs = op * (MAX_PIPES - 1) + (pipe - op - 1);
+                        if (give_uses[op] > 0 && alive)
+                            alive = mbar_wait(smem_u32(&ctl.xch_empty[xs]), par(give_uses[op] - 1), abort_flag, 9, 100);
+                        ++give_uses[op];
+                        dst = xch + xs * xch_floats;
+                    }
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; ++hrow)
+#pragma unroll
+                        for (int n = 0; n < NT; ++n)
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const int m = 8 * n + 2 * t + k;
+                                if (m < M) dst[(g + 8 * hrow) * M + m] = y[hrow][n][k];
+                            }
+                    if (op != pipe) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&ctl.xch_full[op * (MAX_PIPES - 1) + (pipe - op - 1)]));
+                    }
+                    emit = false;
+                }
+                if (tracer && vis == 0) trace(p.debug, 11);
+                if (emit) emit_tile(myrow, y);
+                if (tracer && vis == 0) trace(p.debug, 12);
+            }
+            // ---- the tile this pipe shares with later pipes: their parts have long arrived
+            if (own_contrib > 0) {
+                for (int j = 0; j < own_contrib; ++j) {
+                    if (alive) alive = mbar_wait(smem_u32(&ctl.xch_full[pipe * (MAX_PIPES - 1) + j]), par(own_uses[j]), abort_flag, 9);
+                    ++own_uses[j];
+                }
+                float y[2][NT][2];
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow)
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const int m = 8 * n + 2 * t + k;
+                            float val = 0.f;
+                            if (m < M) {
+                                const int o = (g + 8 * hrow) * M + m;
+                                val = own[pipe * xch_floats + o];
+                                for (int j = 0; j < own_contrib; ++j) val += xch[(pipe * (MAX_PIPES - 1) + j) * xch_floats + o];
+                            }
+                            y[hrow][n][k] = val;
+                        }
+                __syncwarp();                                           // every lane has read the parts
+                if (lane == 0)
+                    for (int j = 0; j < own_contrib; ++j) mbar_arrive(smem_u32(&ctl.xch_empty[pipe * (MAX_PIPES - 1) + j]));
+                if (alive) emit_tile(own_row, y);
+            }
         }
         if (tracer) trace(p.debug, 13);
     } else {
         // ================= consumer warps =================
-        // ---- activations of the K-range as fp16 in fragment order (after the previous kernel in the stream): all
-        // consumer warps of the CTA share the work, every one of them reads all of it afterwards
-        pdl_wait();
-        if (tracer && warp == 0) trace(p.debug, 4);
-        {
-            const int groups = NC * 16;                                 // 8-column groups in the range
-            const int total = MP * groups;
-            const int64_t col0 = (int64_t)kc0 * KC;
-            const int ctid = (pipe * NW + warp) * 32 + lane;            // index among the consumer threads
-            constexpr int CTHREADS = NPIPE * NW * 32;
-            constexpr int UNR = 4;                                      // loads in flight per thread
-            const int x_dtype = p.x_dtype;
-            // x_mode 1 (activations beyond the fp16 range): a first pass finds every token's largest magnitude in this
-            // K-range; the token is then staged times 2^-k, k the smallest exponent that brings it into range, and its
-            // results are multiplied by 2^k on the way out -- both exact.  fp16 input needs no prescale.
-            const bool prescale = p.x_mode == 1 && x_dtype != QVB8_F16;
-            if (prescale) {
-                for (int idx = ctid; idx < total; idx += CTHREADS) {
-                    const int m = idx / groups, u8 = idx - m * groups;
-                    if (m < M) {
-                        const int64_t off = (int64_t)m * p.P + col0 + (int64_t)u8 * 8;
-                        const uint32_t mx = x_dtype == QVB8_BF16 ? amax_x8<QVB8_BF16>(p.X, off) : amax_x8<QVB8_F32>(p.X, off);
-                        if (mx > 0x477fffffu) atomicMax(&ctl.amax[m], mx);      // only magnitudes of 2^16 and above matter
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl.amax_ready));
-                mbar_wait(smem_u32(&ctl.amax_ready), 0, abort_flag, 5);
-                if (ctid < M) ctl.kexp[ctid] = (uint8_t)prescale_exp(ctl.amax[ctid]);
-            }
-            for (int base = ctid; base < total; base += CTHREADS * UNR) {
-                uint32_t h[UNR][8];
-#pragma unroll
-                for (int i = 0; i < UNR; ++i) {
-                    const int idx = base + i * CTHREADS;
-                    const int m = idx / groups, u8 = idx - m * groups;  // u8: natural 8-column group number
-                    if (idx < total && m < M) {
-                        const float sc = prescale ? pow2f(-prescale_exp(ctl.amax[m])) : 1.f;
-                        stage_x8_any(x_dtype, p.X, (int64_t)m * p.P + col0 + (int64_t)u8 * 8, h[i], sc);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) h[i][j] = 0u;
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < UNR; ++i) {
-                    const int idx = base + i * CTHREADS;
-                    if (idx >= total) continue;
-                    const int m = idx / groups, u8 = idx - m * groups;
-                    const int sl = slot_of(u8 * 8, m, MP);
-                    *reinterpret_cast<uint4 *>(xs_a + (sl << 3)) = make_uint4(
-                        h[i][0] | (h[i][2] << 16), h[i][1] | (h[i][3] << 16), h[i][4] | (h[i][6] << 16), h[i][5] | (h[i][7] << 16));
-                    if (DUAL)
-                        *reinterpret_cast<uint4 *>(xs_b + (sl << 3)) = make_uint4(
-                            h[i][0] | (h[i][4] << 16), h[i][1] | (h[i][5] << 16), h[i][2] | (h[i][6] << 16), h[i][3] | (h[i][7] << 16));
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl.x_ready));
-        }
-        bool alive = mbar_wait(smem_u32(&ctl.x_ready), 0, abort_flag, 5);
-        if (tracer && warp == 0) trace(p.debug, 5);
-
-        // ---- walk the run
         const int g = lane >> 2, t = lane & 3;
         const bool xvalid = NT > 1 || g < MP;                           // lanes whose token slot exists
         const uint32_t xstep = xvalid ? (uint32_t)(4 * MP * 16) : 0u;   // bytes between consecutive 8-column groups
         const uint32_t xoff = (uint32_t)((t * MP + g) * 16);
-        const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
-        const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
-        const uint32_t red_full = smem_u32(&pc_.red_full), red_empty = smem_u32(&pc_.red_empty);
         const int cpw = cps / NW;
-        for (int i = 0; i < run.nv && alive; ++i) {
-            const Visit v = run_visit(run, i);
-            // the tile's descriptor arrives in a side slot
-            const int sslot = i % NSIDE;
-            if (!mbar_wait(side_full0 + 8 * sslot, (i / NSIDE) & 1, abort_flag, 8)) { alive = false; break; }
-            if (tracer && warp == 0 && i == 0) trace(p.debug, 6);
-            const TileDesc *d = reinterpret_cast<const TileDesc *>(side + sslot * SIDE_BYTES);
-            const int nb = d->nb, cnt = d->cnt;
-            const uint32_t red_par = (i & 1) ^ 1u;                      // the finishing warp has taken the previous visit's sums
-            float acc[NT][4];
-#pragma unroll
-            for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-            if (nb == 0) {
-                // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
-                // start on a 16-byte boundary).  One row per warp at a time, ids byte-wise from global memory; the
-                // ring is not used.
-                if (!mbar_wait(red_empty, red_par, abort_flag, 4)) { alive = false; break; }
-                float *rr_out = red;                                    // [16][M] complete row results
-                const int c_lo = v.sb * cps * KC, c_hi = min(v.se * cps, NC) * KC;
-                for (int rr = warp; rr < cnt; rr += NW) {
-                    const int q = d->row[rr];
-                    const float ms = d->ms[rr], ts = d->ts[rr];
-                    const int rnb = __ldg(p.nbits + q);
-                    const int64_t base = __ldg(p.bit_off + q) + (int64_t)kc0 * KC * rnb;
-                    for (int m0 = 0; m0 < M; m0 += 8) {
-                        float a[8];
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) a[k] = 0.f;
-                        for (int c = c_lo + lane; c < c_hi; c += 32) {
-                            const float wv = band(field_bytes(p.ids, base + (int64_t)c * rnb, rnb), ts, ms);
-#pragma unroll
-                            for (int k = 0; k < 8; ++k)
-                                if (m0 + k < M) a[k] = __fmaf_rn(xs_read(xs_a, c, m0 + k, MP), wv, a[k]);
-                        }
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-#pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
-                            if (lane == 0 && m0 + k < M) rr_out[rr * M + m0 + k] = a[k];
+        bool alive = true;
+        int vis = 0;                                                    // visits walked so far (all jobs)
+        const int cwarp = pipe * NW + warp;                             // index among the CTA's consumer warps
+        for (int job = 0; job < njobs && alive; ++job) {
+            const JobDesc &jd = jobs[job];
+            const JobGeom gm = job_geom<NPIPE>(p, jd, split, pipe);
+            const Run &run = gm.run;
+            const int kc0 = gm.kc0, NC = gm.NC;
+            float *psum_w = psum + ((job & 1) * CWARPS + cwarp) * M;
+            if (job == 0) {
+                // ---- activations of the first job's K-range as fp16 in fragment order (after the previous kernel in the
+                // stream): all consumer warps of the CTA share the work, every one of them reads all of it afterwards
+                pdl_wait();
+                if (tracer && warp == 0) trace(p.debug, 4);
+                const int ctid = cwarp * 32 + lane;                     // index among the consumer threads
+                constexpr int CTHREADS = CWARPS * 32;
+                // x_mode 1 (activations beyond the fp16 range): a first pass finds every token's largest magnitude in this
+                // K-range; the token is then staged times 2^-k, k the smallest exponent that brings it into range, and its
+                // results are multiplied by 2^k on the way out -- both exact.  fp16 input needs no prescale.
+                const bool prescale = njobs == 1 && jd.x_mode == 1 && jd.x_dtype != QVB8_F16;
+                if (prescale) {
+                    const int groups = NC * 16, total = MP * groups;
+                    const int64_t col0 = (int64_t)kc0 * KC;
+                    for (int idx = ctid; idx < total; idx += CTHREADS) {
+                        const int m = idx / groups, u8 = idx - m * groups;
+                        if (m < M) {
+                            const int64_t off = (int64_t)m * jd.P + col0 + (int64_t)u8 * 8;
+                            const uint32_t mx = jd.x_dtype == QVB8_BF16 ? amax_x8<QVB8_BF16>(jd.X, off) : amax_x8<QVB8_F32>(jd.X, off);
+                            if (mx > 0x477fffffu) atomicMax(&ctl.amax[m], mx);  // only magnitudes of 2^16 and above matter
                         }
                     }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl.amax_ready));
+                    mbar_wait(smem_u32(&ctl.amax_ready), 0, abort_flag, 5);
+                    if (ctid < M) ctl.kexp[ctid] = (uint8_t)prescale_exp(ctl.amax[ctid]);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(side_empty0 + 8 * sslot);
+                const uint32_t *amax = ctl.amax;
+                stage_slice<DUAL, true>(jd.X, jd.x_dtype, jd.P, kc0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
+                                        [&](int m) { return prescale ? pow2f(-prescale_exp(amax[m])) : 1.f; }, psum_w);
             } else {
+                // ---- a later job: its raw activations arrived by a bulk copy while the job before it streamed.  Every
+                // consumer warp of the CTA meets here: all have left the previous job (the staged activations may be
+                // replaced), then each converts its slice.  With all of them in this rarely executed code at once none
+                // is starved by warps that stream.
                 __syncwarp();
-                if (lane == 0) mbar_arrive(side_empty0 + 8 * sslot);    // only the width was needed
-                const uint32_t xbase = (nb >= 6 || !DUAL) ? xs_a32 : xs_b32;
-                bool ok;
+                if (lane == 0) mbar_arrive(smem_u32(&ctl.job_done));
+                alive = mbar_wait(smem_u32(&ctl.job_done), par(job - 1), abort_flag, 10);
+                if (alive) alive = mbar_wait(smem_u32(&ctl.raw_full), par(job - 1), abort_flag, 11);
+                // the finishing warps have reached the previous job: they wait on the same once-per-job barriers by
+                // parity, so no barrier may complete twice while one of them still waits for the first completion
+                if (alive) alive = mbar_wait(smem_u32(&ctl.fin_started), par(job - 1), abort_flag, 12);
+                if (!alive) break;
+                stage_slice<DUAL, false>(raw, jd.x_dtype, jd.P, 0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
+                                         [](int) { return 1.f; }, psum_w);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl.x_ready));
+            alive = mbar_wait(smem_u32(&ctl.x_ready), par(job), abort_flag, 5);
+            if (!alive) break;
+            // the raw activations of the NEXT job: one bulk copy into the buffer this job's conversion has just released
+            if (job + 1 < njobs && cwarp == 0 && lane == 0) {
+                const JobDesc &nd = jobs[job + 1];
+                const uint32_t bytes = (uint32_t)((int64_t)M * nd.P * (nd.x_dtype == QVB8_F32 ? 4 : 2));
+                mbar_expect_tx(smem_u32(&ctl.raw_full), bytes);
+                bulk_g2s(smem_u32(raw), nd.X, bytes, smem_u32(&ctl.raw_full));
+            }
+            if (tracer && warp == 0) { if (job == 0) trace(p.debug, 5); if (job < 4) trace(p.debug, 16 + 4 * job); }
+            const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
+            const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
+            const __half *xsa = xs_a;
+
+            // ---- walk the run
+            for (int i = 0; i < run.nv && alive; ++i, ++vis) {
+                const Visit v = run_visit(run, i);
+                // the tile's descriptor arrives in a side slot
+                const int sslot = vis % NSIDE;
+                if (!mbar_wait(side_full0 + 8 * sslot, par(vis / NSIDE), abort_flag, 8)) { alive = false; break; }
+                if (tracer && warp == 0 && vis == 0) trace(p.debug, 6);
+                const TileDesc *d = reinterpret_cast<const TileDesc *>(side + sslot * side_bytes);
+                const int nb = d->nb, cnt = d->cnt;
+                const int rb = vis & 1;                                 // hand-over buffer of this visit: free once the finishing
+                float *redb = red + rb * RED_FLOATS;                    // warp has taken the sums of the visit before last
+                const uint32_t red_full = smem_u32(&pc_.red_full[rb]), red_empty = smem_u32(&pc_.red_empty[rb]);
+                const uint32_t red_par = par(vis / 2) ^ 1u;
+                float acc[NT][4];
+#pragma unroll
+                for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+                if (nb == 0) {
+                    // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
+                    // start on a 16-byte boundary).  One row per warp at a time, ids byte-wise from global memory; the
+                    // ring is not used.
+                    if (!mbar_wait(red_empty, red_par, abort_flag, 4)) { alive = false; break; }
+                    float *rr_out = redb;                               // [16][M] complete row results
+                    const int c_lo = v.sb * cps * KC, c_hi = min(v.se * cps, NC) * KC;
+                    for (int rr = warp; rr < cnt; rr += NW) {
+                        const int q = d->row[rr];
+                        const float ms = d->ms[rr], ts = d->ts[rr];
+                        const int rnb = __ldg(jd.nbits + q);
+                        const int64_t base = __ldg(jd.bit_off + q) + (int64_t)kc0 * KC * rnb;
+                        for (int m0 = 0; m0 < M; m0 += 8) {
+                            float a[8];
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) a[k] = 0.f;
+                            for (int c = c_lo + lane; c < c_hi; c += 32) {
+                                const float wv = band(field_bytes(jd.ids, base + (int64_t)c * rnb, rnb), ts, ms);
+#pragma unroll
+                                for (int k = 0; k < 8; ++k)
+                                    if (m0 + k < M) a[k] = __fmaf_rn(xs_read(xsa, c, m0 + k, MP), wv, a[k]);
+                            }
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) {
+#pragma unroll
+                                for (int o = 16; o > 0; o >>= 1) a[k] += __shfl_xor_sync(0xffffffffu, a[k], o);
+                                if (lane == 0 && m0 + k < M) rr_out[rr * M + m0 + k] = a[k];
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(side_empty0 + 8 * sslot);
+                } else {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(side_empty0 + 8 * sslot);    // only the width was needed
+                    const uint32_t xbase = (nb >= 6 || !DUAL) ? xs_a32 : xs_b32;
+                    bool ok;
 #define QV_STREAM(NB_)                                                                                                    \
     ok = cpw == 2 ? stream_tile<NB_, NT, DUAL, 2>(p, ctl.pair_table, abort_flag, rp, NC, v.sb, v.se, warp, lane, xbase, xstep, acc) \
        : cpw == 4 ? stream_tile<NB_, NT, DUAL, 4>(p, ctl.pair_table, abort_flag, rp, NC, v.sb, v.se, warp, lane, xbase, xstep, acc) \
                   : stream_tile<NB_, NT, DUAL, 0>(p, ctl.pair_table, abort_flag, rp, NC, v.sb, v.se, warp, lane, xbase, xstep, acc)
-                switch (nb) {                                           // uniform over the pipe
-                    case 7: QV_STREAM(7); break;
-                    case 6: QV_STREAM(6); break;
-                    case 8: QV_STREAM(8); break;
-                    case 5: QV_STREAM(5); break;
-                    case 4: QV_STREAM(4); break;
-                    default: QV_STREAM(3); break;
-                }
+                    switch (nb) {                                       // uniform over the pipe
+                        case 7: QV_STREAM(7); break;
+                        case 6: QV_STREAM(6); break;
+                        case 8: QV_STREAM(8); break;
+                        case 5: QV_STREAM(5); break;
+                        case 4: QV_STREAM(4); break;
+                        default: QV_STREAM(3); break;
+                    }
 #undef QV_STREAM
-                if (!ok) { alive = false; break; }
-                // hand the partial sums to the finishing warp and go on with the next visit
-                if (!mbar_wait(red_empty, red_par, abort_flag, 4)) { alive = false; break; }
+                    if (!ok) { alive = false; break; }
+                    // hand the partial sums to the finishing warp and go on with the next visit
+                    if (!mbar_wait(red_empty, red_par, abort_flag, 4)) { alive = false; break; }
 #pragma unroll
-                for (int n = 0; n < NT; ++n)
+                    for (int n = 0; n < NT; ++n)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) red[(warp * 4 * NT + n * 4 + k) * 32 + lane] = acc[n][k];
+                        for (int k = 0; k < 4; ++k) redb[(warp * 4 * NT + n * 4 + k) * 32 + lane] = acc[n][k];
+                }
+                if (tracer && warp == 0 && vis == 0) trace(p.debug, 7);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(red_full);
             }
-            if (tracer && warp == 0 && i == 0) trace(p.debug, 7);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(red_full);
+            if (tracer && warp == 0 && job < 4) trace(p.debug, 17 + 4 * job);
         }
         if (tracer && warp == 0) trace(p.debug, 8);
     }
-    // ---- several K-ranges: the CTAs (x, 0..S-1) hold partial results of the same tiles; whichever of them gets here
-    // last adds the ranges up in range order for all those tiles at once (one ticket per CTA column, all threads load)
+    // ---- several K-ranges (single job): the CTAs (x, 0..S-1) hold partial results of the same tiles; whichever of them
+    // gets here last adds the ranges up in range order for all those tiles at once (one ticket per CTA column)
     if (p.S > 1) {
         __threadfence();                                                // this thread's partial results are visible
         __syncthreads();
@@ -1298,16 +1469,19 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         __syncthreads();
         if (last_range) {
             __threadfence();
+            const JobDesc &jd = jobs[0];
+            int ct0, ct1;
+            cta_tiles(jd.ntiles, gridDim.x, blockIdx.x, ct0, ct1);      // (a single job is never rotated)
             const int per_tile = 16 * M;
             const int total = (ct1 - ct0) * per_tile;
             for (int i = tid; i < total; i += blockDim.x) {
                 const int tl = ct0 + i / per_tile, rem = i % per_tile;
-                const int row = __ldg(&p.tiles[tl].row[rem / M]), m = rem % M;
+                const int row = __ldg(&jd.tiles[tl].row[rem / M]), m = rem % M;
                 if (row >= 0) {
-                    const int64_t o = (int64_t)m * p.Q + row;
+                    const int64_t o = (int64_t)m * jd.Q + row;
                     float sum = 0.f;
-                    for (int r = 0; r < p.S; ++r) sum += __ldcg(p.part + (int64_t)r * M * p.Q + o);
-                    p.Y[o] = sum;
+                    for (int r = 0; r < p.S; ++r) sum += __ldcg(p.part + (int64_t)r * M * jd.Q + o);
+                    jd.Y[o] = sum;
                 }
             }
             if (tid == 0) p.ticket[blockIdx.x] = 0;
@@ -1321,10 +1495,15 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
 struct Plan {
     int ctas_x, S, nc_per, nc_total, MP, NT, nstg, cps, part_slots, npipe;
     int rs[6], slot_bytes;
+    int xs_halves;             // capacity of the staged activations (halves per layout)
+    int raw_bytes;             // raw-activation buffer of a list launch
+    int esc_cap;               // escape entries per side slot
     bool dual;
     size_t smem_bytes;
     int64_t part_bytes, ticket_bytes;
 };
+constexpr int64_t JOB_TABLE_BYTES_1 = 128;                              // shared-memory job table of a one-job launch
+static int64_t psum_bytes_for(int npipe, int64_t M) { return (2 * (int64_t)npipe * NW * M * 4 + 127) / 128 * 128; }
 
 static int device_sms() {
     static thread_local int dev_cached = -1, n = 148;
@@ -1337,9 +1516,9 @@ static int device_sms() {
     return n;
 }
 
-// Dynamic shared memory of a CTA: 227 KB per block on this architecture, less one kilobyte for the static part.
-constexpr int64_t MAX_DYN_SMEM = 227 * 1024 - 1024;
-static_assert(sizeof(Control) <= 1024 - 64, "static shared memory allowance");
+// Dynamic shared memory of a CTA: 227 KB per block on this architecture, less two kilobytes for the static part.
+constexpr int64_t MAX_DYN_SMEM = 227 * 1024 - 2048;
+static_assert(sizeof(Control) <= 2048 - 64, "static shared memory allowance");
 
 // tuning hooks (qvb8_small_m_set_tuning): 0 = choose automatically
 static int g_fill_pct = 0, g_force_s = 0, g_force_nstg = 0, g_force_cps = 0, g_debug = 0, g_force_pipes = 0;
@@ -1365,8 +1544,10 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P, int max_width = 8) {
     if (cps < NW) cps = NW;
     if (cps > MAX_CPS) cps = MAX_CPS;
     // per pipe next to its ring: side ring, hand-over buffer, escape corrections
-    const int64_t pipe_fixed = (int64_t)NSIDE * SIDE_BYTES + (int64_t)NW * 4 * pl.NT * 32 * 4 + corr_bytes(M);
-    const int64_t shared_fixed = 128 + ((XCH_SLOTS + npipe) * 16 * M * 4 + 127) / 128 * 128;      // zeros, exchange buffers
+    pl.esc_cap = esc_cap_for(P);
+    const int64_t pipe_fixed = (int64_t)NSIDE * side_slot_bytes(pl.esc_cap) + (int64_t)2 * NW * 4 * pl.NT * 32 * 4 + corr_bytes(M, pl.esc_cap);
+    const int64_t shared_fixed = JOB_TABLE_BYTES_1 + 128 + psum_bytes_for(npipe, M) +
+                                 ((XCH_SLOTS + npipe) * 16 * M * 4 + 127) / 128 * 128;   // job table, zeros, activation sums, exchange buffers
     for (;; cps -= NW) {                                                // the longest stage of which two fit per pipe
         pl.cps = cps;
         pl.slot_bytes = 0;                                              // a ring slot: 16 rows of the widest width
@@ -1413,10 +1594,67 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P, int max_width = 8) {
     if (nstg < 2) nstg = 2;
     pl.nstg = nstg;
     pl.smem_bytes = (size_t)(xs_bytes + shared_fixed + npipe * (pipe_fixed + (int64_t)nstg * pl.slot_bytes));
+    pl.xs_halves = pl.nc_per * 16 * pl.MP * 8;
+    pl.raw_bytes = 0;
     pl.part_slots = pl.S > 1 ? pl.S : 0;                                // partial results only between K-ranges
     pl.part_bytes = ((int64_t)pl.part_slots * M * Q * 4 + 255) / 256 * 256;
     pl.ticket_bytes = pl.S > 1 ? TICKET_BYTES : 0;
     return pl;
+}
+
+// Plan of a launch that runs a list of jobs (P and activation element size of every job given): K is never split; one
+// buffer holds the staged activations of the current job, a second one the raw activations of the next; what is left
+// goes to the copy rings.  Returns false when the list does not fit (activations too large for shared memory next to
+// two-stage rings).
+static bool make_group_plan(int64_t M, const int64_t *Ps, const int *esizes, int njobs, Plan &pl) {
+    pl = Plan{};
+    pl.NT = (int)((M + 7) / 8);
+    pl.MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * pl.NT;
+    const int npipe = pipes_for(pl.NT);
+    pl.npipe = npipe;
+    pl.dual = false;
+    int64_t pmax = 0, pmin = Ps[0], raw = 0;
+    for (int j = 0; j < njobs; ++j) {
+        if (Ps[j] > pmax) pmax = Ps[j];
+        if (Ps[j] < pmin) pmin = Ps[j];
+        if (j >= 1 && M * Ps[j] * esizes[j] > raw) raw = M * Ps[j] * esizes[j];
+    }
+    raw = (raw + 127) / 128 * 128;
+    const int64_t cta_bytes = MAX_DYN_SMEM - 256;
+    const int64_t jobs_bytes = ((int64_t)njobs * (int64_t)sizeof(JobDesc) + 127) / 128 * 128;
+    pl.esc_cap = ESC_CAP_MIN;                                           // (a list's escapes are applied by the pre-pass)
+    const int64_t pipe_fixed = (int64_t)NSIDE * side_slot_bytes(pl.esc_cap) + (int64_t)2 * NW * 4 * pl.NT * 32 * 4 + corr_bytes(M, pl.esc_cap);
+    const int64_t shared_fixed = jobs_bytes + 128 + psum_bytes_for(npipe, M) + ((XCH_SLOTS + npipe) * 16 * M * 4 + 127) / 128 * 128;
+    const int64_t xs_bytes = pmax * pl.MP * 2 + raw;
+    int cps = g_force_cps ? g_force_cps : (pmin / KC >= 16 ? 8 : 4);
+    cps = cps / NW * NW;
+    if (cps < NW) cps = NW;
+    if (cps > MAX_CPS) cps = MAX_CPS;
+    int nstg = 0;
+    for (;; cps -= NW) {
+        pl.cps = cps;
+        pl.slot_bytes = 0;
+        for (int nb = 3; nb <= 8; ++nb) {
+            pl.rs[nb - 3] = stage_row_stride(nb, cps);
+            if (16 * pl.rs[nb - 3] > pl.slot_bytes) pl.slot_bytes = 16 * pl.rs[nb - 3];
+        }
+        const int64_t room = (cta_bytes - shared_fixed - xs_bytes) / npipe - pipe_fixed;
+        nstg = room > 0 ? (int)(room / pl.slot_bytes) : 0;
+        if (nstg >= 2 || cps <= NW) break;
+    }
+    if (nstg < 2) return false;
+    if (g_force_nstg && g_force_nstg < nstg) nstg = g_force_nstg;
+    if (nstg > MAX_STAGES) nstg = MAX_STAGES;
+    pl.nstg = nstg;
+    pl.S = 1;
+    pl.nc_per = (int)(pmax / KC);
+    pl.nc_total = pl.nc_per;
+    pl.xs_halves = (int)(pmax / KC) * 16 * pl.MP * 8;
+    pl.raw_bytes = (int)raw;
+    int64_t ctas = (int64_t)device_sms() * (g_fill_pct ? g_fill_pct : 100) / 100;
+    pl.ctas_x = (int)(ctas < 1 ? 1 : ctas);
+    pl.smem_bytes = (size_t)(xs_bytes + shared_fixed + npipe * (pipe_fixed + (int64_t)nstg * pl.slot_bytes));
+    return true;
 }
 
 static bool fast_layout_ok(const qvb8_pack *w, const void *X) {
@@ -1548,6 +1786,28 @@ QV_API int qvb8_plan_build(const qvb8_pack *w, void *plan, int64_t plan_bytes, v
     return QVB8_OK;
 }
 
+namespace qv {
+static void fill_job(JobDesc &jd, const qvb8_pack *w, const void *plan, const void *X, float *Y, int x_dtype, int x_mode, int rot,
+                     int prepass = 0) {
+    const PlanLayout L = plan_layout(w->Q, w->n_esc);
+    const uint8_t *base = reinterpret_cast<const uint8_t *>(plan);
+    jd = JobDesc{};
+    jd.ids = w->ids; jd.nbits = w->nbits; jd.bit_off = w->bit_off;
+    jd.tiles = reinterpret_cast<const TileDesc *>(base + L.tiles);
+    jd.ntiles = L.max_tiles;
+    jd.esc_ent = w->n_esc > 0 ? reinterpret_cast<const EscEntry *>(base + L.esc_ent) : nullptr;
+    jd.X = X; jd.Y = Y;
+    jd.Q = (int)w->Q; jd.P = (int)w->P; jd.nc_total = (int)(w->P / KC);
+    jd.x_dtype = x_dtype; jd.x_mode = x_mode; jd.rot = rot; jd.prepass = prepass;
+}
+static void fill_launch(SmallMParams &prm, const Plan &pl, int M) {
+    prm.M = M; prm.MP = pl.MP; prm.S = pl.S; prm.nc_per = pl.nc_per; prm.nstg = pl.nstg; prm.debug = g_debug;
+    prm.cps = pl.cps; prm.slot_bytes = pl.slot_bytes; prm.esc_cap = pl.esc_cap;
+    prm.xs_halves = pl.xs_halves; prm.raw_bytes = pl.raw_bytes;
+    for (int i = 0; i < 6; ++i) prm.rs[i] = pl.rs[i];
+}
+}  // namespace qv
+
 QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, int x_dtype, int x_mode, int64_t M,
                            float *Y, void *scratch, int64_t scratch_bytes, int flags, void *stream) {
     using namespace qv;
@@ -1564,22 +1824,162 @@ QV_API int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, 
                         (long long)(pl.part_bytes + pl.ticket_bytes), (long long)scratch_bytes);
         if (!aligned(scratch, 16)) return fail(QVB8_ERR_ALIGN, "qvb8_small_m: scratch must be 16-byte aligned");
     }
-    const PlanLayout L = plan_layout(w->Q, w->n_esc);
-    const uint8_t *base = reinterpret_cast<const uint8_t *>(plan);
-    SmallMParams prm{};
-    prm.ids = w->ids; prm.nbits = w->nbits; prm.bit_off = w->bit_off;
-    prm.tiles = reinterpret_cast<const TileDesc *>(base + L.tiles);
-    prm.ntiles = L.max_tiles;
-    if (w->n_esc > 0) prm.esc_ent = reinterpret_cast<const EscEntry *>(base + L.esc_ent);
-    prm.X = X; prm.Y = Y;
+    static thread_local SmallMParams prm;                               // (a few kilobytes: kept off the stack)
+    prm.njobs = 1;
+    fill_job(prm.jobs[0], w, plan, X, Y, x_dtype, x_mode, 0);
     prm.ticket = reinterpret_cast<int *>(scratch);
     prm.part = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + TICKET_BYTES);
-    prm.Q = (int)w->Q; prm.P = (int)w->P; prm.M = (int)M; prm.MP = pl.MP; prm.S = pl.S; prm.x_dtype = x_dtype; prm.x_mode = x_mode;
-    prm.nc_per = pl.nc_per; prm.nc_total = pl.nc_total; prm.nstg = pl.nstg; prm.debug = g_debug;
-    prm.cps = pl.cps; prm.slot_bytes = pl.slot_bytes;
-    for (int i = 0; i < 6; ++i) prm.rs[i] = pl.rs[i];
+    fill_launch(prm, pl, (int)M);
     const bool pdl = (flags & QVB8_FLAG_PDL) != 0;
     return launch_nt(prm, pl, st, pdl);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// several products behind one launch
+namespace qv {
+
+// Escape pre-pass of a job list: Y[m, row] = sum over the row's escapes of x[m, col] * (exact - band), for every row of
+// every job that has escapes (rows without escapes get 0); the streaming kernel then ADDS its products.  Inside the
+// streaming kernel this small, latency-bound sum sits on the finishing warps, which get few issue slots next to the
+// warps that stream.  Here it is one THREAD per (tile, row slot) -- a row has a handful of escapes -- so a list of
+// dozens of jobs is one resident wave and costs a few dependent memory latencies: fused multiply-adds in stored order
+// (same bits every run), entries fetched four at a time so their latencies overlap.
+// The activation is narrowed to saturated fp16 first, as the streaming kernel narrows it.
+struct EscPrepassParams {
+    JobDesc jobs[MAX_JOBS];
+    int tile_start[MAX_JOBS + 1];      // first global tile number of job j (jobs without escapes hold no tiles here)
+    int njobs, M;
+};
+__device__ __forceinline__ float prepass_x(const JobDesc &jd, int m, int col) {
+    const int64_t i = (int64_t)m * jd.P + col;
+    const float x = jd.x_dtype == QVB8_F32 ? load_x<QVB8_F32>(jd.X, i)
+                  : jd.x_dtype == QVB8_BF16 ? load_x<QVB8_BF16>(jd.X, i) : load_x<QVB8_F16>(jd.X, i);
+    return __half2float(sat_half(x));
+}
+__global__ void __launch_bounds__(128) escape_prepass_kernel(const __grid_constant__ EscPrepassParams p) {
+    const int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int gt = (int)(gi >> 4), slot = (int)(gi & 15);
+    if (gt >= p.tile_start[p.njobs]) return;
+    int j = 0;
+    while (j + 1 < p.njobs && gt >= p.tile_start[j + 1]) ++j;
+    const JobDesc &jd = p.jobs[j];
+    const TileDesc *d = jd.tiles + (gt - p.tile_start[j]);
+    const int row = __ldg(&d->row[slot]);
+    if (row < 0) return;
+    const int e0 = __ldg(&d->e0[slot]), e1 = __ldg(&d->e1[slot]);
+    const EscEntry *ent = jd.esc_ent + __ldg(&d->esc0);
+    for (int m0 = 0; m0 < p.M; m0 += 4) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int e = e0; e < e1; e += 4) {
+            int col[4];
+            float delta[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int ee = e + k < e1 ? e + k : e1 - 1;
+                col[k] = __ldg(&ent[ee].col);
+                delta[k] = e + k < e1 ? __ldg(&ent[ee].delta) : 0.f;
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                if (m0 + t < p.M) {
+                    float x[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) x[k] = prepass_x(jd, m0 + t, col[k]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (e + k < e1) s[t] = __fmaf_rn(x[k], delta[k], s[t]);
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+            if (m0 + t < p.M) jd.Y[(int64_t)(m0 + t) * jd.Q + row] = s[t];
+    }
+}
+
+// Can these jobs run as one list launch?  All through the streaming kernel (plan, layout), none K-split.
+static bool group_fits(const qvb8_job *jobs, int n, int64_t M, Plan &pl) {
+    int64_t Ps[MAX_JOBS];
+    int esizes[MAX_JOBS];
+    for (int j = 0; j < n; ++j) {
+        const qvb8_job &jb = jobs[j];
+        if (!jb.plan || !aligned(jb.plan, 16) || !fast_layout_ok(jb.w, jb.X) ||
+            (jb.w->Q + 15) / 16 + NCLASS - 1 > MAX_TICKET_TILES || jb.w->Q == 0 ||
+            (jb.x_mode == 1 && jb.x_dtype != QVB8_F16))                   // the prescale pass is the single launch's
+            return false;
+        Ps[j] = jb.w->P;
+        esizes[j] = jb.x_dtype == QVB8_F32 ? 4 : 2;
+    }
+    return make_group_plan(M, Ps, esizes, n, pl);
+}
+}  // namespace qv
+
+QV_API int64_t qvb8_small_m_group_scratch_bytes(const qvb8_job *jobs, int njobs, int64_t M) {
+    using namespace qv;
+    if (!jobs || njobs <= 0 || M < 1 || M > MAX_M) return 0;
+    int64_t need = 0;
+    for (int j0 = 0; j0 < njobs; j0 += MAX_JOBS) {
+        const int n = njobs - j0 < MAX_JOBS ? njobs - j0 : MAX_JOBS;
+        bool ok = true;
+        for (int j = 0; j < n; ++j) ok = ok && jobs[j0 + j].w && jobs[j0 + j].w->P > 0;
+        Plan pl;
+        if (ok && n > 1 && group_fits(jobs + j0, n, M, pl)) continue;
+        for (int j = 0; j < n; ++j) {                                   // this part of the list runs job by job
+            const qvb8_pack *w = jobs[j0 + j].w;
+            if (!w) continue;
+            const int64_t b = qvb8_small_m_scratch_bytes(M, w->Q, w->P);
+            if (b > need) need = b;
+        }
+    }
+    return need;
+}
+
+QV_API int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *scratch, int64_t scratch_bytes, int flags,
+                              void *stream) {
+    using namespace qv;
+    if (!jobs || njobs <= 0) return fail(QVB8_ERR_ARG, "qvb8_small_m_group: no jobs");
+    for (int j = 0; j < njobs; ++j) {
+        const qvb8_job &jb = jobs[j];
+        if (int rc = check_small_m_args(jb.w, jb.X, jb.x_dtype, jb.x_mode, M, jb.Y, "qvb8_small_m_group")) return rc;
+    }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const bool pdl = (flags & QVB8_FLAG_PDL) != 0;
+    for (int j0 = 0; j0 < njobs; j0 += MAX_JOBS) {
+        const int n = njobs - j0 < MAX_JOBS ? njobs - j0 : MAX_JOBS;
+        Plan pl;
+        if (n > 1 && group_fits(jobs + j0, n, M, pl)) {
+            static thread_local SmallMParams prm;
+            static thread_local EscPrepassParams esc;
+            prm.njobs = n;
+            esc.njobs = n;
+            esc.M = (int)M;
+            esc.tile_start[0] = 0;
+            int rot = 0;
+            for (int j = 0; j < n; ++j) {
+                const qvb8_job &jb = jobs[j0 + j];
+                fill_job(prm.jobs[j], jb.w, jb.plan, jb.X, jb.Y, jb.x_dtype, jb.x_mode, rot, jb.w->n_esc > 0 ? 1 : 0);
+                esc.jobs[j] = prm.jobs[j];
+                esc.tile_start[j + 1] = esc.tile_start[j] + (jb.w->n_esc > 0 ? prm.jobs[j].ntiles : 0);
+                rot = (rot + prm.jobs[j].ntiles % pl.ctas_x) % pl.ctas_x;
+            }
+            if (esc.tile_start[n] > 0) {                                // the escapes first: corrections into Y
+                const int64_t threads = (int64_t)esc.tile_start[n] * 16;
+                escape_prepass_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, st>>>(esc);
+                if (int rc = cuda_status("qvb8_small_m_group escape pre-pass")) return rc;
+            }
+            prm.ticket = nullptr;
+            prm.part = nullptr;
+            fill_launch(prm, pl, (int)M);
+            if (int rc = launch_nt(prm, pl, st, pdl)) return rc;
+        } else {
+            for (int j = 0; j < n; ++j) {
+                const qvb8_job &jb = jobs[j0 + j];
+                if (int rc = qvb8_small_m_ex(jb.w, jb.plan, jb.X, jb.x_dtype, jb.x_mode, M, jb.Y, scratch, scratch_bytes, flags, stream))
+                    return rc;
+            }
+        }
+    }
+    return QVB8_OK;
 }
 
 QV_API int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,

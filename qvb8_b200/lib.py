@@ -28,6 +28,7 @@ EXPORTS = (
     "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
     "qvb8_embed_rows", "qvb8_peer_bytes", "qvb8_peer_alloc", "qvb8_peer_open", "qvb8_peer_close", "qvb8_peer_allreduce",
     "qvb8_peer_allreduce_ex", "qvb8_peer_allreduce_local", "qvb8_device_status_reset", "qvb8r_embed_rows",
+    "qvb8_small_m_group_scratch_bytes", "qvb8_small_m_group",
 )
 
 
@@ -39,6 +40,12 @@ class PackStruct(ctypes.Structure):
         ("Q", ctypes.c_int64), ("P", ctypes.c_int64), ("esc_idx", ctypes.c_void_p), ("esc_vals", ctypes.c_void_p),
         ("n_esc", ctypes.c_int64),
     ]
+
+
+class JobStruct(ctypes.Structure):
+    """``struct qvb8_job`` of the header."""
+    _fields_ = [("w", ctypes.POINTER(PackStruct)), ("plan", ctypes.c_void_p), ("X", ctypes.c_void_p),
+                ("Y", ctypes.c_void_p), ("x_dtype", ctypes.c_int), ("x_mode", ctypes.c_int)]
 
 
 class ExpertStackStruct(ctypes.Structure):
@@ -92,6 +99,10 @@ def load() -> ctypes.CDLL:
             lib.qvb8_plan_build.argtypes = [pk, vp, i64, vp]
             lib.qvb8_small_m_ex.argtypes = [pk, vp, vp, ci, ci, i64, vp, vp, i64, ci, vp]
             lib.qvb8_small_m_set_tuning.argtypes = [ci, ci, ci, ci, ci]
+            jb = ctypes.POINTER(JobStruct)
+            lib.qvb8_small_m_group_scratch_bytes.argtypes = [jb, ci, i64]
+            lib.qvb8_small_m_group_scratch_bytes.restype = i64
+            lib.qvb8_small_m_group.argtypes = [jb, ci, i64, vp, i64, ci, vp]
             lib.qvb8_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
             lib.qvb8_debug_trace.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
             lib.qvb8_small_m_set_tuning.restype = None
@@ -290,6 +301,39 @@ def small_m(pack, keep, X: torch.Tensor, x_mode: int = 0, generic: bool = False,
                                      flags, stream_ptr(dev))
     check(rc, "qvb8_small_m")
     return Y
+
+
+class JobList:
+    """A list of independent products prepared once for :func:`small_m_group`: (pack struct, keepalive, plan, X, Y) per
+    job, all with the same row count M.  The ctypes array and everything it points at is kept alive here."""
+
+    def __init__(self, items, x_mode: int = 0):
+        if not items:
+            raise RuntimeError("qvb8_b200: an empty job list")
+        self.items = list(items)
+        self.M = int(self.items[0][3].shape[0])
+        self.device = self.items[0][1][0].device
+        self.array = (JobStruct * len(self.items))()
+        for k, (st, keep, plan, X, Y) in enumerate(self.items):
+            if X.dim() != 2 or X.shape != (self.M, st.P) or not X.is_contiguous() or X.device != self.device:
+                raise RuntimeError(f"qvb8_b200: job {k}: X must be a contiguous ({self.M}, {st.P}) tensor on the packs' device")
+            if Y.dtype != torch.float32 or Y.shape != (self.M, st.Q) or not Y.is_contiguous() or Y.device != self.device:
+                raise RuntimeError(f"qvb8_b200: job {k}: Y must be a contiguous fp32 ({self.M}, {st.Q}) tensor")
+            if plan is None:
+                raise RuntimeError(f"qvb8_b200: job {k} has no plan")
+            self.array[k] = JobStruct(ctypes.pointer(st), plan.data_ptr(), X.data_ptr(), Y.data_ptr(), dtype_code(X.dtype),
+                                      int(x_mode))
+        self.scratch_bytes = int(load().qvb8_small_m_group_scratch_bytes(self.array, len(self.items), self.M))
+
+
+def small_m_group(jobs: JobList, flags: int = 0) -> None:
+    """Runs the jobs of a :class:`JobList` (outputs land in the Y tensors it was built with) on the current stream."""
+    dev = jobs.device
+    sc = scratch_for(dev, jobs.scratch_bytes)
+    with torch.cuda.device(dev):
+        check(load().qvb8_small_m_group(jobs.array, len(jobs.items), jobs.M, sc.data_ptr() if sc is not None else None,
+                                        sc.numel() if sc is not None else 0, int(flags), stream_ptr(dev)),
+              "qvb8_small_m_group")
 
 
 def prefill(pack, keep, X: torch.Tensor, plan: torch.Tensor | None = None) -> torch.Tensor:

@@ -61,6 +61,10 @@ CONFIGS = {c.name: c for c in (DENSE_9B, DENSE_27B, DENSE_65B)}
 ROW_PARALLEL = ("o", "down")      # sharded by input columns when world > 1; the others by output rows
 
 
+def _lib_max_jobs() -> int:
+    return 32                     # jobs one launch of the streaming kernel takes (MAX_JOBS of the kernel source)
+
+
 class LinearStack:
     """Packs of `layers` decoder layers resident on one device + activation / output buffers + a captured graph.
 
@@ -150,6 +154,8 @@ class LinearStack:
         self.launches_per_step = sum(len(row) for row in self.launches)
         self.pdl = True
         self._host_in = self._host_out = None
+        self.group_layers = 0    # > 0: this many layers' projections behind one launch (set_grouping)
+        self._groups = None
 
     # ---- execution ------------------------------------------------------------------------------------
     def enable_collectives(self, peer: bool = True) -> None:
@@ -171,8 +177,33 @@ class LinearStack:
             import torch.distributed as dist
             dist.all_reduce(t)
 
+    def set_grouping(self, layers_per_launch: int) -> None:
+        """Run the projections of `layers_per_launch` consecutive layers as ONE launch each (``qvb8_small_m_group``):
+        inside a launch the weight stream never drains between projections.  The stack's projections read resident
+        activation buffers and write separate outputs, so they are independent jobs.  0 = one launch per projection.
+        Not combined with the multi-GPU exchange (the all-reduce follows single launches)."""
+        self.group_layers = int(layers_per_launch)
+        self._groups = None
+        self.graph = None
+        if self.group_layers > 0:
+            per = max(1, min(self.group_layers, _lib_max_jobs() // max(1, len(self.launches[0]))))
+            self._groups = []
+            for l0 in range(0, self.layers, per):
+                items = []
+                for li in range(l0, min(self.layers, l0 + per)):
+                    for j, (name, pk, st, keep, xname, _) in enumerate(self.launches[li]):
+                        items.append((st, keep, keep[-1], self.x[xname], self.y_launch[li][j]))
+                self._groups.append(_lib.JobList(items))
+            self.launches_per_step = len(self._groups)
+        else:
+            self.launches_per_step = sum(len(row) for row in self.launches)
+
     def run_eager(self) -> None:
         """One pass over every launch of every layer on the current stream."""
+        if self._groups is not None and not self.reduce:
+            for g in self._groups:
+                _lib.small_m_group(g, flags=_lib.FLAG_PDL if self.pdl else 0)
+            return
         for li, row in enumerate(self.launches):
             for j, (name, pk, st, keep, xname, _) in enumerate(row):
                 _lib.small_m(st, keep, self.x[xname], out=self.y_launch[li][j], plan=keep[-1],
@@ -181,10 +212,15 @@ class LinearStack:
                     self._allreduce(self.y_launch[li][j])
 
     def capture(self) -> None:
-        self.run_eager()                      # warm-up outside capture: shared-memory opt-in, scratch
-        torch.cuda.synchronize(self.device)
+        # warm-up (shared-memory opt-in, scratch) on the stream the capture will use: scratch buffers are kept per
+        # stream, so everything the captured calls need exists before the capture begins
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self.run_eager()
+        s.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+        with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
             self.run_eager()
         self.graph = g
 

@@ -330,7 +330,8 @@ def test_bf16_mode_keeps_the_range(cuda_lib, xdt):
     # the clamping mode on the same input saturates token 2 and differs there, as documented
     y0 = ext.mma_multi(X, *ext_args(pk), perm, tile_nb, False)
     assert rel_fro(y0.cpu().numpy()[2], want[2]) > 0.1
-    assert rel_fro(y0.cpu().numpy()[0], want[0]) < TIGHT
+    want0 = oracle.matmul_f32w(X.float().cpu().numpy()[:1], W, narrow_x=True)      # its own contract: fp16-narrowed activations
+    assert rel_fro(y0.cpu().numpy()[0], want0[0]) < TIGHT
 
 
 def test_config1_single_layer_against_the_oracle(cuda_lib):
@@ -345,3 +346,74 @@ def test_config1_single_layer_against_the_oracle(cuda_lib):
         y = ext.forward(X, *ext_args(pk))
         want = oracle.matmul_f32w(X.float().cpu().numpy(), W, narrow_x=True)
         assert rel_fro(y.cpu().numpy(), want) < TIGHT
+
+
+# ------------------------------------------------------------------------------------------------------------
+# several products behind one launch
+
+def _job_items(shapes, M, seed, x_dtype=torch.bfloat16, widths=None, esc=0.001):
+    from qvb8_b200 import lib
+    items, packs_ = [], []
+    for k, (Q, P) in enumerate(shapes):
+        pk = random_pack(Q, P, widths or (6, 7), seed=seed + k, esc_frac=esc, device=DEV)
+        st, keep = lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx, pk.esc_vals)
+        X = synth.synth_activation(M, P, seed=seed + 10 * k, device=DEV, dtype=x_dtype)
+        Y = torch.full((M, Q), float("nan"), device=DEV)
+        items.append((st, keep, lib.build_plan(st, keep), X, Y))
+        packs_.append(pk)
+    return items, packs_
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+@pytest.mark.parametrize("shapes", [
+    [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)],              # one 9B-class layer
+    [(256, 512), (48, 1024), (16, 128), (1024, 256), (300, 384), (7, 2048), (512, 512)],     # small and ragged
+    [(512, 1024)] * 33,                                                      # more jobs than one launch takes
+])
+def test_job_list_equals_separate_calls(cuda_lib, shapes, M):
+    from qvb8_b200 import lib
+    items, packs_ = _job_items(shapes, M, seed=100 * M)
+    jl = lib.JobList(items)
+    lib.small_m_group(jl)
+    torch.cuda.synchronize()
+    for (st, keep, plan, X, Y), pk in zip(items, packs_):
+        want = lib.small_m(st, keep, X, plan=plan)
+        # the same kernel on the same bytes; only the grouping of the fixed-order partial sums may differ (the list's
+        # CTAs are rotated from job to job, so a tile can be cut at other stage boundaries)
+        assert rel_fro(Y.cpu().numpy(), want.cpu().numpy()) < 1e-6
+    # and against the oracle for the first and the last job
+    for k in (0, len(items) - 1):
+        assert rel_fro(items[k][4].cpu().numpy(), _oracle_y(packs_[k], items[k][3])) < TIGHT
+    # a second run over the same list (barrier phases, exchange buffers start afresh) gives the same bits
+    first = [it[4].clone() for it in items]
+    lib.small_m_group(jl, flags=lib.FLAG_PDL)
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, it[4]) for a, it in zip(first, items))
+    assert lib.device_status(DEV) == 0
+
+
+def test_job_list_mixed_widths_and_range_mode(cuda_lib):
+    from qvb8_b200 import lib
+    shapes = [(320, 1024), (160, 512), (640, 1024), (96, 2048), (320, 1024)]
+    items, packs_ = _job_items(shapes, 9, seed=7, x_dtype=torch.float32, widths=(3, 4, 5, 6, 7, 8, 11), esc=0.003)
+    items[2][3].mul_(1.0e6)                                                # beyond fp16: needs the prescale of x_mode 1
+    jl = lib.JobList(items, x_mode=1)
+    lib.small_m_group(jl)
+    torch.cuda.synchronize()
+    for (st, keep, plan, X, Y), pk in zip(items, packs_):
+        assert rel_fro(Y.cpu().numpy(), lib.small_m(st, keep, X, x_mode=1, plan=plan).cpu().numpy()) < 1e-6
+        W = oracle.qvb8_dense(pack_np(pk))
+        assert rel_fro(Y.cpu().numpy(), oracle.matmul_f32w(X.cpu().numpy(), W, narrow_x=False)) < 1e-3
+    assert lib.device_status(DEV) == 0
+
+
+def test_job_list_that_does_not_fit_runs_job_by_job(cuda_lib):
+    """16 tokens x 12288 columns of activations do not fit shared memory next to the rings: the call falls back to one
+    launch per job (with scratch for the split-K ones) and gives the same results"""
+    from qvb8_b200 import lib
+    items, packs_ = _job_items([(512, 12288), (1024, 4096)], 16, seed=3)
+    jl = lib.JobList(items)
+    lib.small_m_group(jl)
+    torch.cuda.synchronize()
+    for (st, keep, plan, X, Y), pk in zip(items, packs_):
+        assert torch.equal(Y, lib.small_m(st, keep, X, plan=plan))
