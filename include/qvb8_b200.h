@@ -118,8 +118,9 @@ int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, int x_d
  * activations do not fit shared memory next to the rings (large M x P), or whose packs the streaming kernel cannot
  * take, run job by job exactly as qvb8_small_m_ex would; only those need scratch
  * (qvb8_small_m_group_scratch_bytes, zero-filled once); so do lists with x_mode 1 on bf16 / fp32 activations.  Results
- * are deterministic (every sum has a fixed order) and agree with separate calls to rounding: the CTAs' shares are
- * rotated from job to job, so a tile's fixed-order partial sums may be grouped differently. */
+ * are deterministic (every sum has a fixed order) and agree with separate calls to rounding: a list is one stream of
+ * tiles cut into equal per-CTA ranges, so a tile's fixed-order partial sums may be grouped differently, and the escape
+ * corrections of a list are summed by a small pre-pass kernel and the products added to them. */
 typedef struct qvb8_job {
     const qvb8_pack *w;
     const void *plan;       /* qvb8_plan_build of w */

@@ -60,7 +60,7 @@ constexpr int MAX_CPS = 16;               // most chunks per stage (a stage hold
 constexpr int PRODUCER_WARP = NW;         // issues the bulk copies
 constexpr int FINISHER_WARP = NW + 1;     // escape corrections, cross-warp sums, scaling, output
 constexpr int PIPE_THREADS = (NW + 2) * 32;  // threads of one pipe
-constexpr int MAX_STAGES = 4;
+constexpr int MAX_STAGES = 6;
 constexpr int MAX_PIPES = 4;               // pipes per CTA at most
 #ifndef QVB8_PIPES_NT1
 #define QVB8_PIPES_NT1 4
@@ -643,8 +643,7 @@ struct JobDesc {
     int Q, P;
     int nc_total;              // P / 128
     int x_dtype, x_mode;
-    int rot;                   // rotation of the CTA numbering for this job: over a list of jobs every CTA gets its
-                               // fair share of the tiles that do not divide evenly
+    int unit0;                 // list launches: (tile, stage) units of the jobs before this one
     int prepass;               // 1: an escape pre-pass has put the job's corrections into Y; the product is added to them
 };
 static_assert(sizeof(JobDesc) == 88, "job record layout (host and device agree)");
@@ -659,6 +658,7 @@ struct SmallMParams {
     int M, MP;                 // MP: token slots per column group in shared memory (>= M)
     int S;                     // K-ranges (= gridDim.y); 1 when the launch has several jobs
     int nc_per;                // chunks per K-range (the last range may be shorter)
+    int units_total;           // list launches: (tile, stage) units of all jobs
     int xs_halves;             // capacity of the staged activations in halves per layout
     int raw_bytes;             // capacity of the raw-activation buffer (0 for a one-job launch)
     int nstg;                  // slots of each pipe's copy ring
@@ -799,9 +799,18 @@ __device__ __forceinline__ JobGeom job_geom(const SmallMParams &p, const JobDesc
     g.kc0 = split * p.nc_per;
     g.NC = p.njobs > 1 ? jd.nc_total : min(p.nc_per, jd.nc_total - g.kc0);
     g.NSK = (g.NC + p.cps - 1) / p.cps;
-    int c = (int)blockIdx.x + jd.rot;
-    if (c >= (int)gridDim.x) c -= (int)gridDim.x;
-    cta_tiles(jd.ntiles, gridDim.x, c, g.ct0, g.ct1);
+    if (p.njobs > 1) {
+        // A list is ONE stream of (tile, stage) units, job after job, cut into equal contiguous ranges, one per CTA
+        // (snapped to whole tiles: a tile goes to the CTA that holds its first unit).  A CTA therefore meets only the
+        // one or two jobs its range touches, stages activations that often, and all CTAs finish together.
+        const int64_t lo = (int64_t)blockIdx.x * p.units_total / gridDim.x - jd.unit0;
+        const int64_t hi = (int64_t)(blockIdx.x + 1) * p.units_total / gridDim.x - jd.unit0;
+        const int64_t t0 = lo <= 0 ? 0 : (lo + g.NSK - 1) / g.NSK, t1 = hi <= 0 ? 0 : (hi + g.NSK - 1) / g.NSK;
+        g.ct0 = (int)(t0 < jd.ntiles ? t0 : jd.ntiles);
+        g.ct1 = (int)(t1 < jd.ntiles ? t1 : jd.ntiles);
+    } else {
+        cta_tiles(jd.ntiles, gridDim.x, blockIdx.x, g.ct0, g.ct1);
+    }
     g.uc0 = g.ct0 * g.NSK;
     g.uc1 = g.ct1 * g.NSK;
     g.Lp = max(1, (g.uc1 - g.uc0 + NPIPE - 1) / NPIPE);
@@ -950,6 +959,20 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     __syncthreads();
     pdl_launch_dependents();                                            // what follows in the stream may start its own prologue
     if (tracer) trace(p.debug, 1);
+    // the jobs this CTA's range touches: jfirst .. jfirst + jcount - 1 (a list's ranges are contiguous); every warp walks
+    // the same sequence, and counts its barrier phases by the position k in it
+    int jfirst = 0, jcount = njobs;
+    if (njobs > 1) {
+        int jlast = -1;
+        jfirst = njobs;
+        for (int j = 0; j < njobs; ++j) {
+            const JobGeom gj = job_geom<NPIPE>(p, jobs[j], split, 0);
+            if (gj.ct1 > gj.ct0) { if (j < jfirst) jfirst = j; jlast = j; }
+        }
+        jcount = jlast >= jfirst ? jlast - jfirst + 1 : 0;
+        if (jcount == 0) jfirst = 0;
+    }
+    const int jend = jfirst + jcount;
     RingPos rp;
     rp.full = smem_u32(&pc_.full[0]); rp.empty = smem_u32(&pc_.empty[0]); rp.data = smem_u32(pbase);
     rp.slot = 0; rp.phase = 0;
@@ -963,12 +986,13 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         int nb = 0, cnt = 0, esc0 = 0, nesc = 0;
         uint32_t b16 = 0;
         // cursor over (job, visit) pairs that exist
-        int cj = 0, ci = -1;
-        JobGeom cg = job_geom<NPIPE>(p, jobs[0], split, pipe);
+        int cj = jfirst, ci = -1;
+        JobGeom cg = job_geom<NPIPE>(p, jobs[jfirst], split, pipe);
+        if (jcount == 0) cg.run.nv = 0;
         auto advance = [&](int &j, int &i, JobGeom &g) {                // -> false when the list is exhausted
             ++i;
             while (i >= g.run.nv) {
-                if (++j >= njobs) return false;
+                if (++j >= jend) return false;
                 g = job_geom<NPIPE>(p, jobs[j], split, pipe);
                 i = 0;
             }
@@ -1052,7 +1076,8 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         int vis = 0;                                                    // visits handled so far (all jobs)
         int own_uses[MAX_PIPES - 1] = {0, 0, 0};                        // completions waited for on this pipe's xch_full[j]
         int give_uses[MAX_PIPES - 1] = {0, 0, 0};                       // parts handed to owner pipe op (index op)
-        for (int job = 0; job < njobs; ++job) {
+        for (int kj = 0; kj < jcount; ++kj) {
+            const int job = jfirst + kj;
             const JobDesc &jd = jobs[job];
             const JobGeom gm = job_geom<NPIPE>(p, jd, split, pipe);
             const Run &run = gm.run;
@@ -1063,10 +1088,10 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             const bool prescaled = njobs == 1 && jd.x_mode == 1 && jd.x_dtype != QVB8_F16;
             // the job's activations are staged and every consumer warp has left its partial sums of them: this lane
             // keeps the sums of the tokens it writes (8n + 2t + k), added up in warp order (same bits every run)
-            if (alive) alive = mbar_wait(smem_u32(&ctl.x_ready), par(job), abort_flag, 5);
+            if (alive) alive = mbar_wait(smem_u32(&ctl.x_ready), par(kj), abort_flag, 5);
             float sumx_nt[NT][2];
             {
-                const float *ps = psum + (job & 1) * CWARPS * M;
+                const float *ps = psum + (kj & 1) * CWARPS * M;
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -1309,13 +1334,14 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         bool alive = true;
         int vis = 0;                                                    // visits walked so far (all jobs)
         const int cwarp = pipe * NW + warp;                             // index among the CTA's consumer warps
-        for (int job = 0; job < njobs && alive; ++job) {
+        for (int kj = 0; kj < jcount && alive; ++kj) {
+            const int job = jfirst + kj;
             const JobDesc &jd = jobs[job];
             const JobGeom gm = job_geom<NPIPE>(p, jd, split, pipe);
             const Run &run = gm.run;
             const int kc0 = gm.kc0, NC = gm.NC;
-            float *psum_w = psum + ((job & 1) * CWARPS + cwarp) * M;
-            if (job == 0) {
+            float *psum_w = psum + ((kj & 1) * CWARPS + cwarp) * M;
+            if (kj == 0) {
                 // ---- activations of the first job's K-range as fp16 in fragment order (after the previous kernel in the
                 // stream): all consumer warps of the CTA share the work, every one of them reads all of it afterwards
                 pdl_wait();
@@ -1352,27 +1378,27 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 // is starved by warps that stream.
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl.job_done));
-                alive = mbar_wait(smem_u32(&ctl.job_done), par(job - 1), abort_flag, 10);
-                if (alive) alive = mbar_wait(smem_u32(&ctl.raw_full), par(job - 1), abort_flag, 11);
+                alive = mbar_wait(smem_u32(&ctl.job_done), par(kj - 1), abort_flag, 10);
+                if (alive) alive = mbar_wait(smem_u32(&ctl.raw_full), par(kj - 1), abort_flag, 11);
                 // the finishing warps have reached the previous job: they wait on the same once-per-job barriers by
                 // parity, so no barrier may complete twice while one of them still waits for the first completion
-                if (alive) alive = mbar_wait(smem_u32(&ctl.fin_started), par(job - 1), abort_flag, 12);
+                if (alive) alive = mbar_wait(smem_u32(&ctl.fin_started), par(kj - 1), abort_flag, 12);
                 if (!alive) break;
                 stage_slice<DUAL, false>(raw, jd.x_dtype, jd.P, 0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
                                          [](int) { return 1.f; }, psum_w);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl.x_ready));
-            alive = mbar_wait(smem_u32(&ctl.x_ready), par(job), abort_flag, 5);
+            alive = mbar_wait(smem_u32(&ctl.x_ready), par(kj), abort_flag, 5);
             if (!alive) break;
             // the raw activations of the NEXT job: one bulk copy into the buffer this job's conversion has just released
-            if (job + 1 < njobs && cwarp == 0 && lane == 0) {
+            if (kj + 1 < jcount && cwarp == 0 && lane == 0) {
                 const JobDesc &nd = jobs[job + 1];
                 const uint32_t bytes = (uint32_t)((int64_t)M * nd.P * (nd.x_dtype == QVB8_F32 ? 4 : 2));
                 mbar_expect_tx(smem_u32(&ctl.raw_full), bytes);
                 bulk_g2s(smem_u32(raw), nd.X, bytes, smem_u32(&ctl.raw_full));
             }
-            if (tracer && warp == 0) { if (job == 0) trace(p.debug, 5); if (job < 4) trace(p.debug, 16 + 4 * job); }
+            if (tracer && warp == 0) { if (kj == 0) trace(p.debug, 5); if (kj < 4) trace(p.debug, 16 + 4 * kj); }
             const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
             const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
             const __half *xsa = xs_a;
@@ -1455,7 +1481,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(red_full);
             }
-            if (tracer && warp == 0 && job < 4) trace(p.debug, 17 + 4 * job);
+            if (tracer && warp == 0 && kj < 4) trace(p.debug, 17 + 4 * kj);
         }
         if (tracer && warp == 0) trace(p.debug, 8);
     }
@@ -1617,7 +1643,7 @@ static bool make_group_plan(int64_t M, const int64_t *Ps, const int *esizes, int
     for (int j = 0; j < njobs; ++j) {
         if (Ps[j] > pmax) pmax = Ps[j];
         if (Ps[j] < pmin) pmin = Ps[j];
-        if (j >= 1 && M * Ps[j] * esizes[j] > raw) raw = M * Ps[j] * esizes[j];
+        if (M * Ps[j] * esizes[j] > raw) raw = M * Ps[j] * esizes[j];
     }
     raw = (raw + 127) / 128 * 128;
     const int64_t cta_bytes = MAX_DYN_SMEM - 256;
@@ -1787,7 +1813,7 @@ QV_API int qvb8_plan_build(const qvb8_pack *w, void *plan, int64_t plan_bytes, v
 }
 
 namespace qv {
-static void fill_job(JobDesc &jd, const qvb8_pack *w, const void *plan, const void *X, float *Y, int x_dtype, int x_mode, int rot,
+static void fill_job(JobDesc &jd, const qvb8_pack *w, const void *plan, const void *X, float *Y, int x_dtype, int x_mode, int unit0,
                      int prepass = 0) {
     const PlanLayout L = plan_layout(w->Q, w->n_esc);
     const uint8_t *base = reinterpret_cast<const uint8_t *>(plan);
@@ -1798,7 +1824,7 @@ static void fill_job(JobDesc &jd, const qvb8_pack *w, const void *plan, const vo
     jd.esc_ent = w->n_esc > 0 ? reinterpret_cast<const EscEntry *>(base + L.esc_ent) : nullptr;
     jd.X = X; jd.Y = Y;
     jd.Q = (int)w->Q; jd.P = (int)w->P; jd.nc_total = (int)(w->P / KC);
-    jd.x_dtype = x_dtype; jd.x_mode = x_mode; jd.rot = rot; jd.prepass = prepass;
+    jd.x_dtype = x_dtype; jd.x_mode = x_mode; jd.unit0 = unit0; jd.prepass = prepass;
 }
 static void fill_launch(SmallMParams &prm, const Plan &pl, int M) {
     prm.M = M; prm.MP = pl.MP; prm.S = pl.S; prm.nc_per = pl.nc_per; prm.nstg = pl.nstg; prm.debug = g_debug;
@@ -1954,15 +1980,17 @@ QV_API int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *
             esc.njobs = n;
             esc.M = (int)M;
             esc.tile_start[0] = 0;
-            int rot = 0;
+            int64_t units = 0;
             for (int j = 0; j < n; ++j) {
                 const qvb8_job &jb = jobs[j0 + j];
-                fill_job(prm.jobs[j], jb.w, jb.plan, jb.X, jb.Y, jb.x_dtype, jb.x_mode, rot, jb.w->n_esc > 0 ? 1 : 0);
+                fill_job(prm.jobs[j], jb.w, jb.plan, jb.X, jb.Y, jb.x_dtype, jb.x_mode, (int)units, jb.w->n_esc > 0 ? 1 : 0);
                 esc.jobs[j] = prm.jobs[j];
                 esc.tile_start[j + 1] = esc.tile_start[j] + (jb.w->n_esc > 0 ? prm.jobs[j].ntiles : 0);
-                rot = (rot + prm.jobs[j].ntiles % pl.ctas_x) % pl.ctas_x;
+                units += (int64_t)prm.jobs[j].ntiles * ((prm.jobs[j].nc_total + pl.cps - 1) / pl.cps);
             }
-            if (esc.tile_start[n] > 0) {                                // the escapes first: corrections into Y
+            if (units > 0x7fffffff) return fail(QVB8_ERR_ARG, "qvb8_small_m_group: the list is too long for one launch");
+            prm.units_total = (int)units;
+            if (esc.tile_start[n] > 0 && !(g_debug & 32)) {            // the escapes first: corrections into Y (debug bit 5: skipped)
                 const int64_t threads = (int64_t)esc.tile_start[n] * 16;
                 escape_prepass_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, st>>>(esc);
                 if (int rc = cuda_status("qvb8_small_m_group escape pre-pass")) return rc;

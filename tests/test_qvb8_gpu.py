@@ -378,9 +378,9 @@ def test_job_list_equals_separate_calls(cuda_lib, shapes, M):
     torch.cuda.synchronize()
     for (st, keep, plan, X, Y), pk in zip(items, packs_):
         want = lib.small_m(st, keep, X, plan=plan)
-        # the same kernel on the same bytes; only the grouping of the fixed-order partial sums may differ (the list's
-        # CTAs are rotated from job to job, so a tile can be cut at other stage boundaries)
-        assert rel_fro(Y.cpu().numpy(), want.cpu().numpy()) < 1e-6
+        # the same kernel on the same bytes; only the grouping of the fixed-order fp32 partial sums differs (a list cuts
+        # its stream of tiles into per-CTA ranges of its own, and adds the escape corrections in a pre-pass)
+        assert rel_fro(Y.cpu().numpy(), want.cpu().numpy()) < 1e-5
     # and against the oracle for the first and the last job
     for k in (0, len(items) - 1):
         assert rel_fro(items[k][4].cpu().numpy(), _oracle_y(packs_[k], items[k][3])) < TIGHT
@@ -401,7 +401,7 @@ def test_job_list_mixed_widths_and_range_mode(cuda_lib):
     lib.small_m_group(jl)
     torch.cuda.synchronize()
     for (st, keep, plan, X, Y), pk in zip(items, packs_):
-        assert rel_fro(Y.cpu().numpy(), lib.small_m(st, keep, X, x_mode=1, plan=plan).cpu().numpy()) < 1e-6
+        assert rel_fro(Y.cpu().numpy(), lib.small_m(st, keep, X, x_mode=1, plan=plan).cpu().numpy()) < 1e-5
         W = oracle.qvb8_dense(pack_np(pk))
         assert rel_fro(Y.cpu().numpy(), oracle.matmul_f32w(X.cpu().numpy(), W, narrow_x=False)) < 1e-3
     assert lib.device_status(DEV) == 0
