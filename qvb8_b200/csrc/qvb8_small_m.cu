@@ -119,7 +119,6 @@ struct Control {
     alignas(8) uint64_t amax_ready;       // x_mode 1: every consumer warp has folded its share into amax
     alignas(8) uint64_t x_ready;          // once per job: every consumer warp has staged its slice of the activations
     alignas(8) uint64_t job_done;         // once per job boundary: every consumer warp has left the job before
-    alignas(8) uint64_t raw_full;         // once per later job: its raw activations have landed
     alignas(8) uint64_t fin_started;      // once per job: every finishing warp has reached the job and taken its activation sums
     alignas(8) uint64_t xch_full[XCH_SLOTS];   // [owner pipe][contributor]: a contributed part of a shared tile is in place
     alignas(8) uint64_t xch_empty[XCH_SLOTS];  // ... and the owner has taken it
@@ -660,7 +659,6 @@ struct SmallMParams {
     int nc_per;                // chunks per K-range (the last range may be shorter)
     int units_total;           // list launches: (tile, stage) units of all jobs
     int xs_halves;             // capacity of the staged activations in halves per layout
-    int raw_bytes;             // capacity of the raw-activation buffer (0 for a one-job launch)
     int nstg;                  // slots of each pipe's copy ring
     int cps;                   // chunks per stage (a multiple of NW)
     int rs[6];                 // bytes between rows of a stage, by width 3..8
@@ -875,8 +873,9 @@ __device__ __forceinline__ uint32_t par(int n) { return (uint32_t)(n & 1); }
 // the next kernel's CTA to sit beside it and run its prologue early (a tuning switch, see make_plan).
 //
 // A launch runs a LIST of jobs (products) back to back inside the CTAs: the copy rings, barriers and warp roles
-// persist from one job to the next, so the stream of weight bytes never drains between jobs; the raw activations of job
-// j + 1 arrive by one bulk copy while job j streams and are converted by all consumer warps at the job boundary.  The jobs must not depend
+// persist from one job to the next, so the stream of weight bytes never drains between jobs.  A list is cut into one
+// contiguous range of tiles per CTA, so a CTA crosses a job boundary once or twice per launch; there all its consumer
+// warps meet and stage the next job's activations.  The jobs must not depend
 // on one another's outputs.  A launch with one job is the plain product.
 template <int NT, bool DUAL, int NPIPE>
 __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const __grid_constant__ SmallMParams p) {
@@ -893,7 +892,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     const int nstg = p.nstg;
     const int njobs = p.njobs;
     // dynamic shared memory:
-    //   [job table] [activations: layout A, layout B] [raw activations of the next job] [16 zero bytes, padded to 128]
+    //   [job table] [activations: layout A, layout B] [16 zero bytes, padded to 128]
     //   [activation sums by consumer warp, two sets] [exchange buffers of tiles shared by pipes]
     //   per pipe: [ring: nstg stages of 16 rows] [side ring: NSIDE x (descriptor + escapes)] [two hand-over buffers]
     //             [escape corrections]
@@ -901,8 +900,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     const size_t jobs_bytes = (size_t)((njobs * (int)sizeof(JobDesc) + 127) / 128 * 128);
     __half *xs_a = reinterpret_cast<__half *>(smem + jobs_bytes);
     __half *xs_b = DUAL ? xs_a + p.xs_halves : xs_a;
-    uint8_t *raw = reinterpret_cast<uint8_t *>(xs_a + (DUAL ? 2 : 1) * p.xs_halves);   // p.raw_bytes (a multiple of 128)
-    uint32_t *zero16 = reinterpret_cast<uint32_t *>(raw + p.raw_bytes);
+    uint32_t *zero16 = reinterpret_cast<uint32_t *>(xs_a + (DUAL ? 2 : 1) * p.xs_halves);
     float *psum = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(zero16) + 128);   // [2][CWARPS][M]
     const size_t psum_bytes = (size_t)((2 * CWARPS * M * 4 + 127) / 128 * 128);
     const int xch_floats = 16 * M;                                     // one tile's results
@@ -922,6 +920,42 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     const bool tracer = (p.debug & 2) && pipe == 0;
 
     if (tracer) trace(p.debug, 0);
+    // the jobs this CTA's range touches: jfirst .. jend - 1 (a list's ranges are contiguous); every warp walks the same
+    // sequence and counts its barrier phases by the position in it.  Read from the launch parameters: the shared-memory
+    // copy of the job table is not there yet, and the producer wants its first descriptor on the way before anything else.
+    int jfirst = 0, jcount = njobs;
+    if (njobs > 1) {
+        const int64_t lo = (int64_t)blockIdx.x * p.units_total / gridDim.x, hi = (int64_t)(blockIdx.x + 1) * p.units_total / gridDim.x;
+        int j = 0;
+        for (int q = 1; q < njobs; ++q)
+            if (p.jobs[q].unit0 <= lo) j = q;                          // the job that holds the range's first unit
+        int jlast = -1;
+        jfirst = njobs;
+        for (; j < njobs && p.jobs[j].unit0 < hi; ++j) {
+            const JobGeom gj = job_geom<NPIPE>(p, p.jobs[j], split, 0);
+            if (gj.ct1 > gj.ct0) { if (j < jfirst) jfirst = j; jlast = j; }
+        }
+        jcount = jlast >= jfirst ? jlast - jfirst + 1 : 0;
+        if (jcount == 0) jfirst = 0;
+    }
+    const int jend = jfirst + jcount;
+    // the producer's first descriptor fields are on their way from memory while the barriers are set up
+    int pf_nb = 0, pf_cnt = 0, pf_esc0 = 0, pf_nesc = 0, pf_j = -1, pf_i = 0;
+    uint32_t pf_b16 = 0;
+    if (warp == PRODUCER_WARP) {
+        for (int j = jfirst; j < jend && pf_j < 0; ++j) {
+            const JobGeom gj = job_geom<NPIPE>(p, p.jobs[j], split, pipe);
+            if (gj.run.nv > 0) {
+                const TileDesc *d = p.jobs[j].tiles + run_visit(gj.run, 0).tile;
+                pf_nb = __ldg(&d->nb);
+                pf_cnt = __ldg(&d->cnt);
+                pf_esc0 = __ldg(&d->esc0);
+                pf_nesc = __ldg(&d->nesc);
+                pf_b16 = lane < 16 ? __ldg(&d->b16[lane]) : 0u;
+                pf_j = j;
+            }
+        }
+    }
     // the job table: from the launch parameters into shared memory, where every warp reads it at each job boundary
     {
         const uint32_t *src = reinterpret_cast<const uint32_t *>(p.jobs);
@@ -947,7 +981,6 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             mbar_init(smem_u32(&ctl.amax_ready), CWARPS);
             mbar_init(smem_u32(&ctl.x_ready), CWARPS);
             mbar_init(smem_u32(&ctl.job_done), CWARPS);
-            mbar_init(smem_u32(&ctl.raw_full), 1);
             mbar_init(smem_u32(&ctl.fin_started), NPIPE);
             ctl.abort = 0;
         }
@@ -959,20 +992,6 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     __syncthreads();
     pdl_launch_dependents();                                            // what follows in the stream may start its own prologue
     if (tracer) trace(p.debug, 1);
-    // the jobs this CTA's range touches: jfirst .. jfirst + jcount - 1 (a list's ranges are contiguous); every warp walks
-    // the same sequence, and counts its barrier phases by the position k in it
-    int jfirst = 0, jcount = njobs;
-    if (njobs > 1) {
-        int jlast = -1;
-        jfirst = njobs;
-        for (int j = 0; j < njobs; ++j) {
-            const JobGeom gj = job_geom<NPIPE>(p, jobs[j], split, 0);
-            if (gj.ct1 > gj.ct0) { if (j < jfirst) jfirst = j; jlast = j; }
-        }
-        jcount = jlast >= jfirst ? jlast - jfirst + 1 : 0;
-        if (jcount == 0) jfirst = 0;
-    }
-    const int jend = jfirst + jcount;
     RingPos rp;
     rp.full = smem_u32(&pc_.full[0]); rp.empty = smem_u32(&pc_.empty[0]); rp.data = smem_u32(pbase);
     rp.slot = 0; rp.phase = 0;
@@ -1007,7 +1026,10 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             b16 = lane < 16 ? __ldg(&d->b16[lane]) : 0u;
         };
         bool have = advance(cj, ci, cg);
-        if (have) fetch(cj, ci, cg);
+        if (have) {
+            if (cj == pf_j && ci == pf_i) { nb = pf_nb; cnt = pf_cnt; esc0 = pf_esc0; nesc = pf_nesc; b16 = pf_b16; }
+            else fetch(cj, ci, cg);
+        }
         if (tracer) trace(p.debug, 2);
         const bool nocopy = (p.debug & 4) != 0;
         const uint64_t stream_policy = l2_evict_first_policy();
@@ -1045,7 +1067,10 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 if (!mbar_wait(rp.empty, rp.phase ^ 1u, abort_flag, 1, 100)) { alive = false; break; }
                 if (lane == 0) mbar_expect_tx(rp.full, bytes_row * (uint32_t)ccnt);
                 __syncwarp();
-                if (bytes_row && lane < ccnt) bulk_g2s_stream(rp.data + dst_row, src, bytes_row, rp.full, stream_policy);
+                if (bytes_row && lane < ccnt) {
+                    if (p.debug & 16) bulk_g2s(rp.data + dst_row, src, bytes_row, rp.full);
+                    else bulk_g2s_stream(rp.data + dst_row, src, bytes_row, rp.full, stream_policy);
+                }
                 src += step;
                 if (tracer && vis == 0 && s == v.sb) trace(p.debug, 3);
                 ring_advance(rp, (uint32_t)p.slot_bytes, nstg);
@@ -1372,32 +1397,23 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 stage_slice<DUAL, true>(jd.X, jd.x_dtype, jd.P, kc0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
                                         [&](int m) { return prescale ? pow2f(-prescale_exp(amax[m])) : 1.f; }, psum_w);
             } else {
-                // ---- a later job: its raw activations arrived by a bulk copy while the job before it streamed.  Every
-                // consumer warp of the CTA meets here: all have left the previous job (the staged activations may be
-                // replaced), then each converts its slice.  With all of them in this rarely executed code at once none
-                // is starved by warps that stream.
+                // ---- a later job of this CTA's range (a list's CTA meets one or two jobs per launch, so this is rare):
+                // every consumer warp of the CTA meets here -- all have left the previous job, the staged activations
+                // may be replaced -- and stages its slice from global memory.
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl.job_done));
                 alive = mbar_wait(smem_u32(&ctl.job_done), par(kj - 1), abort_flag, 10);
-                if (alive) alive = mbar_wait(smem_u32(&ctl.raw_full), par(kj - 1), abort_flag, 11);
                 // the finishing warps have reached the previous job: they wait on the same once-per-job barriers by
                 // parity, so no barrier may complete twice while one of them still waits for the first completion
                 if (alive) alive = mbar_wait(smem_u32(&ctl.fin_started), par(kj - 1), abort_flag, 12);
                 if (!alive) break;
-                stage_slice<DUAL, false>(raw, jd.x_dtype, jd.P, 0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
-                                         [](int) { return 1.f; }, psum_w);
+                stage_slice<DUAL, true>(jd.X, jd.x_dtype, jd.P, 0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
+                                        [](int) { return 1.f; }, psum_w);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl.x_ready));
             alive = mbar_wait(smem_u32(&ctl.x_ready), par(kj), abort_flag, 5);
             if (!alive) break;
-            // the raw activations of the NEXT job: one bulk copy into the buffer this job's conversion has just released
-            if (kj + 1 < jcount && cwarp == 0 && lane == 0) {
-                const JobDesc &nd = jobs[job + 1];
-                const uint32_t bytes = (uint32_t)((int64_t)M * nd.P * (nd.x_dtype == QVB8_F32 ? 4 : 2));
-                mbar_expect_tx(smem_u32(&ctl.raw_full), bytes);
-                bulk_g2s(smem_u32(raw), nd.X, bytes, smem_u32(&ctl.raw_full));
-            }
             if (tracer && warp == 0) { if (kj == 0) trace(p.debug, 5); if (kj < 4) trace(p.debug, 16 + 4 * kj); }
             const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
             const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
@@ -1522,7 +1538,6 @@ struct Plan {
     int ctas_x, S, nc_per, nc_total, MP, NT, nstg, cps, part_slots, npipe;
     int rs[6], slot_bytes;
     int xs_halves;             // capacity of the staged activations (halves per layout)
-    int raw_bytes;             // raw-activation buffer of a list launch
     int esc_cap;               // escape entries per side slot
     bool dual;
     size_t smem_bytes;
@@ -1621,7 +1636,6 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P, int max_width = 8) {
     pl.nstg = nstg;
     pl.smem_bytes = (size_t)(xs_bytes + shared_fixed + npipe * (pipe_fixed + (int64_t)nstg * pl.slot_bytes));
     pl.xs_halves = pl.nc_per * 16 * pl.MP * 8;
-    pl.raw_bytes = 0;
     pl.part_slots = pl.S > 1 ? pl.S : 0;                                // partial results only between K-ranges
     pl.part_bytes = ((int64_t)pl.part_slots * M * Q * 4 + 255) / 256 * 256;
     pl.ticket_bytes = pl.S > 1 ? TICKET_BYTES : 0;
@@ -1629,9 +1643,9 @@ static Plan make_plan(int64_t M, int64_t Q, int64_t P, int max_width = 8) {
 }
 
 // Plan of a launch that runs a list of jobs (P and activation element size of every job given): K is never split; one
-// buffer holds the staged activations of the current job, a second one the raw activations of the next; what is left
-// goes to the copy rings.  Returns false when the list does not fit (activations too large for shared memory next to
+// buffer holds the staged activations of the job a CTA is in; what is left goes to the copy rings.  Returns false when the list does not fit (activations too large for shared memory next to
 // two-stage rings).
+constexpr int MIN_RING_CHUNKS = 12;
 static bool make_group_plan(int64_t M, const int64_t *Ps, const int *esizes, int njobs, Plan &pl) {
     pl = Plan{};
     pl.NT = (int)((M + 7) / 8);
@@ -1639,19 +1653,18 @@ static bool make_group_plan(int64_t M, const int64_t *Ps, const int *esizes, int
     const int npipe = pipes_for(pl.NT);
     pl.npipe = npipe;
     pl.dual = false;
-    int64_t pmax = 0, pmin = Ps[0], raw = 0;
+    int64_t pmax = 0, pmin = Ps[0];
     for (int j = 0; j < njobs; ++j) {
         if (Ps[j] > pmax) pmax = Ps[j];
         if (Ps[j] < pmin) pmin = Ps[j];
-        if (M * Ps[j] * esizes[j] > raw) raw = M * Ps[j] * esizes[j];
     }
-    raw = (raw + 127) / 128 * 128;
+    (void)esizes;
     const int64_t cta_bytes = MAX_DYN_SMEM - 256;
     const int64_t jobs_bytes = ((int64_t)njobs * (int64_t)sizeof(JobDesc) + 127) / 128 * 128;
     pl.esc_cap = ESC_CAP_MIN;                                           // (a list's escapes are applied by the pre-pass)
     const int64_t pipe_fixed = (int64_t)NSIDE * side_slot_bytes(pl.esc_cap) + (int64_t)2 * NW * 4 * pl.NT * 32 * 4 + corr_bytes(M, pl.esc_cap);
     const int64_t shared_fixed = jobs_bytes + 128 + psum_bytes_for(npipe, M) + ((XCH_SLOTS + npipe) * 16 * M * 4 + 127) / 128 * 128;
-    const int64_t xs_bytes = pmax * pl.MP * 2 + raw;
+    const int64_t xs_bytes = pmax * pl.MP * 2;
     int cps = g_force_cps ? g_force_cps : (pmin / KC >= 16 ? 8 : 4);
     cps = cps / NW * NW;
     if (cps < NW) cps = NW;
@@ -1666,9 +1679,11 @@ static bool make_group_plan(int64_t M, const int64_t *Ps, const int *esizes, int
         }
         const int64_t room = (cta_bytes - shared_fixed - xs_bytes) / npipe - pipe_fixed;
         nstg = room > 0 ? (int)(room / pl.slot_bytes) : 0;
-        if (nstg >= 2 || cps <= NW) break;
+        // a ring must hold about two long stages' worth of bytes, or the stream stalls at every hiccup of its consumers
+        // (measured: with less, a list is slower than the same jobs launched one by one)
+        if (nstg * cps >= MIN_RING_CHUNKS || cps <= NW) break;
     }
-    if (nstg < 2) return false;
+    if (nstg * cps < MIN_RING_CHUNKS) return false;
     if (g_force_nstg && g_force_nstg < nstg) nstg = g_force_nstg;
     if (nstg > MAX_STAGES) nstg = MAX_STAGES;
     pl.nstg = nstg;
@@ -1676,7 +1691,6 @@ static bool make_group_plan(int64_t M, const int64_t *Ps, const int *esizes, int
     pl.nc_per = (int)(pmax / KC);
     pl.nc_total = pl.nc_per;
     pl.xs_halves = (int)(pmax / KC) * 16 * pl.MP * 8;
-    pl.raw_bytes = (int)raw;
     int64_t ctas = (int64_t)device_sms() * (g_fill_pct ? g_fill_pct : 100) / 100;
     pl.ctas_x = (int)(ctas < 1 ? 1 : ctas);
     pl.smem_bytes = (size_t)(xs_bytes + shared_fixed + npipe * (pipe_fixed + (int64_t)nstg * pl.slot_bytes));
@@ -1829,7 +1843,7 @@ static void fill_job(JobDesc &jd, const qvb8_pack *w, const void *plan, const vo
 static void fill_launch(SmallMParams &prm, const Plan &pl, int M) {
     prm.M = M; prm.MP = pl.MP; prm.S = pl.S; prm.nc_per = pl.nc_per; prm.nstg = pl.nstg; prm.debug = g_debug;
     prm.cps = pl.cps; prm.slot_bytes = pl.slot_bytes; prm.esc_cap = pl.esc_cap;
-    prm.xs_halves = pl.xs_halves; prm.raw_bytes = pl.raw_bytes;
+    prm.xs_halves = pl.xs_halves;
     for (int i = 0; i < 6; ++i) prm.rs[i] = pl.rs[i];
 }
 }  // namespace qv
@@ -1883,6 +1897,10 @@ __device__ __forceinline__ float prepass_x(const JobDesc &jd, int m, int col) {
     return __half2float(sat_half(x));
 }
 __global__ void __launch_bounds__(128) escape_prepass_kernel(const __grid_constant__ EscPrepassParams p) {
+    // programmatic dependent launch: the streaming kernel that follows may begin its weight prefetch at once; this
+    // kernel reads activations and writes outputs only after whatever precedes it in the stream has completed
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int gt = (int)(gi >> 4), slot = (int)(gi & 15);
     if (gt >= p.tile_start[p.njobs]) return;
@@ -1923,40 +1941,76 @@ __global__ void __launch_bounds__(128) escape_prepass_kernel(const __grid_consta
     }
 }
 
-// Can these jobs run as one list launch?  All through the streaming kernel (plan, layout), none K-split.
-static bool group_fits(const qvb8_job *jobs, int n, int64_t M, Plan &pl) {
+// Can this job be part of a list launch?  Through the streaming kernel (plan, layout), activations staged whole.
+static bool job_listable(const qvb8_job &jb) {
+    return jb.plan && aligned(jb.plan, 16) && fast_layout_ok(jb.w, jb.X) && jb.w->Q > 0 &&
+           (jb.w->Q + 15) / 16 + NCLASS - 1 <= MAX_TICKET_TILES &&
+           !(jb.x_mode == 1 && jb.x_dtype != QVB8_F16);                  // the prescale pass is the single launch's
+}
+// Do the jobs idx[0 .. n) fit one list launch?
+static bool list_fits(const qvb8_job *jobs, const int *idx, int n, int64_t M, Plan &pl) {
     int64_t Ps[MAX_JOBS];
     int esizes[MAX_JOBS];
     for (int j = 0; j < n; ++j) {
-        const qvb8_job &jb = jobs[j];
-        if (!jb.plan || !aligned(jb.plan, 16) || !fast_layout_ok(jb.w, jb.X) ||
-            (jb.w->Q + 15) / 16 + NCLASS - 1 > MAX_TICKET_TILES || jb.w->Q == 0 ||
-            (jb.x_mode == 1 && jb.x_dtype != QVB8_F16))                   // the prescale pass is the single launch's
-            return false;
-        Ps[j] = jb.w->P;
-        esizes[j] = jb.x_dtype == QVB8_F32 ? 4 : 2;
+        Ps[j] = jobs[idx[j]].w->P;
+        esizes[j] = jobs[idx[j]].x_dtype == QVB8_F32 ? 4 : 2;
     }
     return make_group_plan(M, Ps, esizes, n, pl);
+}
+
+// Walks the jobs in order and cuts them into list launches: a job joins the open list while it can be listed and the
+// list still fits shared memory (at most MAX_JOBS jobs); jobs that cannot be listed, and lists of one, run as single
+// launches.  on_list(idx, n, plan) / on_single(j) are called in an order that may differ from the jobs' order (the
+// jobs are independent).  Returns the first non-zero status of a callback.
+template <typename OnList, typename OnSingle>
+static int walk_group(const qvb8_job *jobs, int njobs, int64_t M, OnList on_list, OnSingle on_single) {
+    int idx[MAX_JOBS], n = 0;
+    Plan pl{};
+    auto flush = [&]() -> int {
+        int rc = QVB8_OK;
+        if (n == 1) rc = on_single(idx[0]);
+        else if (n > 1) rc = on_list(idx, n, pl);
+        n = 0;
+        return rc;
+    };
+    for (int j = 0; j < njobs; ++j) {
+        if (!job_listable(jobs[j])) {
+            if (int rc = on_single(j)) return rc;
+            continue;
+        }
+        idx[n] = j;
+        Plan trial;
+        if (n < MAX_JOBS && list_fits(jobs, idx, n + 1, M, trial)) {
+            pl = trial;
+            ++n;
+            continue;
+        }
+        int alone[1] = {j};
+        if (!list_fits(jobs, alone, 1, M, trial)) {                     // too large for any list: on its own, the open list stays open
+            if (int rc = on_single(j)) return rc;
+            continue;
+        }
+        if (int rc = flush()) return rc;                                // close the open list, start a new one with job j
+        idx[0] = j;
+        pl = trial;
+        n = 1;
+    }
+    return flush();
 }
 }  // namespace qv
 
 QV_API int64_t qvb8_small_m_group_scratch_bytes(const qvb8_job *jobs, int njobs, int64_t M) {
     using namespace qv;
     if (!jobs || njobs <= 0 || M < 1 || M > MAX_M) return 0;
+    for (int j = 0; j < njobs; ++j)
+        if (!jobs[j].w || jobs[j].w->P <= 0 || jobs[j].w->Q < 0) return 0;
     int64_t need = 0;
-    for (int j0 = 0; j0 < njobs; j0 += MAX_JOBS) {
-        const int n = njobs - j0 < MAX_JOBS ? njobs - j0 : MAX_JOBS;
-        bool ok = true;
-        for (int j = 0; j < n; ++j) ok = ok && jobs[j0 + j].w && jobs[j0 + j].w->P > 0;
-        Plan pl;
-        if (ok && n > 1 && group_fits(jobs + j0, n, M, pl)) continue;
-        for (int j = 0; j < n; ++j) {                                   // this part of the list runs job by job
-            const qvb8_pack *w = jobs[j0 + j].w;
-            if (!w) continue;
-            const int64_t b = qvb8_small_m_scratch_bytes(M, w->Q, w->P);
-            if (b > need) need = b;
-        }
-    }
+    walk_group(jobs, njobs, M, [](const int *, int, const Plan &) { return 0; },
+               [&](int j) {
+                   const int64_t b = qvb8_small_m_scratch_bytes(M, jobs[j].w->Q, jobs[j].w->P);
+                   if (b > need) need = b;
+                   return 0;
+               });
     return need;
 }
 
@@ -1970,44 +2024,48 @@ QV_API int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const bool pdl = (flags & QVB8_FLAG_PDL) != 0;
-    for (int j0 = 0; j0 < njobs; j0 += MAX_JOBS) {
-        const int n = njobs - j0 < MAX_JOBS ? njobs - j0 : MAX_JOBS;
-        Plan pl;
-        if (n > 1 && group_fits(jobs + j0, n, M, pl)) {
-            static thread_local SmallMParams prm;
-            static thread_local EscPrepassParams esc;
-            prm.njobs = n;
-            esc.njobs = n;
-            esc.M = (int)M;
-            esc.tile_start[0] = 0;
-            int64_t units = 0;
-            for (int j = 0; j < n; ++j) {
-                const qvb8_job &jb = jobs[j0 + j];
-                fill_job(prm.jobs[j], jb.w, jb.plan, jb.X, jb.Y, jb.x_dtype, jb.x_mode, (int)units, jb.w->n_esc > 0 ? 1 : 0);
-                esc.jobs[j] = prm.jobs[j];
-                esc.tile_start[j + 1] = esc.tile_start[j] + (jb.w->n_esc > 0 ? prm.jobs[j].ntiles : 0);
-                units += (int64_t)prm.jobs[j].ntiles * ((prm.jobs[j].nc_total + pl.cps - 1) / pl.cps);
-            }
-            if (units > 0x7fffffff) return fail(QVB8_ERR_ARG, "qvb8_small_m_group: the list is too long for one launch");
-            prm.units_total = (int)units;
-            if (esc.tile_start[n] > 0 && !(g_debug & 32)) {            // the escapes first: corrections into Y (debug bit 5: skipped)
-                const int64_t threads = (int64_t)esc.tile_start[n] * 16;
-                escape_prepass_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, st>>>(esc);
-                if (int rc = cuda_status("qvb8_small_m_group escape pre-pass")) return rc;
-            }
-            prm.ticket = nullptr;
-            prm.part = nullptr;
-            fill_launch(prm, pl, (int)M);
-            if (int rc = launch_nt(prm, pl, st, pdl)) return rc;
-        } else {
-            for (int j = 0; j < n; ++j) {
-                const qvb8_job &jb = jobs[j0 + j];
-                if (int rc = qvb8_small_m_ex(jb.w, jb.plan, jb.X, jb.x_dtype, jb.x_mode, M, jb.Y, scratch, scratch_bytes, flags, stream))
-                    return rc;
-            }
+    auto on_single = [&](int j) -> int {
+        const qvb8_job &jb = jobs[j];
+        return qvb8_small_m_ex(jb.w, jb.plan, jb.X, jb.x_dtype, jb.x_mode, M, jb.Y, scratch, scratch_bytes, flags, stream);
+    };
+    auto on_list = [&](const int *idx, int n, const Plan &pl) -> int {
+        static thread_local SmallMParams prm;
+        static thread_local EscPrepassParams esc;
+        prm.njobs = n;
+        esc.njobs = n;
+        esc.M = (int)M;
+        esc.tile_start[0] = 0;
+        int64_t units = 0;
+        for (int j = 0; j < n; ++j) {
+            const qvb8_job &jb = jobs[idx[j]];
+            fill_job(prm.jobs[j], jb.w, jb.plan, jb.X, jb.Y, jb.x_dtype, jb.x_mode, (int)units, jb.w->n_esc > 0 ? 1 : 0);
+            esc.jobs[j] = prm.jobs[j];
+            esc.tile_start[j + 1] = esc.tile_start[j] + (jb.w->n_esc > 0 ? prm.jobs[j].ntiles : 0);
+            units += (int64_t)prm.jobs[j].ntiles * ((prm.jobs[j].nc_total + pl.cps - 1) / pl.cps);
         }
-    }
-    return QVB8_OK;
+        if (units > 0x7fffffff) return fail(QVB8_ERR_ARG, "qvb8_small_m_group: the list is too long for one launch");
+        prm.units_total = (int)units;
+        if (esc.tile_start[n] > 0 && !(g_debug & 32)) {                // the escapes first: corrections into Y (debug bit 5: skipped)
+            const int64_t threads = (int64_t)esc.tile_start[n] * 16;
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3((unsigned)((threads + 127) / 128));
+            cfg.blockDim = dim3(128);
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = pdl ? 1 : 0;
+            if (cudaLaunchKernelEx(&cfg, escape_prepass_kernel, esc) != cudaSuccess)
+                return cuda_status("qvb8_small_m_group escape pre-pass launch");
+            if (int rc = cuda_status("qvb8_small_m_group escape pre-pass")) return rc;
+        }
+        prm.ticket = nullptr;
+        prm.part = nullptr;
+        fill_launch(prm, pl, (int)M);
+        return launch_nt(prm, pl, st, pdl);
+    };
+    return walk_group(jobs, njobs, M, on_list, on_single);
 }
 
 QV_API int qvb8_small_m(const qvb8_pack *w, const void *X, int x_dtype, int x_mode, int64_t M, float *Y, void *scratch,
