@@ -285,6 +285,169 @@ def run_prefill(args):
                      "peak_kind": "measured (burst)" if peaks else "fallback", "kernel": "prefill_kernel"}}), flush=True)
 
 
+def run_single(args):
+    """One linear layer (default 4096 x 4096, the single-layer configuration; --shape QxP for others) at M = --rows:
+    `copies` distinct packs of that shape are multiplied back to back per step, so that a step streams more bytes than
+    the L2 holds.  One launch per pack (the reference-shaped call path).  Also the committed driver of the profiler
+    summaries under profiles/."""
+    import oracle
+    from qvb8_b200 import lib, synth
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Q, P = (int(v) for v in args.shape.lower().split("x"))
+    M = args.rows
+    one = synth.synth_pack(Q, P, 1000, tau=1e-3, device=dev, policy=args.policy)
+    copies = max(2, -(-(300 << 20) // max(1, one.weight_bytes())))          # > 2 x L2 per step
+    packs = [one] + [synth.synth_pack(Q, P, 1000 + c, tau=1e-3, device=dev, policy=args.policy) for c in range(1, copies)]
+    work = []
+    X = synth.synth_activation(M, P, seed=7, device=dev)
+    for pk in packs:
+        st, keep = lib.pack_struct(pk.ids, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off, pk.P, pk.esc_idx, pk.esc_vals)
+        work.append((st, keep, lib.build_plan(st, keep), torch.empty(M, Q, device=dev)))
+    lib.reserve_scratch(dev, M, Q, P)
+    nbytes = sum(pk.weight_bytes() for pk in packs)
+
+    def step():
+        for st, keep, plan, Y in work:
+            lib.small_m(st, keep, X, out=Y, plan=plan, flags=lib.FLAG_PDL)
+    s = torch.cuda.Stream(dev)
+    with torch.cuda.stream(s):
+        lib.reserve_scratch(dev, M, Q, P)
+        step()
+    s.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=s):
+        step()
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        ev1.record()
+        torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    # parity of what was just timed: pack 0 against the CPU oracle
+    d = dict(Q=one.Q, P=one.P, ids=one.ids.cpu().numpy(), nbits=one.nbits.cpu().numpy(), bit_off=one.bit_off.cpu().numpy(),
+             min_s=one.min_s.cpu().numpy(), tau_s=one.tau_s.cpu().numpy(), esc_idx=one.esc_idx.cpu().numpy(),
+             esc_vals=one.esc_vals.cpu().numpy())
+    want = oracle.matmul_f32w(X.float().cpu().numpy(), oracle.qvb8_dense(d), narrow_x=True)
+    got = work[0][3].cpu().numpy()
+    import numpy as np
+    err = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+    # end to end: X from pinned host memory, the last pack's result back to the host
+    hx, hy = X.cpu().pin_memory(), torch.empty_like(work[-1][3], device="cpu").pin_memory()
+    def e2e_step():
+        X.copy_(hx, non_blocking=True)
+        graph.replay()
+        hy.copy_(work[-1][3], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    for _ in range(3):
+        e2e_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    # CPU baseline: the oracle's restatement of the reference decoder restoring pack 0 to bf16 + torch matmul
+    threads = oracle.num_threads()
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    sample = [(dict(d, bytes=one.weight_bytes()), X.cpu())]
+    cpu_reference_step(sample, threads)
+    t0 = time.perf_counter()
+    nb = reps = 0
+    while time.perf_counter() - t0 < args.cpu_seconds:
+        nb += cpu_reference_step(sample, threads)
+        reps += 1
+    dt = time.perf_counter() - t0
+    peak, peak_kind = measured_peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"single linear {Q}x{P}, M={M}, QVB8 tau=1e-3, policy={args.policy}: {copies} distinct packs "
+                               "per step, one launch each", "bytes_per_step": nbytes, "us_per_launch": ms * 1e3 / copies,
+                   "l2": "a step streams more than twice the L2", "rel_fro_vs_oracle": err},
+        "clocks": clocks.summary(), "gpu_launches": copies * args.steps,
+        "e2e": {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": hx.numel() * hx.element_size(),
+                "d2h_bytes_per_step": hy.numel() * hy.element_size(), "ms_per_step": e2e_ms},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "peak_kind": peak_kind, "kernel": "small_m_kernel"},
+        "cpu_baseline": {"value": nb / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"pack 0 restored to bf16 by the C restatement of the reference decoder + torch.matmul, "
+                                   f"{reps} repetitions in {dt:.1f} s"}}), flush=True)
+
+
+def run_qvb8r(args):
+    """The entropy-coded format: the seven projections of one 27B-class layer (d_model 5120, MLP 17408, q/o 5120, k/v
+    1024) as QVB8R packs at tau = 2e-3, products at M = --rows (1 = gemv, 2..8 = multi, 9..16 = tc) with the escape
+    pass.  Metric: bytes of the coded stream and its tables per second (the kernel is bound by the decoder's
+    dependency chain, not by HBM: the fraction is reported for completeness).  --layers scales the rows down for quick
+    runs (rows / layers)."""
+    import numpy as np
+    from qvb8_b200 import rans, synth
+    from qvb8_b200.linear_r import QVBandLinearV8R
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    M = args.rows
+    div = max(1, args.layers or 1)
+    d, f = 5120, 17408
+    shapes = [("q", 5120, d), ("k", 1024, d), ("v", 1024, d), ("o", d, 5120), ("gate", f, d), ("up", f, d), ("down", d, f)]
+    t0 = time.perf_counter()
+    mods, nbytes, nweights = [], 0, 0
+    for j, (name, Q, P) in enumerate(shapes):
+        Q = max(64, Q // div)
+        enc = synth.encode_qvb8r(synth.synth_weight(Q, P, 3000 + j), tau=2e-3, K=4, T=max(1, -(-Q // 4096)))
+        nt = len(enc["tiles"])
+        nb8 = len(rans.blocks_for(enc["tiles"], 8))
+        nbytes += 4 * enc["words"].size + 256 * nt + 8 * (nt + 1) + 24 * nt + 12 * nb8 + 16384 * int(enc["K"]) + 16 * Q \
+            + 20 * len(enc["esc_idx"])
+        nweights += Q * P
+        mods.append((name, QVBandLinearV8R(enc, device=dev), synth.synth_activation(M, P, seed=7 + j, device=dev)))
+    t_build = time.perf_counter() - t0
+
+    def step():
+        return [m(x) for _, m, x in mods]
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    hx = [x.cpu().pin_memory() for *_, x in mods]
+    def e2e_step():
+        outs = [m(h.to(dev, non_blocking=True)) for (_, m, _), h in zip(mods, hx)]
+        return outs[-1].float().cpu()
+    e2e_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    peak, peak_kind = measured_peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "qvb8r_coded_stream_bytes_per_s", "value": gbs, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"27B-class layer, 7 projections as QVB8R packs (tau 2e-3), M={M}" + (f", rows / {div}" if div > 1 else ""),
+                   "weights": nweights, "bytes": nbytes, "bits_per_weight": 8.0 * nbytes / nweights,
+                   "weights_per_s": nweights / (ms * 1e-3), "pack_build_s": round(t_build, 1),
+                   "l2": "coded streams of the layer exceed the L2" if nbytes > (126 << 20) else "working set fits the L2"},
+        "clocks": clocks.summary(), "gpu_launches": 2 * len(mods) * args.steps,
+        "e2e": {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+                "h2d_bytes_per_step": int(sum(h.numel() * h.element_size() for h in hx)),
+                "d2h_bytes_per_step": int(mods[-1][1].out_features * M * 4), "ms_per_step": e2e_ms},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "peak_kind": peak_kind, "kernel": "qvb8r_kernel",
+                     "note": "bound by the entropy decoder's per-lane dependency chain, not by HBM"}}), flush=True)
+
+
 def finish(world, dist):
     """Leave a multi-rank run without tearing NCCL down: communicators referenced by captured graphs make
     destroy_process_group wait for ever, so the ranks meet at a barrier, flush and exit."""
@@ -307,14 +470,16 @@ def main():
     ap.add_argument("--rows", type=int, default=1, help="activation rows M (1 = decode)")
     ap.add_argument("--policy", default="escape_outliers")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--workload", default="stack", choices=["stack", "moe", "prefill"],
+    ap.add_argument("--shape", default="4096x4096", help="--workload single: QxP")
+    ap.add_argument("--workload", default="stack", choices=["stack", "moe", "prefill", "single", "qvb8r"],
                     help="stack: the dense linear stack (headline); moe: one 35B-A3B-class expert layer; "
                          "prefill: 27B-class MLP projections for 2048 tokens on the tcgen05 kernel")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection (no same-input fusion)")
     ap.add_argument("--group-layers", type=int, default=-1,
                     help="layers whose projections run behind one launch (0 = one launch per projection; "
-                         "-1 = default: 8 on one GPU, 0 with several)")
+                         "-1 = default: 8)")
     ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: NCCL all-reduce instead of the peer push kernel")
+    ap.add_argument("--no-alt-policy", action="store_true", help="skip the second measurement with the in-band encoder policy")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -325,6 +490,12 @@ def main():
         return
     if args.workload == "prefill" and args.impl != "reference":
         run_prefill(args)
+        return
+    if args.workload == "single" and args.impl != "reference":
+        run_single(args)
+        return
+    if args.workload == "qvb8r" and args.impl != "reference":
+        run_qvb8r(args)
         return
     if args.impl == "reference":
         run_reference_arm(args, cfg)
@@ -376,8 +547,8 @@ def main():
         else:
             st.enable_collectives(peer=False)
 
-    group_layers = args.group_layers if args.group_layers >= 0 else (8 if world == 1 else 0)
-    if world == 1 and group_layers > 0:
+    group_layers = args.group_layers if args.group_layers >= 0 else 8
+    if group_layers > 0:
         st.set_grouping(group_layers)
 
     def one_step():
@@ -439,11 +610,39 @@ def main():
         e2e_s = float(t.item())
     e2e_gbs = total_bytes / e2e_s / 1e9
 
+    # the same stack with the encoder's other policy (outliers kept in band: 8-bit rows, no escape list), one GPU only
+    alt = None
+    if world == 1 and args.policy == "escape_outliers" and not args.no_alt_policy:
+        st2 = S.LinearStack(cfg, args.rows, dev, layers=args.layers, policy="inband", fuse_same_input=not args.no_fuse)
+        if group_layers > 0:
+            st2.set_grouping(group_layers)
+        st2.capture()
+        for _ in range(args.warmup):
+            st2.step()
+        blocks = []
+        t_start = time.perf_counter()
+        while time.perf_counter() - t_start < 0.5 or len(blocks) < 3:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(dev)
+            e0.record()
+            for _ in range(args.steps):
+                st2.step()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            blocks.append(e0.elapsed_time(e1) / args.steps)
+        ms2 = statistics.median(blocks)
+        alt = {"policy": "inband (8-bit rows, no escapes)", "ms_per_step": ms2, "compressed_bytes": st2.compressed_bytes,
+               "value": st2.compressed_bytes / (ms2 * 1e-3) / 1e9, "unit": UNIT,
+               "bits_per_weight": 8.0 * st2.compressed_bytes / max(1, st2.n_weights), "tokens_per_s": 1e3 / ms2 * args.rows}
+        del st2
+
     if rank != 0:
         finish(world, dist)
         return
 
     peak, peak_kind = measured_peaks()
+    if alt is not None:
+        alt["frac_of_hbm_peak"] = alt["value"] / peak
     per_launch_bytes = total_bytes / max(1, launches)
     line = {
         "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -461,9 +660,12 @@ def main():
             "weights": total_weights, "compressed_bytes": total_bytes,
             "bits_per_weight": 8.0 * total_bytes / max(1, total_weights),
             "row_width_hist": {str(k): v for k, v in sorted(st.width_hist.items())}, "escapes": st.n_escapes,
-            "parallelism": f"column/row-parallel pairs x{world}, 2 all-reduces per layer ({allreduce_kind})" if world > 1 else "single GPU",
+            "parallelism": (f"column/row-parallel pairs x{world}; the partial sums of o and down are exchanged by "
+                            f"{'one all-reduce per launch' if st._groups else 'two all-reduces per layer'} ({allreduce_kind})")
+                           if world > 1 else "single GPU",
             "l2": "working set (packs) far larger than L2; every step streams all of it",
             "tokens_per_s": 1e3 / ms_step * args.rows, "pack_build_s": round(t_build, 1),
+            "other_encoder_policy": alt,
         },
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_gbs, "unit": UNIT, "h2d_bytes_per_step": st.h2d_bytes(), "d2h_bytes_per_step": st.d2h_bytes(),

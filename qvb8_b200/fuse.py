@@ -65,6 +65,70 @@ def concat_packs(members: list[QVB8Pack]) -> tuple[QVB8Pack, list[int]]:
     return fused, splits
 
 
+def row_shard(pk: QVB8Pack, r0: int, r1: int) -> QVB8Pack:
+    """The pack of output rows [r0, r1) of `pk`, made from its bytes: rows of a pack are independent (own origin, step,
+    width and bit range), so a shard is a slice of the four per-row vectors, the byte range of those rows, and the
+    escapes that fall into them renumbered.  Nothing is re-encoded: the shard restores to exactly rows [r0, r1) of
+    the whole.  (The reference slices rows the same way, formats/qvb8/module.py:126-160.)"""
+    if not 0 <= r0 < r1 <= pk.Q:
+        raise ValueError(f"row_shard: rows [{r0}, {r1}) of {pk.Q}")
+    bits = pk.nbits.to(torch.int64) * pk.P
+    first_bit = int(pk.bit_off[r0].item())
+    last_bit = int(pk.bit_off[r1 - 1].item()) + int(bits[r1 - 1].item())
+    if first_bit % 8 or (last_bit % 8 and r1 != pk.Q):
+        raise ValueError("row_shard: the rows do not start and end on byte boundaries (P * nbits must be a multiple of 8)")
+    payload = pk.ids[first_bit // 8:(last_bit + 7) // 8]
+    ids = torch.cat([payload, torch.zeros(packs.PAYLOAD_PAD, dtype=torch.uint8, device=pk.device)])
+
+    def esc(idx, vals):
+        keep = (idx >= r0 * pk.P) & (idx < r1 * pk.P)
+        return idx[keep] - r0 * pk.P, vals[keep]
+    ei, ev = esc(pk.esc_idx, pk.esc_vals)
+    same = pk.esc_idx_bf16 is pk.esc_idx
+    eib, evb = (ei, ev) if same else esc(pk.esc_idx_bf16, pk.esc_vals_bf16)
+    nb = pk.nbits[r0:r1]
+    hist = {int(b): int(n) for b, n in zip(*torch.unique(nb, return_counts=True))}
+    return QVB8Pack(Q=r1 - r0, P=pk.P, tau=pk.tau, restore=pk.restore, ids=ids, min_s=pk.min_s[r0:r1].contiguous(),
+                    tau_s=pk.tau_s[r0:r1].contiguous(), nbits=nb.contiguous(),
+                    bit_off=(pk.bit_off[r0:r1] - first_bit).contiguous(), esc_idx=ei, esc_vals=ev, esc_idx_bf16=eib,
+                    esc_vals_bf16=evb, max_err=pk.max_err, stats={"nbits_hist": hist})
+
+
+def column_shard(pk: QVB8Pack, c0: int, c1: int) -> QVB8Pack:
+    """The pack of input columns [c0, c1) of every row of `pk`, made from its bytes -- the shard a row-parallel
+    (input-split) linear needs when a deployment holds only the pack, not the source weight.  A row's ids are a bit
+    string of nbits * P bits; columns [c0, c1) are the bits [c0 * nbits, c1 * nbits) of it, which are whole bytes for
+    every width when c0 and c1 are multiples of 8.  Origins and steps are unchanged, escapes inside the range are
+    renumbered: the shard restores to exactly those columns of the whole, so the ranks' partial products add up to the
+    unsharded product."""
+    P, Q, dev = pk.P, pk.Q, pk.device
+    if not (0 <= c0 < c1 <= P) or c0 % 8 or c1 % 8:
+        raise ValueError(f"column_shard: columns [{c0}, {c1}) of {P} must be multiples of 8")
+    if bool((pk.bit_off % 8 != 0).any()):
+        raise ValueError("column_shard: rows must start on byte boundaries (P * nbits a multiple of 8)")
+    nb = pk.nbits.to(torch.int64)
+    width = c1 - c0
+    row_bytes = nb * (width // 8)                                        # bytes of the slice, per row
+    src0 = pk.bit_off // 8 + nb * (c0 // 8)                              # first source byte, per row
+    dst0 = torch.cumsum(row_bytes, 0) - row_bytes                        # first destination byte, per row
+    total = int(row_bytes.sum().item())
+    row_of = torch.repeat_interleave(torch.arange(Q, device=dev), row_bytes)
+    within = torch.arange(total, device=dev) - dst0[row_of]
+    payload = pk.ids[src0[row_of] + within]
+    ids = torch.cat([payload, torch.zeros(packs.PAYLOAD_PAD, dtype=torch.uint8, device=dev)])
+
+    def esc(idx, vals):
+        q, c = torch.div(idx, P, rounding_mode="floor"), torch.remainder(idx, P)
+        keep = (c >= c0) & (c < c1)
+        return q[keep] * width + (c[keep] - c0), vals[keep]
+    ei, ev = esc(pk.esc_idx, pk.esc_vals)
+    same = pk.esc_idx_bf16 is pk.esc_idx
+    eib, evb = (ei, ev) if same else esc(pk.esc_idx_bf16, pk.esc_vals_bf16)
+    return QVB8Pack(Q=Q, P=width, tau=pk.tau, restore=pk.restore, ids=ids, min_s=pk.min_s, tau_s=pk.tau_s, nbits=pk.nbits,
+                    bit_off=(dst0 * 8).contiguous(), esc_idx=ei, esc_vals=ev, esc_idx_bf16=eib, esc_vals_bf16=evb,
+                    max_err=pk.max_err, stats=dict(pk.stats))
+
+
 # (group name, member names) of a decoder layer whose members are fed the same tensor
 SAME_INPUT_GROUPS = (("qkv", ("q", "k", "v")), ("gate_up", ("gate", "up")))
 

@@ -108,40 +108,42 @@ def encode_symbols(sym: np.ndarray, tile_class: np.ndarray, tile_rows: np.ndarra
     x = np.full((nt, 32), 1 << 32, np.uint64)              # the decoder's state after its last pair
     maxr = int(np.max(tile_rows))
     S2 = P // 64
-    emitted = [[] for _ in range(nt)]                      # per tile: (nt_step) arrays of words in reverse order
     cls = np.asarray(tile_class, np.int64)
+    trows = np.asarray(tile_rows, np.int64)
     lanes = np.arange(32)
+    # every (row, pair) step of the backward walk leaves, per tile and lane, a flag "emitted a word" and the word; the
+    # stream of a tile is those words with the steps in DECODING order (the reverse of this loop) and the lanes ascending
+    steps = maxr * S2
+    flags = np.zeros((steps, nt, 32), bool)
+    lows = np.zeros((steps, nt, 32), np.uint32)
+    k = 0
     for r in range(maxr - 1, -1, -1):
-        act = np.nonzero(np.asarray(tile_rows) > r)[0]     # tiles that have a row r
-        if act.size == 0:
-            continue
+        act = np.nonzero(trows > r)[0]                     # tiles that have a row r
         rows = first[act] + r
-        k = cls[act][:, None]
+        kk = cls[act][:, None]
+        srow = sym[rows]
         for sp in range(S2 - 1, -1, -1):
-            s0 = sym[rows][:, (2 * sp) * 32 + lanes]       # first symbol of the pair per lane
-            s1 = sym[rows][:, (2 * sp + 1) * 32 + lanes]
-            f0, f1 = F[k, s0], F[k, s1]
+            s0 = srow[:, (2 * sp) * 32 + lanes]            # first symbol of the pair per lane
+            s1 = srow[:, (2 * sp + 1) * 32 + lanes]
+            f0, f1 = F[kk, s0], F[kk, s1]
             if (f0 == 0).any() or (f1 == 0).any():
                 raise ValueError("a coded symbol has frequency 0 in its class")
             xa = x[act]
             emit = xa >= ((f0 * f1).astype(np.uint64) << np.uint64(40))
-            low = (xa & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+            flags[k, act] = emit
+            lows[k, act] = (xa & np.uint64(0xFFFFFFFF)).astype(np.uint32)
             xa = np.where(emit, xa >> np.uint64(32), xa)
             # decoder order inside a lane: symbol 0 then symbol 1 -> encode symbol 1 first
-            for f, c in ((f1, C[k, s1]), (f0, C[k, s0])):
+            for f, c in ((f1, C[kk, s1]), (f0, C[kk, s0])):
                 fu = f.astype(np.uint64)
                 xa = ((xa // fu) << np.uint64(PB)) + (xa % fu) + c.astype(np.uint64)
             x[act] = xa
-            for i, t in enumerate(act):                    # decoder hands words out by ascending lane
-                w = low[i][emit[i]]
-                if w.size:
-                    emitted[t].append(w[::-1])
-    words, tile_off = [], [0]
-    for t in range(nt):
-        w = np.concatenate(emitted[t])[::-1] if emitted[t] else np.zeros(0, np.uint32)
-        words.append(w)
-        tile_off.append(tile_off[-1] + w.size)
-    return x, (np.concatenate(words) if words else np.zeros(0, np.uint32)).astype(np.uint32), np.asarray(tile_off, np.uint32)
+            k += 1
+    flags = flags[::-1].transpose(1, 0, 2)                 # (tile, decoding step, lane)
+    lows = lows[::-1].transpose(1, 0, 2)
+    words = lows[flags].astype(np.uint32)                  # tiles in order, steps in decoding order, lanes ascending
+    tile_off = np.concatenate([[0], np.cumsum(flags.reshape(nt, -1).sum(1))]).astype(np.uint32)
+    return x, words, tile_off
 
 
 def model_for(ids: np.ndarray, K: int = 2, T: int = 8) -> dict:

@@ -71,9 +71,10 @@ class LinearStack:
     rank / world: q/k/v and gate/up are sharded by OUTPUT ROWS (column-parallel): rank r holds rows
     [r*Q/world, (r+1)*Q/world), which for a QVB8 pack is a slice of the per-row vectors and a byte range of the ids
     (rows are independent, reference formats/qvb8/module.py:126-160).  Their consumers o and down are sharded by
-    INPUT COLUMNS (row-parallel): rank r holds columns [r*P/world, (r+1)*P/world) of every row, encoded as a pack of
-    its own, reads the matching slice of the activation and produces a partial (M, Q) sum; one all-reduce per
-    column->row pair is the only exchange (two per layer)."""
+    INPUT COLUMNS (row-parallel): rank r holds columns [r*P/world, (r+1)*P/world) of every row, cut out of the whole
+    pack's bytes (``fuse.column_shard``), reads the matching slice of the activation and produces a partial (M, Q)
+    sum; one all-reduce per column->row pair is the only exchange (two per layer, or one per launch when several
+    layers run behind one launch)."""
 
     def __init__(self, cfg: StackConfig, M: int, device, layers: int | None = None, seed_base: int | None = None,
                  rank: int = 0, world: int = 1, policy: str = "escape_outliers", x_dtype=torch.bfloat16,
@@ -93,19 +94,21 @@ class LinearStack:
         for layer in range(self.layers):
             made = {}
             for j, (name, Q, P, xname) in enumerate(cfg.projections()):
+                # every rank encodes the WHOLE weight (a deployment would read the whole pack file) and cuts its shard
+                # out of the pack's bytes: rows for the column-parallel projections, input columns for the row-parallel
                 W = synth.synth_weight(Q, P, seed_base + layer * 16 + j, device=self.device)
-                if name in ROW_PARALLEL:
-                    if P % (128 * world):
-                        raise ValueError(f"{name}: {P} columns do not split over {world} ranks in 128-column units")
-                    Pr = P // world
-                    W = W[:, rank * Pr:(rank + 1) * Pr].contiguous()
-                else:
-                    if Q % world:
-                        raise ValueError(f"{name}: {Q} rows do not split over {world} ranks")
-                    Qr = Q // world
-                    W = W[rank * Qr:(rank + 1) * Qr]
-                made[name] = (synth.encode_qvb8(W, tau=cfg.tau, policy=policy), xname)
+                pk = synth.encode_qvb8(W, tau=cfg.tau, policy=policy)
                 del W
+                if world > 1:
+                    if name in ROW_PARALLEL:
+                        if P % (128 * world):
+                            raise ValueError(f"{name}: {P} columns do not split over {world} ranks in 128-column units")
+                        pk = _fuse.column_shard(pk, rank * (P // world), (rank + 1) * (P // world))
+                    else:
+                        if Q % world:
+                            raise ValueError(f"{name}: {Q} rows do not split over {world} ranks")
+                        pk = _fuse.row_shard(pk, rank * (Q // world), (rank + 1) * (Q // world))
+                made[name] = (pk, xname)
             row, done = [], set()
             for name, _, _, xname in cfg.projections():
                 if name in done:
@@ -134,9 +137,22 @@ class LinearStack:
         shapes = {"x_attn": d, "x_o": cfg.q_out // world, "x_mlp": d, "x_down": f // world}
         self.x = {k: synth.synth_activation(self.M, p, seed=7 + i, device=self.device, dtype=x_dtype)
                   for i, (k, p) in enumerate(shapes.items())}
-        # one output buffer per launch; y[layer][name] are the members' views of it
-        self.y_launch = [[torch.empty((self.M, pk.Q), dtype=torch.float32, device=self.device) for _, pk, *_ in row]
-                         for row in self.launches]
+        # one output buffer per launch; y[layer][name] are the members' views of it.  The outputs of the row-parallel
+        # projections (partial sums that the ranks exchange) lie side by side in ONE buffer, layer after layer, so that
+        # the partial sums of several layers can be exchanged by a single all-reduce.
+        n_rp = sum(1 for name, *_ in self.launches[0] if name in ROW_PARALLEL)
+        self.y_rowpar = torch.empty((self.layers * n_rp, self.M, d), dtype=torch.float32, device=self.device)
+        self.y_launch = []
+        for li, row in enumerate(self.launches):
+            outs, k = [], 0
+            for name, pk, *_ in row:
+                if name in ROW_PARALLEL and pk.Q == d:
+                    outs.append(self.y_rowpar[li * n_rp + k])
+                    k += 1
+                else:
+                    outs.append(torch.empty((self.M, pk.Q), dtype=torch.float32, device=self.device))
+            self.y_launch.append(outs)
+        self._n_rp = n_rp
         self.y = []
         for row, outs in zip(self.launches, self.y_launch):
             views = {}
@@ -167,7 +183,9 @@ class LinearStack:
         self.peer = None
         if self.reduce and peer:
             from .peer import PeerAllReduce
-            cap = max(t.numel() for row in self.y_launch for t in row)
+            # the largest exchange: the row-parallel outputs of up to eight layers at once (see set_grouping)
+            cap = max(max(t.numel() for row in self.y_launch for t in row),
+                      min(self.layers, 8) * self._n_rp * self.M * self.cfg.d_model)
             self.peer = PeerAllReduce(dist.group.WORLD, cap, self.device)
 
     def _allreduce(self, t: torch.Tensor) -> None:
@@ -181,15 +199,17 @@ class LinearStack:
         """Run the projections of `layers_per_launch` consecutive layers as ONE launch each (``qvb8_small_m_group``):
         inside a launch the weight stream never drains between projections.  The stack's projections read resident
         activation buffers and write separate outputs, so they are independent jobs.  0 = one launch per projection.
-        Not combined with the multi-GPU exchange (the all-reduce follows single launches)."""
-        self.group_layers = int(layers_per_launch)
+        With several ranks the partial sums of a launch's row-parallel projections (o and down of its layers) are
+        exchanged by ONE all-reduce after the launch."""
+        self.group_layers = min(int(layers_per_launch), 8)
         self._groups = None
         self.graph = None
         if self.group_layers > 0:
             per = max(1, min(self.group_layers, _lib_max_jobs() // max(1, len(self.launches[0]))))
-            self._groups = []
+            self._groups, self._group_layers = [], []
             for l0 in range(0, self.layers, per):
                 items = []
+                self._group_layers.append((l0, min(self.layers, l0 + per)))
                 for li in range(l0, min(self.layers, l0 + per)):
                     for j, (name, pk, st, keep, xname, _) in enumerate(self.launches[li]):
                         items.append((st, keep, keep[-1], self.x[xname], self.y_launch[li][j]))
@@ -200,9 +220,11 @@ class LinearStack:
 
     def run_eager(self) -> None:
         """One pass over every launch of every layer on the current stream."""
-        if self._groups is not None and not self.reduce:
-            for g in self._groups:
+        if self._groups is not None:
+            for g, (l0, l1) in zip(self._groups, self._group_layers):
                 _lib.small_m_group(g, flags=_lib.FLAG_PDL if self.pdl else 0)
+                if self.reduce:
+                    self._allreduce(self.y_rowpar[l0 * self._n_rp:l1 * self._n_rp].view(-1))
             return
         for li, row in enumerate(self.launches):
             for j, (name, pk, st, keep, xname, _) in enumerate(row):

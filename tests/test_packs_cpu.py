@@ -175,3 +175,29 @@ def test_damaged_legacy_blobs_are_refused():
     d["esc_vals"] = d["esc_vals"][:len(d["esc_idx"])] if len(d["esc_vals"]) >= len(d["esc_idx"]) else np.zeros(len(d["esc_idx"]), np.float32)
     with pytest.raises(packs.PackFormatError):
         packs.validate_pack(d)
+
+
+def test_shards_made_from_pack_bytes_restore_to_slices_of_the_whole():
+    """row_shard / column_shard cut a rank's part out of the pack's bytes: no re-encoding, same restored values"""
+    import oracle
+    from qvb8_b200 import fuse
+    from util import pack_np
+    pk = synth.synth_pack(96, 512, 8, tau=2e-3, restore="fp16+bf16")
+    W = oracle.qvb8_dense(pack_np(pk))
+    Wb = oracle.qvb8_dense(pack_np(pk), table="bf16")
+    for r0, r1 in ((0, 24), (24, 96), (40, 41)):
+        sh = fuse.row_shard(pk, r0, r1)
+        assert np.array_equal(oracle.qvb8_dense(pack_np(sh)).view(np.uint32), W[r0:r1].view(np.uint32))
+        assert np.array_equal(oracle.qvb8_dense(pack_np(sh), table="bf16").view(np.uint32), Wb[r0:r1].view(np.uint32))
+    parts = []
+    for c0, c1 in ((0, 128), (128, 256), (256, 512)):
+        sh = fuse.column_shard(pk, c0, c1)
+        assert (sh.Q, sh.P) == (96, c1 - c0)
+        got = oracle.qvb8_dense(pack_np(sh))
+        assert np.array_equal(got.view(np.uint32), W[:, c0:c1].view(np.uint32))
+        parts.append(got)
+        blob = sh.to_blob("QVBD")                                        # a shard is an ordinary pack: it serialises
+        assert packs.read_qvb8(blob)["P"] == c1 - c0
+    assert np.array_equal(np.hstack(parts), W)
+    with pytest.raises(ValueError):
+        fuse.column_shard(pk, 4, 128)
