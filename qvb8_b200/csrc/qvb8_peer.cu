@@ -7,8 +7,11 @@
 // peers' flags, and adds the slots up in rank order: every rank gets bit-identical sums.
 //
 // Memory of a rank (one allocation, shared with the peers through CUDA IPC):
-//   [0, 1024)                       flags[2][world]: flag[b][r] = last epoch whose data rank r has put into buffer b
-//   [1024 + b * world * cap ...)    recv[b][r][cap floats]: the partial sums of rank r for an epoch of parity b
+//   [0, 8192)                       flags[2][world][32 blocks]: flag[b][r][k] = last epoch whose slice k rank r has put
+//                                   into buffer b; one word at the end counts this rank's finished blocks
+//   [8192 + b * world * cap ...)    recv[b][r][cap floats]: the partial sums of rank r for an epoch of parity b
+// A call is cut into up to 32 blocks; block k exchanges slice k of the vector with the peers' blocks k and depends on
+// no other block of its own grid (so the blocks need not be resident together).
 // Two buffers: a rank can run at most one all-reduce ahead of a peer (it needs the peer's flag of the current epoch,
 // which the peer raises only after it has finished reading the previous one).
 //
@@ -20,7 +23,8 @@
 namespace qv {
 
 constexpr int PEER_MAX_WORLD = 16;
-constexpr int PEER_FLAG_BYTES = 1024;
+constexpr int PEER_FLAG_BYTES = 8192;          // flags[2][world][PEER_MAX_BLOCKS] + the blocks-done counter
+constexpr int PEER_MAX_BLOCKS = 32;           // blocks one all-reduce is cut into (each exchanges its own slice)
 constexpr int PEER_THREADS = 1024;
 
 __device__ int g_peer_error = 0;
@@ -41,32 +45,35 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
 }
 
-// One block per rank.  n floats (a multiple of 4), n <= cap.  `partial` and `out` may be the same buffer (every thread
-// reads the elements it later writes), so neither is declared restrict.  wait_ns: how long the wait for the peers'
-// flags may last before it gives up (error word 31); the time limit is what bounds the wait, the iteration cap only
-// guards against a timer that does not advance.
+// Block k of `nblk` handles floats [k * per, min(n, (k + 1) * per)), per a multiple of 4.  n a multiple of 4, n <= cap.
+// `partial` and `out` may be the same buffer (every thread reads the elements it later writes), so neither is declared
+// restrict.  wait_ns: how long the wait for the peers' flags may last before it gives up (error word 31); the time
+// limit is what bounds the wait, the iteration cap only guards against a timer that does not advance.
 __device__ __forceinline__ void peer_allreduce_body(const PeerParams &p, int rank, uint32_t *epoch_ctr, const float *partial,
-                                                    float *out, int n, uint64_t wait_ns) {
+                                                    float *out, int n, uint64_t wait_ns, int k, int nblk) {
     __shared__ uint32_t s_epoch;
     const int tid = threadIdx.x;
-    if (tid == 0) s_epoch = *epoch_ctr + 1u;
+    if (tid == 0) s_epoch = *epoch_ctr + 1u;              // (advanced only after every block of this call has read it)
     __syncthreads();
     const uint32_t epoch = s_epoch;
     const int b = (int)(epoch & 1u);
+    const int per = ((n / 4 + nblk - 1) / nblk) * 4;
+    const int lo = min(n, k * per), hi = min(n, lo + per);
     const int64_t slot = ((int64_t)b * p.world + rank) * p.cap;
-    // 1. push: this rank's partial sums into slot [b][rank] of every rank (its own included)
+    // 1. push: this rank's slice into slot [b][rank] of every rank (its own included)
     const float4 *src = reinterpret_cast<const float4 *>(partial);
     for (int r = 0; r < p.world; ++r) {
         float4 *dst = reinterpret_cast<float4 *>(p.base[r] + PEER_FLAG_BYTES) + (slot >> 2);
-        for (int i = tid; i < (n >> 2); i += PEER_THREADS) dst[i] = src[i];
+        for (int i = (lo >> 2) + tid; i < (hi >> 2); i += PEER_THREADS) dst[i] = src[i];
     }
     __threadfence_system();
     __syncthreads();
-    // 2. flags: tell every rank that this rank's data of this epoch is in place
-    if (tid < p.world) st_release_sys(reinterpret_cast<uint32_t *>(p.base[tid]) + b * PEER_MAX_WORLD + rank, epoch);
-    // 3. wait for every rank's flag in this rank's memory
+    // 2. flags: tell every rank that this rank's slice of this epoch is in place
+    const int fidx = (b * PEER_MAX_WORLD + rank) * PEER_MAX_BLOCKS + k;
+    if (tid < p.world) st_release_sys(reinterpret_cast<uint32_t *>(p.base[tid]) + fidx, epoch);
+    // 3. wait for every rank's flag of this slice in this rank's memory
     if (tid < p.world) {
-        const uint32_t *f = reinterpret_cast<const uint32_t *>(p.base[rank]) + b * PEER_MAX_WORLD + tid;
+        const uint32_t *f = reinterpret_cast<const uint32_t *>(p.base[rank]) + (b * PEER_MAX_WORLD + tid) * PEER_MAX_BLOCKS + k;
         uint64_t t0, t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
         bool ok = false;
@@ -82,7 +89,7 @@ __device__ __forceinline__ void peer_allreduce_body(const PeerParams &p, int ran
     __syncthreads();
     // 4. sum the slots in rank order
     const float4 *rb = reinterpret_cast<const float4 *>(p.base[rank] + PEER_FLAG_BYTES) + (((int64_t)b * p.world * p.cap) >> 2);
-    for (int i = tid; i < (n >> 2); i += PEER_THREADS) {
+    for (int i = (lo >> 2) + tid; i < (hi >> 2); i += PEER_THREADS) {
         float4 a = rb[i];
         for (int r = 1; r < p.world; ++r) {
             const float4 v = rb[(((int64_t)r * p.cap) >> 2) + i];
@@ -90,7 +97,17 @@ __device__ __forceinline__ void peer_allreduce_body(const PeerParams &p, int ran
         }
         reinterpret_cast<float4 *>(out)[i] = a;
     }
-    if (tid == 0) *epoch_ctr = epoch;
+    // 5. the block that finishes last advances the epoch (every block has read it by then)
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t *done = reinterpret_cast<uint32_t *>(p.base[rank] + PEER_FLAG_BYTES - 4);   // (the flags end at byte 4096)
+        __threadfence();
+        if (atomicAdd(done, 1u) == (uint32_t)nblk - 1u) {
+            *done = 0u;
+            __threadfence();
+            *epoch_ctr = epoch;
+        }
+    }
 }
 
 __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const PeerParams p, const float *partial, float *out,
@@ -99,7 +116,7 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const Peer
     // before it reads anything this grid writes); this grid waits for its predecessor before it reads `partial`
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    peer_allreduce_body(p, p.rank, p.epoch, partial, out, n, wait_ns);
+    peer_allreduce_body(p, p.rank, p.epoch, partial, out, n, wait_ns, blockIdx.x, gridDim.x);
 }
 
 // All ranks of a world in ONE cooperative launch on one device, block r = rank r: the protocol exactly as above, for
@@ -113,7 +130,7 @@ struct PeerLocalRanks {
 __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_local_kernel(const PeerParams p, const PeerLocalRanks l, int n,
                                                                             uint64_t wait_ns) {
     const int rank = blockIdx.x;
-    peer_allreduce_body(p, rank, l.epoch[rank], l.partial[rank], l.out[rank], n, wait_ns);
+    peer_allreduce_body(p, rank, l.epoch[rank], l.partial[rank], l.out[rank], n, wait_ns, 0, 1);
 }
 
 int peer_error_word(int *out) {
@@ -144,6 +161,7 @@ QV_API int qvb8_peer_alloc(int64_t bytes, void **ptr, unsigned char handle[64]) 
     if (int rc = check_device("qvb8_peer_alloc")) return rc;
     if (!ptr || !handle || bytes <= 0) return fail(QVB8_ERR_ARG, "qvb8_peer_alloc: bad arguments");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    static_assert(2 * PEER_MAX_WORLD * PEER_MAX_BLOCKS * 4 <= PEER_FLAG_BYTES - 4, "flag area");
     if (cudaMalloc(ptr, (size_t)bytes) != cudaSuccess) return cuda_status("qvb8_peer_alloc");
     if (cudaMemset(*ptr, 0, (size_t)bytes) != cudaSuccess) return cuda_status("qvb8_peer_alloc memset");
     cudaIpcMemHandle_t h;
@@ -201,7 +219,11 @@ QV_API int qvb8_peer_allreduce_ex(void *const *bases, int rank, int world, int64
     if (!aligned(partial, 16) || !aligned(out, 16)) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: partial / out must be 16-byte aligned");
     p.epoch = reinterpret_cast<uint32_t *>(epoch);
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(1);
+    // one block per 16 K floats, at most PEER_MAX_BLOCKS: a decode-sized vector stays one block, the partial sums of
+    // several layers exchanged at once spread over many SMs (one SM's stores would otherwise bound the push)
+    int nblk = (int)((n + 16383) / 16384);
+    if (nblk > PEER_MAX_BLOCKS) nblk = PEER_MAX_BLOCKS;
+    cfg.gridDim = dim3(nblk);
     cfg.blockDim = dim3(PEER_THREADS);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);

@@ -80,3 +80,29 @@ def test_wait_for_an_absent_peer_runs_out(cuda_lib):
     _lib.check(L.qvb8_device_status_reset(), "qvb8_device_status_reset")
     assert _lib.device_status(DEV) == 0
     assert float((part * 2).sum()) == 2.0 * n                          # the context still computes
+
+
+def test_multi_block_exchange_in_one_process(cuda_lib):
+    """a vector long enough to be cut into many blocks, rank 0 and rank 1 of a world of two as two launches that do
+    NOT wait on one another: each rank's call is made with the peer's slices and flags already in place (written here
+    by a helper call of the peer rank into scratch areas), so no launch ever waits for a later one"""
+    L = cuda_lib
+    world, n, cap = 2, 131072, 131072
+    areas, epochs = _areas(L, world, cap)
+    g = torch.Generator().manual_seed(5)
+    parts = [torch.randn(n, generator=g).to(DEV) for _ in range(world)]
+    outs = [torch.empty(n, device=DEV) for _ in range(world)]
+    # rank 1 first: its wait for rank 0's flags runs out after 1 ms (nothing has set them yet) -- but its pushes and
+    # flags are now in both areas; then rank 0 finds everything it waits for and returns the full sum
+    with torch.cuda.device(DEV):
+        _lib.check(L.qvb8_peer_allreduce_ex(_ptrs(areas), 1, world, cap, epochs[1].data_ptr(), parts[1].data_ptr(),
+                                            outs[1].data_ptr(), n, 0, 1_000_000, _lib.stream_ptr(torch.device(DEV))), "rank 1")
+        torch.cuda.synchronize()
+        assert _lib.device_status(DEV) == 31
+        _lib.check(L.qvb8_device_status_reset(), "reset")
+        _lib.check(L.qvb8_peer_allreduce_ex(_ptrs(areas), 0, world, cap, epochs[0].data_ptr(), parts[0].data_ptr(),
+                                            outs[0].data_ptr(), n, 0, 0, _lib.stream_ptr(torch.device(DEV))), "rank 0")
+    torch.cuda.synchronize()
+    assert _lib.device_status(DEV) == 0
+    assert torch.equal(outs[0], parts[0] + parts[1])
+    assert int(epochs[0].item()) == 1 and int(epochs[1].item()) == 1
