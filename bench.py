@@ -561,7 +561,7 @@ def main():
     if world > 1:
         dist.barrier()
     # The timed block is exactly --steps steps between two CUDA events.  A block of a few dozen milliseconds is too
-    # short to judge clocks by, so blocks are repeated until about a second has passed (the same number on every rank)
+    # short to read clocks by, so blocks are repeated until about a second has passed (the same number on every rank)
     # and the MEDIAN block is reported, with the spread and the clock samples of the whole second.
     block_ms = []
     with ClockSampler(local) as clocks:

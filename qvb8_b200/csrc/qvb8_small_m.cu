@@ -20,20 +20,32 @@
 //
 // Roofline: HBM.  Per weight the kernel moves nbits/8 bytes (about 0.8).  What HBM sees matters as much as how
 // much: a row is a contiguous byte range, so for each of the 16 rows of a tile a producer warp fetches ONE
-// contiguous run of 512 columns (384 - 512 bytes) per stage with a bulk asynchronous copy (cp.async.bulk, completion
-// counted on an mbarrier), several stages ahead; the tile's descriptor travels with its first stage.  CTAs are
-// persistent: a CTA keeps one K-range (its activations stay staged in shared memory as fp16, in fragment order) and
-// walks every (gridDim.x)-th tile, so the copy stream never drains between tiles.
+// contiguous run of columns per stage with a bulk asynchronous copy (cp.async.bulk with an evict-first L2 hint,
+// completion counted on an mbarrier), several stages ahead; the tile's descriptor travels with its first stage.
+// CTAs are persistent and hold up to four independent PIPES (producer warp + four consumer warps + finishing warp
+// each, own rings and barriers), so a stall in one pipe's hand-over does not idle the SM's copy stream.
 //
 // Math.  Four consumer warps each take one 128-column chunk of the stage.  Thread (g = lane / 4, t = lane % 4) owns
 // the 32 ids of rows g and g + 8 that start at column 32 t -- exactly nb 32-bit words -- and turns them into the A
 // fragments of eight m16n8k16 MMAs.  Two ids are converted per instruction: a funnel shift puts one id in the low
 // half-word and one in the high half-word of a register, `(r & mask) | 0x64006400` makes the two fp16 numbers
 // 1024 + id * 2^e, and one HFMA2 removes the 1024 and the 2^e exactly.  At the end of a tile the warps hand their
-// partial accumulators to a sixth, finishing warp through shared memory and go on streaming; the finishing warp adds
-// them in warp order, applies min_s / tau_s, adds the escape corrections it has summed meanwhile (per row, in
-// stored order) and writes the result.  K-ranges of one tile are added in range order by whichever CTA finishes the
-// tile last (a ticket counter per tile).  Every sum has a fixed order: results are identical from run to run.
+// partial accumulators to the pipe's finishing warp through a double-buffered area of shared memory and go on
+// streaming; the finishing warp adds them in warp order, applies min_s / tau_s and the per-token sum of X (collected
+// while X was staged), adds the escape corrections, and writes the result.  K-ranges of one tile are added in range
+// order by whichever CTA finishes the tile last (a ticket counter per tile).
+//
+// Lists.  One launch can run up to 32 independent products (qvb8_small_m_group): the job table travels by value in
+// the kernel's parameters.  All (tile, stage) units of the list form ONE sequence that is cut into equal contiguous
+// per-CTA ranges, so a CTA meets one or two jobs per launch and its rings never drain at a job boundary; at a
+// boundary the consumer warps restage X for the next job from global memory while the producer is already copying
+// that job's first stages.  Rarely executed serial work is expensive on an SM whose other warps stream (a dependent
+// chain costs on the order of 100 cycles per instruction there), so for lists the escape corrections run in a
+// pre-pass kernel, one thread per (tile, row), that writes them into Y; the streaming kernel then adds its result
+// to Y with one atomic add per element -- one writer per element after the ticket, so the sum order stays fixed.
+//
+// Every sum has a fixed order: results are identical from run to run.  A list agrees with separate calls to fp32
+// rounding (the grouping of the K partial sums differs), not bit for bit.
 //
 // Waits.  Every wait on an mbarrier is bounded: after two seconds (or SPIN_LIMIT polls) the waiter raises a per-CTA
 // abort flag and a device-wide error word (qvb8_device_status), every other waiter gives up too, and the kernel

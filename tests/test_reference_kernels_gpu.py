@@ -178,7 +178,7 @@ def _time_us(fn, reps=20, warm=3):
 
 def test_timing_table(cuda_lib, ref8):
     """per-call microseconds of both sides (L2 flushed between calls, CUDA events, Python call overhead included on
-    both); written to gpurun_out/reference_kernel_times.json when that folder exists"""
+    both); also written to $QVB8_RESULTS_DIR/reference_kernel_times.json when that variable names a folder"""
     rows = []
     shapes = [("q+k+v 9B", 6144, 4096), ("o 9B", 4096, 4096), ("gate+up 9B", 24576, 4096), ("down 9B", 4096, 12288),
               ("gate+up 65B", 57344, 8192)]
@@ -200,8 +200,8 @@ def test_timing_table(cuda_lib, ref8):
         del pk
     for r in rows:
         print(r)
-    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(out):
+    out = os.environ.get("QVB8_RESULTS_DIR", "")
+    if out and os.path.isdir(out):
         with open(os.path.join(out, "reference_kernel_times.json"), "w") as fh:
             json.dump(rows, fh, indent=1)
     assert all(r["this_us"] > 0 and r["reference_us"] > 0 for r in rows)
