@@ -168,47 +168,151 @@ def run_reference_arm(args, cfg):
 def run_moe(args):
     """One mixture-of-experts layer of the 35B-A3B-class configuration: 128 experts, top-8 routing from a seeded
     softmax over N(0, 1) logits, d_model 2048, expert FFN 768, QVB8 tau = 1e-3 with the outliers kept in band (expert
-    stacks carry no escapes).  Metric: bytes of the DISTINCT selected experts' gate_up and down packs per second."""
-    from qvb8_b200 import experts, synth
-    dev = torch.device("cuda", 0)
+    stacks carry no escapes).  Metric: bytes of the DISTINCT selected experts' gate_up and down packs per second.
+    N > 1: expert parallelism -- rank r holds experts [r E/N, (r+1) E/N), every rank sees all tokens and the routing,
+    the fp32 partial outputs are all-reduced by the push kernel over peer memory (strong scaling: one layer's work is
+    split)."""
+    from qvb8_b200 import experts, lib, synth
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
     E, topk, d, f, M = 128, 8, 2048, 768, args.rows
-    ups = [synth.encode_qvb8(synth.synth_weight(2 * f, d, 4000 + e, device=dev), tau=1e-3, policy="inband") for e in range(E)]
-    dns = [synth.encode_qvb8(synth.synth_weight(d, f, 5000 + e, device=dev), tau=1e-3, policy="inband") for e in range(E)]
-    per_expert = [u.weight_bytes() + v.weight_bytes() for u, v in zip(ups, dns)]
-    mod = experts.QVBandExpertsV8(ups, dns, num_experts=E)
+    if E % world:
+        raise SystemExit(f"bench.py: {E} experts do not split over {world} ranks")
+    per = E // world
+    mine = range(rank * per, (rank + 1) * per)
+    ups = [synth.encode_qvb8(synth.synth_weight(2 * f, d, 4000 + e, device=dev), tau=1e-3, policy="inband") for e in mine]
+    dns = [synth.encode_qvb8(synth.synth_weight(d, f, 5000 + e, device=dev), tau=1e-3, policy="inband") for e in mine]
+    per_expert = torch.zeros(E, dtype=torch.int64, device=dev)
+    per_expert[rank * per:(rank + 1) * per] = torch.tensor([u.weight_bytes() + v.weight_bytes() for u, v in zip(ups, dns)],
+                                                           device=dev)
+    if world > 1:
+        dist.all_reduce(per_expert)
+    per_expert = per_expert.tolist()
+    mod = experts.QVBandExpertsV8(ups, dns, num_experts=per, first_expert=rank * per, total_experts=E)
+    sample = (ups[:], dns[:]) if rank == 0 else None             # the CPU baseline restores a few of these below
     del ups, dns
+    exchange = None
+    if world > 1:
+        from qvb8_b200.peer import PeerAllReduce
+        peer = PeerAllReduce(dist.group.WORLD, M * d, dev)
+        probe = torch.randn(M * d, device=dev, generator=torch.Generator(device=dev).manual_seed(rank))
+        got, ref = peer.allreduce(probe.clone()), probe.clone()
+        dist.all_reduce(ref)
+        ok = torch.tensor([int(torch.allclose(got, ref, rtol=1e-5, atol=1e-5))], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1 and (M * d) % 4 == 0:
+            mod.set_reduce(lambda t: peer.allreduce(t.view(-1)).view_as(t))
+            exchange = "peer push all-reduce (checked against NCCL)"
+        else:
+            mod.set_reduce(lambda t: dist.all_reduce(t))
+            exchange = "nccl all-reduce"
     g = torch.Generator(device="cpu").manual_seed(11)
     w, idx = torch.topk(torch.softmax(torch.randn(M, E, generator=g), -1), topk, dim=-1)
-    idx, w = idx.to(dev), (w / w.sum(-1, keepdim=True)).float().to(dev)
+    w = (w / w.sum(-1, keepdim=True)).float()
     X = synth.synth_activation(M, d, seed=7, device=dev)
+    host = [X.cpu().pin_memory(), idx.pin_memory(), w.pin_memory()]
+    idx_d, w_d = idx.to(dev), w.to(dev)
     distinct = sorted(set(idx.flatten().tolist()))
     nbytes = sum(per_expert[e] for e in distinct)
-    for _ in range(max(3, args.warmup)):
-        mod(X, idx, w)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()                              # the four launches of the layer, replayed
-    with torch.cuda.graph(graph):
-        out = mod(X, idx, w)
+    warm = max(3, args.warmup)
+    s = torch.cuda.Stream(dev)
+    with torch.cuda.stream(s):
+        for _ in range(warm):
+            mod(X, idx_d, w_d)
+    s.synchronize()
+    graph = torch.cuda.CUDAGraph()                              # the launches of the layer (+ the exchange), replayed
+    with torch.cuda.graph(graph, stream=s, capture_error_mode="thread_local"):
+        out = mod(X, idx_d, w_d)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    with ClockSampler(0) as clocks:
+    barrier()
+    with ClockSampler(local) as clocks:
         for a, b in ev:
             flush.zero_()                                     # the selected experts (<= 250 MB) would otherwise sit in L2
             a.record(); graph.replay(); b.record()
-        torch.cuda.synchronize()
+        barrier()
     ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
+    # end to end: activations, routing and weights from pinned host memory, the layer's output back to the host
+    out_host = torch.empty_like(out, device="cpu").pin_memory()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        X.copy_(host[0], non_blocking=True); idx_d.copy_(host[1], non_blocking=True); w_d.copy_(host[2], non_blocking=True)
+        graph.replay()
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    status = lib.device_status(dev)
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+    # CPU baseline on a bounded sample: restore the first token's experts that rank 0 holds (C restatement of the
+    # reference decoder) and run the expert MLP on them in numpy
+    import numpy as np
+    import oracle
+
+    def pack_np(pk):
+        c = lambda t: t.detach().cpu().numpy()
+        return dict(Q=pk.Q, P=pk.P, ids=c(pk.ids), nbits=c(pk.nbits), bit_off=c(pk.bit_off), min_s=c(pk.min_s),
+                    tau_s=c(pk.tau_s), esc_idx=c(pk.esc_idx), esc_vals=c(pk.esc_vals))
+    chosen = [e for e in idx[0].tolist() if e < per][:4] or [0]
+    host_packs = [(pack_np(sample[0][e]), pack_np(sample[1][e])) for e in chosen]
+    t0, reps = time.perf_counter(), 0
+    while time.perf_counter() - t0 < min(args.cpu_seconds, 10.0):
+        upd = np.stack([oracle.qvb8_dense(u) for u, _ in host_packs])
+        dnd = np.stack([oracle.qvb8_dense(v) for _, v in host_packs])
+        oracle.moe_experts(X[:1].float().cpu().numpy(), np.arange(len(chosen))[None, :],
+                           np.full((1, len(chosen)), 1.0 / len(chosen), np.float32), upd, dnd)
+        reps += 1
+    cpu_s = (time.perf_counter() - t0) / reps
+    cpu_gbs = sum(per_expert[e] for e in chosen) / cpu_s / 1e9
     peak, peak_kind = measured_peaks()
     gbs = nbytes / (ms * 1e-3) / 1e9
+    launches = 4 + (1 if world > 1 else 0)
     print(json.dumps({
-        "metric": "moe_distinct_expert_bytes_per_s", "value": gbs, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": "moe_distinct_expert_bytes_per_s", "value": gbs, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"35B-A3B-class expert layer, E={E}, top-{topk}, d_model {d}, expert FFN {f}, M={M} tokens",
-                   "distinct_experts": len(distinct), "bytes": nbytes, "l2": "256 MB written between steps"},
-        "clocks": clocks.summary(), "gpu_launches": 4 * args.steps,
-        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
-                     "peak_kind": peak_kind, "kernel": "moe_rows_kernel"}}), flush=True)
+                   "distinct_experts": len(distinct), "bytes": nbytes, "l2": "256 MB written between steps",
+                   "parallelism": (f"experts split {per} per rank x{world}, tokens and routing replicated, fp32 partial "
+                                   f"outputs exchanged by one {exchange} per layer") if world > 1 else "single GPU",
+                   "device_status": status},
+        "clocks": clocks.summary(), "gpu_launches": launches * args.steps,
+        "e2e": {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host),
+                "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
+        "roofline": {"bound": "hbm", "achieved": gbs * (1.0 / world), "peak": peak, "unit": "GB/s",
+                     "frac": gbs / world / peak, "traffic": None, "peak_kind": peak_kind, "kernel": "moe_rows_kernel",
+                     "note": "per GPU: distinct-expert bytes of the layer / ranks / step time"},
+        "cpu_baseline": {"value": cpu_gbs, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                         "sample": f"{len(chosen)} experts of the first token: restore gate_up and down (C restatement "
+                                   f"of the reference decoder) + the expert MLP in numpy, {reps} repetitions in "
+                                   f"{cpu_s * reps:.1f} s"}}), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def run_prefill(args):
@@ -478,6 +582,9 @@ def main():
     ap.add_argument("--group-layers", type=int, default=-1,
                     help="layers whose projections run behind one launch (0 = one launch per projection; "
                          "-1 = default: 8)")
+    ap.add_argument("--shard", default="auto", choices=["auto", "pairs", "rows"],
+                    help="N > 1: column/row-parallel pairs + all-reduce, or every projection by output rows + all-gather "
+                         "(auto: rows below 8 activation rows, where the full-length rows stream faster; pairs from 8)")
     ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: NCCL all-reduce instead of the peer push kernel")
     ap.add_argument("--no-alt-policy", action="store_true", help="skip the second measurement with the in-band encoder policy")
     args = ap.parse_args()
@@ -516,8 +623,11 @@ def main():
     from qvb8_b200 import lib
     lib.load()
     t_build = time.perf_counter()
+    shard = args.shard if args.shard != "auto" else ("rows" if args.rows < 8 else "pairs")
+    if world == 1:
+        shard = "pairs"
     st = S.LinearStack(cfg, args.rows, dev, layers=args.layers, rank=rank, world=world, policy=args.policy,
-                       fuse_same_input=not args.no_fuse)
+                       fuse_same_input=not args.no_fuse, shard=shard)
     torch.cuda.synchronize(dev)
     t_build = time.perf_counter() - t_build
 
@@ -529,12 +639,23 @@ def main():
         if not args.nccl_allreduce:
             try:
                 st.enable_collectives(peer=True)
-                probe = torch.randn(args.rows * cfg.d_model, device=dev, generator=torch.Generator(device=dev).manual_seed(rank))
-                mine = st.peer.allreduce(probe.clone())
-                ref = probe.clone()
-                dist.all_reduce(ref)
-                torch.cuda.synchronize(dev)
-                ok = torch.tensor([1 if torch.allclose(mine, ref, rtol=1e-5, atol=1e-5) else 0], device=dev)
+                # two sizes: one (M, d_model) block and the largest exchange of a list launch (several blocks of the
+                # push kernel), each twice so that both flag parities are used
+                good = True
+                for numel in (args.rows * cfg.d_model, st.peer.cap, st.peer.cap, args.rows * cfg.d_model):
+                    probe = torch.randn(numel, device=dev, generator=torch.Generator(device=dev).manual_seed(rank + numel))
+                    mine = st.peer.allreduce(probe.clone())
+                    ref = probe.clone()
+                    dist.all_reduce(ref)
+                    torch.cuda.synchronize(dev)
+                    good = good and bool(torch.allclose(mine, ref, rtol=1e-5, atol=1e-5))
+                    got = st.peer.allgather(probe, torch.empty(world * numel, device=dev))
+                    want = torch.empty(world * numel, device=dev)
+                    dist.all_gather_into_tensor(want, probe)
+                    torch.cuda.synchronize(dev)
+                    good = good and bool(torch.equal(got, want))
+                good = good and lib.device_status() == 0
+                ok = torch.tensor([1 if good else 0], device=dev)
                 dist.all_reduce(ok, op=dist.ReduceOp.MIN)
                 if int(ok.item()) == 1:
                     allreduce_kind = "peer push kernel (checked against NCCL)"
@@ -660,8 +781,12 @@ def main():
             "weights": total_weights, "compressed_bytes": total_bytes,
             "bits_per_weight": 8.0 * total_bytes / max(1, total_weights),
             "row_width_hist": {str(k): v for k, v in sorted(st.width_hist.items())}, "escapes": st.n_escapes,
-            "parallelism": (f"column/row-parallel pairs x{world}; the partial sums of o and down are exchanged by "
-                            f"{'one all-reduce per launch' if st._groups else 'two all-reduces per layer'} ({allreduce_kind})")
+            "parallelism": ((f"column/row-parallel pairs x{world}; the partial sums of o and down are exchanged by "
+                             f"{'one all-reduce per launch' if st._groups else 'two all-reduces per layer'} ({allreduce_kind})")
+                            if shard == "pairs" else
+                            (f"every projection split by output rows x{world}; each rank's slices of the o and down outputs "
+                             f"and of their inputs are exchanged by one all-gather per "
+                             f"{'launch' if st._groups else 'layer'} ({allreduce_kind})"))
                            if world > 1 else "single GPU",
             "l2": "working set (packs) far larger than L2; every step streams all of it",
             "tokens_per_s": 1e3 / ms_step * args.rows, "pack_build_s": round(t_build, 1),

@@ -198,6 +198,15 @@ int qvb8_peer_allreduce_ex(void *const *bases, int rank, int world, int64_t cap_
  * carry no guarantee of running together, the blocks of a cooperative launch do. */
 int qvb8_peer_allreduce_local(void *const *bases, int world, int64_t cap_floats, void *const *epochs,
                               const float *const *partials, float *const *outs, int64_t n, uint64_t wait_ns, void *stream);
+/* All-gather by the same push protocol, for a linear that is split across cards by output rows only (the reference's
+ * row_subset, formats/qvb8/module.py:126-160): out[r * n .. (r + 1) * n) = rank r's part[0 .. n), identical on every
+ * rank.  `out` holds world * n floats and does not overlap `part`; n % 4 == 0, n <= cap_floats.  All-gathers and
+ * all-reduces may be mixed on one communicator (they share the exchange area and the epoch counter).  wait_ns as for
+ * qvb8_peer_allreduce_ex.  qvb8_peer_allgather_local: every rank on one device, as qvb8_peer_allreduce_local. */
+int qvb8_peer_allgather(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *part,
+                        float *out, int64_t n, int flags, uint64_t wait_ns, void *stream);
+int qvb8_peer_allgather_local(void *const *bases, int world, int64_t cap_floats, void *const *epochs,
+                              const float *const *parts, float *const *outs, int64_t n, uint64_t wait_ns, void *stream);
 
 /* ---- mixture-of-experts MLP over stacked expert packs -------------------------------------------------------------
  * Stacked layout of one projection of all E experts (reference formats/qvb8/backends_experts.py:144-196): every

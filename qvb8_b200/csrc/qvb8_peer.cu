@@ -50,7 +50,8 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
 // restrict.  wait_ns: how long the wait for the peers' flags may last before it gives up (error word 31); the time
 // limit is what bounds the wait, the iteration cap only guards against a timer that does not advance.
 __device__ __forceinline__ void peer_allreduce_body(const PeerParams &p, int rank, uint32_t *epoch_ctr, const float *partial,
-                                                    float *out, int n, uint64_t wait_ns, int k, int nblk) {
+                                                    float *out, int n, uint64_t wait_ns, int k, int nblk,
+                                                    bool gather = false) {
     __shared__ uint32_t s_epoch;
     const int tid = threadIdx.x;
     if (tid == 0) s_epoch = *epoch_ctr + 1u;              // (advanced only after every block of this call has read it)
@@ -62,7 +63,8 @@ __device__ __forceinline__ void peer_allreduce_body(const PeerParams &p, int ran
     const int64_t slot = ((int64_t)b * p.world + rank) * p.cap;
     // 1. push: this rank's slice into slot [b][rank] of every rank (its own included)
     const float4 *src = reinterpret_cast<const float4 *>(partial);
-    for (int r = 0; r < p.world; ++r) {
+    for (int j = 0; j < p.world; ++j) {
+        const int r = (rank + j) % p.world;               // every rank starts with another peer
         float4 *dst = reinterpret_cast<float4 *>(p.base[r] + PEER_FLAG_BYTES) + (slot >> 2);
         for (int i = (lo >> 2) + tid; i < (hi >> 2); i += PEER_THREADS) dst[i] = src[i];
     }
@@ -87,8 +89,15 @@ __device__ __forceinline__ void peer_allreduce_body(const PeerParams &p, int ran
         if (!ok) atomicCAS(&g_peer_error, 0, 31);
     }
     __syncthreads();
-    // 4. sum the slots in rank order
+    // 4. sum the slots in rank order (all-gather: lay them side by side, rank r's n floats at out[r * n])
     const float4 *rb = reinterpret_cast<const float4 *>(p.base[rank] + PEER_FLAG_BYTES) + (((int64_t)b * p.world * p.cap) >> 2);
+    if (gather) {
+        for (int r = 0; r < p.world; ++r) {
+            const float4 *from = rb + (((int64_t)r * p.cap) >> 2);
+            float4 *to = reinterpret_cast<float4 *>(out) + (((int64_t)r * n) >> 2);
+            for (int i = (lo >> 2) + tid; i < (hi >> 2); i += PEER_THREADS) to[i] = from[i];
+        }
+    } else
     for (int i = (lo >> 2) + tid; i < (hi >> 2); i += PEER_THREADS) {
         float4 a = rb[i];
         for (int r = 1; r < p.world; ++r) {
@@ -111,12 +120,12 @@ __device__ __forceinline__ void peer_allreduce_body(const PeerParams &p, int ran
 }
 
 __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const PeerParams p, const float *partial, float *out,
-                                                                      int n, uint64_t wait_ns) {
+                                                                      int n, uint64_t wait_ns, int gather) {
     // programmatic dependent launch: the next kernel may begin its prologue now (it waits for this grid's completion
     // before it reads anything this grid writes); this grid waits for its predecessor before it reads `partial`
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    peer_allreduce_body(p, p.rank, p.epoch, partial, out, n, wait_ns, blockIdx.x, gridDim.x);
+    peer_allreduce_body(p, p.rank, p.epoch, partial, out, n, wait_ns, blockIdx.x, gridDim.x, gather != 0);
 }
 
 // All ranks of a world in ONE cooperative launch on one device, block r = rank r: the protocol exactly as above, for
@@ -128,9 +137,9 @@ struct PeerLocalRanks {
     uint32_t *epoch[PEER_MAX_WORLD];
 };
 __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_local_kernel(const PeerParams p, const PeerLocalRanks l, int n,
-                                                                            uint64_t wait_ns) {
+                                                                            uint64_t wait_ns, int gather) {
     const int rank = blockIdx.x;
-    peer_allreduce_body(p, rank, l.epoch[rank], l.partial[rank], l.out[rank], n, wait_ns, 0, 1);
+    peer_allreduce_body(p, rank, l.epoch[rank], l.partial[rank], l.out[rank], n, wait_ns, 0, 1, gather != 0);
 }
 
 int peer_error_word(int *out) {
@@ -209,9 +218,9 @@ static int peer_fill(PeerParams &p, void *const *bases, int rank, int world, int
 }
 }  // namespace qv
 
-QV_API int qvb8_peer_allreduce_ex(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch,
-                                  const float *partial, float *out, int64_t n, int flags, uint64_t wait_ns, void *stream) {
-    using namespace qv;
+namespace qv {
+static int peer_exchange(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
+                         float *out, int64_t n, int flags, uint64_t wait_ns, void *stream, int gather) {
     if (int rc = check_device("qvb8_peer_allreduce")) return rc;
     if (!epoch || !partial || !out) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: bad arguments");
     PeerParams p{};
@@ -219,9 +228,10 @@ QV_API int qvb8_peer_allreduce_ex(void *const *bases, int rank, int world, int64
     if (!aligned(partial, 16) || !aligned(out, 16)) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce: partial / out must be 16-byte aligned");
     p.epoch = reinterpret_cast<uint32_t *>(epoch);
     cudaLaunchConfig_t cfg{};
-    // one block per 16 K floats, at most PEER_MAX_BLOCKS: a decode-sized vector stays one block, the partial sums of
-    // several layers exchanged at once spread over many SMs (one SM's stores would otherwise bound the push)
-    int nblk = (int)((n + 16383) / 16384);
+    // one block per 4 K floats (one 16-byte store per thread and peer), at most PEER_MAX_BLOCKS: a decode-sized vector
+    // stays one block, the partial sums of several layers exchanged at once spread over many SMs (one SM's stores
+    // would otherwise bound the push)
+    int nblk = (int)((n + 4095) / 4096);
     if (nblk > PEER_MAX_BLOCKS) nblk = PEER_MAX_BLOCKS;
     cfg.gridDim = dim3(nblk);
     cfg.blockDim = dim3(PEER_THREADS);
@@ -232,9 +242,24 @@ QV_API int qvb8_peer_allreduce_ex(void *const *bases, int rank, int world, int64
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & QVB8_FLAG_PDL) ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, p, partial, out, (int)n, wait_ns ? wait_ns : PEER_WAIT_NS) != cudaSuccess)
+    if (cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, p, partial, out, (int)n, wait_ns ? wait_ns : PEER_WAIT_NS, gather) !=
+        cudaSuccess)
         return cuda_status("qvb8_peer_allreduce launch");
     return cuda_status("qvb8_peer_allreduce");
+}
+}  // namespace qv
+
+QV_API int qvb8_peer_allreduce_ex(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch,
+                                  const float *partial, float *out, int64_t n, int flags, uint64_t wait_ns, void *stream) {
+    return qv::peer_exchange(bases, rank, world, cap_floats, epoch, partial, out, n, flags, wait_ns, stream, 0);
+}
+
+/* All-gather with the same protocol: out[r * n .. (r + 1) * n) = rank r's part[0 .. n), identical on every rank.  `out`
+ * holds world * n floats and must not overlap `part`.  The two kinds of exchange may be mixed on one communicator (they
+ * share the epoch counter); every rank must make the same sequence of calls. */
+QV_API int qvb8_peer_allgather(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *part,
+                               float *out, int64_t n, int flags, uint64_t wait_ns, void *stream) {
+    return qv::peer_exchange(bases, rank, world, cap_floats, epoch, part, out, n, flags, wait_ns, stream, 1);
 }
 
 QV_API int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t cap_floats, void *epoch, const float *partial,
@@ -246,10 +271,10 @@ QV_API int qvb8_peer_allreduce(void *const *bases, int rank, int world, int64_t 
  * partials[r], outs[r] are rank r's exchange area, epoch counter, input and output, all in this device's memory.  For
  * machines with fewer GPUs than ranks: kernels that wait on one another must not run as separate launches on one
  * GPU, the blocks of a cooperative launch may. */
-QV_API int qvb8_peer_allreduce_local(void *const *bases, int world, int64_t cap_floats, void *const *epochs,
-                                     const float *const *partials, float *const *outs, int64_t n, uint64_t wait_ns,
-                                     void *stream) {
-    using namespace qv;
+namespace qv {
+static int peer_exchange_local(void *const *bases, int world, int64_t cap_floats, void *const *epochs,
+                               const float *const *partials, float *const *outs, int64_t n, uint64_t wait_ns, void *stream,
+                               int gather) {
     if (int rc = check_device("qvb8_peer_allreduce_local")) return rc;
     if (!epochs || !partials || !outs) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce_local: bad arguments");
     PeerParams p{};
@@ -268,9 +293,23 @@ QV_API int qvb8_peer_allreduce_local(void *const *bases, int world, int64_t cap_
     if (!coop) return fail(QVB8_ERR_ARG, "qvb8_peer_allreduce_local: the device has no cooperative launch");
     int nn = (int)n;
     uint64_t wn = wait_ns ? wait_ns : PEER_WAIT_NS;
-    void *args[] = {&p, &l, &nn, &wn};
+    void *args[] = {&p, &l, &nn, &wn, &gather};
     if (cudaLaunchCooperativeKernel((const void *)peer_allreduce_local_kernel, dim3(world), dim3(PEER_THREADS), args, 0,
                                     reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess)
         return cuda_status("qvb8_peer_allreduce_local launch");
     return cuda_status("qvb8_peer_allreduce_local");
+}
+}  // namespace qv
+
+QV_API int qvb8_peer_allreduce_local(void *const *bases, int world, int64_t cap_floats, void *const *epochs,
+                                     const float *const *partials, float *const *outs, int64_t n, uint64_t wait_ns,
+                                     void *stream) {
+    return qv::peer_exchange_local(bases, world, cap_floats, epochs, partials, outs, n, wait_ns, stream, 0);
+}
+
+/* The all-gather of every rank of a `world` on one device, as qvb8_peer_allreduce_local does for the all-reduce. */
+QV_API int qvb8_peer_allgather_local(void *const *bases, int world, int64_t cap_floats, void *const *epochs,
+                                     const float *const *parts, float *const *outs, int64_t n, uint64_t wait_ns,
+                                     void *stream) {
+    return qv::peer_exchange_local(bases, world, cap_floats, epochs, parts, outs, n, wait_ns, stream, 1);
 }

@@ -45,10 +45,22 @@ def stack_packs(members: list[QVB8Pack]) -> dict:
 class QVBandExpertsV8(torch.nn.Module):
     """Expert MLP stack over stacked QVB8 packs (fused path of the reference module, backends_experts.py:216-226).
 
-    act: "silu" (gated: the up stack is gate_up with 2 I rows) or "relu2" (non-gated, qvb8_cuda.cu:994-1000)."""
+    act: "silu" (gated: the up stack is gate_up with 2 I rows) or "relu2" (non-gated, qvb8_cuda.cu:994-1000).
 
-    def __init__(self, up_packs: list[QVB8Pack], down_packs: list[QVB8Pack], *, num_experts: int, act: str = "silu"):
+    Expert parallelism (several devices): a rank holds the experts [first_expert, first_expert + num_experts) of a
+    layer with `total_experts`; every rank sees all tokens and the full routing.  ``forward`` renumbers the routing to
+    the local stack -- pairs routed to other ranks' experts fall outside it and contribute zero, which the kernels
+    guarantee -- computes in fp32, and hands the partial (M, d_model) sums to ``reduce`` (an all-reduce over the ranks,
+    set with :meth:`set_reduce`); the result is cast back to the activations' type."""
+
+    def __init__(self, up_packs: list[QVB8Pack], down_packs: list[QVB8Pack], *, num_experts: int, act: str = "silu",
+                 first_expert: int = 0, total_experts: int | None = None):
         super().__init__()
+        self.first_expert = int(first_expert)
+        self.total_experts = int(total_experts) if total_experts is not None else int(num_experts)
+        if self.first_expert < 0 or self.first_expert + int(num_experts) > self.total_experts:
+            raise ValueError("the local experts must lie inside [0, total_experts)")
+        self.reduce = None
         if len(up_packs) != num_experts:
             raise ValueError(f"expected {num_experts} up-projection experts, got {len(up_packs)}")
         if len(down_packs) != num_experts:
@@ -61,9 +73,27 @@ class QVBandExpertsV8(torch.nn.Module):
         if hidden != self.down["P"] or self.up["P"] != self.down["Q"]:
             raise ValueError("up and down expert shapes disagree")
 
+    @property
+    def sharded(self) -> bool:
+        return self.total_experts != self.num_experts
+
+    def set_reduce(self, fn) -> None:
+        """fn(t) sums the fp32 tensor t over the ranks in place (or returns the sum); None = no exchange."""
+        self.reduce = fn
+
     def forward(self, hidden_states: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor):
         u, d = self.up, self.down
         fn = ext_qvb8.ext.moe_experts if self.act == "silu" else ext_qvb8.ext.moe_experts_relu2
-        return fn(hidden_states.contiguous(), top_k_index.contiguous(), top_k_weights.float(),
-                  u["ids"], u["min_s"], u["tau_s"], u["nbits"], u["bit_off"], u["Q"], u["P"],
-                  d["ids"], d["min_s"], d["tau_s"], d["nbits"], d["bit_off"], d["Q"], d["P"])
+        x, idx = hidden_states.contiguous(), top_k_index.contiguous()
+        if self.sharded:
+            x = x.float()                                   # partial sums leave the kernels in fp32
+            idx = idx - self.first_expert                   # other ranks' experts: outside [0, E), contribute zero
+        out = fn(x, idx, top_k_weights.float(),
+                 u["ids"], u["min_s"], u["tau_s"], u["nbits"], u["bit_off"], u["Q"], u["P"],
+                 d["ids"], d["min_s"], d["tau_s"], d["nbits"], d["bit_off"], d["Q"], d["P"])
+        if self.sharded:
+            if self.reduce is not None:
+                r = self.reduce(out)
+                out = out if r is None else r
+            out = out.to(hidden_states.dtype)
+        return out

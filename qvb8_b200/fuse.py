@@ -4,8 +4,9 @@ The reference does this for its entropy-coded format (formats/qvb8r/fuse.py:1-60
 into one virtual tensor, every kernel path runs unchanged on it, the output is split back per member).  A QVB8 pack
 concatenates even more simply, because its rows are independent: the bit-packed rows are laid back to back, the
 per-row vectors are concatenated, row bit offsets are shifted by the bits that precede them, and escape positions
-by the rows that precede them.  Each row's sum is computed exactly as in the separate launch, so the fused output is
-bit-identical to the members' outputs side by side.
+by the rows that precede them.  Each row's weights, band and escapes are the same bytes; the fused output equals the
+members' outputs side by side bit for bit whenever the launches cut K into the same ranges (a taller pack may be given
+fewer K-ranges, which changes the order of the fp32 partial sums and nothing else).
 """
 from __future__ import annotations
 

@@ -27,7 +27,7 @@ EXPORTS = (
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
     "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
     "qvb8_embed_rows", "qvb8_peer_bytes", "qvb8_peer_alloc", "qvb8_peer_open", "qvb8_peer_close", "qvb8_peer_allreduce",
-    "qvb8_peer_allreduce_ex", "qvb8_peer_allreduce_local", "qvb8_device_status_reset", "qvb8r_embed_rows",
+    "qvb8_peer_allreduce_ex", "qvb8_peer_allreduce_local", "qvb8_peer_allgather", "qvb8_peer_allgather_local", "qvb8_device_status_reset", "qvb8r_embed_rows",
     "qvb8_small_m_group_scratch_bytes", "qvb8_small_m_group",
 )
 
@@ -119,6 +119,8 @@ def load() -> ctypes.CDLL:
             lib.qvb8_peer_allreduce_ex.argtypes = [ctypes.POINTER(vp), ci, ci, i64, vp, vp, vp, i64, ci, ctypes.c_uint64, vp]
             lib.qvb8_peer_allreduce_local.argtypes = [ctypes.POINTER(vp), ci, i64, ctypes.POINTER(vp), ctypes.POINTER(vp),
                                                       ctypes.POINTER(vp), i64, ctypes.c_uint64, vp]
+            lib.qvb8_peer_allgather.argtypes = lib.qvb8_peer_allreduce_ex.argtypes
+            lib.qvb8_peer_allgather_local.argtypes = lib.qvb8_peer_allreduce_local.argtypes
             lib.qvb8_device_status_reset.argtypes = []
             lib.qvb8_prefill_set_tuning.argtypes = [ci]
             lib.qvb8_prefill_set_tuning.restype = None

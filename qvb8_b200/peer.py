@@ -81,6 +81,20 @@ class PeerAllReduce:
                        "qvb8_peer_allreduce")
         return out
 
+    def allgather(self, part: torch.Tensor, out: torch.Tensor, flags: int = 0) -> torch.Tensor:
+        """out[r] = rank r's `part` (fp32, contiguous, numel % 4 == 0; out holds world x part.numel() floats), on the
+        current stream, by the same push protocol."""
+        if any(t.dtype != torch.float32 or not t.is_contiguous() or t.device != self.device for t in (part, out)):
+            raise RuntimeError("qvb8_b200: the peer all-gather takes contiguous fp32 tensors on its device")
+        n = part.numel()
+        if out.numel() != n * self.world:
+            raise RuntimeError("qvb8_b200: the all-gather's output holds world x part.numel() floats")
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().qvb8_peer_allgather(self._ptrs, self.rank, self.world, self.cap, self.epoch.data_ptr(),
+                                                       part.data_ptr(), out.data_ptr(), n, int(flags), 0,
+                                                       _lib.stream_ptr(self.device)), "qvb8_peer_allgather")
+        return out
+
     def _release(self, L) -> None:
         if self.device.type != "cuda" or not torch.cuda.is_available():
             return

@@ -74,11 +74,21 @@ class LinearStack:
     INPUT COLUMNS (row-parallel): rank r holds columns [r*P/world, (r+1)*P/world) of every row, cut out of the whole
     pack's bytes (``fuse.column_shard``), reads the matching slice of the activation and produces a partial (M, Q)
     sum; one all-reduce per column->row pair is the only exchange (two per layer, or one per launch when several
-    layers run behind one launch)."""
+    layers run behind one launch).
+
+    shard="rows": EVERY projection is sharded by output rows, the reference's own cut (``row_subset``).  The shards of o
+    and down keep their full-length rows -- eight times fewer, eight times longer tiles than the column shards at
+    world 8, which the streaming kernel runs markedly faster at M = 1 -- at the price of more exchanges: o and down
+    need their whole input, so the ranks all-gather their slices of the attention output and the MLP activation as
+    well as the slices of the o and down outputs (four all-gathers per layer in a model; here one all-gather per
+    launch carrying all four slices of the launch's layers)."""
 
     def __init__(self, cfg: StackConfig, M: int, device, layers: int | None = None, seed_base: int | None = None,
                  rank: int = 0, world: int = 1, policy: str = "escape_outliers", x_dtype=torch.bfloat16,
-                 fuse_same_input: bool = True):
+                 fuse_same_input: bool = True, shard: str = "pairs"):
+        if shard not in ("pairs", "rows"):
+            raise ValueError("shard must be 'pairs' or 'rows'")
+        self.shard = shard
         self.cfg, self.M, self.device = cfg, int(M), torch.device(device)
         self.layers = cfg.layers if layers is None else int(layers)
         self.rank, self.world = rank, world
@@ -100,7 +110,7 @@ class LinearStack:
                 pk = synth.encode_qvb8(W, tau=cfg.tau, policy=policy)
                 del W
                 if world > 1:
-                    if name in ROW_PARALLEL:
+                    if name in ROW_PARALLEL and shard == "pairs":
                         if P % (128 * world):
                             raise ValueError(f"{name}: {P} columns do not split over {world} ranks in 128-column units")
                         pk = _fuse.column_shard(pk, rank * (P // world), (rank + 1) * (P // world))
@@ -134,20 +144,34 @@ class LinearStack:
             self.launches.append(row)
         d, f = cfg.d_model, cfg.mlp
         # row-parallel projections read only this rank's slice of their input
-        shapes = {"x_attn": d, "x_o": cfg.q_out // world, "x_mlp": d, "x_down": f // world}
+        cut = world if shard == "pairs" else 1
+        shapes = {"x_attn": d, "x_o": cfg.q_out // cut, "x_mlp": d, "x_down": f // cut}
         self.x = {k: synth.synth_activation(self.M, p, seed=7 + i, device=self.device, dtype=x_dtype)
                   for i, (k, p) in enumerate(shapes.items())}
         # one output buffer per launch; y[layer][name] are the members' views of it.  The outputs of the row-parallel
         # projections (partial sums that the ranks exchange) lie side by side in ONE buffer, layer after layer, so that
         # the partial sums of several layers can be exchanged by a single all-reduce.
         n_rp = sum(1 for name, *_ in self.launches[0] if name in ROW_PARALLEL)
-        self.y_rowpar = torch.empty((self.layers * n_rp, self.M, d), dtype=torch.float32, device=self.device)
+        d_out = d if shard == "pairs" else d // world
+        if shard == "pairs":
+            self.y_rowpar = torch.empty((self.layers * n_rp, self.M, d_out), dtype=torch.float32, device=self.device)
+            rp_out = [self.y_rowpar[i] for i in range(self.layers * n_rp)]
+        else:
+            # everything split by output rows: what a rank must hand to the others, per layer, is its slice of the o and
+            # down outputs and its slice of their inputs (attention output, MLP activation -- produced outside this
+            # path, random here).  One contiguous part per layer, so a launch's layers are exchanged by one all-gather.
+            extra = self.M * (cfg.q_out + f) // world
+            self.part = torch.randn((self.layers, n_rp * self.M * d_out + extra), dtype=torch.float32, device=self.device,
+                                    generator=torch.Generator(device=self.device).manual_seed(11 + rank))
+            self.gathered = None
+            rp_out = [self.part[i // n_rp, (i % n_rp) * self.M * d_out:(i % n_rp + 1) * self.M * d_out].view(self.M, d_out)
+                      for i in range(self.layers * n_rp)]
         self.y_launch = []
         for li, row in enumerate(self.launches):
             outs, k = [], 0
             for name, pk, *_ in row:
-                if name in ROW_PARALLEL and pk.Q == d:
-                    outs.append(self.y_rowpar[li * n_rp + k])
+                if name in ROW_PARALLEL and pk.Q == d_out:
+                    outs.append(rp_out[li * n_rp + k])
                     k += 1
                 else:
                     outs.append(torch.empty((self.M, pk.Q), dtype=torch.float32, device=self.device))
@@ -184,9 +208,25 @@ class LinearStack:
         if self.reduce and peer:
             from .peer import PeerAllReduce
             # the largest exchange: the row-parallel outputs of up to eight layers at once (see set_grouping)
-            cap = max(max(t.numel() for row in self.y_launch for t in row),
-                      min(self.layers, 8) * self._n_rp * self.M * self.cfg.d_model)
+            if self.shard == "pairs":
+                cap = max(max(t.numel() for row in self.y_launch for t in row),
+                          min(self.layers, 8) * self._n_rp * self.M * self.cfg.d_model)
+            else:
+                cap = min(self.layers, 8) * self.part.shape[1]
             self.peer = PeerAllReduce(dist.group.WORLD, cap, self.device)
+        if self.reduce and self.shard == "rows":
+            self.gathered = torch.empty((self.world, min(self.layers, 8) * self.part.shape[1]), dtype=torch.float32,
+                                        device=self.device)
+
+    def _allgather(self, l0: int, l1: int) -> None:
+        """Exchange the parts of layers [l0, l1): afterwards gathered[r] holds rank r's."""
+        part = self.part[l0:l1].view(-1)
+        out = self.gathered.view(-1)[:self.world * part.numel()]
+        if self.peer is not None and part.numel() % 4 == 0:
+            self.peer.allgather(part, out, flags=_lib.FLAG_PDL if self.pdl else 0)
+        else:
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(out, part)
 
     def _allreduce(self, t: torch.Tensor) -> None:
         if self.peer is not None and t.numel() % 4 == 0:
@@ -223,15 +263,19 @@ class LinearStack:
         if self._groups is not None:
             for g, (l0, l1) in zip(self._groups, self._group_layers):
                 _lib.small_m_group(g, flags=_lib.FLAG_PDL if self.pdl else 0)
-                if self.reduce:
+                if self.reduce and self.shard == "rows":
+                    self._allgather(l0, l1)
+                elif self.reduce:
                     self._allreduce(self.y_rowpar[l0 * self._n_rp:l1 * self._n_rp].view(-1))
             return
         for li, row in enumerate(self.launches):
             for j, (name, pk, st, keep, xname, _) in enumerate(row):
                 _lib.small_m(st, keep, self.x[xname], out=self.y_launch[li][j], plan=keep[-1],
                              flags=_lib.FLAG_PDL if self.pdl else 0)
-                if self.reduce and name in ROW_PARALLEL:
+                if self.reduce and name in ROW_PARALLEL and self.shard == "pairs":
                     self._allreduce(self.y_launch[li][j])
+            if self.reduce and self.shard == "rows":
+                self._allgather(li, li + 1)
 
     def capture(self) -> None:
         # warm-up (shared-memory opt-in, scratch) on the stream the capture will use: scratch buffers are kept per

@@ -102,6 +102,41 @@ def test_moe_config_shape_and_bad_index(cuda_lib):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_shards_sum_to_the_whole(cuda_lib, world):
+    """experts split over `world` ranks (here: modules on one device, run one after the other), tokens and routing
+    replicated: the ranks' fp32 partial outputs add up to the unsharded layer's output, and a shard asked alone returns
+    only its own experts' contributions"""
+    E, topk, P, hidden, M = 8, 3, 256, 64, 6
+    ups, dns = _experts(E, 2 * hidden, P, P, hidden, (5, 7, 8), seed=21)
+    ups, dns = [u.to(DEV) for u in ups], [d.to(DEV) for d in dns]
+    whole = experts.QVBandExpertsV8(ups, dns, num_experts=E)
+    idx, w = _routing(M, E, topk, seed=3)
+    X = synth.synth_activation(M, P, seed=8, device=DEV, dtype=torch.float32) * 0.5
+    want = whole(X, idx.to(DEV), w.to(DEV))
+    per = E // world
+    parts = []
+    for r in range(world):
+        shard = experts.QVBandExpertsV8(ups[r * per:(r + 1) * per], dns[r * per:(r + 1) * per], num_experts=per,
+                                        first_expert=r * per, total_experts=E)
+        assert shard.sharded
+        parts.append(shard(X, idx.to(DEV), w.to(DEV)))
+        # the same shard with the other ranks' pairs given weight zero on the whole layer
+        mask = ((idx >= r * per) & (idx < (r + 1) * per)).float()
+        alone = whole(X, idx.to(DEV), (w * mask).to(DEV))
+        assert float((parts[-1] - alone).abs().max()) <= 1e-5 * float(want.abs().max())
+    total = torch.stack(parts).sum(0)
+    assert float((total - want).abs().max()) <= 1e-5 * float(want.abs().max())
+    # the reduce hook receives the fp32 partial sums; the result comes back in the activations' type
+    seen = []
+    shard.set_reduce(lambda t: seen.append(t.dtype) or t * 2)
+    out = shard(X.to(torch.bfloat16), idx.to(DEV), w.to(DEV))
+    assert seen == [torch.float32] and out.dtype == torch.bfloat16
+    from qvb8_b200 import lib
+    assert lib.device_status() == 0
+
+
+@pytest.mark.gpu
 def test_moe_full_size_properties(cuda_lib):
     """The 35B-A3B-class layer at its full size (128 experts, top-8, d_model 2048, expert FFN 768, 32 tokens): too
     large for the oracle, so size-independent properties are checked: doubling the routing weights doubles the result

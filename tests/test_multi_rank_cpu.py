@@ -69,6 +69,49 @@ def test_row_sharded_product_equals_the_whole(tmp_path):
     assert float(np.abs(w_row - synth.synth_weight(Q, P, 4242).float().numpy()).max()) <= 1e-3
 
 
+def _expert_worker(rank: int, world: int, port: int, out_dir: str):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        E, topk, P, hidden, M = 4, 2, 64, 16, 5
+        per = E // world
+        # every rank builds only ITS experts (seeded by the global expert number) and sees all tokens and the routing
+        ups = [synth.encode_qvb8(synth.synth_weight(2 * hidden, P, 300 + e), tau=1e-3, policy="inband")
+               for e in range(rank * per, (rank + 1) * per)]
+        dns = [synth.encode_qvb8(synth.synth_weight(P, hidden, 400 + e), tau=1e-3, policy="inband")
+               for e in range(rank * per, (rank + 1) * per)]
+        g = torch.Generator().manual_seed(1)
+        wts, idx = torch.topk(torch.softmax(torch.randn(M, E, generator=g), -1), topk, dim=-1)
+        X = synth.synth_activation(M, P, seed=2).float().numpy()
+        local = idx - rank * per                               # what the sharded module hands to the kernels
+        mine = (local >= 0) & (local < per)                    # pairs outside the local stack contribute zero
+        part = oracle.moe_experts(X, torch.where(mine, local, torch.zeros_like(local)).numpy(),
+                                  (wts * mine).numpy(), np.stack([oracle.qvb8_dense(pack_np(u)) for u in ups]),
+                                  np.stack([oracle.qvb8_dense(pack_np(d)) for d in dns]))
+        t = torch.from_numpy(part)
+        dist.all_reduce(t)
+        if rank == 0:
+            np.save(os.path.join(out_dir, "moe.npy"), t.numpy())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_partial_sums_equal_the_whole_layer(tmp_path):
+    world = 2
+    mp.spawn(_expert_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    E, topk, P, hidden, M = 4, 2, 64, 16, 5
+    ups = [synth.encode_qvb8(synth.synth_weight(2 * hidden, P, 300 + e), tau=1e-3, policy="inband") for e in range(E)]
+    dns = [synth.encode_qvb8(synth.synth_weight(P, hidden, 400 + e), tau=1e-3, policy="inband") for e in range(E)]
+    g = torch.Generator().manual_seed(1)
+    wts, idx = torch.topk(torch.softmax(torch.randn(M, E, generator=g), -1), topk, dim=-1)
+    X = synth.synth_activation(M, P, seed=2).float().numpy()
+    want = oracle.moe_experts(X, idx.numpy(), wts.numpy(), np.stack([oracle.qvb8_dense(pack_np(u)) for u in ups]),
+                              np.stack([oracle.qvb8_dense(pack_np(d)) for d in dns]))
+    assert np.allclose(np.load(tmp_path / "moe.npy"), want, rtol=1e-12, atol=1e-12)
+
+
 def test_row_subset_of_a_module_is_the_rows_of_the_whole():
     """The zero-copy shard: a module over a subset of rows shares the packed ids and restores to those rows."""
     from qvb8_b200.linear import QVBandLinearV8

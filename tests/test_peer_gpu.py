@@ -49,6 +49,25 @@ def test_all_ranks_in_one_cooperative_launch(cuda_lib, world):
     assert _lib.device_status(DEV) == 0
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_all_gather_in_one_cooperative_launch(cuda_lib, world):
+    L = cuda_lib
+    n, cap = 1536, 2048
+    areas, epochs = _areas(L, world, cap)
+    g = torch.Generator().manual_seed(10 + world)
+    for step in range(3):
+        parts = [torch.randn(n, generator=g).to(DEV) for _ in range(world)]
+        outs = [torch.empty(world * n, device=DEV) for _ in range(world)]
+        with torch.cuda.device(DEV):
+            _lib.check(L.qvb8_peer_allgather_local(_ptrs(areas), world, cap, _ptrs(epochs), _ptrs(parts), _ptrs(outs), n,
+                                                   0, _lib.stream_ptr(torch.device(DEV))), "qvb8_peer_allgather_local")
+        torch.cuda.synchronize()
+        want = torch.cat(parts)
+        for o in outs:
+            assert torch.equal(o, want)
+    assert _lib.device_status(DEV) == 0
+
+
 def test_in_place_reduction(cuda_lib):
     L = cuda_lib
     world, n, cap = 2, 1024, 1024
