@@ -581,7 +581,7 @@ def main():
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection (no same-input fusion)")
     ap.add_argument("--group-layers", type=int, default=-1,
                     help="layers whose projections run behind one launch (0 = one launch per projection; "
-                         "-1 = default: 8)")
+                         "-1 = default: 16)")
     ap.add_argument("--shard", default="auto", choices=["auto", "pairs", "rows"],
                     help="N > 1: column/row-parallel pairs + all-reduce, or every projection by output rows + all-gather "
                          "(auto: rows below 8 activation rows, where the full-length rows stream faster; pairs from 8)")
@@ -668,7 +668,7 @@ def main():
         else:
             st.enable_collectives(peer=False)
 
-    group_layers = args.group_layers if args.group_layers >= 0 else 8
+    group_layers = args.group_layers if args.group_layers >= 0 else 16
     if group_layers > 0:
         st.set_grouping(group_layers)
 

@@ -135,7 +135,10 @@ int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *scratch
 /* Tuning hook for tests and sweeps (process-wide; 0 = choose automatically): fill_pct = CTAs launched, in percent of
  * one resident wave; force_s = number of K-ranges (raised to what shared memory requires); nstg = slots of the copy
  * ring (2..8); cps = 128-column chunks per ring stage (4, 8, 12 or 16); debug bit 0 = skip the fragment math (copy
- * stream only), bit 1 = record qvb8_debug_trace stamps, bit 2 = skip the row copies (results meaningless); bits 8..11 =
+ * stream only), bit 1 = record qvb8_debug_trace stamps, bit 2 = skip the row copies (results meaningless), bit 4 = plain
+ * bulk copies without the evict-first hint, bit 5 = list launches skip the escape pre-pass (results lack the escapes),
+ * bit 6 = the stamps follow the finishing warp's visits 4..7 instead of the consumers' jobs, bit 7 = list launches cut
+ * products with many columns into column ranges (correct, measured slower than launching them alone); bits 8..11 =
  * pipes per CTA for up to 8 tokens (2 instead of the default 4). */
 void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int cps, int debug);
 
@@ -236,6 +239,21 @@ int64_t qvb8_moe_scratch_bytes(int64_t M, int64_t topk, int64_t E, int64_t Pup, 
 int qvb8_moe_experts(const void *X, int x_dtype, int64_t M, const int64_t *idx, const float *w, int64_t topk, int64_t E,
                      const qvb8_expert_stack *up, const qvb8_expert_stack *dn, int act, void *out, void *scratch,
                      int64_t scratch_bytes, void *stream);
+/* The same through the streaming kernel when per-expert plans are given and M <= 8 (else exactly qvb8_moe_experts):
+ * every distinct selected expert is one job of the small-M streaming kernel (bulk-copy rings, tensor-core sums) with all
+ * M tokens as its activations; the job tables are written on the device from the routing.  The hidden activations go
+ * through that kernel's fp16 staging, each (expert, token) row scaled by a power of two first so that nothing saturates
+ * (undone exactly afterwards): a hidden value carries a relative rounding of 2^-11 that qvb8_moe_experts does not have.
+ * Needs up->P and dn->P multiples of 128 and 16-byte aligned stacks; otherwise the plans are ignored.
+ * qvb8_moe_plan_bytes(E, Q) / qvb8_moe_plan_build: the plans of one stack (E experts of Q rows), built once; 256-byte
+ * aligned device memory owned by the caller.  scratch: as qvb8_moe_scratch_bytes says (it covers both routes).
+ * qvb8_moe_streams: 1 when this shape, given plans, runs through the streaming kernel. */
+int qvb8_moe_streams(int64_t M, int64_t topk, int64_t E, const qvb8_expert_stack *up, const qvb8_expert_stack *dn);
+int64_t qvb8_moe_plan_bytes(int64_t E, int64_t Q);
+int qvb8_moe_plan_build(const qvb8_expert_stack *stack, int64_t E, void *plan, int64_t plan_bytes, void *stream);
+int qvb8_moe_experts_planned(const void *X, int x_dtype, int64_t M, const int64_t *idx, const float *w, int64_t topk,
+                             int64_t E, const qvb8_expert_stack *up, const qvb8_expert_stack *dn, const void *up_plan,
+                             const void *dn_plan, int act, void *out, void *scratch, int64_t scratch_bytes, void *stream);
 int qvb8_moe_bad_index(const void *scratch, int64_t M, int64_t topk, int64_t E, int64_t Pup, int64_t Qup, int64_t Qdn,
                        int act, int *bad);
 

@@ -47,4 +47,33 @@ inline PlanLayout plan_layout(int64_t Q, int64_t n_esc) {
     return L;
 }
 
+// One product of a launch: a pack (with its plan), its activations and its output -- or one K-RANGE of such a product:
+// columns [kc0 * 128, (kc0 + nc_total) * 128) of every row, the ranges of one pack being consecutive jobs of a list that
+// share unit0 and nsk_part, so that every CTA (and every thread of it) meets the same tiles in each of them and adds a
+// later range's sums to what it wrote for the earlier ones.
+struct JobDesc {
+    const uint8_t *ids;
+    const uint8_t *nbits;      // per-element class only
+    const int64_t *bit_off;    // per-element class only
+    const TileDesc *tiles;
+    const EscEntry *esc_ent;   // escapes grouped by tile; null: the pack has no escapes
+    const void *X;             // (M, P), row 0, column 0
+    float *Y;                  // (M, Q)
+    int ntiles;                // length of the tile table (real tiles first, then empty ones)
+    int Q, P;
+    int nc_total;              // 128-column chunks of this job (P / 128, or the K-range's share)
+    int x_dtype, x_mode;
+    int unit0;                 // list launches: (tile, stage) units of the jobs before this one (before the pack's first range)
+    int yflags;                // bit 0: an escape pre-pass has put the pack's corrections into Y (sums are added to them
+                               // atomically); bit 1: a later K-range (sums are added to what the earlier ranges wrote)
+    int kc0;                   // first chunk of the K-range (0 for a whole product)
+    int nsk_part;              // stages per tile over ALL K-ranges of the pack (0: this job's own count)
+};
+static_assert(sizeof(JobDesc) == 96, "job record layout (host and device agree)");
+
+// qvb8_small_m.cu: list launches of the streaming kernel over a job table in device memory
+int small_m_devlist_units(int64_t M, int64_t P, int cap_jobs, int ntiles);
+int small_m_devlist_launch(const JobDesc *dev_jobs, const int *dev_njobs, int cap_jobs, int64_t M, int64_t P, int ntiles,
+                           bool pdl, cudaStream_t st);
+
 }  // namespace qv

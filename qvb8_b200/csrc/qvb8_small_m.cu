@@ -35,7 +35,7 @@
 // while X was staged), adds the escape corrections, and writes the result.  K-ranges of one tile are added in range
 // order by whichever CTA finishes the tile last (a ticket counter per tile).
 //
-// Lists.  One launch can run up to 32 independent products (qvb8_small_m_group): the job table travels by value in
+// Lists.  One launch can run up to 64 independent products (qvb8_small_m_group): the job table travels by value in
 // the kernel's parameters.  All (tile, stage) units of the list form ONE sequence that is cut into equal contiguous
 // per-CTA ranges, so a CTA meets one or two jobs per launch and its rings never drain at a job boundary; at a
 // boundary the consumer warps restage X for the next job from global memory while the producer is already copying
@@ -641,29 +641,16 @@ __global__ void __launch_bounds__(1024) tile_escapes_kernel(TileDesc *__restrict
     }
 }
 
-// One product of a launch: a pack (with its plan), its activations and its output.
-struct JobDesc {
-    const uint8_t *ids;
-    const uint8_t *nbits;      // per-element class only
-    const int64_t *bit_off;    // per-element class only
-    const TileDesc *tiles;
-    const EscEntry *esc_ent;   // escapes grouped by tile; null: the pack has no escapes
-    const void *X;             // (M, P)
-    float *Y;                  // (M, Q)
-    int ntiles;                // length of the tile table (real tiles first, then empty ones)
-    int Q, P;
-    int nc_total;              // P / 128
-    int x_dtype, x_mode;
-    int unit0;                 // list launches: (tile, stage) units of the jobs before this one
-    int prepass;               // 1: an escape pre-pass has put the job's corrections into Y; the product is added to them
-};
-static_assert(sizeof(JobDesc) == 88, "job record layout (host and device agree)");
-constexpr int MAX_JOBS = 32;   // jobs behind one launch
+constexpr int MAX_JOBS = 64;   // jobs behind one launch (the table travels in the kernel's parameters: 6 KB of the 32 KB
+                               // a launch may carry)
 
 struct SmallMParams {
     JobDesc jobs[MAX_JOBS];    // the launch's jobs, by value (they travel with the launch: nothing to keep alive, and a
                                // captured graph holds its own copy)
-    int njobs;
+    int njobs;                 // jobs in `jobs`; with a device-resident table: its capacity
+    const JobDesc *dev_jobs;   // device-resident job table (written by an earlier kernel of the stream), or null
+    const int *dev_njobs;      // its length, in device memory (null: the table above is used)
+    int units_per_job;         // device-resident table: every job has this many (tile, stage) units; unit0 = index x this
     float *part;               // (slots, M, Q) partial results of tiles shared by several K-ranges (single job only)
     int *ticket;               // one counter per CTA column (zero on entry, zero on exit)
     int M, MP;                 // MP: token slots per column group in shared memory (>= M)
@@ -803,19 +790,21 @@ struct JobGeom {
     int ct0, ct1;              // the CTA's tiles
     Run run;                   // this pipe's run
 };
+struct ListShape { bool list; int units_total; };     // list = one stream of units cut into per-CTA ranges
 template <int NPIPE>
-__device__ __forceinline__ JobGeom job_geom(const SmallMParams &p, const JobDesc &jd, int split, int pipe) {
+__device__ __forceinline__ JobGeom job_geom(const SmallMParams &p, const ListShape &ls, const JobDesc &jd, int split, int pipe) {
     JobGeom g;
-    g.kc0 = split * p.nc_per;
-    g.NC = p.njobs > 1 ? jd.nc_total : min(p.nc_per, jd.nc_total - g.kc0);
+    g.kc0 = ls.list ? jd.kc0 : split * p.nc_per;
+    g.NC = ls.list ? jd.nc_total : min(p.nc_per, jd.nc_total - g.kc0);
     g.NSK = (g.NC + p.cps - 1) / p.cps;
-    if (p.njobs > 1) {
+    const int nskp = jd.nsk_part > 0 ? jd.nsk_part : g.NSK;            // units per tile in the list's unit count
+    if (ls.list) {
         // A list is ONE stream of (tile, stage) units, job after job, cut into equal contiguous ranges, one per CTA
         // (snapped to whole tiles: a tile goes to the CTA that holds its first unit).  A CTA therefore meets only the
         // one or two jobs its range touches, stages activations that often, and all CTAs finish together.
-        const int64_t lo = (int64_t)blockIdx.x * p.units_total / gridDim.x - jd.unit0;
-        const int64_t hi = (int64_t)(blockIdx.x + 1) * p.units_total / gridDim.x - jd.unit0;
-        const int64_t t0 = lo <= 0 ? 0 : (lo + g.NSK - 1) / g.NSK, t1 = hi <= 0 ? 0 : (hi + g.NSK - 1) / g.NSK;
+        const int64_t lo = (int64_t)blockIdx.x * ls.units_total / gridDim.x - jd.unit0;
+        const int64_t hi = (int64_t)(blockIdx.x + 1) * ls.units_total / gridDim.x - jd.unit0;
+        const int64_t t0 = lo <= 0 ? 0 : (lo + nskp - 1) / nskp, t1 = hi <= 0 ? 0 : (hi + nskp - 1) / nskp;
         g.ct0 = (int)(t0 < jd.ntiles ? t0 : jd.ntiles);
         g.ct1 = (int)(t1 < jd.ntiles ? t1 : jd.ntiles);
     } else {
@@ -842,6 +831,45 @@ __device__ __forceinline__ void stage_slice(const void *X, int x_dtype, int64_t 
     const int g0 = cw * per, g1 = min(groups, g0 + per);
     const int64_t col0 = (int64_t)kc0 * KC;
     constexpr int UNR = 4;                                              // loads in flight per thread
+    if (per <= 32 && MP > 1) {
+        // At most one column group per lane: the loads of four TOKENS are in flight together (with the loop below every
+        // token would be one round trip to memory).  The same arithmetic per token, hence the same bits.
+        const int u8 = g0 + lane;
+        const bool on = u8 < g1;
+        for (int m0 = 0; m0 < MP; m0 += UNR) {
+            uint32_t h[UNR][8];
+#pragma unroll
+            for (int i = 0; i < UNR; ++i) {
+                const int m = m0 + i;
+                if (on && m < M) {
+                    stage_x8_any<GLOBAL>(x_dtype, X, (int64_t)m * ldx + col0 + (int64_t)u8 * 8, h[i], sc_of(m));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) h[i][j] = 0u;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < UNR; ++i) {
+                const int m = m0 + i;
+                if (m >= MP) break;
+                float s = 0.f;
+                if (on) {
+                    const int sl = slot_of(u8 * 8, m, MP);
+                    *reinterpret_cast<uint4 *>(xs_a + (sl << 3)) = make_uint4(
+                        h[i][0] | (h[i][2] << 16), h[i][1] | (h[i][3] << 16), h[i][4] | (h[i][6] << 16), h[i][5] | (h[i][7] << 16));
+                    if (DUAL)
+                        *reinterpret_cast<uint4 *>(xs_b + (sl << 3)) = make_uint4(
+                            h[i][0] | (h[i][4] << 16), h[i][1] | (h[i][5] << 16), h[i][2] | (h[i][6] << 16), h[i][3] | (h[i][7] << 16));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) s += __half2float(__ushort_as_half((unsigned short)h[i][j]));
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane == 0 && m < M) psum_w[m] = s;
+            }
+        }
+        return;
+    }
     for (int m = 0; m < MP; ++m) {
         float s = 0.f;
         const float sc = m < M ? sc_of(m) : 1.f;
@@ -902,14 +930,20 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     const int cps = p.cps;
     const int MP = p.MP, M = p.M;
     const int nstg = p.nstg;
-    const int njobs = p.njobs;
+    // A device-resident job table was written by the kernel before this one in the stream: wait for it first.
+    const bool devlist = p.dev_njobs != nullptr;
+    if (devlist) pdl_wait();
+    const int njobs = devlist ? min(__ldg(p.dev_njobs), p.njobs) : p.njobs;
+    if (njobs <= 0) return;                                            // (an empty device-resident table: nothing to do)
+    const JobDesc *jtab = devlist ? p.dev_jobs : p.jobs;
+    const ListShape ls{devlist || njobs > 1, devlist ? njobs * p.units_per_job : p.units_total};
     // dynamic shared memory:
     //   [job table] [activations: layout A, layout B] [16 zero bytes, padded to 128]
     //   [activation sums by consumer warp, two sets] [exchange buffers of tiles shared by pipes]
     //   per pipe: [ring: nstg stages of 16 rows] [side ring: NSIDE x (descriptor + escapes)] [two hand-over buffers]
     //             [escape corrections]
     JobDesc *jobs = reinterpret_cast<JobDesc *>(smem);
-    const size_t jobs_bytes = (size_t)((njobs * (int)sizeof(JobDesc) + 127) / 128 * 128);
+    const size_t jobs_bytes = (size_t)((p.njobs * (int)sizeof(JobDesc) + 127) / 128 * 128);
     __half *xs_a = reinterpret_cast<__half *>(smem + jobs_bytes);
     __half *xs_b = DUAL ? xs_a + p.xs_halves : xs_a;
     uint32_t *zero16 = reinterpret_cast<uint32_t *>(xs_a + (DUAL ? 2 : 1) * p.xs_halves);
@@ -936,15 +970,19 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     // sequence and counts its barrier phases by the position in it.  Read from the launch parameters: the shared-memory
     // copy of the job table is not there yet, and the producer wants its first descriptor on the way before anything else.
     int jfirst = 0, jcount = njobs;
-    if (njobs > 1) {
-        const int64_t lo = (int64_t)blockIdx.x * p.units_total / gridDim.x, hi = (int64_t)(blockIdx.x + 1) * p.units_total / gridDim.x;
+    if (ls.list) {
+        const int64_t lo = (int64_t)blockIdx.x * ls.units_total / gridDim.x, hi = (int64_t)(blockIdx.x + 1) * ls.units_total / gridDim.x;
         int j = 0;
-        for (int q = 1; q < njobs; ++q)
-            if (p.jobs[q].unit0 <= lo) j = q;                          // the job that holds the range's first unit
+        if (devlist) {
+            j = min(njobs - 1, (int)(lo / max(1, p.units_per_job)));
+        } else {
+            for (int q = 1; q < njobs; ++q)                             // the job that holds the range's first unit (the
+                if (jtab[q].unit0 <= lo && jtab[q].unit0 != jtab[j].unit0) j = q;   // first K-range of its pack)
+        }
         int jlast = -1;
         jfirst = njobs;
-        for (; j < njobs && p.jobs[j].unit0 < hi; ++j) {
-            const JobGeom gj = job_geom<NPIPE>(p, p.jobs[j], split, 0);
+        for (; j < njobs && jtab[j].unit0 < hi; ++j) {
+            const JobGeom gj = job_geom<NPIPE>(p, ls, jtab[j], split, 0);
             if (gj.ct1 > gj.ct0) { if (j < jfirst) jfirst = j; jlast = j; }
         }
         jcount = jlast >= jfirst ? jlast - jfirst + 1 : 0;
@@ -956,9 +994,9 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     uint32_t pf_b16 = 0;
     if (warp == PRODUCER_WARP) {
         for (int j = jfirst; j < jend && pf_j < 0; ++j) {
-            const JobGeom gj = job_geom<NPIPE>(p, p.jobs[j], split, pipe);
+            const JobGeom gj = job_geom<NPIPE>(p, ls, jtab[j], split, pipe);
             if (gj.run.nv > 0) {
-                const TileDesc *d = p.jobs[j].tiles + run_visit(gj.run, 0).tile;
+                const TileDesc *d = jtab[j].tiles + run_visit(gj.run, 0).tile;
                 pf_nb = __ldg(&d->nb);
                 pf_cnt = __ldg(&d->cnt);
                 pf_esc0 = __ldg(&d->esc0);
@@ -970,7 +1008,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     }
     // the job table: from the launch parameters into shared memory, where every warp reads it at each job boundary
     {
-        const uint32_t *src = reinterpret_cast<const uint32_t *>(p.jobs);
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(jtab);
         uint32_t *dst = reinterpret_cast<uint32_t *>(jobs);
         for (int i = tid; i < njobs * (int)(sizeof(JobDesc) / 4); i += blockDim.x) dst[i] = src[i];
     }
@@ -1018,13 +1056,13 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         uint32_t b16 = 0;
         // cursor over (job, visit) pairs that exist
         int cj = jfirst, ci = -1;
-        JobGeom cg = job_geom<NPIPE>(p, jobs[jfirst], split, pipe);
+        JobGeom cg = job_geom<NPIPE>(p, ls, jobs[jfirst], split, pipe);
         if (jcount == 0) cg.run.nv = 0;
         auto advance = [&](int &j, int &i, JobGeom &g) {                // -> false when the list is exhausted
             ++i;
             while (i >= g.run.nv) {
                 if (++j >= jend) return false;
-                g = job_geom<NPIPE>(p, jobs[j], split, pipe);
+                g = job_geom<NPIPE>(p, ls, jobs[j], split, pipe);
                 i = 0;
             }
             return true;
@@ -1051,7 +1089,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             const Visit v = run_visit(cg.run, ci);
             const int NC = cg.NC, kc0 = cg.kc0;
             const int cnb = nb, ccnt = cnt;
-            const bool planned = jd.esc_ent != nullptr && !jd.prepass;   // (a pre-pass has applied the job's escapes)
+            const bool planned = jd.esc_ent != nullptr && !(jd.yflags & 1);   // (a pre-pass has applied the job's escapes)
             const uint32_t ebytes = planned ? (uint32_t)(min((nesc + 1) & ~1, esc_cap) * 8) : 0u;
             const EscEntry *esrc = jd.esc_ent + esc0;
             const uint32_t step = (uint32_t)(cps * 16 * cnb);           // bytes of a row per full stage
@@ -1116,12 +1154,13 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         for (int kj = 0; kj < jcount; ++kj) {
             const int job = jfirst + kj;
             const JobDesc &jd = jobs[job];
-            const JobGeom gm = job_geom<NPIPE>(p, jd, split, pipe);
+            const JobGeom gm = job_geom<NPIPE>(p, ls, jd, split, pipe);
             const Run &run = gm.run;
             const int kc0 = gm.kc0, NC = gm.NC, NSK = gm.NSK;
             const __half *xsa = xs_a;
-            const bool planned = jd.esc_ent != nullptr && !jd.prepass;     // escapes corrected here (else: by the pre-pass)
-            const bool add_to_y = jd.esc_ent != nullptr && jd.prepass;     // Y holds the pre-pass's corrections: add to it
+            const bool planned = jd.esc_ent != nullptr && !(jd.yflags & 1);   // escapes corrected here (else: by the pre-pass)
+            const bool add_to_y = jd.esc_ent != nullptr && (jd.yflags & 1);   // Y holds the pre-pass's corrections: add to it
+            const bool later_range = (jd.yflags & 2) != 0;                 // Y holds this thread's sums of the earlier K-ranges
             const bool prescaled = njobs == 1 && jd.x_mode == 1 && jd.x_dtype != QVB8_F16;
             // the job's activations are staged and every consumer warp has left its partial sums of them: this lane
             // keeps the sums of the tokens it writes (8n + 2t + k), added up in warp order (same bits every run)
@@ -1156,7 +1195,10 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                             const int m = 8 * n + 2 * t + k;
                             if (rows[hrow] >= 0 && m < M) {
                                 float *dst = out + (int64_t)m * jd.Q + rows[hrow];
-                                if (add_to_y) atomicAdd(dst, y[hrow][n][k]);   // one addition per element: any order gives the same sum
+                                // after a pre-pass: one atomic addition per element and K-range; the ranges of a pack are
+                                // added by the same thread in program order, so the sum has one order
+                                if (add_to_y) atomicAdd(dst, y[hrow][n][k]);
+                                else if (later_range) *dst += y[hrow][n][k];
                                 else *dst = y[hrow][n][k];
                             }
                         }
@@ -1165,7 +1207,10 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 const Visit v = run_visit(run, i);
                 // ---- the tile's descriptor and escapes arrive in a side slot
                 const int sslot = vis % NSIDE;
+                const bool fstamp = tracer && (p.debug & 64) && vis >= 4 && vis < 8;   // tuning: time stamps of visits 4..7
+                if (fstamp) trace(p.debug, 16 + 4 * (vis - 4));
                 if (alive) alive = mbar_wait(side_full0 + 8 * sslot, par(vis / NSIDE), abort_flag, 8, 200);
+                if (fstamp) trace(p.debug, 17 + 4 * (vis - 4));
                 const TileDesc *d = reinterpret_cast<const TileDesc *>(side + sslot * side_bytes);
                 const EscEntry *ent = reinterpret_cast<const EscEntry *>(side + sslot * side_bytes + DESC_SLOT);
                 int cnb = 0, myrow[2] = {-1, -1};
@@ -1254,6 +1299,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 const float *redb = red + rb * RED_FLOATS;
                 if (alive) alive = mbar_wait(smem_u32(&pc_.red_full[rb]), par(vis / 2), abort_flag, 3, 200);
                 if (tracer && vis == 0) trace(p.debug, 10);
+                if (fstamp) trace(p.debug, 18 + 4 * (vis - 4));
                 float acc[NT][4];
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
@@ -1331,6 +1377,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 if (tracer && vis == 0) trace(p.debug, 11);
                 if (emit) emit_tile(myrow, y);
                 if (tracer && vis == 0) trace(p.debug, 12);
+                if (fstamp) trace(p.debug, 19 + 4 * (vis - 4));
             }
             // ---- the tile this pipe shares with later pipes: their parts have long arrived
             if (own_contrib > 0) {
@@ -1374,7 +1421,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         for (int kj = 0; kj < jcount && alive; ++kj) {
             const int job = jfirst + kj;
             const JobDesc &jd = jobs[job];
-            const JobGeom gm = job_geom<NPIPE>(p, jd, split, pipe);
+            const JobGeom gm = job_geom<NPIPE>(p, ls, jd, split, pipe);
             const Run &run = gm.run;
             const int kc0 = gm.kc0, NC = gm.NC;
             float *psum_w = psum + ((kj & 1) * CWARPS + cwarp) * M;
@@ -1419,14 +1466,14 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 // parity, so no barrier may complete twice while one of them still waits for the first completion
                 if (alive) alive = mbar_wait(smem_u32(&ctl.fin_started), par(kj - 1), abort_flag, 12);
                 if (!alive) break;
-                stage_slice<DUAL, true>(jd.X, jd.x_dtype, jd.P, 0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
+                stage_slice<DUAL, true>(jd.X, jd.x_dtype, jd.P, kc0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
                                         [](int) { return 1.f; }, psum_w);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl.x_ready));
             alive = mbar_wait(smem_u32(&ctl.x_ready), par(kj), abort_flag, 5);
             if (!alive) break;
-            if (tracer && warp == 0) { if (kj == 0) trace(p.debug, 5); if (kj < 4) trace(p.debug, 16 + 4 * kj); }
+            if (tracer && warp == 0) { if (kj == 0) trace(p.debug, 5); if (kj < 4 && !(p.debug & 64)) trace(p.debug, 16 + 4 * kj); }
             const uint32_t xs_a32 = xvalid ? smem_u32(xs_a) + xoff : smem_u32(zero16);
             const uint32_t xs_b32 = xvalid ? smem_u32(xs_b) + xoff : smem_u32(zero16);
             const __half *xsa = xs_a;
@@ -1509,7 +1556,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(red_full);
             }
-            if (tracer && warp == 0 && kj < 4) trace(p.debug, 17 + 4 * kj);
+            if (tracer && warp == 0 && kj < 4 && !(p.debug & 64)) trace(p.debug, 17 + 4 * kj);
         }
         if (tracer && warp == 0) trace(p.debug, 8);
     }
@@ -1850,13 +1897,50 @@ static void fill_job(JobDesc &jd, const qvb8_pack *w, const void *plan, const vo
     jd.esc_ent = w->n_esc > 0 ? reinterpret_cast<const EscEntry *>(base + L.esc_ent) : nullptr;
     jd.X = X; jd.Y = Y;
     jd.Q = (int)w->Q; jd.P = (int)w->P; jd.nc_total = (int)(w->P / KC);
-    jd.x_dtype = x_dtype; jd.x_mode = x_mode; jd.unit0 = unit0; jd.prepass = prepass;
+    jd.x_dtype = x_dtype; jd.x_mode = x_mode; jd.unit0 = unit0; jd.yflags = prepass ? 1 : 0;
+    jd.kc0 = 0; jd.nsk_part = 0;
 }
 static void fill_launch(SmallMParams &prm, const Plan &pl, int M) {
     prm.M = M; prm.MP = pl.MP; prm.S = pl.S; prm.nc_per = pl.nc_per; prm.nstg = pl.nstg; prm.debug = g_debug;
     prm.cps = pl.cps; prm.slot_bytes = pl.slot_bytes; prm.esc_cap = pl.esc_cap;
     prm.xs_halves = pl.xs_halves;
     for (int i = 0; i < 6; ++i) prm.rs[i] = pl.rs[i];
+    prm.dev_jobs = nullptr; prm.dev_njobs = nullptr; prm.units_per_job = 0;
+}
+
+// A list launch whose job table lives in DEVICE memory (written by an earlier kernel of the stream, e.g. from a
+// routing decision): up to `cap_jobs` jobs, all with `ntiles` tiles of rows P columns long and no escapes, M <= 8.
+// devlist_units: the (tile, stage) units of one such job -- job i of the table must carry unit0 = i * units -- or 0
+// when such a list does not fit the kernel (the caller takes another route).
+static bool devlist_plan(int64_t M, int64_t P, int cap_jobs, Plan &pl) {
+    int64_t Ps[1024];
+    int esizes[1024];
+    for (int j = 0; j < cap_jobs; ++j) { Ps[j] = P; esizes[j] = 4; }
+    return make_group_plan(M, Ps, esizes, cap_jobs, pl);
+}
+int small_m_devlist_units(int64_t M, int64_t P, int cap_jobs, int ntiles) {
+    if (M < 1 || M > 8 || P <= 0 || P % KC != 0 || cap_jobs < 1 || cap_jobs > 1024 || ntiles < 1) return 0;
+    Plan pl;
+    if (!devlist_plan(M, P, cap_jobs, pl)) return 0;
+    const int64_t units = (int64_t)ntiles * ((P / KC + pl.cps - 1) / pl.cps);
+    return units * cap_jobs > 0x7fffffff ? 0 : (int)units;
+}
+int small_m_devlist_launch(const JobDesc *dev_jobs, const int *dev_njobs, int cap_jobs, int64_t M, int64_t P, int ntiles,
+                           bool pdl, cudaStream_t st) {
+    const int units = small_m_devlist_units(M, P, cap_jobs, ntiles);
+    if (units <= 0) return fail(QVB8_ERR_ARG, "qvb8_small_m: a device-resident job list of this shape does not fit");
+    Plan pl;
+    devlist_plan(M, P, cap_jobs, pl);
+    static thread_local SmallMParams prm;
+    prm.njobs = cap_jobs;
+    prm.units_total = 0;
+    prm.ticket = nullptr;
+    prm.part = nullptr;
+    fill_launch(prm, pl, (int)M);
+    prm.dev_jobs = dev_jobs;
+    prm.dev_njobs = dev_njobs;
+    prm.units_per_job = units;
+    return launch_nt(prm, pl, st, pdl);
 }
 }  // namespace qv
 
@@ -1959,29 +2043,47 @@ static bool job_listable(const qvb8_job &jb) {
            (jb.w->Q + 15) / 16 + NCLASS - 1 <= MAX_TICKET_TILES &&
            !(jb.x_mode == 1 && jb.x_dtype != QVB8_F16);                  // the prescale pass is the single launch's
 }
-// Do the jobs idx[0 .. n) fit one list launch?
-static bool list_fits(const qvb8_job *jobs, const int *idx, int n, int64_t M, Plan &pl) {
+// K-ranges of a job in a list.  The staged activations of a job take P x MP x 2 bytes of shared memory, which the copy
+// rings then lack; a product can be cut into KR equal column ranges that run as consecutive jobs of the list (each CTA
+// meets the same tiles in every range and adds the later ranges' sums to the first's).  Measured on B200 this loses to
+// launching such a job on its own with K split across CTAs (9B-class stack, 8 tokens: 2.88 ms against 2.58 ms; every
+// range boundary drains the rings and restages activations), so it is off unless tuning bit 7 asks for it
+// (qvb8_small_m_set_tuning): the budget below then bounds the staged activations of one range.
+constexpr int64_t XS_BUDGET = 72 * 1024;
+static int k_ranges(int64_t P, int64_t M) {
+    if (!(g_debug & 128)) return 1;
+    const int NT = (int)((M + 7) / 8);
+    const int64_t MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * NT;
+    const int64_t nc = P / KC;
+    for (int64_t kr = 1; kr <= nc; ++kr)
+        if (nc % kr == 0 && (nc / kr) * KC * MP * 2 <= XS_BUDGET) return (int)kr;
+    return (int)nc;
+}
+struct ListEntry { int job, r, kr; };                                   // K-range r of kr of jobs[job]
+// Do the entries e[0 .. n) fit one list launch?
+static bool list_fits(const qvb8_job *jobs, const ListEntry *e, int n, int64_t M, Plan &pl) {
     int64_t Ps[MAX_JOBS];
     int esizes[MAX_JOBS];
     for (int j = 0; j < n; ++j) {
-        Ps[j] = jobs[idx[j]].w->P;
-        esizes[j] = jobs[idx[j]].x_dtype == QVB8_F32 ? 4 : 2;
+        Ps[j] = jobs[e[j].job].w->P / e[j].kr;
+        esizes[j] = jobs[e[j].job].x_dtype == QVB8_F32 ? 4 : 2;
     }
     return make_group_plan(M, Ps, esizes, n, pl);
 }
 
-// Walks the jobs in order and cuts them into list launches: a job joins the open list while it can be listed and the
-// list still fits shared memory (at most MAX_JOBS jobs); jobs that cannot be listed, and lists of one, run as single
-// launches.  on_list(idx, n, plan) / on_single(j) are called in an order that may differ from the jobs' order (the
-// jobs are independent).  Returns the first non-zero status of a callback.
+// Walks the jobs in order and cuts them into list launches: a job (all its K-ranges) joins the open list while it can be
+// listed and the list still fits shared memory (at most MAX_JOBS entries); jobs that cannot be listed, and lists of one
+// whole job, run as single launches.  on_list(entries, n, plan) / on_single(j) are called in an order that may differ
+// from the jobs' order (the jobs are independent).  Returns the first non-zero status of a callback.
 template <typename OnList, typename OnSingle>
 static int walk_group(const qvb8_job *jobs, int njobs, int64_t M, OnList on_list, OnSingle on_single) {
-    int idx[MAX_JOBS], n = 0;
+    ListEntry ent[MAX_JOBS];
+    int n = 0;
     Plan pl{};
     auto flush = [&]() -> int {
         int rc = QVB8_OK;
-        if (n == 1) rc = on_single(idx[0]);
-        else if (n > 1) rc = on_list(idx, n, pl);
+        if (n == 1) rc = on_single(ent[0].job);
+        else if (n > 1) rc = on_list(ent, n, pl);
         n = 0;
         return rc;
     };
@@ -1990,22 +2092,30 @@ static int walk_group(const qvb8_job *jobs, int njobs, int64_t M, OnList on_list
             if (int rc = on_single(j)) return rc;
             continue;
         }
-        idx[n] = j;
-        Plan trial;
-        if (n < MAX_JOBS && list_fits(jobs, idx, n + 1, M, trial)) {
-            pl = trial;
-            ++n;
+        const int kr = k_ranges(jobs[j].w->P, M);
+        if (kr > MAX_JOBS) {
+            if (int rc = on_single(j)) return rc;
             continue;
         }
-        int alone[1] = {j};
-        if (!list_fits(jobs, alone, 1, M, trial)) {                     // too large for any list: on its own, the open list stays open
+        Plan trial;
+        if (n + kr <= MAX_JOBS) {
+            for (int r = 0; r < kr; ++r) ent[n + r] = ListEntry{j, r, kr};
+            if (list_fits(jobs, ent, n + kr, M, trial)) {
+                pl = trial;
+                n += kr;
+                continue;
+            }
+        }
+        ListEntry alone[MAX_JOBS];
+        for (int r = 0; r < kr; ++r) alone[r] = ListEntry{j, r, kr};
+        if (!list_fits(jobs, alone, kr, M, trial)) {                    // fits no list: on its own, the open list stays open
             if (int rc = on_single(j)) return rc;
             continue;
         }
         if (int rc = flush()) return rc;                                // close the open list, start a new one with job j
-        idx[0] = j;
+        for (int r = 0; r < kr; ++r) ent[r] = alone[r];
         pl = trial;
-        n = 1;
+        n = kr;
     }
     return flush();
 }
@@ -2017,7 +2127,7 @@ QV_API int64_t qvb8_small_m_group_scratch_bytes(const qvb8_job *jobs, int njobs,
     for (int j = 0; j < njobs; ++j)
         if (!jobs[j].w || jobs[j].w->P <= 0 || jobs[j].w->Q < 0) return 0;
     int64_t need = 0;
-    walk_group(jobs, njobs, M, [](const int *, int, const Plan &) { return 0; },
+    walk_group(jobs, njobs, M, [](const ListEntry *, int, const Plan &) { return 0; },
                [&](int j) {
                    const int64_t b = qvb8_small_m_scratch_bytes(M, jobs[j].w->Q, jobs[j].w->P);
                    if (b > need) need = b;
@@ -2040,7 +2150,7 @@ QV_API int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *
         const qvb8_job &jb = jobs[j];
         return qvb8_small_m_ex(jb.w, jb.plan, jb.X, jb.x_dtype, jb.x_mode, M, jb.Y, scratch, scratch_bytes, flags, stream);
     };
-    auto on_list = [&](const int *idx, int n, const Plan &pl) -> int {
+    auto on_list = [&](const ListEntry *ent, int n, const Plan &pl) -> int {
         static thread_local SmallMParams prm;
         static thread_local EscPrepassParams esc;
         prm.njobs = n;
@@ -2049,11 +2159,19 @@ QV_API int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *
         esc.tile_start[0] = 0;
         int64_t units = 0;
         for (int j = 0; j < n; ++j) {
-            const qvb8_job &jb = jobs[idx[j]];
-            fill_job(prm.jobs[j], jb.w, jb.plan, jb.X, jb.Y, jb.x_dtype, jb.x_mode, (int)units, jb.w->n_esc > 0 ? 1 : 0);
-            esc.jobs[j] = prm.jobs[j];
-            esc.tile_start[j + 1] = esc.tile_start[j] + (jb.w->n_esc > 0 ? prm.jobs[j].ntiles : 0);
-            units += (int64_t)prm.jobs[j].ntiles * ((prm.jobs[j].nc_total + pl.cps - 1) / pl.cps);
+            const qvb8_job &jb = jobs[ent[j].job];
+            JobDesc &jd = prm.jobs[j];
+            fill_job(jd, jb.w, jb.plan, jb.X, jb.Y, jb.x_dtype, jb.x_mode, (int)units, jb.w->n_esc > 0 ? 1 : 0);
+            const int kr = ent[j].kr, r = ent[j].r;
+            const int nc_r = jd.nc_total / kr, nsk_r = (nc_r + pl.cps - 1) / pl.cps;
+            jd.nc_total = nc_r;
+            jd.kc0 = r * nc_r;
+            jd.nsk_part = nsk_r * kr;
+            if (r > 0) jd.yflags |= 2;
+            // the pre-pass sees a pack once (its first range), with all its columns
+            esc.jobs[j] = jd;
+            esc.tile_start[j + 1] = esc.tile_start[j] + (jb.w->n_esc > 0 && r == 0 ? jd.ntiles : 0);
+            if (r == kr - 1) units += (int64_t)jd.ntiles * jd.nsk_part;
         }
         if (units > 0x7fffffff) return fail(QVB8_ERR_ARG, "qvb8_small_m_group: the list is too long for one launch");
         prm.units_total = (int)units;

@@ -24,7 +24,8 @@ EXPORTS = (
     "qvb8_last_error", "qvb8_version", "qvb8_decode", "qvb8_small_m_scratch_bytes", "qvb8_small_m",
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
-    "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index",
+    "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index", "qvb8_moe_plan_bytes", "qvb8_moe_plan_build",
+    "qvb8_moe_experts_planned", "qvb8_moe_streams",
     "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
     "qvb8_embed_rows", "qvb8_peer_bytes", "qvb8_peer_alloc", "qvb8_peer_open", "qvb8_peer_close", "qvb8_peer_allreduce",
     "qvb8_peer_allreduce_ex", "qvb8_peer_allreduce_local", "qvb8_peer_allgather", "qvb8_peer_allgather_local", "qvb8_device_status_reset", "qvb8r_embed_rows",
@@ -134,6 +135,11 @@ def load() -> ctypes.CDLL:
             lib.qvb8_moe_scratch_bytes.argtypes = [i64, i64, i64, i64, i64, i64, ci]
             lib.qvb8_moe_scratch_bytes.restype = i64
             lib.qvb8_moe_experts.argtypes = [vp, ci, i64, vp, vp, i64, i64, es, es, ci, vp, vp, i64, vp]
+            lib.qvb8_moe_streams.argtypes = [i64, i64, i64, es, es]
+            lib.qvb8_moe_plan_bytes.argtypes = [i64, i64]
+            lib.qvb8_moe_plan_bytes.restype = i64
+            lib.qvb8_moe_plan_build.argtypes = [es, i64, vp, i64, vp]
+            lib.qvb8_moe_experts_planned.argtypes = [vp, ci, i64, vp, vp, i64, i64, es, es, vp, vp, ci, vp, vp, i64, vp]
             lib.qvb8_moe_bad_index.argtypes = [vp, i64, i64, i64, i64, i64, i64, ci, ctypes.POINTER(ctypes.c_int)]
             _lib = lib
     return _lib
@@ -376,6 +382,32 @@ def expert_stack_struct(ids, min_s, tau_s, nbits, bit_off, Q: int, P: int):
     return s, [ids, min_s, tau_s, nbits, bit_off], n // int(Q)
 
 
+def moe_plan_on(stack) -> torch.Tensor | None:
+    """The per-expert plans of a stack (struct, keepalive, E), cached on its `ids` tensor object like a pack's plan.
+    None while a stream capture is in progress and no plan exists yet (the caller then takes the plan-less route)."""
+    st, keep, E = stack
+    ids = keep[0]
+    key = ("moe", st.ids, st.Q, st.P, E, st.bit_off, st.min_s)
+    cache = ids.__dict__.setdefault("_qvb8_plans", {}) if hasattr(ids, "__dict__") else {}
+    plan = cache.get(key)
+    if plan is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        L = load()
+        nbytes = int(L.qvb8_moe_plan_bytes(E, st.Q))
+        plan = torch.empty(nbytes, dtype=torch.uint8, device=ids.device)
+        with torch.cuda.device(ids.device):
+            check(L.qvb8_moe_plan_build(ctypes.byref(st), E, plan.data_ptr(), nbytes, stream_ptr(ids.device)),
+                  "qvb8_moe_plan_build")
+        if len(cache) > 8:
+            cache.clear()
+        cache[key] = plan
+    return plan
+
+
+MOE_STREAM_TOKENS = 8        # up to this many tokens the expert layer runs on the streaming kernel (needs plans)
+
+
 def moe_experts(X: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, up, dn, act: int) -> torch.Tensor:
     """(M, Qdn) in X.dtype.  `up` / `dn` = (struct, keepalive, E) from expert_stack_struct; act 0 gated SiLU, 1 relu^2."""
     ust, ukeep, E = up
@@ -397,8 +429,14 @@ def moe_experts(X: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, up, dn, act
     nbytes = int(lib.qvb8_moe_scratch_bytes(M, topk, E, ust.P, ust.Q, dst.Q, act))
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)       # stream-ordered: torch's allocator
     out = torch.empty((M, dst.Q), dtype=X.dtype, device=dev)
+    uplan = dplan = None
+    if M <= MOE_STREAM_TOKENS and ust.P % 128 == 0 and dst.P % 128 == 0:
+        uplan, dplan = moe_plan_on(up), moe_plan_on(dn)
     with torch.cuda.device(dev):
-        check(lib.qvb8_moe_experts(X.data_ptr(), dtype_code(X.dtype), M, idx.data_ptr(), w.data_ptr(), topk, E,
-                                   ctypes.byref(ust), ctypes.byref(dst), act, out.data_ptr(), scratch.data_ptr(),
-                                   nbytes, stream_ptr(dev)), "qvb8_moe_experts")
+        check(lib.qvb8_moe_experts_planned(X.data_ptr(), dtype_code(X.dtype), M, idx.data_ptr(), w.data_ptr(), topk, E,
+                                           ctypes.byref(ust), ctypes.byref(dst),
+                                           uplan.data_ptr() if uplan is not None and dplan is not None else None,
+                                           dplan.data_ptr() if uplan is not None and dplan is not None else None,
+                                           act, out.data_ptr(), scratch.data_ptr(), nbytes, stream_ptr(dev)),
+              "qvb8_moe_experts")
     return out

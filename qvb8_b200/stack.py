@@ -62,7 +62,10 @@ ROW_PARALLEL = ("o", "down")      # sharded by input columns when world > 1; the
 
 
 def _lib_max_jobs() -> int:
-    return 32                     # jobs one launch of the streaming kernel takes (MAX_JOBS of the kernel source)
+    return 64                     # jobs one launch of the streaming kernel takes (MAX_JOBS of the kernel source)
+
+
+MAX_GROUP_LAYERS = 16             # layers behind one launch at most (four fused projections each)
 
 
 class LinearStack:
@@ -207,15 +210,15 @@ class LinearStack:
         self.peer = None
         if self.reduce and peer:
             from .peer import PeerAllReduce
-            # the largest exchange: the row-parallel outputs of up to eight layers at once (see set_grouping)
+            # the largest exchange: the row-parallel outputs of up to MAX_GROUP_LAYERS layers at once (see set_grouping)
             if self.shard == "pairs":
                 cap = max(max(t.numel() for row in self.y_launch for t in row),
-                          min(self.layers, 8) * self._n_rp * self.M * self.cfg.d_model)
+                          min(self.layers, MAX_GROUP_LAYERS) * self._n_rp * self.M * self.cfg.d_model)
             else:
-                cap = min(self.layers, 8) * self.part.shape[1]
+                cap = min(self.layers, MAX_GROUP_LAYERS) * self.part.shape[1]
             self.peer = PeerAllReduce(dist.group.WORLD, cap, self.device)
         if self.reduce and self.shard == "rows":
-            self.gathered = torch.empty((self.world, min(self.layers, 8) * self.part.shape[1]), dtype=torch.float32,
+            self.gathered = torch.empty((self.world, min(self.layers, MAX_GROUP_LAYERS) * self.part.shape[1]), dtype=torch.float32,
                                         device=self.device)
 
     def _allgather(self, l0: int, l1: int) -> None:
@@ -241,7 +244,7 @@ class LinearStack:
         activation buffers and write separate outputs, so they are independent jobs.  0 = one launch per projection.
         With several ranks the partial sums of a launch's row-parallel projections (o and down of its layers) are
         exchanged by ONE all-reduce after the launch."""
-        self.group_layers = min(int(layers_per_launch), 8)
+        self.group_layers = min(int(layers_per_launch), MAX_GROUP_LAYERS)
         self._groups = None
         self.graph = None
         if self.group_layers > 0:

@@ -106,9 +106,10 @@ def test_fuse_qvb8_block(cuda_lib, M):
         assert isinstance(m, FusedMember)
         got = m(x).float()
         # rows are independent, but a pack of another height may split K differently: equal up to the order of the
-        # fp32 sums, i.e. to an ulp of the bf16 output
-        assert torch.allclose(got, before[n], rtol=2.0 ** -7, atol=2e-3), n
-        assert float((got - before[n]).norm() / before[n].norm()) < 2e-3, n
+        # fp32 sums, i.e. to an ulp of the bf16 product (magnitudes up to 2 here; a member's bias is added after that
+        # rounding, so the absolute error does not shrink with the result)
+        assert torch.allclose(got, before[n], rtol=2.0 ** -7, atol=2.0 ** -6), n
+        assert float((got - before[n]).norm() / before[n].norm()) < 8e-3, n   # (one bf16 ulp is 4e-3 to 8e-3)
     assert blk.self_attn._qvb8_fused.launches == 1 and blk.mlp._qvb8_fused.launches == 1
     assert fuse_same_input(model) == 0                           # nothing left to fuse
 
@@ -134,5 +135,5 @@ def test_fuse_qvb8r_block(cuda_lib, tmp_path):
     assert fuse_same_input(wrap) == 1
     after = [getattr(attn, n)(x).float() for n in ("q_proj", "k_proj", "v_proj")]
     for a, b in zip(after, before):
-        assert a.shape == b.shape and torch.allclose(a, b, rtol=2.0 ** -7, atol=2e-3)
+        assert a.shape == b.shape and torch.allclose(a, b, rtol=2.0 ** -7, atol=2.0 ** -6)
     assert attn._qvb8_fused.launches == 1

@@ -368,7 +368,7 @@ def _job_items(shapes, M, seed, x_dtype=torch.bfloat16, widths=None, esc=0.001):
 @pytest.mark.parametrize("shapes", [
     [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)],              # one 9B-class layer
     [(256, 512), (48, 1024), (16, 128), (1024, 256), (300, 384), (7, 2048), (512, 512)],     # small and ragged
-    [(512, 1024)] * 33,                                                      # more jobs than one launch takes
+    [(512, 1024)] * 67,                                                      # more jobs than one launch takes
 ])
 def test_job_list_equals_separate_calls(cuda_lib, shapes, M):
     from qvb8_b200 import lib
@@ -407,13 +407,36 @@ def test_job_list_mixed_widths_and_range_mode(cuda_lib):
     assert lib.device_status(DEV) == 0
 
 
-def test_job_list_that_does_not_fit_runs_job_by_job(cuda_lib):
-    """16 tokens x 12288 columns of activations do not fit shared memory next to the rings: the call falls back to one
-    launch per job (with scratch for the split-K ones) and gives the same results"""
+@pytest.mark.parametrize("M,shapes", [
+    (16, [(512, 12288), (1024, 4096)]),                    # 16 tokens: six and two column ranges
+    (8, [(640, 8192), (96, 28672), (2048, 512)]),          # two ranges, seven ranges, whole
+    (24, [(320, 4096), (160, 2048)]),
+    (3, [(200, 28672), (64, 128)]),
+])
+def test_job_list_with_column_ranges(cuda_lib, M, shapes):
+    """activations that would crowd the copy rings out of shared memory are staged a column range at a time: the pack
+    runs as consecutive jobs of the list, one per range, and every thread adds the later ranges to what it wrote for
+    the first"""
     from qvb8_b200 import lib
-    items, packs_ = _job_items([(512, 12288), (1024, 4096)], 16, seed=3)
+    items, packs_ = _job_items(shapes, M, seed=3 + M, esc=0.002)
     jl = lib.JobList(items)
+    L = lib.load()
+    try:
+        L.qvb8_small_m_set_tuning(0, 0, 0, 0, 128)                         # column ranges are a tuning option
+        lib.small_m_group(jl)
+        torch.cuda.synchronize()
+        for (st, keep, plan, X, Y), pk in zip(items, packs_):
+            assert rel_fro(Y.cpu().numpy(), lib.small_m(st, keep, X, plan=plan).cpu().numpy()) < 1e-5
+            assert rel_fro(Y.cpu().numpy(), _oracle_y(pk, X)) < TIGHT
+        first = [it[4].clone() for it in items]
+        lib.small_m_group(jl, flags=lib.FLAG_PDL)
+        torch.cuda.synchronize()
+        assert all(torch.equal(a, it[4]) for a, it in zip(first, items))   # one sum order, run after run
+    finally:
+        L.qvb8_small_m_set_tuning(0, 0, 0, 0, 0)
+    # without the option the large jobs run on their own (K split across CTAs): the same results as separate calls
     lib.small_m_group(jl)
     torch.cuda.synchronize()
     for (st, keep, plan, X, Y), pk in zip(items, packs_):
-        assert torch.equal(Y, lib.small_m(st, keep, X, plan=plan))
+        assert rel_fro(Y.cpu().numpy(), lib.small_m(st, keep, X, plan=plan).cpu().numpy()) < 1e-5
+    assert lib.device_status(DEV) == 0
