@@ -581,7 +581,7 @@ def main():
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection (no same-input fusion)")
     ap.add_argument("--group-layers", type=int, default=-1,
                     help="layers whose projections run behind one launch (0 = one launch per projection; "
-                         "-1 = default: 16)")
+                         "-1 = default: 32)")
     ap.add_argument("--shard", default="auto", choices=["auto", "pairs", "rows"],
                     help="N > 1: column/row-parallel pairs + all-reduce, or every projection by output rows + all-gather "
                          "(auto: rows below 8 activation rows, where the full-length rows stream faster; pairs from 8)")
@@ -668,7 +668,7 @@ def main():
         else:
             st.enable_collectives(peer=False)
 
-    group_layers = args.group_layers if args.group_layers >= 0 else 16
+    group_layers = args.group_layers if args.group_layers >= 0 else 32
     if group_layers > 0:
         st.set_grouping(group_layers)
 
@@ -707,11 +707,13 @@ def main():
         block_ms = t.tolist()
     ms = statistics.median(block_ms)
     if world > 1:
-        tot = torch.tensor([st.compressed_bytes, st.n_weights, st.launches_per_step], device=dev, dtype=torch.int64)
+        tot = torch.tensor([st.compressed_bytes, st.n_weights, st.launches_per_step, st.kernels_per_step()], device=dev,
+                           dtype=torch.int64)
         dist.all_reduce(tot)
-        total_bytes, total_weights, launches = (int(v) for v in tot.tolist())
+        total_bytes, total_weights, launches, kernels = (int(v) for v in tot.tolist())
     else:
         total_bytes, total_weights, launches = st.compressed_bytes, st.n_weights, st.launches_per_step
+        kernels = st.kernels_per_step()
     ms_step = ms / args.steps
     gbs = total_bytes / (ms_step * 1e-3) / 1e9
 
@@ -795,7 +797,7 @@ def main():
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_gbs, "unit": UNIT, "h2d_bytes_per_step": st.h2d_bytes(), "d2h_bytes_per_step": st.d2h_bytes(),
                 "ms_per_step": e2e_s * 1e3},
-        "gpu_launches": launches * args.steps,
+        "gpu_launches": kernels * args.steps,
         "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
                      # dram bytes per launch: ncu measured 89.6 MB read + 0.1 MB written for the 89.3 MB launch (gate+up,
                      # 24576 x 4096); traffic grows with the streamed bytes, so the ratio is applied to the average launch

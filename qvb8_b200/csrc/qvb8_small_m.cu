@@ -35,7 +35,7 @@
 // while X was staged), adds the escape corrections, and writes the result.  K-ranges of one tile are added in range
 // order by whichever CTA finishes the tile last (a ticket counter per tile).
 //
-// Lists.  One launch can run up to 64 independent products (qvb8_small_m_group): the job table travels by value in
+// Lists.  One launch can run up to 128 independent products (qvb8_small_m_group): the job table travels by value in
 // the kernel's parameters.  All (tile, stage) units of the list form ONE sequence that is cut into equal contiguous
 // per-CTA ranges, so a CTA meets one or two jobs per launch and its rings never drain at a job boundary; at a
 // boundary the consumer warps restage X for the next job from global memory while the producer is already copying
@@ -641,7 +641,11 @@ __global__ void __launch_bounds__(1024) tile_escapes_kernel(TileDesc *__restrict
     }
 }
 
-constexpr int MAX_JOBS = 64;   // jobs behind one launch (the table travels in the kernel's parameters: 6 KB of the 32 KB
+constexpr int SMEM_JOBS = 8;   // jobs of a CTA's own range kept in shared memory
+__host__ __device__ constexpr int64_t job_table_bytes(int njobs) {
+    return ((int64_t)(njobs < SMEM_JOBS ? njobs : SMEM_JOBS) * 96 + 127) / 128 * 128;
+}
+constexpr int MAX_JOBS = 128;  // jobs behind one launch (the table travels in the kernel's parameters: 12 KB of the 32 KB
                                // a launch may carry)
 
 struct SmallMParams {
@@ -942,8 +946,10 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
     //   [activation sums by consumer warp, two sets] [exchange buffers of tiles shared by pipes]
     //   per pipe: [ring: nstg stages of 16 rows] [side ring: NSIDE x (descriptor + escapes)] [two hand-over buffers]
     //             [escape corrections]
-    JobDesc *jobs = reinterpret_cast<JobDesc *>(smem);
-    const size_t jobs_bytes = (size_t)((p.njobs * (int)sizeof(JobDesc) + 127) / 128 * 128);
+    // The table in shared memory holds only the jobs THIS CTA's range touches (a list's CTA meets one or two; SMEM_JOBS
+    // at most -- a range that touches more reads the launch's table where it lies).
+    JobDesc *jobs_sm = reinterpret_cast<JobDesc *>(smem);
+    const size_t jobs_bytes = (size_t)job_table_bytes(p.njobs);
     __half *xs_a = reinterpret_cast<__half *>(smem + jobs_bytes);
     __half *xs_b = DUAL ? xs_a + p.xs_halves : xs_a;
     uint32_t *zero16 = reinterpret_cast<uint32_t *>(xs_a + (DUAL ? 2 : 1) * p.xs_halves);
@@ -976,8 +982,15 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         if (devlist) {
             j = min(njobs - 1, (int)(lo / max(1, p.units_per_job)));
         } else {
-            for (int q = 1; q < njobs; ++q)                             // the job that holds the range's first unit (the
-                if (jtab[q].unit0 <= lo && jtab[q].unit0 != jtab[j].unit0) j = q;   // first K-range of its pack)
+            // the job that holds the range's first unit (the first K-range of its pack): unit0 never decreases along
+            // the table, so a bisection finds the last job with unit0 <= lo, and a short walk back its pack's first range
+            int a = 0, b = njobs - 1;
+            while (a < b) {
+                const int mid = (a + b + 1) >> 1;
+                if (jtab[mid].unit0 <= lo) a = mid; else b = mid - 1;
+            }
+            while (a > 0 && jtab[a - 1].unit0 == jtab[a].unit0) --a;
+            j = a;
         }
         int jlast = -1;
         jfirst = njobs;
@@ -1006,11 +1019,14 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             }
         }
     }
-    // the job table: from the launch parameters into shared memory, where every warp reads it at each job boundary
-    {
-        const uint32_t *src = reinterpret_cast<const uint32_t *>(jtab);
-        uint32_t *dst = reinterpret_cast<uint32_t *>(jobs);
-        for (int i = tid; i < njobs * (int)(sizeof(JobDesc) / 4); i += blockDim.x) dst[i] = src[i];
+    // the CTA's jobs: from the launch parameters (or the device-resident table) into shared memory, where every warp
+    // reads them at each job boundary; indexed by job number like the table they come from
+    const bool table_in_smem = jcount <= SMEM_JOBS;
+    const JobDesc *jobs = table_in_smem ? jobs_sm - jfirst : jtab;
+    if (table_in_smem) {
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(jtab + jfirst);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(jobs_sm);
+        for (int i = tid; i < jcount * (int)(sizeof(JobDesc) / 4); i += blockDim.x) dst[i] = src[i];
     }
     // barriers: one thread each
     {
@@ -1570,7 +1586,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         __syncthreads();
         if (last_range) {
             __threadfence();
-            const JobDesc &jd = jobs[0];
+            const JobDesc &jd = jtab[0];
             int ct0, ct1;
             cta_tiles(jd.ntiles, gridDim.x, blockIdx.x, ct0, ct1);      // (a single job is never rotated)
             const int per_tile = 16 * M;
@@ -1719,7 +1735,7 @@ static bool make_group_plan(int64_t M, const int64_t *Ps, const int *esizes, int
     }
     (void)esizes;
     const int64_t cta_bytes = MAX_DYN_SMEM - 256;
-    const int64_t jobs_bytes = ((int64_t)njobs * (int64_t)sizeof(JobDesc) + 127) / 128 * 128;
+    const int64_t jobs_bytes = job_table_bytes(njobs);
     pl.esc_cap = ESC_CAP_MIN;                                           // (a list's escapes are applied by the pre-pass)
     const int64_t pipe_fixed = (int64_t)NSIDE * side_slot_bytes(pl.esc_cap) + (int64_t)2 * NW * 4 * pl.NT * 32 * 4 + corr_bytes(M, pl.esc_cap);
     const int64_t shared_fixed = jobs_bytes + 128 + psum_bytes_for(npipe, M) + ((XCH_SLOTS + npipe) * 16 * M * 4 + 127) / 128 * 128;

@@ -62,10 +62,10 @@ ROW_PARALLEL = ("o", "down")      # sharded by input columns when world > 1; the
 
 
 def _lib_max_jobs() -> int:
-    return 64                     # jobs one launch of the streaming kernel takes (MAX_JOBS of the kernel source)
+    return 128                    # jobs one launch of the streaming kernel takes (MAX_JOBS of the kernel source)
 
 
-MAX_GROUP_LAYERS = 16             # layers behind one launch at most (four fused projections each)
+MAX_GROUP_LAYERS = 32             # layers behind one launch at most (four fused projections each)
 
 
 class LinearStack:
@@ -260,6 +260,20 @@ class LinearStack:
             self.launches_per_step = len(self._groups)
         else:
             self.launches_per_step = sum(len(row) for row in self.launches)
+
+    def kernels_per_step(self) -> int:
+        """Kernels of this library one step launches: per list launch the streaming kernel, the escape pre-pass when a
+        pack of the list carries escapes, and the exchange kernel when ranks exchange; per single launch one (a lower
+        bound: a list whose jobs do not all fit one launch is cut into several)."""
+        extra = 1 if self.reduce else 0
+        if self._groups is not None:
+            n = 0
+            for l0, l1 in self._group_layers:
+                esc = any(pk.esc_idx.numel() > 0 for li in range(l0, l1) for _, pk, *_ in self.launches[li])
+                n += 1 + (1 if esc else 0) + extra
+            return n
+        per_layer_exchanges = (self._n_rp if self.shard == "pairs" else 1) * extra
+        return sum(len(row) + per_layer_exchanges for row in self.launches)
 
     def run_eager(self) -> None:
         """One pass over every launch of every layer on the current stream."""

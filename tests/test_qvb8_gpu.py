@@ -368,7 +368,7 @@ def _job_items(shapes, M, seed, x_dtype=torch.bfloat16, widths=None, esc=0.001):
 @pytest.mark.parametrize("shapes", [
     [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)],              # one 9B-class layer
     [(256, 512), (48, 1024), (16, 128), (1024, 256), (300, 384), (7, 2048), (512, 512)],     # small and ragged
-    [(512, 1024)] * 67,                                                      # more jobs than one launch takes
+    [(512, 1024)] * 131,                                                     # more jobs than one launch takes
 ])
 def test_job_list_equals_separate_calls(cuda_lib, shapes, M):
     from qvb8_b200 import lib
