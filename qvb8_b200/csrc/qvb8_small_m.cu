@@ -110,8 +110,13 @@ __host__ __device__ constexpr int esc_cap_for(int64_t P) {
 
 // Bytes of a pipe's escape area: the finishing warp's corrections [16][M] and, for one token, a staging array of
 // (difference, activation) pairs of the tile's entries (see the finishing warp).
+__host__ __device__ constexpr int64_t corr_stride_bytes(int64_t M) { return (16 * M * 4 + 127) / 128 * 128; }
+constexpr int INLINE_ESC_MAX_M = 4;       // lists of up to this many tokens sum their escapes on the consumer warps
+__host__ __device__ constexpr int64_t corr_buffers(int64_t M) { return M <= INLINE_ESC_MAX_M ? 2 * NW : 2; }
 __host__ __device__ constexpr int64_t corr_bytes(int64_t M, int esc_cap) {
-    return (16 * M * 4 + 127) / 128 * 128 + (M == 1 ? (int64_t)esc_cap * 8 : 0);
+    // [16][M] buffers: a single launch's finishing warp uses the first; a list's consumer warps write one each per visit,
+    // two sets alternating like the hand-over buffers ([2][NW][16][M]); then the one-token staging array
+    return corr_buffers(M) * corr_stride_bytes(M) + (M == 1 ? (int64_t)esc_cap * 8 : 0);
 }
 
 // Per-CTA control block in static shared memory.
@@ -1106,7 +1111,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             const int NC = cg.NC, kc0 = cg.kc0;
             const int cnb = nb, ccnt = cnt;
             const bool planned = jd.esc_ent != nullptr && !(jd.yflags & 1);   // (a pre-pass has applied the job's escapes)
-            const uint32_t ebytes = planned ? (uint32_t)(min((nesc + 1) & ~1, esc_cap) * 8) : 0u;
+            const uint32_t ebytes = planned ? (uint32_t)(min((nesc + 1) & ~1, esc_cap) * 8) : 0u;   // (in-line: yflags bit 2)
             const EscEntry *esrc = jd.esc_ent + esc0;
             const uint32_t step = (uint32_t)(cps * 16 * cnb);           // bytes of a row per full stage
             const uint8_t *src = jd.ids + ((uint64_t)b16 + (uint64_t)kc0 * cnb) * 16u + (size_t)v.sb * step;
@@ -1174,7 +1179,8 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             const Run &run = gm.run;
             const int kc0 = gm.kc0, NC = gm.NC, NSK = gm.NSK;
             const __half *xsa = xs_a;
-            const bool planned = jd.esc_ent != nullptr && !(jd.yflags & 1);   // escapes corrected here (else: by the pre-pass)
+            const bool inline_esc = jd.esc_ent != nullptr && (jd.yflags & 4);   // a consumer warp sums each tile's corrections
+            const bool planned = jd.esc_ent != nullptr && !(jd.yflags & 5);   // escapes corrected here (else: pre-pass / in-line)
             const bool add_to_y = jd.esc_ent != nullptr && (jd.yflags & 1);   // Y holds the pre-pass's corrections: add to it
             const bool later_range = (jd.yflags & 2) != 0;                 // Y holds this thread's sums of the earlier K-ranges
             const bool prescaled = njobs == 1 && jd.x_mode == 1 && jd.x_dtype != QVB8_F16;
@@ -1247,7 +1253,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                     // multiply-adds as below, so the result has the same bits.  This warp shares its scheduler with
                     // issue-bound consumer warps: a long serial loop here ends after the stream and delays the CTA's end.
                     const int clo = (kc0 + v.sb * cps) * KC, chi = (kc0 + min(v.se * cps, NC)) * KC, cbase = kc0 * KC;
-                    float2 *pd = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(corr) + (16 * M * 4 + 127) / 128 * 128);
+                    float2 *pd = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(corr) + corr_buffers(M) * corr_stride_bytes(M));
                     const int ne = min(d->nesc, esc_cap);
                     for (int e = lane; e < ne; e += 32) {
                         const EscEntry en = ent[e];
@@ -1332,7 +1338,23 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                         }
                         acc[n][k] = a;
                     }
-                __syncwarp();                                           // every lane is done with the buffer
+                // in-line escapes: the visit's corrections lie in the correction buffers of the same parity, one partial
+                // sum per consumer warp, written before the warps handed over their sums
+                float cin[NT][4];
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int m = 8 * n + 2 * t + (k & 1);
+                        float c = 0.f;
+                        if (inline_esc && m < M) {
+                            const float *cw = corr + rb * NW * (int)(corr_stride_bytes(M) / 4) + (g + 8 * (k >> 1)) * M + m;
+#pragma unroll
+                            for (int w = 0; w < NW; ++w) c += cw[w * (int)(corr_stride_bytes(M) / 4)];   // warp order
+                        }
+                        cin[n][k] = c;
+                    }
+                __syncwarp();                                           // every lane is done with the buffers
                 if (lane == 0) mbar_arrive(smem_u32(&pc_.red_empty[rb]));
                 // y = tau_s * sum(x * id) + min_s * sum(x) + corrections for rows g, g+8 and tokens 8n+2t, 8n+2t+1
                 // (per-element rows arrive complete); the min_s term goes with the visit that holds the first stage
@@ -1351,6 +1373,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                                     if (v.sb == 0) val = __fmaf_rn(myms[hrow], sumx_nt[n][k], val);
                                 }
                                 if (planned) val += corr[(g + 8 * hrow) * M + m];
+                                if (inline_esc) val += cin[n][2 * hrow + k];
                                 if (prescaled) val *= pow2f(ctl.kexp[m]);
                             }
                             y[hrow][n][k] = val;
@@ -1440,6 +1463,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
             const JobGeom gm = job_geom<NPIPE>(p, ls, jd, split, pipe);
             const Run &run = gm.run;
             const int kc0 = gm.kc0, NC = gm.NC;
+            const bool inline_esc = jd.esc_ent != nullptr && (jd.yflags & 4);   // this job's escapes are summed here
             float *psum_w = psum + ((kj & 1) * CWARPS + cwarp) * M;
             if (kj == 0) {
                 // ---- activations of the first job's K-range as fp16 in fragment order (after the previous kernel in the
@@ -1510,6 +1534,51 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 float acc[NT][4];
 #pragma unroll
                 for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+                if (inline_esc) {
+                    // ---- in-line escapes.  Lane (g, t) of warp w sums, for rows g and g + 8 and its tokens,
+                    // x * (exact - band) over every fourth entry of the row (entries w, w + 4, ... of the tile's list,
+                    // those of the visit's columns) and leaves the partial sums for the finishing warp, which adds the four
+                    // warps' parts in warp order.  The buffers of this visit's parity are free once the finishing warp has
+                    // taken the visit before last.  The code runs with every tile, so it stays warm, unlike the same sums
+                    // on the finishing warp; spread over the four warps it delays none of them against the others.
+                    if (!mbar_wait(red_empty, red_par, abort_flag, 4)) { alive = false; break; }
+                    float *cb = corr + (rb * NW + warp) * (int)(corr_stride_bytes(M) / 4);
+                    const EscEntry *ent = reinterpret_cast<const EscEntry *>(side + sslot * side_bytes + DESC_SLOT);
+                    const EscEntry *gent = jd.esc_ent + d->esc0;        // the same list in global memory (for the overflow)
+                    const int clo = (kc0 + v.sb * cps) * KC, chi = (kc0 + min(v.se * cps, NC)) * KC, cbase = kc0 * KC;
+                    if (2 * t < M) {
+#pragma unroll
+                        for (int hrow = 0; hrow < 2; ++hrow) {
+                            const int rs = g + 8 * hrow;
+                            float a[NT][2];
+#pragma unroll
+                            for (int n = 0; n < NT; ++n) a[n][0] = a[n][1] = 0.f;
+                            if (d->row[rs] >= 0) {
+                                const int ce0 = d->e0[rs], ce1 = d->e1[rs];
+                                for (int e = ce0 + ((warp - ce0) & (NW - 1)); e < ce1; e += NW) {
+                                    EscEntry en;
+                                    if (e < esc_cap) en = ent[e];
+                                    else { en.col = __ldg(&gent[e].col); en.delta = __ldg(&gent[e].delta); }
+                                    if (en.col >= clo && en.col < chi) {
+                                        const int cc = en.col - cbase;
+                                        const __half *xp = xsa + ((size_t)slot_of(cc, 2 * t, MP) << 3) + pos_a(cc & 7);
+#pragma unroll
+                                        for (int n = 0; n < NT; ++n)
+#pragma unroll
+                                            for (int k = 0; k < 2; ++k)
+                                                if (8 * n + 2 * t + k < M)   // consecutive tokens lie one slot (8 halves) apart
+                                                    a[n][k] = __fmaf_rn(__half2float(xp[(8 * n + k) * 8]), en.delta, a[n][k]);
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                                for (int k = 0; k < 2; ++k)
+                                    if (8 * n + 2 * t + k < M) cb[rs * M + 8 * n + 2 * t + k] = a[n][k];
+                        }
+                    }
+                }
                 if (nb == 0) {
                     // per-element class: rows the fragment path cannot read (width outside 3..8, or a row that does not
                     // start on a 16-byte boundary).  One row per warp at a time, ids byte-wise from global memory; the
@@ -1736,8 +1805,11 @@ static bool make_group_plan(int64_t M, const int64_t *Ps, const int *esizes, int
     (void)esizes;
     const int64_t cta_bytes = MAX_DYN_SMEM - 256;
     const int64_t jobs_bytes = job_table_bytes(njobs);
-    pl.esc_cap = ESC_CAP_MIN;                                           // (a list's escapes are applied by the pre-pass)
-    const int64_t pipe_fixed = (int64_t)NSIDE * side_slot_bytes(pl.esc_cap) + (int64_t)2 * NW * 4 * pl.NT * 32 * 4 + corr_bytes(M, pl.esc_cap);
+    pl.esc_cap = ESC_CAP_MIN;
+    auto pipe_fixed_for = [&](int cap) {
+        return (int64_t)NSIDE * side_slot_bytes(cap) + (int64_t)2 * NW * 4 * pl.NT * 32 * 4 + corr_bytes(M, cap);
+    };
+    int64_t pipe_fixed = pipe_fixed_for(pl.esc_cap);
     const int64_t shared_fixed = jobs_bytes + 128 + psum_bytes_for(npipe, M) + ((XCH_SLOTS + npipe) * 16 * M * 4 + 127) / 128 * 128;
     const int64_t xs_bytes = pmax * pl.MP * 2;
     int cps = g_force_cps ? g_force_cps : (pmin / KC >= 16 ? 8 : 4);
@@ -1762,6 +1834,14 @@ static bool make_group_plan(int64_t M, const int64_t *Ps, const int *esizes, int
     if (g_force_nstg && g_force_nstg < nstg) nstg = g_force_nstg;
     if (nstg > MAX_STAGES) nstg = MAX_STAGES;
     pl.nstg = nstg;
+    // escape entries that travel with a tile's descriptor (the in-line escape sums read them from the side slot; what
+    // does not fit is read from global memory): as many as the widest job's tiles typically hold, if that costs no
+    // ring stage
+    for (int cap : {esc_cap_for(pmax) < 256 ? esc_cap_for(pmax) : 256, 128}) {
+        if (cap <= pl.esc_cap) continue;
+        const int64_t room = (cta_bytes - shared_fixed - xs_bytes) / npipe - pipe_fixed_for(cap);
+        if (room >= (int64_t)nstg * pl.slot_bytes) { pl.esc_cap = cap; pipe_fixed = pipe_fixed_for(cap); break; }
+    }
     pl.S = 1;
     pl.nc_per = (int)(pmax / KC);
     pl.nc_total = pl.nc_per;
@@ -2169,6 +2249,12 @@ QV_API int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *
     auto on_list = [&](const ListEntry *ent, int n, const Plan &pl) -> int {
         static thread_local SmallMParams prm;
         static thread_local EscPrepassParams esc;
+        // A list's escapes: a pre-pass kernel leaves the corrections in Y before the streaming kernel adds its sums.  The
+        // alternative (tuning bit 5, up to INLINE_ESC_MAX_M tokens): the four consumer warps sum each tile's entries in
+        // line, a quarter each -- correct and tested, but measured slower on B200 (9B-class stack, one token, same box:
+        // 1.23-1.28 ms against 1.17-1.21 ms with the pre-pass, whose 56 us it saves: the sums sit in front of every
+        // tile's stream on all four warps).
+        const bool use_prepass = (g_debug & 32) == 0 || M > INLINE_ESC_MAX_M;
         prm.njobs = n;
         esc.njobs = n;
         esc.M = (int)M;
@@ -2177,7 +2263,8 @@ QV_API int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *
         for (int j = 0; j < n; ++j) {
             const qvb8_job &jb = jobs[ent[j].job];
             JobDesc &jd = prm.jobs[j];
-            fill_job(jd, jb.w, jb.plan, jb.X, jb.Y, jb.x_dtype, jb.x_mode, (int)units, jb.w->n_esc > 0 ? 1 : 0);
+            fill_job(jd, jb.w, jb.plan, jb.X, jb.Y, jb.x_dtype, jb.x_mode, (int)units, jb.w->n_esc > 0 && use_prepass ? 1 : 0);
+            if (jb.w->n_esc > 0 && !use_prepass) jd.yflags |= 4;
             const int kr = ent[j].kr, r = ent[j].r;
             const int nc_r = jd.nc_total / kr, nsk_r = (nc_r + pl.cps - 1) / pl.cps;
             jd.nc_total = nc_r;
@@ -2186,12 +2273,12 @@ QV_API int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *
             if (r > 0) jd.yflags |= 2;
             // the pre-pass sees a pack once (its first range), with all its columns
             esc.jobs[j] = jd;
-            esc.tile_start[j + 1] = esc.tile_start[j] + (jb.w->n_esc > 0 && r == 0 ? jd.ntiles : 0);
+            esc.tile_start[j + 1] = esc.tile_start[j] + (jb.w->n_esc > 0 && r == 0 && use_prepass ? jd.ntiles : 0);
             if (r == kr - 1) units += (int64_t)jd.ntiles * jd.nsk_part;
         }
         if (units > 0x7fffffff) return fail(QVB8_ERR_ARG, "qvb8_small_m_group: the list is too long for one launch");
         prm.units_total = (int)units;
-        if (esc.tile_start[n] > 0 && !(g_debug & 32)) {                // the escapes first: corrections into Y (debug bit 5: skipped)
+        if (esc.tile_start[n] > 0) {                                   // the escapes first: corrections into Y
             const int64_t threads = (int64_t)esc.tile_start[n] * 16;
             cudaLaunchConfig_t cfg{};
             cfg.gridDim = dim3((unsigned)((threads + 127) / 128));

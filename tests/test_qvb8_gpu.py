@@ -392,6 +392,36 @@ def test_job_list_equals_separate_calls(cuda_lib, shapes, M):
     assert lib.device_status(DEV) == 0
 
 
+def test_job_list_escapes_by_pre_pass_and_in_line(cuda_lib):
+    """a list's escapes are applied by the pre-pass kernel; the tuning alternative sums them on the consumer warps, tile
+    by tile (here with more entries per tile than travel with a descriptor: the rest comes from global memory) -- the
+    same results"""
+    from qvb8_b200 import lib
+    L = lib.load()
+    for M in (1, 3, 4, 8):
+        items, packs_ = _job_items([(256, 4096), (200, 1024), (48, 12288), (512, 512)], M, seed=40 + M, esc=0.02)
+        jl = lib.JobList(items)
+        lib.small_m_group(jl)
+        torch.cuda.synchronize()
+        first = [it[4].clone() for it in items]
+        for y, (st, keep, plan, X, Y), pk in zip(first, items, packs_):
+            assert rel_fro(y.cpu().numpy(), _oracle_y(pk, X)) < TIGHT
+        try:
+            L.qvb8_small_m_set_tuning(0, 0, 0, 0, 32)                      # in line (8 tokens: still the pre-pass)
+            lib.small_m_group(jl)
+            torch.cuda.synchronize()
+            second = [it[4].clone() for it in items]
+            lib.small_m_group(jl, flags=lib.FLAG_PDL)
+            torch.cuda.synchronize()
+            assert all(torch.equal(a, it[4]) for a, it in zip(second, items))     # one sum order
+        finally:
+            L.qvb8_small_m_set_tuning(0, 0, 0, 0, 0)
+        for y, pk, it in zip(first, packs_, items):
+            assert rel_fro(it[4].cpu().numpy(), y.cpu().numpy()) < 1e-5
+            assert rel_fro(it[4].cpu().numpy(), _oracle_y(pk, it[3])) < TIGHT
+    assert lib.device_status(DEV) == 0
+
+
 def test_job_list_mixed_widths_and_range_mode(cuda_lib):
     from qvb8_b200 import lib
     shapes = [(320, 1024), (160, 512), (640, 1024), (96, 2048), (320, 1024)]
