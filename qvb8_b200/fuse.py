@@ -186,3 +186,64 @@ def concat_qvb8r(members: list[dict]) -> tuple[dict, list[int]]:
         acc += int(m["Q"])
         splits.append(acc)
     return fused, splits
+
+
+def qvb8r_shard_bounds(d: dict, world: int) -> list[int]:
+    """Tile boundaries t[0] = 0 <= t[1] <= ... <= t[world] = tiles that split an entropy-coded tensor into `world` runs of
+    whole tiles with about the same number of coded words each (a rank's time is its decoder's time)."""
+    import numpy as np
+    off = np.asarray(d["tile_off"], np.int64)
+    nt = off.size - 1
+    total = int(off[-1])
+    cuts = [0]
+    for r in range(1, world):
+        t = int(np.searchsorted(off, total * r / world, side="left"))
+        cuts.append(min(nt, max(cuts[-1], t)))
+    return cuts + [nt]
+
+
+def qvb8r_tile_shard(d: dict, t0: int, t1: int) -> tuple[dict, "np.ndarray"]:
+    """Tiles [t0, t1) of a parsed ``.qvb8r`` tensor as a tensor of its own, made from the file's arrays without
+    re-encoding: rANS streams run per tile, so a rank can hold a contiguous run of tiles (their words, states and word
+    offsets), the class tables, and the per-row metadata and escapes of the rows those tiles code.  A QVB8R tensor cannot
+    be cut by columns (a stream is sequential along the row) and not by arbitrary rows either (tiles hold the rows in
+    the coder's sorted order), so tiles are the unit -- the output rows of a shard are scattered over the whole tensor.
+
+    Returns (dict, rows): the dict has the same keys as the parsed file, with the shard's rows numbered 0 .. Q' - 1 in the
+    coder's sorted order; rows[i] is the row of the whole tensor that the shard's output row i is.  The whole product is
+    ``y[..., rows_r] = y_r`` over the shards r."""
+    import numpy as np
+    tiles = np.asarray(d["tiles"], np.int64).reshape(-1, 3)
+    if not (0 <= t0 <= t1 <= tiles.shape[0]):
+        raise ValueError("qvb8r_tile_shard: tile range outside the tensor")
+    P = int(d["P"])
+    off = np.asarray(d["tile_off"], np.int64)
+    perm = np.asarray(d["perm"], np.int64)
+    if t0 == t1:
+        r0 = r1 = 0
+    else:
+        r0 = int(tiles[t0, 1])
+        r1 = int(tiles[t1 - 1, 1] + tiles[t1 - 1, 2])
+    rows = perm[r0:r1]                                         # sorted position r0 + i -> row of the whole tensor
+    local = np.full(int(d["Q"]), -1, np.int64)
+    local[rows] = np.arange(rows.size)
+    sub = tiles[t0:t1].copy()
+    sub[:, 1] -= r0
+    ei = np.asarray(d["esc_idx"], np.int64)
+    mine = local[ei // P] >= 0 if ei.size else np.zeros(0, bool)
+    new_idx = local[ei[mine] // P] * P + ei[mine] % P
+    order = np.argsort(new_idx, kind="stable")
+    first = d
+    shard = dict(
+        Q=int(rows.size), P=P, K=int(d["K"]), N=int(d["N"]), T=int(d["T"]),
+        perm=np.arange(rows.size, dtype=np.int32), freq=np.asarray(d["freq"]),
+        tiles=sub.astype(np.int32), tile_off=(off[t0:t1 + 1] - off[t0]).astype(np.asarray(first["tile_off"]).dtype),
+        states=np.asarray(d["states"], np.uint64).reshape(-1, 32)[t0:t1].copy(),
+        words=np.asarray(d["words"], np.uint32)[int(off[t0]):int(off[t1])].copy(),
+        drow=np.asarray(d["drow"])[rows], min_s=np.asarray(d["min_s"], np.float32)[rows],
+        tau_s=np.asarray(d["tau_s"], np.float32)[rows],
+        esc_idx=new_idx[order], esc_val=np.asarray(d["esc_val"], np.float32)[mine][order],
+        esc_delta=np.asarray(d["esc_delta"], np.float32)[mine][order],
+        tau=float(d.get("tau", 0.0)), max_err=float(d.get("max_err", 0.0)))
+    return shard, rows
+

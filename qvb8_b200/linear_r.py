@@ -219,3 +219,67 @@ class QVBandLinearV8R(nn.Module):
         if self.esc_flat.numel():
             W.view(-1)[self.esc_flat] = self.esc_val.to(W.dtype)
         return W if W.dtype == dtype else W.to(dtype)
+
+
+class QVBandLinearV8RShard(nn.Module):
+    """One rank's share of an entropy-coded linear split over `world` ranks by TILES (the only cut a ``.qvb8r`` tensor
+    allows without re-encoding, :func:`qvb8_b200.fuse.qvb8r_tile_shard`): the rank decodes and multiplies a contiguous
+    run of tiles -- about 1 / world of the coded words -- and the ranks' output rows, which lie scattered over the whole
+    tensor, are exchanged by one all-gather (padded to the largest shard) and put in place.
+
+    `group`: a torch.distributed group, or None for a shard used on its own (``forward`` then returns the local rows and
+    ``rows`` says which rows of the whole tensor they are)."""
+
+    def __init__(self, d: dict, rank: int, world: int, *, bias=None, device="cuda", group=None):
+        super().__init__()
+        from . import fuse
+        if not (0 <= rank < world):
+            raise ValueError("rank outside the world")
+        bounds = fuse.qvb8r_shard_bounds(d, world)
+        self.rank, self.world, self.group = int(rank), int(world), group
+        self.out_features, self.in_features = int(d["Q"]), int(d["P"])
+        shard, rows = fuse.qvb8r_tile_shard(d, bounds[rank], bounds[rank + 1])
+        self.local = QVBandLinearV8R(shard, device=device) if shard["Q"] else None
+        dev = torch.device(device)
+        self.register_buffer("rows", torch.from_numpy(np.ascontiguousarray(rows, dtype=np.int64)).to(dev), persistent=False)
+        # every rank's rows (the same on all ranks: the bounds follow from the file alone), padded to the largest shard
+        all_rows = [fuse.qvb8r_tile_shard(d, bounds[r], bounds[r + 1])[1] for r in range(world)] if world > 1 else [rows]
+        self.pad = max(1, max(len(r) for r in all_rows))
+        place = np.full((world, self.pad), self.out_features, np.int64)          # padding lands in a spare column
+        for r, rr in enumerate(all_rows):
+            place[r, :len(rr)] = rr
+        self.register_buffer("place", torch.from_numpy(place.reshape(-1)).to(dev), persistent=False)
+        self.bias = nn.Parameter(torch.as_tensor(bias).detach().to(dev), requires_grad=False) if bias is not None else None
+
+    def local_product(self, x: torch.Tensor) -> torch.Tensor:
+        """(.., rows.numel()) -- this rank's output rows, in the order of ``rows``."""
+        if self.local is None:
+            return torch.zeros(*x.shape[:-1], 0, dtype=x.dtype, device=self.rows.device)
+        return self.local(x)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.local_product(x)
+        if self.world > 1 and self.group is None:
+            return y                                                     # a shard on its own: the local rows
+        out = gather_rows(y, self.place, self.pad, self.world, self.out_features, self.group)
+        if self.bias is not None:
+            out = out + self.bias.to(out.dtype)
+        return out
+
+
+def gather_rows(y: torch.Tensor, place: torch.Tensor, pad: int, world: int, out_features: int, group) -> torch.Tensor:
+    """The whole (.., out_features) product from every rank's local rows y (.., n_r): one all-gather of the rows padded
+    to `pad` columns, then every column put where `place` (world * pad positions, `out_features` = discard) says."""
+    lead = y.shape[:-1]
+    padded = torch.zeros(*lead, pad, dtype=y.dtype, device=y.device)
+    padded[..., :y.shape[-1]] = y
+    if world > 1:
+        import torch.distributed as dist
+        parts = torch.empty(world, *lead, pad, dtype=y.dtype, device=y.device)
+        dist.all_gather_into_tensor(parts.view(-1), padded.contiguous().view(-1), group=group)   # (1-D: every backend takes it)
+        flat = parts.movedim(0, -2).reshape(*lead, world * pad)
+    else:
+        flat = padded
+    out = torch.empty(*lead, out_features + 1, dtype=y.dtype, device=y.device)
+    out[..., place] = flat
+    return out[..., :out_features]

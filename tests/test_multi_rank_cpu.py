@@ -112,6 +112,46 @@ def test_expert_parallel_partial_sums_equal_the_whole_layer(tmp_path):
     assert np.allclose(np.load(tmp_path / "moe.npy"), want, rtol=1e-12, atol=1e-12)
 
 
+def _qvb8r_worker(rank: int, world: int, port: int, out_dir: str):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from qvb8_b200 import fuse
+        from qvb8_b200.linear_r import gather_rows
+        Q, P, M = 150, 128, 3
+        d = synth.encode_qvb8r(synth.synth_weight(Q, P, 77), tau=2e-3, K=3, T=4)       # every rank reads the whole file
+        bounds = fuse.qvb8r_shard_bounds(d, world)
+        shards = [fuse.qvb8r_tile_shard(d, bounds[r], bounds[r + 1]) for r in range(world)]
+        mine, rows = shards[rank]
+        X = synth.synth_activation(M, P, seed=5).float().numpy()
+        y = torch.from_numpy(oracle.matmul_f32w(X, oracle.qvb8r_dense(mine), narrow_x=True)) if mine["Q"] else \
+            torch.zeros(M, 0, dtype=torch.float64)
+        pad = max(len(r) for _, r in shards)
+        place = np.full((world, pad), Q, np.int64)
+        for r, (_, rr) in enumerate(shards):
+            place[r, :len(rr)] = rr
+        out = gather_rows(y, torch.from_numpy(place.reshape(-1)), pad, world, Q, dist.group.WORLD)
+        np.save(os.path.join(out_dir, f"qvb8r_{rank}.npy"), out.numpy())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_qvb8r_tile_shards_gathered_equal_the_whole(tmp_path):
+    """an entropy-coded tensor split by tiles over three ranks: every rank's product rows, gathered and put in place,
+    are the whole product bit for bit on every rank (rows are decoded from the same words)"""
+    world = 3
+    mp.spawn(_qvb8r_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    Q, P, M = 150, 128, 3
+    d = synth.encode_qvb8r(synth.synth_weight(Q, P, 77), tau=2e-3, K=3, T=4)
+    X = synth.synth_activation(M, P, seed=5).float().numpy()
+    want = oracle.matmul_f32w(X, oracle.qvb8r_dense(d), narrow_x=True)
+    for r in range(world):
+        got = np.load(tmp_path / f"qvb8r_{r}.npy")
+        assert got.dtype == want.dtype and np.array_equal(got, want)
+
+
 def test_row_subset_of_a_module_is_the_rows_of_the_whole():
     """The zero-copy shard: a module over a subset of rows shares the packed ids and restores to those rows."""
     from qvb8_b200.linear import QVBandLinearV8

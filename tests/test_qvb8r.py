@@ -200,6 +200,52 @@ def test_same_input_fusion_is_the_members_side_by_side():
     assert np.array_equal(_dense(packs.read_qvb8r(blob)).view(np.uint32), want.view(np.uint32))
 
 
+def test_tile_shards_are_the_rows_of_the_whole():
+    """runs of whole tiles as tensors of their own (no re-encoding): restored, they are the whole tensor's rows; the
+    escapes go with their rows; the bounds balance the coded words"""
+    from qvb8_b200 import fuse
+    _, d = _pack(200, 256, seed=61, K=3, T=4)
+    whole = _dense(d)
+    for world in (1, 2, 3, 8, 64):
+        bounds = fuse.qvb8r_shard_bounds(d, world)
+        assert bounds[0] == 0 and bounds[-1] == len(d["tiles"]) and all(a <= b for a, b in zip(bounds, bounds[1:]))
+        got, seen, n_esc = np.zeros_like(whole), np.zeros(200, int), 0
+        for r in range(world):
+            sh, rows = fuse.qvb8r_tile_shard(d, bounds[r], bounds[r + 1])
+            assert sh["Q"] == len(rows) and sh["words"].size == int(d["tile_off"][bounds[r + 1]] - d["tile_off"][bounds[r]])
+            if sh["Q"]:
+                got[rows] = _dense(sh)
+            seen[rows] += 1
+            n_esc += len(sh["esc_idx"])
+            assert np.all(np.diff(sh["esc_idx"]) > 0)
+        assert np.array_equal(got.view(np.uint32), whole.view(np.uint32)) and seen.min() == seen.max() == 1
+        assert n_esc == len(d["esc_idx"])
+        if world in (2, 3):
+            sizes = [int(d["tile_off"][b] - d["tile_off"][a]) for a, b in zip(bounds, bounds[1:])]
+            assert max(sizes) - min(sizes) <= 2 * int(np.diff(d["tile_off"]).max())
+    with pytest.raises(ValueError):
+        fuse.qvb8r_tile_shard(d, 3, len(d["tiles"]) + 1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 9, 40])
+def test_tile_sharded_modules_cover_the_whole_product(cuda_lib, M):
+    """three shard modules on one device, each with its run of tiles: their local rows, put in place, are the whole
+    module's output"""
+    from qvb8_b200.linear_r import QVBandLinearV8R, QVBandLinearV8RShard
+    P = 512
+    _, d = _pack(330, P, seed=71, K=3, T=4)
+    X = synth.synth_activation(M, P, seed=M, device=DEV, dtype=torch.bfloat16)
+    want = QVBandLinearV8R(d, device=DEV)(X).float()
+    got = torch.full_like(want, float("nan"))
+    for r in range(3):
+        sh = QVBandLinearV8RShard(d, r, 3, device=DEV)
+        got[:, sh.rows] = sh(X).float()
+    assert torch.equal(got, want)
+    one = QVBandLinearV8RShard(d, 0, 1, device=DEV)
+    assert torch.equal(one(X).float(), want)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("M", [1, 6, 14, 70])
 def test_same_input_fusion_module(cuda_lib, M):
