@@ -181,12 +181,32 @@ __global__ void __launch_bounds__(256) moe_combine_slots_kernel(const float *__r
                                                                 const int *__restrict__ kexp, OutT *__restrict__ out, int topk,
                                                                 int D, int M, int E, const int *__restrict__ valid) {
     const int t = blockIdx.y, d = blockIdx.x * blockDim.x + threadIdx.x;
+    // the token's pairs once per block: slot (-1 = the pair counts zero), routing weight, scale exponent
+    constexpr int TOPK_SMEM = 64;
+    __shared__ int s_slot[TOPK_SMEM], s_k[TOPK_SMEM];
+    __shared__ float s_w[TOPK_SMEM];
+    const bool staged = topk <= TOPK_SMEM;
+    if (staged && t < M) {
+        for (int j = threadIdx.x; j < topk; j += blockDim.x) {
+            const int sl = valid[t * topk + j] ? slot_of[(int)idx[t * topk + j]] : -1;
+            s_slot[j] = sl;
+            s_w[j] = w[t * topk + j];
+            s_k[j] = sl >= 0 ? kexp[sl * M + t] : 0;
+        }
+    }
+    __syncthreads();
     if (t >= M || d >= D) return;
     float a = 0.f;
     for (int j = 0; j < topk; ++j) {
-        if (!valid[t * topk + j]) continue;
-        const int s = slot_of[(int)idx[t * topk + j]];
-        a = __fmaf_rn(__ldg(w + t * topk + j), ldexpf(Yd[((size_t)s * M + t) * D + d], kexp[s * M + t]), a);
+        int sl, k;
+        float wj;
+        if (staged) { sl = s_slot[j]; k = s_k[j]; wj = s_w[j]; }
+        else {
+            sl = valid[t * topk + j] ? slot_of[(int)idx[t * topk + j]] : -1;
+            k = sl >= 0 ? kexp[sl * M + t] : 0;
+            wj = w[t * topk + j];
+        }
+        if (sl >= 0) a = __fmaf_rn(wj, ldexpf(Yd[((size_t)sl * M + t) * D + d], k), a);
     }
     out[(size_t)t * D + d] = narrow<OutT>(a);
 }

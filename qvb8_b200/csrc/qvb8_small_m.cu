@@ -1506,8 +1506,17 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                 // parity, so no barrier may complete twice while one of them still waits for the first completion
                 if (alive) alive = mbar_wait(smem_u32(&ctl.fin_started), par(kj - 1), abort_flag, 12);
                 if (!alive) break;
-                stage_slice<DUAL, true>(jd.X, jd.x_dtype, jd.P, kc0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
-                                        [](int) { return 1.f; }, psum_w);
+                const JobDesc &pj = jobs[job - 1];
+                if (pj.X == jd.X && pj.P == jd.P && pj.x_dtype == jd.x_dtype && pj.kc0 == jd.kc0 && pj.nc_total == jd.nc_total &&
+                    pj.x_mode == jd.x_mode) {
+                    // the same activations as the job before (the experts of a mixture layer all read the layer's input):
+                    // what is staged stays, the slice's sums move to this job's set
+                    const float *prev = psum + (((kj - 1) & 1) * CWARPS + cwarp) * M;
+                    for (int m = lane; m < M; m += 32) psum_w[m] = prev[m];
+                } else {
+                    stage_slice<DUAL, true>(jd.X, jd.x_dtype, jd.P, kc0, NC, M, MP, xs_a, xs_b, cwarp, CWARPS, lane,
+                                            [](int) { return 1.f; }, psum_w);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl.x_ready));
