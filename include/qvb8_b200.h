@@ -70,6 +70,16 @@ int qvb8_decode(const qvb8_pack *w, int out_dtype, void *out, void *stream);
  * so the table is bit-identical with the reference's.  A row index outside [0, Q) yields a row of zeros. */
 int qvb8_embed_rows(const qvb8_pack *w, const int64_t *rows, int64_t n, int out_dtype, void *out, void *stream);
 
+/* Greedy token choice over logits (no counterpart in the reference, which takes torch.argmax of the whole logits; the
+ * head itself is a QVBandLinearV8 like any other, run/run_inference.py): best_val[m], best_idx[m] = the largest of
+ * Y[m, 0 .. V) (fp32, rows ldy floats apart) and index_base + the LOWEST column that holds it; NaNs are passed over (a
+ * row of NaNs gives -inf and index_base).  With the vocabulary split over ranks by output rows each rank reduces its
+ * slice of the logits to one pair per token and the ranks exchange 16 bytes per token (qvb8_b200/lm_head.py).
+ * scratch: qvb8_argmax_scratch_bytes(M) bytes, 8-byte aligned, contents don't matter.  M <= 65535, V < 2^32 - 1. */
+int64_t qvb8_argmax_scratch_bytes(int64_t M);
+int qvb8_argmax_rows(const float *Y, int64_t M, int64_t V, int64_t ldy, int64_t index_base, float *best_val,
+                     int64_t *best_idx, void *scratch, int64_t scratch_bytes, void *stream);
+
 /* Bytes of scratch qvb8_small_m needs for these sizes (0 is possible).  The scratch must be zero-filled once
  * when it is allocated; the kernel leaves it in a reusable state.  Calls that share one scratch buffer must not
  * overlap on the device. */

@@ -240,3 +240,80 @@ QV_API int qvb8_embed_rows(const qvb8_pack *w, const int64_t *rows, int64_t n, i
 #undef QV_EMBED
     return cuda_status("qvb8_embed_rows");
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Greedy token choice over logits: per row of Y the largest value and the LOWEST index that holds it.  With the
+// vocabulary split over ranks by output rows (the lm_head is the largest linear of a decoder) a rank reduces its own
+// slice of the logits to one (value, index) pair per token, and the ranks exchange 16 bytes per token instead of their
+// logits.  NaNs never win (a row of NaNs yields index_base and -inf).
+namespace qv {
+
+constexpr int ARGMAX_BLOCKS = 64;        // partial results per row
+__device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t i) {
+    // larger value first; among equal values the lower index: order-preserving float bits above, inverted index below
+    uint32_t b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - i);
+}
+__device__ __forceinline__ unsigned long long key_max(unsigned long long a, unsigned long long b) { return a > b ? a : b; }
+
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float *__restrict__ Y, int64_t V, int64_t ldy,
+                                                             unsigned long long *__restrict__ part) {
+    const int m = blockIdx.y;
+    const float *y = Y + (int64_t)m * ldy;
+    const int64_t per = (V + gridDim.x - 1) / gridDim.x;
+    const int64_t lo = (int64_t)blockIdx.x * per, hi = lo + per < V ? lo + per : V;
+    unsigned long long best = argmax_key(-INFINITY, 0xffffffffu);       // below every real candidate
+    for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = __ldg(y + i);
+        if (v == v) best = key_max(best, argmax_key(v, (uint32_t)i));
+    }
+    for (int o = 16; o > 0; o >>= 1) best = key_max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    __shared__ unsigned long long s[8];
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int k = 1; k < 8; ++k) best = key_max(best, s[k]);
+        part[(int64_t)m * gridDim.x + blockIdx.x] = best;
+    }
+}
+__global__ void __launch_bounds__(32) argmax_final_kernel(const unsigned long long *__restrict__ part, int nblk,
+                                                          int64_t index_base, float *__restrict__ best_val,
+                                                          int64_t *__restrict__ best_idx) {
+    const int m = blockIdx.x;
+    unsigned long long best = argmax_key(-INFINITY, 0xffffffffu);
+    for (int k = threadIdx.x; k < nblk; k += 32) best = key_max(best, part[(int64_t)m * nblk + k]);
+    for (int o = 16; o > 0; o >>= 1) best = key_max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if (threadIdx.x == 0) {
+        uint32_t b = (uint32_t)(best >> 32);
+        b = (b & 0x80000000u) ? (b & 0x7fffffffu) : ~b;
+        const uint32_t i = 0xffffffffu - (uint32_t)(best & 0xffffffffu);
+        const bool none = i == 0xffffffffu;                             // no candidate: every value was a NaN (or V = 0)
+        best_val[m] = none ? -INFINITY : __uint_as_float(b);
+        best_idx[m] = index_base + (none ? 0 : (int64_t)i);
+    }
+}
+
+}  // namespace qv
+
+QV_API int64_t qvb8_argmax_scratch_bytes(int64_t M) { return M > 0 ? M * qv::ARGMAX_BLOCKS * 8 : 0; }
+
+/* best_val[m], best_idx[m] = the largest of Y[m, 0 .. V) (fp32, rows ldy apart) and index_base + the lowest column
+ * that holds it; NaNs are passed over.  scratch: qvb8_argmax_scratch_bytes(M) bytes, 8-byte aligned. */
+QV_API int qvb8_argmax_rows(const float *Y, int64_t M, int64_t V, int64_t ldy, int64_t index_base, float *best_val,
+                            int64_t *best_idx, void *scratch, int64_t scratch_bytes, void *stream) {
+    using namespace qv;
+    if (int rc = check_device("qvb8_argmax_rows")) return rc;
+    if (!Y || !best_val || !best_idx || M < 0 || M > 65535 || V < 0 || V >= 0xffffffffll || ldy < V)
+        return fail(QVB8_ERR_ARG, "qvb8_argmax_rows: bad arguments");
+    if (M == 0) return QVB8_OK;
+    if (!scratch || scratch_bytes < qvb8_argmax_scratch_bytes(M) || !aligned(scratch, 8))
+        return fail(QVB8_ERR_SCRATCH, "qvb8_argmax_rows: scratch of %lld bytes (8-byte aligned) needed",
+                    (long long)qvb8_argmax_scratch_bytes(M));
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    unsigned long long *part = reinterpret_cast<unsigned long long *>(scratch);
+    argmax_partial_kernel<<<dim3(ARGMAX_BLOCKS, (unsigned)M), 256, 0, st>>>(Y, V, ldy, part);
+    if (int rc = cuda_status("qvb8_argmax_rows partial")) return rc;
+    argmax_final_kernel<<<(unsigned)M, 32, 0, st>>>(part, ARGMAX_BLOCKS, index_base, best_val, best_idx);
+    return cuda_status("qvb8_argmax_rows");
+}

@@ -25,7 +25,7 @@ EXPORTS = (
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index", "qvb8_moe_plan_bytes", "qvb8_moe_plan_build",
-    "qvb8_moe_experts_planned", "qvb8_moe_streams",
+    "qvb8_moe_experts_planned", "qvb8_moe_streams", "qvb8_argmax_scratch_bytes", "qvb8_argmax_rows",
     "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
     "qvb8_embed_rows", "qvb8_peer_bytes", "qvb8_peer_alloc", "qvb8_peer_open", "qvb8_peer_close", "qvb8_peer_allreduce",
     "qvb8_peer_allreduce_ex", "qvb8_peer_allreduce_local", "qvb8_peer_allgather", "qvb8_peer_allgather_local", "qvb8_device_status_reset", "qvb8r_embed_rows",
@@ -136,6 +136,9 @@ def load() -> ctypes.CDLL:
             lib.qvb8_moe_scratch_bytes.restype = i64
             lib.qvb8_moe_experts.argtypes = [vp, ci, i64, vp, vp, i64, i64, es, es, ci, vp, vp, i64, vp]
             lib.qvb8_moe_streams.argtypes = [i64, i64, i64, es, es]
+            lib.qvb8_argmax_scratch_bytes.argtypes = [i64]
+            lib.qvb8_argmax_scratch_bytes.restype = i64
+            lib.qvb8_argmax_rows.argtypes = [vp, i64, i64, i64, i64, vp, vp, vp, i64, vp]
             lib.qvb8_moe_plan_bytes.argtypes = [i64, i64]
             lib.qvb8_moe_plan_bytes.restype = i64
             lib.qvb8_moe_plan_build.argtypes = [es, i64, vp, i64, vp]
@@ -362,6 +365,24 @@ def prefill(pack, keep, X: torch.Tensor, plan: torch.Tensor | None = None) -> to
                                dtype_code(X.dtype), M, Y.data_ptr(), scratch.data_ptr(), nbytes, stream_ptr(dev)),
               "qvb8_prefill")
     return Y
+
+
+def argmax_rows(Y: torch.Tensor, index_base: int = 0):
+    """(values fp32 (M,), indices int64 (M,)) of the largest logit per row of Y (M, V) fp32 and the lowest column that
+    holds it (+ index_base), on Y's device and current stream."""
+    if not Y.is_cuda or Y.dtype != torch.float32 or Y.dim() != 2 or Y.stride(1) != 1:
+        raise RuntimeError("qvb8_b200: argmax_rows takes a CUDA fp32 matrix with contiguous rows (there is no CPU path)")
+    M, V = Y.shape
+    L = load()
+    dev = Y.device
+    val = torch.empty(M, dtype=torch.float32, device=dev)
+    idx = torch.empty(M, dtype=torch.int64, device=dev)
+    nbytes = int(L.qvb8_argmax_scratch_bytes(M))
+    scratch = torch.empty(max(8, nbytes), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(L.qvb8_argmax_rows(Y.data_ptr(), M, V, Y.stride(0) if M > 1 else V, int(index_base), val.data_ptr(),
+                                 idx.data_ptr(), scratch.data_ptr(), nbytes, stream_ptr(dev)), "qvb8_argmax_rows")
+    return val, idx
 
 
 # ---------------------------------------------------------------------------------------------------------------
