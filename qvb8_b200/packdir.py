@@ -12,6 +12,8 @@ from __future__ import annotations
 import json
 import os
 
+import torch
+
 from . import packs
 
 EXPERT_KEY_SEP = "#expert"
@@ -80,18 +82,61 @@ def read_manifest(folder: str) -> dict:
     return m
 
 
-def load_linear(folder: str, name: str, *, bias=None, device: str = "cuda", manifest: dict | None = None):
-    """The module of tensor `name`: QVBandLinearV8 for qvb8 / qvband packs, QVBandLinearV8R for qvb8r."""
+def load_linear(folder: str, name: str, *, bias=None, device: str = "cuda", manifest: dict | None = None,
+                shard: tuple | None = None, group=None):
+    """The module of tensor `name`: QVBandLinearV8 for qvb8 / qvband packs, QVBandLinearV8R for qvb8r.
+
+    shard = (rank, world, cut): only this rank's share is built and uploaded -- the whole file is parsed on the host,
+    the shard is cut from its bytes there (nothing is re-encoded), and the device never sees the rest.  cut "rows":
+    output rows [rank Q / world, (rank + 1) Q / world) (the bias is sliced with them); cut "cols": input columns
+    [rank P / world, ...) of every row (a partial product: the bias stays with rank 0).  A qvb8r tensor has one cut,
+    runs of whole tiles (``QVBandLinearV8RShard``, which all-gathers the ranks' rows over `group`)."""
     m = manifest or read_manifest(folder)
     if name not in m["tensors"]:
         raise KeyError(f"{name!r} is not in the manifest of {folder}" + (" (listed as failed)" if name in m["failed"] else ""))
     e = m["tensors"][name]
     path = os.path.join(folder, e["pack"])
+    if shard is not None:
+        rank, world, cut = int(shard[0]), int(shard[1]), (shard[2] if len(shard) > 2 else "rows")
+        if not (0 <= rank < world) or cut not in ("rows", "cols"):
+            raise ValueError("shard = (rank, world, 'rows' | 'cols') with 0 <= rank < world")
     if m["format"] == "qvb8r":
-        from .linear_r import QVBandLinearV8R
+        from .linear_r import QVBandLinearV8R, QVBandLinearV8RShard
+        if shard is not None and world > 1:
+            with open(path, "rb") as fh:
+                d = packs.read_qvb8r(fh.read(), str(path))
+            if (int(d["Q"]), int(d["P"])) != (int(e["Q"]), int(e["P"])):
+                raise packs.PackFormatError(f"{path}: shape {(d['Q'], d['P'])} differs from the manifest's {(e['Q'], e['P'])}")
+            return QVBandLinearV8RShard(d, rank, world, bias=bias, device=device, group=group)
         mod = QVBandLinearV8R.from_packfile(path, bias=bias, device=device)
     else:
         from .linear import QVBandLinearV8
+        if shard is not None and world > 1:
+            from . import fuse
+            from .synth import QVB8Pack
+            with open(path, "rb") as fh:
+                d = packs.read_qvb8(fh.read(), str(path))
+            if (int(d["Q"]), int(d["P"])) != (int(e["Q"]), int(e["P"])):
+                raise packs.PackFormatError(f"{path}: shape {(d['Q'], d['P'])} differs from the manifest's {(e['Q'], e['P'])}")
+            packs.validate_pack(d, str(path))
+            whole = QVB8Pack.from_parsed(d, device="cpu")
+            Q, P = whole.Q, whole.P
+            b = None if bias is None else torch.as_tensor(bias).detach()
+            if cut == "rows":
+                if Q % world:
+                    raise ValueError(f"{name}: {Q} rows do not split over {world} ranks")
+                r0, r1 = rank * (Q // world), (rank + 1) * (Q // world)
+                part = fuse.row_shard(whole, r0, r1)
+                b = None if b is None else b[r0:r1]
+            else:
+                if P % (8 * world):
+                    raise ValueError(f"{name}: {P} columns do not split over {world} ranks in 8-column units")
+                part = fuse.column_shard(whole, rank * (P // world), (rank + 1) * (P // world))
+                b = b if rank == 0 else None
+            mod = QVBandLinearV8.from_pack(part.to(device), bias=None if b is None else b.to(device))
+            mod.fp16_table_missing = bool(d.get("fp16_table_missing", False))
+            mod._where = f"{path} [{cut} shard {rank} of {world}]"
+            return mod
         mod = QVBandLinearV8.from_packfile(path, bias=bias, device=device)
     if (mod.out_features, mod.in_features) != (int(e["Q"]), int(e["P"])):
         raise packs.PackFormatError(f"{path}: shape {(mod.out_features, mod.in_features)} differs from the manifest's {(e['Q'], e['P'])}")
