@@ -147,8 +147,8 @@ int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *scratch
  * ring (2..8); cps = 128-column chunks per ring stage (4, 8, 12 or 16); debug bit 0 = skip the fragment math (copy
  * stream only), bit 1 = record qvb8_debug_trace stamps, bit 2 = skip the row copies (results meaningless), bit 4 = plain
  * bulk copies without the evict-first hint, bit 5 = list launches of up to 4 tokens sum escapes on the consumer warps instead of by the pre-pass kernel,
- * bit 6 = the stamps follow the finishing warp's visits 4..7 instead of the consumers' jobs, bit 7 = list launches cut
- * products with many columns into column ranges (correct, measured slower than launching them alone); bits 8..11 =
+ * bit 6 = the stamps follow the finishing warp's visits 4..7 instead of the consumers' jobs, bit 7 = list launches do not cut
+ * products with many columns into column ranges (a non-zero force_s is also the activation budget of a range, in KB); bits 8..11 =
  * pipes per CTA for up to 8 tokens (2 instead of the default 4). */
 void qvb8_small_m_set_tuning(int fill_pct, int force_s, int nstg, int cps, int debug);
 

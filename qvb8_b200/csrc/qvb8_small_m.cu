@@ -354,7 +354,7 @@ __host__ __device__ constexpr int stage_row_stride(int nb, int cps) {
 
 // One 128-column chunk of a 16-row tile of width NB: 8 MMAs per token group.
 //   wa, wb   shared addresses of this thread's blocks in rows g and g + 8 of the stage
-//   xa       shared address of this thread's first activation slot of the chunk (token 8n + g -> + n * 128 bytes)
+//   xa       shared address of this thread's first activation slot of the chunk (token 8n + g -> + n * 512 bytes)
 //   xstep    bytes between the slots of consecutive 8-column groups (= 4 * MP * 16; 0 for lanes without a token)
 //   DUAL     true: a second activation layout exists for widths that pair ids at distance 4 (xa points into it);
 //            false: only layout A is staged and those widths rebuild their operands with byte permutes
@@ -374,7 +374,7 @@ __device__ __forceinline__ void chunk_mma(uint32_t wa, uint32_t wb, uint32_t xa,
         for (int n = 0; n < NT; ++n)
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                          : "=r"(xw[n][0]), "=r"(xw[n][1]), "=r"(xw[n][2]), "=r"(xw[n][3])
-                         : "r"(xa + i * xstep + n * 128));
+                         : "r"(xa + i * xstep + n * 512));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             // ids of this MMA: D == 2 -> {8i+4h .. 8i+4h+3} paired (f, f+2);  D == 4 -> {8i+2h, +1, +4, +5} paired (f, f+4)
@@ -397,12 +397,14 @@ __device__ __forceinline__ void chunk_mma(uint32_t wa, uint32_t wb, uint32_t xa,
 }
 
 // Activation layouts in shared memory.  A 16-byte slot holds the 8 activations of one token for one 8-column group;
-// slots are ordered (chunk, group-in-block i, block t, token).  Inside a slot the halves are permuted so that word
+// slots are ordered (chunk, group-in-block i, token, block t): lane (g, t) of a warp reads token g, block t, so the 32
+// lanes of a 16-byte load read 512 consecutive bytes in lane order and no two lanes of a quarter-warp share a bank
+// (with the block outside the token, lanes of equal g lay 128 bytes apart: four-way conflicts on every such load).  Inside a slot the halves are permuted so that word
 // pairs are the B operands directly:  layout A (ids paired at distance 2): x0 x2 x1 x3 x4 x6 x5 x7;
 // layout B (distance 4): x0 x4 x1 x5 x2 x6 x3 x7.
 __device__ __forceinline__ int slot_of(int c, int m, int MP) {
     const int chunk = c >> 7, t = (c >> 5) & 3, i = (c >> 3) & 3;
-    return ((chunk * 4 + i) * 4 + t) * MP + m;
+    return ((chunk * 4 + i) * MP + m) * 4 + t;
 }
 __device__ __forceinline__ int pos_a(int e) { return (e & 4) | ((e & 1) << 1) | ((e >> 1) & 1); }
 // natural-order read of X[m, c] (c relative to the CTA's first column) from layout A
@@ -1298,12 +1300,12 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                                 if (e < esc_cap) en = ent[e];
                                 else { en.col = __ldg(&gent[e].col); en.delta = __ldg(&gent[e].delta); }
                                 if (en.col >= clo && en.col < chi) {
-                                    // the column's activations of consecutive tokens lie one slot (8 halves) apart
+                                    // the column's activations of consecutive tokens lie four slots (32 halves) apart
                                     const int cc = en.col - cbase;
-                                    const __half *xp = xsa + ((size_t)(slot_of(cc, 0, MP) + m0) << 3) + pos_a(cc & 7);
+                                    const __half *xp = xsa + ((size_t)slot_of(cc, m0, MP) << 3) + pos_a(cc & 7);
 #pragma unroll
                                     for (int k = 0; k < 8; ++k)
-                                        if (m0 + k < M) a[k] = __fmaf_rn(__half2float(xp[k * 8]), en.delta, a[k]);
+                                        if (m0 + k < M) a[k] = __fmaf_rn(__half2float(xp[k * 32]), en.delta, a[k]);
                                 }
                             }
 #pragma unroll
@@ -1452,7 +1454,7 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
         const int g = lane >> 2, t = lane & 3;
         const bool xvalid = NT > 1 || g < MP;                           // lanes whose token slot exists
         const uint32_t xstep = xvalid ? (uint32_t)(4 * MP * 16) : 0u;   // bytes between consecutive 8-column groups
-        const uint32_t xoff = (uint32_t)((t * MP + g) * 16);
+        const uint32_t xoff = (uint32_t)((g * 4 + t) * 16);
         const int cpw = cps / NW;
         bool alive = true;
         int vis = 0;                                                    // visits walked so far (all jobs)
@@ -1575,8 +1577,8 @@ __global__ void __launch_bounds__(NPIPE * PIPE_THREADS, 1) small_m_kernel(const 
                                         for (int n = 0; n < NT; ++n)
 #pragma unroll
                                             for (int k = 0; k < 2; ++k)
-                                                if (8 * n + 2 * t + k < M)   // consecutive tokens lie one slot (8 halves) apart
-                                                    a[n][k] = __fmaf_rn(__half2float(xp[(8 * n + k) * 8]), en.delta, a[n][k]);
+                                                if (8 * n + 2 * t + k < M)   // consecutive tokens lie four slots (32 halves) apart
+                                                    a[n][k] = __fmaf_rn(__half2float(xp[(8 * n + k) * 32]), en.delta, a[n][k]);
                                     }
                                 }
                             }
@@ -2149,19 +2151,23 @@ static bool job_listable(const qvb8_job &jb) {
            !(jb.x_mode == 1 && jb.x_dtype != QVB8_F16);                  // the prescale pass is the single launch's
 }
 // K-ranges of a job in a list.  The staged activations of a job take P x MP x 2 bytes of shared memory, which the copy
-// rings then lack; a product can be cut into KR equal column ranges that run as consecutive jobs of the list (each CTA
-// meets the same tiles in every range and adds the later ranges' sums to the first's).  Measured on B200 this loses to
-// launching such a job on its own with K split across CTAs (9B-class stack, 8 tokens: 2.88 ms against 2.58 ms; every
-// range boundary drains the rings and restages activations), so it is off unless tuning bit 7 asks for it
-// (qvb8_small_m_set_tuning): the budget below then bounds the staged activations of one range.
+// rings then lack -- and a list has ONE ring geometry, set by its largest job: one product with many columns and a few
+// tokens pushes the whole list to short stages (9B-class stack: 4 tokens x 12288 columns = 96 KB of activations, and
+// every job of the list streams with 4-chunk stages, which run a third slower than 8-chunk ones).  So a product whose
+// activations exceed XS_BUDGET is cut into KR equal column ranges that run as consecutive jobs of the list: each CTA
+// meets the same tiles in every range and every thread adds the later ranges' sums to what it wrote for the first.
+// Measured on B200, 16 layers of the 9B-class stack behind one launch: 4 tokens 928 -> 604 us, 8 tokens 1359 -> 919 us
+// (a budget of 36-40 KB: 975 us, 20 KB: 1961 us -- every range boundary drains the rings and restages activations).
+// Tuning bit 7 switches the cut off; a non-zero force_s of qvb8_small_m_set_tuning also sets this budget, in KB.
 constexpr int64_t XS_BUDGET = 72 * 1024;
 static int k_ranges(int64_t P, int64_t M) {
-    if (!(g_debug & 128)) return 1;
+    if (g_debug & 128) return 1;
     const int NT = (int)((M + 7) / 8);
     const int64_t MP = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8 * NT;
     const int64_t nc = P / KC;
+    const int64_t budget = g_force_s > 0 ? (int64_t)g_force_s * 1024 : XS_BUDGET;   // (force_s doubles as the budget in KB)
     for (int64_t kr = 1; kr <= nc; ++kr)
-        if (nc % kr == 0 && (nc / kr) * KC * MP * 2 <= XS_BUDGET) return (int)kr;
+        if (nc % kr == 0 && (nc / kr) * KC * MP * 2 <= budget) return (int)kr;
     return (int)nc;
 }
 struct ListEntry { int job, r, kr; };                                   // K-range r of kr of jobs[job]

@@ -451,22 +451,31 @@ def test_job_list_with_column_ranges(cuda_lib, M, shapes):
     items, packs_ = _job_items(shapes, M, seed=3 + M, esc=0.002)
     jl = lib.JobList(items)
     L = lib.load()
+    refs = [lib.small_m(st, keep, X, plan=plan) for st, keep, plan, X, Y in items]      # every job on its own
+    torch.cuda.synchronize()
+    for budget_kb in (0, 20):                                              # the default budget, and a small one: more ranges
+        try:
+            L.qvb8_small_m_set_tuning(0, budget_kb, 0, 0, 0)
+            jl = lib.JobList(items)                                        # (a list sizes its scratch when it is made)
+            lib.small_m_group(jl)
+            torch.cuda.synchronize()
+            first = [it[4].clone() for it in items]
+            lib.small_m_group(jl, flags=lib.FLAG_PDL)
+            torch.cuda.synchronize()
+        finally:
+            L.qvb8_small_m_set_tuning(0, 0, 0, 0, 0)
+        assert all(torch.equal(a, it[4]) for a, it in zip(first, items))   # one sum order, run after run
+        for (st, keep, plan, X, Y), pk, ref in zip(items, packs_, refs):
+            assert rel_fro(Y.cpu().numpy(), ref.cpu().numpy()) < 1e-5
+            assert rel_fro(Y.cpu().numpy(), _oracle_y(pk, X)) < TIGHT
+    # with the cut switched off the large jobs run on their own (K split across CTAs): the same results
     try:
-        L.qvb8_small_m_set_tuning(0, 0, 0, 0, 128)                         # column ranges are a tuning option
+        L.qvb8_small_m_set_tuning(0, 0, 0, 0, 128)
+        jl = lib.JobList(items)
         lib.small_m_group(jl)
         torch.cuda.synchronize()
-        for (st, keep, plan, X, Y), pk in zip(items, packs_):
-            assert rel_fro(Y.cpu().numpy(), lib.small_m(st, keep, X, plan=plan).cpu().numpy()) < 1e-5
-            assert rel_fro(Y.cpu().numpy(), _oracle_y(pk, X)) < TIGHT
-        first = [it[4].clone() for it in items]
-        lib.small_m_group(jl, flags=lib.FLAG_PDL)
-        torch.cuda.synchronize()
-        assert all(torch.equal(a, it[4]) for a, it in zip(first, items))   # one sum order, run after run
     finally:
         L.qvb8_small_m_set_tuning(0, 0, 0, 0, 0)
-    # without the option the large jobs run on their own (K split across CTAs): the same results as separate calls
-    lib.small_m_group(jl)
-    torch.cuda.synchronize()
-    for (st, keep, plan, X, Y), pk in zip(items, packs_):
-        assert rel_fro(Y.cpu().numpy(), lib.small_m(st, keep, X, plan=plan).cpu().numpy()) < 1e-5
+    for (st, keep, plan, X, Y), ref in zip(items, refs):
+        assert rel_fro(Y.cpu().numpy(), ref.cpu().numpy()) < 1e-5
     assert lib.device_status(DEV) == 0
