@@ -10,8 +10,11 @@ seeded).  One step = one pass over every projection of every layer = one decode 
 
   value   whole-job GB/s with the activations resident in HBM (CUDA-graph replay, CUDA events, max over ranks)
   e2e     the same through LinearStack.step_host: pinned host activations -> device, the step, outputs -> host
-  N > 1   q/k/v and gate/up are sharded by output rows (column parallel), o and down by input columns (row parallel)
-          with one NCCL all-reduce of the (M, d_model) partial sums after each; total bytes stay fixed ("strong")
+  N > 1   below 8 tokens every projection is sharded by output rows and the ranks all-gather the slices of the o / down
+          outputs and inputs; from 8 tokens q/k/v and gate/up by output rows, o and down by input columns, partial sums
+          all-reduced (--shard).  One exchange per list launch, by this library's push kernels over peer memory (checked
+          against NCCL first; --nccl-allreduce uses NCCL).  Total bytes stay fixed ("strong")
+  other workloads (--workload): single, qvb8r, moe, prefill -- each prints its own JSON line
 
 --impl reference times the CPU path the reference itself would run for this op (it ships no CPU GEMV): restore the
 pack to bf16 weights, then torch.matmul on the host cores -- here through the CPU oracle's restatement of the
