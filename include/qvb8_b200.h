@@ -124,10 +124,12 @@ int qvb8_small_m_ex(const qvb8_pack *w, const void *plan, const void *X, int x_d
  * persistent CTAs: copy rings, barriers and warp roles carry over from one job to the next, so the stream of weight
  * bytes never drains at a job boundary, and the next job's activations are staged while the current one streams.
  * The jobs must be INDEPENDENT: no job may read what another job of the same call writes (projections that read the
- * outputs of earlier ones go into a later call).  All jobs share M; every job needs its plan.  Lists whose
- * activations do not fit shared memory next to the rings (large M x P), or whose packs the streaming kernel cannot
- * take, run job by job exactly as qvb8_small_m_ex would; only those need scratch
- * (qvb8_small_m_group_scratch_bytes, zero-filled once); so do lists with x_mode 1 on bf16 / fp32 activations.  Results
+ * outputs of earlier ones go into a later call).  All jobs share M; every job needs its plan.  Any number of jobs: a
+ * launch takes up to 128, longer lists become several launches.  A product whose staged activations (P x tokens x 2
+ * bytes) would crowd the copy rings is cut into column ranges that run as consecutive jobs of the list; jobs the
+ * streaming kernel cannot take at all (no plan, P % 128 != 0, unaligned buffers, x_mode 1 on bf16 / fp32 activations)
+ * run on their own exactly as qvb8_small_m_ex would; only those need scratch (qvb8_small_m_group_scratch_bytes,
+ * zero-filled once).  Results
  * are deterministic (every sum has a fixed order) and agree with separate calls to rounding: a list is one stream of
  * tiles cut into equal per-CTA ranges, so a tile's fixed-order partial sums may be grouped differently, and the escape
  * corrections of a list are summed by a small pre-pass kernel and the products added to them. */
