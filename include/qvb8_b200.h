@@ -141,6 +141,11 @@ typedef struct qvb8_job {
     int x_dtype, x_mode;    /* as for qvb8_small_m */
 } qvb8_job;
 int64_t qvb8_small_m_group_scratch_bytes(const qvb8_job *jobs, int njobs, int64_t M);
+/* How qvb8_small_m_group would run these jobs (host arithmetic only: nothing is launched, no device is needed):
+ * launches of the streaming kernel that run a list, the jobs of those lists (a product cut into column ranges counts
+ * once per range), and the jobs that run on their own. */
+int qvb8_small_m_group_describe(const qvb8_job *jobs, int njobs, int64_t M, int *list_launches, int *list_entries,
+                                int *single_jobs);
 int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *scratch, int64_t scratch_bytes, int flags,
                        void *stream);
 

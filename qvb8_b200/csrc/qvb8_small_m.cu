@@ -2247,6 +2247,27 @@ QV_API int64_t qvb8_small_m_group_scratch_bytes(const qvb8_job *jobs, int njobs,
     return need;
 }
 
+/* How qvb8_small_m_group would run these jobs (host arithmetic only; nothing is launched, no device needed):
+ * list_launches = launches of the streaming kernel that run a list, list_entries = jobs of those lists (a product cut
+ * into column ranges counts once per range), single_jobs = jobs that run on their own. */
+QV_API int qvb8_small_m_group_describe(const qvb8_job *jobs, int njobs, int64_t M, int *list_launches, int *list_entries,
+                                       int *single_jobs) {
+    using namespace qv;
+    if (!jobs || njobs <= 0 || M < 1 || M > MAX_M || !list_launches || !list_entries || !single_jobs)
+        return fail(QVB8_ERR_ARG, "qvb8_small_m_group_describe: bad arguments");
+    for (int j = 0; j < njobs; ++j)
+        if (!jobs[j].w || jobs[j].w->P <= 0 || jobs[j].w->Q < 0)
+            return fail(QVB8_ERR_ARG, "qvb8_small_m_group_describe: job %d has no pack", j);
+    int launches = 0, entries = 0, singles = 0;
+    walk_group(jobs, njobs, M,
+               [&](const ListEntry *, int n, const Plan &) { ++launches; entries += n; return 0; },
+               [&](int) { ++singles; return 0; });
+    *list_launches = launches;
+    *list_entries = entries;
+    *single_jobs = singles;
+    return QVB8_OK;
+}
+
 QV_API int qvb8_small_m_group(const qvb8_job *jobs, int njobs, int64_t M, void *scratch, int64_t scratch_bytes, int flags,
                               void *stream) {
     using namespace qv;

@@ -25,7 +25,7 @@ EXPORTS = (
     "qvb8_small_m_generic", "qvb8_plan_bytes", "qvb8_plan_build", "qvb8_small_m_ex", "qvb8_small_m_set_tuning",
     "qvb8_device_status", "qvb8_debug_trace", "qvb8_small_m_static_max_scratch", "qvb8_small_m_static",
     "qvb8_moe_scratch_bytes", "qvb8_moe_experts", "qvb8_moe_bad_index", "qvb8_moe_plan_bytes", "qvb8_moe_plan_build",
-    "qvb8_moe_experts_planned", "qvb8_moe_streams", "qvb8_argmax_scratch_bytes", "qvb8_argmax_rows",
+    "qvb8_moe_experts_planned", "qvb8_moe_streams", "qvb8_argmax_scratch_bytes", "qvb8_argmax_rows", "qvb8_small_m_group_describe",
     "qvb8r_ids", "qvb8r_decode", "qvb8r_small_m", "qvb8r_fix_escapes", "qvb8_prefill_scratch_bytes", "qvb8_prefill", "qvb8_prefill_set_tuning",
     "qvb8_embed_rows", "qvb8_peer_bytes", "qvb8_peer_alloc", "qvb8_peer_open", "qvb8_peer_close", "qvb8_peer_allreduce",
     "qvb8_peer_allreduce_ex", "qvb8_peer_allreduce_local", "qvb8_peer_allgather", "qvb8_peer_allgather_local", "qvb8_device_status_reset", "qvb8r_embed_rows",
@@ -104,6 +104,8 @@ def load() -> ctypes.CDLL:
             lib.qvb8_small_m_group_scratch_bytes.argtypes = [jb, ci, i64]
             lib.qvb8_small_m_group_scratch_bytes.restype = i64
             lib.qvb8_small_m_group.argtypes = [jb, ci, i64, vp, i64, ci, vp]
+            pi = ctypes.POINTER(ctypes.c_int)
+            lib.qvb8_small_m_group_describe.argtypes = [jb, ci, i64, pi, pi, pi]
             lib.qvb8_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
             lib.qvb8_debug_trace.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
             lib.qvb8_small_m_set_tuning.restype = None

@@ -51,3 +51,43 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no CPU or eager fallback"):
         lib.load()
+
+
+def _describe(shapes, M, per_shape=1):
+    """(list launches, list entries, single jobs) for products of the given (Q, P) shapes -- host arithmetic of the
+    library, no device: the pointers only have to look aligned"""
+    import ctypes
+    from qvb8_b200 import lib
+    L = lib.load()
+    packs, jobs = [], (lib.JobStruct * (len(shapes) * per_shape))()
+    k = 0
+    for Q, P in shapes:
+        for _ in range(per_shape):
+            pk = lib.PackStruct()
+            pk.ids, pk.ids_bytes, pk.min_s, pk.tau_s, pk.nbits, pk.bit_off = 0x10000, 1 << 30, 0x10000, 0x10000, 0x10000, 0x10000
+            pk.Q, pk.P, pk.esc_idx, pk.esc_vals, pk.n_esc = Q, P, None, None, 0
+            packs.append(pk)
+            jobs[k].w = ctypes.pointer(pk)
+            jobs[k].plan, jobs[k].X, jobs[k].Y = 0x20000, 0x30000, 0x40000
+            jobs[k].x_dtype, jobs[k].x_mode = 1, 0
+            k += 1
+    a, b, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    rc = L.qvb8_small_m_group_describe(jobs, k, M, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+    assert rc == 0, L.qvb8_last_error()
+    return a.value, b.value, c.value
+
+
+def test_how_a_list_is_cut_into_launches(built):
+    layer = [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)]       # the four fused projections of a 9B layer
+    # one token: nothing is cut; 128 jobs are one launch, 129 two
+    assert _describe(layer, 1, per_shape=32) == (1, 128, 0)
+    assert _describe(layer + [(512, 1024)], 1, per_shape=32)[:1] == (2,)
+    # eight tokens: 12288 columns x 8 tokens = 192 KB of activations are cut into three column ranges (64 KB each), the
+    # 4096-column products stay whole: 6 entries per layer
+    assert _describe(layer, 8) == (1, 6, 0)
+    assert _describe(layer, 8, per_shape=32) == (2, 192, 0)
+    # four tokens: 96 KB -> two ranges
+    assert _describe(layer, 4) == (1, 5, 0)
+    # columns that are no multiple of 128 cannot stream: on their own
+    assert _describe([(256, 4096), (256, 1000)], 1) == (0, 0, 2)            # (a list of one is a single launch too)
+    assert _describe([(256, 4096), (256, 4096), (256, 1000)], 1) == (1, 2, 1)
