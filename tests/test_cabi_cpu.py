@@ -91,3 +91,22 @@ def test_how_a_list_is_cut_into_launches(built):
     # columns that are no multiple of 128 cannot stream: on their own
     assert _describe([(256, 4096), (256, 1000)], 1) == (0, 0, 2)            # (a list of one is a single launch too)
     assert _describe([(256, 4096), (256, 4096), (256, 1000)], 1) == (1, 2, 1)
+
+
+def test_which_expert_layers_take_the_streaming_route(built):
+    """host arithmetic: up to 8 tokens, column counts that are multiples of 128, at most 128 distinct experts"""
+    import ctypes
+    from qvb8_b200 import lib
+    L = lib.load()
+
+    def stack(Q, P, ids=0x10000):
+        return lib.ExpertStackStruct(ids, 1 << 30, 0x10000, 0x10000, 0x10000, 0x10000, Q, P)
+
+    def streams(M, topk, E, up, dn):
+        return L.qvb8_moe_streams(M, topk, E, ctypes.byref(up), ctypes.byref(dn))
+    up, dn = stack(1536, 2048), stack(2048, 768)                # the 35B-A3B-class expert: gate_up 1536 x 2048, down 2048 x 768
+    assert [streams(M, 8, 128, up, dn) for M in (1, 4, 8, 9, 32)] == [1, 1, 1, 0, 0]
+    assert streams(8, 8, 128, stack(192, 256), stack(256, 96)) == 0          # 96 columns: no multiple of 128
+    assert streams(8, 8, 128, stack(1536, 2048, ids=0x10008), dn) == 0       # stack not 16-byte aligned
+    assert streams(8, 32, 512, up, dn) == 0                                  # up to 256 distinct experts: too many jobs
+    assert L.qvb8_moe_plan_bytes(128, 1536) > 128 * 102 * 400                # a plan per expert, a descriptor per tile
