@@ -84,31 +84,61 @@ class FusedGroup(nn.Module):
 
 
 class FusedMember(nn.Module):
-    """Stands where a member linear stood: same ``in_features`` / ``out_features`` / ``bias``, output taken from the
-    group."""
+    """Stands where a member linear stood and answers with its slice of the group's product.  Built from the module it
+    replaces: it takes over that module's ``in_features`` / ``out_features`` and its bias (added to the slice)."""
 
-    def __init__(self, group: FusedGroup, i: int, in_features: int, out_features: int, bias):
+    def __init__(self, group: FusedGroup, index: int, replaced: nn.Module | None = None, *, in_features: int | None = None,
+                 out_features: int | None = None, bias=None):
         super().__init__()
-        # every member refers to the one group; it is registered once, under the members' owner, not under each member
-        object.__setattr__(self, "group", group)
-        self.i, self.in_features, self.out_features = int(i), int(in_features), int(out_features)
-        self.bias = bias
+        self.index = int(index)
+        self.in_features = int(in_features if in_features is not None else replaced.in_features)
+        self.out_features = int(out_features if out_features is not None else replaced.out_features)
+        self.bias = bias if replaced is None else replaced.bias
+        # all members point at ONE group, which the owner registers once; a plain attribute here, not a submodule
+        self.__dict__["group"] = group
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = self.group.get(x, self.i)
-        return y if self.bias is None else y + self.bias.to(y.dtype)
+        part = self.group.get(x, self.index)
+        if self.bias is not None:
+            part = part + self.bias.to(part.dtype)
+        return part
 
     def extra_repr(self) -> str:
-        return f"in_features={self.in_features}, out_features={self.out_features}, member {self.i} of a fused launch"
+        return f"in_features={self.in_features}, out_features={self.out_features}, member {self.index} of a fused launch"
 
 
-def _fusable(owner, names) -> str | None:
-    mods = [getattr(owner, a, None) for a in names]
-    if all(isinstance(m, QVBandLinearV8) for m in mods):
+def _kind_of_group(owner, names) -> str | None:
+    """'qvb8' / 'qvb8r' when every named child of `owner` is a packed linear of that format (qvb8r: loaded from a file,
+    which the fused tensor is rebuilt from), else None."""
+    children = [getattr(owner, a, None) for a in names]
+    if all(isinstance(c, QVBandLinearV8) for c in children):
         return "qvb8"
-    if all(isinstance(m, QVBandLinearV8R) and m.path for m in mods):
+    if all(isinstance(c, QVBandLinearV8R) and c.path for c in children):
         return "qvb8r"
     return None
+
+
+def _fuse_owner(owner, names, kind: str) -> None:
+    """Replace the children `names` of `owner` by members of one fused group (registered on the owner once)."""
+    old = [getattr(owner, a) for a in names]
+    shapes = [(c.in_features, c.out_features, c.bias) for c in old]
+    if kind == "qvb8":
+        group = FusedGroup.from_qvb8(old)
+    else:
+        device, files = old[0].words.device, [c.path for c in old]
+        for a in names:                                              # the separate device copies go before the fused one arrives
+            setattr(owner, a, None)
+        del old
+        if device.type == "cuda":
+            torch.cuda.empty_cache()
+        parsed = []
+        for f in files:
+            with open(f, "rb") as fh:
+                parsed.append(_packs.read_qvb8r(fh.read(), str(f)))
+        group = FusedGroup.from_qvb8r(parsed, device)
+    owner.add_module("_qvb8_fused", group)
+    for i, (a, (n_in, n_out, b)) in enumerate(zip(names, shapes)):
+        setattr(owner, a, FusedMember(group, i, in_features=n_in, out_features=n_out, bias=b))
 
 
 def fuse_same_input(model: nn.Module, groups=SAME_INPUT_GROUPS) -> int:
@@ -116,42 +146,17 @@ def fuse_same_input(model: nn.Module, groups=SAME_INPUT_GROUPS) -> int:
     of groups fused.  Called once after the packed modules are in place (the reference's loader calls its counterpart
     through the format's ``finalize`` hook).
 
-    Memory: the owners are collected first, and each group's separate modules are dropped before its fused module is
-    built, so at no time does the model exist twice on the device (QVB8R members are re-read from their files; QVB8
-    members' byte buffers are concatenated, which needs the group's bytes twice for a moment, not the model's)."""
-    todo = []
-    for parent in model.modules():
-        for sub, names in groups:
-            owner = getattr(parent, sub, None)
-            if owner is not None and _fusable(owner, names):
-                todo.append((owner, names))
-    done = 0
-    for owner, names in todo:
-        kind = _fusable(owner, names)
-        if kind is None:                                     # (an owner reachable twice was fused the first time)
-            continue
-        meta = [(getattr(owner, a).in_features, getattr(owner, a).out_features, getattr(owner, a).bias) for a in names]
-        if kind == "qvb8":
-            group = FusedGroup.from_qvb8([getattr(owner, a) for a in names])
-            for a in names:
-                setattr(owner, a, None)
-        else:
-            device = getattr(owner, names[0]).words.device
-            paths = [getattr(owner, a).path for a in names]
-            for a in names:                                  # the separate copies go before the fused one arrives
-                setattr(owner, a, None)
-            if device.type == "cuda":
-                torch.cuda.empty_cache()
-            parsed = []
-            for pth in paths:
-                with open(pth, "rb") as fh:
-                    parsed.append(_packs.read_qvb8r(fh.read(), str(pth)))
-            group = FusedGroup.from_qvb8r(parsed, device)
-            del parsed
-        owner.add_module("_qvb8_fused", group)
-        for i, (a, (n_in, n_out, bias)) in enumerate(zip(names, meta)):
-            setattr(owner, a, FusedMember(group, i, n_in, n_out, bias))
-        done += 1
-    if done and torch.cuda.is_available():
+    Memory: the owners are found first and fused one at a time, and a group's separate modules are dropped before (qvb8r:
+    re-read from their files) or right after (qvb8: byte buffers concatenated) its fused module is built, so at no time
+    does the model exist twice on the device -- one group's bytes do, for a moment."""
+    found = [(getattr(parent, sub), names) for parent in model.modules() for sub, names in groups
+             if getattr(parent, sub, None) is not None and _kind_of_group(getattr(parent, sub), names)]
+    fused = 0
+    for owner, names in found:
+        kind = _kind_of_group(owner, names)                   # (an owner reachable twice was fused the first time)
+        if kind is not None:
+            _fuse_owner(owner, names, kind)
+            fused += 1
+    if fused and torch.cuda.is_available():
         torch.cuda.empty_cache()
-    return done
+    return fused

@@ -26,7 +26,7 @@ class _Counting(nn.Module):
 def _group():
     W = torch.arange(6 * 4, dtype=torch.float32).reshape(6, 4)
     g = FusedGroup(_Counting(W), [2, 5])                         # members of 2, 3 and 1 rows
-    members = [FusedMember(g, i, 4, n, None) for i, n in enumerate((2, 3, 1))]
+    members = [FusedMember(g, i, in_features=4, out_features=n) for i, n in enumerate((2, 3, 1))]
     return W, g, members
 
 
@@ -59,7 +59,7 @@ def test_anything_but_the_same_unchanged_tensor_recomputes():
 
 def test_member_adds_its_own_bias():
     W, g, _ = _group()
-    m = FusedMember(g, 1, 4, 3, torch.tensor([1.0, 2.0, 3.0]))
+    m = FusedMember(g, 1, in_features=4, out_features=3, bias=torch.tensor([1.0, 2.0, 3.0]))
     x = torch.ones(1, 4)
     assert torch.equal(m(x), (x @ W.t())[:, 2:5] + torch.tensor([1.0, 2.0, 3.0]))
     assert "member 1" in m.extra_repr()
