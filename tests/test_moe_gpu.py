@@ -41,6 +41,20 @@ def test_stack_layout_cpu():
         experts.stack_packs([ups[0], bad])
 
 
+def test_expert_range_of_a_rank_cpu():
+    """a rank's module names its experts' place in the whole layer; ranges outside the layer are refused"""
+    ups, dns = _experts(4, 16, 64, 64, 8, (5, 7), seed=3)
+    whole = experts.QVBandExpertsV8(ups, dns, num_experts=4)
+    assert not whole.sharded and whole.first_expert == 0 and whole.total_experts == 4
+    part = experts.QVBandExpertsV8(ups[2:], dns[2:], num_experts=2, first_expert=2, total_experts=4)
+    assert part.sharded and part.up["min_s"].shape == (2, 16)
+    part.set_reduce(None)
+    with pytest.raises(ValueError):
+        experts.QVBandExpertsV8(ups[2:], dns[2:], num_experts=2, first_expert=3, total_experts=4)
+    with pytest.raises(ValueError):
+        experts.QVBandExpertsV8(ups, dns, num_experts=3)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("act", ["silu", "relu2"])
 @pytest.mark.parametrize("M,dtype", [(1, torch.bfloat16), (5, torch.float16), (19, torch.float32)])
